@@ -1,0 +1,199 @@
+"""Pins the CPU oracle against the reference's own golden vectors and known-answer tests.
+
+Golden vectors: fixtures/moe/*_layer0.{json,safetensors} and deepseek_block.* of the reference,
+re-packed by tests/golden/make_golden.py.  The reference asserts them in
+tests/moe_numerical_equivalence_test.rs:86-109 (gate max_abs < 0.5),
+tests/moe_hf_convention_test.rs:124-156 (< 1e-4 vs atenia_ref, < 1e-3 vs hf_ref) and
+tests/moe_deepseek_block_test.rs:41-74 (< 1e-3).  The bars here are far tighter.
+"""
+import os
+
+import numpy as np
+import pytest
+
+from oracle import oracle as orc
+
+
+def _load(golden_dir, name):
+    z = np.load(os.path.join(golden_dir, name + ".npz"))
+    return {k: z[k] for k in z.files}
+
+
+def _layer(g, renormalize, gated):
+    shared = None
+    if "shared_gate_proj" in g:
+        shared = [g["shared_gate_proj"], g["shared_up_proj"], g["shared_down_proj"]]
+    gate_vec = g.get("shared_gate_vec") if gated else None
+    return orc.OracleLayer(g["router"], g["gate"], g["up"], g["down"], int(g["top_k"]), renormalize,
+                           shared=shared, shared_gate_vec=gate_vec, shared_gated=gated)
+
+
+def _rel_l2(a, b):
+    a = a.astype(np.float64).ravel()
+    b = b.astype(np.float64).ravel()
+    return float(np.linalg.norm(a - b) / max(np.linalg.norm(b), 1e-300))
+
+
+LAYER0 = ["mixtral_layer0", "qwen15_moe_layer0", "qwen2_moe_layer0", "qwen3_moe_layer0"]
+
+
+@pytest.mark.parametrize("name", LAYER0)
+def test_atenia_convention_matches_atenia_ref(golden_dir, name):
+    g = _load(golden_dir, name)
+    out = _layer(g, renormalize=True, gated=False).forward(g["input"].astype(np.float32))
+    assert _rel_l2(out, g["atenia_ref"]) < 1e-6
+    assert np.max(np.abs(out - g["atenia_ref"])) < 1e-8
+
+
+@pytest.mark.parametrize("name", LAYER0)
+def test_hf_qwen_convention_matches_atenia_hf_ref(golden_dir, name):
+    g = _load(golden_dir, name)
+    gated = "shared_gate_vec" in g
+    # the fixture generator renormalises this variant only when the model sets norm_topk_prob
+    renorm = bool(g["norm_topk_prob"])
+    out = _layer(g, renormalize=renorm, gated=gated).forward(g["input"].astype(np.float32))
+    assert _rel_l2(out, g["atenia_hf_ref"]) < 1e-6
+
+
+@pytest.mark.parametrize("name", LAYER0)
+def test_family_convention_matches_hf_transformers(golden_dir, name):
+    """hf_ref is HuggingFace's own f64 output: renormalised iff norm_topk_prob (Mixtral always
+    renormalises), shared expert sigmoid-gated when the gate tensor exists."""
+    g = _load(golden_dir, name)
+    renorm = bool(g["norm_topk_prob"]) or name.startswith("mixtral")
+    gated = "shared_gate_vec" in g
+    out = _layer(g, renormalize=renorm, gated=gated).forward(g["input"].astype(np.float32))
+    assert np.max(np.abs(out - g["hf_ref"])) < 1e-6
+    assert int(np.argmax(out)) == int(np.argmax(g["hf_ref"]))
+
+
+def test_deepseek_block_is_non_renormalised_ungated(golden_dir):
+    g = _load(golden_dir, "deepseek_block")
+    out = _layer(g, renormalize=False, gated=False).forward(g["input"].astype(np.float32))
+    assert _rel_l2(out, g["mlp_output"]) < 1e-6
+    # the renormalised convention is measurably different on this fixture
+    out2 = _layer(g, renormalize=True, gated=False).forward(g["input"].astype(np.float32))
+    assert _rel_l2(out2, g["mlp_output"]) > 1e-2
+
+
+def test_f32_accumulation_stays_within_strict_tolerance(golden_dir):
+    g = _load(golden_dir, "mixtral_layer0")
+    lay = _layer(g, True, False)
+    a = lay.forward(g["input"].astype(np.float32), accum=orc.ACC_F64)
+    b = lay.forward(g["input"].astype(np.float32), accum=orc.ACC_F32)
+    assert np.max(np.abs(a - b)) < 1e-6
+
+
+# ---- known-answer tests restated from the reference's unit tests -------------------------------
+
+def test_top_k_selects_largest():  # src/moe/sparse.rs:294-297
+    rc, idx, _ = orc.top_k([0.1, 0.5, 0.2, 0.4], 2)
+    assert rc == 0 and idx.tolist() == [1, 3]
+
+
+def test_top_k_ties_pick_lower_index():  # src/moe/sparse.rs:300-304
+    rc, idx, _ = orc.top_k([0.25, 0.25, 0.25, 0.25], 2)
+    assert rc == 0 and idx.tolist() == [0, 1]
+
+
+def test_top_k_rejects_bad_k():  # src/moe/sparse.rs:307-317
+    assert orc.top_k([0.5, 0.5], 0)[0] == -1
+    assert orc.top_k([0.5, 0.5], 3)[0] == -2
+
+
+def test_top_k_renormalises():  # src/moe/sparse.rs:320-327
+    rc, idx, w = orc.top_k([0.1, 0.6, 0.3], 2)
+    assert rc == 0 and idx.tolist() == [1, 2]
+    assert abs(float(w.sum()) - 1.0) < 1e-6
+    assert abs(w[0] - 0.6 / 0.9) < 1e-5 and abs(w[1] - 0.3 / 0.9) < 1e-5
+    rc, idx, w = orc.top_k([0.1, 0.6, 0.3], 2, renormalize=False)
+    assert w.tolist() == [np.float32(0.6), np.float32(0.3)]
+
+
+def test_top_k_rejects_non_finite_and_negative():  # src/moe/sparse.rs:330-339
+    assert orc.top_k([0.5, float("nan"), 0.5], 2)[0] == -3
+    assert orc.top_k([0.5, -0.1], 1)[0] == -4
+
+
+def test_softmax_uniform_and_sums_to_one():  # src/moe/dense.rs:592-602, :457
+    w = orc.softmax([5.0, 5.0, 5.0, 5.0])
+    assert np.all(w == np.float32(0.25))
+    rng = np.random.default_rng(0)
+    w = orc.softmax(rng.normal(size=64).astype(np.float32))
+    assert abs(float(w.sum()) - 1.0) < 1e-6
+
+
+def test_combine_selected_is_weighted_sum():  # src/moe/sparse.rs:87-116
+    eo = np.arange(12, dtype=np.float32).reshape(3, 4)
+    rc, out = orc.combine_selected([0, 2], [0.25, 0.75], eo, 4)
+    assert rc == 0
+    np.testing.assert_array_equal(out, np.float32(0.25) * eo[0] + np.float32(0.75) * eo[2])
+    assert orc.combine_selected([3], [1.0], eo, 4)[0] == -1
+
+
+def test_int8_round_trip_bound_and_zero_row():  # src/tensor/disk_tier.rs:1310-1334
+    rng = np.random.default_rng(1)
+    w = rng.normal(0, 0.02, size=(16, 96)).astype(np.float32)
+    w[3] = 0.0
+    q, s = orc.quantize_per_row_i8(w)
+    assert s[3] == 1.0 and not q[3].any()
+    dq = orc.dequantize_per_row_i8(q, s)
+    assert np.all(np.abs(w - dq) <= s[:, None] / 2 + 1e-9)
+    assert q.min() >= -127 and q.max() <= 127
+    # one entry per row reaches +-127
+    assert np.all(np.abs(q[np.arange(16) != 3]).max(axis=1) == 127)
+
+
+def test_int8_layer_equals_f32_layer_on_dequantised_weights(golden_dir):
+    g = _load(golden_dir, "qwen2_moe_layer0")
+    E = g["gate"].shape[0]
+    qs = {k: [orc.quantize_per_row_i8(g[k][e]) for e in range(E)] for k in ("gate", "up", "down")}
+    sh = [orc.quantize_per_row_i8(g[k]) for k in ("shared_gate_proj", "shared_up_proj", "shared_down_proj")]
+    lay_q = orc.OracleLayer(g["router"], [p[0] for p in qs["gate"]], [p[0] for p in qs["up"]],
+                            [p[0] for p in qs["down"]], 2, True, shared=[p[0] for p in sh],
+                            scales={k: [p[1] for p in qs[k]] for k in qs},
+                            shared_scales=[p[1] for p in sh], shared_gated=False)
+    deq = {k: [orc.dequantize_per_row_i8(*p) for p in qs[k]] for k in qs}
+    lay_f = orc.OracleLayer(g["router"], deq["gate"], deq["up"], deq["down"], 2, True,
+                            shared=[orc.dequantize_per_row_i8(*p) for p in sh], shared_gated=False)
+    x = g["input"].astype(np.float32)
+    np.testing.assert_array_equal(lay_q.forward(x), lay_f.forward(x))
+
+
+def test_bf16_weights_decode_as_high_half():
+    rng = np.random.default_rng(2)
+    w = rng.normal(0, 0.02, size=(2, 8, 16)).astype(np.float32)
+    bits = (w.view(np.uint32) >> 16).astype(np.uint16)
+    back = (bits.astype(np.uint32) << 16).view(np.float32)
+    r = rng.normal(0, 0.02, size=(2, 16)).astype(np.float32)
+    dn = rng.normal(0, 0.02, size=(2, 16, 8)).astype(np.float32)
+    dbits = (dn.view(np.uint32) >> 16).astype(np.uint16)
+    dback = (dbits.astype(np.uint32) << 16).view(np.float32)
+    x = rng.normal(size=(3, 16)).astype(np.float32)
+    a = orc.OracleLayer(r, bits, bits, dbits, 1, True).forward(x)
+    b = orc.OracleLayer(r, back, back, dback, 1, True).forward(x)
+    np.testing.assert_array_equal(a, b)
+
+
+def test_dispatch_permutation_is_stable_counting_sort():
+    rng = np.random.default_rng(3)
+    T, k, E = 37, 3, 7
+    idx = np.stack([np.sort(rng.choice(E, size=k, replace=False)) for _ in range(T)]).astype(np.int32)
+    off, perm, inv = orc.dispatch_permutation(idx, E)
+    flat = idx.ravel()
+    want = np.argsort(flat, kind="stable").astype(np.int32)
+    np.testing.assert_array_equal(perm, want)
+    np.testing.assert_array_equal(inv[perm], np.arange(T * k))
+    np.testing.assert_array_equal(off, np.concatenate([[0], np.cumsum(np.bincount(flat, minlength=E))]))
+
+
+def test_batch_is_rowwise_and_thread_count_independent(golden_dir):
+    g = _load(golden_dir, "qwen15_moe_layer0")
+    lay = _layer(g, False, True)
+    rng = np.random.default_rng(4)
+    x = rng.normal(size=(9, lay.d)).astype(np.float32)
+    a = lay.forward(x, nthreads=1)
+    b = lay.forward(x, nthreads=4)
+    np.testing.assert_array_equal(a, b)
+    for t in range(9):
+        np.testing.assert_array_equal(a[t], lay.forward(x[t:t + 1])[0])
