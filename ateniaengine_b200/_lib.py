@@ -1,0 +1,105 @@
+"""ctypes loader for libatenia_moe.so (the C ABI declared in include/atenia_moe.h).
+
+There is no fallback: if the shared library is missing the import of any op raises.
+"""
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "csrc", "libatenia_moe.so")
+
+IO_BF16, IO_F32 = 0, 1
+W_BF16, W_INT8_ROW = 0, 1
+
+ERR_LAYER_NOT_FOUND = -5
+ERR_DIM_MISMATCH = -6
+
+
+class MoeConfig(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in (
+        "num_experts", "experts_per_token", "d_model", "d_ff", "shared_d_ff", "renormalize",
+        "shared_gated", "weight_dtype", "max_tokens", "ep_rank", "ep_world")]
+
+
+class MoeWeights(C.Structure):
+    _fields_ = [
+        ("w_router", C.c_void_p), ("router_bias", C.c_void_p),
+        ("w_gate", C.POINTER(C.c_void_p)), ("w_up", C.POINTER(C.c_void_p)), ("w_down", C.POINTER(C.c_void_p)),
+        ("s_gate", C.POINTER(C.c_void_p)), ("s_up", C.POINTER(C.c_void_p)), ("s_down", C.POINTER(C.c_void_p)),
+        ("shared_w_gate", C.c_void_p), ("shared_w_up", C.c_void_p), ("shared_w_down", C.c_void_p),
+        ("shared_s_gate", C.c_void_p), ("shared_s_up", C.c_void_p), ("shared_s_down", C.c_void_p),
+        ("shared_gate_vec", C.c_void_p),
+    ]
+
+
+class MoeAux(C.Structure):
+    _fields_ = [("topk_idx", C.c_void_p), ("topk_w", C.c_void_p), ("logits", C.c_void_p),
+                ("perm", C.c_void_p), ("expert_offsets", C.c_void_p)]
+
+
+class HostMoeLayer(C.Structure):
+    _fields_ = [
+        ("config", MoeConfig), ("w_router", C.c_void_p),
+        ("w_gate", C.POINTER(C.c_void_p)), ("w_up", C.POINTER(C.c_void_p)), ("w_down", C.POINTER(C.c_void_p)),
+        ("shared_w_gate", C.c_void_p), ("shared_w_up", C.c_void_p), ("shared_w_down", C.c_void_p),
+        ("shared_gate_vec", C.c_void_p),
+    ]
+
+
+EXPORTS = [
+    "atenia_moe_create", "atenia_moe_destroy", "atenia_moe_set_weights", "atenia_moe_forward",
+    "atenia_moe_forward_sync", "atenia_moe_check", "atenia_moe_route_from_logits",
+    "atenia_quantize_per_row_i8", "atenia_register_real_moe_layer", "atenia_execute_real_moe_layer",
+    "atenia_get_real_moe_layer", "atenia_moe_ep_unique_id_bytes", "atenia_moe_ep_get_unique_id",
+    "atenia_moe_ep_init", "atenia_moe_status_str", "atenia_moe_counter", "atenia_moe_enable_timing",
+    "atenia_moe_last_gemm_ms",
+]
+
+_lib = None
+
+
+class AteniaError(RuntimeError):
+    def __init__(self, status, where=""):
+        self.status = status
+        msg = lib().atenia_moe_status_str(C.c_int(status)).decode()
+        super().__init__(f"{where}: status {status}: {msg}")
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(
+                f"{LIB_PATH} is missing: build it with `python -c 'import __graft_entry__ as g; g.build()'` "
+                "(nvcc, sm_100a).  There is no CPU or PyTorch fallback for the MoE block.")
+        l = C.CDLL(LIB_PATH)
+        l.atenia_moe_status_str.restype = C.c_char_p
+        l.atenia_moe_counter.restype = C.c_uint64
+        l.atenia_register_real_moe_layer.restype = C.c_int64
+        l.atenia_get_real_moe_layer.restype = C.c_void_p
+        l.atenia_get_real_moe_layer.argtypes = [C.c_int64]
+        l.atenia_moe_last_gemm_ms.restype = C.c_float
+        l.atenia_moe_last_gemm_ms.argtypes = [C.c_void_p, C.c_int]
+        l.atenia_moe_enable_timing.argtypes = [C.c_void_p, C.c_int]
+        l.atenia_moe_create.argtypes = [C.POINTER(MoeConfig), C.POINTER(C.c_void_p)]
+        l.atenia_moe_destroy.argtypes = [C.c_void_p]
+        l.atenia_moe_set_weights.argtypes = [C.c_void_p, C.POINTER(MoeWeights)]
+        fwd = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_int, C.POINTER(MoeAux), C.c_void_p]
+        l.atenia_moe_forward.argtypes = fwd
+        l.atenia_moe_forward_sync.argtypes = fwd
+        l.atenia_moe_check.argtypes = [C.c_void_p, C.c_void_p]
+        l.atenia_moe_route_from_logits.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p,
+                                                   C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+        l.atenia_quantize_per_row_i8.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p,
+                                                 C.c_void_p]
+        l.atenia_register_real_moe_layer.argtypes = [C.POINTER(HostMoeLayer)]
+        l.atenia_execute_real_moe_layer.argtypes = [C.c_int64, C.c_void_p, C.c_size_t, C.c_void_p]
+        l.atenia_moe_ep_get_unique_id.argtypes = [C.c_void_p]
+        l.atenia_moe_ep_init.argtypes = [C.c_void_p, C.c_void_p]
+        _lib = l
+    return _lib
+
+
+def check(status, where=""):
+    if status != 0:
+        raise AteniaError(status, where)

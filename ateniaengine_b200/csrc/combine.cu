@@ -1,0 +1,140 @@
+// Combine: gate-weighted sum of a token's expert outputs back in token order, plus the shared expert.
+//
+// The reference accumulates out[d] += w * y_e[d] over the selected experts in ascending expert order
+// with an f32 multiply followed by an f32 add (src/moe/sparse.rs:227-233), then adds scale * shared
+// (src/moe/layer.rs:415-429).  The kernel gathers each token's k rows from the dispatch-ordered
+// buffer in slot order (slots are ascending experts) and repeats that arithmetic, so the result does
+// not depend on scheduling: no atomics.
+//
+// Also here: the small elementwise kernels of the library (int8 per-row quantiser, widening passes).
+#include "common.cuh"
+
+namespace atenia {
+namespace {
+
+__global__ void __launch_bounds__(256) combine_kernel(CombineArgs a) {
+  const int t = blockIdx.x;
+  const int nvec = a.d / 8;
+  int rows[8];
+  float w[8];
+  for (int s = 0; s < a.k; ++s) {
+    rows[s] = a.inv_perm[(size_t)t * a.k + s];
+    w[s] = a.topk_w[(size_t)t * a.k + s];
+  }
+  const float scale = a.gate_scale ? a.gate_scale[t] : 1.0f;
+  for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int s = 0; s < a.k; ++s) {
+      const uint4 y = *reinterpret_cast<const uint4*>(a.y_rows + (size_t)rows[s] * a.d + v * 8);
+      const uint32_t p[4] = {y.x, y.y, y.z, y.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        acc[2 * j] = __fadd_rn(acc[2 * j], __fmul_rn(w[s], bf16lo(p[j])));
+        acc[2 * j + 1] = __fadd_rn(acc[2 * j + 1], __fmul_rn(w[s], bf16hi(p[j])));
+      }
+    }
+    if (a.y_shared) {
+      const uint4 y = *reinterpret_cast<const uint4*>(a.y_shared + (size_t)t * a.d + v * 8);
+      const uint32_t p[4] = {y.x, y.y, y.z, y.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        acc[2 * j] = __fadd_rn(acc[2 * j], __fmul_rn(scale, bf16lo(p[j])));
+        acc[2 * j + 1] = __fadd_rn(acc[2 * j + 1], __fmul_rn(scale, bf16hi(p[j])));
+      }
+    }
+    if (a.out_is_f32) {
+      float4* o = reinterpret_cast<float4*>(static_cast<float*>(a.out) + (size_t)t * a.d + v * 8);
+      o[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+      o[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+    } else {
+      uint4* o = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(a.out) + (size_t)t * a.d + v * 8);
+      *o = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]),
+                      pack_bf16x2(acc[6], acc[7]));
+    }
+  }
+}
+
+// One block per row: scale = max|row| / 127 (1 for a zero row), q = clamp(round_half_away(w * (1/scale))).
+__global__ void __launch_bounds__(256) quantize_rows_kernel(const float* __restrict__ w, int64_t cols,
+                                                             int8_t* __restrict__ q, float* __restrict__ scales) {
+  __shared__ float red[8];
+  __shared__ float s_scale;
+  const int64_t r = blockIdx.x;
+  const float* row = w + r * cols;
+  float amax = 0.f;
+  for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) amax = fmaxf(amax, fabsf(row[c]));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float m = red[0];
+    for (int i = 1; i < (int)(blockDim.x >> 5); ++i) m = fmaxf(m, red[i]);
+    float sc = m > 0.f ? __fdiv_rn(m, 127.0f) : 1.0f;
+    s_scale = sc;
+    scales[r] = sc;
+  }
+  __syncthreads();
+  const float inv = __fdiv_rn(1.0f, s_scale);
+  for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) {
+    float v = roundf(__fmul_rn(row[c], inv));  // roundf: halves away from zero, like Rust's f32::round
+    v = fminf(fmaxf(v, -127.0f), 127.0f);
+    q[r * cols + c] = (int8_t)v;
+  }
+}
+
+__global__ void dequant_rows_kernel(const int8_t* __restrict__ q, const float* __restrict__ scales, int64_t rows,
+                                    int64_t cols, __nv_bfloat16* __restrict__ dst) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t n = rows * cols;
+  for (; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    float s = scales ? scales[i / cols] : 1.0f;
+    dst[i] = __float2bfloat16((float)q[i] * s);
+  }
+}
+
+__global__ void f32_to_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, int64_t n) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  for (; i < n; i += (int64_t)gridDim.x * blockDim.x) dst[i] = __float2bfloat16(src[i]);
+}
+
+}  // namespace
+
+int launch_combine(const CombineArgs& a, cudaStream_t s) {
+  if (a.T <= 0) return ATENIA_OK;
+  combine_kernel<<<a.T, 256, 0, s>>>(a);
+  count_launch();
+  return (int)cudaGetLastError();
+}
+
+int launch_dequant_rows(const int8_t* q, const float* scales, int64_t rows, int64_t cols, __nv_bfloat16* dst,
+                        cudaStream_t s) {
+  int64_t n = rows * cols;
+  if (n <= 0) return ATENIA_OK;
+  int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+  dequant_rows_kernel<<<blocks, 256, 0, s>>>(q, scales, rows, cols, dst);
+  count_launch();
+  return (int)cudaGetLastError();
+}
+
+int launch_f32_to_bf16(const float* src, __nv_bfloat16* dst, int64_t n, cudaStream_t s) {
+  if (n <= 0) return ATENIA_OK;
+  int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+  f32_to_bf16_kernel<<<blocks, 256, 0, s>>>(src, dst, n);
+  count_launch();
+  return (int)cudaGetLastError();
+}
+
+}  // namespace atenia
+
+extern "C" int atenia_quantize_per_row_i8(const float* w, int64_t rows, int64_t cols, int8_t* q, float* scales,
+                                          void* stream) {
+  if (!w || !q || !scales) return ATENIA_ERR_NULL;
+  if (rows < 0 || cols <= 0 || rows > 0x7fffffff) return ATENIA_ERR_SHAPE;
+  if (rows == 0) return ATENIA_OK;
+  atenia::quantize_rows_kernel<<<(unsigned)rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(w, cols, q, scales);
+  atenia::count_launch();
+  return (int)cudaGetLastError();
+}

@@ -1,0 +1,144 @@
+// Shared declarations of the MoE library's translation units (sm_100a only).
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/atenia_moe.h"
+
+namespace atenia {
+
+// Error word written by kernels (first error wins).  Values are the negative status codes of the
+// public header; a second word keeps a site id for diagnosis.
+struct DeviceError {
+  int32_t code;
+  int32_t site;
+};
+
+__device__ __forceinline__ void report_error(DeviceError* err, int code, int site) {
+  if (err && atomicCAS(&err->code, 0, code) == 0) err->site = site;
+}
+
+// ---- bf16 helpers ---------------------------------------------------------------------------
+__device__ __forceinline__ float bf16_bits_to_f32(uint32_t b) { return __uint_as_float(b << 16); }
+__device__ __forceinline__ float bf16lo(uint32_t packed) { return __uint_as_float(packed << 16); }
+__device__ __forceinline__ float bf16hi(uint32_t packed) { return __uint_as_float(packed & 0xffff0000u); }
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// ---- launch bookkeeping ---------------------------------------------------------------------
+void count_launch(int n = 1);
+void count_tcgen05_launch();
+void count_bytes(int which, uint64_t n);
+
+#define ATENIA_CUDA_TRY(expr)                \
+  do {                                       \
+    cudaError_t e__ = (expr);                \
+    if (e__ != cudaSuccess) return (int)e__; \
+  } while (0)
+
+// ---- router / routing ------------------------------------------------------------------------
+struct RouterArgs {
+  const void* x;          // [T, d] bf16 or f32
+  int x_is_f32;
+  const float* w_router;  // [E, d] f32
+  const float* bias;      // [E] or null
+  const float* gate_vec;  // [d] or null
+  int T, d, E, k, renormalize;
+  int32_t* topk_idx;   // [T, k]
+  float* topk_w;       // [T, k]
+  float* gate_scale;   // [T] or null
+  float* logits;       // [T, E] or null
+  DeviceError* err;
+};
+int launch_router(const RouterArgs& a, cudaStream_t s);
+int launch_route_from_logits(const float* logits, int T, int E, int k, int renormalize,
+                             int32_t* topk_idx, float* topk_w, DeviceError* err, cudaStream_t s);
+
+// ---- dispatch --------------------------------------------------------------------------------
+struct DispatchArgs {
+  const int32_t* topk_idx;  // [n] flat (t*k + s) -> expert
+  int n;                    // T * k
+  int E;
+  int32_t* block_counts;  // [nblk, E]
+  int32_t* block_base;    // [nblk, E]
+  int32_t* expert_offsets;  // [E + 1]
+  int32_t* perm;            // [n]
+  int32_t* inv_perm;        // [n]
+  int32_t* extra_offsets;   // [2] = {0, T} for the shared-expert group, or null
+  int T;
+  DeviceError* err;
+};
+constexpr int kDispatchChunk = 256;  // flat entries per block
+int launch_dispatch(const DispatchArgs& a, cudaStream_t s);
+
+// x_perm[r, :] = bf16(x[perm[r] / k, :]); optionally x_bf16 = bf16(x) when x is f32.
+int launch_gather_rows(const void* x, int x_is_f32, const int32_t* perm, int n_rows, int k, int d,
+                       __nv_bfloat16* x_perm, __nv_bfloat16* x_bf16, int T, cudaStream_t s);
+
+// ---- combine ---------------------------------------------------------------------------------
+struct CombineArgs {
+  const __nv_bfloat16* y_rows;  // [n, d] expert outputs in dispatch order
+  const int32_t* inv_perm;      // [T*k]
+  const float* topk_w;          // [T*k]
+  const __nv_bfloat16* y_shared;  // [T, d] or null
+  const float* gate_scale;        // [T] or null (null = 1.0)
+  void* out;
+  int out_is_f32;
+  int T, k, d;
+};
+int launch_combine(const CombineArgs& a, cudaStream_t s);
+
+// ---- grouped GEMM ----------------------------------------------------------------------------
+// One "group" is a contiguous block of rows of A multiplied by that group's own weight matrices.
+//   kSwiGLU: out[r, n] = silu(A[r,:].B0_g[n,:]) * (A[r,:].B1_g[n,:])      (gate / up, N = d_ff)
+//   kPlain:  out[r, n] = A[r,:].B0_g[n,:]                                   (down, N = d_model)
+// B matrices are row-major [N, K] (K contiguous): the reference's weight layout.
+enum GemmMode { kSwiGLU = 0, kPlain = 1 };
+
+struct GroupedGemmArgs {
+  CUtensorMap tmap_a;              // A [rows_cap, K] bf16, box {64, 128}, 128B swizzle
+  const CUtensorMap* tmap_b0;      // device array [num_groups]
+  const CUtensorMap* tmap_b1;      // device array [num_groups] (kSwiGLU only)
+  const int32_t* group_offsets;    // device [num_groups + 1] row offsets into A / out
+  int num_groups;
+  int N, K;
+  int mode;
+  __nv_bfloat16* out;  // [rows_cap, N]
+  // INT8 weights: per-group device pointers to f32 per-row scales (null for bf16)
+  const float* const* scale0;  // device array [num_groups] of device pointers
+  const float* const* scale1;
+  DeviceError* err;
+  int max_rows;  // upper bound on total rows (sizes nothing; used by the checking kernel's grid)
+};
+int launch_grouped_gemm_tcgen05(const GroupedGemmArgs& a, int num_sms, cudaStream_t s);
+
+// Plain CUDA-core version of the same contraction, reading the same buffers through ordinary
+// pointers.  Used by the test-suite to localise a fault; never selected by the forward path.
+struct GroupedGemmCheckArgs {
+  const __nv_bfloat16* a;  // [rows, K]
+  const void* const* b0;   // device array [num_groups] of device pointers to [N, K]
+  const void* const* b1;
+  int b_is_int8;
+  const float* const* scale0;
+  const float* const* scale1;
+  const int32_t* group_offsets;
+  int num_groups, N, K, mode;
+  __nv_bfloat16* out;
+  int max_rows;
+};
+int launch_grouped_gemm_check(const GroupedGemmCheckArgs& a, cudaStream_t s);
+
+// dst[r, c] = bf16((float)q[r, c] * scale[r])  -- widening pass used by the INT8 path
+int launch_dequant_rows(const int8_t* q, const float* scales, int64_t rows, int64_t cols,
+                        __nv_bfloat16* dst, cudaStream_t s);
+int launch_f32_to_bf16(const float* src, __nv_bfloat16* dst, int64_t n, cudaStream_t s);
+
+// Tensor-map encoding through the driver entry point (no link-time dependency on libcuda).
+int encode_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols,
+                        uint32_t box_rows, uint32_t box_cols);
+
+}  // namespace atenia

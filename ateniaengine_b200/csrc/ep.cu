@@ -1,0 +1,135 @@
+// Expert parallelism: experts sharded contiguously by id over the ranks of one node, rows exchanged
+// with NCCL point-to-point groups (an all-to-all with per-peer sizes) over NVLink.
+//
+// Per forward, on every rank:
+//   1. route the rank's own tokens over all E experts and sort its (token, slot) rows by expert
+//      (done by the caller); rows bound for one rank are then contiguous
+//   2. all-gather the per-expert row counts, read them on the host (the one host sync of the path)
+//   3. exchange rows: send each peer its slice, receive the peers' slices into recv_x, laid out
+//      [source rank][local expert][rows]
+//   4. run the local experts over recv_x with one GEMM group per (source rank, local expert)
+//   5. exchange the results back into y_perm, which has the caller's dispatch order again
+// The reference has no multi-GPU path; the result is defined by the single-GPU path: rows are the
+// same rows, experts the same experts, and the combine order is unchanged.
+#include <nccl.h>
+
+#include <vector>
+
+#include "layer.cuh"
+
+namespace atenia {
+namespace {
+
+__global__ void counts_kernel(const int32_t* __restrict__ off, int E, int32_t* __restrict__ counts) {
+  int e = blockIdx.x * blockDim.x + threadIdx.x;
+  if (e < E) counts[e] = off[e + 1] - off[e];
+}
+
+// group g = p * e_local + j covers the rows source rank p sent for local expert j
+__global__ void group_offsets_kernel(const int32_t* __restrict__ counts_all, int world, int E, int e_begin,
+                                     int e_local, int32_t* __restrict__ group_offsets) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  int run = 0;
+  for (int p = 0; p < world; ++p)
+    for (int j = 0; j < e_local; ++j) {
+      group_offsets[p * e_local + j] = run;
+      run += counts_all[p * E + e_begin + j];
+    }
+  group_offsets[world * e_local] = run;
+}
+
+#define NCCL_TRY(expr)                                 \
+  do {                                                 \
+    ncclResult_t r__ = (expr);                         \
+    if (r__ != ncclSuccess) return ATENIA_ERR_NCCL;    \
+  } while (0)
+
+int exchange(ncclComm_t comm, int rank, int world, const __nv_bfloat16* send, const std::vector<int64_t>& s_off,
+             const std::vector<int64_t>& s_cnt, __nv_bfloat16* recv, const std::vector<int64_t>& r_off,
+             const std::vector<int64_t>& r_cnt, int d, cudaStream_t s) {
+  if (s_cnt[rank] > 0)
+    ATENIA_CUDA_TRY(cudaMemcpyAsync(recv + r_off[rank] * d, send + s_off[rank] * d,
+                                    (size_t)s_cnt[rank] * d * sizeof(__nv_bfloat16), cudaMemcpyDeviceToDevice, s));
+  NCCL_TRY(ncclGroupStart());
+  for (int p = 0; p < world; ++p) {
+    if (p == rank) continue;
+    if (s_cnt[p] > 0) NCCL_TRY(ncclSend(send + s_off[p] * d, (size_t)s_cnt[p] * d, ncclBfloat16, p, comm, s));
+    if (r_cnt[p] > 0) NCCL_TRY(ncclRecv(recv + r_off[p] * d, (size_t)r_cnt[p] * d, ncclBfloat16, p, comm, s));
+  }
+  NCCL_TRY(ncclGroupEnd());
+  return ATENIA_OK;
+}
+
+}  // namespace
+
+int ep_forward_exchange(AteniaMoeLayer* L, int T, cudaStream_t s) {
+  (void)T;
+  const AteniaMoeConfig& c = L->cfg;
+  const int G = c.ep_world, E = c.num_experts, El = L->e_local, rank = c.ep_rank, d = c.d_model;
+  ncclComm_t comm = reinterpret_cast<ncclComm_t>(L->comm);
+  counts_kernel<<<1, 128, 0, s>>>(L->expert_offsets, E, L->d_counts_all + (size_t)rank * E);
+  count_launch();
+  NCCL_TRY(ncclAllGather(L->d_counts_all + (size_t)rank * E, L->d_counts_all, (size_t)E, ncclInt32, comm, s));
+  ATENIA_CUDA_TRY(cudaMemcpyAsync(L->h_counts_all, L->d_counts_all, (size_t)G * E * sizeof(int32_t),
+                                  cudaMemcpyDeviceToHost, s));
+  group_offsets_kernel<<<1, 32, 0, s>>>(L->d_counts_all, G, E, L->e_begin, El, L->d_group_offsets);
+  count_launch();
+  ATENIA_CUDA_TRY(cudaStreamSynchronize(s));
+  std::vector<int64_t> s_off(G), s_cnt(G), r_off(G), r_cnt(G);
+  int64_t so = 0, ro = 0;
+  for (int p = 0; p < G; ++p) {
+    int64_t sc = 0, rc = 0;
+    for (int j = 0; j < El; ++j) {
+      sc += L->h_counts_all[(size_t)rank * E + p * El + j];
+      rc += L->h_counts_all[(size_t)p * E + L->e_begin + j];
+    }
+    s_off[p] = so;
+    s_cnt[p] = sc;
+    r_off[p] = ro;
+    r_cnt[p] = rc;
+    so += sc;
+    ro += rc;
+  }
+  if (ro > L->recv_cap) return ATENIA_ERR_CAPACITY;
+  int rc = exchange(comm, rank, G, L->x_perm, s_off, s_cnt, L->recv_x, r_off, r_cnt, d, s);
+  if (rc) return rc;
+  rc = run_expert_gemms(L, L->tm_recv_x, L->tm_recv_h, L->recv_x, L->recv_h, L->recv_y, L->d_group_offsets,
+                        L->n_groups, (int)ro, s);
+  if (rc) return rc;
+  return exchange(comm, rank, G, L->recv_y, r_off, r_cnt, L->y_perm, s_off, s_cnt, d, s);
+}
+
+void ep_destroy(AteniaMoeLayer* L) {
+  if (L->comm) {
+    ncclCommDestroy(reinterpret_cast<ncclComm_t>(L->comm));
+    L->comm = nullptr;
+  }
+}
+
+}  // namespace atenia
+
+extern "C" {
+
+int atenia_moe_ep_unique_id_bytes(void) { return (int)sizeof(ncclUniqueId); }
+
+int atenia_moe_ep_get_unique_id(void* id_out) {
+  if (!id_out) return ATENIA_ERR_NULL;
+  ncclUniqueId id;
+  if (ncclGetUniqueId(&id) != ncclSuccess) return ATENIA_ERR_NCCL;
+  memcpy(id_out, &id, sizeof(id));
+  return ATENIA_OK;
+}
+
+int atenia_moe_ep_init(AteniaMoeLayer* L, const void* unique_id) {
+  if (!L || !unique_id) return ATENIA_ERR_NULL;
+  if (L->cfg.ep_world <= 1) return ATENIA_ERR_STATE;
+  if (L->comm) return ATENIA_OK;
+  ncclUniqueId id;
+  memcpy(&id, unique_id, sizeof(id));
+  ncclComm_t comm = nullptr;
+  if (ncclCommInitRank(&comm, L->cfg.ep_world, id, L->cfg.ep_rank) != ncclSuccess) return ATENIA_ERR_NCCL;
+  L->comm = reinterpret_cast<ncclComm*>(comm);
+  return ATENIA_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,528 @@
+// Grouped expert GEMM for sm_100a: TMA-fed tcgen05.mma with TMEM accumulators.
+//
+// One launch covers every expert of a layer.  A persistent grid (one CTA per SM) walks a tile list
+// derived on the device from the dispatch offsets, so the host never reads routing results.
+//
+//   tile            = 128 rows of one expert  x  BN_OUT output columns
+//   kSwiGLU         : B tile = 128 rows of W_gate || 128 rows of W_up  -> one M128 x N256 MMA,
+//                     epilogue h = silu(g) * u, BN_OUT = 128
+//   kPlain          : B tile = 256 rows of W_down                       -> one M128 x N256 MMA,
+//                     BN_OUT = 256
+//   k-block         = 64 bf16 (128 bytes: exactly one 128B-swizzle row), 4 MMAs of K = 16
+//
+// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM allocator + MMA issuer,
+// warps 2..5 = epilogue (each owns the 32 TMEM lanes its warp id modulo 4 selects).
+// The accumulator is double buffered (2 x 256 TMEM columns), so the epilogue of tile i overlaps the
+// main loop of tile i+1.
+//
+// Every wait is bounded: a wait that runs out records ATENIA_ERR_DEVICE_TIMEOUT with a site id and
+// the CTA leaves its loops, waits (bounded) for its own TMA copies, frees TMEM and returns.
+#include "common.cuh"
+
+namespace atenia {
+namespace {
+
+constexpr int BM = 128;
+constexpr int BN = 256;  // MMA N
+constexpr int BK = 64;
+constexpr int UMMA_K = 16;
+constexpr int STAGES = 4;
+constexpr int ACC_BUFS = 2;
+constexpr int TMEM_COLS = 512;
+constexpr int A_STAGE_BYTES = BM * BK * 2;      // 16 KiB
+constexpr int B_STAGE_BYTES = BN * BK * 2;      // 32 KiB
+constexpr int B_HALF_BYTES = B_STAGE_BYTES / 2; // 16 KiB
+constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int NUM_THREADS = 192;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+
+constexpr uint32_t kSpinLimit = 1u << 26;  // iterations of a try_wait loop before giving up
+
+// ---- PTX wrappers ----------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+// Bounded wait.  Returns false when the limit ran out or another role already gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          uint32_t limit = kSpinLimit) {
+  for (uint32_t i = 0; i < limit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 1023u) == 1023u && *abort_flag) return false;
+  }
+  return false;
+}
+__device__ __forceinline__ void fence_barrier_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void tmap_acquire(const CUtensorMap* m) {
+  // A tensor map that lives in global memory and was written by the host is made visible to the
+  // tensor-map proxy of this CTA before its first use.
+  asm volatile("fence.proxy.tensormap::generic.acquire.sys [%0], 128;" ::"l"(reinterpret_cast<uint64_t>(m))
+               : "memory");
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x,
+                                            int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void tc_mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows of 128 bytes, eight-row
+// groups 1024 bytes apart.  Bits: [0,14) address>>4, [16,30) leading offset>>4 (unused with a
+// swizzled K-major tile, set to 1), [32,46) stride offset>>4, [46,48) version = 1, [61,64) swizzle
+// mode (2 = 128B).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr >> 4) & 0x3FFF);
+  d |= static_cast<uint64_t>(1) << 16;
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(2) << 61;
+  return d;
+}
+// Instruction descriptor, kind::f16: D = f32 (bit 4), A = B = bf16 (bits 7, 10), both K-major,
+// N >> 3 at bit 17, M >> 4 at bit 24.
+constexpr uint32_t kInstrDesc = (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(BN >> 3) << 17) |
+                                (uint32_t(BM >> 4) << 24);
+
+// ---- tile walk ---------------------------------------------------------------------------------
+struct TileCursor {
+  int group;      // current group
+  int base;       // first tile index of the current group
+  int m_tiles;    // m tiles of the current group
+  int row_begin;  // first row of the group
+  int row_end;
+};
+struct TileCoord {
+  int group, row0, row_end, n0;
+};
+
+__device__ __forceinline__ void cursor_load(TileCursor& c, const int32_t* __restrict__ off) {
+  c.row_begin = off[c.group];
+  c.row_end = off[c.group + 1];
+  c.m_tiles = (c.row_end - c.row_begin + BM - 1) / BM;
+}
+// Advance the cursor to the group holding `tile`; false when the tile list is exhausted.
+__device__ __forceinline__ bool cursor_seek(TileCursor& c, int tile, int n_tiles, int num_groups,
+                                            const int32_t* __restrict__ off, TileCoord& out, int bn_out) {
+  while (c.group < num_groups) {
+    int tiles_here = c.m_tiles * n_tiles;
+    if (tile < c.base + tiles_here) {
+      int local = tile - c.base;
+      int nt = local / c.m_tiles;  // n-major, m-minor: neighbouring CTAs share a weight tile
+      int mt = local - nt * c.m_tiles;
+      out.group = c.group;
+      out.row0 = c.row_begin + mt * BM;
+      out.row_end = c.row_end;
+      out.n0 = nt * bn_out;
+      return true;
+    }
+    c.base += tiles_here;
+    c.group += 1;
+    if (c.group < num_groups) cursor_load(c, off);
+  }
+  return false;
+}
+
+struct __align__(8) SharedBarriers {
+  uint64_t full[STAGES];
+  uint64_t empty[STAGES];
+  uint64_t acc_full[ACC_BUFS];
+  uint64_t acc_empty[ACC_BUFS];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+__device__ __forceinline__ float silu_mul(float g, float u) {
+  // silu(g) * u = g * u / (1 + exp(-g))
+  return __fdividef(g * u, 1.0f + __expf(-g));
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const CUtensorMap* __restrict__ tmap_b0,
+                            const CUtensorMap* __restrict__ tmap_b1, const int32_t* __restrict__ group_offsets,
+                            int num_groups, int N, int K, __nv_bfloat16* __restrict__ out,
+                            const float* const* __restrict__ scale0, const float* const* __restrict__ scale1,
+                            DeviceError* err) {
+  extern __shared__ uint8_t smem_raw[];
+  constexpr int BN_OUT = (MODE == kSwiGLU) ? BN / 2 : BN;
+  // 1024-byte alignment is required by the 128B swizzle atoms.
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
+  SharedBarriers* bars = reinterpret_cast<SharedBarriers*>(smem_aligned + STAGES * STAGE_BYTES);
+  volatile int* abort_flag = &bars->abort_flag;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_kb = (K + BK - 1) / BK;
+  const int n_tiles = (N + BN_OUT - 1) / BN_OUT;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(smem_u32(&bars->full[s]), 1);
+      mbar_init(smem_u32(&bars->empty[s]), 1);
+    }
+    for (int b = 0; b < ACC_BUFS; ++b) {
+      mbar_init(smem_u32(&bars->acc_full[b]), 1);
+      mbar_init(smem_u32(&bars->acc_empty[b]), 4);
+    }
+    bars->abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(&bars->tmem_base)),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  TileCursor cur;
+  cur.group = 0;
+  cur.base = 0;
+  if (num_groups > 0) cursor_load(cur, group_offsets);
+  TileCoord tc;
+
+  if (warp == 0) {
+    // ================= TMA producer =================
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int last_group = -1;
+      uint32_t armed = 0;  // stages with a copy possibly in flight
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && cursor_seek(cur, tile, n_tiles, num_groups, group_offsets, tc, BN_OUT);
+           tile += gridDim.x) {
+        if (tc.group != last_group) {
+          tmap_acquire(&tmap_b0[tc.group]);
+          if (MODE == kSwiGLU) tmap_acquire(&tmap_b1[tc.group]);
+          last_group = tc.group;
+        }
+        const CUtensorMap* mb0 = &tmap_b0[tc.group];
+        const CUtensorMap* mb1 = (MODE == kSwiGLU) ? &tmap_b1[tc.group] : mb0;
+        const int n1 = (MODE == kSwiGLU) ? tc.n0 : tc.n0 + BN / 2;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(smem_u32(&bars->empty[stage]), phase ^ 1u, abort_flag)) {
+            report_error(err, ATENIA_ERR_DEVICE_TIMEOUT, 100 + stage);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          const uint32_t full = smem_u32(&bars->full[stage]);
+          const uint32_t sa = smem_base + stage * STAGE_BYTES;
+          const uint32_t sb = sa + A_STAGE_BYTES;
+          mbar_expect_tx(full, STAGE_BYTES);
+          tma_load_2d(sa, &tmap_a, full, kb * BK, tc.row0);
+          tma_load_2d(sb, mb0, full, kb * BK, tc.n0);
+          tma_load_2d(sb + B_HALF_BYTES, mb1, full, kb * BK, n1);
+          armed |= 1u << stage;
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      if (*abort_flag) {
+        // Let copies already issued land before the CTA's shared memory is released.
+        for (int s = 0; s < STAGES; ++s) {
+          if (!(armed & (1u << s))) continue;
+          uint32_t par = (s < stage) ? phase : (phase ^ 1u);
+          mbar_wait(smem_u32(&bars->full[s]), par, abort_flag + 0 * s, 1u << 20);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ================= MMA issuer =================
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t acc_phase[ACC_BUFS] = {0, 0};
+      int it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && cursor_seek(cur, tile, n_tiles, num_groups, group_offsets, tc, BN_OUT);
+           tile += gridDim.x, ++it) {
+        const int acc = it & 1;
+        if (!mbar_wait(smem_u32(&bars->acc_empty[acc]), acc_phase[acc] ^ 1u, abort_flag)) {
+          report_error(err, ATENIA_ERR_DEVICE_TIMEOUT, 200 + acc);
+          *abort_flag = 1;
+          break;
+        }
+        acc_phase[acc] ^= 1u;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(smem_u32(&bars->full[stage]), phase, abort_flag)) {
+            report_error(err, ATENIA_ERR_DEVICE_TIMEOUT, 300 + stage);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_base + stage * STAGE_BYTES;
+          const uint32_t sb = sa + A_STAGE_BYTES;
+          const uint64_t da = make_smem_desc(sa);
+          const uint64_t db = make_smem_desc(sb);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            // advancing 16 bf16 = 32 bytes along K inside the swizzle row: +2 in address>>4 units
+            tc_mma_bf16(d_tmem, da + 2 * k, db + 2 * k, kInstrDesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          tc_commit(smem_u32(&bars->empty[stage]));  // frees the stage once these MMAs have read it
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (ok) tc_commit(smem_u32(&bars->acc_full[acc]));
+      }
+    }
+  } else {
+    // ================= epilogue (warps 2..5) =================
+    const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter + 32) belong to this warp
+    const int row_in_tile = quarter * 32 + lane;
+    uint32_t acc_phase[ACC_BUFS] = {0, 0};
+    int it = 0;
+    for (int tile = blockIdx.x; cursor_seek(cur, tile, n_tiles, num_groups, group_offsets, tc, BN_OUT);
+         tile += gridDim.x, ++it) {
+      const int acc = it & 1;
+      if (!mbar_wait(smem_u32(&bars->acc_full[acc]), acc_phase[acc], abort_flag)) {
+        if (lane == 0) report_error(err, ATENIA_ERR_DEVICE_TIMEOUT, 400 + acc);
+        *abort_flag = 1;
+        break;
+      }
+      acc_phase[acc] ^= 1u;
+      tc_fence_after();
+      const int grow = tc.row0 + row_in_tile;
+      const bool row_ok = grow < tc.row_end;
+      const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN;
+      __nv_bfloat16* orow = out + (size_t)grow * N;
+      const float* sc0 = scale0 ? scale0[tc.group] : nullptr;
+      const float* sc1 = (scale1 && MODE == kSwiGLU) ? scale1[tc.group] : nullptr;
+      if (MODE == kSwiGLU) {
+#pragma unroll 1
+        for (int c = 0; c < BN_OUT; c += 16) {
+          uint32_t g[16], u[16];
+          tc_ld16(taddr + c, g);
+          tc_ld16(taddr + BN_OUT + c, u);
+          tc_ld_wait();
+          const int n = tc.n0 + c;
+          if (row_ok && n < N) {
+            uint32_t p[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              float g0 = __uint_as_float(g[2 * j]), g1 = __uint_as_float(g[2 * j + 1]);
+              float u0 = __uint_as_float(u[2 * j]), u1 = __uint_as_float(u[2 * j + 1]);
+              if (sc0) {
+                g0 *= sc0[n + 2 * j];
+                g1 *= sc0[n + 2 * j + 1];
+                u0 *= sc1[n + 2 * j];
+                u1 *= sc1[n + 2 * j + 1];
+              }
+              p[j] = pack_bf16x2(silu_mul(g0, u0), silu_mul(g1, u1));
+            }
+            uint4* dst = reinterpret_cast<uint4*>(orow + n);
+            dst[0] = make_uint4(p[0], p[1], p[2], p[3]);
+            dst[1] = make_uint4(p[4], p[5], p[6], p[7]);
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < BN_OUT; c += 16) {
+          uint32_t v[16];
+          tc_ld16(taddr + c, v);
+          tc_ld_wait();
+          const int n = tc.n0 + c;
+          if (row_ok && n < N) {
+            uint32_t p[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              float a0 = __uint_as_float(v[2 * j]), a1 = __uint_as_float(v[2 * j + 1]);
+              if (sc0) {
+                a0 *= sc0[n + 2 * j];
+                a1 *= sc0[n + 2 * j + 1];
+              }
+              p[j] = pack_bf16x2(a0, a1);
+            }
+            uint4* dst = reinterpret_cast<uint4*>(orow + n);
+            dst[0] = make_uint4(p[0], p[1], p[2], p[3]);
+            dst[1] = make_uint4(p[4], p[5], p[6], p[7]);
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bars->acc_empty[acc]));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS)
+                 : "memory");
+  }
+}
+
+// ---- CUDA-core checking kernel ----------------------------------------------------------------
+__global__ void grouped_gemm_check_kernel(GroupedGemmCheckArgs a) {
+  const int n = blockIdx.x * blockDim.x + threadIdx.x;
+  const int row = blockIdx.y;
+  if (n >= a.N) return;
+  const int total = a.group_offsets[a.num_groups];
+  if (row >= total) return;
+  int g = 0;
+  while (g + 1 < a.num_groups && row >= a.group_offsets[g + 1]) ++g;
+  const __nv_bfloat16* x = a.a + (size_t)row * a.K;
+  float acc0 = 0.f, acc1 = 0.f;
+  if (a.b_is_int8) {
+    const int8_t* w0 = static_cast<const int8_t*>(a.b0[g]) + (size_t)n * a.K;
+    const int8_t* w1 = a.mode == kSwiGLU ? static_cast<const int8_t*>(a.b1[g]) + (size_t)n * a.K : nullptr;
+    for (int k = 0; k < a.K; ++k) {
+      float xv = __bfloat162float(x[k]);
+      acc0 = fmaf(xv, (float)w0[k], acc0);
+      if (w1) acc1 = fmaf(xv, (float)w1[k], acc1);
+    }
+  } else {
+    const __nv_bfloat16* w0 = static_cast<const __nv_bfloat16*>(a.b0[g]) + (size_t)n * a.K;
+    const __nv_bfloat16* w1 =
+        a.mode == kSwiGLU ? static_cast<const __nv_bfloat16*>(a.b1[g]) + (size_t)n * a.K : nullptr;
+    for (int k = 0; k < a.K; ++k) {
+      float xv = __bfloat162float(x[k]);
+      acc0 = fmaf(xv, __bfloat162float(w0[k]), acc0);
+      if (w1) acc1 = fmaf(xv, __bfloat162float(w1[k]), acc1);
+    }
+  }
+  if (a.scale0) {
+    acc0 *= a.scale0[g][n];
+    if (a.mode == kSwiGLU) acc1 *= a.scale1[g][n];
+  }
+  float r = a.mode == kSwiGLU ? acc0 / (1.0f + expf(-acc0)) * acc1 : acc0;
+  a.out[(size_t)row * a.N + n] = __float2bfloat16(r);
+}
+
+}  // namespace
+
+int launch_grouped_gemm_tcgen05(const GroupedGemmArgs& a, int num_sms, cudaStream_t s) {
+  if (a.num_groups <= 0) return ATENIA_OK;
+  if (a.N % 16 != 0 || a.K % 16 != 0) return ATENIA_ERR_SHAPE;
+  static bool attr_set = false;
+  if (!attr_set) {
+    ATENIA_CUDA_TRY(cudaFuncSetAttribute(grouped_gemm_tcgen05_kernel<kSwiGLU>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    ATENIA_CUDA_TRY(cudaFuncSetAttribute(grouped_gemm_tcgen05_kernel<kPlain>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    attr_set = true;
+  }
+  dim3 grid(num_sms), block(NUM_THREADS);
+  if (a.mode == kSwiGLU) {
+    grouped_gemm_tcgen05_kernel<kSwiGLU><<<grid, block, SMEM_BYTES, s>>>(
+        a.tmap_a, a.tmap_b0, a.tmap_b1, a.group_offsets, a.num_groups, a.N, a.K, a.out, a.scale0, a.scale1,
+        a.err);
+  } else {
+    grouped_gemm_tcgen05_kernel<kPlain><<<grid, block, SMEM_BYTES, s>>>(
+        a.tmap_a, a.tmap_b0, a.tmap_b0, a.group_offsets, a.num_groups, a.N, a.K, a.out, a.scale0, a.scale1,
+        a.err);
+  }
+  count_launch();
+  count_tcgen05_launch();
+  return (int)cudaGetLastError();
+}
+
+int launch_grouped_gemm_check(const GroupedGemmCheckArgs& a, cudaStream_t s) {
+  if (a.num_groups <= 0 || a.max_rows <= 0) return ATENIA_OK;
+  dim3 block(128), grid((a.N + 127) / 128, a.max_rows);
+  grouped_gemm_check_kernel<<<grid, block, 0, s>>>(a);
+  count_launch();
+  return (int)cudaGetLastError();
+}
+
+// ---- tensor maps --------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+  }
+  return fn;
+}
+
+int encode_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
+                        uint32_t box_cols) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return ATENIA_ERR_DRIVER;
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0 || (cols * 2) % 16 != 0) return ATENIA_ERR_SHAPE;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {cols * 2};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? ATENIA_OK : ATENIA_ERR_DRIVER;
+}
+
+}  // namespace atenia

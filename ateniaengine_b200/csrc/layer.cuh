@@ -1,0 +1,81 @@
+// Internal definition of AteniaMoeLayer (shared by moe_layer.cu, ep.cu, registry.cu).
+#pragma once
+#include <vector>
+
+#include "common.cuh"
+
+struct ncclComm;
+
+struct AteniaMoeLayer {
+  AteniaMoeConfig cfg{};
+  int device = 0;
+  int num_sms = 0;
+  int e_local = 0;   // experts owned by this rank
+  int e_begin = 0;   // first owned expert id
+  int n_groups = 0;  // GEMM groups per launch: e_local (single GPU) or ep_world * e_local
+  bool weights_set = false;
+  bool use_check_gemm = false;  // diagnostic: CUDA-core contraction instead of tcgen05
+  bool timing = false;
+
+  // weights (device)
+  float* d_router = nullptr;    // [E, d]
+  float* d_bias = nullptr;      // [E]
+  float* d_gate_vec = nullptr;  // [d]
+  bool has_bias = false, has_gate_vec = false, has_shared = false;
+  CUtensorMap* d_tm_gate = nullptr;  // [n_groups]
+  CUtensorMap* d_tm_up = nullptr;
+  CUtensorMap* d_tm_down = nullptr;
+  CUtensorMap* d_tm_shared = nullptr;  // [3]: gate, up, down
+  const float** d_sc_gate = nullptr;   // [n_groups] device pointers (INT8) or null
+  const float** d_sc_up = nullptr;
+  const float** d_sc_down = nullptr;
+  const float** d_sc_shared = nullptr;  // [3]
+  const void** d_p_gate = nullptr;      // [n_groups] raw matrix pointers (checking kernel)
+  const void** d_p_up = nullptr;
+  const void** d_p_down = nullptr;
+  const void** d_p_shared = nullptr;  // [3]
+  std::vector<void*> owned;           // device buffers this layer allocated for weights
+
+  // workspace (device), sized by cfg.max_tokens
+  int rows_cap = 0;  // rows of the dispatch-ordered buffers
+  int32_t* topk_idx = nullptr;
+  float* topk_w = nullptr;
+  float* gate_scale = nullptr;
+  int32_t* perm = nullptr;
+  int32_t* inv_perm = nullptr;
+  int32_t* expert_offsets = nullptr;  // [E + 1]
+  int32_t* shared_offsets = nullptr;  // [2]
+  int32_t* block_counts = nullptr;
+  int32_t* block_base = nullptr;
+  __nv_bfloat16* x_perm = nullptr;  // [rows_cap, d]
+  __nv_bfloat16* h = nullptr;       // [rows_cap, F]
+  __nv_bfloat16* y_perm = nullptr;  // [rows_cap, d]
+  __nv_bfloat16* x_bf16 = nullptr;  // [max_tokens, d]
+  __nv_bfloat16* h_shared = nullptr;  // [max_tokens, Fs]
+  __nv_bfloat16* y_shared = nullptr;  // [max_tokens, d]
+  atenia::DeviceError* d_err = nullptr;
+  CUtensorMap tm_x_perm{}, tm_h{}, tm_h_shared{};
+
+  // expert parallelism
+  ncclComm* comm = nullptr;
+  int recv_cap = 0;                    // rows of the receive-side buffers
+  __nv_bfloat16* recv_x = nullptr;     // [recv_cap, d]
+  __nv_bfloat16* recv_h = nullptr;     // [recv_cap, F]
+  __nv_bfloat16* recv_y = nullptr;     // [recv_cap, d]
+  int32_t* d_counts_all = nullptr;     // [world, E] rows per (source rank, expert)
+  int32_t* h_counts_all = nullptr;     // pinned host copy
+  int32_t* d_group_offsets = nullptr;  // [world * e_local + 1]
+  CUtensorMap tm_recv_x{}, tm_recv_h{};
+
+  // timing
+  cudaEvent_t ev[8] = {};
+  bool ev_valid[4] = {false, false, false, false};
+};
+
+namespace atenia {
+int ep_forward_exchange(AteniaMoeLayer* L, int T, cudaStream_t s);  // ep.cu
+void ep_destroy(AteniaMoeLayer* L);
+int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorMap& tm_mid,
+                     const __nv_bfloat16* a_ptr, __nv_bfloat16* mid, __nv_bfloat16* out,
+                     const int32_t* group_offsets, int num_groups, int max_rows, cudaStream_t s);
+}  // namespace atenia

@@ -1,0 +1,587 @@
+// C ABI of the MoE block: layer life cycle, weight binding, the forward pass.
+#include <atomic>
+#include <cstdlib>
+#include <cstring>
+#include <new>
+
+#include "layer.cuh"
+
+namespace atenia {
+
+static std::atomic<uint64_t> g_counters[8];
+
+void count_launch(int n) { g_counters[ATENIA_COUNTER_KERNEL_LAUNCHES] += (uint64_t)n; }
+void count_tcgen05_launch() { g_counters[ATENIA_COUNTER_TCGEN05_LAUNCHES] += 1; }
+void count_bytes(int which, uint64_t n) { g_counters[which] += n; }
+
+namespace {
+
+template <typename T>
+int dev_alloc(T** p, size_t count) {
+  *p = nullptr;
+  if (count == 0) return ATENIA_OK;
+  return (int)cudaMalloc(reinterpret_cast<void**>(p), count * sizeof(T));
+}
+
+int validate_config(const AteniaMoeConfig& c) {
+  if (c.num_experts < 1 || c.num_experts > 128) return ATENIA_ERR_SHAPE;
+  if (c.experts_per_token < 1 || c.experts_per_token > 8 || c.experts_per_token > c.num_experts)
+    return ATENIA_ERR_SHAPE;
+  if (c.d_model < 16 || c.d_model % 16 || c.d_ff < 16 || c.d_ff % 16) return ATENIA_ERR_SHAPE;
+  if (c.shared_d_ff < 0 || c.shared_d_ff % 16) return ATENIA_ERR_SHAPE;
+  if (c.weight_dtype != ATENIA_W_BF16 && c.weight_dtype != ATENIA_W_INT8_ROW) return ATENIA_ERR_SHAPE;
+  if (c.max_tokens < 1) return ATENIA_ERR_SHAPE;
+  if (c.ep_world != 1 && c.ep_world != 2 && c.ep_world != 4 && c.ep_world != 8) return ATENIA_ERR_SHAPE;
+  if (c.ep_rank < 0 || c.ep_rank >= c.ep_world || c.num_experts % c.ep_world) return ATENIA_ERR_SHAPE;
+  if ((int64_t)c.max_tokens * c.experts_per_token * c.ep_world > (int64_t)1 << 30) return ATENIA_ERR_SHAPE;
+  return ATENIA_OK;
+}
+
+}  // namespace
+
+int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorMap& tm_mid,
+                     const __nv_bfloat16* a_ptr, __nv_bfloat16* mid, __nv_bfloat16* out,
+                     const int32_t* group_offsets, int num_groups, int max_rows, cudaStream_t s) {
+  const AteniaMoeConfig& c = L->cfg;
+  const bool q = c.weight_dtype == ATENIA_W_INT8_ROW;
+  if (L->timing) cudaEventRecord(L->ev[0], s);
+  if (L->use_check_gemm) {
+    GroupedGemmCheckArgs k1{a_ptr, L->d_p_gate, L->d_p_up, 0, q ? L->d_sc_gate : nullptr,
+                            q ? L->d_sc_up : nullptr, group_offsets, num_groups, c.d_ff, c.d_model,
+                            kSwiGLU, mid, max_rows};
+    int rc = launch_grouped_gemm_check(k1, s);
+    if (rc) return rc;
+  } else {
+    GroupedGemmArgs g1{};
+    g1.tmap_a = tm_a;
+    g1.tmap_b0 = L->d_tm_gate;
+    g1.tmap_b1 = L->d_tm_up;
+    g1.group_offsets = group_offsets;
+    g1.num_groups = num_groups;
+    g1.N = c.d_ff;
+    g1.K = c.d_model;
+    g1.mode = kSwiGLU;
+    g1.out = mid;
+    g1.scale0 = q ? L->d_sc_gate : nullptr;
+    g1.scale1 = q ? L->d_sc_up : nullptr;
+    g1.err = L->d_err;
+    g1.max_rows = max_rows;
+    int rc = launch_grouped_gemm_tcgen05(g1, L->num_sms, s);
+    if (rc) return rc;
+  }
+  if (L->timing) cudaEventRecord(L->ev[1], s);
+  if (L->use_check_gemm) {
+    GroupedGemmCheckArgs k2{mid, L->d_p_down, nullptr, 0, q ? L->d_sc_down : nullptr, nullptr,
+                            group_offsets, num_groups, c.d_model, c.d_ff, kPlain, out, max_rows};
+    int rc = launch_grouped_gemm_check(k2, s);
+    if (rc) return rc;
+  } else {
+    GroupedGemmArgs g2{};
+    g2.tmap_a = tm_mid;
+    g2.tmap_b0 = L->d_tm_down;
+    g2.tmap_b1 = L->d_tm_down;
+    g2.group_offsets = group_offsets;
+    g2.num_groups = num_groups;
+    g2.N = c.d_model;
+    g2.K = c.d_ff;
+    g2.mode = kPlain;
+    g2.out = out;
+    g2.scale0 = q ? L->d_sc_down : nullptr;
+    g2.scale1 = nullptr;
+    g2.err = L->d_err;
+    g2.max_rows = max_rows;
+    int rc = launch_grouped_gemm_tcgen05(g2, L->num_sms, s);
+    if (rc) return rc;
+  }
+  if (L->timing) {
+    cudaEventRecord(L->ev[2], s);
+    L->ev_valid[0] = L->ev_valid[1] = true;
+  }
+  return ATENIA_OK;
+}
+
+namespace {
+
+int run_shared_gemms(AteniaMoeLayer* L, const __nv_bfloat16* xb, int T, cudaStream_t s) {
+  const AteniaMoeConfig& c = L->cfg;
+  const bool q = c.weight_dtype == ATENIA_W_INT8_ROW;
+  if (L->timing) cudaEventRecord(L->ev[3], s);
+  if (L->use_check_gemm) {
+    GroupedGemmCheckArgs k1{xb, L->d_p_shared, L->d_p_shared + 1, 0, q ? L->d_sc_shared : nullptr,
+                            q ? L->d_sc_shared + 1 : nullptr, L->shared_offsets, 1, c.shared_d_ff, c.d_model,
+                            kSwiGLU, L->h_shared, T};
+    int rc = launch_grouped_gemm_check(k1, s);
+    if (rc) return rc;
+    GroupedGemmCheckArgs k2{L->h_shared, L->d_p_shared + 2, nullptr, 0, q ? L->d_sc_shared + 2 : nullptr,
+                            nullptr, L->shared_offsets, 1, c.d_model, c.shared_d_ff, kPlain, L->y_shared, T};
+    rc = launch_grouped_gemm_check(k2, s);
+    if (rc) return rc;
+    return ATENIA_OK;
+  }
+  GroupedGemmArgs g1{};
+  int rc = encode_tmap_2d_bf16(&g1.tmap_a, xb, (uint64_t)T, (uint64_t)c.d_model, 128, 64);
+  if (rc) return rc;
+  g1.tmap_b0 = L->d_tm_shared;
+  g1.tmap_b1 = L->d_tm_shared + 1;
+  g1.group_offsets = L->shared_offsets;
+  g1.num_groups = 1;
+  g1.N = c.shared_d_ff;
+  g1.K = c.d_model;
+  g1.mode = kSwiGLU;
+  g1.out = L->h_shared;
+  g1.scale0 = q ? L->d_sc_shared : nullptr;
+  g1.scale1 = q ? L->d_sc_shared + 1 : nullptr;
+  g1.err = L->d_err;
+  g1.max_rows = T;
+  rc = launch_grouped_gemm_tcgen05(g1, L->num_sms, s);
+  if (rc) return rc;
+  if (L->timing) cudaEventRecord(L->ev[4], s);
+  GroupedGemmArgs g2{};
+  g2.tmap_a = L->tm_h_shared;
+  g2.tmap_b0 = L->d_tm_shared + 2;
+  g2.tmap_b1 = L->d_tm_shared + 2;
+  g2.group_offsets = L->shared_offsets;
+  g2.num_groups = 1;
+  g2.N = c.d_model;
+  g2.K = c.shared_d_ff;
+  g2.mode = kPlain;
+  g2.out = L->y_shared;
+  g2.scale0 = q ? L->d_sc_shared + 2 : nullptr;
+  g2.err = L->d_err;
+  g2.max_rows = T;
+  rc = launch_grouped_gemm_tcgen05(g2, L->num_sms, s);
+  if (rc) return rc;
+  if (L->timing) {
+    cudaEventRecord(L->ev[5], s);
+    L->ev_valid[2] = L->ev_valid[3] = true;
+  }
+  return ATENIA_OK;
+}
+
+}  // namespace
+}  // namespace atenia
+
+using namespace atenia;
+
+extern "C" {
+
+int atenia_moe_create(const AteniaMoeConfig* cfg, AteniaMoeLayer** out) {
+  if (!cfg || !out) return ATENIA_ERR_NULL;
+  *out = nullptr;
+  int rc = validate_config(*cfg);
+  if (rc) return rc;
+  AteniaMoeLayer* L = new (std::nothrow) AteniaMoeLayer();
+  if (!L) return (int)cudaErrorMemoryAllocation;
+  L->cfg = *cfg;
+  const AteniaMoeConfig& c = L->cfg;
+  cudaError_t e = cudaGetDevice(&L->device);
+  if (e == cudaSuccess) e = cudaDeviceGetAttribute(&L->num_sms, cudaDevAttrMultiProcessorCount, L->device);
+  if (e != cudaSuccess) {
+    delete L;
+    return (int)e;
+  }
+  L->e_local = c.num_experts / c.ep_world;
+  L->e_begin = c.ep_rank * L->e_local;
+  L->n_groups = c.ep_world == 1 ? L->e_local : c.ep_world * L->e_local;
+  L->has_shared = c.shared_d_ff > 0;
+  L->use_check_gemm = std::getenv("ATENIA_MOE_CHECK_GEMM") && std::atoi(std::getenv("ATENIA_MOE_CHECK_GEMM")) != 0;
+  const size_t Tm = (size_t)c.max_tokens, k = (size_t)c.experts_per_token, E = (size_t)c.num_experts;
+  const size_t d = (size_t)c.d_model, F = (size_t)c.d_ff, Fs = (size_t)c.shared_d_ff;
+  const size_t R = Tm * k;
+  L->rows_cap = (int)R;
+  const size_t nblk = (R + kDispatchChunk - 1) / kDispatchChunk;
+#define TRY_ALLOC(ptr, n)                  \
+  do {                                     \
+    rc = dev_alloc(&(ptr), (n));           \
+    if (rc) {                              \
+      atenia_moe_destroy(L);               \
+      return rc;                           \
+    }                                      \
+  } while (0)
+  TRY_ALLOC(L->d_router, E * d);
+  TRY_ALLOC(L->d_bias, E);
+  TRY_ALLOC(L->d_gate_vec, d);
+  TRY_ALLOC(L->topk_idx, R);
+  TRY_ALLOC(L->topk_w, R);
+  TRY_ALLOC(L->gate_scale, Tm);
+  TRY_ALLOC(L->perm, R);
+  TRY_ALLOC(L->inv_perm, R);
+  TRY_ALLOC(L->expert_offsets, E + 1);
+  TRY_ALLOC(L->shared_offsets, 2);
+  TRY_ALLOC(L->block_counts, nblk * E);
+  TRY_ALLOC(L->block_base, nblk * E);
+  TRY_ALLOC(L->x_perm, R * d);
+  TRY_ALLOC(L->y_perm, R * d);
+  if (c.ep_world == 1) TRY_ALLOC(L->h, R * F);
+  TRY_ALLOC(L->x_bf16, Tm * d);
+  if (L->has_shared) {
+    TRY_ALLOC(L->h_shared, Tm * Fs);
+    TRY_ALLOC(L->y_shared, Tm * d);
+  }
+  TRY_ALLOC(L->d_err, 1);
+  TRY_ALLOC(L->d_tm_gate, (size_t)L->n_groups);
+  TRY_ALLOC(L->d_tm_up, (size_t)L->n_groups);
+  TRY_ALLOC(L->d_tm_down, (size_t)L->n_groups);
+  TRY_ALLOC(L->d_tm_shared, 3);
+  TRY_ALLOC(L->d_sc_gate, (size_t)L->n_groups);
+  TRY_ALLOC(L->d_sc_up, (size_t)L->n_groups);
+  TRY_ALLOC(L->d_sc_down, (size_t)L->n_groups);
+  TRY_ALLOC(L->d_sc_shared, 3);
+  TRY_ALLOC(L->d_p_gate, (size_t)L->n_groups);
+  TRY_ALLOC(L->d_p_up, (size_t)L->n_groups);
+  TRY_ALLOC(L->d_p_down, (size_t)L->n_groups);
+  TRY_ALLOC(L->d_p_shared, 3);
+  if (c.ep_world > 1) {
+    // Worst case every token of every rank selects only experts of this rank.
+    const size_t RC = R * (size_t)c.ep_world;
+    L->recv_cap = (int)RC;
+    TRY_ALLOC(L->recv_x, RC * d);
+    TRY_ALLOC(L->recv_h, RC * F);
+    TRY_ALLOC(L->recv_y, RC * d);
+    TRY_ALLOC(L->d_counts_all, (size_t)c.ep_world * E);
+    TRY_ALLOC(L->d_group_offsets, (size_t)L->n_groups + 1);
+    e = cudaMallocHost(reinterpret_cast<void**>(&L->h_counts_all), (size_t)c.ep_world * E * sizeof(int32_t));
+    if (e != cudaSuccess) {
+      atenia_moe_destroy(L);
+      return (int)e;
+    }
+  }
+#undef TRY_ALLOC
+  e = cudaMemset(L->d_err, 0, sizeof(DeviceError));
+  if (e == cudaSuccess) e = cudaMemset(L->perm, 0, R * sizeof(int32_t));
+  if (e == cudaSuccess) e = cudaMemset(L->inv_perm, 0, R * sizeof(int32_t));
+  if (e != cudaSuccess) {
+    atenia_moe_destroy(L);
+    return (int)e;
+  }
+  rc = encode_tmap_2d_bf16(&L->tm_x_perm, L->x_perm, R, d, 128, 64);
+  if (!rc && L->h) rc = encode_tmap_2d_bf16(&L->tm_h, L->h, R, F, 128, 64);
+  if (!rc && L->has_shared) rc = encode_tmap_2d_bf16(&L->tm_h_shared, L->h_shared, Tm, Fs, 128, 64);
+  if (!rc && c.ep_world > 1) {
+    rc = encode_tmap_2d_bf16(&L->tm_recv_x, L->recv_x, (uint64_t)L->recv_cap, d, 128, 64);
+    if (!rc) rc = encode_tmap_2d_bf16(&L->tm_recv_h, L->recv_h, (uint64_t)L->recv_cap, F, 128, 64);
+  }
+  if (rc) {
+    atenia_moe_destroy(L);
+    return rc;
+  }
+  for (int i = 0; i < 8; ++i) cudaEventCreate(&L->ev[i]);
+  *out = L;
+  return ATENIA_OK;
+}
+
+int atenia_moe_destroy(AteniaMoeLayer* L) {
+  if (!L) return ATENIA_OK;
+  cudaDeviceSynchronize();
+  ep_destroy(L);
+  void* ptrs[] = {L->d_router,   L->d_bias,      L->d_gate_vec,  L->topk_idx,       L->topk_w,
+                  L->gate_scale, L->perm,        L->inv_perm,    L->expert_offsets, L->shared_offsets,
+                  L->block_counts, L->block_base, L->x_perm,     L->h,              L->y_perm,
+                  L->x_bf16,     L->h_shared,    L->y_shared,    L->d_err,          L->d_tm_gate,
+                  L->d_tm_up,    L->d_tm_down,   L->d_tm_shared, L->d_sc_gate,      L->d_sc_up,
+                  L->d_sc_down,  L->d_sc_shared, L->d_p_gate,    L->d_p_up,         L->d_p_down,
+                  L->d_p_shared, L->recv_x,      L->recv_h,      L->recv_y,         L->d_counts_all,
+                  L->d_group_offsets};
+  for (void* p : ptrs)
+    if (p) cudaFree(p);
+  for (void* p : L->owned) cudaFree(p);
+  if (L->h_counts_all) cudaFreeHost(L->h_counts_all);
+  for (int i = 0; i < 8; ++i)
+    if (L->ev[i]) cudaEventDestroy(L->ev[i]);
+  delete L;
+  return ATENIA_OK;
+}
+
+int atenia_moe_set_weights(AteniaMoeLayer* L, const AteniaMoeWeights* w) {
+  if (!L || !w || !w->w_router || !w->w_gate || !w->w_up || !w->w_down) return ATENIA_ERR_NULL;
+  const AteniaMoeConfig& c = L->cfg;
+  const bool q = c.weight_dtype == ATENIA_W_INT8_ROW;
+  if (q && (!w->s_gate || !w->s_up || !w->s_down)) return ATENIA_ERR_NULL;
+  if (L->has_shared && (!w->shared_w_gate || !w->shared_w_up || !w->shared_w_down)) return ATENIA_ERR_NULL;
+  if (L->has_shared && q && (!w->shared_s_gate || !w->shared_s_up || !w->shared_s_down)) return ATENIA_ERR_NULL;
+  if (c.shared_gated && L->has_shared && !w->shared_gate_vec) return ATENIA_ERR_NULL;
+  const size_t d = (size_t)c.d_model, F = (size_t)c.d_ff, Fs = (size_t)c.shared_d_ff, E = (size_t)c.num_experts;
+  for (void* p : L->owned) cudaFree(p);
+  L->owned.clear();
+  L->weights_set = false;
+
+  ATENIA_CUDA_TRY(cudaMemcpy(L->d_router, w->w_router, E * d * sizeof(float), cudaMemcpyDeviceToDevice));
+  L->has_bias = w->router_bias != nullptr;
+  if (L->has_bias)
+    ATENIA_CUDA_TRY(cudaMemcpy(L->d_bias, w->router_bias, E * sizeof(float), cudaMemcpyDeviceToDevice));
+  L->has_gate_vec = w->shared_gate_vec != nullptr && c.shared_gated && L->has_shared;
+  if (L->has_gate_vec)
+    ATENIA_CUDA_TRY(cudaMemcpy(L->d_gate_vec, w->shared_gate_vec, d * sizeof(float), cudaMemcpyDeviceToDevice));
+
+  // INT8: the tensor-core kernel consumes bf16 operands.  The int8 codes (|q| <= 127, exact in bf16)
+  // are widened once into library-owned bf16 matrices and the per-row scale multiplies the f32
+  // accumulator column in the epilogue, which is the exact factorisation of (q * scale) . x.
+  auto operand = [&](const void* src, size_t rows, size_t cols, const void** out_ptr) -> int {
+    if (!src) return ATENIA_ERR_NULL;
+    if (!q) {
+      *out_ptr = src;
+      return ATENIA_OK;
+    }
+    __nv_bfloat16* wide = nullptr;
+    ATENIA_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&wide), rows * cols * sizeof(__nv_bfloat16)));
+    L->owned.push_back(wide);
+    int rc2 = launch_dequant_rows(static_cast<const int8_t*>(src), nullptr, (int64_t)rows, (int64_t)cols, wide, 0);
+    *out_ptr = wide;
+    return rc2;
+  };
+
+  const int G = L->n_groups, El = L->e_local;
+  std::vector<CUtensorMap> tg(G), tu(G), td(G);
+  std::vector<const void*> pg(G), pu(G), pd(G);
+  std::vector<const float*> sg(G, nullptr), su(G, nullptr), sd(G, nullptr);
+  for (int e = 0; e < El; ++e) {
+    int rc = operand(w->w_gate[e], F, d, &pg[e]);
+    if (!rc) rc = operand(w->w_up[e], F, d, &pu[e]);
+    if (!rc) rc = operand(w->w_down[e], d, F, &pd[e]);
+    if (!rc) rc = encode_tmap_2d_bf16(&tg[e], pg[e], F, d, 128, 64);
+    if (!rc) rc = encode_tmap_2d_bf16(&tu[e], pu[e], F, d, 128, 64);
+    if (!rc) rc = encode_tmap_2d_bf16(&td[e], pd[e], d, F, 128, 64);
+    if (rc) return rc;
+    if (q) {
+      if (!w->s_gate[e] || !w->s_up[e] || !w->s_down[e]) return ATENIA_ERR_NULL;
+      sg[e] = w->s_gate[e];
+      su[e] = w->s_up[e];
+      sd[e] = w->s_down[e];
+    }
+  }
+  // Under expert parallelism the groups are (source rank, local expert) pairs: replicate.
+  for (int g = El; g < G; ++g) {
+    tg[g] = tg[g % El];
+    tu[g] = tu[g % El];
+    td[g] = td[g % El];
+    pg[g] = pg[g % El];
+    pu[g] = pu[g % El];
+    pd[g] = pd[g % El];
+    sg[g] = sg[g % El];
+    su[g] = su[g % El];
+    sd[g] = sd[g % El];
+  }
+  const size_t mb = (size_t)G * sizeof(CUtensorMap), pb = (size_t)G * sizeof(void*);
+  ATENIA_CUDA_TRY(cudaMemcpy(L->d_tm_gate, tg.data(), mb, cudaMemcpyHostToDevice));
+  ATENIA_CUDA_TRY(cudaMemcpy(L->d_tm_up, tu.data(), mb, cudaMemcpyHostToDevice));
+  ATENIA_CUDA_TRY(cudaMemcpy(L->d_tm_down, td.data(), mb, cudaMemcpyHostToDevice));
+  ATENIA_CUDA_TRY(cudaMemcpy(L->d_p_gate, pg.data(), pb, cudaMemcpyHostToDevice));
+  ATENIA_CUDA_TRY(cudaMemcpy(L->d_p_up, pu.data(), pb, cudaMemcpyHostToDevice));
+  ATENIA_CUDA_TRY(cudaMemcpy(L->d_p_down, pd.data(), pb, cudaMemcpyHostToDevice));
+  ATENIA_CUDA_TRY(cudaMemcpy(L->d_sc_gate, sg.data(), pb, cudaMemcpyHostToDevice));
+  ATENIA_CUDA_TRY(cudaMemcpy(L->d_sc_up, su.data(), pb, cudaMemcpyHostToDevice));
+  ATENIA_CUDA_TRY(cudaMemcpy(L->d_sc_down, sd.data(), pb, cudaMemcpyHostToDevice));
+  if (L->has_shared) {
+    CUtensorMap ts[3];
+    const void* ps[3];
+    const float* ss[3] = {q ? w->shared_s_gate : nullptr, q ? w->shared_s_up : nullptr,
+                          q ? w->shared_s_down : nullptr};
+    int rc = operand(w->shared_w_gate, Fs, d, &ps[0]);
+    if (!rc) rc = operand(w->shared_w_up, Fs, d, &ps[1]);
+    if (!rc) rc = operand(w->shared_w_down, d, Fs, &ps[2]);
+    if (!rc) rc = encode_tmap_2d_bf16(&ts[0], ps[0], Fs, d, 128, 64);
+    if (!rc) rc = encode_tmap_2d_bf16(&ts[1], ps[1], Fs, d, 128, 64);
+    if (!rc) rc = encode_tmap_2d_bf16(&ts[2], ps[2], d, Fs, 128, 64);
+    if (rc) return rc;
+    ATENIA_CUDA_TRY(cudaMemcpy(L->d_tm_shared, ts, sizeof(ts), cudaMemcpyHostToDevice));
+    ATENIA_CUDA_TRY(cudaMemcpy(L->d_p_shared, ps, sizeof(ps), cudaMemcpyHostToDevice));
+    ATENIA_CUDA_TRY(cudaMemcpy(L->d_sc_shared, ss, sizeof(ss), cudaMemcpyHostToDevice));
+  }
+  ATENIA_CUDA_TRY(cudaDeviceSynchronize());
+  L->weights_set = true;
+  return ATENIA_OK;
+}
+
+int atenia_moe_forward(AteniaMoeLayer* L, const void* x, int x_dtype, int T, void* out, int out_dtype,
+                       const AteniaMoeAux* aux, void* stream) {
+  if (!L || !x || !out) return ATENIA_ERR_NULL;
+  if (!L->weights_set) return ATENIA_ERR_STATE;
+  if (T < 0) return ATENIA_ERR_SHAPE;
+  if (T > L->cfg.max_tokens) return ATENIA_ERR_CAPACITY;
+  if ((x_dtype != ATENIA_IO_BF16 && x_dtype != ATENIA_IO_F32) ||
+      (out_dtype != ATENIA_IO_BF16 && out_dtype != ATENIA_IO_F32))
+    return ATENIA_ERR_SHAPE;
+  if (L->cfg.ep_world > 1 && !L->comm) return ATENIA_ERR_STATE;
+  g_counters[ATENIA_COUNTER_FORWARD_CALLS] += 1;
+  if (T == 0 && L->cfg.ep_world == 1) return ATENIA_OK;
+  const AteniaMoeConfig& c = L->cfg;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int k = c.experts_per_token, n = T * k;
+  const bool x_f32 = x_dtype == ATENIA_IO_F32;
+
+  RouterArgs ra{};
+  ra.x = x;
+  ra.x_is_f32 = x_f32;
+  ra.w_router = L->d_router;
+  ra.bias = L->has_bias ? L->d_bias : nullptr;
+  ra.gate_vec = L->has_gate_vec ? L->d_gate_vec : nullptr;
+  ra.T = T;
+  ra.d = c.d_model;
+  ra.E = c.num_experts;
+  ra.k = k;
+  ra.renormalize = c.renormalize;
+  ra.topk_idx = L->topk_idx;
+  ra.topk_w = L->topk_w;
+  ra.gate_scale = L->has_gate_vec ? L->gate_scale : nullptr;
+  ra.logits = aux ? aux->logits : nullptr;
+  ra.err = L->d_err;
+  int rc = launch_router(ra, s);
+  if (rc) return rc;
+
+  DispatchArgs da{};
+  da.topk_idx = L->topk_idx;
+  da.n = n;
+  da.E = c.num_experts;
+  da.block_counts = L->block_counts;
+  da.block_base = L->block_base;
+  da.expert_offsets = L->expert_offsets;
+  da.perm = L->perm;
+  da.inv_perm = L->inv_perm;
+  da.extra_offsets = L->shared_offsets;
+  da.T = T;
+  da.err = L->d_err;
+  rc = launch_dispatch(da, s);
+  if (rc) return rc;
+
+  const bool need_xb = x_f32 && L->has_shared;
+  rc = launch_gather_rows(x, x_f32, L->perm, n, k, c.d_model, L->x_perm, need_xb ? L->x_bf16 : nullptr, T, s);
+  if (rc) return rc;
+
+  if (c.ep_world == 1) {
+    rc = run_expert_gemms(L, L->tm_x_perm, L->tm_h, L->x_perm, L->h, L->y_perm, L->expert_offsets,
+                          c.num_experts, n, s);
+  } else {
+    rc = ep_forward_exchange(L, T, s);
+  }
+  if (rc) return rc;
+
+  if (L->has_shared && T > 0) {
+    const __nv_bfloat16* xb = x_f32 ? L->x_bf16 : static_cast<const __nv_bfloat16*>(x);
+    rc = run_shared_gemms(L, xb, T, s);
+    if (rc) return rc;
+  }
+
+  CombineArgs ca{};
+  ca.y_rows = L->y_perm;
+  ca.inv_perm = L->inv_perm;
+  ca.topk_w = L->topk_w;
+  ca.y_shared = L->has_shared ? L->y_shared : nullptr;
+  ca.gate_scale = L->has_gate_vec ? L->gate_scale : nullptr;
+  ca.out = out;
+  ca.out_is_f32 = out_dtype == ATENIA_IO_F32;
+  ca.T = T;
+  ca.k = k;
+  ca.d = c.d_model;
+  rc = launch_combine(ca, s);
+  if (rc) return rc;
+
+  if (aux) {
+    if (aux->topk_idx)
+      ATENIA_CUDA_TRY(cudaMemcpyAsync(aux->topk_idx, L->topk_idx, (size_t)n * 4, cudaMemcpyDeviceToDevice, s));
+    if (aux->topk_w)
+      ATENIA_CUDA_TRY(cudaMemcpyAsync(aux->topk_w, L->topk_w, (size_t)n * 4, cudaMemcpyDeviceToDevice, s));
+    if (aux->perm) ATENIA_CUDA_TRY(cudaMemcpyAsync(aux->perm, L->perm, (size_t)n * 4, cudaMemcpyDeviceToDevice, s));
+    if (aux->expert_offsets)
+      ATENIA_CUDA_TRY(cudaMemcpyAsync(aux->expert_offsets, L->expert_offsets, (size_t)(c.num_experts + 1) * 4,
+                                      cudaMemcpyDeviceToDevice, s));
+  }
+  return ATENIA_OK;
+}
+
+int atenia_moe_check(AteniaMoeLayer* L, void* stream) {
+  if (!L) return ATENIA_ERR_NULL;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  ATENIA_CUDA_TRY(cudaStreamSynchronize(s));
+  DeviceError he{};
+  ATENIA_CUDA_TRY(cudaMemcpy(&he, L->d_err, sizeof(he), cudaMemcpyDeviceToHost));
+  if (he.code != 0) {
+    ATENIA_CUDA_TRY(cudaMemset(L->d_err, 0, sizeof(DeviceError)));
+    return he.code;
+  }
+  return ATENIA_OK;
+}
+
+int atenia_moe_forward_sync(AteniaMoeLayer* L, const void* x, int x_dtype, int T, void* out, int out_dtype,
+                            const AteniaMoeAux* aux, void* stream) {
+  int rc = atenia_moe_forward(L, x, x_dtype, T, out, out_dtype, aux, stream);
+  if (rc) return rc;
+  return atenia_moe_check(L, stream);
+}
+
+int atenia_moe_route_from_logits(AteniaMoeLayer* L, const float* logits, int T, int32_t* topk_idx, float* topk_w,
+                                 int32_t* perm, int32_t* inv_perm, int32_t* expert_offsets, void* stream) {
+  if (!L || !logits || !topk_idx || !topk_w) return ATENIA_ERR_NULL;
+  if (T < 0) return ATENIA_ERR_SHAPE;
+  if (T > L->cfg.max_tokens) return ATENIA_ERR_CAPACITY;
+  if (T == 0) return ATENIA_OK;
+  const AteniaMoeConfig& c = L->cfg;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int rc = launch_route_from_logits(logits, T, c.num_experts, c.experts_per_token, c.renormalize, topk_idx, topk_w,
+                                    L->d_err, s);
+  if (rc) return rc;
+  if (perm || inv_perm || expert_offsets) {
+    const int n = T * c.experts_per_token;
+    DispatchArgs da{};
+    da.topk_idx = topk_idx;
+    da.n = n;
+    da.E = c.num_experts;
+    da.block_counts = L->block_counts;
+    da.block_base = L->block_base;
+    da.expert_offsets = L->expert_offsets;
+    da.perm = L->perm;
+    da.inv_perm = L->inv_perm;
+    da.extra_offsets = nullptr;
+    da.T = T;
+    da.err = L->d_err;
+    rc = launch_dispatch(da, s);
+    if (rc) return rc;
+    if (perm) ATENIA_CUDA_TRY(cudaMemcpyAsync(perm, L->perm, (size_t)n * 4, cudaMemcpyDeviceToDevice, s));
+    if (inv_perm) ATENIA_CUDA_TRY(cudaMemcpyAsync(inv_perm, L->inv_perm, (size_t)n * 4, cudaMemcpyDeviceToDevice, s));
+    if (expert_offsets)
+      ATENIA_CUDA_TRY(cudaMemcpyAsync(expert_offsets, L->expert_offsets, (size_t)(c.num_experts + 1) * 4,
+                                      cudaMemcpyDeviceToDevice, s));
+  }
+  return ATENIA_OK;
+}
+
+const char* atenia_moe_status_str(int status) {
+  switch (status) {
+    case ATENIA_OK: return "ok";
+    case ATENIA_ERR_NULL: return "a required pointer is NULL";
+    case ATENIA_ERR_SHAPE: return "sizes violate a stated constraint";
+    case ATENIA_ERR_CAPACITY: return "more tokens than the layer's max_tokens";
+    case ATENIA_ERR_STATE: return "layer not ready (weights or expert-parallel group not set)";
+    case ATENIA_ERR_LAYER_NOT_FOUND: return "moe layer id not found";
+    case ATENIA_ERR_DIM_MISMATCH: return "input length is not a positive multiple of d_model";
+    case ATENIA_ERR_UNSUPPORTED: return "not supported by this build";
+    case ATENIA_ERR_DEVICE_TIMEOUT: return "a bounded wait inside a kernel gave up";
+    case ATENIA_ERR_ROUTING: return "routing weights non-finite or selected sum <= 0";
+    case ATENIA_ERR_NCCL: return "an NCCL call failed";
+    case ATENIA_ERR_DRIVER: return "tensor-map encode or driver entry point unavailable";
+    default: break;
+  }
+  if (status > 0) return cudaGetErrorString(static_cast<cudaError_t>(status));
+  return "unknown status";
+}
+
+uint64_t atenia_moe_counter(int which) {
+  if (which < 0 || which >= 8) return 0;
+  return g_counters[which].load();
+}
+
+int atenia_moe_enable_timing(AteniaMoeLayer* L, int enable) {
+  if (!L) return ATENIA_ERR_NULL;
+  L->timing = enable != 0;
+  for (bool& v : L->ev_valid) v = false;
+  return ATENIA_OK;
+}
+
+float atenia_moe_last_gemm_ms(AteniaMoeLayer* L, int which) {
+  if (!L || which < 0 || which > 3 || !L->ev_valid[which]) return -1.0f;
+  static const int first[4] = {0, 1, 3, 4};
+  float ms = -1.0f;
+  if (cudaEventElapsedTime(&ms, L->ev[first[which]], L->ev[first[which] + 1]) != cudaSuccess) return -1.0f;
+  return ms;
+}
+
+}  // extern "C"

@@ -1,0 +1,183 @@
+// Operator registry: the host-memory interface of the reference's graph op
+// (register_real_moe_layer / execute_real_moe_layer, src/moe/graph_op.rs:221-350).
+// Ids are append-only and stable for the process; one mutex guards the table and is held across a
+// forward, like the reference's registry lock (src/moe/graph_op.rs:304-316).
+#include <mutex>
+#include <vector>
+
+#include "layer.cuh"
+
+namespace atenia {
+namespace {
+
+struct Registered {
+  AteniaMoeLayer* layer = nullptr;
+  std::vector<void*> weights;  // device buffers owned by the registry entry
+  void* d_in = nullptr;        // [max_tokens, d] f32
+  void* d_out = nullptr;
+  cudaStream_t stream = nullptr;
+};
+
+std::mutex g_mu;
+std::vector<Registered> g_layers;
+
+// Upload a host f32 matrix and store it as bf16 (round to nearest even) or per-row int8 + scales.
+int upload_matrix(const float* host, size_t rows, size_t cols, bool int8, Registered& reg, const void** w_out,
+                  const float** s_out, float* staging) {
+  if (!host) return ATENIA_ERR_NULL;
+  const size_t n = rows * cols;
+  ATENIA_CUDA_TRY(cudaMemcpy(staging, host, n * sizeof(float), cudaMemcpyHostToDevice));
+  count_bytes(ATENIA_COUNTER_H2D_BYTES, n * sizeof(float));
+  if (int8) {
+    int8_t* q = nullptr;
+    float* sc = nullptr;
+    ATENIA_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&q), n));
+    reg.weights.push_back(q);
+    ATENIA_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&sc), rows * sizeof(float)));
+    reg.weights.push_back(sc);
+    int rc = atenia_quantize_per_row_i8(staging, (int64_t)rows, (int64_t)cols, q, sc, nullptr);
+    if (rc) return rc;
+    *w_out = q;
+    *s_out = sc;
+  } else {
+    __nv_bfloat16* b = nullptr;
+    ATENIA_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&b), n * sizeof(__nv_bfloat16)));
+    reg.weights.push_back(b);
+    int rc = launch_f32_to_bf16(staging, b, (int64_t)n, nullptr);
+    if (rc) return rc;
+    *w_out = b;
+    *s_out = nullptr;
+  }
+  ATENIA_CUDA_TRY(cudaDeviceSynchronize());
+  return ATENIA_OK;
+}
+
+void release(Registered& r) {
+  if (r.layer) atenia_moe_destroy(r.layer);
+  for (void* p : r.weights) cudaFree(p);
+  if (r.d_in) cudaFree(r.d_in);
+  if (r.d_out) cudaFree(r.d_out);
+  if (r.stream) cudaStreamDestroy(r.stream);
+  r = Registered();
+}
+
+}  // namespace
+}  // namespace atenia
+
+using namespace atenia;
+
+extern "C" {
+
+int64_t atenia_register_real_moe_layer(const AteniaHostMoeLayer* h) {
+  if (!h || !h->w_router || !h->w_gate || !h->w_up || !h->w_down) return ATENIA_ERR_NULL;
+  AteniaMoeConfig cfg = h->config;
+  if (cfg.max_tokens <= 0) cfg.max_tokens = 4096;
+  if (cfg.ep_world <= 0) {
+    cfg.ep_world = 1;
+    cfg.ep_rank = 0;
+  }
+  if (cfg.ep_world != 1) return ATENIA_ERR_UNSUPPORTED;  // the registry path is single GPU
+  Registered reg;
+  int rc = atenia_moe_create(&cfg, &reg.layer);
+  if (rc) return rc;
+  const size_t E = (size_t)cfg.num_experts, d = (size_t)cfg.d_model, F = (size_t)cfg.d_ff,
+               Fs = (size_t)cfg.shared_d_ff;
+  const bool q = cfg.weight_dtype == ATENIA_W_INT8_ROW;
+  size_t stage_elems = E * d;
+  if (F * d > stage_elems) stage_elems = F * d;
+  if (Fs * d > stage_elems) stage_elems = Fs * d;
+  float* staging = nullptr;
+  cudaError_t ce = cudaMalloc(reinterpret_cast<void**>(&staging), stage_elems * sizeof(float));
+  if (ce != cudaSuccess) {
+    release(reg);
+    return (int)ce;
+  }
+  std::vector<const void*> pg(E), pu(E), pd(E);
+  std::vector<const float*> sg(E), su(E), sd(E);
+  AteniaMoeWeights w{};
+  float* d_router = nullptr;
+  float* d_gate_vec = nullptr;
+  auto fail = [&](int code) -> int64_t {
+    cudaFree(staging);
+    if (d_router) cudaFree(d_router);
+    if (d_gate_vec) cudaFree(d_gate_vec);
+    release(reg);
+    return code;
+  };
+  ce = cudaMalloc(reinterpret_cast<void**>(&d_router), E * d * sizeof(float));
+  if (ce != cudaSuccess) return fail((int)ce);
+  ce = cudaMemcpy(d_router, h->w_router, E * d * sizeof(float), cudaMemcpyHostToDevice);
+  if (ce != cudaSuccess) return fail((int)ce);
+  w.w_router = d_router;
+  for (size_t e = 0; e < E; ++e) {
+    rc = upload_matrix(h->w_gate[e], F, d, q, reg, &pg[e], &sg[e], staging);
+    if (!rc) rc = upload_matrix(h->w_up[e], F, d, q, reg, &pu[e], &su[e], staging);
+    if (!rc) rc = upload_matrix(h->w_down[e], d, F, q, reg, &pd[e], &sd[e], staging);
+    if (rc) return fail(rc);
+  }
+  w.w_gate = pg.data();
+  w.w_up = pu.data();
+  w.w_down = pd.data();
+  w.s_gate = sg.data();
+  w.s_up = su.data();
+  w.s_down = sd.data();
+  if (Fs > 0) {
+    rc = upload_matrix(h->shared_w_gate, Fs, d, q, reg, &w.shared_w_gate, &w.shared_s_gate, staging);
+    if (!rc) rc = upload_matrix(h->shared_w_up, Fs, d, q, reg, &w.shared_w_up, &w.shared_s_up, staging);
+    if (!rc) rc = upload_matrix(h->shared_w_down, d, Fs, q, reg, &w.shared_w_down, &w.shared_s_down, staging);
+    if (rc) return fail(rc);
+    if (h->shared_gate_vec && cfg.shared_gated) {
+      ce = cudaMalloc(reinterpret_cast<void**>(&d_gate_vec), d * sizeof(float));
+      if (ce == cudaSuccess) ce = cudaMemcpy(d_gate_vec, h->shared_gate_vec, d * sizeof(float), cudaMemcpyHostToDevice);
+      if (ce != cudaSuccess) return fail((int)ce);
+      w.shared_gate_vec = d_gate_vec;
+    }
+  }
+  rc = atenia_moe_set_weights(reg.layer, &w);
+  if (rc) return fail(rc);
+  cudaFree(staging);
+  cudaFree(d_router);  // copied by set_weights
+  if (d_gate_vec) cudaFree(d_gate_vec);
+  const size_t io = (size_t)cfg.max_tokens * d * sizeof(float);
+  ce = cudaMalloc(&reg.d_in, io);
+  if (ce == cudaSuccess) ce = cudaMalloc(&reg.d_out, io);
+  if (ce == cudaSuccess) ce = cudaStreamCreateWithFlags(&reg.stream, cudaStreamNonBlocking);
+  if (ce != cudaSuccess) {
+    release(reg);
+    return (int)ce;
+  }
+  std::lock_guard<std::mutex> lk(g_mu);
+  g_layers.push_back(reg);
+  return (int64_t)g_layers.size() - 1;
+}
+
+int atenia_execute_real_moe_layer(int64_t layer_id, const float* input, size_t len, float* output) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  if (layer_id < 0 || (size_t)layer_id >= g_layers.size() || !g_layers[(size_t)layer_id].layer)
+    return ATENIA_ERR_LAYER_NOT_FOUND;
+  Registered& r = g_layers[(size_t)layer_id];
+  const size_t d = (size_t)r.layer->cfg.d_model;
+  if (len == 0 || len % d != 0) return ATENIA_ERR_DIM_MISMATCH;
+  if (!input || !output) return ATENIA_ERR_NULL;
+  ATENIA_CUDA_TRY(cudaSetDevice(r.layer->device));
+  const size_t n = len / d, cap = (size_t)r.layer->cfg.max_tokens;
+  for (size_t t0 = 0; t0 < n; t0 += cap) {
+    const size_t tn = n - t0 < cap ? n - t0 : cap;
+    const size_t bytes = tn * d * sizeof(float);
+    ATENIA_CUDA_TRY(cudaMemcpyAsync(r.d_in, input + t0 * d, bytes, cudaMemcpyHostToDevice, r.stream));
+    int rc = atenia_moe_forward(r.layer, r.d_in, ATENIA_IO_F32, (int)tn, r.d_out, ATENIA_IO_F32, nullptr, r.stream);
+    if (rc) return rc;
+    ATENIA_CUDA_TRY(cudaMemcpyAsync(output + t0 * d, r.d_out, bytes, cudaMemcpyDeviceToHost, r.stream));
+    count_bytes(ATENIA_COUNTER_H2D_BYTES, bytes);
+    count_bytes(ATENIA_COUNTER_D2H_BYTES, bytes);
+  }
+  return atenia_moe_check(r.layer, r.stream);
+}
+
+AteniaMoeLayer* atenia_get_real_moe_layer(int64_t layer_id) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  if (layer_id < 0 || (size_t)layer_id >= g_layers.size()) return nullptr;
+  return g_layers[(size_t)layer_id].layer;
+}
+
+}  // extern "C"

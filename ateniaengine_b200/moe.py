@@ -1,0 +1,273 @@
+"""Host-side mirror of the reference's MoE block operator, on top of the C ABI.
+
+Names and argument meaning follow the reference (paths relative to its project root):
+  MoeLayerConfig, MoeExecutionConvention, RealMoeLayer        src/moe/layer.rs:37-43, :185-212
+  RealMoeLayer.forward / forward_with / forward_auto          src/moe/layer.rs:374-431
+  register_real_moe_layer / execute_real_moe_layer            src/moe/graph_op.rs:228, :327
+  quantize_per_row_i8                                         src/tensor/disk_tier.rs:231-245
+Every computation runs in the CUDA library; torch only owns device memory and streams.
+"""
+import ctypes as C
+import enum
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+
+from . import _lib
+from ._lib import IO_BF16, IO_F32, W_BF16, W_INT8_ROW
+
+
+class MoeLayerError(RuntimeError):
+    """Mirrors MoeLayerError: `kind` is 'LayerNotFound', 'DimMismatch' or 'Status'."""
+
+    def __init__(self, kind, status, msg):
+        super().__init__(f"moe-layer: {kind}: {msg}")
+        self.kind = kind
+        self.status = status
+
+
+class MoeExecutionConvention(enum.Enum):
+    Atenia = 0           # renormalised top-k, ungated shared expert
+    HuggingFaceQwen = 1  # raw top-k weights, shared expert scaled by sigmoid(gate . x)
+
+
+@dataclass
+class MoeLayerConfig:
+    num_experts: int
+    experts_per_token: int
+    has_shared_expert: bool
+    d_model: int
+    d_ff: int
+
+    def validate(self):
+        if self.num_experts < 1 or self.experts_per_token < 1 or self.experts_per_token > self.num_experts:
+            raise ValueError("moe-layer: invalid expert counts")
+        if self.d_model < 1 or self.d_ff < 1:
+            raise ValueError("moe-layer: invalid dims")
+
+
+def _ptr(t):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def _io_dtype(t):
+    if t.dtype == torch.bfloat16:
+        return IO_BF16
+    if t.dtype == torch.float32:
+        return IO_F32
+    raise TypeError(f"activations must be bf16 or f32, got {t.dtype}")
+
+
+def quantize_per_row_i8(w):
+    """Per-row symmetric int8 of a CUDA f32 [rows, cols] tensor -> (q int8, scales f32)."""
+    assert w.is_cuda and w.dtype == torch.float32 and w.dim() == 2
+    w = w.contiguous()
+    q = torch.empty(w.shape, dtype=torch.int8, device=w.device)
+    s = torch.empty(w.shape[0], dtype=torch.float32, device=w.device)
+    with torch.cuda.device(w.device):
+        st = torch.cuda.current_stream().cuda_stream
+        _lib.check(_lib.lib().atenia_quantize_per_row_i8(_ptr(w), w.shape[0], w.shape[1], _ptr(q), _ptr(s),
+                                                         C.c_void_p(st)), "quantize_per_row_i8")
+    return q, s
+
+
+class RealMoeLayer:
+    """A runnable MoE layer whose weights live in device memory.
+
+    `gate`, `up` are lists of [F, d] tensors, `down` a list of [d, F] tensors (bf16, or int8 with
+    `scales = {"gate": [...], "up": [...], "down": [...]}` of f32 [rows] tensors).  `router` is
+    f32 [E, d].  `shared` is an optional (gate [Fs, d], up [Fs, d], down [d, Fs]) triple with
+    `shared_scales` for int8; `shared_gate` the optional f32 [d] sigmoid-gate vector.
+    `convention` None means "auto": HuggingFaceQwen when a shared gate is present, else Atenia
+    (RealMoeLayer::resolve_convention); pass `renormalize` to override only the top-k rule (the
+    DeepSeek runtime does this from norm_topk_prob).
+    Under expert parallelism (`ep_world > 1`) the lists hold this rank's experts only.
+    """
+
+    def __init__(self, config, router, gate, up, down, shared=None, shared_gate=None, scales=None,
+                 shared_scales=None, convention=None, renormalize=None, router_bias=None, max_tokens=4096,
+                 ep_rank=0, ep_world=1):
+        config.validate()
+        self.config = config
+        dev = router.device
+        assert dev.type == "cuda", "weights must be CUDA tensors"
+        self.device = dev
+        if convention is None:
+            convention = (MoeExecutionConvention.HuggingFaceQwen if shared_gate is not None
+                          else MoeExecutionConvention.Atenia)
+        self.convention = convention
+        if renormalize is None:
+            renormalize = convention == MoeExecutionConvention.Atenia
+        gated = convention == MoeExecutionConvention.HuggingFaceQwen and shared_gate is not None
+        int8 = gate[0].dtype == torch.int8
+        self._keep = [router, gate, up, down, shared, shared_gate, scales, shared_scales, router_bias]
+        Fs = shared[0].shape[0] if shared is not None else 0
+        cfg = _lib.MoeConfig(config.num_experts, config.experts_per_token, config.d_model, config.d_ff, Fs,
+                             int(renormalize), int(gated), W_INT8_ROW if int8 else W_BF16, int(max_tokens),
+                             ep_rank, ep_world)
+        self.max_tokens = int(max_tokens)
+        self.ep_world = ep_world
+        self._h = C.c_void_p()
+        with torch.cuda.device(dev):
+            _lib.check(_lib.lib().atenia_moe_create(C.byref(cfg), C.byref(self._h)), "atenia_moe_create")
+            n = len(gate)
+            assert n == config.num_experts // ep_world
+            arr = lambda ts: (C.c_void_p * n)(*[t.data_ptr() for t in ts])
+            w = _lib.MoeWeights()
+            router = router.contiguous()
+            assert router.dtype == torch.float32
+            w.w_router = router.data_ptr()
+            w.router_bias = None if router_bias is None else router_bias.data_ptr()
+            self._arrs = [arr(gate), arr(up), arr(down)]
+            w.w_gate, w.w_up, w.w_down = self._arrs
+            if int8:
+                self._sarrs = [arr(scales["gate"]), arr(scales["up"]), arr(scales["down"])]
+                w.s_gate, w.s_up, w.s_down = self._sarrs
+            if shared is not None:
+                w.shared_w_gate, w.shared_w_up, w.shared_w_down = [t.data_ptr() for t in shared]
+                if int8:
+                    w.shared_s_gate, w.shared_s_up, w.shared_s_down = [t.data_ptr() for t in shared_scales]
+                if shared_gate is not None:
+                    w.shared_gate_vec = shared_gate.data_ptr()
+            _lib.check(_lib.lib().atenia_moe_set_weights(self._h, C.byref(w)), "atenia_moe_set_weights")
+
+    def close(self):
+        if getattr(self, "_h", None) is not None and self._h.value:
+            _lib.lib().atenia_moe_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @property
+    def handle(self):
+        return self._h
+
+    def ep_init(self, unique_id: bytes):
+        buf = C.create_string_buffer(unique_id, len(unique_id))
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.lib().atenia_moe_ep_init(self._h, buf), "atenia_moe_ep_init")
+
+    def forward(self, x, out=None, out_dtype=None, aux=False, sync=False):
+        """x: [T, d] CUDA bf16 or f32.  Returns out (and a dict of routing tensors when aux)."""
+        assert x.is_cuda and x.dim() == 2 and x.shape[1] == self.config.d_model
+        x = x.contiguous()
+        T = x.shape[0]
+        if out is None:
+            out = torch.empty((T, self.config.d_model), dtype=out_dtype or x.dtype, device=x.device)
+        auxs = None
+        aux_t = None
+        if aux:
+            k, E = self.config.experts_per_token, self.config.num_experts
+            aux_t = {
+                "topk_idx": torch.empty((T, k), dtype=torch.int32, device=x.device),
+                "topk_w": torch.empty((T, k), dtype=torch.float32, device=x.device),
+                "logits": torch.empty((T, E), dtype=torch.float32, device=x.device),
+                "perm": torch.empty((T * k,), dtype=torch.int32, device=x.device),
+                "expert_offsets": torch.empty((E + 1,), dtype=torch.int32, device=x.device),
+            }
+            auxs = _lib.MoeAux(*[aux_t[n].data_ptr() for n in ("topk_idx", "topk_w", "logits", "perm",
+                                                               "expert_offsets")])
+        with torch.cuda.device(x.device):
+            st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+            fn = _lib.lib().atenia_moe_forward_sync if sync else _lib.lib().atenia_moe_forward
+            _lib.check(fn(self._h, _ptr(x), _io_dtype(x), T, _ptr(out), _io_dtype(out),
+                          C.byref(auxs) if auxs is not None else None, st), "atenia_moe_forward")
+        return (out, aux_t) if aux else out
+
+    forward_auto = forward
+
+    def check(self):
+        with torch.cuda.device(self.device):
+            st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+            _lib.check(_lib.lib().atenia_moe_check(self._h, st), "atenia_moe_check")
+
+    def route_from_logits(self, logits, want_perm=True):
+        assert logits.is_cuda and logits.dtype == torch.float32
+        logits = logits.contiguous()
+        T, E = logits.shape
+        k = self.config.experts_per_token
+        idx = torch.empty((T, k), dtype=torch.int32, device=logits.device)
+        w = torch.empty((T, k), dtype=torch.float32, device=logits.device)
+        perm = torch.empty((T * k,), dtype=torch.int32, device=logits.device) if want_perm else None
+        inv = torch.empty((T * k,), dtype=torch.int32, device=logits.device) if want_perm else None
+        off = torch.empty((E + 1,), dtype=torch.int32, device=logits.device) if want_perm else None
+        with torch.cuda.device(logits.device):
+            st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+            _lib.check(_lib.lib().atenia_moe_route_from_logits(self._h, _ptr(logits), T, _ptr(idx), _ptr(w),
+                                                               _ptr(perm), _ptr(inv), _ptr(off), st),
+                       "atenia_moe_route_from_logits")
+            _lib.check(_lib.lib().atenia_moe_check(self._h, st), "atenia_moe_route_from_logits")
+        return idx, w, perm, inv, off
+
+    def enable_timing(self, on=True):
+        _lib.lib().atenia_moe_enable_timing(self._h, int(on))
+
+    def last_gemm_ms(self, which):
+        return float(_lib.lib().atenia_moe_last_gemm_ms(self._h, which))
+
+
+# ---- operator registry (host buffers) ---------------------------------------------------------
+
+def register_real_moe_layer(config, router, gate, up, down, shared=None, shared_gate=None,
+                            convention=None, renormalize=None, int8=False, max_tokens=4096):
+    """Host numpy f32 weights -> layer id.  Mirrors register_real_moe_layer(RealMoeLayer)."""
+    config.validate()
+    f32 = lambda a: np.ascontiguousarray(a, dtype=np.float32)
+    router = f32(router)
+    gate, up, down = [f32(a) for a in gate], [f32(a) for a in up], [f32(a) for a in down]
+    if convention is None:
+        convention = (MoeExecutionConvention.HuggingFaceQwen if shared_gate is not None
+                      else MoeExecutionConvention.Atenia)
+    if renormalize is None:
+        renormalize = convention == MoeExecutionConvention.Atenia
+    gated = convention == MoeExecutionConvention.HuggingFaceQwen and shared_gate is not None
+    n = config.num_experts
+    arr = lambda ts: (C.c_void_p * n)(*[t.ctypes.data for t in ts])
+    h = _lib.HostMoeLayer()
+    Fs = 0
+    keep = [router, gate, up, down]
+    if shared is not None:
+        shared = [f32(a) for a in shared]
+        Fs = shared[0].shape[0]
+        h.shared_w_gate, h.shared_w_up, h.shared_w_down = [a.ctypes.data for a in shared]
+        keep.append(shared)
+        if shared_gate is not None:
+            shared_gate = f32(shared_gate).reshape(-1)
+            h.shared_gate_vec = shared_gate.ctypes.data
+            keep.append(shared_gate)
+    h.config = _lib.MoeConfig(config.num_experts, config.experts_per_token, config.d_model, config.d_ff, Fs,
+                              int(renormalize), int(gated), W_INT8_ROW if int8 else W_BF16, int(max_tokens), 0, 1)
+    h.w_router = router.ctypes.data
+    a1, a2, a3 = arr(gate), arr(up), arr(down)
+    h.w_gate, h.w_up, h.w_down = a1, a2, a3
+    lid = _lib.lib().atenia_register_real_moe_layer(C.byref(h))
+    if lid < 0:
+        raise MoeLayerError("Status", int(lid), _lib.lib().atenia_moe_status_str(C.c_int(int(lid))).decode())
+    return int(lid)
+
+
+def execute_real_moe_layer(layer_id, input, out=None):
+    """Flat host f32 [n * d_model] -> [n * d_model], the graph op's contract."""
+    inp = np.ascontiguousarray(input, dtype=np.float32).reshape(-1)
+    if out is None:
+        out = np.empty_like(inp)
+    rc = _lib.lib().atenia_execute_real_moe_layer(int(layer_id), C.c_void_p(inp.ctypes.data), inp.size,
+                                                  C.c_void_p(out.ctypes.data))
+    if rc == _lib.ERR_LAYER_NOT_FOUND:
+        raise MoeLayerError("LayerNotFound", rc, f"layer_id {layer_id}")
+    if rc == _lib.ERR_DIM_MISMATCH:
+        raise MoeLayerError("DimMismatch", rc, f"input length {inp.size}")
+    if rc != 0:
+        raise MoeLayerError("Status", rc, _lib.lib().atenia_moe_status_str(C.c_int(rc)).decode())
+    return out
+
+
+def execute_real_moe_layer_ptr(layer_id, in_ptr, n_floats, out_ptr):
+    """Same call on raw host pointers (e.g. pinned buffers); returns the status."""
+    return _lib.lib().atenia_execute_real_moe_layer(int(layer_id), C.c_void_p(in_ptr), n_floats,
+                                                    C.c_void_p(out_ptr))

@@ -1,0 +1,215 @@
+/*
+ * atenia_moe.h -- C ABI of the B200 (sm_100a) mixture-of-experts block.
+ *
+ * This is the boundary a Rust `unsafe extern "C"` block (or any FFI) binds.  It replaces, for the
+ * MoE block only, the CPU path of the reference engine:
+ *
+ *   reference (paths relative to the reference project root)      this library
+ *   ------------------------------------------------------------  ---------------------------------
+ *   RealMoeLayer / MoeLayerConfig        src/moe/layer.rs:185-212  AteniaMoeConfig + atenia_moe_create
+ *   RealMoeLayer::assemble (weights)     src/moe/layer.rs:276-351  atenia_moe_set_weights
+ *   RealMoeLayer::forward_with           src/moe/layer.rs:405-431  atenia_moe_forward
+ *   MoeDenseLayer::route + top_k_routing src/moe/dense.rs:325-337,
+ *                                        src/moe/sparse.rs:142-191 atenia_moe_route_from_logits
+ *   register_real_moe_layer              src/moe/graph_op.rs:228   atenia_register_real_moe_layer
+ *   execute_real_moe_layer               src/moe/graph_op.rs:327   atenia_execute_real_moe_layer
+ *   quantize_per_row_i8                  src/tensor/disk_tier.rs:231-245  atenia_quantize_per_row_i8
+ *
+ * Conventions follow the reference's existing CUDA FFI (src/cuda/*.cu): plain `extern "C"` functions,
+ * `int` status (0 = ok, > 0 = a cudaError_t value, < 0 = argument / shape / state errors listed
+ * below), raw pointers and integer sizes, and the caller owns every buffer it passes.  Nothing here
+ * falls back to the CPU: an error is returned as a status.
+ *
+ * Pointer kinds are stated per argument: "device" pointers must be valid on the layer's CUDA device,
+ * "host" pointers are ordinary process memory.
+ */
+#ifndef ATENIA_MOE_H_
+#define ATENIA_MOE_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define ATENIA_API __attribute__((visibility("default")))
+#else
+#define ATENIA_API
+#endif
+
+/* ---- status codes ------------------------------------------------------------------------- */
+#define ATENIA_OK 0
+#define ATENIA_ERR_NULL (-1)            /* a required pointer is NULL */
+#define ATENIA_ERR_SHAPE (-2)           /* sizes violate a stated constraint */
+#define ATENIA_ERR_CAPACITY (-3)        /* more tokens than the layer's max_tokens */
+#define ATENIA_ERR_STATE (-4)           /* e.g. forward before set_weights */
+#define ATENIA_ERR_LAYER_NOT_FOUND (-5) /* unknown registry id (MoeBindingError::LayerNotFound) */
+#define ATENIA_ERR_DIM_MISMATCH (-6)    /* input length not a multiple of d_model (MoeDenseError::DimMismatch) */
+#define ATENIA_ERR_UNSUPPORTED (-7)     /* valid in the reference, not built here */
+#define ATENIA_ERR_DEVICE_TIMEOUT (-8)  /* a bounded wait inside a kernel gave up */
+#define ATENIA_ERR_ROUTING (-9)         /* non-finite routing weight or selected sum <= 0 (MoeSparseError) */
+#define ATENIA_ERR_NCCL (-10)           /* an NCCL call failed */
+#define ATENIA_ERR_DRIVER (-11)         /* tensor-map encode or driver entry point unavailable */
+
+/* ---- enums -------------------------------------------------------------------------------- */
+#define ATENIA_IO_BF16 0 /* activations as bf16 (high half of an f32, src/tensor/tensor.rs:294-308) */
+#define ATENIA_IO_F32 1  /* activations as f32 (what execute_real_moe_layer passes) */
+
+#define ATENIA_W_BF16 0     /* expert weights bf16 */
+#define ATENIA_W_INT8_ROW 1 /* expert weights int8, one f32 scale per output row (disk_tier.rs:231-259) */
+
+/* ---- layer description (mirrors MoeLayerConfig + MoeExecutionConvention) ------------------- */
+typedef struct AteniaMoeConfig {
+  int32_t num_experts;       /* routed experts E (global count under expert parallelism), 1..128 */
+  int32_t experts_per_token; /* top-k, 1..min(E, 8) */
+  int32_t d_model;           /* multiple of 16 */
+  int32_t d_ff;              /* routed expert width F, multiple of 16 */
+  int32_t shared_d_ff;       /* shared expert width Fs (0 = no shared expert), multiple of 16 */
+  int32_t renormalize;       /* 1: selected weights divided by their sum (Atenia / Mixtral) */
+  int32_t shared_gated;      /* 1: shared output scaled by sigmoid(g . x) (HuggingFaceQwen) */
+  int32_t weight_dtype;      /* ATENIA_W_* for routed and shared expert matrices */
+  int32_t max_tokens;        /* capacity of the layer's device workspace, tokens per forward call */
+  int32_t ep_rank;           /* expert-parallel rank of this process (0 when ep_world == 1) */
+  int32_t ep_world;          /* expert-parallel world size: 1, 2, 4 or 8; must divide num_experts */
+} AteniaMoeConfig;
+
+/* Device pointers to the weights.  Expert matrices keep the reference's row-major layouts
+ * (src/moe/dense.rs:203-216): gate, up [F, d]; down [d, F].  The per-expert pointer arrays are HOST
+ * arrays of `num_experts / ep_world` DEVICE pointers (the experts this rank owns, ascending id).
+ * The library borrows the matrices: they must stay alive and unchanged while the layer is used.
+ * The router matrix, the bias and the shared gate vector are copied at the call.
+ * Scale arrays (f32, one per output row: F for gate/up, d for down) are required for INT8 and
+ * ignored for bf16. */
+typedef struct AteniaMoeWeights {
+  const float* w_router;         /* device [E, d] f32; the router is never quantised (residency.rs:621-622) */
+  const float* router_bias;      /* device [E] f32 or NULL; extra logit term for synthetic load skew */
+  const void* const* w_gate;     /* host array of device pointers */
+  const void* const* w_up;
+  const void* const* w_down;
+  const float* const* s_gate;    /* host array of device pointers, INT8 only */
+  const float* const* s_up;
+  const float* const* s_down;
+  const void* shared_w_gate;     /* device [Fs, d] */
+  const void* shared_w_up;       /* device [Fs, d] */
+  const void* shared_w_down;     /* device [d, Fs] */
+  const float* shared_s_gate;    /* device [Fs], INT8 only */
+  const float* shared_s_up;      /* device [Fs], INT8 only */
+  const float* shared_s_down;    /* device [d], INT8 only */
+  const float* shared_gate_vec;  /* device [d] f32 or NULL (shared_expert_gate, layer.rs:208-211) */
+} AteniaMoeWeights;
+
+/* Optional per-call outputs (device pointers, any may be NULL). */
+typedef struct AteniaMoeAux {
+  int32_t* topk_idx;       /* [T, k] selected experts, ascending per token */
+  float* topk_w;           /* [T, k] combine weights */
+  float* logits;           /* [T, E] router logits (f32) */
+  int32_t* perm;           /* [T*k] dispatch order: row r holds flat entry t*k+s */
+  int32_t* expert_offsets; /* [E+1] first row of each expert in dispatch order */
+} AteniaMoeAux;
+
+typedef struct AteniaMoeLayer AteniaMoeLayer;
+
+/* Create a layer on the current CUDA device and allocate its workspace (sized by max_tokens). */
+ATENIA_API int atenia_moe_create(const AteniaMoeConfig* cfg, AteniaMoeLayer** out);
+ATENIA_API int atenia_moe_destroy(AteniaMoeLayer* layer);
+
+/* Bind weights (see AteniaMoeWeights).  Builds the TMA descriptors of the expert matrices. */
+ATENIA_API int atenia_moe_set_weights(AteniaMoeLayer* layer, const AteniaMoeWeights* w);
+
+/* out[T, d] = MoE(x[T, d]).  x and out are device pointers of the stated io dtype; the call is
+ * asynchronous on `stream` (a cudaStream_t passed as void*; NULL = the default stream).
+ * Follows RealMoeLayer::forward_with row by row; the convention is the one in the config. */
+ATENIA_API int atenia_moe_forward(AteniaMoeLayer* layer, const void* x, int x_dtype, int T, void* out,
+                                  int out_dtype, const AteniaMoeAux* aux, void* stream);
+
+/* Same, then waits for the stream and returns any error a kernel recorded (routing errors,
+ * bounded-wait timeouts).  Mirrors the reference's synchronous launchers. */
+ATENIA_API int atenia_moe_forward_sync(AteniaMoeLayer* layer, const void* x, int x_dtype, int T, void* out,
+                                       int out_dtype, const AteniaMoeAux* aux, void* stream);
+
+/* Wait for `stream` and return the error word kernels of this layer recorded since the last check
+ * (ATENIA_OK if none); the word is cleared. */
+ATENIA_API int atenia_moe_check(AteniaMoeLayer* layer, void* stream);
+
+/* Routing only, from caller-provided f32 logits [T, E] (device): softmax (dense.rs:172-187), top-k
+ * with lowest-index tie-break and optional renormalisation (sparse.rs:142-191), and the dispatch
+ * permutation (stable counting sort of the (token, slot) list by expert).  Integer outputs are
+ * bit-identical to the CPU algorithm on the same logits.  All outputs are device pointers; perm,
+ * inv_perm and expert_offsets may be NULL. */
+ATENIA_API int atenia_moe_route_from_logits(AteniaMoeLayer* layer, const float* logits, int T,
+                                            int32_t* topk_idx, float* topk_w, int32_t* perm,
+                                            int32_t* inv_perm, int32_t* expert_offsets, void* stream);
+
+/* Per-row symmetric int8 quantisation of a row-major [rows, cols] f32 device matrix:
+ * scale = max|row| / 127 (1.0 for a zero row), q = clamp(round_half_away(w * (1/scale)), -127, 127).
+ * Bit-identical to quantize_per_row_i8 (src/tensor/disk_tier.rs:231-245). */
+ATENIA_API int atenia_quantize_per_row_i8(const float* w, int64_t rows, int64_t cols, int8_t* q,
+                                          float* scales, void* stream);
+
+/* ---- operator registry (host-memory interface of the reference's graph op) ---------------- */
+
+/* Host-side description used by the registry: all weights are HOST f32 arrays in the reference's
+ * layouts, exactly the fields of RealMoeLayer.  They are rounded to bf16 (nearest even) or quantised
+ * per row to int8 and uploaded once; the host arrays are not referenced after the call returns. */
+typedef struct AteniaHostMoeLayer {
+  AteniaMoeConfig config;       /* weight_dtype selects bf16 or int8 storage on the device */
+  const float* w_router;        /* [E, d] */
+  const float* const* w_gate;   /* E pointers, each [F, d] */
+  const float* const* w_up;     /* E pointers, each [F, d] */
+  const float* const* w_down;   /* E pointers, each [d, F] */
+  const float* shared_w_gate;   /* [Fs, d] or NULL */
+  const float* shared_w_up;     /* [Fs, d] or NULL */
+  const float* shared_w_down;   /* [d, Fs] or NULL */
+  const float* shared_gate_vec; /* [d] or NULL */
+} AteniaHostMoeLayer;
+
+/* register_real_moe_layer: returns the new layer id (>= 0; ids are append-only and stable for the
+ * process) or a negative status. */
+ATENIA_API int64_t atenia_register_real_moe_layer(const AteniaHostMoeLayer* layer);
+
+/* execute_real_moe_layer: `input` is a flat HOST [n * d_model] f32 batch, `output` receives
+ * [n * d_model] f32.  Rows are independent.  Unknown id -> ATENIA_ERR_LAYER_NOT_FOUND; a length that
+ * is not a positive multiple of d_model -> ATENIA_ERR_DIM_MISMATCH.  Copies host->device, runs the
+ * block, copies back and waits; batches larger than the layer's capacity run in several passes. */
+ATENIA_API int atenia_execute_real_moe_layer(int64_t layer_id, const float* input, size_t len,
+                                             float* output);
+
+/* The device layer behind a registry id (NULL if unknown), for callers that keep activations on the
+ * device. */
+ATENIA_API AteniaMoeLayer* atenia_get_real_moe_layer(int64_t layer_id);
+
+/* ---- expert parallelism ------------------------------------------------------------------- */
+
+/* Size of the opaque NCCL unique id, and a fresh id (rank 0 creates it, the host program
+ * broadcasts it to the other ranks by any means). */
+ATENIA_API int atenia_moe_ep_unique_id_bytes(void);
+ATENIA_API int atenia_moe_ep_get_unique_id(void* id_out);
+
+/* Join the expert-parallel group of `layer` (config.ep_world ranks, one process per GPU).  After
+ * this, atenia_moe_forward routes this rank's tokens, exchanges rows with the ranks that own the
+ * selected experts, runs the local experts and exchanges the results back. */
+ATENIA_API int atenia_moe_ep_init(AteniaMoeLayer* layer, const void* unique_id);
+
+/* ---- diagnostics -------------------------------------------------------------------------- */
+ATENIA_API const char* atenia_moe_status_str(int status);
+
+#define ATENIA_COUNTER_FORWARD_CALLS 0   /* forwards issued */
+#define ATENIA_COUNTER_KERNEL_LAUNCHES 1 /* kernels of this library launched */
+#define ATENIA_COUNTER_TCGEN05_LAUNCHES 2 /* tensor-core grouped-GEMM launches among them */
+#define ATENIA_COUNTER_H2D_BYTES 3       /* bytes copied host->device by the registry path */
+#define ATENIA_COUNTER_D2H_BYTES 4       /* bytes copied device->host by the registry path */
+ATENIA_API uint64_t atenia_moe_counter(int which);
+
+/* Time of the most recent grouped-GEMM launches of this layer, measured with CUDA events on the
+ * launching stream while timing is enabled (enable != 0).  `which`: 0 = routed gate/up + SwiGLU,
+ * 1 = routed down, 2 = shared gate/up, 3 = shared down.  Returns milliseconds, or a negative value
+ * if nothing was recorded.  Enabling timing adds event records to every forward. */
+ATENIA_API int atenia_moe_enable_timing(AteniaMoeLayer* layer, int enable);
+ATENIA_API float atenia_moe_last_gemm_ms(AteniaMoeLayer* layer, int which);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ATENIA_MOE_H_ */

@@ -1,0 +1,268 @@
+"""GPU parity tests: the CUDA library (called through its C ABI) against the CPU oracle.
+
+Bars: integer results (top-k indices, permutation, offsets, int8 codes) bit-exact; layer outputs
+relative L2 <= 1e-2 for bf16 weights and <= 2e-2 for W8A16, against the f64-accumulating oracle fed
+the same bf16-rounded (or int8 + scale) values.
+"""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as orc
+from tests.helpers import oracle_layer, reference_metrics, rel_l2
+
+pytestmark = pytest.mark.gpu
+
+TOL_BF16 = 1e-2
+TOL_W8A16 = 2e-2
+
+
+@pytest.fixture(scope="module")
+def dev():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    return torch.device("cuda:0")
+
+
+def _synth():
+    from ateniaengine_b200 import synth
+    return synth
+
+
+# ---- integer paths: bit-exact -----------------------------------------------------------------
+
+def test_quantizer_is_bit_identical_to_cpu(dev):
+    from ateniaengine_b200 import quantize_per_row_i8
+    g = torch.Generator(device=dev).manual_seed(11)
+    w = torch.randn((257, 1408), generator=g, device=dev) * 0.02
+    w[5] = 0.0
+    w[7, 3] = w[7].abs().max() * 2  # a clear row maximum
+    q, s = quantize_per_row_i8(w)
+    q_ref, s_ref = orc.quantize_per_row_i8(w.cpu().numpy())
+    np.testing.assert_array_equal(s.cpu().numpy(), s_ref)
+    np.testing.assert_array_equal(q.cpu().numpy(), q_ref)
+    assert s_ref[5] == 1.0
+
+
+@pytest.mark.parametrize("E,k,renorm", [(8, 2, True), (60, 4, False), (64, 6, False), (4, 2, True), (128, 8, True)])
+def test_route_from_logits_bit_exact(dev, E, k, renorm):
+    synth = _synth()
+    shape = synth.MoeShape("r", 64, 64, E, k, renorm)
+    w = synth.make_weights(shape, 1, dev)
+    T = 1537
+    layer = synth.build_layer(shape, w, max_tokens=T)
+    g = torch.Generator(device=dev).manual_seed(E * 100 + k)
+    logits = torch.randn((T, E), generator=g, device=dev) * 2.0
+    # ties: identical logits in whole rows, pairs, and near-ties one ulp apart
+    logits[0] = 1.25
+    logits[1, : E // 2] = 0.5
+    logits[2] = logits[2].round()
+    logits[3, 1] = logits[3, 0]
+    logits[4, E - 1] = torch.nextafter(logits[4, 0], torch.tensor(10.0, device=dev))
+    # saturated softmax: huge spread rounds most weights to 0 -> ties at zero resolved by index
+    logits[5] = torch.linspace(-200.0, 200.0, E, device=dev)
+    idx, tw, perm, inv, off = layer.route_from_logits(logits)
+    idx_ref, tw_ref = orc.route_from_logits(logits.cpu().numpy(), k, renorm)
+    np.testing.assert_array_equal(idx.cpu().numpy(), idx_ref)
+    # weights: same algorithm; exp() may differ in the last bit between libm and CUDA
+    np.testing.assert_allclose(tw.cpu().numpy(), tw_ref, rtol=2e-7, atol=0)
+    off_ref, perm_ref, inv_ref = orc.dispatch_permutation(idx_ref, E)
+    np.testing.assert_array_equal(off.cpu().numpy(), off_ref)
+    np.testing.assert_array_equal(perm.cpu().numpy(), perm_ref)
+    np.testing.assert_array_equal(inv.cpu().numpy(), inv_ref)
+
+
+def test_route_from_logits_rejects_non_finite(dev):
+    from ateniaengine_b200._lib import AteniaError
+    synth = _synth()
+    shape = synth.MoeShape("r", 64, 64, 8, 2, True)
+    layer = synth.build_layer(shape, synth.make_weights(shape, 1, dev), max_tokens=16)
+    logits = torch.zeros((4, 8), device=dev)
+    logits[2, 3] = float("nan")
+    with pytest.raises(AteniaError) as ei:
+        layer.route_from_logits(logits)
+    assert ei.value.status == -9
+
+
+# ---- layer parity ------------------------------------------------------------------------------
+
+def _run_parity(dev, shape, T, tol, seed=3, x_dtype=torch.bfloat16, sample=None):
+    synth = _synth()
+    w = synth.make_weights(shape, seed, dev)
+    x = synth.make_activations(shape, seed, dev, tokens=T, dtype=x_dtype)
+    layer = synth.build_layer(shape, w, max_tokens=max(T, 1))
+    out, aux = layer.forward(x, out_dtype=torch.float32, aux=True, sync=True)
+    out = out.cpu().numpy()
+    ol = oracle_layer(shape, w)
+    rows = np.arange(T) if sample is None or sample >= T else np.sort(
+        np.random.default_rng(seed).choice(T, size=sample, replace=False))
+    xs = x.float().cpu().numpy()[rows]
+    ref, raux = ol.forward(xs, want_aux=True)
+    # routing: identical selection given the GPU's own logits, and (nearly always) the oracle's
+    g_logits = aux["logits"].cpu().numpy()
+    idx_from_gpu_logits, _ = orc.route_from_logits(g_logits, shape.top_k, shape.renormalize)
+    np.testing.assert_array_equal(aux["topk_idx"].cpu().numpy(), idx_from_gpu_logits)
+    off_ref, perm_ref, _ = orc.dispatch_permutation(idx_from_gpu_logits, shape.num_experts)
+    np.testing.assert_array_equal(aux["perm"].cpu().numpy(), perm_ref)
+    np.testing.assert_array_equal(aux["expert_offsets"].cpu().numpy(), off_ref)
+    np.testing.assert_allclose(g_logits[rows], raux["logits"], rtol=0, atol=2e-6)
+    same = (aux["topk_idx"].cpu().numpy()[rows] == raux["topk_idx"]).all(axis=1)
+    assert same.mean() >= 0.995, f"top-k sets differ from the oracle on {np.sum(~same)} of {len(rows)} tokens"
+    err = rel_l2(out[rows][same], ref[same])
+    assert err <= tol, f"{shape.name}: rel-L2 {err:.3e} > {tol}"
+    return err, reference_metrics(out[rows][same], ref[same])
+
+
+def test_tiny_config_matches_oracle(dev):
+    """The reference's CPU-runnable case: d512, F1408, 8 experts top-2, 64 tokens."""
+    synth = _synth()
+    _run_parity(dev, synth.SHAPES["tiny"], 64, TOL_BF16, seed=0)
+
+
+def test_tiny_config_f32_io(dev):
+    synth = _synth()
+    _run_parity(dev, synth.SHAPES["tiny"], 64, TOL_BF16, seed=0, x_dtype=torch.float32)
+
+
+@pytest.mark.parametrize("T", [1, 2, 16, 127, 129, 300])
+def test_mixtral_structure_ragged_token_counts(dev, T):
+    synth = _synth()
+    shape = synth.small(synth.SHAPES["mixtral"], d_model=1024, d_ff=2048)
+    _run_parity(dev, shape, T, TOL_BF16, seed=T)
+
+
+def test_qwen_structure_shared_gated(dev):
+    synth = _synth()
+    shape = synth.small(synth.SHAPES["qwen_moe"], d_model=512, d_ff=384, shared_d_ff=768)
+    _run_parity(dev, shape, 333, TOL_BF16)
+
+
+def test_deepseek_structure_shared_ungated(dev):
+    synth = _synth()
+    shape = synth.small(synth.SHAPES["deepseek_v2_lite"], d_model=512, d_ff=384, shared_d_ff=768)
+    _run_parity(dev, shape, 515, TOL_BF16)
+
+
+def test_w8a16_structure(dev):
+    synth = _synth()
+    shape = synth.small(synth.SHAPES["mixtral_int8"], d_model=1024, d_ff=2048)
+    for T in (1, 8, 64):
+        _run_parity(dev, shape, T, TOL_W8A16, seed=T)
+
+
+def test_w8a16_with_shared_expert(dev):
+    synth = _synth()
+    from dataclasses import replace
+    shape = replace(synth.small(synth.SHAPES["qwen_moe"], d_model=512, d_ff=384, shared_d_ff=768), int8=True)
+    _run_parity(dev, shape, 200, TOL_W8A16)
+
+
+def test_all_tokens_on_one_expert_and_empty_experts(dev):
+    """A bias that dominates the logits sends every token to experts 2 and 5; the rest get no rows."""
+    synth = _synth()
+    shape = synth.small(synth.SHAPES["mixtral"], d_model=512, d_ff=512)
+    w = synth.make_weights(shape, 5, dev)
+    bias = torch.full((8,), -50.0, device=dev)
+    bias[2] = 50.0
+    bias[5] = 49.0
+    w["router_bias"] = bias
+    x = synth.make_activations(shape, 5, dev, tokens=200)
+    layer = synth.build_layer(shape, w, max_tokens=200)
+    out, aux = layer.forward(x, out_dtype=torch.float32, aux=True, sync=True)
+    assert (aux["topk_idx"].cpu().numpy() == np.array([2, 5])).all()
+    off = aux["expert_offsets"].cpu().numpy()
+    assert off.tolist() == [0, 0, 0, 200, 200, 200, 400, 400, 400]
+    ref = oracle_layer(shape, w).forward(x.float().cpu().numpy())
+    assert rel_l2(out.cpu().numpy(), ref) <= TOL_BF16
+
+
+def test_tensor_core_kernel_agrees_with_cuda_core_check(dev, monkeypatch):
+    synth = _synth()
+    shape = synth.small(synth.SHAPES["deepseek_v2_lite"], d_model=256, d_ff=384, shared_d_ff=256)
+    w = synth.make_weights(shape, 9, dev)
+    x = synth.make_activations(shape, 9, dev, tokens=300)
+    a = synth.build_layer(shape, w, max_tokens=300).forward(x, out_dtype=torch.float32, sync=True)
+    monkeypatch.setenv("ATENIA_MOE_CHECK_GEMM", "1")
+    b = synth.build_layer(shape, w, max_tokens=300).forward(x, out_dtype=torch.float32, sync=True)
+    assert rel_l2(a.cpu().numpy(), b.cpu().numpy()) < 2e-3
+
+
+def test_token_order_does_not_change_rows(dev):
+    """The block is position-wise: shuffling the tokens shuffles the outputs, bit for bit."""
+    synth = _synth()
+    shape = synth.small(synth.SHAPES["mixtral"], d_model=512, d_ff=1024)
+    w = synth.make_weights(shape, 13, dev)
+    x = synth.make_activations(shape, 13, dev, tokens=777)
+    layer = synth.build_layer(shape, w, max_tokens=777)
+    a = layer.forward(x, sync=True)
+    p = torch.randperm(777, device=dev)
+    b = layer.forward(x[p].contiguous(), sync=True)
+    assert torch.equal(a[p], b)
+    # and repeated calls are deterministic
+    assert torch.equal(layer.forward(x, sync=True), a)
+
+
+# ---- the reference's golden vectors, through the operator registry ------------------------------
+
+def _golden(golden_dir, name):
+    import os
+    z = np.load(os.path.join(golden_dir, name + ".npz"))
+    return {k: z[k] for k in z.files}
+
+
+def _pad16(a, axis):
+    n = a.shape[axis]
+    m = (n + 15) // 16 * 16
+    if m == n:
+        return a
+    pad = [(0, 0)] * a.ndim
+    pad[axis] = (0, m - n)
+    return np.pad(a, pad)
+
+
+@pytest.mark.parametrize("name,key,conv,renorm", [
+    ("mixtral_layer0", "atenia_ref", "Atenia", True),
+    ("qwen2_moe_layer0", "atenia_hf_ref", "HuggingFaceQwen", False),
+    ("qwen2_moe_layer0", "atenia_ref", "Atenia", True),
+    ("qwen3_moe_layer0", "atenia_ref", "Atenia", True),
+    ("qwen15_moe_layer0", "atenia_hf_ref", "HuggingFaceQwen", False),
+    ("deepseek_block", "mlp_output", "Atenia", False),
+])
+def test_reference_golden_vectors_through_registry(dev, golden_dir, name, key, conv, renorm):
+    """register_real_moe_layer + execute_real_moe_layer on the reference's own fixtures.  d_ff that is
+    not a multiple of 16 is zero-padded (zero gate/up rows give h = 0, zero down columns ignore it)."""
+    import ateniaengine_b200 as ae
+    g = _golden(golden_dir, name)
+    E, F, d = g["gate"].shape
+    gate = [_pad16(g["gate"][e], 0) for e in range(E)]
+    up = [_pad16(g["up"][e], 0) for e in range(E)]
+    down = [_pad16(g["down"][e], 1) for e in range(E)]
+    shared = None
+    if "shared_gate_proj" in g:
+        shared = [_pad16(g["shared_gate_proj"], 0), _pad16(g["shared_up_proj"], 0), _pad16(g["shared_down_proj"], 1)]
+    convention = ae.MoeExecutionConvention[conv]
+    gate_vec = g.get("shared_gate_vec") if convention == ae.MoeExecutionConvention.HuggingFaceQwen else None
+    cfg = ae.MoeLayerConfig(E, int(g["top_k"]), shared is not None, d, gate[0].shape[0])
+    lid = ae.register_real_moe_layer(cfg, g["router"], gate, up, down, shared=shared, shared_gate=gate_vec,
+                                     convention=convention, renormalize=renorm, max_tokens=64)
+    out = ae.execute_real_moe_layer(lid, g["input"].astype(np.float32).ravel())
+    assert rel_l2(out, g[key]) <= TOL_BF16
+
+
+def test_registry_error_behaviour(dev, golden_dir):
+    import ateniaengine_b200 as ae
+    with pytest.raises(ae.MoeLayerError) as ei:
+        ae.execute_real_moe_layer(10 ** 6, np.zeros(64, dtype=np.float32))
+    assert ei.value.kind == "LayerNotFound"
+    g = _golden(golden_dir, "mixtral_layer0")
+    E, F, d = g["gate"].shape
+    cfg = ae.MoeLayerConfig(E, 2, False, d, F)
+    lid = ae.register_real_moe_layer(cfg, g["router"], list(g["gate"]), list(g["up"]), list(g["down"]), max_tokens=8)
+    with pytest.raises(ae.MoeLayerError) as ei:
+        ae.execute_real_moe_layer(lid, np.zeros(d + 1, dtype=np.float32))
+    assert ei.value.kind == "DimMismatch"
+    # a batch larger than the layer's capacity runs in passes; rows stay independent
+    x = np.random.default_rng(0).normal(size=(19, d)).astype(np.float32)
+    full = ae.execute_real_moe_layer(lid, x.ravel()).reshape(19, d)
+    one = ae.execute_real_moe_layer(lid, x[11]).reshape(d)
+    np.testing.assert_array_equal(full[11], one)
