@@ -10,5 +10,6 @@ from .moe import (  # noqa: F401
     MoeLayerError,
     execute_real_moe_layer,
     register_real_moe_layer,
+    register_resident_moe_layer,
     quantize_per_row_i8,
 )

@@ -49,7 +49,7 @@ class HostMoeLayer(C.Structure):
 EXPORTS = [
     "atenia_moe_create", "atenia_moe_destroy", "atenia_moe_set_weights", "atenia_moe_forward",
     "atenia_moe_forward_sync", "atenia_moe_check", "atenia_moe_route_from_logits",
-    "atenia_quantize_per_row_i8", "atenia_register_real_moe_layer", "atenia_execute_real_moe_layer",
+    "atenia_quantize_per_row_i8", "atenia_register_real_moe_layer", "atenia_register_resident_moe_layer", "atenia_execute_real_moe_layer",
     "atenia_get_real_moe_layer", "atenia_moe_ep_unique_id_bytes", "atenia_moe_ep_get_unique_id",
     "atenia_moe_ep_init", "atenia_moe_status_str", "atenia_moe_counter", "atenia_moe_enable_timing",
     "atenia_moe_last_gemm_ms",
@@ -77,6 +77,8 @@ def lib():
         l.atenia_moe_counter.restype = C.c_uint64
         l.atenia_register_real_moe_layer.restype = C.c_int64
         l.atenia_get_real_moe_layer.restype = C.c_void_p
+        l.atenia_register_resident_moe_layer.restype = C.c_int64
+        l.atenia_register_resident_moe_layer.argtypes = [C.c_void_p]
         l.atenia_get_real_moe_layer.argtypes = [C.c_int64]
         l.atenia_moe_last_gemm_ms.restype = C.c_float
         l.atenia_moe_last_gemm_ms.argtypes = [C.c_void_p, C.c_int]

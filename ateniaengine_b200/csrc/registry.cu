@@ -12,6 +12,7 @@ namespace {
 
 struct Registered {
   AteniaMoeLayer* layer = nullptr;
+  bool owns_layer = true;
   std::vector<void*> weights;  // device buffers owned by the registry entry
   void* d_in = nullptr;        // [max_tokens, d] f32
   void* d_out = nullptr;
@@ -53,7 +54,7 @@ int upload_matrix(const float* host, size_t rows, size_t cols, bool int8, Regist
 }
 
 void release(Registered& r) {
-  if (r.layer) atenia_moe_destroy(r.layer);
+  if (r.layer && r.owns_layer) atenia_moe_destroy(r.layer);
   for (void* p : r.weights) cudaFree(p);
   if (r.d_in) cudaFree(r.d_in);
   if (r.d_out) cudaFree(r.d_out);
@@ -140,6 +141,26 @@ int64_t atenia_register_real_moe_layer(const AteniaHostMoeLayer* h) {
   if (d_gate_vec) cudaFree(d_gate_vec);
   const size_t io = (size_t)cfg.max_tokens * d * sizeof(float);
   ce = cudaMalloc(&reg.d_in, io);
+  if (ce == cudaSuccess) ce = cudaMalloc(&reg.d_out, io);
+  if (ce == cudaSuccess) ce = cudaStreamCreateWithFlags(&reg.stream, cudaStreamNonBlocking);
+  if (ce != cudaSuccess) {
+    release(reg);
+    return (int)ce;
+  }
+  std::lock_guard<std::mutex> lk(g_mu);
+  g_layers.push_back(reg);
+  return (int64_t)g_layers.size() - 1;
+}
+
+int64_t atenia_register_resident_moe_layer(AteniaMoeLayer* layer) {
+  if (!layer) return ATENIA_ERR_NULL;
+  if (!layer->weights_set || layer->cfg.ep_world != 1) return ATENIA_ERR_STATE;
+  Registered reg;
+  reg.layer = layer;
+  reg.owns_layer = false;
+  cudaError_t ce = cudaSetDevice(layer->device);
+  const size_t io = (size_t)layer->cfg.max_tokens * (size_t)layer->cfg.d_model * sizeof(float);
+  if (ce == cudaSuccess) ce = cudaMalloc(&reg.d_in, io);
   if (ce == cudaSuccess) ce = cudaMalloc(&reg.d_out, io);
   if (ce == cudaSuccess) ce = cudaStreamCreateWithFlags(&reg.stream, cudaStreamNonBlocking);
   if (ce != cudaSuccess) {

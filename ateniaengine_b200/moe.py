@@ -251,6 +251,15 @@ def register_real_moe_layer(config, router, gate, up, down, shared=None, shared_
     return int(lid)
 
 
+def register_resident_moe_layer(layer):
+    """Enter a device-resident RealMoeLayer into the registry (register_resident_moe_layer).  The
+    registry borrows the layer; keep the Python object alive while the id is used."""
+    lid = _lib.lib().atenia_register_resident_moe_layer(layer.handle)
+    if lid < 0:
+        raise MoeLayerError("Status", int(lid), _lib.lib().atenia_moe_status_str(C.c_int(int(lid))).decode())
+    return int(lid)
+
+
 def execute_real_moe_layer(layer_id, input, out=None):
     """Flat host f32 [n * d_model] -> [n * d_model], the graph op's contract."""
     inp = np.ascontiguousarray(input, dtype=np.float32).reshape(-1)

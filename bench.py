@@ -1,0 +1,339 @@
+#!/usr/bin/env python
+"""Benchmark of the MoE block: tokens/s through one Mixtral-8x7B-shaped layer.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+                    [--tokens T]
+
+One "step" is one forward of the block over one batch of synthetic tokens (seeded; weights
+N(0, 0.02^2) rounded to bf16, activations N(0, 1), per-expert logit bias N(0, 0.5^2) for load skew).
+At N = 1 the default workload is the Mixtral-8x7B layer at 4096 tokens in bf16.  At N > 1 the experts
+are sharded expert-parallel and every rank routes its own 4096 tokens (weak scaling); launch with
+torchrun, one rank per GPU.
+
+The JSON line carries:
+  value     tokens/s with activations already resident in HBM (CUDA events, max over ranks)
+  e2e       tokens/s through execute_real_moe_layer with pinned HOST f32 buffers, copies included
+  roofline  the routed gate/up + SwiGLU grouped GEMM (the dominant kernel) against the measured bf16 peak
+  cpu_baseline  the CPU oracle (a port of the reference's per-token f64 path) on a bounded token sample
+`--impl reference` times that CPU path alone, on all host threads.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "moe_layer_tokens_per_s"
+UNIT = "tokens/s"
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the routed gate/up kernel, from the ncu
+# capture summarised under profiles/ (scaled to this workload by rows where the capture was smaller).
+NCU_TRAFFIC_BYTES = {}
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            d = json.load(open(p))
+            return {k: float(d[k]) for k in FALLBACK_PEAKS}, "measured"
+        except Exception:
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+    NAMES = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.samples = []
+        self.proc = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) == 6:
+                self.samples.append(parts)
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for s in self.samples:
+            try:
+                sm.append(float(s[0]))
+                mx.append(float(s[1]))
+            except ValueError:
+                continue
+            for name, v in zip(self.NAMES, s[2:]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_oracle_rate(shape, w, x_host, max_seconds, threads=0):
+    """tokens/s of the CPU oracle (f64 accumulation, all host threads) on a bounded token sample."""
+    from oracle import oracle as orc
+    from tests.helpers import oracle_layer
+
+    ol = oracle_layer(shape, w)
+    cores = orc.max_threads() if threads <= 0 else threads
+    n0 = min(x_host.shape[0], max(cores, 4))
+    t = time.perf_counter()
+    ol.forward(x_host[:n0], nthreads=threads)
+    dt = time.perf_counter() - t
+    rate = n0 / dt
+    n = int(min(x_host.shape[0], max(n0, rate * max_seconds)))
+    n = max(cores, n // cores * cores) if n >= cores else n
+    n = min(n, x_host.shape[0])
+    t = time.perf_counter()
+    ol.forward(x_host[:n], nthreads=threads)
+    dt = time.perf_counter() - t
+    return n / dt, cores, n, ol
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="mixtral")
+    ap.add_argument("--tokens", type=int, default=0, help="tokens per rank (default: the workload's)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world > 1:
+        args.gpus = world
+
+    import numpy as np
+    import torch
+
+    from ateniaengine_b200 import synth
+
+    shape = synth.SHAPES[args.workload]
+    T = args.tokens or shape.tokens
+    dtype_name = "int8 weights, bf16 activations (W8A16)" if shape.int8 else "bf16"
+    config = {"workload": f"{shape.name}: d_model={shape.d_model} d_ff={shape.d_ff} experts={shape.num_experts} "
+                          f"top_k={shape.top_k} shared_d_ff={shape.shared_d_ff} tokens_per_rank={T}",
+              "tokens_per_step": T * max(args.gpus, 1),
+              "routing_skew": shape.bias,
+              "parallelism": "single GPU" if args.gpus == 1 else f"expert-parallel ep{args.gpus}, NCCL all-to-all",
+              "l2_policy": "inputs larger than L2: every step streams the expert weights "
+                           f"({3 * shape.d_model * shape.d_ff * shape.num_experts * (1 if shape.int8 else 2) / 1e6:.0f} MB)"}
+
+    # ------------------------------------------------------------------ reference arm (CPU)
+    if args.impl == "reference":
+        if rank != 0:
+            return 0
+        dev = "cuda:0" if torch.cuda.is_available() else "cpu"
+        if dev == "cpu" and shape.int8:
+            print(json.dumps({"impl": "reference", "unavailable": "int8 synthetic weights are quantised on the GPU"}))
+            return 0
+        w = synth.make_weights(shape, 2, dev)
+        x = synth.make_activations(shape, 2, dev, tokens=min(T, 512)).float().cpu().numpy()
+        from oracle import oracle as orc
+        from tests.helpers import oracle_layer
+        ol = oracle_layer(shape, w)
+        del w
+        cores = orc.max_threads()
+        # size one step to about 2 s of CPU work; the sizing run and one more step are the warm-up
+        # (CPU steps have no clocks or caches to settle beyond that)
+        n0 = min(x.shape[0], max(cores, 4))
+        t = time.perf_counter()
+        ol.forward(x[:n0])
+        rate0 = n0 / (time.perf_counter() - t)
+        n = int(min(x.shape[0], max(n0, rate0 * 2.0)))
+        ol.forward(x[:n])
+        t = time.perf_counter()
+        for _ in range(args.steps):
+            ol.forward(x[:n])
+        dt = time.perf_counter() - t
+        val = n * args.steps / dt
+        line = {"metric": METRIC, "value": val, "unit": UNIT, "impl": "reference", "n_gpus": args.gpus,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f64 accumulate",
+                "data": "synthetic", "config": config,
+                "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port",
+                                 "sample": f"{n} tokens per step, CPU oracle (C restatement of the reference's "
+                                           f"per-token f64 path), {cores} OpenMP threads"},
+                "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                "gpu_launches": 0}
+        print(json.dumps(line))
+        return 0
+
+    # ------------------------------------------------------------------ our arm (GPU)
+    import ctypes as C
+
+    import ateniaengine_b200 as ae
+    from ateniaengine_b200 import _lib
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if args.gpus > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    E = shape.num_experts
+    el = E // args.gpus
+    w = synth.make_weights(shape, 2, dev, experts=(rank * el, el))
+    x = synth.make_activations(shape, 2 + rank, dev, tokens=T)
+    layer = synth.build_layer(shape, w, max_tokens=T, ep_rank=rank, ep_world=args.gpus)
+    if args.gpus > 1:
+        nb = _lib.lib().atenia_moe_ep_unique_id_bytes()
+        idt = torch.zeros(nb, dtype=torch.uint8, device=dev)
+        if rank == 0:
+            buf = C.create_string_buffer(nb)
+            _lib.check(_lib.lib().atenia_moe_ep_get_unique_id(buf), "ep_get_unique_id")
+            idt = torch.frombuffer(bytearray(buf.raw), dtype=torch.uint8).to(dev)
+        dist.broadcast(idt, 0)
+        layer.ep_init(bytes(idt.cpu().numpy().tobytes()))
+    out = torch.empty_like(x)
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        layer.forward(x, out=out)
+    layer.check()
+    sync_all()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches0 = _lib.lib().atenia_moe_counter(1)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(args.steps):
+        layer.forward(x, out=out)
+    ev1.record()
+    sync_all()
+    ms = ev0.elapsed_time(ev1) / args.steps
+    launches = int(_lib.lib().atenia_moe_counter(1) - launches0)
+    layer.check()
+    # keep the sampler running over the kernel-timing pass too: short timed regions give few samples
+    if dist is not None:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+
+    # ---- dominant kernel: routed gate/up + SwiGLU grouped GEMM, CUDA events on the launching stream
+    layer.enable_timing(True)
+    g1, g2 = [], []
+    for _ in range(args.steps):
+        layer.forward(x, out=out)
+        torch.cuda.synchronize()
+        g1.append(layer.last_gemm_ms(0))
+        g2.append(layer.last_gemm_ms(1))
+    layer.enable_timing(False)
+    clocks = sampler.stop() if rank == 0 else None
+    gemm1_ms = sum(g1) / len(g1)
+    gemm2_ms = sum(g2) / len(g2)
+
+    if rank != 0:
+        if dist is not None:
+            dist.barrier()
+            dist.destroy_process_group()
+        return 0
+
+    peaks, peak_src = load_peaks()
+    rows = T * shape.top_k  # rows this rank's experts process under uniform sharding
+    flops1 = 4.0 * rows * shape.d_model * shape.d_ff  # gate and up: 2 * 2 * rows * d * F
+    achieved = flops1 / (gemm1_ms * 1e-3) / 1e12
+    roofline = {"bound": "tensor", "kernel": "grouped_gemm_tcgen05_kernel<kSwiGLU> (routed gate/up + SwiGLU)",
+                "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                "frac": achieved / peaks["bf16_tflops"], "peak_source": f"{peak_src} (burst cuBLAS bf16)",
+                "traffic": NCU_TRAFFIC_BYTES.get(f"{shape.name}:{T}"),
+                "launch_ms": gemm1_ms, "down_gemm_ms": gemm2_ms,
+                "down_gemm_tflops": 2.0 * rows * shape.d_model * shape.d_ff / (gemm2_ms * 1e-3) / 1e12,
+                "layer_frac_of_tensor_roofline": (T * shape.top_k * 6.0 * shape.d_model * shape.d_ff +
+                                                  T * 6.0 * shape.d_model * shape.shared_d_ff) /
+                                                 (ms * 1e-3) / 1e12 / peaks["bf16_tflops"]}
+
+    # ---- end to end through the operator registry with pinned host buffers (N = 1 only)
+    e2e = None
+    if args.gpus == 1:
+        lid = ae.register_resident_moe_layer(layer)
+        hin = torch.empty((T, shape.d_model), dtype=torch.float32).pin_memory()
+        hin.copy_(x.float().cpu())
+        hout = torch.empty_like(hin).pin_memory()
+        from ateniaengine_b200.moe import execute_real_moe_layer_ptr
+        nfl = T * shape.d_model
+        for _ in range(3):
+            rc = execute_real_moe_layer_ptr(lid, hin.data_ptr(), nfl, hout.data_ptr())
+            _lib.check(rc, "execute_real_moe_layer")
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            rc = execute_real_moe_layer_ptr(lid, hin.data_ptr(), nfl, hout.data_ptr())
+        torch.cuda.synchronize()
+        dt = (time.perf_counter() - t0) / args.steps
+        _lib.check(rc, "execute_real_moe_layer")
+        assert torch.isfinite(hout).all()
+        e2e = {"value": T / dt, "unit": UNIT, "h2d_bytes_per_step": nfl * 4, "d2h_bytes_per_step": nfl * 4,
+               "ms_per_step": dt * 1e3, "api": "atenia_execute_real_moe_layer (host f32 in/out, pinned)"}
+
+    # ---- CPU baseline on a bounded sample (N = 1 only)
+    cpu = None
+    if args.gpus == 1 and not args.no_cpu_baseline:
+        xs = x[: min(T, 512)].float().cpu().numpy()
+        rate, cores, n, _ = cpu_oracle_rate(shape, w, xs, args.cpu_seconds)
+        cpu = {"value": rate, "unit": UNIT, "cores": cores, "kind": "port",
+               "sample": f"{n} of the step's {T} tokens, CPU oracle (C restatement of the reference's per-token "
+                         f"f64 path), {cores} OpenMP threads"}
+
+    value = T * args.gpus / (ms * 1e-3)
+    line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": dtype_name, "data": "synthetic", "config": config,
+            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks, "gpu_launches": launches,
+            "tensor_core_launches_per_step": 2 + (2 if shape.shared_d_ff else 0)}
+    print(json.dumps(line))
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

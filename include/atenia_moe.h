@@ -12,6 +12,7 @@
  *   MoeDenseLayer::route + top_k_routing src/moe/dense.rs:325-337,
  *                                        src/moe/sparse.rs:142-191 atenia_moe_route_from_logits
  *   register_real_moe_layer              src/moe/graph_op.rs:228   atenia_register_real_moe_layer
+ *   register_resident_moe_layer          src/moe/graph_op.rs:237   atenia_register_resident_moe_layer
  *   execute_real_moe_layer               src/moe/graph_op.rs:327   atenia_execute_real_moe_layer
  *   quantize_per_row_i8                  src/tensor/disk_tier.rs:231-245  atenia_quantize_per_row_i8
  *
@@ -168,6 +169,12 @@ typedef struct AteniaHostMoeLayer {
 /* register_real_moe_layer: returns the new layer id (>= 0; ids are append-only and stable for the
  * process) or a negative status. */
 ATENIA_API int64_t atenia_register_real_moe_layer(const AteniaHostMoeLayer* layer);
+
+/* register_resident_moe_layer (src/moe/graph_op.rs:237): enter an existing device layer, whose
+ * weights are already resident in HBM, into the registry.  The registry borrows the layer: the
+ * caller keeps ownership and must not destroy it while the id is in use.  Returns the id or a
+ * negative status. */
+ATENIA_API int64_t atenia_register_resident_moe_layer(AteniaMoeLayer* layer);
 
 /* execute_real_moe_layer: `input` is a flat HOST [n * d_model] f32 batch, `output` receives
  * [n * d_model] f32.  Rows are independent.  Unknown id -> ATENIA_ERR_LAYER_NOT_FOUND; a length that
