@@ -280,3 +280,18 @@ def execute_real_moe_layer_ptr(layer_id, in_ptr, n_floats, out_ptr):
     """Same call on raw host pointers (e.g. pinned buffers); returns the status."""
     return _lib.lib().atenia_execute_real_moe_layer(int(layer_id), C.c_void_p(in_ptr), n_floats,
                                                     C.c_void_p(out_ptr))
+
+
+def dispatch_noalloc(topk_idx, num_experts, perm, inv_perm, expert_offsets):
+    """Dispatch order of a routed batch through the entry point that allocates nothing.
+
+    For hosts that cannot allocate device memory (everything already sits in the host runtime's
+    pool, or an allocation's synchronisation is not acceptable) and so cannot hold a RealMoeLayer.
+    All five tensors are the caller's: topk_idx [T, k] int32 in, perm / inv_perm [T*k] and
+    expert_offsets [E+1] int32 out.  Limits: T*k <= 65536 and E <= 128.  Returns the status code.
+    """
+    T, k = topk_idx.shape
+    with torch.cuda.device(topk_idx.device):
+        st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+        return _lib.lib().atenia_moe_dispatch_noalloc(_ptr(topk_idx), T, k, int(num_experts), _ptr(perm),
+                                                      _ptr(inv_perm), _ptr(expert_offsets), st)

@@ -53,6 +53,7 @@ extern "C" {
 #define ATENIA_ERR_ROUTING (-9)         /* non-finite routing weight or selected sum <= 0 (MoeSparseError) */
 #define ATENIA_ERR_NCCL (-10)           /* an NCCL call failed */
 #define ATENIA_ERR_DRIVER (-11)         /* tensor-map encode or driver entry point unavailable */
+#define ATENIA_ERR_SCRATCH_LIMIT (-12)  /* request larger than the fixed scratch of atenia_moe_dispatch_noalloc */
 
 /* ---- enums -------------------------------------------------------------------------------- */
 #define ATENIA_IO_BF16 0 /* activations as bf16 (high half of an f32, src/tensor/tensor.rs:294-308) */
@@ -142,6 +143,26 @@ ATENIA_API int atenia_moe_check(AteniaMoeLayer* layer, void* stream);
 ATENIA_API int atenia_moe_route_from_logits(AteniaMoeLayer* layer, const float* logits, int T,
                                             int32_t* topk_idx, float* topk_w, int32_t* perm,
                                             int32_t* inv_perm, int32_t* expert_offsets, void* stream);
+
+/* Dispatch order without any allocation.  (No counterpart in the reference: it exists for hosts
+ * that cannot call cudaMalloc -- all device memory already belongs to the host runtime's own pool,
+ * an allocation's device-wide synchronisation is not acceptable, or the caller is only allowed to
+ * touch the buffers it is handed -- and that therefore cannot create an AteniaMoeLayer.)
+ * Given topk_idx [T, k] (device, expert ids in [0, E), ascending per token) it writes the same
+ * perm [T*k], inv_perm [T*k] and expert_offsets [E+1] (all device, all required) as
+ * atenia_moe_route_from_logits.  Scratch is a fixed 256 KiB array inside the library, present on
+ * every GPU that loads it; hence the limits T*k <= ATENIA_NOALLOC_MAX_ENTRIES and
+ * E <= ATENIA_NOALLOC_MAX_EXPERTS, beyond which the call returns ATENIA_ERR_SCRATCH_LIMIT and does
+ * nothing.  Entries whose expert id is out of range are skipped.  Asynchronous on `stream`; the
+ * library calls no cudaMalloc / cudaFree / allocating routine here.
+ * The first call on each device looks up the array's device address; make that first call
+ * outside any stream capture.  All calls on one GPU share the array: two calls whose kernels can
+ * overlap on that GPU (different streams without ordering, or different host threads) race on it;
+ * order them on one stream or with events. */
+#define ATENIA_NOALLOC_MAX_ENTRIES 65536
+#define ATENIA_NOALLOC_MAX_EXPERTS 128
+ATENIA_API int atenia_moe_dispatch_noalloc(const int32_t* topk_idx, int T, int k, int E, int32_t* perm,
+                                           int32_t* inv_perm, int32_t* expert_offsets, void* stream);
 
 /* Per-row symmetric int8 quantisation of a row-major [rows, cols] f32 device matrix:
  * scale = max|row| / 127 (1.0 for a zero row), q = clamp(round_half_away(w * (1/scale)), -127, 127).
