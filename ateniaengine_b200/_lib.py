@@ -52,7 +52,7 @@ EXPORTS = [
     "atenia_quantize_per_row_i8", "atenia_register_real_moe_layer", "atenia_register_resident_moe_layer", "atenia_execute_real_moe_layer",
     "atenia_get_real_moe_layer", "atenia_moe_ep_unique_id_bytes", "atenia_moe_ep_get_unique_id",
     "atenia_moe_ep_init", "atenia_moe_status_str", "atenia_moe_counter", "atenia_moe_enable_timing",
-    "atenia_moe_last_gemm_ms", "atenia_moe_dispatch_noalloc",
+    "atenia_moe_last_gemm_ms", "atenia_moe_dispatch_noalloc", "atenia_moe_ep_plan",
 ]
 
 _lib = None

@@ -76,20 +76,10 @@ int ep_forward_exchange(AteniaMoeLayer* L, int T, cudaStream_t s) {
   count_launch();
   ATENIA_CUDA_TRY(cudaStreamSynchronize(s));
   std::vector<int64_t> s_off(G), s_cnt(G), r_off(G), r_cnt(G);
-  int64_t so = 0, ro = 0;
-  for (int p = 0; p < G; ++p) {
-    int64_t sc = 0, rc = 0;
-    for (int j = 0; j < El; ++j) {
-      sc += L->h_counts_all[(size_t)rank * E + p * El + j];
-      rc += L->h_counts_all[(size_t)p * E + L->e_begin + j];
-    }
-    s_off[p] = so;
-    s_cnt[p] = sc;
-    r_off[p] = ro;
-    r_cnt[p] = rc;
-    so += sc;
-    ro += rc;
-  }
+  int64_t ro = 0;
+  int prc = atenia_moe_ep_plan(L->h_counts_all, G, E, rank, s_off.data(), s_cnt.data(), r_off.data(),
+                               r_cnt.data(), nullptr, &ro);
+  if (prc) return prc;
   if (ro > L->recv_cap) return ATENIA_ERR_CAPACITY;
   int rc = exchange(comm, rank, G, L->x_perm, s_off, s_cnt, L->recv_x, r_off, r_cnt, d, s);
   if (rc) return rc;
@@ -109,6 +99,34 @@ void ep_destroy(AteniaMoeLayer* L) {
 }  // namespace atenia
 
 extern "C" {
+
+// Exchange plan of one rank, from the all-gathered count matrix.  Pure host arithmetic.
+int atenia_moe_ep_plan(const int32_t* counts_all, int world, int num_experts, int rank, int64_t* send_off,
+                       int64_t* send_cnt, int64_t* recv_off, int64_t* recv_cnt, int64_t* group_offsets,
+                       int64_t* total_recv) {
+  if (!counts_all || !send_off || !send_cnt || !recv_off || !recv_cnt) return ATENIA_ERR_NULL;
+  if (world < 1 || num_experts < 1 || num_experts % world || rank < 0 || rank >= world) return ATENIA_ERR_SHAPE;
+  const int El = num_experts / world, e_begin = rank * El;
+  int64_t so = 0, ro = 0;
+  for (int p = 0; p < world; ++p) {
+    int64_t sc = 0, rc = 0;
+    for (int j = 0; j < El; ++j) {
+      sc += counts_all[(size_t)rank * num_experts + p * El + j];
+      const int32_t c = counts_all[(size_t)p * num_experts + e_begin + j];
+      if (group_offsets) group_offsets[p * El + j] = ro + rc;
+      rc += c;
+    }
+    send_off[p] = so;
+    send_cnt[p] = sc;
+    recv_off[p] = ro;
+    recv_cnt[p] = rc;
+    so += sc;
+    ro += rc;
+  }
+  if (group_offsets) group_offsets[world * El] = ro;
+  if (total_recv) *total_recv = ro;
+  return ATENIA_OK;
+}
 
 int atenia_moe_ep_unique_id_bytes(void) { return (int)sizeof(ncclUniqueId); }
 

@@ -12,10 +12,6 @@
 namespace atenia {
 namespace {
 
-constexpr int kTokPerWarp = 8;
-constexpr int kWarps = 4;
-constexpr int kTokPerBlock = kTokPerWarp * kWarps;  // 32
-constexpr int kChunk = 64;                          // k elements staged per step
 constexpr int kMaxK = 8;
 
 // softmax + top-k for one token, executed by one thread.  `lg` holds E f32 logits (stride 1).
@@ -69,74 +65,230 @@ __device__ int route_one(const float* lg, int E, int k, int renormalize, int32_t
   return 0;
 }
 
+// Softmax + top-k for one token by one warp.  `lg` holds E f32 logits in shared memory.
+// Follows the reference's sequence: f32 maximum, exp((f64)(v - max)) with the subtraction in f32,
+// the f64 sum accumulated in ascending expert order by one lane, f32 weights, then k rounds of
+// "largest weight, lowest index" and a renormalisation summed in ascending index order.
+template <int EPL>
+__device__ __forceinline__ int route_one_warp(const float* lg, int E, int k, int renormalize, int lane,
+                                              int32_t* idx_out, float* w_out, double* exps /* smem, E */) {
+  float mx = -INFINITY;
+  bool finite = true;
+#pragma unroll
+  for (int j = 0; j < EPL; ++j) {
+    int e = lane + 32 * j;
+    if (e < E) {
+      float v = lg[e];
+      if (!isfinite(v)) finite = false;
+      mx = fmaxf(mx, v);
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  if (__any_sync(0xffffffffu, !finite)) return ATENIA_ERR_ROUTING;
+  double ex[EPL];
+#pragma unroll
+  for (int j = 0; j < EPL; ++j) {
+    int e = lane + 32 * j;
+    ex[j] = 0.0;
+    if (e < E) {
+      ex[j] = exp((double)__fsub_rn(lg[e], mx));
+      exps[e] = ex[j];
+    }
+  }
+  __syncwarp();
+  double sum = 0.0;
+  if (lane == 0)
+    for (int e = 0; e < E; ++e) sum += exps[e];
+  sum = __shfl_sync(0xffffffffu, sum, 0);
+  const double inv = sum > 0.0 ? 1.0 / sum : 0.0;
+  float p[EPL];
+  bool taken[EPL];
+#pragma unroll
+  for (int j = 0; j < EPL; ++j) {
+    p[j] = (float)(ex[j] * inv);
+    taken[j] = (lane + 32 * j) >= E;  // slots past E never compete
+  }
+  for (int s = 0; s < k; ++s) {
+    float bw = -1.0f;  // weights are >= 0
+    int bi = 0x7fffffff;
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) {
+      if (!taken[j] && p[j] > bw) {  // ascending j = ascending index: strict > keeps the lower one
+        bw = p[j];
+        bi = lane + 32 * j;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      float ow = __shfl_xor_sync(0xffffffffu, bw, o);
+      int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ow > bw || (ow == bw && oi < bi)) {
+        bw = ow;
+        bi = oi;
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < EPL; ++j)
+      if (lane + 32 * j == bi) taken[j] = true;
+  }
+  // selected experts in ascending order: rank of each selected slot among the selected
+  int m_before = 0;
+  double ssum = 0.0;
+#pragma unroll
+  for (int j = 0; j < EPL; ++j) {
+    bool sel = taken[j] && (lane + 32 * j) < E;
+    unsigned mask = __ballot_sync(0xffffffffu, sel);
+    int rank = m_before + __popc(mask & ((1u << lane) - 1u));
+    if (sel) {
+      idx_out[rank] = lane + 32 * j;
+      exps[rank] = (double)p[j];  // reuse as the selected-weight list (ascending index)
+    }
+    m_before += __popc(mask);
+  }
+  __syncwarp();
+  if (lane == 0)
+    for (int s = 0; s < k; ++s) ssum += exps[s];
+  ssum = __shfl_sync(0xffffffffu, ssum, 0);
+  if (!(ssum > 0.0)) return ATENIA_ERR_ROUTING;
+  const double scale = renormalize ? 1.0 / ssum : 1.0;
+  if (lane < k) w_out[lane] = (float)(exps[lane] * scale);
+  __syncwarp();
+  return 0;
+}
+
+// Router kernel.  One CTA (8 warps) handles TOK tokens.
+//   * per chunk of KC values of k, the CTA stages x[TOK, KC] as f64 ([k][token]: one 16-byte load
+//     gives two tokens at one k) and W_router[E, KC] transposed as f32 ([k][expert]) in shared memory,
+//     so global memory is read with full sectors and every operand of the inner loop is a
+//     conflict-free shared-memory read;
+//   * warp w owns the k-slice [w*KC/8, (w+1)*KC/8) of the chunk; lane l owns experts (l % EL) + EL*j
+//     and the contiguous sub-slice l / EL of its warp's slice; it accumulates TOK tokens x EPL experts
+//     in f64;
+//   * the sub-slices are folded with shuffles inside a warp and through shared memory across warps
+//     (one warp after the other, a fixed order);
+//   * the warps then route the tokens (route_one_warp).
 // E_T: experts rounded up to a power of two in {8,16,32,64,128}.
-// Lane l of a warp owns experts (l % EL) + EL*j, j < EPL, and the k-slice l / EL of KS slices.
-template <int E_T>
-__global__ void __launch_bounds__(kWarps * 32) router_kernel(RouterArgs a) {
+constexpr int kRWarps = 8;
+
+template <int E_T, int TOK>
+struct RouterSmem {
+  static constexpr int KC = E_T >= 128 ? 64 : 128;
+  static constexpr int kXs = KC * TOK * 8;
+  static constexpr int kWs = KC * E_T * 4;
+  static constexpr int kAcc = TOK * (E_T + 1) * 8;
+  static constexpr int kLg = TOK * E_T * 4;
+  static constexpr int kExps = TOK * E_T * 8;
+  static constexpr int kGate = kRWarps * TOK * 8;
+  static constexpr int kSel = TOK * kMaxK * 8;
+  static constexpr int kLoop = kXs + kWs;
+  static constexpr int kTail = kAcc + kLg + kExps + kGate + kSel;
+  static constexpr int kBytes = kLoop > kTail ? kLoop : kTail;
+};
+
+template <int E_T, int TOK>
+__global__ void __launch_bounds__(kRWarps * 32) router_kernel(RouterArgs a) {
+  using SM = RouterSmem<E_T, TOK>;
+  constexpr int KC = SM::KC;
   constexpr int EL = E_T < 32 ? E_T : 32;
   constexpr int KS = 32 / EL;
   constexpr int EPL = E_T / EL;
-  __shared__ double xs[kTokPerBlock][kChunk + 1];  // +1: the token-major reads below stay conflict-light
-  __shared__ float lg_s[kTokPerBlock][E_T];
+  constexpr int SLICE = KC / kRWarps;  // k values per warp per chunk
+  constexpr int KPL = SLICE / KS;      // k values per lane per chunk
+  static_assert(KPL >= 1, "chunk too small for this expert count");
+  __shared__ __align__(16) unsigned char smem[SM::kBytes];
+  // main-loop view
+  double (*xs)[TOK] = reinterpret_cast<double (*)[TOK]>(smem);
+  float (*ws)[E_T] = reinterpret_cast<float (*)[E_T]>(smem + SM::kXs);
+  // tail view (after the last __syncthreads of the loop)
+  double (*acc_s)[E_T + 1] = reinterpret_cast<double (*)[E_T + 1]>(smem);
+  float (*lg_s)[E_T] = reinterpret_cast<float (*)[E_T]>(smem + SM::kAcc);
+  double (*exps_s)[E_T] = reinterpret_cast<double (*)[E_T]>(smem + SM::kAcc + SM::kLg);
+  double (*gate_s)[TOK] = reinterpret_cast<double (*)[TOK]>(smem + SM::kAcc + SM::kLg + SM::kExps);
+  int32_t (*idx_s)[kMaxK] = reinterpret_cast<int32_t (*)[kMaxK]>(smem + SM::kAcc + SM::kLg + SM::kExps + SM::kGate);
+  float (*w_s)[kMaxK] = reinterpret_cast<float (*)[kMaxK]>(smem + SM::kAcc + SM::kLg + SM::kExps + SM::kGate +
+                                                          TOK * kMaxK * 4);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t_block = blockIdx.x * kTokPerBlock;
-  const int t_warp = t_block + warp * kTokPerWarp;
+  const int t0 = blockIdx.x * TOK;
   const int e_lane = lane % EL;
   const int ks = lane / EL;
   const int d = a.d, E = a.E;
 
-  double acc[kTokPerWarp][EPL];
+  double acc[TOK][EPL];
 #pragma unroll
-  for (int t = 0; t < kTokPerWarp; ++t)
+  for (int t = 0; t < TOK; ++t)
 #pragma unroll
     for (int j = 0; j < EPL; ++j) acc[t][j] = 0.0;
-  double gacc[kTokPerWarp];
-#pragma unroll
-  for (int t = 0; t < kTokPerWarp; ++t) gacc[t] = 0.0;
+  double gacc = 0.0;  // lane t (< TOK) of every warp accumulates the gate dot product of token t
 
-  for (int k0 = 0; k0 < d; k0 += kChunk) {
-    const int kc = min(kChunk, d - k0);
+  for (int k0 = 0; k0 < d; k0 += KC) {
     __syncthreads();
-    // stage x[t_block .. +32, k0 .. +kc] as f64
-    for (int i = threadIdx.x; i < kTokPerBlock * kChunk; i += blockDim.x) {
-      int t = i / kChunk, c = i - t * kChunk;
-      double v = 0.0;
-      int tg = t_block + t;
-      if (tg < a.T && c < kc) {
-        size_t off = (size_t)tg * d + k0 + c;
-        v = a.x_is_f32 ? (double)static_cast<const float*>(a.x)[off]
-                       : (double)__bfloat162float(static_cast<const __nv_bfloat16*>(a.x)[off]);
+    // stage x: each thread converts 8 consecutive k of one token; neighbouring threads take
+    // neighbouring tokens so the f64 stores fall in distinct banks
+    for (int i = threadIdx.x; i < TOK * (KC / 8); i += blockDim.x) {
+      const int g = i / TOK, t = i - g * TOK;
+      const int kk = k0 + g * 8;
+      const int tg = t0 + t;
+      float v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = 0.f;
+      if (tg < a.T && kk < d) {  // d is a multiple of 16, so a group of 8 is all in or all out
+        if (a.x_is_f32) {
+          const float4* p = reinterpret_cast<const float4*>(static_cast<const float*>(a.x) + (size_t)tg * d + kk);
+          float4 u0 = p[0], u1 = p[1];
+          v[0] = u0.x; v[1] = u0.y; v[2] = u0.z; v[3] = u0.w;
+          v[4] = u1.x; v[5] = u1.y; v[6] = u1.z; v[7] = u1.w;
+        } else {
+          const uint4 u = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(a.x) + (size_t)tg * d + kk);
+          v[0] = bf16lo(u.x); v[1] = bf16hi(u.x); v[2] = bf16lo(u.y); v[3] = bf16hi(u.y);
+          v[4] = bf16lo(u.z); v[5] = bf16hi(u.z); v[6] = bf16lo(u.w); v[7] = bf16hi(u.w);
+        }
       }
-      xs[t][c] = v;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) xs[g * 8 + j][t] = (double)v[j];
+    }
+    // stage W transposed: a thread reads 4 consecutive k of one expert row (a float4); neighbouring
+    // threads take neighbouring experts so the transposed stores fall in distinct banks
+    for (int i = threadIdx.x; i < E_T * (KC / 4); i += blockDim.x) {
+      const int g = i / E_T, e = i - g * E_T;
+      const int kk = k0 + g * 4;
+      float4 u = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (e < E && kk < d) u = __ldg(reinterpret_cast<const float4*>(a.w_router + (size_t)e * d + kk));
+      ws[g * 4 + 0][e] = u.x;
+      ws[g * 4 + 1][e] = u.y;
+      ws[g * 4 + 2][e] = u.z;
+      ws[g * 4 + 3][e] = u.w;
     }
     __syncthreads();
-    // this lane's k values: c = ks, ks + KS, ...
-    for (int c = ks; c < kc; c += KS) {
+    const int kbase = warp * SLICE + ks * KPL;  // within the chunk; rows past d hold zeros
+#pragma unroll 4
+    for (int c = 0; c < KPL; ++c) {
+      const int kc = kbase + c;
       double w[EPL];
 #pragma unroll
-      for (int j = 0; j < EPL; ++j) {
-        int e = e_lane + EL * j;
-        w[j] = e < E ? (double)__ldg(a.w_router + (size_t)e * d + k0 + c) : 0.0;
-      }
+      for (int j = 0; j < EPL; ++j) w[j] = (double)ws[kc][e_lane + EL * j];
+      const double2* xr = reinterpret_cast<const double2*>(&xs[kc][0]);
 #pragma unroll
-      for (int t = 0; t < kTokPerWarp; ++t) {
-        double xv = xs[warp * kTokPerWarp + t][c];
+      for (int t2 = 0; t2 < TOK / 2; ++t2) {
+        const double2 xv = xr[t2];
 #pragma unroll
-        for (int j = 0; j < EPL; ++j) acc[t][j] = fma(w[j], xv, acc[t][j]);
+        for (int j = 0; j < EPL; ++j) {
+          acc[2 * t2][j] = fma(w[j], xv.x, acc[2 * t2][j]);
+          acc[2 * t2 + 1][j] = fma(w[j], xv.y, acc[2 * t2 + 1][j]);
+        }
       }
     }
-    if (a.gate_vec) {
-      for (int c = lane; c < kc; c += 32) {
-        double gv = (double)__ldg(a.gate_vec + k0 + c);
-#pragma unroll
-        for (int t = 0; t < kTokPerWarp; ++t) gacc[t] = fma(gv, xs[warp * kTokPerWarp + t][c], gacc[t]);
+    if (a.gate_vec && lane < TOK) {
+      for (int c = 0; c < SLICE; ++c) {
+        const int kc = warp * SLICE + c;
+        if (k0 + kc < d) gacc = fma((double)__ldg(a.gate_vec + k0 + kc), xs[kc][lane], gacc);
       }
     }
   }
-  // reduce the k-slices (lanes with equal e_lane)
+  // fold the k sub-slices inside the warp
 #pragma unroll
-  for (int t = 0; t < kTokPerWarp; ++t) {
+  for (int t = 0; t < TOK; ++t) {
 #pragma unroll
     for (int j = 0; j < EPL; ++j) {
       double v = acc[t][j];
@@ -144,55 +296,54 @@ __global__ void __launch_bounds__(kWarps * 32) router_kernel(RouterArgs a) {
       for (int o = EL; o < 32; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
       acc[t][j] = v;
     }
-    if (a.gate_vec) {
-      double v = gacc[t];
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-      gacc[t] = v;
-    }
   }
-  if (ks == 0) {
+  __syncthreads();  // the loop's shared-memory view is dead from here on
+  // fold the warps, one after the other
+  for (int w = 0; w < kRWarps; ++w) {
+    if (warp == w && ks == 0) {
 #pragma unroll
-    for (int t = 0; t < kTokPerWarp; ++t)
+      for (int t = 0; t < TOK; ++t)
 #pragma unroll
-      for (int j = 0; j < EPL; ++j) {
-        int e = e_lane + EL * j;
-        if (e < E) {
-          double v = acc[t][j];
-          if (a.bias) v += (double)a.bias[e];
-          lg_s[warp * kTokPerWarp + t][e] = (float)v;
+        for (int j = 0; j < EPL; ++j) {
+          const int e = e_lane + EL * j;
+          if (e < E) acc_s[t][e] = (w == 0 ? 0.0 : acc_s[t][e]) + acc[t][j];
         }
-      }
+    }
+    __syncthreads();
   }
-  if (a.gate_vec && a.gate_scale && lane < kTokPerWarp) {
-    // every lane holds all eight sums after the butterfly; lane t writes token t
-    double v = 0.0;
-#pragma unroll
-    for (int t = 0; t < kTokPerWarp; ++t)
-      if (lane == t) v = gacc[t];
-    int tg = t_warp + lane;
-    if (tg < a.T) a.gate_scale[tg] = (float)(1.0 / (1.0 + exp(-v)));
+  if (a.gate_vec && lane < TOK) gate_s[warp][lane] = gacc;
+  // logits: bias joins the f64 sum before the rounding to f32
+  for (int i = threadIdx.x; i < TOK * E; i += blockDim.x) {
+    const int t = i / E, e = i - t * E;
+    double v = acc_s[t][e];
+    if (a.bias) v += (double)a.bias[e];
+    const float f = (float)v;
+    lg_s[t][e] = f;
+    const int tg = t0 + t;
+    if (a.logits && tg < a.T) a.logits[(size_t)tg * E + e] = f;
   }
   __syncthreads();
-  if (threadIdx.x < kTokPerBlock) {
-    int tg = t_block + threadIdx.x;
-    if (tg < a.T) {
-      int32_t idx[kMaxK];
-      float w[kMaxK];
-      if (a.logits)
-        for (int e = 0; e < E; ++e) a.logits[(size_t)tg * E + e] = lg_s[threadIdx.x][e];
-      int rc = route_one(lg_s[threadIdx.x], E, a.k, a.renormalize, idx, w, lg_s[threadIdx.x]);
-      if (rc) {
-        report_error(a.err, rc, 1000);
-        for (int s = 0; s < a.k; ++s) {  // keep downstream kernels in bounds
-          idx[s] = s;
-          w[s] = 0.f;
-        }
+  if (a.gate_vec && a.gate_scale && threadIdx.x < TOK) {
+    const int t = threadIdx.x, tg = t0 + t;
+    double v = 0.0;
+    for (int w = 0; w < kRWarps; ++w) v += gate_s[w][t];
+    if (tg < a.T) a.gate_scale[tg] = (float)(1.0 / (1.0 + exp(-v)));
+  }
+  for (int t = warp; t < TOK; t += kRWarps) {
+    const int tg = t0 + t;
+    if (tg >= a.T) continue;
+    int rc = route_one_warp<(E_T + 31) / 32>(lg_s[t], E, a.k, a.renormalize, lane, idx_s[t], w_s[t], exps_s[t]);
+    if (rc) {
+      if (lane == 0) report_error(a.err, rc, 1000);
+      if (lane < a.k) {  // keep downstream kernels in bounds
+        idx_s[t][lane] = lane;
+        w_s[t][lane] = 0.f;
       }
-      for (int s = 0; s < a.k; ++s) {
-        a.topk_idx[(size_t)tg * a.k + s] = idx[s];
-        a.topk_w[(size_t)tg * a.k + s] = w[s];
-      }
+    }
+    __syncwarp();
+    if (lane < a.k) {
+      a.topk_idx[(size_t)tg * a.k + lane] = idx_s[t][lane];
+      a.topk_w[(size_t)tg * a.k + lane] = w_s[t][lane];
     }
   }
 }
@@ -224,12 +375,13 @@ __global__ void route_from_logits_kernel(const float* __restrict__ logits, int T
 int launch_router(const RouterArgs& a, cudaStream_t s) {
   if (a.T <= 0) return ATENIA_OK;
   if (a.k > kMaxK || a.E > 128) return ATENIA_ERR_UNSUPPORTED;
-  dim3 grid((a.T + kTokPerBlock - 1) / kTokPerBlock), block(kWarps * 32);
-  if (a.E <= 8) router_kernel<8><<<grid, block, 0, s>>>(a);
-  else if (a.E <= 16) router_kernel<16><<<grid, block, 0, s>>>(a);
-  else if (a.E <= 32) router_kernel<32><<<grid, block, 0, s>>>(a);
-  else if (a.E <= 64) router_kernel<64><<<grid, block, 0, s>>>(a);
-  else router_kernel<128><<<grid, block, 0, s>>>(a);
+  dim3 block(kRWarps * 32);
+  // more tokens per CTA for many experts: the router matrix is re-read once per CTA
+  if (a.E <= 8) router_kernel<8, 8><<<(a.T + 7) / 8, block, 0, s>>>(a);
+  else if (a.E <= 16) router_kernel<16, 8><<<(a.T + 7) / 8, block, 0, s>>>(a);
+  else if (a.E <= 32) router_kernel<32, 8><<<(a.T + 7) / 8, block, 0, s>>>(a);
+  else if (a.E <= 64) router_kernel<64, 16><<<(a.T + 15) / 16, block, 0, s>>>(a);
+  else router_kernel<128, 16><<<(a.T + 15) / 16, block, 0, s>>>(a);
   count_launch();
   return (int)cudaGetLastError();
 }

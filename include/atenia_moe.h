@@ -220,6 +220,18 @@ ATENIA_API int atenia_moe_ep_get_unique_id(void* id_out);
  * selected experts, runs the local experts and exchanges the results back. */
 ATENIA_API int atenia_moe_ep_init(AteniaMoeLayer* layer, const void* unique_id);
 
+/* The exchange plan one rank derives from the all-gathered count matrix counts_all[world][E]
+ * (rows rank p holds for expert e, in p's dispatch order).  Experts are owned contiguously:
+ * expert e lives on rank e / (E / world).  Pure host arithmetic (no CUDA, no NCCL); exported so the
+ * partition can be tested without GPUs.  Outputs (host arrays of `world` entries; rows, not bytes):
+ *   send_off/send_cnt[p]  slice of this rank's dispatch-ordered rows bound for rank p
+ *   recv_off/recv_cnt[p]  where rank p's rows land in this rank's receive buffer
+ *   group_offsets[world * E/world + 1] (may be NULL) first receive-buffer row of each
+ *                         (source rank, local expert) group, in buffer order; total_recv may be NULL */
+ATENIA_API int atenia_moe_ep_plan(const int32_t* counts_all, int world, int num_experts, int rank,
+                                  int64_t* send_off, int64_t* send_cnt, int64_t* recv_off, int64_t* recv_cnt,
+                                  int64_t* group_offsets, int64_t* total_recv);
+
 /* ---- diagnostics -------------------------------------------------------------------------- */
 ATENIA_API const char* atenia_moe_status_str(int status);
 
