@@ -113,6 +113,7 @@ struct GroupedGemmArgs {
   const float* const* scale1;
   DeviceError* err;
   int max_rows;  // upper bound on total rows (sizes nothing; used by the checking kernel's grid)
+  int w8;        // B matrices are int8 (tensor maps of bytes), widened to bf16 inside the kernel
 };
 int launch_grouped_gemm_tcgen05(const GroupedGemmArgs& a, int num_sms, cudaStream_t s);
 
@@ -132,7 +133,7 @@ struct GroupedGemmCheckArgs {
 };
 int launch_grouped_gemm_check(const GroupedGemmCheckArgs& a, cudaStream_t s);
 
-// dst[r, c] = bf16((float)q[r, c] * scale[r])  -- widening pass used by the INT8 path
+// dst[r, c] = bf16((float)q[r, c] * scale[r])  (scale may be null: plain widening)
 int launch_dequant_rows(const int8_t* q, const float* scales, int64_t rows, int64_t cols,
                         __nv_bfloat16* dst, cudaStream_t s);
 int launch_f32_to_bf16(const float* src, __nv_bfloat16* dst, int64_t n, cudaStream_t s);
@@ -140,5 +141,8 @@ int launch_f32_to_bf16(const float* src, __nv_bfloat16* dst, int64_t n, cudaStre
 // Tensor-map encoding through the driver entry point (no link-time dependency on libcuda).
 int encode_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols,
                         uint32_t box_rows, uint32_t box_cols);
+// int8 matrix [rows, cols], unswizzled box (the widening warps read it with plain 16-byte loads)
+int encode_tmap_2d_u8(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
+                      uint32_t box_cols);
 
 }  // namespace atenia

@@ -15,6 +15,12 @@
 // The accumulator is double buffered (2 x 256 TMEM columns), so the epilogue of tile i overlaps the
 // main loop of tile i+1.
 //
+// INT8 weights (W8A16, template flag W8): the weight tiles arrive by TMA as int8 (16 KiB per stage
+// instead of 32), four extra warps widen them to bf16 in registers and write the 128B-swizzled
+// operand tile the MMA reads; the per-row scale multiplies the f32 accumulator column in the
+// epilogue ((q*s).x = s*(q.x) exactly, and |q| <= 127 is exact in bf16).  HBM and L2 see one byte per
+// weight.
+//
 // Every wait is bounded: a wait that runs out records ATENIA_ERR_DEVICE_TIMEOUT with a site id and
 // the CTA leaves its loops, waits (bounded) for its own TMA copies, frees TMEM and returns.
 #include "common.cuh"
@@ -35,6 +41,15 @@ constexpr int B_HALF_BYTES = B_STAGE_BYTES / 2; // 16 KiB
 constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
 constexpr int NUM_THREADS = 192;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+// W8A16 variant: TMA ring of {A bf16 16 KiB, B int8 16 KiB} x 3 and a ring of widened bf16 B tiles x 3.
+constexpr int Q_STAGE_BYTES = BN * BK;               // 16 KiB of int8
+constexpr int Q_HALF_BYTES = Q_STAGE_BYTES / 2;
+constexpr int W8_STAGE_BYTES = A_STAGE_BYTES + Q_STAGE_BYTES;  // 32 KiB
+constexpr int W8_STAGES = 3;
+constexpr int CONV_STAGES = 3;
+constexpr int CONV_WARPS = 8;
+constexpr int W8_NUM_THREADS = 192 + CONV_WARPS * 32;  // + warps 6..13: widen int8 -> bf16
+constexpr int W8_SMEM_BYTES = W8_STAGES * W8_STAGE_BYTES + CONV_STAGES * B_STAGE_BYTES + 1024 + 256;
 
 constexpr uint32_t kSpinLimit = 1u << 26;  // iterations of a try_wait loop before giving up
 
@@ -133,6 +148,7 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
 constexpr uint32_t kInstrDesc = (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(BN >> 3) << 17) |
                                 (uint32_t(BM >> 4) << 24);
 
+
 // ---- tile walk ---------------------------------------------------------------------------------
 struct TileCursor {
   int group;      // current group
@@ -175,6 +191,8 @@ __device__ __forceinline__ bool cursor_seek(TileCursor& c, int tile, int n_tiles
 struct __align__(8) SharedBarriers {
   uint64_t full[STAGES];
   uint64_t empty[STAGES];
+  uint64_t conv_full[CONV_STAGES];   // W8: widened tile ready (every widening warp arrives)
+  uint64_t conv_empty[CONV_STAGES];  // W8: MMAs that read the widened tile are done
   uint64_t acc_full[ACC_BUFS];
   uint64_t acc_empty[ACC_BUFS];
   uint32_t tmem_base;
@@ -186,8 +204,24 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
   return __fdividef(g * u, 1.0f + __expf(-g));
 }
 
-template <int MODE>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+// Four int8 codes (one 32-bit word) -> two packed bf16 pairs, exact.  With v = q & 0x7f and b7 the
+// sign bit, q = (128 + v) - (128 + 128*b7).  Both terms are bf16 numbers that can be assembled by
+// byte permutes: 0x43:v is 128 + v (bf16 has unit spacing in [128, 256)) and 0x43:(b7 << 7) is 128
+// or 256.  One packed subtraction gives q.  (A and B of one tcgen05 kind::f16 MMA must have the
+// same element type: bf16 activations with f16 weights is an illegal instruction on sm_100a.)
+__device__ __forceinline__ void widen4(uint32_t w, uint32_t& lo, uint32_t& hi) {
+  const uint32_t v = w & 0x7f7f7f7fu;
+  const uint32_t sg = w & 0x80808080u;
+  const uint32_t a = __byte_perm(v, 0x43434343u, 0x5140);   // {0x43:v1, 0x43:v0}
+  const uint32_t c = __byte_perm(sg, 0x43434343u, 0x5140);
+  const uint32_t b = __byte_perm(v, 0x43434343u, 0x5342);   // {0x43:v3, 0x43:v2}
+  const uint32_t d = __byte_perm(sg, 0x43434343u, 0x5342);
+  asm("sub.bf16x2 %0, %1, %2;" : "=r"(lo) : "r"(a), "r"(c));
+  asm("sub.bf16x2 %0, %1, %2;" : "=r"(hi) : "r"(b), "r"(d));
+}
+
+template <int MODE, bool W8>
+__global__ void __launch_bounds__(W8 ? W8_NUM_THREADS : NUM_THREADS, 1)
 grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const CUtensorMap* __restrict__ tmap_b0,
                             const CUtensorMap* __restrict__ tmap_b1, const int32_t* __restrict__ group_offsets,
                             int num_groups, int N, int K, __nv_bfloat16* __restrict__ out,
@@ -198,7 +232,14 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const CU
   // 1024-byte alignment is required by the 128B swizzle atoms.
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
-  SharedBarriers* bars = reinterpret_cast<SharedBarriers*>(smem_aligned + STAGES * STAGE_BYTES);
+  // ring strides: bf16 weights keep A and B of a stage together; W8 keeps {A, int8 B} in the TMA ring
+  // and the widened B tiles in a second ring behind it
+  constexpr int RING_STRIDE = W8 ? W8_STAGE_BYTES : STAGE_BYTES;
+  constexpr int TX_BYTES = RING_STRIDE;
+  constexpr int NS = W8 ? W8_STAGES : STAGES;  // depth of the TMA ring
+  constexpr uint32_t CONV_BASE_OFF = W8_STAGES * W8_STAGE_BYTES;
+  constexpr int TOTAL_TILE_BYTES = W8 ? W8_STAGES * W8_STAGE_BYTES + CONV_STAGES * B_STAGE_BYTES : STAGES * STAGE_BYTES;
+  SharedBarriers* bars = reinterpret_cast<SharedBarriers*>(smem_aligned + TOTAL_TILE_BYTES);
   volatile int* abort_flag = &bars->abort_flag;
 
   const int warp = threadIdx.x >> 5;
@@ -209,7 +250,11 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const CU
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(smem_u32(&bars->full[s]), 1);
-      mbar_init(smem_u32(&bars->empty[s]), 1);
+      mbar_init(smem_u32(&bars->empty[s]), W8 ? 1 + CONV_WARPS : 1);  // MMA commit (+ the widening warps)
+    }
+    for (int c = 0; c < CONV_STAGES; ++c) {
+      mbar_init(smem_u32(&bars->conv_full[c]), CONV_WARPS);
+      mbar_init(smem_u32(&bars->conv_empty[c]), 1);
     }
     for (int b = 0; b < ACC_BUFS; ++b) {
       mbar_init(smem_u32(&bars->acc_full[b]), 1);
@@ -262,14 +307,14 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const CU
             break;
           }
           const uint32_t full = smem_u32(&bars->full[stage]);
-          const uint32_t sa = smem_base + stage * STAGE_BYTES;
+          const uint32_t sa = smem_base + stage * RING_STRIDE;
           const uint32_t sb = sa + A_STAGE_BYTES;
-          mbar_expect_tx(full, STAGE_BYTES);
+          mbar_expect_tx(full, TX_BYTES);
           tma_load_2d(sa, &tmap_a, full, kb * BK, tc.row0);
           tma_load_2d(sb, mb0, full, kb * BK, tc.n0);
-          tma_load_2d(sb + B_HALF_BYTES, mb1, full, kb * BK, n1);
+          tma_load_2d(sb + (W8 ? Q_HALF_BYTES : B_HALF_BYTES), mb1, full, kb * BK, n1);
           armed |= 1u << stage;
-          if (++stage == STAGES) {
+          if (++stage == NS) {
             stage = 0;
             phase ^= 1u;
           }
@@ -277,7 +322,7 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const CU
       }
       if (*abort_flag) {
         // Let copies already issued land before the CTA's shared memory is released.
-        for (int s = 0; s < STAGES; ++s) {
+        for (int s = 0; s < NS; ++s) {
           if (!(armed & (1u << s))) continue;
           uint32_t par = (s < stage) ? phase : (phase ^ 1u);
           mbar_wait(smem_u32(&bars->full[s]), par, abort_flag + 0 * s, 1u << 20);
@@ -289,6 +334,8 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const CU
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
+      int cstage = 0;
+      uint32_t cphase = 0;
       uint32_t acc_phase[ACC_BUFS] = {0, 0};
       int it = 0;
       bool ok = true;
@@ -310,9 +357,15 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const CU
             ok = false;
             break;
           }
+          if (W8 && !mbar_wait(smem_u32(&bars->conv_full[cstage]), cphase, abort_flag)) {
+            report_error(err, ATENIA_ERR_DEVICE_TIMEOUT, 350 + cstage);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
           tc_fence_after();
-          const uint32_t sa = smem_base + stage * STAGE_BYTES;
-          const uint32_t sb = sa + A_STAGE_BYTES;
+          const uint32_t sa = smem_base + stage * RING_STRIDE;
+          const uint32_t sb = W8 ? smem_base + CONV_BASE_OFF + cstage * B_STAGE_BYTES : sa + A_STAGE_BYTES;
           const uint64_t da = make_smem_desc(sa);
           const uint64_t db = make_smem_desc(sb);
 #pragma unroll
@@ -321,12 +374,73 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const CU
             tc_mma_bf16(d_tmem, da + 2 * k, db + 2 * k, kInstrDesc, (kb > 0 || k > 0) ? 1u : 0u);
           }
           tc_commit(smem_u32(&bars->empty[stage]));  // frees the stage once these MMAs have read it
-          if (++stage == STAGES) {
+          if (W8) {
+            tc_commit(smem_u32(&bars->conv_empty[cstage]));
+            if (++cstage == CONV_STAGES) {
+              cstage = 0;
+              cphase ^= 1u;
+            }
+          }
+          if (++stage == NS) {
             stage = 0;
             phase ^= 1u;
           }
         }
         if (ok) tc_commit(smem_u32(&bars->acc_full[acc]));
+      }
+    }
+  } else if (W8 && warp >= 6) {
+    // ================= int8 -> bf16 widening (warps 6..13, W8 only) =================
+    // Per k-block: 256 rows x 64 int8.  Thread t of the 256 handles 16-byte pieces (row, c) with
+    // row = (t >> 2) + 64 * i, c = t & 3: sixteen codes become two 16-byte pieces of the row's 128-byte
+    // bf16 line, stored at the 128B-swizzled position (piece index XOR row mod 8) the MMA expects.
+    const int ct = threadIdx.x - 192;
+    const int cw = ct >> 5;
+    int stage = 0;
+    uint32_t phase = 0;
+    int cstage = 0;
+    uint32_t cphase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && cursor_seek(cur, tile, n_tiles, num_groups, group_offsets, tc, BN_OUT);
+         tile += gridDim.x) {
+      for (int kb = 0; kb < num_kb; ++kb) {
+        if (!mbar_wait(smem_u32(&bars->full[stage]), phase, abort_flag) ||
+            !mbar_wait(smem_u32(&bars->conv_empty[cstage]), cphase ^ 1u, abort_flag)) {
+          if (lane == 0) report_error(err, ATENIA_ERR_DEVICE_TIMEOUT, 500 + cw);
+          *abort_flag = 1;
+          ok = false;
+          break;
+        }
+        const uint8_t* q = smem_aligned + stage * W8_STAGE_BYTES + A_STAGE_BYTES;
+        uint8_t* b = smem_aligned + CONV_BASE_OFF + cstage * B_STAGE_BYTES;
+        const int c = ct & 3;
+#pragma unroll
+        for (int i = 0; i < BN / (CONV_WARPS * 8); ++i) {
+          const int row = (ct >> 2) + CONV_WARPS * 8 * i;
+          const uint4 v = *reinterpret_cast<const uint4*>(q + row * BK + c * 16);
+          uint4 o0, o1;
+          widen4(v.x, o0.x, o0.y);
+          widen4(v.y, o0.z, o0.w);
+          widen4(v.z, o1.x, o1.y);
+          widen4(v.w, o1.z, o1.w);
+          uint8_t* line = b + row * 128;
+          *reinterpret_cast<uint4*>(line + (((2 * c) ^ (row & 7)) << 4)) = o0;
+          *reinterpret_cast<uint4*>(line + (((2 * c + 1) ^ (row & 7)) << 4)) = o1;
+        }
+        fence_proxy_async();  // generic-proxy writes above must be visible to the MMA's async-proxy reads
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(smem_u32(&bars->conv_full[cstage]));
+          mbar_arrive(smem_u32(&bars->empty[stage]));  // the int8 tile of this stage has been read
+        }
+        if (++cstage == CONV_STAGES) {
+          cstage = 0;
+          cphase ^= 1u;
+        }
+        if (++stage == NS) {
+          stage = 0;
+          phase ^= 1u;
+        }
       }
     }
   } else {
@@ -456,30 +570,32 @@ __global__ void grouped_gemm_check_kernel(GroupedGemmCheckArgs a) {
 
 }  // namespace
 
+template <int MODE, bool W8>
+static int launch_one(const GroupedGemmArgs& a, int num_sms, cudaStream_t s) {
+  constexpr int kSmem = W8 ? W8_SMEM_BYTES : SMEM_BYTES;
+  constexpr int kThreads = W8 ? W8_NUM_THREADS : NUM_THREADS;
+  static bool attr_set = false;
+  if (!attr_set) {
+    ATENIA_CUDA_TRY(cudaFuncSetAttribute(grouped_gemm_tcgen05_kernel<MODE, W8>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
+    attr_set = true;
+  }
+  grouped_gemm_tcgen05_kernel<MODE, W8><<<dim3(num_sms), dim3(kThreads), kSmem, s>>>(
+      a.tmap_a, a.tmap_b0, MODE == kSwiGLU ? a.tmap_b1 : a.tmap_b0, a.group_offsets, a.num_groups, a.N, a.K, a.out,
+      a.scale0, a.scale1, a.err);
+  return (int)cudaGetLastError();
+}
+
 int launch_grouped_gemm_tcgen05(const GroupedGemmArgs& a, int num_sms, cudaStream_t s) {
   if (a.num_groups <= 0) return ATENIA_OK;
   if (a.N % 16 != 0 || a.K % 16 != 0) return ATENIA_ERR_SHAPE;
-  static bool attr_set = false;
-  if (!attr_set) {
-    ATENIA_CUDA_TRY(cudaFuncSetAttribute(grouped_gemm_tcgen05_kernel<kSwiGLU>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-    ATENIA_CUDA_TRY(cudaFuncSetAttribute(grouped_gemm_tcgen05_kernel<kPlain>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-    attr_set = true;
-  }
-  dim3 grid(num_sms), block(NUM_THREADS);
-  if (a.mode == kSwiGLU) {
-    grouped_gemm_tcgen05_kernel<kSwiGLU><<<grid, block, SMEM_BYTES, s>>>(
-        a.tmap_a, a.tmap_b0, a.tmap_b1, a.group_offsets, a.num_groups, a.N, a.K, a.out, a.scale0, a.scale1,
-        a.err);
-  } else {
-    grouped_gemm_tcgen05_kernel<kPlain><<<grid, block, SMEM_BYTES, s>>>(
-        a.tmap_a, a.tmap_b0, a.tmap_b0, a.group_offsets, a.num_groups, a.N, a.K, a.out, a.scale0, a.scale1,
-        a.err);
-  }
+  if (a.w8 && (!a.scale0 || (a.mode == kSwiGLU && !a.scale1))) return ATENIA_ERR_NULL;
+  int rc;
+  if (a.mode == kSwiGLU) rc = a.w8 ? launch_one<kSwiGLU, true>(a, num_sms, s) : launch_one<kSwiGLU, false>(a, num_sms, s);
+  else rc = a.w8 ? launch_one<kPlain, true>(a, num_sms, s) : launch_one<kPlain, false>(a, num_sms, s);
   count_launch();
   count_tcgen05_launch();
-  return (int)cudaGetLastError();
+  return rc;
 }
 
 int launch_grouped_gemm_check(const GroupedGemmCheckArgs& a, cudaStream_t s) {
@@ -508,6 +624,21 @@ static EncodeTiledFn get_encode_fn() {
     }
   }
   return fn;
+}
+
+int encode_tmap_2d_u8(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
+                      uint32_t box_cols) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return ATENIA_ERR_DRIVER;
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0 || cols % 16 != 0) return ATENIA_ERR_SHAPE;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {cols};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? ATENIA_OK : ATENIA_ERR_DRIVER;
 }
 
 int encode_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,

@@ -46,7 +46,7 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
   const bool q = c.weight_dtype == ATENIA_W_INT8_ROW;
   if (L->timing) cudaEventRecord(L->ev[0], s);
   if (L->use_check_gemm) {
-    GroupedGemmCheckArgs k1{a_ptr, L->d_p_gate, L->d_p_up, 0, q ? L->d_sc_gate : nullptr,
+    GroupedGemmCheckArgs k1{a_ptr, L->d_p_gate, L->d_p_up, q ? 1 : 0, q ? L->d_sc_gate : nullptr,
                             q ? L->d_sc_up : nullptr, group_offsets, num_groups, c.d_ff, c.d_model,
                             kSwiGLU, mid, max_rows};
     int rc = launch_grouped_gemm_check(k1, s);
@@ -66,12 +66,13 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
     g1.scale1 = q ? L->d_sc_up : nullptr;
     g1.err = L->d_err;
     g1.max_rows = max_rows;
+    g1.w8 = q;
     int rc = launch_grouped_gemm_tcgen05(g1, L->num_sms, s);
     if (rc) return rc;
   }
   if (L->timing) cudaEventRecord(L->ev[1], s);
   if (L->use_check_gemm) {
-    GroupedGemmCheckArgs k2{mid, L->d_p_down, nullptr, 0, q ? L->d_sc_down : nullptr, nullptr,
+    GroupedGemmCheckArgs k2{mid, L->d_p_down, nullptr, q ? 1 : 0, q ? L->d_sc_down : nullptr, nullptr,
                             group_offsets, num_groups, c.d_model, c.d_ff, kPlain, out, max_rows};
     int rc = launch_grouped_gemm_check(k2, s);
     if (rc) return rc;
@@ -90,6 +91,7 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
     g2.scale1 = nullptr;
     g2.err = L->d_err;
     g2.max_rows = max_rows;
+    g2.w8 = q;
     int rc = launch_grouped_gemm_tcgen05(g2, L->num_sms, s);
     if (rc) return rc;
   }
@@ -107,12 +109,12 @@ int run_shared_gemms(AteniaMoeLayer* L, const __nv_bfloat16* xb, int T, cudaStre
   const bool q = c.weight_dtype == ATENIA_W_INT8_ROW;
   if (L->timing) cudaEventRecord(L->ev[3], s);
   if (L->use_check_gemm) {
-    GroupedGemmCheckArgs k1{xb, L->d_p_shared, L->d_p_shared + 1, 0, q ? L->d_sc_shared : nullptr,
+    GroupedGemmCheckArgs k1{xb, L->d_p_shared, L->d_p_shared + 1, q ? 1 : 0, q ? L->d_sc_shared : nullptr,
                             q ? L->d_sc_shared + 1 : nullptr, L->shared_offsets, 1, c.shared_d_ff, c.d_model,
                             kSwiGLU, L->h_shared, T};
     int rc = launch_grouped_gemm_check(k1, s);
     if (rc) return rc;
-    GroupedGemmCheckArgs k2{L->h_shared, L->d_p_shared + 2, nullptr, 0, q ? L->d_sc_shared + 2 : nullptr,
+    GroupedGemmCheckArgs k2{L->h_shared, L->d_p_shared + 2, nullptr, q ? 1 : 0, q ? L->d_sc_shared + 2 : nullptr,
                             nullptr, L->shared_offsets, 1, c.d_model, c.shared_d_ff, kPlain, L->y_shared, T};
     rc = launch_grouped_gemm_check(k2, s);
     if (rc) return rc;
@@ -133,6 +135,7 @@ int run_shared_gemms(AteniaMoeLayer* L, const __nv_bfloat16* xb, int T, cudaStre
   g1.scale1 = q ? L->d_sc_shared + 1 : nullptr;
   g1.err = L->d_err;
   g1.max_rows = T;
+  g1.w8 = q;
   rc = launch_grouped_gemm_tcgen05(g1, L->num_sms, s);
   if (rc) return rc;
   if (L->timing) cudaEventRecord(L->ev[4], s);
@@ -149,6 +152,7 @@ int run_shared_gemms(AteniaMoeLayer* L, const __nv_bfloat16* xb, int T, cudaStre
   g2.scale0 = q ? L->d_sc_shared + 2 : nullptr;
   g2.err = L->d_err;
   g2.max_rows = T;
+  g2.w8 = q;
   rc = launch_grouped_gemm_tcgen05(g2, L->num_sms, s);
   if (rc) return rc;
   if (L->timing) {
@@ -313,21 +317,11 @@ int atenia_moe_set_weights(AteniaMoeLayer* L, const AteniaMoeWeights* w) {
   if (L->has_gate_vec)
     ATENIA_CUDA_TRY(cudaMemcpy(L->d_gate_vec, w->shared_gate_vec, d * sizeof(float), cudaMemcpyDeviceToDevice));
 
-  // INT8: the tensor-core kernel consumes bf16 operands.  The int8 codes (|q| <= 127, exact in bf16)
-  // are widened once into library-owned bf16 matrices and the per-row scale multiplies the f32
-  // accumulator column in the epilogue, which is the exact factorisation of (q * scale) . x.
-  auto operand = [&](const void* src, size_t rows, size_t cols, const void** out_ptr) -> int {
+  // INT8 matrices are borrowed as they are: their tensor maps describe bytes and the grouped GEMM
+  // widens the codes to bf16 on chip.
+  auto encode = [&](CUtensorMap* m, const void* src, size_t rows, size_t cols) -> int {
     if (!src) return ATENIA_ERR_NULL;
-    if (!q) {
-      *out_ptr = src;
-      return ATENIA_OK;
-    }
-    __nv_bfloat16* wide = nullptr;
-    ATENIA_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&wide), rows * cols * sizeof(__nv_bfloat16)));
-    L->owned.push_back(wide);
-    int rc2 = launch_dequant_rows(static_cast<const int8_t*>(src), nullptr, (int64_t)rows, (int64_t)cols, wide, 0);
-    *out_ptr = wide;
-    return rc2;
+    return q ? encode_tmap_2d_u8(m, src, rows, cols, 128, 64) : encode_tmap_2d_bf16(m, src, rows, cols, 128, 64);
   };
 
   const int G = L->n_groups, El = L->e_local;
@@ -335,12 +329,12 @@ int atenia_moe_set_weights(AteniaMoeLayer* L, const AteniaMoeWeights* w) {
   std::vector<const void*> pg(G), pu(G), pd(G);
   std::vector<const float*> sg(G, nullptr), su(G, nullptr), sd(G, nullptr);
   for (int e = 0; e < El; ++e) {
-    int rc = operand(w->w_gate[e], F, d, &pg[e]);
-    if (!rc) rc = operand(w->w_up[e], F, d, &pu[e]);
-    if (!rc) rc = operand(w->w_down[e], d, F, &pd[e]);
-    if (!rc) rc = encode_tmap_2d_bf16(&tg[e], pg[e], F, d, 128, 64);
-    if (!rc) rc = encode_tmap_2d_bf16(&tu[e], pu[e], F, d, 128, 64);
-    if (!rc) rc = encode_tmap_2d_bf16(&td[e], pd[e], d, F, 128, 64);
+    pg[e] = w->w_gate[e];
+    pu[e] = w->w_up[e];
+    pd[e] = w->w_down[e];
+    int rc = encode(&tg[e], pg[e], F, d);
+    if (!rc) rc = encode(&tu[e], pu[e], F, d);
+    if (!rc) rc = encode(&td[e], pd[e], d, F);
     if (rc) return rc;
     if (q) {
       if (!w->s_gate[e] || !w->s_up[e] || !w->s_down[e]) return ATENIA_ERR_NULL;
@@ -376,12 +370,12 @@ int atenia_moe_set_weights(AteniaMoeLayer* L, const AteniaMoeWeights* w) {
     const void* ps[3];
     const float* ss[3] = {q ? w->shared_s_gate : nullptr, q ? w->shared_s_up : nullptr,
                           q ? w->shared_s_down : nullptr};
-    int rc = operand(w->shared_w_gate, Fs, d, &ps[0]);
-    if (!rc) rc = operand(w->shared_w_up, Fs, d, &ps[1]);
-    if (!rc) rc = operand(w->shared_w_down, d, Fs, &ps[2]);
-    if (!rc) rc = encode_tmap_2d_bf16(&ts[0], ps[0], Fs, d, 128, 64);
-    if (!rc) rc = encode_tmap_2d_bf16(&ts[1], ps[1], Fs, d, 128, 64);
-    if (!rc) rc = encode_tmap_2d_bf16(&ts[2], ps[2], d, Fs, 128, 64);
+    ps[0] = w->shared_w_gate;
+    ps[1] = w->shared_w_up;
+    ps[2] = w->shared_w_down;
+    int rc = encode(&ts[0], ps[0], Fs, d);
+    if (!rc) rc = encode(&ts[1], ps[1], Fs, d);
+    if (!rc) rc = encode(&ts[2], ps[2], d, Fs);
     if (rc) return rc;
     ATENIA_CUDA_TRY(cudaMemcpy(L->d_tm_shared, ts, sizeof(ts), cudaMemcpyHostToDevice));
     ATENIA_CUDA_TRY(cudaMemcpy(L->d_p_shared, ps, sizeof(ps), cudaMemcpyHostToDevice));

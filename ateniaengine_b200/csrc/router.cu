@@ -222,45 +222,79 @@ __global__ void __launch_bounds__(kRWarps * 32) router_kernel(RouterArgs a) {
     for (int j = 0; j < EPL; ++j) acc[t][j] = 0.0;
   double gacc = 0.0;  // lane t (< TOK) of every warp accumulates the gate dot product of token t
 
+  // Global loads of chunk i+1 are issued before the arithmetic of chunk i and land in registers;
+  // they are converted and written to shared memory at the top of the next iteration.
+  constexpr int XV = (TOK * (KC / 8) + kRWarps * 32 - 1) / (kRWarps * 32);   // 16-byte x loads per thread
+  constexpr int WV = (E_T * (KC / 4) + kRWarps * 32 - 1) / (kRWarps * 32);   // float4 W loads per thread
+  uint4 xq[XV][2];  // bf16 input uses [.][0] only; f32 input uses both halves
+  float4 wq[WV];
+  auto fetch = [&](int k0) {
+#pragma unroll
+    for (int r = 0; r < XV; ++r) {
+      const int i = threadIdx.x + r * kRWarps * 32;
+      const int g = i / TOK, t = i - g * TOK;
+      const int kk = k0 + g * 8, tg = t0 + t;
+      xq[r][0] = make_uint4(0, 0, 0, 0);
+      xq[r][1] = make_uint4(0, 0, 0, 0);
+      if (i < TOK * (KC / 8) && tg < a.T && kk < d) {  // d is a multiple of 16: a group of 8 is all in or out
+        if (a.x_is_f32) {
+          const uint4* p = reinterpret_cast<const uint4*>(static_cast<const float*>(a.x) + (size_t)tg * d + kk);
+          xq[r][0] = p[0];
+          xq[r][1] = p[1];
+        } else {
+          xq[r][0] = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(a.x) + (size_t)tg * d + kk);
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < WV; ++r) {
+      const int i = threadIdx.x + r * kRWarps * 32;
+      const int g = i / E_T, e = i - g * E_T;
+      const int kk = k0 + g * 4;
+      wq[r] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (i < E_T * (KC / 4) && e < E && kk < d)
+        wq[r] = __ldg(reinterpret_cast<const float4*>(a.w_router + (size_t)e * d + kk));
+    }
+  };
+  fetch(0);
   for (int k0 = 0; k0 < d; k0 += KC) {
     __syncthreads();
-    // stage x: each thread converts 8 consecutive k of one token; neighbouring threads take
-    // neighbouring tokens so the f64 stores fall in distinct banks
-    for (int i = threadIdx.x; i < TOK * (KC / 8); i += blockDim.x) {
-      const int g = i / TOK, t = i - g * TOK;
-      const int kk = k0 + g * 8;
-      const int tg = t0 + t;
-      float v[8];
+    // x as f64, [k][token]: neighbouring threads hold neighbouring tokens, so the stores fall in
+    // distinct banks
 #pragma unroll
-      for (int j = 0; j < 8; ++j) v[j] = 0.f;
-      if (tg < a.T && kk < d) {  // d is a multiple of 16, so a group of 8 is all in or all out
+    for (int r = 0; r < XV; ++r) {
+      const int i = threadIdx.x + r * kRWarps * 32;
+      if (i < TOK * (KC / 8)) {
+        const int g = i / TOK, t = i - g * TOK;
+        float v[8];
         if (a.x_is_f32) {
-          const float4* p = reinterpret_cast<const float4*>(static_cast<const float*>(a.x) + (size_t)tg * d + kk);
-          float4 u0 = p[0], u1 = p[1];
-          v[0] = u0.x; v[1] = u0.y; v[2] = u0.z; v[3] = u0.w;
-          v[4] = u1.x; v[5] = u1.y; v[6] = u1.z; v[7] = u1.w;
+          v[0] = __uint_as_float(xq[r][0].x); v[1] = __uint_as_float(xq[r][0].y);
+          v[2] = __uint_as_float(xq[r][0].z); v[3] = __uint_as_float(xq[r][0].w);
+          v[4] = __uint_as_float(xq[r][1].x); v[5] = __uint_as_float(xq[r][1].y);
+          v[6] = __uint_as_float(xq[r][1].z); v[7] = __uint_as_float(xq[r][1].w);
         } else {
-          const uint4 u = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(a.x) + (size_t)tg * d + kk);
+          const uint4 u = xq[r][0];
           v[0] = bf16lo(u.x); v[1] = bf16hi(u.x); v[2] = bf16lo(u.y); v[3] = bf16hi(u.y);
           v[4] = bf16lo(u.z); v[5] = bf16hi(u.z); v[6] = bf16lo(u.w); v[7] = bf16hi(u.w);
         }
-      }
 #pragma unroll
-      for (int j = 0; j < 8; ++j) xs[g * 8 + j][t] = (double)v[j];
+        for (int j = 0; j < 8; ++j) xs[g * 8 + j][t] = (double)v[j];
+      }
     }
-    // stage W transposed: a thread reads 4 consecutive k of one expert row (a float4); neighbouring
-    // threads take neighbouring experts so the transposed stores fall in distinct banks
-    for (int i = threadIdx.x; i < E_T * (KC / 4); i += blockDim.x) {
-      const int g = i / E_T, e = i - g * E_T;
-      const int kk = k0 + g * 4;
-      float4 u = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (e < E && kk < d) u = __ldg(reinterpret_cast<const float4*>(a.w_router + (size_t)e * d + kk));
-      ws[g * 4 + 0][e] = u.x;
-      ws[g * 4 + 1][e] = u.y;
-      ws[g * 4 + 2][e] = u.z;
-      ws[g * 4 + 3][e] = u.w;
+    // W transposed, [k][expert]: neighbouring threads hold neighbouring experts
+#pragma unroll
+    for (int r = 0; r < WV; ++r) {
+      const int i = threadIdx.x + r * kRWarps * 32;
+      if (i < E_T * (KC / 4)) {
+        const int g = i / E_T, e = i - g * E_T;
+        ws[g * 4 + 0][e] = wq[r].x;
+        ws[g * 4 + 1][e] = wq[r].y;
+        ws[g * 4 + 2][e] = wq[r].z;
+        ws[g * 4 + 3][e] = wq[r].w;
+      }
     }
     __syncthreads();
+    if (k0 + KC < d) fetch(k0 + KC);
     const int kbase = warp * SLICE + ks * KPL;  // within the chunk; rows past d hold zeros
 #pragma unroll 4
     for (int c = 0; c < KPL; ++c) {
