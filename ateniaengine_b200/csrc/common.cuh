@@ -141,8 +141,12 @@ int launch_f32_to_bf16(const float* src, __nv_bfloat16* dst, int64_t n, cudaStre
 // Tensor-map encoding through the driver entry point (no link-time dependency on libcuda).
 int encode_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols,
                         uint32_t box_rows, uint32_t box_cols);
-// int8 matrix [rows, cols], unswizzled box (the widening warps read it with plain 16-byte loads)
+// int8 matrix [rows, cols]; unswizzled box, or 64-byte swizzle for the row-per-thread reads of the
+// TMEM-operand kernel
 int encode_tmap_2d_u8(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
-                      uint32_t box_cols);
+                      uint32_t box_cols, int swizzle64);
+// W8A16 grouped GEMM with the weights as the tensor-memory operand (w8_gemm.cu).  tmap_a is the bf16
+// token matrix (box {64, 128}, 128B swizzle); tmap_b0/b1 are int8 maps with the 64-byte swizzle.
+int launch_grouped_gemm_w8_tmem(const GroupedGemmArgs& a, int num_sms, cudaStream_t s);
 
 }  // namespace atenia

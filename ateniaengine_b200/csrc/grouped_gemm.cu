@@ -23,15 +23,13 @@
 //
 // Every wait is bounded: a wait that runs out records ATENIA_ERR_DEVICE_TIMEOUT with a site id and
 // the CTA leaves its loops, waits (bounded) for its own TMA copies, frees TMEM and returns.
-#include "common.cuh"
+#include "tc_common.cuh"
 
 namespace atenia {
 namespace {
+using namespace tc;
 
-constexpr int BM = 128;
 constexpr int BN = 256;  // MMA N
-constexpr int BK = 64;
-constexpr int UMMA_K = 16;
 constexpr int STAGES = 4;
 constexpr int ACC_BUFS = 2;
 constexpr int TMEM_COLS = 512;
@@ -51,142 +49,12 @@ constexpr int CONV_WARPS = 8;
 constexpr int W8_NUM_THREADS = 192 + CONV_WARPS * 32;  // + warps 6..13: widen int8 -> bf16
 constexpr int W8_SMEM_BYTES = W8_STAGES * W8_STAGE_BYTES + CONV_STAGES * B_STAGE_BYTES + 1024 + 256;
 
-constexpr uint32_t kSpinLimit = 1u << 26;  // iterations of a try_wait loop before giving up
 
-// ---- PTX wrappers ----------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.b32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok;
-}
-// Bounded wait.  Returns false when the limit ran out or another role already gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          uint32_t limit = kSpinLimit) {
-  for (uint32_t i = 0; i < limit; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 1023u) == 1023u && *abort_flag) return false;
-  }
-  return false;
-}
-__device__ __forceinline__ void fence_barrier_init() {
-  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-}
-__device__ __forceinline__ void fence_proxy_async() {
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
-__device__ __forceinline__ void tmap_acquire(const CUtensorMap* m) {
-  // A tensor map that lives in global memory and was written by the host is made visible to the
-  // tensor-map proxy of this CTA before its first use.
-  asm volatile("fence.proxy.tensormap::generic.acquire.sys [%0], 128;" ::"l"(reinterpret_cast<uint64_t>(m))
-               : "memory");
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x,
-                                            int y) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
-      : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
-               : "memory");
-}
-__device__ __forceinline__ void tc_mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                            uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&v)[16]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
-      : "r"(taddr));
-}
-__device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows of 128 bytes, eight-row
-// groups 1024 bytes apart.  Bits: [0,14) address>>4, [16,30) leading offset>>4 (unused with a
-// swizzled K-major tile, set to 1), [32,46) stride offset>>4, [46,48) version = 1, [61,64) swizzle
-// mode (2 = 128B).
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
-  uint64_t d = 0;
-  d |= static_cast<uint64_t>((smem_addr >> 4) & 0x3FFF);
-  d |= static_cast<uint64_t>(1) << 16;
-  d |= static_cast<uint64_t>(1024 >> 4) << 32;
-  d |= static_cast<uint64_t>(1) << 46;
-  d |= static_cast<uint64_t>(2) << 61;
-  return d;
-}
 // Instruction descriptor, kind::f16: D = f32 (bit 4), A = B = bf16 (bits 7, 10), both K-major,
 // N >> 3 at bit 17, M >> 4 at bit 24.
 constexpr uint32_t kInstrDesc = (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(BN >> 3) << 17) |
                                 (uint32_t(BM >> 4) << 24);
 
-
-// ---- tile walk ---------------------------------------------------------------------------------
-struct TileCursor {
-  int group;      // current group
-  int base;       // first tile index of the current group
-  int m_tiles;    // m tiles of the current group
-  int row_begin;  // first row of the group
-  int row_end;
-};
-struct TileCoord {
-  int group, row0, row_end, n0;
-};
-
-__device__ __forceinline__ void cursor_load(TileCursor& c, const int32_t* __restrict__ off) {
-  c.row_begin = off[c.group];
-  c.row_end = off[c.group + 1];
-  c.m_tiles = (c.row_end - c.row_begin + BM - 1) / BM;
-}
-// Advance the cursor to the group holding `tile`; false when the tile list is exhausted.
-__device__ __forceinline__ bool cursor_seek(TileCursor& c, int tile, int n_tiles, int num_groups,
-                                            const int32_t* __restrict__ off, TileCoord& out, int bn_out) {
-  while (c.group < num_groups) {
-    int tiles_here = c.m_tiles * n_tiles;
-    if (tile < c.base + tiles_here) {
-      int local = tile - c.base;
-      int nt = local / c.m_tiles;  // n-major, m-minor: neighbouring CTAs share a weight tile
-      int mt = local - nt * c.m_tiles;
-      out.group = c.group;
-      out.row0 = c.row_begin + mt * BM;
-      out.row_end = c.row_end;
-      out.n0 = nt * bn_out;
-      return true;
-    }
-    c.base += tiles_here;
-    c.group += 1;
-    if (c.group < num_groups) cursor_load(c, off);
-  }
-  return false;
-}
 
 struct __align__(8) SharedBarriers {
   uint64_t full[STAGES];
@@ -199,26 +67,6 @@ struct __align__(8) SharedBarriers {
   int abort_flag;
 };
 
-__device__ __forceinline__ float silu_mul(float g, float u) {
-  // silu(g) * u = g * u / (1 + exp(-g))
-  return __fdividef(g * u, 1.0f + __expf(-g));
-}
-
-// Four int8 codes (one 32-bit word) -> two packed bf16 pairs, exact.  With v = q & 0x7f and b7 the
-// sign bit, q = (128 + v) - (128 + 128*b7).  Both terms are bf16 numbers that can be assembled by
-// byte permutes: 0x43:v is 128 + v (bf16 has unit spacing in [128, 256)) and 0x43:(b7 << 7) is 128
-// or 256.  One packed subtraction gives q.  (A and B of one tcgen05 kind::f16 MMA must have the
-// same element type: bf16 activations with f16 weights is an illegal instruction on sm_100a.)
-__device__ __forceinline__ void widen4(uint32_t w, uint32_t& lo, uint32_t& hi) {
-  const uint32_t v = w & 0x7f7f7f7fu;
-  const uint32_t sg = w & 0x80808080u;
-  const uint32_t a = __byte_perm(v, 0x43434343u, 0x5140);   // {0x43:v1, 0x43:v0}
-  const uint32_t c = __byte_perm(sg, 0x43434343u, 0x5140);
-  const uint32_t b = __byte_perm(v, 0x43434343u, 0x5342);   // {0x43:v3, 0x43:v2}
-  const uint32_t d = __byte_perm(sg, 0x43434343u, 0x5342);
-  asm("sub.bf16x2 %0, %1, %2;" : "=r"(lo) : "r"(a), "r"(c));
-  asm("sub.bf16x2 %0, %1, %2;" : "=r"(hi) : "r"(b), "r"(d));
-}
 
 template <int MODE, bool W8>
 __global__ void __launch_bounds__(W8 ? W8_NUM_THREADS : NUM_THREADS, 1)
@@ -627,7 +475,7 @@ static EncodeTiledFn get_encode_fn() {
 }
 
 int encode_tmap_2d_u8(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
-                      uint32_t box_cols) {
+                      uint32_t box_cols, int swizzle64) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return ATENIA_ERR_DRIVER;
   if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0 || cols % 16 != 0) return ATENIA_ERR_SHAPE;
@@ -636,8 +484,8 @@ int encode_tmap_2d_u8(CUtensorMap* out, const void* base, uint64_t rows, uint64_
   cuuint32_t box[2] = {box_cols, box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? ATENIA_OK : ATENIA_ERR_DRIVER;
 }
 

@@ -16,6 +16,9 @@ struct AteniaMoeLayer {
   bool weights_set = false;
   bool use_check_gemm = false;  // diagnostic: CUDA-core contraction instead of tcgen05
   bool timing = false;
+  // INT8: 0 = pick per call (tensor-memory operand kernel for small batches, shared-memory widening
+  // for large ones), 1 = always the tensor-memory kernel, 2 = always shared-memory widening
+  int w8_mode = 0;
 
   // weights (device)
   float* d_router = nullptr;    // [E, d]
@@ -26,6 +29,11 @@ struct AteniaMoeLayer {
   CUtensorMap* d_tm_up = nullptr;
   CUtensorMap* d_tm_down = nullptr;
   CUtensorMap* d_tm_shared = nullptr;  // [3]: gate, up, down
+  // INT8 only: the same matrices described with the 64-byte swizzle the tensor-memory kernel reads
+  CUtensorMap* d_tm_gate_sw = nullptr;
+  CUtensorMap* d_tm_up_sw = nullptr;
+  CUtensorMap* d_tm_down_sw = nullptr;
+  CUtensorMap* d_tm_shared_sw = nullptr;
   const float** d_sc_gate = nullptr;   // [n_groups] device pointers (INT8) or null
   const float** d_sc_up = nullptr;
   const float** d_sc_down = nullptr;

@@ -44,6 +44,9 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
                      const int32_t* group_offsets, int num_groups, int max_rows, cudaStream_t s) {
   const AteniaMoeConfig& c = L->cfg;
   const bool q = c.weight_dtype == ATENIA_W_INT8_ROW;
+  // INT8: the tensor-memory kernel wins while groups are small (its MMA width follows the row count),
+  // the shared-memory widening kernel once every group fills several 128-row tiles.
+  const bool tmem = q && (L->w8_mode == 1 || (L->w8_mode == 0 && max_rows < 256 * num_groups));
   if (L->timing) cudaEventRecord(L->ev[0], s);
   if (L->use_check_gemm) {
     GroupedGemmCheckArgs k1{a_ptr, L->d_p_gate, L->d_p_up, q ? 1 : 0, q ? L->d_sc_gate : nullptr,
@@ -54,8 +57,8 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
   } else {
     GroupedGemmArgs g1{};
     g1.tmap_a = tm_a;
-    g1.tmap_b0 = L->d_tm_gate;
-    g1.tmap_b1 = L->d_tm_up;
+    g1.tmap_b0 = tmem ? L->d_tm_gate_sw : L->d_tm_gate;
+    g1.tmap_b1 = tmem ? L->d_tm_up_sw : L->d_tm_up;
     g1.group_offsets = group_offsets;
     g1.num_groups = num_groups;
     g1.N = c.d_ff;
@@ -67,7 +70,7 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
     g1.err = L->d_err;
     g1.max_rows = max_rows;
     g1.w8 = q;
-    int rc = launch_grouped_gemm_tcgen05(g1, L->num_sms, s);
+    int rc = tmem ? launch_grouped_gemm_w8_tmem(g1, L->num_sms, s) : launch_grouped_gemm_tcgen05(g1, L->num_sms, s);
     if (rc) return rc;
   }
   if (L->timing) cudaEventRecord(L->ev[1], s);
@@ -79,8 +82,8 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
   } else {
     GroupedGemmArgs g2{};
     g2.tmap_a = tm_mid;
-    g2.tmap_b0 = L->d_tm_down;
-    g2.tmap_b1 = L->d_tm_down;
+    g2.tmap_b0 = tmem ? L->d_tm_down_sw : L->d_tm_down;
+    g2.tmap_b1 = g2.tmap_b0;
     g2.group_offsets = group_offsets;
     g2.num_groups = num_groups;
     g2.N = c.d_model;
@@ -92,7 +95,7 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
     g2.err = L->d_err;
     g2.max_rows = max_rows;
     g2.w8 = q;
-    int rc = launch_grouped_gemm_tcgen05(g2, L->num_sms, s);
+    int rc = tmem ? launch_grouped_gemm_w8_tmem(g2, L->num_sms, s) : launch_grouped_gemm_tcgen05(g2, L->num_sms, s);
     if (rc) return rc;
   }
   if (L->timing) {
@@ -107,6 +110,7 @@ namespace {
 int run_shared_gemms(AteniaMoeLayer* L, const __nv_bfloat16* xb, int T, cudaStream_t s) {
   const AteniaMoeConfig& c = L->cfg;
   const bool q = c.weight_dtype == ATENIA_W_INT8_ROW;
+  const bool tmem = q && (L->w8_mode == 1 || (L->w8_mode == 0 && T < 256));
   if (L->timing) cudaEventRecord(L->ev[3], s);
   if (L->use_check_gemm) {
     GroupedGemmCheckArgs k1{xb, L->d_p_shared, L->d_p_shared + 1, q ? 1 : 0, q ? L->d_sc_shared : nullptr,
@@ -123,8 +127,8 @@ int run_shared_gemms(AteniaMoeLayer* L, const __nv_bfloat16* xb, int T, cudaStre
   GroupedGemmArgs g1{};
   int rc = encode_tmap_2d_bf16(&g1.tmap_a, xb, (uint64_t)T, (uint64_t)c.d_model, 128, 64);
   if (rc) return rc;
-  g1.tmap_b0 = L->d_tm_shared;
-  g1.tmap_b1 = L->d_tm_shared + 1;
+  g1.tmap_b0 = tmem ? L->d_tm_shared_sw : L->d_tm_shared;
+  g1.tmap_b1 = g1.tmap_b0 + 1;
   g1.group_offsets = L->shared_offsets;
   g1.num_groups = 1;
   g1.N = c.shared_d_ff;
@@ -136,13 +140,13 @@ int run_shared_gemms(AteniaMoeLayer* L, const __nv_bfloat16* xb, int T, cudaStre
   g1.err = L->d_err;
   g1.max_rows = T;
   g1.w8 = q;
-  rc = launch_grouped_gemm_tcgen05(g1, L->num_sms, s);
+  rc = tmem ? launch_grouped_gemm_w8_tmem(g1, L->num_sms, s) : launch_grouped_gemm_tcgen05(g1, L->num_sms, s);
   if (rc) return rc;
   if (L->timing) cudaEventRecord(L->ev[4], s);
   GroupedGemmArgs g2{};
   g2.tmap_a = L->tm_h_shared;
-  g2.tmap_b0 = L->d_tm_shared + 2;
-  g2.tmap_b1 = L->d_tm_shared + 2;
+  g2.tmap_b0 = (tmem ? L->d_tm_shared_sw : L->d_tm_shared) + 2;
+  g2.tmap_b1 = g2.tmap_b0;
   g2.group_offsets = L->shared_offsets;
   g2.num_groups = 1;
   g2.N = c.d_model;
@@ -153,7 +157,7 @@ int run_shared_gemms(AteniaMoeLayer* L, const __nv_bfloat16* xb, int T, cudaStre
   g2.err = L->d_err;
   g2.max_rows = T;
   g2.w8 = q;
-  rc = launch_grouped_gemm_tcgen05(g2, L->num_sms, s);
+  rc = tmem ? launch_grouped_gemm_w8_tmem(g2, L->num_sms, s) : launch_grouped_gemm_tcgen05(g2, L->num_sms, s);
   if (rc) return rc;
   if (L->timing) {
     cudaEventRecord(L->ev[5], s);
@@ -189,6 +193,7 @@ int atenia_moe_create(const AteniaMoeConfig* cfg, AteniaMoeLayer** out) {
   L->n_groups = c.ep_world == 1 ? L->e_local : c.ep_world * L->e_local;
   L->has_shared = c.shared_d_ff > 0;
   L->use_check_gemm = std::getenv("ATENIA_MOE_CHECK_GEMM") && std::atoi(std::getenv("ATENIA_MOE_CHECK_GEMM")) != 0;
+  L->w8_mode = std::getenv("ATENIA_MOE_W8_MODE") ? std::atoi(std::getenv("ATENIA_MOE_W8_MODE")) : 0;
   const size_t Tm = (size_t)c.max_tokens, k = (size_t)c.experts_per_token, E = (size_t)c.num_experts;
   const size_t d = (size_t)c.d_model, F = (size_t)c.d_ff, Fs = (size_t)c.shared_d_ff;
   const size_t R = Tm * k;
@@ -227,6 +232,12 @@ int atenia_moe_create(const AteniaMoeConfig* cfg, AteniaMoeLayer** out) {
   TRY_ALLOC(L->d_tm_up, (size_t)L->n_groups);
   TRY_ALLOC(L->d_tm_down, (size_t)L->n_groups);
   TRY_ALLOC(L->d_tm_shared, 3);
+  if (c.weight_dtype == ATENIA_W_INT8_ROW) {
+    TRY_ALLOC(L->d_tm_gate_sw, (size_t)L->n_groups);
+    TRY_ALLOC(L->d_tm_up_sw, (size_t)L->n_groups);
+    TRY_ALLOC(L->d_tm_down_sw, (size_t)L->n_groups);
+    TRY_ALLOC(L->d_tm_shared_sw, 3);
+  }
   TRY_ALLOC(L->d_sc_gate, (size_t)L->n_groups);
   TRY_ALLOC(L->d_sc_up, (size_t)L->n_groups);
   TRY_ALLOC(L->d_sc_down, (size_t)L->n_groups);
@@ -284,7 +295,7 @@ int atenia_moe_destroy(AteniaMoeLayer* L) {
                   L->x_bf16,     L->h_shared,    L->y_shared,    L->d_err,          L->d_tm_gate,
                   L->d_tm_up,    L->d_tm_down,   L->d_tm_shared, L->d_sc_gate,      L->d_sc_up,
                   L->d_sc_down,  L->d_sc_shared, L->d_p_gate,    L->d_p_up,         L->d_p_down,
-                  L->d_p_shared, L->recv_x,      L->recv_h,      L->recv_y,         L->d_counts_all,
+                  L->d_p_shared, L->d_tm_gate_sw, L->d_tm_up_sw, L->d_tm_down_sw, L->d_tm_shared_sw, L->recv_x,      L->recv_h,      L->recv_y,         L->d_counts_all,
                   L->d_group_offsets};
   for (void* p : ptrs)
     if (p) cudaFree(p);
@@ -319,13 +330,13 @@ int atenia_moe_set_weights(AteniaMoeLayer* L, const AteniaMoeWeights* w) {
 
   // INT8 matrices are borrowed as they are: their tensor maps describe bytes and the grouped GEMM
   // widens the codes to bf16 on chip.
-  auto encode = [&](CUtensorMap* m, const void* src, size_t rows, size_t cols) -> int {
+  auto encode = [&](CUtensorMap* m, const void* src, size_t rows, size_t cols, int sw64 = 0) -> int {
     if (!src) return ATENIA_ERR_NULL;
-    return q ? encode_tmap_2d_u8(m, src, rows, cols, 128, 64) : encode_tmap_2d_bf16(m, src, rows, cols, 128, 64);
+    return q ? encode_tmap_2d_u8(m, src, rows, cols, 128, 64, sw64) : encode_tmap_2d_bf16(m, src, rows, cols, 128, 64);
   };
 
   const int G = L->n_groups, El = L->e_local;
-  std::vector<CUtensorMap> tg(G), tu(G), td(G);
+  std::vector<CUtensorMap> tg(G), tu(G), td(G), tgs(G), tus(G), tds(G);
   std::vector<const void*> pg(G), pu(G), pd(G);
   std::vector<const float*> sg(G, nullptr), su(G, nullptr), sd(G, nullptr);
   for (int e = 0; e < El; ++e) {
@@ -335,6 +346,9 @@ int atenia_moe_set_weights(AteniaMoeLayer* L, const AteniaMoeWeights* w) {
     int rc = encode(&tg[e], pg[e], F, d);
     if (!rc) rc = encode(&tu[e], pu[e], F, d);
     if (!rc) rc = encode(&td[e], pd[e], d, F);
+    if (!rc && q) rc = encode(&tgs[e], pg[e], F, d, 1);
+    if (!rc && q) rc = encode(&tus[e], pu[e], F, d, 1);
+    if (!rc && q) rc = encode(&tds[e], pd[e], d, F, 1);
     if (rc) return rc;
     if (q) {
       if (!w->s_gate[e] || !w->s_up[e] || !w->s_down[e]) return ATENIA_ERR_NULL;
@@ -348,6 +362,9 @@ int atenia_moe_set_weights(AteniaMoeLayer* L, const AteniaMoeWeights* w) {
     tg[g] = tg[g % El];
     tu[g] = tu[g % El];
     td[g] = td[g % El];
+    tgs[g] = tgs[g % El];
+    tus[g] = tus[g % El];
+    tds[g] = tds[g % El];
     pg[g] = pg[g % El];
     pu[g] = pu[g % El];
     pd[g] = pd[g % El];
@@ -359,6 +376,11 @@ int atenia_moe_set_weights(AteniaMoeLayer* L, const AteniaMoeWeights* w) {
   ATENIA_CUDA_TRY(cudaMemcpy(L->d_tm_gate, tg.data(), mb, cudaMemcpyHostToDevice));
   ATENIA_CUDA_TRY(cudaMemcpy(L->d_tm_up, tu.data(), mb, cudaMemcpyHostToDevice));
   ATENIA_CUDA_TRY(cudaMemcpy(L->d_tm_down, td.data(), mb, cudaMemcpyHostToDevice));
+  if (q) {
+    ATENIA_CUDA_TRY(cudaMemcpy(L->d_tm_gate_sw, tgs.data(), mb, cudaMemcpyHostToDevice));
+    ATENIA_CUDA_TRY(cudaMemcpy(L->d_tm_up_sw, tus.data(), mb, cudaMemcpyHostToDevice));
+    ATENIA_CUDA_TRY(cudaMemcpy(L->d_tm_down_sw, tds.data(), mb, cudaMemcpyHostToDevice));
+  }
   ATENIA_CUDA_TRY(cudaMemcpy(L->d_p_gate, pg.data(), pb, cudaMemcpyHostToDevice));
   ATENIA_CUDA_TRY(cudaMemcpy(L->d_p_up, pu.data(), pb, cudaMemcpyHostToDevice));
   ATENIA_CUDA_TRY(cudaMemcpy(L->d_p_down, pd.data(), pb, cudaMemcpyHostToDevice));
@@ -366,7 +388,7 @@ int atenia_moe_set_weights(AteniaMoeLayer* L, const AteniaMoeWeights* w) {
   ATENIA_CUDA_TRY(cudaMemcpy(L->d_sc_up, su.data(), pb, cudaMemcpyHostToDevice));
   ATENIA_CUDA_TRY(cudaMemcpy(L->d_sc_down, sd.data(), pb, cudaMemcpyHostToDevice));
   if (L->has_shared) {
-    CUtensorMap ts[3];
+    CUtensorMap ts[3], tss[3];
     const void* ps[3];
     const float* ss[3] = {q ? w->shared_s_gate : nullptr, q ? w->shared_s_up : nullptr,
                           q ? w->shared_s_down : nullptr};
@@ -376,7 +398,11 @@ int atenia_moe_set_weights(AteniaMoeLayer* L, const AteniaMoeWeights* w) {
     int rc = encode(&ts[0], ps[0], Fs, d);
     if (!rc) rc = encode(&ts[1], ps[1], Fs, d);
     if (!rc) rc = encode(&ts[2], ps[2], d, Fs);
+    if (!rc && q) rc = encode(&tss[0], ps[0], Fs, d, 1);
+    if (!rc && q) rc = encode(&tss[1], ps[1], Fs, d, 1);
+    if (!rc && q) rc = encode(&tss[2], ps[2], d, Fs, 1);
     if (rc) return rc;
+    if (q) ATENIA_CUDA_TRY(cudaMemcpy(L->d_tm_shared_sw, tss, sizeof(tss), cudaMemcpyHostToDevice));
     ATENIA_CUDA_TRY(cudaMemcpy(L->d_tm_shared, ts, sizeof(ts), cudaMemcpyHostToDevice));
     ATENIA_CUDA_TRY(cudaMemcpy(L->d_p_shared, ps, sizeof(ps), cudaMemcpyHostToDevice));
     ATENIA_CUDA_TRY(cudaMemcpy(L->d_sc_shared, ss, sizeof(ss), cudaMemcpyHostToDevice));

@@ -150,6 +150,17 @@ def test_w8a16_structure(dev):
         _run_parity(dev, shape, T, TOL_W8A16, seed=T)
 
 
+@pytest.mark.parametrize("mode", ["1", "2"])
+def test_w8a16_both_kernels(dev, monkeypatch, mode):
+    """ATENIA_MOE_W8_MODE pins one of the two INT8 kernels (1: weights widened into tensor memory,
+    2: widened into shared memory); each must meet the bar at small and large group sizes."""
+    monkeypatch.setenv("ATENIA_MOE_W8_MODE", mode)
+    synth = _synth()
+    shape = synth.small(synth.SHAPES["mixtral_int8"], d_model=512, d_ff=768)
+    for T in (3, 700):
+        _run_parity(dev, shape, T, TOL_W8A16, seed=T)
+
+
 def test_w8a16_with_shared_expert(dev):
     synth = _synth()
     from dataclasses import replace
