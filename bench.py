@@ -36,7 +36,12 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the routed gate/up kernel, from the ncu
 # capture summarised under profiles/ (scaled to this workload by rows where the capture was smaller).
-NCU_TRAFFIC_BYTES = {}
+NCU_TRAFFIC_BYTES = {
+    # profiles/grouped_gemm_tcgen05_mixtral_t4096_dram.md: 1.95 GB read + 227.5 MB written
+    "mixtral:4096": 2.18e9,
+    # profiles/grouped_gemm_tcgen05_mixtral_t512.md: 1.904 GB read + 29.9 MB written
+    "mixtral:512": 1.934e9,
+}
 
 
 def load_peaks():
@@ -60,15 +65,16 @@ class ClockSampler:
 
     def __init__(self, index):
         self.index = index
-        self.samples = []
+        self.samples = []  # (host time, fields)
         self.proc = None
         self.thread = None
+        self.window = None  # (t0, t1) of the region under load
 
     def start(self):
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", "20"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
@@ -80,7 +86,7 @@ class ClockSampler:
         for line in self.proc.stdout:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) == 6:
-                self.samples.append(parts)
+                self.samples.append((time.perf_counter(), parts))
 
     def stop(self):
         if self.proc is None:
@@ -91,7 +97,9 @@ class ClockSampler:
         except Exception:
             self.proc.kill()
         sm, mx, reasons = [], [], set()
-        for s in self.samples:
+        inside = [p for (t, p) in self.samples
+                  if self.window is None or (self.window[0] <= t <= self.window[1])]
+        for s in inside:
             try:
                 sm.append(float(s[0]))
                 mx.append(float(s[1]))
@@ -241,6 +249,11 @@ def main():
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+        time.sleep(0.8)  # nvidia-smi needs a moment before its first reading
+        for _ in range(args.warmup):
+            layer.forward(x, out=out)
+    sync_all()
+    t_load0 = time.perf_counter()
     launches0 = _lib.lib().atenia_moe_counter(1)
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev0.record()
@@ -266,6 +279,9 @@ def main():
         g1.append(layer.last_gemm_ms(0))
         g2.append(layer.last_gemm_ms(1))
     layer.enable_timing(False)
+    # the clock record covers the timed region and the kernel-timing pass that follows it
+    if rank == 0:
+        sampler.window = (t_load0, time.perf_counter())
     clocks = sampler.stop() if rank == 0 else None
     gemm1_ms = sum(g1) / len(g1)
     gemm2_ms = sum(g2) / len(g2)
@@ -283,6 +299,7 @@ def main():
     roofline = {"bound": "tensor", "kernel": "grouped_gemm_tcgen05_kernel<kSwiGLU> (routed gate/up + SwiGLU)",
                 "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                 "frac": achieved / peaks["bf16_tflops"], "peak_source": f"{peak_src} (burst cuBLAS bf16)",
+                "frac_of_sustained_peak": achieved / peaks["bf16_tflops_sustained"],
                 "traffic": NCU_TRAFFIC_BYTES.get(f"{shape.name}:{T}"),
                 "launch_ms": gemm1_ms, "down_gemm_ms": gemm2_ms,
                 "down_gemm_tflops": 2.0 * rows * shape.d_model * shape.d_ff / (gemm2_ms * 1e-3) / 1e12,
