@@ -19,6 +19,9 @@ struct AteniaMoeLayer {
   // INT8: 0 = pick per call (tensor-memory operand kernel for small batches, shared-memory widening
   // for large ones), 1 = always the tensor-memory kernel, 2 = always shared-memory widening
   int w8_mode = 0;
+  // bf16: 0 = pick per call (CTA-pair kernel once groups average >= 512 rows), 1 = always pairs,
+  // 2 = always the single-CTA kernel
+  int pair_mode = 0;
 
   // weights (device)
   float* d_router = nullptr;    // [E, d]

@@ -47,6 +47,8 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
   // INT8: the tensor-memory kernel wins while groups are small (its MMA width follows the row count),
   // the shared-memory widening kernel once every group fills several 128-row tiles.
   const bool tmem = q && (L->w8_mode == 1 || (L->w8_mode == 0 && max_rows < 256 * num_groups));
+  // bf16: 256-row CTA-pair tiles pay off once an average group fills a few of them
+  const bool pairs = !q && (L->pair_mode == 1 || (L->pair_mode == 0 && max_rows >= 512 * num_groups));
   if (L->timing) cudaEventRecord(L->ev[0], s);
   if (L->use_check_gemm) {
     GroupedGemmCheckArgs k1{a_ptr, L->d_p_gate, L->d_p_up, q ? 1 : 0, q ? L->d_sc_gate : nullptr,
@@ -70,7 +72,8 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
     g1.err = L->d_err;
     g1.max_rows = max_rows;
     g1.w8 = q;
-    int rc = tmem ? launch_grouped_gemm_w8_tmem(g1, L->num_sms, s) : launch_grouped_gemm_tcgen05(g1, L->num_sms, s);
+    int rc = tmem ? launch_grouped_gemm_w8_tmem(g1, L->num_sms, s)
+                  : pairs ? launch_grouped_gemm_2cta(g1, L->num_sms, s) : launch_grouped_gemm_tcgen05(g1, L->num_sms, s);
     if (rc) return rc;
   }
   if (L->timing) cudaEventRecord(L->ev[1], s);
@@ -95,7 +98,8 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
     g2.err = L->d_err;
     g2.max_rows = max_rows;
     g2.w8 = q;
-    int rc = tmem ? launch_grouped_gemm_w8_tmem(g2, L->num_sms, s) : launch_grouped_gemm_tcgen05(g2, L->num_sms, s);
+    int rc = tmem ? launch_grouped_gemm_w8_tmem(g2, L->num_sms, s)
+                  : pairs ? launch_grouped_gemm_2cta(g2, L->num_sms, s) : launch_grouped_gemm_tcgen05(g2, L->num_sms, s);
     if (rc) return rc;
   }
   if (L->timing) {
@@ -111,6 +115,7 @@ int run_shared_gemms(AteniaMoeLayer* L, const __nv_bfloat16* xb, int T, cudaStre
   const AteniaMoeConfig& c = L->cfg;
   const bool q = c.weight_dtype == ATENIA_W_INT8_ROW;
   const bool tmem = q && (L->w8_mode == 1 || (L->w8_mode == 0 && T < 256));
+  const bool pairs = !q && (L->pair_mode == 1 || (L->pair_mode == 0 && T >= 512));
   if (L->timing) cudaEventRecord(L->ev[3], s);
   if (L->use_check_gemm) {
     GroupedGemmCheckArgs k1{xb, L->d_p_shared, L->d_p_shared + 1, q ? 1 : 0, q ? L->d_sc_shared : nullptr,
@@ -140,7 +145,8 @@ int run_shared_gemms(AteniaMoeLayer* L, const __nv_bfloat16* xb, int T, cudaStre
   g1.err = L->d_err;
   g1.max_rows = T;
   g1.w8 = q;
-  rc = tmem ? launch_grouped_gemm_w8_tmem(g1, L->num_sms, s) : launch_grouped_gemm_tcgen05(g1, L->num_sms, s);
+  rc = tmem ? launch_grouped_gemm_w8_tmem(g1, L->num_sms, s)
+            : pairs ? launch_grouped_gemm_2cta(g1, L->num_sms, s) : launch_grouped_gemm_tcgen05(g1, L->num_sms, s);
   if (rc) return rc;
   if (L->timing) cudaEventRecord(L->ev[4], s);
   GroupedGemmArgs g2{};
@@ -157,7 +163,8 @@ int run_shared_gemms(AteniaMoeLayer* L, const __nv_bfloat16* xb, int T, cudaStre
   g2.err = L->d_err;
   g2.max_rows = T;
   g2.w8 = q;
-  rc = tmem ? launch_grouped_gemm_w8_tmem(g2, L->num_sms, s) : launch_grouped_gemm_tcgen05(g2, L->num_sms, s);
+  rc = tmem ? launch_grouped_gemm_w8_tmem(g2, L->num_sms, s)
+            : pairs ? launch_grouped_gemm_2cta(g2, L->num_sms, s) : launch_grouped_gemm_tcgen05(g2, L->num_sms, s);
   if (rc) return rc;
   if (L->timing) {
     cudaEventRecord(L->ev[5], s);
@@ -194,6 +201,7 @@ int atenia_moe_create(const AteniaMoeConfig* cfg, AteniaMoeLayer** out) {
   L->has_shared = c.shared_d_ff > 0;
   L->use_check_gemm = std::getenv("ATENIA_MOE_CHECK_GEMM") && std::atoi(std::getenv("ATENIA_MOE_CHECK_GEMM")) != 0;
   L->w8_mode = std::getenv("ATENIA_MOE_W8_MODE") ? std::atoi(std::getenv("ATENIA_MOE_W8_MODE")) : 0;
+  L->pair_mode = std::getenv("ATENIA_MOE_PAIR_MODE") ? std::atoi(std::getenv("ATENIA_MOE_PAIR_MODE")) : 0;
   const size_t Tm = (size_t)c.max_tokens, k = (size_t)c.experts_per_token, E = (size_t)c.num_experts;
   const size_t d = (size_t)c.d_model, F = (size_t)c.d_ff, Fs = (size_t)c.shared_d_ff;
   const size_t R = Tm * k;

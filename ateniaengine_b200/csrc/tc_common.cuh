@@ -156,14 +156,15 @@ struct TileCoord {
   int group, row0, row_end, n0;
 };
 
-__device__ __forceinline__ void cursor_load(TileCursor& c, const int32_t* __restrict__ off) {
+__device__ __forceinline__ void cursor_load(TileCursor& c, const int32_t* __restrict__ off, int tile_rows = BM) {
   c.row_begin = off[c.group];
   c.row_end = off[c.group + 1];
-  c.m_tiles = (c.row_end - c.row_begin + BM - 1) / BM;
+  c.m_tiles = (c.row_end - c.row_begin + tile_rows - 1) / tile_rows;
 }
 // Advance the cursor to the group holding `tile`; false when the tile list is exhausted.
 __device__ __forceinline__ bool cursor_seek(TileCursor& c, int tile, int n_tiles, int num_groups,
-                                            const int32_t* __restrict__ off, TileCoord& out, int bn_out) {
+                                            const int32_t* __restrict__ off, TileCoord& out, int bn_out,
+                                            int tile_rows = BM) {
   while (c.group < num_groups) {
     int tiles_here = c.m_tiles * n_tiles;
     if (tile < c.base + tiles_here) {
@@ -171,14 +172,14 @@ __device__ __forceinline__ bool cursor_seek(TileCursor& c, int tile, int n_tiles
       int nt = local / c.m_tiles;  // n-major, m-minor: neighbouring CTAs share a weight tile
       int mt = local - nt * c.m_tiles;
       out.group = c.group;
-      out.row0 = c.row_begin + mt * BM;
+      out.row0 = c.row_begin + mt * tile_rows;
       out.row_end = c.row_end;
       out.n0 = nt * bn_out;
       return true;
     }
     c.base += tiles_here;
     c.group += 1;
-    if (c.group < num_groups) cursor_load(c, off);
+    if (c.group < num_groups) cursor_load(c, off, tile_rows);
   }
   return false;
 }

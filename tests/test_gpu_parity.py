@@ -198,6 +198,23 @@ def test_tensor_core_kernel_agrees_with_cuda_core_check(dev, monkeypatch):
     assert rel_l2(a.cpu().numpy(), b.cpu().numpy()) < 2e-3
 
 
+@pytest.mark.parametrize("T", [5, 300, 1100])
+def test_cta_pair_kernel_matches_single_cta_kernel(dev, monkeypatch, T):
+    """ATENIA_MOE_PAIR_MODE pins the bf16 kernel (1: CTA pairs with 256-row tiles, 2: single CTA).
+    Both see the same rows and accumulate over k in the same order."""
+    synth = _synth()
+    shape = synth.small(synth.SHAPES["deepseek_v2_lite"], d_model=512, d_ff=384, shared_d_ff=256)
+    w = synth.make_weights(shape, 21, dev)
+    x = synth.make_activations(shape, 21, dev, tokens=T)
+    monkeypatch.setenv("ATENIA_MOE_PAIR_MODE", "2")
+    a = synth.build_layer(shape, w, max_tokens=T).forward(x, out_dtype=torch.float32, sync=True)
+    monkeypatch.setenv("ATENIA_MOE_PAIR_MODE", "1")
+    b = synth.build_layer(shape, w, max_tokens=T).forward(x, out_dtype=torch.float32, sync=True)
+    assert rel_l2(b.cpu().numpy(), a.cpu().numpy()) < 1e-3
+    ref = oracle_layer(shape, w).forward(x.float().cpu().numpy())
+    assert rel_l2(b.cpu().numpy(), ref) <= TOL_BF16
+
+
 def test_token_order_does_not_change_rows(dev):
     """The block is position-wise: shuffling the tokens shuffles the outputs, bit for bit."""
     synth = _synth()
