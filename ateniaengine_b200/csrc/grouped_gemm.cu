@@ -44,9 +44,11 @@ constexpr int Q_STAGE_BYTES = BN * BK;               // 16 KiB of int8
 constexpr int Q_HALF_BYTES = Q_STAGE_BYTES / 2;
 constexpr int W8_STAGE_BYTES = A_STAGE_BYTES + Q_STAGE_BYTES;  // 32 KiB
 constexpr int W8_STAGES = 3;
-constexpr int CONV_STAGES = 3;
-constexpr int CONV_WARPS = 8;
-constexpr int W8_NUM_THREADS = 192 + CONV_WARPS * 32;  // + warps 6..13: widen int8 -> bf16
+constexpr int CONV_STAGES = 3;  // must not be a multiple of CONV_GROUPS apart from 1 (groups rotate through the ring)
+constexpr int CONV_GROUPS = 2;       // groups of widening warps, taking k-blocks in turn
+constexpr int CONV_GROUP_WARPS = 8;  // warps per group
+constexpr int CONV_WARPS = CONV_GROUPS * CONV_GROUP_WARPS;
+constexpr int W8_NUM_THREADS = 192 + CONV_WARPS * 32;  // + warps 6..21: widen int8 -> bf16
 constexpr int W8_SMEM_BYTES = W8_STAGES * W8_STAGE_BYTES + CONV_STAGES * B_STAGE_BYTES + 1024 + 256;
 
 
@@ -98,10 +100,10 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const CU
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(smem_u32(&bars->full[s]), 1);
-      mbar_init(smem_u32(&bars->empty[s]), W8 ? 1 + CONV_WARPS : 1);  // MMA commit (+ the widening warps)
+      mbar_init(smem_u32(&bars->empty[s]), W8 ? 1 + CONV_GROUP_WARPS : 1);  // MMA commit (+ one widening group)
     }
     for (int c = 0; c < CONV_STAGES; ++c) {
-      mbar_init(smem_u32(&bars->conv_full[c]), CONV_WARPS);
+      mbar_init(smem_u32(&bars->conv_full[c]), CONV_GROUP_WARPS);
       mbar_init(smem_u32(&bars->conv_empty[c]), 1);
     }
     for (int b = 0; b < ACC_BUFS; ++b) {
@@ -238,20 +240,25 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const CU
       }
     }
   } else if (W8 && warp >= 6) {
-    // ================= int8 -> bf16 widening (warps 6..13, W8 only) =================
-    // Per k-block: 256 rows x 64 int8.  Thread t of the 256 handles 16-byte pieces (row, c) with
-    // row = (t >> 2) + 64 * i, c = t & 3: sixteen codes become two 16-byte pieces of the row's 128-byte
+    // ================= int8 -> bf16 widening (warps 6.., W8 only) =================
+    // Per k-block: 256 rows x 64 int8.  Thread t of the CONV_WARPS * 32 handles 16-byte pieces (row, c)
+    // with row = (t >> 2) + CONV_WARPS * 8 * i, c = t & 3 (each warp is latency-bound on its own chain of
+    // load, widen, store, so many warps with little work each beat few warps with a lot): sixteen codes become two 16-byte pieces of the row's 128-byte
     // bf16 line, stored at the 128B-swizzled position (piece index XOR row mod 8) the MMA expects.
-    const int ct = threadIdx.x - 192;
-    const int cw = ct >> 5;
-    int stage = 0;
-    uint32_t phase = 0;
-    int cstage = 0;
-    uint32_t cphase = 0;
+    // The widening warps form CONV_GROUPS groups that take k-blocks in turn: a group's chain of wait,
+    // load, widen, store, proxy fence and arrive has a latency of several hundred cycles, and groups
+    // working on different k-blocks overlap those chains.
+    const int ct = (threadIdx.x - 192) % (CONV_GROUP_WARPS * 32);
+    const int grp = (threadIdx.x - 192) / (CONV_GROUP_WARPS * 32);
+    const int cw = (threadIdx.x - 192) >> 5;
+    uint32_t gk = 0;  // k-blocks seen so far, across tiles
     bool ok = true;
     for (int tile = blockIdx.x; ok && cursor_seek(cur, tile, n_tiles, num_groups, group_offsets, tc, BN_OUT);
          tile += gridDim.x) {
-      for (int kb = 0; kb < num_kb; ++kb) {
+      for (int kb = 0; kb < num_kb; ++kb, ++gk) {
+        if ((int)(gk % CONV_GROUPS) != grp) continue;
+        const int stage = gk % NS, cstage = gk % CONV_STAGES;
+        const uint32_t phase = (gk / NS) & 1u, cphase = (gk / CONV_STAGES) & 1u;
         if (!mbar_wait(smem_u32(&bars->full[stage]), phase, abort_flag) ||
             !mbar_wait(smem_u32(&bars->conv_empty[cstage]), cphase ^ 1u, abort_flag)) {
           if (lane == 0) report_error(err, ATENIA_ERR_DEVICE_TIMEOUT, 500 + cw);
@@ -263,8 +270,8 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const CU
         uint8_t* b = smem_aligned + CONV_BASE_OFF + cstage * B_STAGE_BYTES;
         const int c = ct & 3;
 #pragma unroll
-        for (int i = 0; i < BN / (CONV_WARPS * 8); ++i) {
-          const int row = (ct >> 2) + CONV_WARPS * 8 * i;
+        for (int i = 0; i < BN / (CONV_GROUP_WARPS * 8); ++i) {
+          const int row = (ct >> 2) + CONV_GROUP_WARPS * 8 * i;
           const uint4 v = *reinterpret_cast<const uint4*>(q + row * BK + c * 16);
           uint4 o0, o1;
           widen4(v.x, o0.x, o0.y);
@@ -280,14 +287,6 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const CU
         if (lane == 0) {
           mbar_arrive(smem_u32(&bars->conv_full[cstage]));
           mbar_arrive(smem_u32(&bars->empty[stage]));  // the int8 tile of this stage has been read
-        }
-        if (++cstage == CONV_STAGES) {
-          cstage = 0;
-          cphase ^= 1u;
-        }
-        if (++stage == NS) {
-          stage = 0;
-          phase ^= 1u;
         }
       }
     }

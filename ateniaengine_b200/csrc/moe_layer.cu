@@ -48,7 +48,8 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
   // the shared-memory widening kernel once every group fills several 128-row tiles.
   const bool tmem = q && (L->w8_mode == 1 || (L->w8_mode == 0 && max_rows < 256 * num_groups));
   // bf16: 256-row CTA-pair tiles pay off once an average group fills a few of them
-  const bool pairs = !q && (L->pair_mode == 1 || (L->pair_mode == 0 && max_rows >= 512 * num_groups));
+  // (INT8 has a pair kernel too, but it measures slower than the single-CTA one: only on request.)
+  const bool pairs = !tmem && (L->pair_mode == 1 || (L->pair_mode == 0 && !q && max_rows >= 512 * num_groups));
   if (L->timing) cudaEventRecord(L->ev[0], s);
   if (L->use_check_gemm) {
     GroupedGemmCheckArgs k1{a_ptr, L->d_p_gate, L->d_p_up, q ? 1 : 0, q ? L->d_sc_gate : nullptr,
@@ -115,7 +116,7 @@ int run_shared_gemms(AteniaMoeLayer* L, const __nv_bfloat16* xb, int T, cudaStre
   const AteniaMoeConfig& c = L->cfg;
   const bool q = c.weight_dtype == ATENIA_W_INT8_ROW;
   const bool tmem = q && (L->w8_mode == 1 || (L->w8_mode == 0 && T < 256));
-  const bool pairs = !q && (L->pair_mode == 1 || (L->pair_mode == 0 && T >= 512));
+  const bool pairs = !tmem && (L->pair_mode == 1 || (L->pair_mode == 0 && !q && T >= 512));
   if (L->timing) cudaEventRecord(L->ev[3], s);
   if (L->use_check_gemm) {
     GroupedGemmCheckArgs k1{xb, L->d_p_shared, L->d_p_shared + 1, q ? 1 : 0, q ? L->d_sc_shared : nullptr,
