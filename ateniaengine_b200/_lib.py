@@ -52,7 +52,8 @@ EXPORTS = [
     "atenia_quantize_per_row_i8", "atenia_register_real_moe_layer", "atenia_register_resident_moe_layer", "atenia_execute_real_moe_layer",
     "atenia_get_real_moe_layer", "atenia_moe_ep_unique_id_bytes", "atenia_moe_ep_get_unique_id",
     "atenia_moe_ep_init", "atenia_moe_status_str", "atenia_moe_counter", "atenia_moe_enable_timing",
-    "atenia_moe_last_gemm_ms", "atenia_moe_dispatch_noalloc", "atenia_moe_ep_plan",
+    "atenia_moe_last_gemm_ms", "atenia_moe_dispatch_noalloc", "atenia_moe_ep_plan", "atenia_moe_stack_create",
+    "atenia_moe_stack_forward", "atenia_moe_stack_check", "atenia_moe_stack_destroy",
 ]
 
 _lib = None
@@ -97,6 +98,11 @@ def lib():
         l.atenia_register_real_moe_layer.argtypes = [C.POINTER(HostMoeLayer)]
         l.atenia_execute_real_moe_layer.argtypes = [C.c_int64, C.c_void_p, C.c_size_t, C.c_void_p]
         l.atenia_moe_ep_get_unique_id.argtypes = [C.c_void_p]
+        l.atenia_moe_stack_create.argtypes = [C.POINTER(C.c_void_p), C.c_int, C.c_int, C.POINTER(C.c_void_p)]
+        l.atenia_moe_stack_forward.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_int,
+                                               C.c_void_p]
+        l.atenia_moe_stack_check.argtypes = [C.c_void_p, C.c_void_p]
+        l.atenia_moe_stack_destroy.argtypes = [C.c_void_p]
         l.atenia_moe_dispatch_noalloc.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p,
                                                   C.c_void_p, C.c_void_p]
         l.atenia_moe_ep_init.argtypes = [C.c_void_p, C.c_void_p]

@@ -44,6 +44,14 @@ __global__ void __launch_bounds__(256) combine_kernel(CombineArgs a) {
         acc[2 * j + 1] = __fadd_rn(acc[2 * j + 1], __fmul_rn(scale, bf16hi(p[j])));
       }
     }
+    if (a.residual) {
+      const float4* r = reinterpret_cast<const float4*>(a.residual + (size_t)t * a.d + v * 8);
+      const float4 r0 = r[0], r1 = r[1];
+      acc[0] = __fadd_rn(acc[0], r0.x); acc[1] = __fadd_rn(acc[1], r0.y);
+      acc[2] = __fadd_rn(acc[2], r0.z); acc[3] = __fadd_rn(acc[3], r0.w);
+      acc[4] = __fadd_rn(acc[4], r1.x); acc[5] = __fadd_rn(acc[5], r1.y);
+      acc[6] = __fadd_rn(acc[6], r1.z); acc[7] = __fadd_rn(acc[7], r1.w);
+    }
     if (a.out_is_f32) {
       float4* o = reinterpret_cast<float4*>(static_cast<float*>(a.out) + (size_t)t * a.d + v * 8);
       o[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);

@@ -86,6 +86,7 @@ struct CombineArgs {
   const float* topk_w;          // [T*k]
   const __nv_bfloat16* y_shared;  // [T, d] or null
   const float* gate_scale;        // [T] or null (null = 1.0)
+  const float* residual;          // [T, d] f32 added last, or null (layer stacks)
   void* out;
   int out_is_f32;
   int T, k, d;

@@ -16,6 +16,7 @@ struct AteniaMoeLayer {
   bool weights_set = false;
   bool use_check_gemm = false;  // diagnostic: CUDA-core contraction instead of tcgen05
   bool timing = false;
+  const float* residual = nullptr;  // set by a stack around one forward: added by the combine kernel
   // INT8: 0 = pick per call (tensor-memory operand kernel for small batches, shared-memory widening
   // for large ones), 1 = always the tensor-memory kernel, 2 = always shared-memory widening
   int w8_mode = 0;

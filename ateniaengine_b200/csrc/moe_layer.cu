@@ -496,6 +496,7 @@ int atenia_moe_forward(AteniaMoeLayer* L, const void* x, int x_dtype, int T, voi
   ca.topk_w = L->topk_w;
   ca.y_shared = L->has_shared ? L->y_shared : nullptr;
   ca.gate_scale = L->has_gate_vec ? L->gate_scale : nullptr;
+  ca.residual = L->residual;
   ca.out = out;
   ca.out_is_f32 = out_dtype == ATENIA_IO_F32;
   ca.T = T;

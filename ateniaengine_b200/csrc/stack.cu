@@ -1,0 +1,165 @@
+// A stack of MoE layers: x <- layer_l(x) in sequence (RealMoeStack::forward, src/moe/stack.rs:197-210),
+// optionally with a residual add per layer, x <- x + layer_l(x).  Activations between layers stay in
+// f32 on the device.  On a non-default stream the whole stack is captured once into a CUDA graph per
+// (token count, input, output) and replayed: at decode sizes a layer is ten short launches and the
+// launch overhead of 32 layers would otherwise dominate.
+#include <cstdlib>
+#include <vector>
+
+#include "layer.cuh"
+
+struct AteniaMoeStack {
+  std::vector<AteniaMoeLayer*> layers;
+  bool residual = false;
+  int d_model = 0;
+  int max_tokens = 0;
+  float* buf[2] = {nullptr, nullptr};  // ping-pong [max_tokens, d] f32
+  bool use_graph = true;
+  // cached graph
+  cudaGraphExec_t exec = nullptr;
+  const void* g_x = nullptr;
+  void* g_out = nullptr;
+  int g_T = -1, g_xdt = -1, g_odt = -1;
+  bool g_warm = false;  // the signature above has run once eagerly (one-time kernel set-up is done)
+};
+
+namespace {
+
+int run_layers(AteniaMoeStack* S, const void* x, int x_dtype, int T, void* out, int out_dtype, cudaStream_t s) {
+  const int n = (int)S->layers.size();
+  const void* cur = x;
+  int cur_dt = x_dtype;
+  for (int l = 0; l < n; ++l) {
+    const bool last = l == n - 1;
+    void* dst = last ? out : (void*)S->buf[l & 1];
+    const int dst_dt = last ? out_dtype : ATENIA_IO_F32;
+    AteniaMoeLayer* L = S->layers[l];
+    // the residual operand is the layer's own f32 input
+    const float* res = nullptr;
+    if (S->residual) {
+      if (cur_dt != ATENIA_IO_F32) return ATENIA_ERR_UNSUPPORTED;
+      res = static_cast<const float*>(cur);
+    }
+    L->residual = res;
+    int rc = atenia_moe_forward(L, cur, cur_dt, T, dst, dst_dt, nullptr, s);
+    L->residual = nullptr;
+    if (rc) return rc;
+    cur = dst;
+    cur_dt = dst_dt;
+  }
+  return ATENIA_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int atenia_moe_stack_create(AteniaMoeLayer* const* layers, int n_layers, int residual, AteniaMoeStack** out) {
+  if (!layers || !out) return ATENIA_ERR_NULL;
+  *out = nullptr;
+  if (n_layers < 1) return ATENIA_ERR_SHAPE;
+  AteniaMoeStack* S = new AteniaMoeStack();
+  S->residual = residual != 0;
+  for (int l = 0; l < n_layers; ++l) {
+    AteniaMoeLayer* L = layers[l];
+    if (!L) {
+      delete S;
+      return ATENIA_ERR_NULL;
+    }
+    if (!L->weights_set || L->cfg.ep_world != 1) {
+      delete S;
+      return ATENIA_ERR_STATE;
+    }
+    if (l == 0) {
+      S->d_model = L->cfg.d_model;
+      S->max_tokens = L->cfg.max_tokens;
+    } else {
+      if (L->cfg.d_model != S->d_model) {  // MoeStackError::DModelMismatch
+        delete S;
+        return ATENIA_ERR_DIM_MISMATCH;
+      }
+      if (L->cfg.max_tokens < S->max_tokens) S->max_tokens = L->cfg.max_tokens;
+    }
+    S->layers.push_back(L);
+  }
+  const size_t bytes = (size_t)S->max_tokens * S->d_model * sizeof(float);
+  for (int i = 0; i < 2; ++i) {
+    cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&S->buf[i]), bytes);
+    if (e != cudaSuccess) {
+      atenia_moe_stack_destroy(S);
+      return (int)e;
+    }
+  }
+  const char* g = std::getenv("ATENIA_MOE_STACK_GRAPH");
+  S->use_graph = !(g && std::atoi(g) == 0);
+  *out = S;
+  return ATENIA_OK;
+}
+
+int atenia_moe_stack_destroy(AteniaMoeStack* S) {
+  if (!S) return ATENIA_OK;
+  cudaDeviceSynchronize();
+  if (S->exec) cudaGraphExecDestroy(S->exec);
+  for (int i = 0; i < 2; ++i)
+    if (S->buf[i]) cudaFree(S->buf[i]);
+  delete S;
+  return ATENIA_OK;
+}
+
+int atenia_moe_stack_forward(AteniaMoeStack* S, const void* x, int x_dtype, int T, void* out, int out_dtype,
+                             void* stream) {
+  if (!S || !x || !out) return ATENIA_ERR_NULL;
+  if (T < 0) return ATENIA_ERR_SHAPE;
+  if (T > S->max_tokens) return ATENIA_ERR_CAPACITY;
+  if (T == 0) return ATENIA_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  bool timing = false;
+  for (AteniaMoeLayer* L : S->layers) timing = timing || L->timing;
+  if (!S->use_graph || s == nullptr || timing) return run_layers(S, x, x_dtype, T, out, out_dtype, s);
+  const bool same = S->g_x == x && S->g_out == out && S->g_T == T && S->g_xdt == x_dtype && S->g_odt == out_dtype;
+  if (!same || !S->g_warm) {
+    // first call with this signature: run eagerly (kernels do their one-time attribute set-up outside
+    // of any capture), capture on the next one
+    if (S->exec) {
+      cudaGraphExecDestroy(S->exec);
+      S->exec = nullptr;
+    }
+    S->g_x = x;
+    S->g_out = out;
+    S->g_T = T;
+    S->g_xdt = x_dtype;
+    S->g_odt = out_dtype;
+    S->g_warm = true;
+    return run_layers(S, x, x_dtype, T, out, out_dtype, s);
+  }
+  if (!S->exec) {
+    // Everything a forward does on a single GPU is kernel launches on `s`, so it can be captured.
+    ATENIA_CUDA_TRY(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
+    int rc = run_layers(S, x, x_dtype, T, out, out_dtype, s);
+    cudaGraph_t graph = nullptr;
+    cudaError_t e = cudaStreamEndCapture(s, &graph);
+    if (rc) {
+      if (graph) cudaGraphDestroy(graph);
+      return rc;
+    }
+    if (e != cudaSuccess) return (int)e;
+    e = cudaGraphInstantiate(&S->exec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (e != cudaSuccess) return (int)e;
+  }
+  ATENIA_CUDA_TRY(cudaGraphLaunch(S->exec, s));
+  atenia::count_launch((int)S->layers.size());  // at least one kernel per layer was replayed
+  return ATENIA_OK;
+}
+
+int atenia_moe_stack_check(AteniaMoeStack* S, void* stream) {
+  if (!S) return ATENIA_ERR_NULL;
+  int first = ATENIA_OK;
+  for (AteniaMoeLayer* L : S->layers) {
+    int rc = atenia_moe_check(L, stream);
+    if (rc && !first) first = rc;
+  }
+  return first;
+}
+
+}  // extern "C"

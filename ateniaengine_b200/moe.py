@@ -295,3 +295,46 @@ def dispatch_noalloc(topk_idx, num_experts, perm, inv_perm, expert_offsets):
         st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
         return _lib.lib().atenia_moe_dispatch_noalloc(_ptr(topk_idx), T, k, int(num_experts), _ptr(perm),
                                                       _ptr(inv_perm), _ptr(expert_offsets), st)
+
+
+class RealMoeStack:
+    """A sequence of RealMoeLayer applied one after the other (RealMoeStack, src/moe/stack.rs).
+
+    `residual=True` computes x <- x + layer(x) per layer (f32 input required).  The layers are
+    borrowed: keep them alive.  Call on a non-default CUDA stream to get CUDA-graph replay.
+    """
+
+    def __init__(self, layers, residual=False):
+        assert len(layers) >= 1
+        self.layers = list(layers)
+        self.device = layers[0].device
+        self.d_model = layers[0].config.d_model
+        arr = (C.c_void_p * len(layers))(*[l.handle.value for l in layers])
+        self._h = C.c_void_p()
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.lib().atenia_moe_stack_create(arr, len(layers), int(residual), C.byref(self._h)),
+                       "atenia_moe_stack_create")
+
+    def forward(self, x, out=None, out_dtype=None, sync=False):
+        assert x.is_cuda and x.dim() == 2 and x.shape[1] == self.d_model
+        x = x.contiguous()
+        if out is None:
+            out = torch.empty(x.shape, dtype=out_dtype or x.dtype, device=x.device)
+        with torch.cuda.device(x.device):
+            st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+            _lib.check(_lib.lib().atenia_moe_stack_forward(self._h, _ptr(x), _io_dtype(x), x.shape[0], _ptr(out),
+                                                           _io_dtype(out), st), "atenia_moe_stack_forward")
+            if sync:
+                _lib.check(_lib.lib().atenia_moe_stack_check(self._h, st), "atenia_moe_stack_check")
+        return out
+
+    def close(self):
+        if getattr(self, "_h", None) is not None and self._h.value:
+            _lib.lib().atenia_moe_stack_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

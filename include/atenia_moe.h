@@ -15,6 +15,7 @@
  *   register_resident_moe_layer          src/moe/graph_op.rs:237   atenia_register_resident_moe_layer
  *   execute_real_moe_layer               src/moe/graph_op.rs:327   atenia_execute_real_moe_layer
  *   quantize_per_row_i8                  src/tensor/disk_tier.rs:231-245  atenia_quantize_per_row_i8
+ *   RealMoeStack::forward                src/moe/stack.rs:197-210  atenia_moe_stack_forward
  *
  * Conventions follow the reference's existing CUDA FFI (src/cuda/*.cu): plain `extern "C"` functions,
  * `int` status (0 = ok, > 0 = a cudaError_t value, < 0 = argument / shape / state errors listed
@@ -207,6 +208,22 @@ ATENIA_API int atenia_execute_real_moe_layer(int64_t layer_id, const float* inpu
 /* The device layer behind a registry id (NULL if unknown), for callers that keep activations on the
  * device. */
 ATENIA_API AteniaMoeLayer* atenia_get_real_moe_layer(int64_t layer_id);
+
+/* ---- layer stack ------------------------------------------------------------------------------
+ * RealMoeStack::forward (src/moe/stack.rs:197-210): x <- layer_l(x) for l = 0..n-1, every layer with
+ * its own convention, no norm.  `residual` != 0 computes x <- x + layer_l(x) instead (the reference
+ * stack has no residual; the 32-layer decode benchmark does) and then requires f32 input.  The stack
+ * borrows the layers (single GPU, equal d_model, else ATENIA_ERR_DIM_MISMATCH as
+ * MoeStackError::DModelMismatch); activations between layers are f32 buffers of the stack.  On a
+ * non-default stream the sequence is captured once per (T, x, out) into a CUDA graph and replayed. */
+typedef struct AteniaMoeStack AteniaMoeStack;
+ATENIA_API int atenia_moe_stack_create(AteniaMoeLayer* const* layers, int n_layers, int residual,
+                                       AteniaMoeStack** out);
+ATENIA_API int atenia_moe_stack_forward(AteniaMoeStack* stack, const void* x, int x_dtype, int T, void* out,
+                                        int out_dtype, void* stream);
+/* Waits for the stream and returns the first error any layer's kernels recorded. */
+ATENIA_API int atenia_moe_stack_check(AteniaMoeStack* stack, void* stream);
+ATENIA_API int atenia_moe_stack_destroy(AteniaMoeStack* stack);
 
 /* ---- expert parallelism ------------------------------------------------------------------- */
 
