@@ -54,6 +54,7 @@ EXPORTS = [
     "atenia_moe_ep_init", "atenia_moe_status_str", "atenia_moe_counter", "atenia_moe_enable_timing",
     "atenia_moe_last_gemm_ms", "atenia_moe_dispatch_noalloc", "atenia_moe_ep_plan", "atenia_moe_stack_create",
     "atenia_moe_stack_forward", "atenia_moe_stack_check", "atenia_moe_stack_destroy",
+    "atenia_moe_forward_selected",
 ]
 
 _lib = None
@@ -91,6 +92,8 @@ def lib():
         l.atenia_moe_forward.argtypes = fwd
         l.atenia_moe_forward_sync.argtypes = fwd
         l.atenia_moe_check.argtypes = [C.c_void_p, C.c_void_p]
+        l.atenia_moe_forward_selected.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p,
+                                                  C.c_void_p, C.c_int, C.c_void_p]
         l.atenia_moe_route_from_logits.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p,
                                                    C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
         l.atenia_quantize_per_row_i8.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p,

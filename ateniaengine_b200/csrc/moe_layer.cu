@@ -421,8 +421,22 @@ int atenia_moe_set_weights(AteniaMoeLayer* L, const AteniaMoeWeights* w) {
   return ATENIA_OK;
 }
 
+static int forward_impl(AteniaMoeLayer* L, const void* x, int x_dtype, int T, void* out, int out_dtype,
+                        const AteniaMoeAux* aux, void* stream, const int32_t* sel_idx, const float* sel_w);
+
 int atenia_moe_forward(AteniaMoeLayer* L, const void* x, int x_dtype, int T, void* out, int out_dtype,
                        const AteniaMoeAux* aux, void* stream) {
+  return forward_impl(L, x, x_dtype, T, out, out_dtype, aux, stream, nullptr, nullptr);
+}
+
+int atenia_moe_forward_selected(AteniaMoeLayer* L, const void* x, int x_dtype, int T, const int32_t* topk_idx,
+                                const float* topk_w, void* out, int out_dtype, void* stream) {
+  if (!topk_idx || !topk_w) return ATENIA_ERR_NULL;
+  return forward_impl(L, x, x_dtype, T, out, out_dtype, nullptr, stream, topk_idx, topk_w);
+}
+
+static int forward_impl(AteniaMoeLayer* L, const void* x, int x_dtype, int T, void* out, int out_dtype,
+                        const AteniaMoeAux* aux, void* stream, const int32_t* sel_idx, const float* sel_w) {
   if (!L || !x || !out) return ATENIA_ERR_NULL;
   if (!L->weights_set) return ATENIA_ERR_STATE;
   if (T < 0) return ATENIA_ERR_SHAPE;
@@ -456,6 +470,11 @@ int atenia_moe_forward(AteniaMoeLayer* L, const void* x, int x_dtype, int T, voi
   ra.err = L->d_err;
   int rc = launch_router(ra, s);
   if (rc) return rc;
+  if (sel_idx && n > 0) {
+    // the caller's selection replaces the router's (the router still ran: it owns the shared gate)
+    ATENIA_CUDA_TRY(cudaMemcpyAsync(L->topk_idx, sel_idx, (size_t)n * 4, cudaMemcpyDeviceToDevice, s));
+    ATENIA_CUDA_TRY(cudaMemcpyAsync(L->topk_w, sel_w, (size_t)n * 4, cudaMemcpyDeviceToDevice, s));
+  }
 
   DispatchArgs da{};
   da.topk_idx = L->topk_idx;

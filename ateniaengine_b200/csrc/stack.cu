@@ -11,6 +11,8 @@
 struct AteniaMoeStack {
   std::vector<AteniaMoeLayer*> layers;
   bool residual = false;
+  bool prenorm = false;       // residual == 2: x <- x + layer(rmsnorm(x))
+  float* normed = nullptr;    // [max_tokens, d] f32
   int d_model = 0;
   int max_tokens = 0;
   float* buf[2] = {nullptr, nullptr};  // ping-pong [max_tokens, d] f32
@@ -24,6 +26,27 @@ struct AteniaMoeStack {
 };
 
 namespace {
+
+// y[t, :] = x[t, :] / sqrt(mean(x[t, :]^2) + 1e-5): RMSNorm with unit gain, one block per row.
+__global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const float* __restrict__ x, float* __restrict__ y, int d) {
+  __shared__ float red[8];
+  __shared__ float s_inv;
+  const float* row = x + (size_t)blockIdx.x * d;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < d; c += blockDim.x) ss += row[c] * row[c];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int i = 0; i < 8; ++i) t += red[i];
+    s_inv = rsqrtf(t / (float)d + 1e-5f);
+  }
+  __syncthreads();
+  const float inv = s_inv;
+  for (int c = threadIdx.x; c < d; c += blockDim.x) y[(size_t)blockIdx.x * d + c] = row[c] * inv;
+}
 
 int run_layers(AteniaMoeStack* S, const void* x, int x_dtype, int T, void* out, int out_dtype, cudaStream_t s) {
   const int n = (int)S->layers.size();
@@ -40,8 +63,14 @@ int run_layers(AteniaMoeStack* S, const void* x, int x_dtype, int T, void* out, 
       if (cur_dt != ATENIA_IO_F32) return ATENIA_ERR_UNSUPPORTED;
       res = static_cast<const float*>(cur);
     }
+    const void* in = cur;
+    if (S->prenorm) {
+      rmsnorm_rows_kernel<<<T, 256, 0, s>>>(static_cast<const float*>(cur), S->normed, S->d_model);
+      atenia::count_launch();
+      in = S->normed;
+    }
     L->residual = res;
-    int rc = atenia_moe_forward(L, cur, cur_dt, T, dst, dst_dt, nullptr, s);
+    int rc = atenia_moe_forward(L, in, cur_dt, T, dst, dst_dt, nullptr, s);
     L->residual = nullptr;
     if (rc) return rc;
     cur = dst;
@@ -60,6 +89,7 @@ int atenia_moe_stack_create(AteniaMoeLayer* const* layers, int n_layers, int res
   if (n_layers < 1) return ATENIA_ERR_SHAPE;
   AteniaMoeStack* S = new AteniaMoeStack();
   S->residual = residual != 0;
+  S->prenorm = residual == 2;
   for (int l = 0; l < n_layers; ++l) {
     AteniaMoeLayer* L = layers[l];
     if (!L) {
@@ -90,6 +120,13 @@ int atenia_moe_stack_create(AteniaMoeLayer* const* layers, int n_layers, int res
       return (int)e;
     }
   }
+  if (S->prenorm) {
+    cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&S->normed), bytes);
+    if (e != cudaSuccess) {
+      atenia_moe_stack_destroy(S);
+      return (int)e;
+    }
+  }
   const char* g = std::getenv("ATENIA_MOE_STACK_GRAPH");
   S->use_graph = !(g && std::atoi(g) == 0);
   *out = S;
@@ -102,6 +139,7 @@ int atenia_moe_stack_destroy(AteniaMoeStack* S) {
   if (S->exec) cudaGraphExecDestroy(S->exec);
   for (int i = 0; i < 2; ++i)
     if (S->buf[i]) cudaFree(S->buf[i]);
+  if (S->normed) cudaFree(S->normed);
   delete S;
   return ATENIA_OK;
 }

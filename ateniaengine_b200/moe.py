@@ -181,6 +181,24 @@ class RealMoeLayer:
 
     forward_auto = forward
 
+    def forward_selected(self, x, topk_idx, topk_w, out_dtype=None, sync=True):
+        """The block with a caller-supplied selection (the graph primitives MoeDynamicDispatch /
+        MoeSparseCombine in batched form): topk_idx [T, k] int32, topk_w [T, k] f32."""
+        x = x.contiguous()
+        T = x.shape[0]
+        out = torch.empty((T, self.config.d_model), dtype=out_dtype or x.dtype, device=x.device)
+        topk_idx = topk_idx.contiguous()
+        topk_w = topk_w.contiguous()
+        assert topk_idx.dtype == torch.int32 and topk_w.dtype == torch.float32
+        with torch.cuda.device(x.device):
+            st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+            _lib.check(_lib.lib().atenia_moe_forward_selected(self._h, _ptr(x), _io_dtype(x), T, _ptr(topk_idx),
+                                                              _ptr(topk_w), _ptr(out), _io_dtype(out), st),
+                       "atenia_moe_forward_selected")
+            if sync:
+                _lib.check(_lib.lib().atenia_moe_check(self._h, st), "atenia_moe_forward_selected")
+        return out
+
     def check(self):
         with torch.cuda.device(self.device):
             st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
@@ -300,7 +318,8 @@ def dispatch_noalloc(topk_idx, num_experts, perm, inv_perm, expert_offsets):
 class RealMoeStack:
     """A sequence of RealMoeLayer applied one after the other (RealMoeStack, src/moe/stack.rs).
 
-    `residual=True` computes x <- x + layer(x) per layer (f32 input required).  The layers are
+    `residual=True` (or 1) computes x <- x + layer(x) per layer; `residual=2` computes the pre-norm
+    block x <- x + layer(rmsnorm(x)) (unit gain, eps 1e-5); both need f32 input.  The layers are
     borrowed: keep them alive.  Call on a non-default CUDA stream to get CUDA-graph replay.
     """
 

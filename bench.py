@@ -133,6 +133,84 @@ def cpu_oracle_rate(shape, w, x_host, max_seconds, threads=0):
     return n / dt, cores, n, ol
 
 
+def run_stack_bench(args):
+    """Decode benchmark: a stack of W8A16 Mixtral-shaped MoE-FFN layers with a residual add between
+    layers (attention omitted), Zipf-skewed routing, small batches.  One step = one pass of the batch
+    through all layers (replayed from a CUDA graph on a side stream)."""
+    import numpy as np
+    import torch
+
+    from ateniaengine_b200 import _lib, synth
+    from ateniaengine_b200.moe import RealMoeStack
+
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    shape = synth.SHAPES["mixtral_int8"]
+    B = args.tokens or 8
+    n_layers = args.layers
+    ws = [synth.make_weights(shape, 5 + l, dev) for l in range(n_layers)]
+    layers = [synth.build_layer(shape, w, max_tokens=max(B, 1)) for w in ws]
+    stack = RealMoeStack(layers, residual=2)
+    x = synth.make_activations(shape, 5, dev, tokens=B, dtype=torch.float32)
+    out = torch.empty_like(x)
+    # experts touched per layer (weights that must cross HBM): one eager pass with routing outputs
+    cur = x
+    touched = []
+    gemm_ms = 0.0
+    for l in layers:
+        l.enable_timing(True)
+        xn = cur * torch.rsqrt((cur * cur).mean(dim=1, keepdim=True) + 1e-5)
+        y, aux = l.forward(xn, out_dtype=torch.float32, aux=True, sync=True)
+        touched.append(int(torch.unique(aux["topk_idx"]).numel()))
+        gemm_ms += l.last_gemm_ms(0) + l.last_gemm_ms(1)
+        l.enable_timing(False)
+        cur = cur + y
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        for _ in range(max(args.warmup, 3)):
+            stack.forward(x, out=out)
+        side.synchronize()
+        sampler = ClockSampler(0)
+        sampler.start()
+        time.sleep(0.8)
+        for _ in range(3):
+            stack.forward(x, out=out)
+        side.synchronize()
+        t0 = time.perf_counter()
+        launches0 = _lib.lib().atenia_moe_counter(1)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(side)
+        for _ in range(args.steps):
+            stack.forward(x, out=out)
+        e1.record(side)
+        side.synchronize()
+        ms = e0.elapsed_time(e1) / args.steps
+        launches = int(_lib.lib().atenia_moe_counter(1) - launches0)
+        sampler.window = (t0, time.perf_counter())
+        clocks = sampler.stop()
+    _lib.check(_lib.lib().atenia_moe_stack_check(stack._h, None), "stack_check")
+    assert torch.isfinite(out).all()
+    peaks, peak_src = load_peaks()
+    wbytes = sum(t * 3 * shape.d_model * shape.d_ff for t in touched)  # one byte per weight
+    achieved = wbytes / (ms * 1e-3) / 1e9
+    line = {"metric": "moe_ffn_stack_tokens_per_s", "value": B / (ms * 1e-3), "unit": UNIT, "n_gpus": 1,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "int8 weights, bf16 operands, f32 residual stream (W8A16)",
+            "data": "synthetic",
+            "config": {"workload": f"mixtral_int8 stack: {n_layers} layers, d_model={shape.d_model} d_ff={shape.d_ff} "
+                                   f"experts={shape.num_experts} top_k={shape.top_k}, pre-norm residual blocks x + MoE(rmsnorm(x)), batch={B}",
+                       "routing_skew": "zipf(1.1)", "experts_touched_per_layer": touched,
+                       "l2_policy": f"inputs larger than L2: {wbytes / 1e6:.0f} MB of expert weights per step"},
+            "roofline": {"bound": "hbm", "kernel": "whole step (weights of the touched experts, once per step)",
+                         "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": achieved / peaks["hbm_gbs"], "peak_source": peak_src, "traffic": None,
+                         "eager_gemm_ms_per_step": gemm_ms},
+            "cpu_baseline": None, "e2e": None, "clocks": clocks, "gpu_launches": launches,
+            "note": "launches replayed from a CUDA graph are counted once per layer"}
+    print(json.dumps(line))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -143,7 +221,12 @@ def main():
     ap.add_argument("--tokens", type=int, default=0, help="tokens per rank (default: the workload's)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    ap.add_argument("--layers", type=int, default=32, help="layers of the mixtral_int8_stack workload")
     args = ap.parse_args()
+    if args.workload == "mixtral_int8_stack":
+        if int(os.environ.get("RANK", "0")) != 0:
+            return 0
+        return run_stack_bench(args)
     args.warmup = max(args.warmup, 3)
 
     rank = int(os.environ.get("RANK", "0"))

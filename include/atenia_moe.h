@@ -127,6 +127,18 @@ ATENIA_API int atenia_moe_set_weights(AteniaMoeLayer* layer, const AteniaMoeWeig
 ATENIA_API int atenia_moe_forward(AteniaMoeLayer* layer, const void* x, int x_dtype, int T, void* out,
                                   int out_dtype, const AteniaMoeAux* aux, void* stream);
 
+/* The block with the selection supplied by the caller instead of the router: topk_idx [T, k] (device,
+ * int32, expert ids in [0, E), need not be sorted) and topk_w [T, k] (device, f32) are used as they
+ * are; everything after routing is unchanged (out = sum_s w[t,s] * expert_{idx[t,s]}(x_t), slots in
+ * the given order, + the shared expert).  This is the batched form of the reference's decomposed
+ * graph primitives MoeDynamicDispatch / ConditionalExpert / MoeSparseCombine
+ * (src/moe/graph_op.rs:84-188, src/amg/graph.rs:5406-5566), whose selection tensor is the flat
+ * [idx0, w0, idx1, w1, ...] list; the router primitives MoeRouterSoftmax / MoeTopK are
+ * atenia_moe_route_from_logits.  An id outside [0, E) records ATENIA_ERR_ROUTING. */
+ATENIA_API int atenia_moe_forward_selected(AteniaMoeLayer* layer, const void* x, int x_dtype, int T,
+                                           const int32_t* topk_idx, const float* topk_w, void* out,
+                                           int out_dtype, void* stream);
+
 /* Same, then waits for the stream and returns any error a kernel recorded (routing errors,
  * bounded-wait timeouts).  Mirrors the reference's synchronous launchers. */
 ATENIA_API int atenia_moe_forward_sync(AteniaMoeLayer* layer, const void* x, int x_dtype, int T, void* out,
@@ -211,8 +223,11 @@ ATENIA_API AteniaMoeLayer* atenia_get_real_moe_layer(int64_t layer_id);
 
 /* ---- layer stack ------------------------------------------------------------------------------
  * RealMoeStack::forward (src/moe/stack.rs:197-210): x <- layer_l(x) for l = 0..n-1, every layer with
- * its own convention, no norm.  `residual` != 0 computes x <- x + layer_l(x) instead (the reference
- * stack has no residual; the 32-layer decode benchmark does) and then requires f32 input.  The stack
+ * its own convention, no norm.  `residual` = 1 computes x <- x + layer_l(x) instead (the reference
+ * stack has no residual; the 32-layer decode benchmark does); `residual` = 2 computes the pre-norm
+ * block of a transformer with attention left out, x <- x + layer_l(rmsnorm(x)) with unit gain and
+ * eps 1e-5 (without a norm, random SwiGLU layers blow the residual stream up within a few layers).
+ * Both require f32 input.  The stack
  * borrows the layers (single GPU, equal d_model, else ATENIA_ERR_DIM_MISMATCH as
  * MoeStackError::DModelMismatch); activations between layers are f32 buffers of the stack.  On a
  * non-default stream the sequence is captured once per (T, x, out) into a CUDA graph and replayed. */

@@ -19,7 +19,7 @@ def _build(n_layers, int8):
     return shape, ws, layers
 
 
-@pytest.mark.parametrize("residual,int8", [(True, True), (False, False)])
+@pytest.mark.parametrize("residual,int8", [(1, True), (2, True), (0, False)])
 def test_stack_matches_layerwise_oracle(residual, int8):
     if not torch.cuda.is_available():
         pytest.skip("needs a CUDA device")
@@ -41,7 +41,10 @@ def test_stack_matches_layerwise_oracle(residual, int8):
     if residual:
         ref = x.cpu().numpy()
         for w in ws:
-            ref = ref + oracle_layer(shape, w).forward(ref)
+            xin = ref
+            if residual == 2:
+                xin = (ref / np.sqrt((ref.astype(np.float64) ** 2).mean(axis=1, keepdims=True) + 1e-5)).astype(np.float32)
+            ref = ref + oracle_layer(shape, w).forward(xin)
         assert rel_l2(eager.cpu().numpy(), ref) <= tol
     else:
         # Without a residual the activations shrink towards zero, the router's logits with them, and
