@@ -115,6 +115,7 @@ struct GroupedGemmArgs {
   DeviceError* err;
   int max_rows;  // upper bound on total rows (sizes nothing; used by the checking kernel's grid)
   int w8;        // B matrices are int8 (tensor maps of bytes), widened to bf16 inside the kernel
+  float* splitk_ws;  // W8 tensor-memory kernel: workspace for stream-K partial sums (null: whole tiles only)
 };
 int launch_grouped_gemm_tcgen05(const GroupedGemmArgs& a, int num_sms, cudaStream_t s);
 
@@ -149,6 +150,7 @@ int encode_tmap_2d_u8(CUtensorMap* out, const void* base, uint64_t rows, uint64_
 // W8A16 grouped GEMM with the weights as the tensor-memory operand (w8_gemm.cu).  tmap_a is the bf16
 // token matrix (box {64, 128}, 128B swizzle); tmap_b0/b1 are int8 maps with the 64-byte swizzle.
 int launch_grouped_gemm_w8_tmem(const GroupedGemmArgs& a, int num_sms, cudaStream_t s);
+constexpr size_t kW8SplitKSlotFloats = 2 * 128 * 128;  // per CTA: two slots of this size
 // bf16 weights, CTA pairs (tcgen05 cta_group::2): 256-row tiles, each CTA stages half of the weight tile
 int launch_grouped_gemm_2cta(const GroupedGemmArgs& a, int num_sms, cudaStream_t s);
 

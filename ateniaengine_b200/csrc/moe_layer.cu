@@ -73,6 +73,8 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
     g1.err = L->d_err;
     g1.max_rows = max_rows;
     g1.w8 = q;
+  g1.splitk_ws = L->splitk_ws;
+    g1.splitk_ws = L->splitk_ws;
     int rc = tmem ? launch_grouped_gemm_w8_tmem(g1, L->num_sms, s)
                   : pairs ? launch_grouped_gemm_2cta(g1, L->num_sms, s) : launch_grouped_gemm_tcgen05(g1, L->num_sms, s);
     if (rc) return rc;
@@ -99,6 +101,8 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
     g2.err = L->d_err;
     g2.max_rows = max_rows;
     g2.w8 = q;
+  g2.splitk_ws = L->splitk_ws;
+    g2.splitk_ws = L->splitk_ws;
     int rc = tmem ? launch_grouped_gemm_w8_tmem(g2, L->num_sms, s)
                   : pairs ? launch_grouped_gemm_2cta(g2, L->num_sms, s) : launch_grouped_gemm_tcgen05(g2, L->num_sms, s);
     if (rc) return rc;
@@ -146,6 +150,7 @@ int run_shared_gemms(AteniaMoeLayer* L, const __nv_bfloat16* xb, int T, cudaStre
   g1.err = L->d_err;
   g1.max_rows = T;
   g1.w8 = q;
+  g1.splitk_ws = L->splitk_ws;
   rc = tmem ? launch_grouped_gemm_w8_tmem(g1, L->num_sms, s)
             : pairs ? launch_grouped_gemm_2cta(g1, L->num_sms, s) : launch_grouped_gemm_tcgen05(g1, L->num_sms, s);
   if (rc) return rc;
@@ -164,6 +169,7 @@ int run_shared_gemms(AteniaMoeLayer* L, const __nv_bfloat16* xb, int T, cudaStre
   g2.err = L->d_err;
   g2.max_rows = T;
   g2.w8 = q;
+  g2.splitk_ws = L->splitk_ws;
   rc = tmem ? launch_grouped_gemm_w8_tmem(g2, L->num_sms, s)
             : pairs ? launch_grouped_gemm_2cta(g2, L->num_sms, s) : launch_grouped_gemm_tcgen05(g2, L->num_sms, s);
   if (rc) return rc;
@@ -242,6 +248,7 @@ int atenia_moe_create(const AteniaMoeConfig* cfg, AteniaMoeLayer** out) {
   TRY_ALLOC(L->d_tm_down, (size_t)L->n_groups);
   TRY_ALLOC(L->d_tm_shared, 3);
   if (c.weight_dtype == ATENIA_W_INT8_ROW) {
+    TRY_ALLOC(L->splitk_ws, (size_t)L->num_sms * 2 * kW8SplitKSlotFloats);
     TRY_ALLOC(L->d_tm_gate_sw, (size_t)L->n_groups);
     TRY_ALLOC(L->d_tm_up_sw, (size_t)L->n_groups);
     TRY_ALLOC(L->d_tm_down_sw, (size_t)L->n_groups);
@@ -304,7 +311,7 @@ int atenia_moe_destroy(AteniaMoeLayer* L) {
                   L->x_bf16,     L->h_shared,    L->y_shared,    L->d_err,          L->d_tm_gate,
                   L->d_tm_up,    L->d_tm_down,   L->d_tm_shared, L->d_sc_gate,      L->d_sc_up,
                   L->d_sc_down,  L->d_sc_shared, L->d_p_gate,    L->d_p_up,         L->d_p_down,
-                  L->d_p_shared, L->d_tm_gate_sw, L->d_tm_up_sw, L->d_tm_down_sw, L->d_tm_shared_sw, L->recv_x,      L->recv_h,      L->recv_y,         L->d_counts_all,
+                  L->d_p_shared, L->d_tm_gate_sw, L->d_tm_up_sw, L->d_tm_down_sw, L->d_tm_shared_sw, L->splitk_ws, L->recv_x,      L->recv_h,      L->recv_y,         L->d_counts_all,
                   L->d_group_offsets};
   for (void* p : ptrs)
     if (p) cudaFree(p);

@@ -59,13 +59,76 @@ __device__ __forceinline__ uint32_t idesc_for(int n) {
   return (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(n >> 3) << 17) | (uint32_t(WROWS >> 4) << 24);
 }
 
+// ---- work decomposition ---------------------------------------------------------------------------
+// Whole tiles dealt round-robin (large batches), or "stream-K": the flattened list of (tile, k-block)
+// pairs is cut into one contiguous span per CTA, so that every SM streams the same number of weight
+// bytes even when there are fewer tiles than SMs (decode batches).  A span covers at most one partial
+// piece at its start and one at its end; partial pieces leave their raw f32 accumulators in a
+// workspace slot (2 per CTA) and a second kernel adds the pieces of a tile in CTA order.
+constexpr int SLOT_FLOATS = 2 * TN * WROWS;  // [accumulator][token][feature]
+
+struct PieceIter {
+  bool splitk;
+  int num_kb, n_tiles, num_groups, bn_out;
+  const int32_t* off;
+  TileCursor cur;
+  int tile, stride;       // round-robin mode
+  long long g, g0, g_end; // stream-K mode: flattened k-block range of this CTA
+  // current piece
+  TileCoord tc;
+  int kb0, nkb, slot;     // slot: -1 = the piece is a whole tile, else the workspace slot of this CTA
+
+  __device__ void init(bool sk, int num_kb_, int n_tiles_, int num_groups_, int bn_out_, const int32_t* off_) {
+    splitk = sk;
+    num_kb = num_kb_;
+    n_tiles = n_tiles_;
+    num_groups = num_groups_;
+    bn_out = bn_out_;
+    off = off_;
+    cur.group = 0;
+    cur.base = 0;
+    if (num_groups > 0) cursor_load(cur, off);
+    tile = blockIdx.x;
+    stride = gridDim.x;
+    g = g0 = g_end = 0;
+    if (splitk) {
+      long long total_tiles = 0;
+      for (int gi = 0; gi < num_groups; ++gi)
+        total_tiles += (long long)((off[gi + 1] - off[gi] + BM - 1) / BM) * n_tiles;
+      const long long total = total_tiles * num_kb;
+      const long long span = (total + gridDim.x - 1) / gridDim.x;
+      g0 = g = (long long)blockIdx.x * span;
+      g_end = g0 + span < total ? g0 + span : total;
+    }
+  }
+  __device__ bool next() {
+    if (!splitk) {
+      if (!cursor_seek(cur, tile, n_tiles, num_groups, off, tc, bn_out)) return false;
+      tile += stride;
+      kb0 = 0;
+      nkb = num_kb;
+      slot = -1;
+      return true;
+    }
+    if (g >= g_end) return false;
+    const int t = (int)(g / num_kb);
+    kb0 = (int)(g - (long long)t * num_kb);
+    const long long left = g_end - g;
+    nkb = (num_kb - kb0) < left ? (num_kb - kb0) : (int)left;
+    if (!cursor_seek(cur, t, n_tiles, num_groups, off, tc, bn_out)) return false;
+    slot = (nkb == num_kb) ? -1 : (g == g0 ? 0 : 1);
+    g += nkb;
+    return true;
+  }
+};
+
 template <int MODE>
 __global__ void __launch_bounds__(NUM_THREADS_W8, 1)
 grouped_gemm_w8_tmem_kernel(const __grid_constant__ CUtensorMap tmap_x, const CUtensorMap* __restrict__ tmap_w0,
                             const CUtensorMap* __restrict__ tmap_w1, const int32_t* __restrict__ group_offsets,
                             int num_groups, int N, int K, __nv_bfloat16* __restrict__ out,
                             const float* const* __restrict__ scale0, const float* const* __restrict__ scale1,
-                            DeviceError* err, int dbg) {
+                            DeviceError* err, int dbg, int splitk, float* __restrict__ ws) {
   extern __shared__ uint8_t smem_raw[];
   // kSwiGLU: 128 output columns per tile (gate rows and up rows of the same 128 features);
   // kPlain: 256 output columns per tile (two 128-row halves of W_down).
@@ -106,11 +169,9 @@ grouped_gemm_w8_tmem_kernel(const __grid_constant__ CUtensorMap tmap_x, const CU
   tc_fence_after();
   const uint32_t tmem_base = bars->tmem_base;
 
-  TileCursor cur;
-  cur.group = 0;
-  cur.base = 0;
-  if (num_groups > 0) cursor_load(cur, group_offsets);
-  TileCoord tc;
+  PieceIter it;
+  it.init(splitk != 0, num_kb, n_tiles, num_groups, BN_OUT, group_offsets);
+  TileCoord& tc = it.tc;
 
   if (warp == 0) {
     // ================= TMA producer =================
@@ -120,8 +181,7 @@ grouped_gemm_w8_tmem_kernel(const __grid_constant__ CUtensorMap tmap_x, const CU
       int last_group = -1;
       uint32_t armed = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && cursor_seek(cur, tile, n_tiles, num_groups, group_offsets, tc, BN_OUT);
-           tile += gridDim.x) {
+      while (ok && it.next()) {
         if (tc.group != last_group) {
           tmap_acquire(&tmap_w0[tc.group]);
           if (MODE == kSwiGLU) tmap_acquire(&tmap_w1[tc.group]);
@@ -130,7 +190,7 @@ grouped_gemm_w8_tmem_kernel(const __grid_constant__ CUtensorMap tmap_x, const CU
         const CUtensorMap* m0 = &tmap_w0[tc.group];
         const CUtensorMap* m1 = (MODE == kSwiGLU) ? &tmap_w1[tc.group] : m0;
         const int n1 = (MODE == kSwiGLU) ? tc.n0 : tc.n0 + WROWS;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = it.kb0; kb < it.kb0 + it.nkb; ++kb) {
           if (!mbar_wait(smem_u32(&bars->empty[stage]), phase ^ 1u, abort_flag)) {
             report_error(err, ATENIA_ERR_DEVICE_TIMEOUT, 600 + stage);
             *abort_flag = 1;
@@ -165,8 +225,7 @@ grouped_gemm_w8_tmem_kernel(const __grid_constant__ CUtensorMap tmap_x, const CU
       int stage = 0, tstage = 0;
       uint32_t phase = 0, tphase = 0, acc_phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && cursor_seek(cur, tile, n_tiles, num_groups, group_offsets, tc, BN_OUT);
-           tile += gridDim.x) {
+      while (ok && it.next()) {
         if (!mbar_wait(smem_u32(&bars->acc_empty), acc_phase ^ 1u, abort_flag)) {
           report_error(err, ATENIA_ERR_DEVICE_TIMEOUT, 700);
           *abort_flag = 1;
@@ -177,7 +236,7 @@ grouped_gemm_w8_tmem_kernel(const __grid_constant__ CUtensorMap tmap_x, const CU
         int rows = tc.row_end - tc.row0;
         if (rows > TN) rows = TN;
         const uint32_t idesc = idesc_for((rows + 15) & ~15);
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = it.kb0; kb < it.kb0 + it.nkb; ++kb) {
           if (!mbar_wait(smem_u32(&bars->full[stage]), phase, abort_flag) ||
               !mbar_wait(smem_u32(&bars->a_full[tstage]), tphase, abort_flag)) {
             report_error(err, ATENIA_ERR_DEVICE_TIMEOUT, 710 + stage);
@@ -191,7 +250,7 @@ grouped_gemm_w8_tmem_kernel(const __grid_constant__ CUtensorMap tmap_x, const CU
           const uint32_t a1 = a0 + A_TILE_COLS;
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
-            const uint32_t accum = (kb > 0 || k > 0) ? 1u : 0u;
+            const uint32_t accum = (kb > it.kb0 || k > 0) ? 1u : 0u;
             // 16 bf16 of K = 8 TMEM columns of the A tile, 32 bytes of the swizzled B row
             tc_mma_bf16_tmem_a(tmem_base, a0 + k * (UMMA_K / 2), db + 2 * k, idesc, accum);
             if (!(dbg & 1)) tc_mma_bf16_tmem_a(tmem_base + ACC1_COL, a1 + k * (UMMA_K / 2), db + 2 * k, idesc, accum);
@@ -235,9 +294,8 @@ grouped_gemm_w8_tmem_kernel(const __grid_constant__ CUtensorMap tmap_x, const CU
       }
       pend_stage = -1;
     };
-    for (int tile = blockIdx.x; ok && cursor_seek(cur, tile, n_tiles, num_groups, group_offsets, tc, BN_OUT);
-         tile += gridDim.x) {
-      for (int kb = 0; kb < num_kb; ++kb) {
+    while (ok && it.next()) {
+      for (int kb = it.kb0; kb < it.kb0 + it.nkb; ++kb) {
         if (!mbar_wait(smem_u32(&bars->full[stage]), phase, abort_flag)) {
           if (lane == 0) report_error(err, ATENIA_ERR_DEVICE_TIMEOUT, 800 + warp);
           *abort_flag = 1;
@@ -296,8 +354,7 @@ grouped_gemm_w8_tmem_kernel(const __grid_constant__ CUtensorMap tmap_x, const CU
     const int f = quarter * 32 + lane;
     const int half = (warp - 12) >> 2;  // which of the two warps of this lane quarter
     uint32_t acc_phase = 0;
-    for (int tile = blockIdx.x; cursor_seek(cur, tile, n_tiles, num_groups, group_offsets, tc, BN_OUT);
-         tile += gridDim.x) {
+    while (it.next()) {
       if (!mbar_wait(smem_u32(&bars->acc_full), acc_phase, abort_flag)) {
         if (lane == 0) report_error(err, ATENIA_ERR_DEVICE_TIMEOUT, 900);
         *abort_flag = 1;
@@ -309,7 +366,24 @@ grouped_gemm_w8_tmem_kernel(const __grid_constant__ CUtensorMap tmap_x, const CU
       if (rows > TN) rows = TN;
       const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16);
       const float* sc0 = scale0[tc.group];
-      if (MODE == kSwiGLU) {
+      if (it.slot >= 0) {
+        // partial piece: raw accumulators to this CTA's workspace slot, [accumulator][token][feature]
+        float* slot = ws + ((size_t)blockIdx.x * 2 + it.slot) * SLOT_FLOATS;
+#pragma unroll 1
+        for (int c = half * 16; c < rows; c += 32) {
+          uint32_t a[16], b[16];
+          tc_ld16(taddr + c, a);
+          tc_ld16(taddr + ACC1_COL + c, b);
+          tc_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            if (c + j < rows) {
+              slot[(size_t)(c + j) * WROWS + f] = __uint_as_float(a[j]);
+              slot[(size_t)(TN + c + j) * WROWS + f] = __uint_as_float(b[j]);
+            }
+          }
+        }
+      } else if (MODE == kSwiGLU) {
         const int n = tc.n0 + f;
         const bool n_ok = n < N;
         const float sg = n_ok ? sc0[n] : 0.f;
@@ -367,6 +441,69 @@ grouped_gemm_w8_tmem_kernel(const __grid_constant__ CUtensorMap tmap_x, const CU
   }
 }
 
+// Adds the partial pieces of every tile that stream-K cut across CTAs, in CTA order, and applies the
+// same scale / activation / store as the main kernel's epilogue.  One block per tile, one thread per
+// weight row (feature).
+template <int MODE>
+__global__ void __launch_bounds__(WROWS) w8_splitk_reduce_kernel(const int32_t* __restrict__ group_offsets,
+                                                                  int num_groups, int N, int K,
+                                                                  __nv_bfloat16* __restrict__ out,
+                                                                  const float* const* __restrict__ scale0,
+                                                                  const float* const* __restrict__ scale1,
+                                                                  const float* __restrict__ ws, int num_ctas) {
+  constexpr int BN_OUT = (MODE == kSwiGLU) ? WROWS : 2 * WROWS;
+  const int num_kb = (K + BK - 1) / BK;
+  const int n_tiles = (N + BN_OUT - 1) / BN_OUT;
+  long long total_tiles = 0;
+  for (int gi = 0; gi < num_groups; ++gi)
+    total_tiles += (long long)((group_offsets[gi + 1] - group_offsets[gi] + BM - 1) / BM) * n_tiles;
+  const long long t = blockIdx.x;
+  if (t >= total_tiles) return;
+  const long long total = total_tiles * num_kb;
+  const long long span = (total + num_ctas - 1) / num_ctas;
+  const int c0 = (int)((t * num_kb) / span), c1 = (int)(((t + 1) * num_kb - 1) / span);
+  if (c0 == c1) return;  // the tile was computed whole by one CTA
+  TileCursor cur;
+  cur.group = 0;
+  cur.base = 0;
+  cursor_load(cur, group_offsets);
+  TileCoord tc;
+  if (!cursor_seek(cur, (int)t, n_tiles, num_groups, group_offsets, tc, BN_OUT)) return;
+  const int f = threadIdx.x;
+  int rows = tc.row_end - tc.row0;
+  if (rows > TN) rows = TN;
+  const float* sc0 = scale0[tc.group];
+  const int n_lo = tc.n0 + f, n_hi = tc.n0 + WROWS + f;
+  float s_a, s_b;
+  bool ok_a, ok_b;
+  if (MODE == kSwiGLU) {
+    ok_a = ok_b = n_lo < N;
+    s_a = ok_a ? sc0[n_lo] : 0.f;
+    s_b = ok_a ? scale1[tc.group][n_lo] : 0.f;
+  } else {
+    ok_a = n_lo < N;
+    ok_b = n_hi < N;
+    s_a = ok_a ? sc0[n_lo] : 0.f;
+    s_b = ok_b ? sc0[n_hi] : 0.f;
+  }
+  for (int tok = 0; tok < rows; ++tok) {
+    float a = 0.f, b = 0.f;
+    for (int c = c0; c <= c1; ++c) {
+      const int slot = (t == ((long long)c * span) / num_kb) ? 0 : 1;
+      const float* p = ws + ((size_t)c * 2 + slot) * SLOT_FLOATS;
+      a += p[(size_t)tok * WROWS + f];
+      b += p[(size_t)(TN + tok) * WROWS + f];
+    }
+    __nv_bfloat16* orow = out + (size_t)(tc.row0 + tok) * N;
+    if (MODE == kSwiGLU) {
+      if (ok_a) orow[n_lo] = __float2bfloat16(silu_mul(a * s_a, b * s_b));
+    } else {
+      if (ok_a) orow[n_lo] = __float2bfloat16(a * s_a);
+      if (ok_b) orow[n_hi] = __float2bfloat16(b * s_b);
+    }
+  }
+}
+
 template <int MODE>
 int launch_w8_one(const GroupedGemmArgs& a, int num_sms, cudaStream_t s) {
   static bool attr_set = false;
@@ -378,9 +515,23 @@ int launch_w8_one(const GroupedGemmArgs& a, int num_sms, cudaStream_t s) {
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES_W8));
     attr_set = true;
   }
+  // stream-K only where groups fit one token tile (decode: one workspace slot holds 128 tokens) and
+  // the tiles that can exist (groups that can have a row x column tiles) are too few to balance SMs
+  constexpr int BN_OUT_H = (MODE == kSwiGLU) ? WROWS : 2 * WROWS;
+  const int active_groups = a.max_rows < a.num_groups ? a.max_rows : a.num_groups;
+  const int tile_bound = active_groups * ((a.N + BN_OUT_H - 1) / BN_OUT_H);
+  const bool splitk = a.splitk_ws != nullptr && a.max_rows <= TN && tile_bound < 4 * num_sms;
   grouped_gemm_w8_tmem_kernel<MODE><<<dim3(num_sms), dim3(NUM_THREADS_W8), SMEM_BYTES_W8, s>>>(
       a.tmap_a, a.tmap_b0, MODE == kSwiGLU ? a.tmap_b1 : a.tmap_b0, a.group_offsets, a.num_groups, a.N, a.K, a.out,
-      a.scale0, a.scale1, a.err, dbg);
+      a.scale0, a.scale1, a.err, dbg, splitk ? 1 : 0, a.splitk_ws);
+  int rc = (int)cudaGetLastError();
+  if (rc || !splitk) return rc;
+  constexpr int BN_OUT = (MODE == kSwiGLU) ? WROWS : 2 * WROWS;
+  const int n_tiles = (a.N + BN_OUT - 1) / BN_OUT;
+  const int max_tiles = a.num_groups * n_tiles;  // every group has at most one token tile here
+  w8_splitk_reduce_kernel<MODE><<<dim3(max_tiles), dim3(WROWS), 0, s>>>(a.group_offsets, a.num_groups, a.N, a.K, a.out,
+                                                                         a.scale0, a.scale1, a.splitk_ws, num_sms);
+  count_launch();
   return (int)cudaGetLastError();
 }
 
