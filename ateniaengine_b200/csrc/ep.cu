@@ -13,6 +13,9 @@
 // same rows, experts the same experts, and the combine order is unchanged.
 #include <nccl.h>
 
+#include <chrono>
+#include <cstdlib>
+#include <thread>
 #include <vector>
 
 #include "layer.cuh"
@@ -44,6 +47,34 @@ __global__ void group_offsets_kernel(const int32_t* __restrict__ counts_all, int
     if (r__ != ncclSuccess) return ATENIA_ERR_NCCL;    \
   } while (0)
 
+// Wait for `s` with a deadline instead of blocking: a peer that died or never joined must not hang
+// this rank for ever.  Polls the stream and the communicator's asynchronous error state; on an
+// error or when the deadline (ATENIA_MOE_EP_TIMEOUT_S, default 60 s) passes the communicator is
+// aborted, which also ends NCCL kernels still waiting on the device, and ATENIA_ERR_NCCL is returned.
+int bounded_stream_wait(AteniaMoeLayer* L, cudaStream_t s) {
+  static const double limit_s = [] {
+    const char* e = std::getenv("ATENIA_MOE_EP_TIMEOUT_S");
+    double v = e ? std::atof(e) : 60.0;
+    return v > 0.0 ? v : 60.0;
+  }();
+  ncclComm_t comm = reinterpret_cast<ncclComm_t>(L->comm);
+  const auto t0 = std::chrono::steady_clock::now();
+  for (;;) {
+    cudaError_t q = cudaStreamQuery(s);
+    if (q == cudaSuccess) return ATENIA_OK;
+    if (q != cudaErrorNotReady) return (int)q;
+    ncclResult_t async = ncclSuccess;
+    const bool bad = ncclCommGetAsyncError(comm, &async) != ncclSuccess || (async != ncclSuccess && async != ncclInProgress);
+    const double waited = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+    if (bad || waited > limit_s) {
+      ncclCommAbort(comm);
+      L->comm = nullptr;
+      return ATENIA_ERR_NCCL;
+    }
+    if (waited > 0.002) std::this_thread::sleep_for(std::chrono::microseconds(50));
+  }
+}
+
 int exchange(ncclComm_t comm, int rank, int world, const __nv_bfloat16* send, const std::vector<int64_t>& s_off,
              const std::vector<int64_t>& s_cnt, __nv_bfloat16* recv, const std::vector<int64_t>& r_off,
              const std::vector<int64_t>& r_cnt, int d, cudaStream_t s) {
@@ -74,7 +105,10 @@ int ep_forward_exchange(AteniaMoeLayer* L, int T, cudaStream_t s) {
                                   cudaMemcpyDeviceToHost, s));
   group_offsets_kernel<<<1, 32, 0, s>>>(L->d_counts_all, G, E, L->e_begin, El, L->d_group_offsets);
   count_launch();
-  ATENIA_CUDA_TRY(cudaStreamSynchronize(s));
+  {
+    int wrc = bounded_stream_wait(L, s);
+    if (wrc) return wrc;
+  }
   std::vector<int64_t> s_off(G), s_cnt(G), r_off(G), r_cnt(G);
   int64_t ro = 0;
   int prc = atenia_moe_ep_plan(L->h_counts_all, G, E, rank, s_off.data(), s_cnt.data(), r_off.data(),

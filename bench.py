@@ -211,6 +211,18 @@ def run_stack_bench(args):
     return 0
 
 
+def arm_watchdog(seconds, what):
+    """A rank that waits for a peer that died would wait for ever: end the process instead."""
+    def fire():
+        sys.stderr.write(f"bench.py: {what} exceeded {seconds:.0f} s, giving up\n")
+        sys.stderr.flush()
+        os._exit(3)
+    t = threading.Timer(seconds, fire)
+    t.daemon = True
+    t.start()
+    return t
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -223,6 +235,7 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--layers", type=int, default=32, help="layers of the mixtral_int8_stack workload")
     args = ap.parse_args()
+    arm_watchdog(float(os.environ.get("ATENIA_BENCH_WATCHDOG_S", "300")), "the whole run")
     if args.workload == "mixtral_int8_stack":
         if int(os.environ.get("RANK", "0")) != 0:
             return 0

@@ -16,6 +16,11 @@ import torch.distributed as dist
 
 
 def main():
+    import threading
+    # a rank whose peer died must not wait for ever
+    wd = threading.Timer(200.0, lambda: os._exit(4))
+    wd.daemon = True
+    wd.start()
     from ateniaengine_b200 import _lib, synth
 
     name = sys.argv[1]
@@ -62,7 +67,7 @@ def main():
         print(f"EP{world} {name} tokens={sizes}: equal={ok} max_abs={float((ref - got).abs().max()):.3e}", flush=True)
     dist.barrier()
     dist.destroy_process_group()
-    return 0 if ok else 1
+    os._exit(0 if ok else 1)
 
 
 if __name__ == "__main__":

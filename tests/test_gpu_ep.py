@@ -15,11 +15,12 @@ def test_expert_parallel_equals_single_gpu(name):
     n = torch.cuda.device_count() if torch.cuda.is_available() else 0
     if n < 2:
         pytest.skip("needs at least 2 GPUs")
-    world = 4 if n >= 4 else 2
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    # two ranks by default; ATENIA_EP_TEST_WORLD=4 (or 8) widens the group on a box that has the GPUs
+    world = min(n, int(os.environ.get("ATENIA_EP_TEST_WORLD", "2")))
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", ATENIA_MOE_EP_TIMEOUT_S="30")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
-           "--master-addr", "127.0.0.1", "--master-port", "29611", os.path.join(ROOT, "tests", "ep_worker.py"),
+           "--master-addr", "127.0.0.1", "--master-port", str(29611 + (0 if name == "mixtral" else 7)), os.path.join(ROOT, "tests", "ep_worker.py"),
            name, "301"]
-    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=240, env=env)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     assert "equal=True" in r.stdout
