@@ -235,7 +235,8 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--layers", type=int, default=32, help="layers of the mixtral_int8_stack workload")
     args = ap.parse_args()
-    arm_watchdog(float(os.environ.get("ATENIA_BENCH_WATCHDOG_S", "300")), "the whole run")
+    arm_watchdog(float(os.environ.get("ATENIA_BENCH_WATCHDOG_S", "600" if args.impl == "reference" else "300")),
+                 "the whole run")
     if args.workload == "mixtral_int8_stack":
         if int(os.environ.get("RANK", "0")) != 0:
             return 0
@@ -285,7 +286,9 @@ def main():
         t = time.perf_counter()
         ol.forward(x[:n0])
         rate0 = n0 / (time.perf_counter() - t)
-        n = int(min(x.shape[0], max(n0, rate0 * 2.0)))
+        # about 2 s per step, less when many steps are asked for: the whole run stays near two minutes
+        per_step_s = min(2.0, 120.0 / (args.steps + 1))
+        n = int(min(x.shape[0], max(1, rate0 * per_step_s)))
         ol.forward(x[:n])
         t = time.perf_counter()
         for _ in range(args.steps):
