@@ -21,8 +21,6 @@
 //
 // The accumulator is single-buffered (TMEM is full); the TMA ring and the widening run ahead into the
 // next tile while the epilogue drains.  All waits are bounded as in grouped_gemm.cu.
-#include <cstdlib>
-
 #include "tc_common.cuh"
 
 namespace atenia {
@@ -128,7 +126,7 @@ grouped_gemm_w8_tmem_kernel(const __grid_constant__ CUtensorMap tmap_x, const CU
                             const CUtensorMap* __restrict__ tmap_w1, const int32_t* __restrict__ group_offsets,
                             int num_groups, int N, int K, __nv_bfloat16* __restrict__ out,
                             const float* const* __restrict__ scale0, const float* const* __restrict__ scale1,
-                            DeviceError* err, int dbg, int splitk, float* __restrict__ ws) {
+                            DeviceError* err, int splitk, float* __restrict__ ws) {
   extern __shared__ uint8_t smem_raw[];
   // kSwiGLU: 128 output columns per tile (gate rows and up rows of the same 128 features);
   // kPlain: 256 output columns per tile (two 128-row halves of W_down).
@@ -253,7 +251,7 @@ grouped_gemm_w8_tmem_kernel(const __grid_constant__ CUtensorMap tmap_x, const CU
             const uint32_t accum = (kb > it.kb0 || k > 0) ? 1u : 0u;
             // 16 bf16 of K = 8 TMEM columns of the A tile, 32 bytes of the swizzled B row
             tc_mma_bf16_tmem_a(tmem_base, a0 + k * (UMMA_K / 2), db + 2 * k, idesc, accum);
-            if (!(dbg & 1)) tc_mma_bf16_tmem_a(tmem_base + ACC1_COL, a1 + k * (UMMA_K / 2), db + 2 * k, idesc, accum);
+            tc_mma_bf16_tmem_a(tmem_base + ACC1_COL, a1 + k * (UMMA_K / 2), db + 2 * k, idesc, accum);
           }
           tc_commit(smem_u32(&bars->empty[stage]));     // token tile of this stage consumed
           tc_commit(smem_u32(&bars->a_empty[tstage]));  // widened tiles of this TMEM stage consumed
@@ -308,13 +306,6 @@ grouped_gemm_w8_tmem_kernel(const __grid_constant__ CUtensorMap tmap_x, const CU
 #pragma unroll
         for (int c = 0; c < 4; ++c) p[c] = *reinterpret_cast<const uint4*>(q + ((c ^ sw) << 4));
         uint32_t v[32];
-        if (dbg & 2) {
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            v[8 * c + 0] = p[c].x; v[8 * c + 1] = p[c].y; v[8 * c + 2] = p[c].z; v[8 * c + 3] = p[c].w;
-            v[8 * c + 4] = p[c].x; v[8 * c + 5] = p[c].y; v[8 * c + 6] = p[c].z; v[8 * c + 7] = p[c].w;
-          }
-        } else
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           widen4(p[c].x, v[8 * c + 0], v[8 * c + 1]);
@@ -395,7 +386,7 @@ grouped_gemm_w8_tmem_kernel(const __grid_constant__ CUtensorMap tmap_x, const CU
           tc_ld16(taddr + c, g);
           tc_ld16(taddr + ACC1_COL + c, u);
           tc_ld_wait();
-          if (n_ok && !(dbg & 4)) {
+          if (n_ok) {
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               if (c + j < rows) {
@@ -507,10 +498,7 @@ __global__ void __launch_bounds__(WROWS) w8_splitk_reduce_kernel(const int32_t* 
 template <int MODE>
 int launch_w8_one(const GroupedGemmArgs& a, int num_sms, cudaStream_t s) {
   static bool attr_set = false;
-  static int dbg = 0;
   if (!attr_set) {
-    const char* e = getenv("ATENIA_MOE_W8_DBG");
-    dbg = e ? atoi(e) : 0;
     ATENIA_CUDA_TRY(cudaFuncSetAttribute(grouped_gemm_w8_tmem_kernel<MODE>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES_W8));
     attr_set = true;
@@ -523,7 +511,7 @@ int launch_w8_one(const GroupedGemmArgs& a, int num_sms, cudaStream_t s) {
   const bool splitk = a.splitk_ws != nullptr && a.max_rows <= TN && tile_bound < 4 * num_sms;
   grouped_gemm_w8_tmem_kernel<MODE><<<dim3(num_sms), dim3(NUM_THREADS_W8), SMEM_BYTES_W8, s>>>(
       a.tmap_a, a.tmap_b0, MODE == kSwiGLU ? a.tmap_b1 : a.tmap_b0, a.group_offsets, a.num_groups, a.N, a.K, a.out,
-      a.scale0, a.scale1, a.err, dbg, splitk ? 1 : 0, a.splitk_ws);
+      a.scale0, a.scale1, a.err, splitk ? 1 : 0, a.splitk_ws);
   int rc = (int)cudaGetLastError();
   if (rc || !splitk) return rc;
   constexpr int BN_OUT = (MODE == kSwiGLU) ? WROWS : 2 * WROWS;

@@ -78,7 +78,9 @@ def pack_layer0(fix_dir, name, out_dir):
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_golden.py /path/to/ateniaengine")
+    ref = sys.argv[1]
     fix_dir = os.path.join(ref, "fixtures", "moe")
     out_dir = os.path.dirname(os.path.abspath(__file__))
     for name in ("mixtral_layer0", "qwen15_moe_layer0", "qwen2_moe_layer0", "qwen3_moe_layer0",
