@@ -444,9 +444,11 @@ int atenia_moe_forward_selected(AteniaMoeLayer* L, const void* x, int x_dtype, i
 
 static int forward_impl(AteniaMoeLayer* L, const void* x, int x_dtype, int T, void* out, int out_dtype,
                         const AteniaMoeAux* aux, void* stream, const int32_t* sel_idx, const float* sel_w) {
-  if (!L || !x || !out) return ATENIA_ERR_NULL;
+  if (!L) return ATENIA_ERR_NULL;
   if (!L->weights_set) return ATENIA_ERR_STATE;
   if (T < 0) return ATENIA_ERR_SHAPE;
+  if (T == 0 && L->cfg.ep_world == 1) return ATENIA_OK;  // an empty batch has no buffers to check
+  if (!x || !out) return ATENIA_ERR_NULL;
   if (T > L->cfg.max_tokens) return ATENIA_ERR_CAPACITY;
   if ((x_dtype != ATENIA_IO_BF16 && x_dtype != ATENIA_IO_F32) ||
       (out_dtype != ATENIA_IO_BF16 && out_dtype != ATENIA_IO_F32))

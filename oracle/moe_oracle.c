@@ -400,6 +400,106 @@ ORACLE_API int oracle_combine_selected(const int32_t* indices, const float* weig
   return 0;
 }
 
+/* DeepSeek-V3 routing for one token: src/moe/v3_router.rs:206-309.
+ * scores = sigmoid(logits) in f64; choice = scores + bias; group score = sum of the two largest
+ * choices of a group; the topk_group best groups stay eligible (ties: lower group); top_k experts by
+ * choice among them (ties: lower index; -inf only if nothing else is left); combine weights are the
+ * ORIGINAL scores, divided by (their sum + 1e-20) when norm_topk_prob, times routed_scaling_factor.
+ * Outputs: idx_out ascending, w_out f32, dense_out[n] (may be NULL).  Returns 0 or a negative code:
+ * -1 zero parameter, -2 n % n_group, -3 group < 2 experts, -4 topk_group > n_group,
+ * -5 top_k > selectable, -6 non-finite input. */
+static void v3_top_k(const double* score, int n, int k, int* out) {
+  uint8_t* used = (uint8_t*)calloc((size_t)n, 1);
+  for (int s = 0; s < k; ++s) {
+    int best = -1;
+    for (int i = 0; i < n; ++i) {
+      if (used[i]) continue;
+      if (best < 0 || score[i] > score[best]) best = i; /* strict >: ties keep the lower index */
+    }
+    used[best] = 1;
+    out[s] = best;
+  }
+  free(used);
+}
+
+ORACLE_API int oracle_v3_route(const float* logits, const float* bias, int n, int top_k, int n_group,
+                               int topk_group, double scaling, int norm_topk_prob, int32_t* idx_out,
+                               float* w_out, float* dense_out) {
+  if (top_k <= 0 || n_group <= 0 || topk_group <= 0) return -1;
+  if (n % n_group) return -2;
+  const int epg = n / n_group;
+  if (epg < 2) return -3;
+  if (topk_group > n_group) return -4;
+  if (top_k > topk_group * epg) return -5;
+  for (int i = 0; i < n; ++i)
+    if (!isfinite(logits[i]) || !isfinite(bias[i])) return -6;
+  double* scores = (double*)malloc(sizeof(double) * (size_t)n * 3);
+  double* choice = scores + n;
+  double* masked = choice + n;
+  for (int i = 0; i < n; ++i) {
+    scores[i] = 1.0 / (1.0 + exp(-(double)logits[i]));
+    choice[i] = scores[i] + (double)bias[i];
+  }
+  double* gscore = (double*)malloc(sizeof(double) * (size_t)n_group);
+  int* gsel = (int*)malloc(sizeof(int) * (size_t)(topk_group + top_k));
+  int* esel = gsel + topk_group;
+  for (int g = 0; g < n_group; ++g) {
+    double a = -INFINITY, b = -INFINITY; /* two largest, a >= b */
+    for (int j = 0; j < epg; ++j) {
+      double v = choice[g * epg + j];
+      if (v > a) {
+        b = a;
+        a = v;
+      } else if (v > b) {
+        b = v;
+      }
+    }
+    gscore[g] = a + b;
+  }
+  v3_top_k(gscore, n_group, topk_group, gsel);
+  for (int i = 0; i < n; ++i) masked[i] = -INFINITY;
+  for (int s = 0; s < topk_group; ++s)
+    for (int j = 0; j < epg; ++j) masked[gsel[s] * epg + j] = choice[gsel[s] * epg + j];
+  v3_top_k(masked, n, top_k, esel);
+  /* ascending indices */
+  for (int a = 1; a < top_k; ++a) {
+    int v = esel[a], b = a - 1;
+    while (b >= 0 && esel[b] > v) {
+      esel[b + 1] = esel[b];
+      --b;
+    }
+    esel[b + 1] = v;
+  }
+  double denom = 0.0;
+  for (int s = 0; s < top_k; ++s) denom += scores[esel[s]];
+  denom += 1e-20;
+  if (dense_out)
+    for (int i = 0; i < n; ++i) dense_out[i] = 0.0f;
+  for (int s = 0; s < top_k; ++s) {
+    double w = scores[esel[s]];
+    if (norm_topk_prob) w /= denom;
+    w *= scaling;
+    idx_out[s] = esel[s];
+    w_out[s] = (float)w;
+    if (dense_out) dense_out[esel[s]] = (float)w;
+  }
+  free(gsel);
+  free(gscore);
+  free(scores);
+  return 0;
+}
+
+/* One expert's forward for one token (src/moe/dense.rs:253-270), f32 weights, exported for tests
+ * that compose a block from routing weights themselves. */
+ORACLE_API void oracle_expert_forward_f32(const float* w_gate, const float* w_up, const float* w_down, int d,
+                                          int F, int accum, const float* x, float* y) {
+  OracleMat g = {w_gate, NULL}, u = {w_up, NULL}, dn = {w_down, NULL};
+  int cmax = d > F ? d : F;
+  float* buf = (float*)malloc(sizeof(float) * ((size_t)3 * F + (size_t)RB * cmax));
+  expert_forward(&g, &u, &dn, ORACLE_W_F32, accum, d, F, x, y, buf, buf + F, buf + 2 * F, buf + 3 * F);
+  free(buf);
+}
+
 ORACLE_API float oracle_mat_at(const OracleMat* m, int kind, size_t r, size_t cols, size_t c) {
   return mat_at(m, kind, r, cols, c);
 }

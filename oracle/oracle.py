@@ -227,3 +227,39 @@ def combine_selected(indices, weights, expert_outputs, d):
 
 def max_threads():
     return lib().oracle_max_threads()
+
+
+def v3_route(logits, bias, top_k, n_group, topk_group, scaling, norm_topk_prob):
+    """DeepSeek-V3 routing of one token.  Returns (rc, indices, weights, dense_weights)."""
+    logits = np.ascontiguousarray(logits, dtype=np.float32)
+    bias = np.ascontiguousarray(bias, dtype=np.float32)
+    n = logits.size
+    idx = np.zeros(max(top_k, 1), dtype=np.int32)
+    w = np.zeros(max(top_k, 1), dtype=np.float32)
+    dense = np.zeros(n, dtype=np.float32)
+    rc = lib().oracle_v3_route(_ptr(logits), _ptr(bias), C.c_int(n), C.c_int(top_k), C.c_int(n_group),
+                               C.c_int(topk_group), C.c_double(scaling), C.c_int(int(norm_topk_prob)),
+                               _ptr(idx), _ptr(w), _ptr(dense))
+    return rc, idx[:top_k], w[:top_k], dense
+
+
+def router_logits(w_router, x, bias=None):
+    w_router = np.ascontiguousarray(w_router, dtype=np.float32)
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    E, d = w_router.shape
+    out = np.empty(E, dtype=np.float32)
+    b = None if bias is None else np.ascontiguousarray(bias, dtype=np.float32)
+    lib().oracle_router_logits(_ptr(w_router), _ptr(b), C.c_int(E), C.c_int(d), _ptr(x), _ptr(out))
+    return out
+
+
+def expert_forward(w_gate, w_up, w_down, x, accum=ACC_F64):
+    w_gate = np.ascontiguousarray(w_gate, dtype=np.float32)
+    w_up = np.ascontiguousarray(w_up, dtype=np.float32)
+    w_down = np.ascontiguousarray(w_down, dtype=np.float32)
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    F, d = w_gate.shape
+    y = np.empty(d, dtype=np.float32)
+    lib().oracle_expert_forward_f32(_ptr(w_gate), _ptr(w_up), _ptr(w_down), C.c_int(d), C.c_int(F),
+                                    C.c_int(accum), _ptr(x), _ptr(y))
+    return y

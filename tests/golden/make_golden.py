@@ -25,6 +25,8 @@ Fields of each .npz:
     hf_ref         HuggingFace transformers f64 output
     mlp_output     (deepseek_block) non-renormalised top-k, ungated shared
   top_k, norm_topk_prob                                             int
+v3_route_ref.npz: router [n,d], router_bias [n], gate/up/down per expert, shared_*, hidden [T,d],
+  selected_experts [T,k], dense_combine_weights [T,n], block_out [T,d] and the routing parameters.
 """
 import json
 import os
@@ -77,6 +79,33 @@ def pack_layer0(fix_dir, name, out_dir):
     print(name, {k: getattr(v, "shape", v) for k, v in rec.items()})
 
 
+def pack_v3_route(fix_dir, out_dir):
+    """fixtures/moe/v3_route_ref.*: DeepSeek-V3-like routing on a reduced block, HF transformers f64
+    reference (asserted by tests/moe_v3_route_scale_cert_test.rs)."""
+    meta = json.load(open(os.path.join(fix_dir, "v3_route_ref.json")))
+    st = load_st(os.path.join(fix_dir, "v3_route_ref.safetensors"))
+    n = meta["n_routed_experts"]
+    rec = {
+        "router": st["router.weight"].astype(np.float32), "router_bias": st["router.bias"].astype(np.float32),
+        "gate": np.stack([st[f"expert.{e}.w_gate"] for e in range(n)]).astype(np.float32),
+        "up": np.stack([st[f"expert.{e}.w_up"] for e in range(n)]).astype(np.float32),
+        "down": np.stack([st[f"expert.{e}.w_down"] for e in range(n)]).astype(np.float32),
+        "shared_gate_proj": st["shared.w_gate"].astype(np.float32),
+        "shared_up_proj": st["shared.w_up"].astype(np.float32),
+        "shared_down_proj": st["shared.w_down"].astype(np.float32),
+        "hidden": st["hidden"].astype(np.float32),
+        "selected_experts": np.asarray(meta["selected_experts"], dtype=np.int32),
+        "dense_combine_weights": np.asarray(meta["dense_combine_weights"], dtype=np.float64).reshape(meta["tokens"], n),
+        "block_out": np.asarray(meta["block_out"], dtype=np.float64).reshape(meta["tokens"], meta["hidden_size"]),
+        "top_k": np.int32(meta["top_k"]), "n_group": np.int32(meta["n_group"]),
+        "topk_group": np.int32(meta["topk_group"]),
+        "routed_scaling_factor": np.float64(meta["routed_scaling_factor"]),
+        "norm_topk_prob": np.int32(bool(meta["norm_topk_prob"])),
+    }
+    np.savez_compressed(os.path.join(out_dir, "v3_route_ref.npz"), **rec)
+    print("v3_route_ref", {k: getattr(v, "shape", v) for k, v in rec.items()})
+
+
 def main():
     if len(sys.argv) < 2:
         sys.exit("usage: make_golden.py /path/to/ateniaengine")
@@ -86,6 +115,7 @@ def main():
     for name in ("mixtral_layer0", "qwen15_moe_layer0", "qwen2_moe_layer0", "qwen3_moe_layer0",
                  "deepseek_block"):
         pack_layer0(fix_dir, name, out_dir)
+    pack_v3_route(fix_dir, out_dir)
 
 
 if __name__ == "__main__":

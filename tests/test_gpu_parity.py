@@ -249,6 +249,18 @@ def test_forward_with_caller_selection(dev):
     assert torch.isfinite(y1).all() and y1.abs().sum() > 0
 
 
+def test_empty_batch_and_capacity(dev):
+    from ateniaengine_b200._lib import AteniaError
+    synth = _synth()
+    shape = synth.small(synth.SHAPES["mixtral"], d_model=256, d_ff=256)
+    layer = synth.build_layer(shape, synth.make_weights(shape, 1, dev), max_tokens=8)
+    out = layer.forward(torch.empty((0, 256), dtype=torch.bfloat16, device=dev), sync=True)
+    assert out.shape == (0, 256)
+    with pytest.raises(AteniaError) as ei:
+        layer.forward(torch.zeros((9, 256), dtype=torch.bfloat16, device=dev))
+    assert ei.value.status == -3  # more tokens than max_tokens
+
+
 def test_token_order_does_not_change_rows(dev):
     """The block is position-wise: shuffling the tokens shuffles the outputs, bit for bit."""
     synth = _synth()

@@ -197,3 +197,57 @@ def test_batch_is_rowwise_and_thread_count_independent(golden_dir):
     np.testing.assert_array_equal(a, b)
     for t in range(9):
         np.testing.assert_array_equal(a[t], lay.forward(x[t:t + 1])[0])
+
+
+# ---- DeepSeek-V3 routing (src/moe/v3_router.rs), pinned by fixtures/moe/v3_route_ref.* -------------
+
+def test_v3_routing_matches_reference_golden(golden_dir):
+    """tests/moe_v3_route_scale_cert_test.rs: selected sets equal, dense combine weights and the block
+    output within 1e-3 of the HF f64 reference (measured here: far tighter)."""
+    g = _load(golden_dir, "v3_route_ref")
+    n = g["router"].shape[0]
+    args = (int(g["top_k"]), int(g["n_group"]), int(g["topk_group"]), float(g["routed_scaling_factor"]),
+            bool(g["norm_topk_prob"]))
+    for t in range(g["hidden"].shape[0]):
+        h = g["hidden"][t]
+        logits = orc.router_logits(g["router"], h)
+        rc, idx, w, dense = orc.v3_route(logits, g["router_bias"], *args)
+        assert rc == 0
+        assert idx.tolist() == g["selected_experts"][t].tolist()
+        assert np.max(np.abs(dense - g["dense_combine_weights"][t])) < 1e-6
+        out = np.zeros(h.shape[0], dtype=np.float64)
+        for s, e in enumerate(idx):
+            out += float(w[s]) * orc.expert_forward(g["gate"][e], g["up"][e], g["down"][e], h).astype(np.float64)
+        out += orc.expert_forward(g["shared_gate_proj"], g["shared_up_proj"], g["shared_down_proj"], h)
+        assert np.max(np.abs(out - g["block_out"][t])) < 1e-6
+        # deterministic
+        rc2, idx2, w2, _ = orc.v3_route(logits, g["router_bias"], *args)
+        assert idx2.tolist() == idx.tolist() and np.array_equal(w2, w)
+
+
+def test_v3_routing_rules():
+    z = np.zeros(8, dtype=np.float32)
+    # equal scores: groups 0 and 1 win the tie, then experts 0 and 1
+    rc, idx, w, dense = orc.v3_route(z, z, 2, 4, 2, 2.5, True)
+    assert rc == 0 and idx.tolist() == [0, 1]
+    np.testing.assert_allclose(w, [1.25, 1.25], rtol=1e-6)
+    # the bias steers the selection but not the weights
+    b = z.copy()
+    b[6] = 1.0
+    b[7] = 0.9
+    rc, idx, w, _ = orc.v3_route(z, b, 2, 4, 2, 1.0, False)
+    assert idx.tolist() == [6, 7]
+    np.testing.assert_allclose(w, [0.5, 0.5], rtol=1e-6)
+    # group limit: the single best expert of a weak group loses to a strong group
+    lg = np.array([4.0, -9.0, 1.0, 1.0, 0.9, 0.9, -9.0, -9.0], dtype=np.float32)
+    rc, idx, _, _ = orc.v3_route(lg, z, 2, 4, 1, 1.0, True)
+    assert idx.tolist() == [2, 3]
+    # invalid configurations
+    assert orc.v3_route(z, z, 0, 4, 2, 1.0, True)[0] == -1
+    assert orc.v3_route(z, z, 2, 3, 2, 1.0, True)[0] == -2
+    assert orc.v3_route(z, z, 2, 8, 2, 1.0, True)[0] == -3
+    assert orc.v3_route(z, z, 2, 4, 5, 1.0, True)[0] == -4
+    assert orc.v3_route(z, z, 5, 4, 2, 1.0, True)[0] == -5
+    bad = z.copy()
+    bad[3] = np.inf
+    assert orc.v3_route(bad, z, 2, 4, 2, 1.0, True)[0] == -6
