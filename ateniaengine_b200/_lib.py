@@ -54,7 +54,8 @@ EXPORTS = [
     "atenia_moe_ep_init", "atenia_moe_status_str", "atenia_moe_counter", "atenia_moe_enable_timing",
     "atenia_moe_last_gemm_ms", "atenia_moe_dispatch_noalloc", "atenia_moe_ep_plan", "atenia_moe_stack_create",
     "atenia_moe_stack_forward", "atenia_moe_stack_check", "atenia_moe_stack_destroy",
-    "atenia_moe_forward_selected",
+    "atenia_moe_forward_selected", "atenia_tier_detect_dtype", "atenia_tier_read_qint8", "atenia_tier_read_bf16",
+    "atenia_tier_read_f32",
 ]
 
 _lib = None
@@ -101,6 +102,11 @@ def lib():
         l.atenia_register_real_moe_layer.argtypes = [C.POINTER(HostMoeLayer)]
         l.atenia_execute_real_moe_layer.argtypes = [C.c_int64, C.c_void_p, C.c_size_t, C.c_void_p]
         l.atenia_moe_ep_get_unique_id.argtypes = [C.c_void_p]
+        for fn in (l.atenia_tier_detect_dtype,):
+            fn.argtypes = [C.c_char_p, C.c_int64, C.c_int64]
+        l.atenia_tier_read_qint8.argtypes = [C.c_char_p, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p]
+        l.atenia_tier_read_bf16.argtypes = [C.c_char_p, C.c_int64, C.c_int64, C.c_void_p]
+        l.atenia_tier_read_f32.argtypes = [C.c_char_p, C.c_int64, C.c_int64, C.c_void_p]
         l.atenia_moe_stack_create.argtypes = [C.POINTER(C.c_void_p), C.c_int, C.c_int, C.POINTER(C.c_void_p)]
         l.atenia_moe_stack_forward.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_int,
                                                C.c_void_p]

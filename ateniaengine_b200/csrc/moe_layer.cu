@@ -616,6 +616,8 @@ const char* atenia_moe_status_str(int status) {
     case ATENIA_ERR_ROUTING: return "routing weights non-finite or selected sum <= 0";
     case ATENIA_ERR_NCCL: return "an NCCL call failed";
     case ATENIA_ERR_DRIVER: return "tensor-map encode or driver entry point unavailable";
+    case ATENIA_ERR_IO: return "a tier file is missing or could not be read";
+    case ATENIA_ERR_TIER_FORMAT: return "tier file length matches none of its encodings (or not the one asked for)";
     case ATENIA_ERR_SCRATCH_LIMIT:
       return "request exceeds the fixed scratch of atenia_moe_dispatch_noalloc (T*k <= 65536, E <= 128)";
     default: break;

@@ -54,6 +54,8 @@ extern "C" {
 #define ATENIA_ERR_ROUTING (-9)         /* non-finite routing weight or selected sum <= 0 (MoeSparseError) */
 #define ATENIA_ERR_NCCL (-10)           /* an NCCL call failed */
 #define ATENIA_ERR_DRIVER (-11)         /* tensor-map encode or driver entry point unavailable */
+#define ATENIA_ERR_IO (-13)             /* a tier file is missing or could not be read */
+#define ATENIA_ERR_TIER_FORMAT (-14)    /* a tier file's length matches none of its encodings (or not the one asked for) */
 #define ATENIA_ERR_SCRATCH_LIMIT (-12)  /* request larger than the fixed scratch of atenia_moe_dispatch_noalloc */
 
 /* ---- enums -------------------------------------------------------------------------------- */
@@ -182,6 +184,25 @@ ATENIA_API int atenia_moe_dispatch_noalloc(const int32_t* topk_idx, int T, int k
  * Bit-identical to quantize_per_row_i8 (src/tensor/disk_tier.rs:231-245). */
 ATENIA_API int atenia_quantize_per_row_i8(const float* w, int64_t rows, int64_t cols, int8_t* q,
                                           float* scales, void* stream);
+
+/* ---- persistent expert tier files (host only) -----------------------------------------------
+ * The reference persists each projection of each expert as one file `L{l}.e{i}.{gate,up,down}.bin`
+ * (`L{l}.shared.*`, `L{l}.router.bin`, `L{l}.shared_gate.bin`) and recognises the encoding by the
+ * byte length (src/moe/residency.rs:511-551; qint8 layout src/tensor/disk_tier.rs:168-224).  These
+ * readers return the bytes in the form the GPU path consumes, so a tier written by the reference
+ * loads without re-encoding.  All pointers are HOST memory; no CUDA call is made. */
+#define ATENIA_TIER_F32 0
+#define ATENIA_TIER_BF16 1
+#define ATENIA_TIER_QINT8 2
+/* The encoding of a [rows, cols] tensor file (ATENIA_TIER_*), ATENIA_ERR_IO if it cannot be opened,
+ * ATENIA_ERR_TIER_FORMAT if its length matches none. */
+ATENIA_API int atenia_tier_detect_dtype(const char* path, int64_t rows, int64_t cols);
+/* qint8: q [rows*cols] int8 and scales [rows] f32 exactly as stored. */
+ATENIA_API int atenia_tier_read_qint8(const char* path, int64_t rows, int64_t cols, int8_t* q, float* scales);
+/* bf16: the 16-bit words exactly as stored. */
+ATENIA_API int atenia_tier_read_bf16(const char* path, int64_t rows, int64_t cols, uint16_t* out);
+/* Any encoding materialised as f32 the way the reference does (bf16 bits << 16; (f32)q * scale). */
+ATENIA_API int atenia_tier_read_f32(const char* path, int64_t rows, int64_t cols, float* out);
 
 /* ---- operator registry (host-memory interface of the reference's graph op) ---------------- */
 
