@@ -348,9 +348,10 @@ def main():
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-        time.sleep(0.8)  # nvidia-smi needs a moment before its first reading
-        for _ in range(args.warmup):
-            layer.forward(x, out=out)
+    time.sleep(0.8)  # nvidia-smi needs a moment before its first reading
+    # every rank runs the same forwards: under expert parallelism each one is a set of collectives
+    for _ in range(args.warmup):
+        layer.forward(x, out=out)
     sync_all()
     t_load0 = time.perf_counter()
     launches0 = _lib.lib().atenia_moe_counter(1)
@@ -395,7 +396,12 @@ def main():
     rows = T * shape.top_k  # rows this rank's experts process under uniform sharding
     flops1 = 4.0 * rows * shape.d_model * shape.d_ff  # gate and up: 2 * 2 * rows * d * F
     achieved = flops1 / (gemm1_ms * 1e-3) / 1e12
-    roofline = {"bound": "tensor", "kernel": "grouped_gemm_tcgen05_kernel<kSwiGLU> (routed gate/up + SwiGLU)",
+    groups = (shape.num_experts // args.gpus) * (args.gpus if args.gpus > 1 else 1)
+    if shape.int8:
+        kname = "grouped_gemm_w8_tmem_kernel<kSwiGLU>" if rows < 256 * groups else "grouped_gemm_tcgen05_kernel<kSwiGLU, W8>"
+    else:
+        kname = "grouped_gemm_2cta_kernel<kSwiGLU>" if rows >= 512 * groups else "grouped_gemm_tcgen05_kernel<kSwiGLU>"
+    roofline = {"bound": "tensor", "kernel": kname + " (routed gate/up + SwiGLU)",
                 "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                 "frac": achieved / peaks["bf16_tflops"], "peak_source": f"{peak_src} (burst cuBLAS bf16)",
                 "frac_of_sustained_peak": achieved / peaks["bf16_tflops_sustained"],
