@@ -34,6 +34,17 @@ void count_launch(int n = 1);
 void count_tcgen05_launch();
 void count_bytes(int which, uint64_t n);
 
+// One-time kernel attributes are per device: `flags` is a per-kernel array indexed by device ordinal.
+// Returns true exactly once per (kernel, device); a benign double set under a race is harmless.
+constexpr int kMaxDevices = 64;
+inline bool first_use_on_current_device(bool (&flags)[kMaxDevices]) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return true;
+  if (flags[dev]) return false;
+  flags[dev] = true;
+  return true;
+}
+
 #define ATENIA_CUDA_TRY(expr)                \
   do {                                       \
     cudaError_t e__ = (expr);                \

@@ -421,11 +421,10 @@ template <int MODE, bool W8>
 static int launch_one(const GroupedGemmArgs& a, int num_sms, cudaStream_t s) {
   constexpr int kSmem = W8 ? W8_SMEM_BYTES : SMEM_BYTES;
   constexpr int kThreads = W8 ? W8_NUM_THREADS : NUM_THREADS;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static bool attr_set[kMaxDevices] = {};
+  if (first_use_on_current_device(attr_set)) {
     ATENIA_CUDA_TRY(cudaFuncSetAttribute(grouped_gemm_tcgen05_kernel<MODE, W8>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
-    attr_set = true;
   }
   grouped_gemm_tcgen05_kernel<MODE, W8><<<dim3(num_sms), dim3(kThreads), kSmem, s>>>(
       a.tmap_a, a.tmap_b0, MODE == kSwiGLU ? a.tmap_b1 : a.tmap_b0, a.group_offsets, a.num_groups, a.N, a.K, a.out,

@@ -610,11 +610,10 @@ grouped_gemm_2cta_w8_kernel(const __grid_constant__ CUtensorMap tmap_a, const CU
 
 template <int MODE>
 int launch_2cta_w8_one(const GroupedGemmArgs& a, int num_sms, cudaStream_t s) {
-  static bool attr_set = false;
-  if (!attr_set) {
+  static bool attr_set[kMaxDevices] = {};
+  if (first_use_on_current_device(attr_set)) {
     ATENIA_CUDA_TRY(cudaFuncSetAttribute(grouped_gemm_2cta_w8_kernel<MODE>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, W8P_SMEM));
-    attr_set = true;
   }
   const int grid = num_sms & ~1;
   grouped_gemm_2cta_w8_kernel<MODE><<<dim3(grid), dim3(W8P_THREADS), W8P_SMEM, s>>>(
@@ -625,11 +624,10 @@ int launch_2cta_w8_one(const GroupedGemmArgs& a, int num_sms, cudaStream_t s) {
 
 template <int MODE>
 int launch_2cta_one(const GroupedGemmArgs& a, int num_sms, cudaStream_t s) {
-  static bool attr_set = false;
-  if (!attr_set) {
+  static bool attr_set[kMaxDevices] = {};
+  if (first_use_on_current_device(attr_set)) {
     ATENIA_CUDA_TRY(cudaFuncSetAttribute(grouped_gemm_2cta_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          SMEM_BYTES2));
-    attr_set = true;
   }
   const int grid = num_sms & ~1;  // whole pairs
   grouped_gemm_2cta_kernel<MODE><<<dim3(grid), dim3(NUM_THREADS2), SMEM_BYTES2, s>>>(

@@ -497,11 +497,10 @@ __global__ void __launch_bounds__(WROWS) w8_splitk_reduce_kernel(const int32_t* 
 
 template <int MODE>
 int launch_w8_one(const GroupedGemmArgs& a, int num_sms, cudaStream_t s) {
-  static bool attr_set = false;
-  if (!attr_set) {
+  static bool attr_set[kMaxDevices] = {};
+  if (first_use_on_current_device(attr_set)) {
     ATENIA_CUDA_TRY(cudaFuncSetAttribute(grouped_gemm_w8_tmem_kernel<MODE>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES_W8));
-    attr_set = true;
   }
   // stream-K only where groups fit one token tile (decode: one workspace slot holds 128 tokens) and
   // the tiles that can exist (groups that can have a row x column tiles) are too few to balance SMs
