@@ -17,7 +17,7 @@
  *   quantize_per_row_i8                  src/tensor/disk_tier.rs:231-245  atenia_quantize_per_row_i8
  *   RealMoeStack::forward                src/moe/stack.rs:197-210  atenia_moe_stack_forward
  *
- * Conventions follow the reference's existing CUDA FFI (src/cuda/*.cu): plain `extern "C"` functions,
+ * Conventions follow the reference's existing CUDA FFI (the .cu files under src/cuda): plain `extern "C"` functions,
  * `int` status (0 = ok, > 0 = a cudaError_t value, < 0 = argument / shape / state errors listed
  * below), raw pointers and integer sizes, and the caller owns every buffer it passes.  Nothing here
  * falls back to the CPU: an error is returned as a status.
