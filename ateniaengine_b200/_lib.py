@@ -18,7 +18,8 @@ ERR_DIM_MISMATCH = -6
 class MoeConfig(C.Structure):
     _fields_ = [(n, C.c_int32) for n in (
         "num_experts", "experts_per_token", "d_model", "d_ff", "shared_d_ff", "renormalize",
-        "shared_gated", "weight_dtype", "max_tokens", "ep_rank", "ep_world")]
+        "shared_gated", "weight_dtype", "max_tokens", "ep_rank", "ep_world", "router_mode", "n_group",
+        "topk_group")] + [("routed_scaling_factor", C.c_float)]
 
 
 class MoeWeights(C.Structure):
@@ -28,7 +29,7 @@ class MoeWeights(C.Structure):
         ("s_gate", C.POINTER(C.c_void_p)), ("s_up", C.POINTER(C.c_void_p)), ("s_down", C.POINTER(C.c_void_p)),
         ("shared_w_gate", C.c_void_p), ("shared_w_up", C.c_void_p), ("shared_w_down", C.c_void_p),
         ("shared_s_gate", C.c_void_p), ("shared_s_up", C.c_void_p), ("shared_s_down", C.c_void_p),
-        ("shared_gate_vec", C.c_void_p),
+        ("shared_gate_vec", C.c_void_p), ("e_score_bias", C.c_void_p),
     ]
 
 
@@ -42,7 +43,7 @@ class HostMoeLayer(C.Structure):
         ("config", MoeConfig), ("w_router", C.c_void_p),
         ("w_gate", C.POINTER(C.c_void_p)), ("w_up", C.POINTER(C.c_void_p)), ("w_down", C.POINTER(C.c_void_p)),
         ("shared_w_gate", C.c_void_p), ("shared_w_up", C.c_void_p), ("shared_w_down", C.c_void_p),
-        ("shared_gate_vec", C.c_void_p),
+        ("shared_gate_vec", C.c_void_p), ("e_score_bias", C.c_void_p),
     ]
 
 

@@ -69,6 +69,11 @@ int launch_router(const RouterArgs& a, cudaStream_t s);
 int launch_route_from_logits(const float* logits, int T, int E, int k, int renormalize,
                              int32_t* topk_idx, float* topk_w, DeviceError* err, cudaStream_t s);
 
+// DeepSeek-V3 routing from logits (one thread per token runs v3_route_one of v3_route.cuh).
+int launch_v3_route(const float* logits, const float* e_score_bias, int T, int E, int k, int n_group, int topk_group,
+                    int norm_topk_prob, float scaling, int32_t* topk_idx, float* topk_w, DeviceError* err,
+                    cudaStream_t s);
+
 // ---- dispatch --------------------------------------------------------------------------------
 struct DispatchArgs {
   const int32_t* topk_idx;  // [n] flat (t*k + s) -> expert

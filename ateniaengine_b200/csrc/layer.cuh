@@ -28,6 +28,8 @@ struct AteniaMoeLayer {
   float* d_router = nullptr;    // [E, d]
   float* d_bias = nullptr;      // [E]
   float* d_gate_vec = nullptr;  // [d]
+  float* d_escore = nullptr;    // [E] V3 e_score_correction_bias (zeros if none given)
+  float* logits_ws = nullptr;   // [max_tokens, E] V3: logits between the router and the V3 selection
   bool has_bias = false, has_gate_vec = false, has_shared = false;
   CUtensorMap* d_tm_gate = nullptr;  // [n_groups]
   CUtensorMap* d_tm_up = nullptr;

@@ -5,6 +5,7 @@
 #include <new>
 
 #include "layer.cuh"
+#include "v3_route.cuh"
 
 namespace atenia {
 
@@ -34,6 +35,12 @@ int validate_config(const AteniaMoeConfig& c) {
   if (c.ep_world != 1 && c.ep_world != 2 && c.ep_world != 4 && c.ep_world != 8) return ATENIA_ERR_SHAPE;
   if (c.ep_rank < 0 || c.ep_rank >= c.ep_world || c.num_experts % c.ep_world) return ATENIA_ERR_SHAPE;
   if ((int64_t)c.max_tokens * c.experts_per_token * c.ep_world > (int64_t)1 << 30) return ATENIA_ERR_SHAPE;
+  if (c.router_mode != ATENIA_ROUTER_SOFTMAX && c.router_mode != ATENIA_ROUTER_V3) return ATENIA_ERR_SHAPE;
+  if (c.router_mode == ATENIA_ROUTER_V3) {
+    V3RouteParams p{c.num_experts, c.experts_per_token, c.n_group, c.topk_group, c.renormalize,
+                    (double)c.routed_scaling_factor};
+    if (v3_validate(p) != 0) return ATENIA_ERR_SHAPE;
+  }
   return ATENIA_OK;
 }
 
@@ -225,6 +232,10 @@ int atenia_moe_create(const AteniaMoeConfig* cfg, AteniaMoeLayer** out) {
   TRY_ALLOC(L->d_router, E * d);
   TRY_ALLOC(L->d_bias, E);
   TRY_ALLOC(L->d_gate_vec, d);
+  if (c.router_mode == ATENIA_ROUTER_V3) {
+    TRY_ALLOC(L->d_escore, E);
+    TRY_ALLOC(L->logits_ws, Tm * E);
+  }
   TRY_ALLOC(L->topk_idx, R);
   TRY_ALLOC(L->topk_w, R);
   TRY_ALLOC(L->gate_scale, Tm);
@@ -311,7 +322,7 @@ int atenia_moe_destroy(AteniaMoeLayer* L) {
                   L->x_bf16,     L->h_shared,    L->y_shared,    L->d_err,          L->d_tm_gate,
                   L->d_tm_up,    L->d_tm_down,   L->d_tm_shared, L->d_sc_gate,      L->d_sc_up,
                   L->d_sc_down,  L->d_sc_shared, L->d_p_gate,    L->d_p_up,         L->d_p_down,
-                  L->d_p_shared, L->d_tm_gate_sw, L->d_tm_up_sw, L->d_tm_down_sw, L->d_tm_shared_sw, L->splitk_ws, L->recv_x,      L->recv_h,      L->recv_y,         L->d_counts_all,
+                  L->d_p_shared, L->d_tm_gate_sw, L->d_tm_up_sw, L->d_tm_down_sw, L->d_tm_shared_sw, L->splitk_ws, L->d_escore, L->logits_ws, L->recv_x,      L->recv_h,      L->recv_y,         L->d_counts_all,
                   L->d_group_offsets};
   for (void* p : ptrs)
     if (p) cudaFree(p);
@@ -340,6 +351,12 @@ int atenia_moe_set_weights(AteniaMoeLayer* L, const AteniaMoeWeights* w) {
   L->has_bias = w->router_bias != nullptr;
   if (L->has_bias)
     ATENIA_CUDA_TRY(cudaMemcpy(L->d_bias, w->router_bias, E * sizeof(float), cudaMemcpyDeviceToDevice));
+  if (c.router_mode == ATENIA_ROUTER_V3) {
+    if (w->e_score_bias)
+      ATENIA_CUDA_TRY(cudaMemcpy(L->d_escore, w->e_score_bias, E * sizeof(float), cudaMemcpyDeviceToDevice));
+    else
+      ATENIA_CUDA_TRY(cudaMemset(L->d_escore, 0, E * sizeof(float)));
+  }
   L->has_gate_vec = w->shared_gate_vec != nullptr && c.shared_gated && L->has_shared;
   if (L->has_gate_vec)
     ATENIA_CUDA_TRY(cudaMemcpy(L->d_gate_vec, w->shared_gate_vec, d * sizeof(float), cudaMemcpyDeviceToDevice));
@@ -475,10 +492,17 @@ static int forward_impl(AteniaMoeLayer* L, const void* x, int x_dtype, int T, vo
   ra.topk_idx = L->topk_idx;
   ra.topk_w = L->topk_w;
   ra.gate_scale = L->has_gate_vec ? L->gate_scale : nullptr;
-  ra.logits = aux ? aux->logits : nullptr;
+  const bool v3 = c.router_mode == ATENIA_ROUTER_V3;
+  ra.logits = (aux && aux->logits) ? aux->logits : (v3 ? L->logits_ws : nullptr);
   ra.err = L->d_err;
   int rc = launch_router(ra, s);
   if (rc) return rc;
+  if (v3) {
+    // the router kernel supplied the f64-accumulated logits; the V3 rule replaces its selection
+    rc = launch_v3_route(ra.logits, L->d_escore, T, c.num_experts, k, c.n_group, c.topk_group, c.renormalize,
+                         c.routed_scaling_factor, L->topk_idx, L->topk_w, L->d_err, s);
+    if (rc) return rc;
+  }
   if (sel_idx && n > 0) {
     // the caller's selection replaces the router's (the router still ran: it owns the shared gate)
     ATENIA_CUDA_TRY(cudaMemcpyAsync(L->topk_idx, sel_idx, (size_t)n * 4, cudaMemcpyDeviceToDevice, s));
@@ -574,8 +598,11 @@ int atenia_moe_route_from_logits(AteniaMoeLayer* L, const float* logits, int T, 
   if (T == 0) return ATENIA_OK;
   const AteniaMoeConfig& c = L->cfg;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  int rc = launch_route_from_logits(logits, T, c.num_experts, c.experts_per_token, c.renormalize, topk_idx, topk_w,
-                                    L->d_err, s);
+  int rc = c.router_mode == ATENIA_ROUTER_V3
+               ? launch_v3_route(logits, L->d_escore, T, c.num_experts, c.experts_per_token, c.n_group, c.topk_group,
+                                 c.renormalize, c.routed_scaling_factor, topk_idx, topk_w, L->d_err, s)
+               : launch_route_from_logits(logits, T, c.num_experts, c.experts_per_token, c.renormalize, topk_idx,
+                                          topk_w, L->d_err, s);
   if (rc) return rc;
   if (perm || inv_perm || expert_offsets) {
     const int n = T * c.experts_per_token;

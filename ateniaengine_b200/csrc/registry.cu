@@ -98,10 +98,12 @@ int64_t atenia_register_real_moe_layer(const AteniaHostMoeLayer* h) {
   AteniaMoeWeights w{};
   float* d_router = nullptr;
   float* d_gate_vec = nullptr;
+  float* d_escore = nullptr;
   auto fail = [&](int code) -> int64_t {
     cudaFree(staging);
     if (d_router) cudaFree(d_router);
     if (d_gate_vec) cudaFree(d_gate_vec);
+    if (d_escore) cudaFree(d_escore);
     release(reg);
     return code;
   };
@@ -134,11 +136,18 @@ int64_t atenia_register_real_moe_layer(const AteniaHostMoeLayer* h) {
       w.shared_gate_vec = d_gate_vec;
     }
   }
+  if (h->e_score_bias && cfg.router_mode == ATENIA_ROUTER_V3) {
+    ce = cudaMalloc(reinterpret_cast<void**>(&d_escore), E * sizeof(float));
+    if (ce == cudaSuccess) ce = cudaMemcpy(d_escore, h->e_score_bias, E * sizeof(float), cudaMemcpyHostToDevice);
+    if (ce != cudaSuccess) return fail((int)ce);
+    w.e_score_bias = d_escore;
+  }
   rc = atenia_moe_set_weights(reg.layer, &w);
   if (rc) return fail(rc);
   cudaFree(staging);
   cudaFree(d_router);  // copied by set_weights
   if (d_gate_vec) cudaFree(d_gate_vec);
+  if (d_escore) cudaFree(d_escore);
   const size_t io = (size_t)cfg.max_tokens * d * sizeof(float);
   ce = cudaMalloc(&reg.d_in, io);
   if (ce == cudaSuccess) ce = cudaMalloc(&reg.d_out, io);

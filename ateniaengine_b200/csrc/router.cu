@@ -8,6 +8,7 @@
 // reference's router matvec (src/moe/dense.rs:97-115, :333), so they round to the same f32 except
 // when the f64 sums differ in their last bits across summation orders.
 #include "common.cuh"
+#include "v3_route.cuh"
 
 namespace atenia {
 namespace {
@@ -404,7 +405,41 @@ __global__ void route_from_logits_kernel(const float* __restrict__ logits, int T
   }
 }
 
+__global__ void __launch_bounds__(128) v3_route_kernel(const float* __restrict__ logits,
+                                                        const float* __restrict__ e_score_bias, int T,
+                                                        V3RouteParams p, int32_t* __restrict__ topk_idx,
+                                                        float* __restrict__ topk_w, DeviceError* err) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= T) return;
+  double scores[kV3MaxExperts], choice[kV3MaxExperts];
+  int32_t idx[kV3MaxTopK];
+  float w[kV3MaxTopK];
+  const int rc = v3_route_one(logits + (size_t)t * p.n, e_score_bias, p, idx, w, scores, choice);
+  if (rc) {
+    report_error(err, ATENIA_ERR_ROUTING, 1002);
+    for (int s = 0; s < p.top_k; ++s) {  // keep downstream kernels in bounds
+      idx[s] = s;
+      w[s] = 0.f;
+    }
+  }
+  for (int s = 0; s < p.top_k; ++s) {
+    topk_idx[(size_t)t * p.top_k + s] = idx[s];
+    topk_w[(size_t)t * p.top_k + s] = w[s];
+  }
+}
+
 }  // namespace
+
+int launch_v3_route(const float* logits, const float* e_score_bias, int T, int E, int k, int n_group, int topk_group,
+                    int norm_topk_prob, float scaling, int32_t* topk_idx, float* topk_w, DeviceError* err,
+                    cudaStream_t s) {
+  if (T <= 0) return ATENIA_OK;
+  V3RouteParams p{E, k, n_group, topk_group, norm_topk_prob, (double)scaling};
+  if (v3_validate(p) != 0) return ATENIA_ERR_SHAPE;
+  v3_route_kernel<<<(T + 127) / 128, 128, 0, s>>>(logits, e_score_bias, T, p, topk_idx, topk_w, err);
+  count_launch();
+  return (int)cudaGetLastError();
+}
 
 int launch_router(const RouterArgs& a, cudaStream_t s) {
   if (a.T <= 0) return ATENIA_OK;

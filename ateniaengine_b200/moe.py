@@ -83,11 +83,13 @@ class RealMoeLayer:
     (RealMoeLayer::resolve_convention); pass `renormalize` to override only the top-k rule (the
     DeepSeek runtime does this from norm_topk_prob).
     Under expert parallelism (`ep_world > 1`) the lists hold this rank's experts only.
+    `v3 = {"n_group", "topk_group", "scaling", "e_score_bias" (f32 [E] tensor or None)}` selects
+    DeepSeek-V3 routing (src/moe/v3_router.rs); `renormalize` then means norm_topk_prob.
     """
 
     def __init__(self, config, router, gate, up, down, shared=None, shared_gate=None, scales=None,
                  shared_scales=None, convention=None, renormalize=None, router_bias=None, max_tokens=4096,
-                 ep_rank=0, ep_world=1):
+                 ep_rank=0, ep_world=1, v3=None):
         config.validate()
         self.config = config
         dev = router.device
@@ -101,11 +103,16 @@ class RealMoeLayer:
             renormalize = convention == MoeExecutionConvention.Atenia
         gated = convention == MoeExecutionConvention.HuggingFaceQwen and shared_gate is not None
         int8 = gate[0].dtype == torch.int8
-        self._keep = [router, gate, up, down, shared, shared_gate, scales, shared_scales, router_bias]
+        self._keep = [router, gate, up, down, shared, shared_gate, scales, shared_scales, router_bias, v3]
         Fs = shared[0].shape[0] if shared is not None else 0
         cfg = _lib.MoeConfig(config.num_experts, config.experts_per_token, config.d_model, config.d_ff, Fs,
                              int(renormalize), int(gated), W_INT8_ROW if int8 else W_BF16, int(max_tokens),
                              ep_rank, ep_world)
+        if v3 is not None:
+            cfg.router_mode = 1
+            cfg.n_group = int(v3["n_group"])
+            cfg.topk_group = int(v3["topk_group"])
+            cfg.routed_scaling_factor = float(v3["scaling"])
         self.max_tokens = int(max_tokens)
         self.ep_world = ep_world
         self._h = C.c_void_p()
@@ -130,6 +137,8 @@ class RealMoeLayer:
                     w.shared_s_gate, w.shared_s_up, w.shared_s_down = [t.data_ptr() for t in shared_scales]
                 if shared_gate is not None:
                     w.shared_gate_vec = shared_gate.data_ptr()
+            if v3 is not None and v3.get("e_score_bias") is not None:
+                w.e_score_bias = v3["e_score_bias"].data_ptr()
             _lib.check(_lib.lib().atenia_moe_set_weights(self._h, C.byref(w)), "atenia_moe_set_weights")
 
     def close(self):

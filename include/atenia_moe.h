@@ -78,7 +78,18 @@ typedef struct AteniaMoeConfig {
   int32_t max_tokens;        /* capacity of the layer's device workspace, tokens per forward call */
   int32_t ep_rank;           /* expert-parallel rank of this process (0 when ep_world == 1) */
   int32_t ep_world;          /* expert-parallel world size: 1, 2, 4 or 8; must divide num_experts */
+  /* Router family.  ATENIA_ROUTER_SOFTMAX (0): softmax + top-k as above.  ATENIA_ROUTER_V3 (1): DeepSeek-V3
+   * routing (src/moe/v3_router.rs:206-309): sigmoid scores, e_score_correction_bias for selection only,
+   * groups ranked by the sum of their two best, top-k inside the topk_group best groups, weights =
+   * original scores, normalised when `renormalize` (norm_topk_prob), times routed_scaling_factor.
+   * Invalid combinations (V3RouterConfig::validate) are ATENIA_ERR_SHAPE at create. */
+  int32_t router_mode;
+  int32_t n_group;               /* V3 only */
+  int32_t topk_group;            /* V3 only */
+  float routed_scaling_factor;   /* V3 only */
 } AteniaMoeConfig;
+#define ATENIA_ROUTER_SOFTMAX 0
+#define ATENIA_ROUTER_V3 1
 
 /* Device pointers to the weights.  Expert matrices keep the reference's row-major layouts
  * (src/moe/dense.rs:203-216): gate, up [F, d]; down [d, F].  The per-expert pointer arrays are HOST
@@ -103,6 +114,7 @@ typedef struct AteniaMoeWeights {
   const float* shared_s_up;      /* device [Fs], INT8 only */
   const float* shared_s_down;    /* device [d], INT8 only */
   const float* shared_gate_vec;  /* device [d] f32 or NULL (shared_expert_gate, layer.rs:208-211) */
+  const float* e_score_bias;     /* device [E] f32 or NULL (= zeros): V3 e_score_correction_bias */
 } AteniaMoeWeights;
 
 /* Optional per-call outputs (device pointers, any may be NULL). */
@@ -219,6 +231,7 @@ typedef struct AteniaHostMoeLayer {
   const float* shared_w_up;     /* [Fs, d] or NULL */
   const float* shared_w_down;   /* [d, Fs] or NULL */
   const float* shared_gate_vec; /* [d] or NULL */
+  const float* e_score_bias;    /* [E] or NULL: V3 e_score_correction_bias */
 } AteniaHostMoeLayer;
 
 /* register_real_moe_layer: returns the new layer id (>= 0; ids are append-only and stable for the

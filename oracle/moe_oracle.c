@@ -47,6 +47,10 @@ typedef struct {
   int32_t shared_gated; /* 1 = shared output scaled by sigmoid(g.x) */
   int32_t weight_kind;  /* ORACLE_W_* for expert matrices (router is always f32) */
   int32_t accum;        /* ORACLE_ACC_* for the expert matvecs (router is always f64) */
+  int32_t router_mode;  /* 0 softmax + top-k, 1 DeepSeek-V3 routing (renormalize = norm_topk_prob) */
+  int32_t n_group;
+  int32_t topk_group;
+  double scaling;       /* routed_scaling_factor */
 } OracleConfig;
 
 typedef struct {
@@ -59,6 +63,7 @@ typedef struct {
   OracleMat shared_up_proj;   /* [Fs, d] */
   OracleMat shared_down_proj; /* [d, Fs] */
   const float* shared_gate;   /* [d] or NULL */
+  const float* e_score_bias;  /* [E] or NULL (zeros): V3 e_score_correction_bias */
 } OracleWeights;
 
 /* bf16 is the high half of an f32: decode is bits << 16 (src/tensor/tensor.rs:294-308). */
@@ -236,6 +241,10 @@ static float sigmoid_dot(const float* g, const float* x, int n) {
   return (float)(1.0 / (1.0 + exp(-acc)));
 }
 
+ORACLE_API int oracle_v3_route(const float* logits, const float* bias, int n, int top_k, int n_group,
+                               int topk_group, double scaling, int norm_topk_prob, int32_t* idx_out,
+                               float* w_out, float* dense_out);
+
 /* One token: src/moe/layer.rs:405-431 over src/moe/sparse.rs:218-238. */
 static int token_forward(const OracleConfig* c, const OracleWeights* w, const float* x, float* out,
                          int32_t* idx, float* tw, float* logits, float* buf) {
@@ -250,8 +259,15 @@ static int token_forward(const OracleConfig* c, const OracleWeights* w, const fl
   float* scratch = h + Fmax;        /* RB * cmax */
   (void)cmax;
   oracle_router_logits(w->w_router, w->router_bias, E, d, x, logits);
-  oracle_softmax(logits, E, probs);
-  int rc = oracle_top_k(probs, E, k, c->renormalize, idx, tw);
+  int rc;
+  if (c->router_mode == 1) {
+    /* V3: logits exclude the synthetic bias; selection bias is e_score_bias (zeros when absent) */
+    for (int e = 0; e < E; ++e) probs[e] = w->e_score_bias ? w->e_score_bias[e] : 0.0f;
+    rc = oracle_v3_route(logits, probs, E, k, c->n_group, c->topk_group, c->scaling, c->renormalize, idx, tw, NULL);
+  } else {
+    oracle_softmax(logits, E, probs);
+    rc = oracle_top_k(probs, E, k, c->renormalize, idx, tw);
+  }
   if (rc) return rc;
   for (int i = 0; i < d; ++i) out[i] = 0.0f;
   for (int s = 0; s < k; ++s) {

@@ -24,7 +24,7 @@ class _Mat(C.Structure):
 class _Config(C.Structure):
     _fields_ = [(n, C.c_int32) for n in (
         "num_experts", "top_k", "d_model", "d_ff", "shared_d_ff", "renormalize", "shared_gated",
-        "weight_kind", "accum")]
+        "weight_kind", "accum", "router_mode", "n_group", "topk_group")] + [("scaling", C.c_double)]
 
 
 class _Weights(C.Structure):
@@ -32,7 +32,7 @@ class _Weights(C.Structure):
         ("w_router", C.c_void_p), ("router_bias", C.c_void_p),
         ("gate", C.POINTER(_Mat)), ("up", C.POINTER(_Mat)), ("down", C.POINTER(_Mat)),
         ("shared_gate_proj", _Mat), ("shared_up_proj", _Mat), ("shared_down_proj", _Mat),
-        ("shared_gate", C.c_void_p),
+        ("shared_gate", C.c_void_p), ("e_score_bias", C.c_void_p),
     ]
 
 
@@ -85,7 +85,7 @@ class OracleLayer:
     """
 
     def __init__(self, router, gate, up, down, top_k, renormalize, shared=None, shared_gate_vec=None,
-                 shared_gated=None, router_bias=None, scales=None, shared_scales=None):
+                 shared_gated=None, router_bias=None, scales=None, shared_scales=None, v3=None):
         self.router = np.ascontiguousarray(router, dtype=np.float32)
         self.E, self.d = self.router.shape
         self.gate = [np.ascontiguousarray(g) for g in gate]
@@ -101,6 +101,11 @@ class OracleLayer:
             shared_gate_vec, dtype=np.float32).reshape(-1)
         self.shared_gated = (self.shared_gate_vec is not None) if shared_gated is None else bool(shared_gated)
         self.router_bias = None if router_bias is None else np.ascontiguousarray(router_bias, dtype=np.float32)
+        # v3: {"n_group", "topk_group", "scaling", "e_score_bias"} selects DeepSeek-V3 routing
+        self.v3 = v3
+        self.e_score_bias = None
+        if v3 is not None and v3.get("e_score_bias") is not None:
+            self.e_score_bias = np.ascontiguousarray(v3["e_score_bias"], dtype=np.float32)
         # scales: dict with "gate","up","down" lists of per-expert f32 [rows]
         self.scales = scales
         self.shared_scales = shared_scales
@@ -125,6 +130,11 @@ class OracleLayer:
         assert x.shape[1] == self.d
         cfg = _Config(self.E, self.top_k, self.d, self.F, self.Fs, int(self.renormalize),
                       int(self.shared_gated), self.kind, accum)
+        if self.v3 is not None:
+            cfg.router_mode = 1
+            cfg.n_group = int(self.v3["n_group"])
+            cfg.topk_group = int(self.v3["topk_group"])
+            cfg.scaling = float(self.v3["scaling"])
         sc = self.scales if self.kind == W_INT8_ROW else None
         g = self._mats(self.gate, sc["gate"] if sc else None)
         u = self._mats(self.up, sc["up"] if sc else None)
@@ -140,6 +150,7 @@ class OracleLayer:
                 mm = _Mat(a.ctypes.data, None if s is None else s.ctypes.data)
                 setattr(w, name, mm)
         w.shared_gate = None if self.shared_gate_vec is None else self.shared_gate_vec.ctypes.data
+        w.e_score_bias = None if self.e_score_bias is None else self.e_score_bias.ctypes.data
         out = np.empty((T, self.d), dtype=np.float32)
         idx = np.empty((T, self.top_k), dtype=np.int32)
         tw = np.empty((T, self.top_k), dtype=np.float32)

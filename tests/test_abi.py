@@ -56,6 +56,20 @@ def test_create_rejects_bad_arguments_without_a_device(lib):
         assert not h.value
 
 
+def test_create_rejects_invalid_v3_router_configs_without_a_device(lib):
+    """V3RouterConfig::validate (src/moe/v3_router.rs:150-183) at the ABI."""
+    from ateniaengine_b200 import _lib
+    h = C.c_void_p()
+    base = dict(num_experts=8, experts_per_token=2, d_model=64, d_ff=64, shared_d_ff=0, renormalize=1,
+                shared_gated=0, weight_dtype=0, max_tokens=8, ep_rank=0, ep_world=1, router_mode=1, n_group=4,
+                topk_group=2, routed_scaling_factor=2.5)
+    for bad in (dict(n_group=0), dict(topk_group=0), dict(n_group=3), dict(n_group=8), dict(topk_group=5),
+                dict(experts_per_token=5), dict(router_mode=2)):
+        cfg = _lib.MoeConfig(**{**base, **bad})
+        assert lib.atenia_moe_create(C.byref(cfg), C.byref(h)) == -2, bad
+        assert not h.value
+
+
 def test_registry_rejects_unknown_layer_and_null(lib):
     x = np.zeros(16, dtype=np.float32)
     assert lib.atenia_execute_real_moe_layer(12345, x.ctypes.data, 16, x.ctypes.data) == -5

@@ -251,3 +251,16 @@ def test_v3_routing_rules():
     bad = z.copy()
     bad[3] = np.inf
     assert orc.v3_route(bad, z, 2, 4, 2, 1.0, True)[0] == -6
+
+
+def test_v3_layer_forward_matches_reference_block(golden_dir):
+    """The oracle's layer forward in V3 mode (routing + experts + ungated shared) against block_out."""
+    g = _load(golden_dir, "v3_route_ref")
+    lay = orc.OracleLayer(g["router"], g["gate"], g["up"], g["down"], int(g["top_k"]), bool(g["norm_topk_prob"]),
+                          shared=[g["shared_gate_proj"], g["shared_up_proj"], g["shared_down_proj"]],
+                          shared_gated=False,
+                          v3={"n_group": int(g["n_group"]), "topk_group": int(g["topk_group"]),
+                              "scaling": float(g["routed_scaling_factor"]), "e_score_bias": g["router_bias"]})
+    out, aux = lay.forward(g["hidden"], want_aux=True)
+    np.testing.assert_array_equal(aux["topk_idx"], g["selected_experts"])
+    assert np.max(np.abs(out - g["block_out"])) < 1e-6
