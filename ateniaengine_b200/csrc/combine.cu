@@ -6,7 +6,7 @@
 // buffer in slot order (slots are ascending experts) and repeats that arithmetic, so the result does
 // not depend on scheduling: no atomics.
 //
-// Also here: the small elementwise kernels of the library (int8 per-row quantiser, widening passes).
+// Also here: the small elementwise kernels of the library (int8 per-row quantiser, f32 to bf16 conversion).
 #include "common.cuh"
 
 namespace atenia {
@@ -93,16 +93,6 @@ __global__ void __launch_bounds__(256) quantize_rows_kernel(const float* __restr
   }
 }
 
-__global__ void dequant_rows_kernel(const int8_t* __restrict__ q, const float* __restrict__ scales, int64_t rows,
-                                    int64_t cols, __nv_bfloat16* __restrict__ dst) {
-  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  int64_t n = rows * cols;
-  for (; i < n; i += (int64_t)gridDim.x * blockDim.x) {
-    float s = scales ? scales[i / cols] : 1.0f;
-    dst[i] = __float2bfloat16((float)q[i] * s);
-  }
-}
-
 __global__ void f32_to_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, int64_t n) {
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   for (; i < n; i += (int64_t)gridDim.x * blockDim.x) dst[i] = __float2bfloat16(src[i]);
@@ -113,16 +103,6 @@ __global__ void f32_to_bf16_kernel(const float* __restrict__ src, __nv_bfloat16*
 int launch_combine(const CombineArgs& a, cudaStream_t s) {
   if (a.T <= 0) return ATENIA_OK;
   combine_kernel<<<a.T, 256, 0, s>>>(a);
-  count_launch();
-  return (int)cudaGetLastError();
-}
-
-int launch_dequant_rows(const int8_t* q, const float* scales, int64_t rows, int64_t cols, __nv_bfloat16* dst,
-                        cudaStream_t s) {
-  int64_t n = rows * cols;
-  if (n <= 0) return ATENIA_OK;
-  int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
-  dequant_rows_kernel<<<blocks, 256, 0, s>>>(q, scales, rows, cols, dst);
   count_launch();
   return (int)cudaGetLastError();
 }

@@ -151,9 +151,6 @@ struct GroupedGemmCheckArgs {
 };
 int launch_grouped_gemm_check(const GroupedGemmCheckArgs& a, cudaStream_t s);
 
-// dst[r, c] = bf16((float)q[r, c] * scale[r])  (scale may be null: plain widening)
-int launch_dequant_rows(const int8_t* q, const float* scales, int64_t rows, int64_t cols,
-                        __nv_bfloat16* dst, cudaStream_t s);
 int launch_f32_to_bf16(const float* src, __nv_bfloat16* dst, int64_t n, cudaStream_t s);
 
 // Tensor-map encoding through the driver entry point (no link-time dependency on libcuda).
