@@ -112,23 +112,27 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def cpu_oracle_rate(shape, w, x_host, max_seconds, threads=0):
-    """tokens/s of the CPU oracle (f64 accumulation, all host threads) on a bounded token sample."""
+def cpu_oracle_rate(shape, w, x_host, max_seconds, threads=0, accum=None, ol=None):
+    """tokens/s of the CPU oracle (all host threads) on a bounded token sample; `accum` picks the
+    reference's accumulation mode (default f64, its certified path; ACC_F32 is its strict path)."""
     from oracle import oracle as orc
     from tests.helpers import oracle_layer
 
-    ol = oracle_layer(shape, w)
+    if ol is None:
+        ol = oracle_layer(shape, w)
+    if accum is None:
+        accum = orc.ACC_F64
     cores = orc.max_threads() if threads <= 0 else threads
     n0 = min(x_host.shape[0], max(cores, 4))
     t = time.perf_counter()
-    ol.forward(x_host[:n0], nthreads=threads)
+    ol.forward(x_host[:n0], accum=accum, nthreads=threads)
     dt = time.perf_counter() - t
     rate = n0 / dt
     n = int(min(x_host.shape[0], max(n0, rate * max_seconds)))
     n = max(cores, n // cores * cores) if n >= cores else n
     n = min(n, x_host.shape[0])
     t = time.perf_counter()
-    ol.forward(x_host[:n], nthreads=threads)
+    ol.forward(x_host[:n], accum=accum, nthreads=threads)
     dt = time.perf_counter() - t
     return n / dt, cores, n, ol
 
@@ -439,10 +443,15 @@ def main():
     cpu = None
     if args.gpus == 1 and not args.no_cpu_baseline:
         xs = x[: min(T, 512)].float().cpu().numpy()
-        rate, cores, n, _ = cpu_oracle_rate(shape, w, xs, args.cpu_seconds)
+        from oracle import oracle as orc
+        rate, cores, n, ol = cpu_oracle_rate(shape, w, xs, args.cpu_seconds * 0.6)
+        rate32, _, n32, _ = cpu_oracle_rate(shape, w, xs, args.cpu_seconds * 0.4, accum=orc.ACC_F32, ol=ol)
         cpu = {"value": rate, "unit": UNIT, "cores": cores, "kind": "port",
                "sample": f"{n} of the step's {T} tokens, CPU oracle (C restatement of the reference's per-token "
-                         f"f64 path), {cores} OpenMP threads"}
+                         f"f64 path), {cores} OpenMP threads",
+               "f32_accumulate": {"value": rate32, "unit": UNIT,
+                                  "sample": f"{n32} tokens, the same oracle accumulating in f32 (the reference's "
+                                            "strict mode)"}}
 
     value = T * args.gpus / (ms * 1e-3)
     line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
