@@ -12,4 +12,6 @@ from .moe import (  # noqa: F401
     register_real_moe_layer,
     register_resident_moe_layer,
     quantize_per_row_i8,
+    quantize_per_group_i8,
+    int8_to_bf16_per_group,
 )

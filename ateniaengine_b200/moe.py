@@ -5,6 +5,8 @@ Names and argument meaning follow the reference (paths relative to its project r
   RealMoeLayer.forward / forward_with / forward_auto          src/moe/layer.rs:374-431
   register_real_moe_layer / execute_real_moe_layer            src/moe/graph_op.rs:228, :327
   quantize_per_row_i8                                         src/tensor/disk_tier.rs:231-245
+  quantize_per_group_i8 (absmax_per_{channel,group}_symmetric) src/tensor/quantizer.rs:67-118, 176-246
+  int8_to_bf16_per_group                                      src/cuda/int8_to_bf16.cu:24-40, 99-117
 Every computation runs in the CUDA library; torch only owns device memory and streams.
 """
 import ctypes as C
@@ -70,6 +72,39 @@ def quantize_per_row_i8(w):
         _lib.check(_lib.lib().atenia_quantize_per_row_i8(_ptr(w), w.shape[0], w.shape[1], _ptr(q), _ptr(s),
                                                          C.c_void_p(st)), "quantize_per_row_i8")
     return q, s
+
+
+def quantize_per_group_i8(w, group_size=0):
+    """Dense W8A16 quantiser of a CUDA f32 [K, N] weight: one scale per (group of `group_size` rows,
+    column); group_size 0 = per output channel.  Mirrors absmax_per_channel_symmetric /
+    absmax_per_group_symmetric (src/tensor/quantizer.rs:67-118, :176-246) -> (q int8 [K, N],
+    scales f32 [groups, N])."""
+    assert w.is_cuda and w.dtype == torch.float32 and w.dim() == 2 and group_size >= 0
+    w = w.contiguous()
+    K, N = w.shape
+    g = K if group_size == 0 or group_size > K else group_size
+    groups = (K + g - 1) // g if K else 0
+    q = torch.empty((K, N), dtype=torch.int8, device=w.device)
+    s = torch.empty((groups, N), dtype=torch.float32, device=w.device)
+    with torch.cuda.device(w.device):
+        st = torch.cuda.current_stream().cuda_stream
+        _lib.check(_lib.lib().atenia_quantize_per_group_i8(_ptr(w), K, N, group_size, _ptr(q), _ptr(s), C.c_void_p(st)),
+                   "quantize_per_group_i8")
+    return q, s
+
+
+def int8_to_bf16_per_group(q, scales, group_size=0):
+    """The reference's truncating dequant of the dense W8A16 layout (src/cuda/int8_to_bf16.cu:24-40,
+    :99-117) -> bf16 [K, N]."""
+    assert q.is_cuda and q.dtype == torch.int8 and q.dim() == 2 and scales.dtype == torch.float32
+    q, scales = q.contiguous(), scales.contiguous()
+    K, N = q.shape
+    out = torch.empty((K, N), dtype=torch.bfloat16, device=q.device)
+    with torch.cuda.device(q.device):
+        st = torch.cuda.current_stream().cuda_stream
+        _lib.check(_lib.lib().atenia_int8_to_bf16_per_group(_ptr(q), _ptr(scales), K, N, group_size, _ptr(out),
+                                                            C.c_void_p(st)), "int8_to_bf16_per_group")
+    return out
 
 
 class RealMoeLayer:

@@ -15,6 +15,11 @@
  *   register_resident_moe_layer          src/moe/graph_op.rs:237   atenia_register_resident_moe_layer
  *   execute_real_moe_layer               src/moe/graph_op.rs:327   atenia_execute_real_moe_layer
  *   quantize_per_row_i8                  src/tensor/disk_tier.rs:231-245  atenia_quantize_per_row_i8
+ *   absmax_per_channel_symmetric,        src/tensor/quantizer.rs:67-118,
+ *   absmax_per_group_symmetric           :176-246                  atenia_quantize_per_group_i8
+ *   int8_to_bf16_per_{channel,group}_launch_device
+ *                                        src/cuda/int8_to_bf16.cu:42-73, :119-150
+ *                                                                  atenia_int8_to_bf16_per_group
  *   RealMoeStack::forward                src/moe/stack.rs:197-210  atenia_moe_stack_forward
  *
  * Conventions follow the reference's existing CUDA FFI (the .cu files under src/cuda): plain `extern "C"` functions,
@@ -196,6 +201,24 @@ ATENIA_API int atenia_moe_dispatch_noalloc(const int32_t* topk_idx, int T, int k
  * Bit-identical to quantize_per_row_i8 (src/tensor/disk_tier.rs:231-245). */
 ATENIA_API int atenia_quantize_per_row_i8(const float* w, int64_t rows, int64_t cols, int8_t* q,
                                           float* scales, void* stream);
+
+/* Dense W8A16 layout (the reference's non-MoE linear weights): row-major [K, N] f32 device matrix,
+ * one scale per (group of `group_size` consecutive rows, column): scales is [ceil(K / group_size), N].
+ * group_size 0 (or > K) means one group of K rows, i.e. per output channel.
+ * scale = max(amax / 127, 1e-12), q = clamp(round_half_away(w / scale), -127, 127), a NaN quotient
+ * gives 0.  Bit-identical to absmax_per_channel_symmetric (src/tensor/quantizer.rs:67-118) and
+ * absmax_per_group_symmetric (:176-246).  Asynchronous on `stream`; an empty matrix is a no-op. */
+ATENIA_API int atenia_quantize_per_group_i8(const float* w, int64_t K, int64_t N, int64_t group_size, int8_t* q,
+                                            float* scales, void* stream);
+
+/* The reference's materialising dequant of that layout: out[k, n] = the high 16 bits of
+ * (float)q[k, n] * scales[k / group_size, n] (bf16 by truncation).  Bit-identical to
+ * int8_to_bf16_per_channel_kernel / int8_to_bf16_per_group_kernel (src/cuda/int8_to_bf16.cu:24-40,
+ * :99-117); unlike those launchers it takes a stream and sizes as int64.  The MoE kernels of this
+ * library never materialise widened weights; this entry point exists for callers that hand the
+ * result to their own bf16 GEMM. */
+ATENIA_API int atenia_int8_to_bf16_per_group(const int8_t* q, const float* scales, int64_t K, int64_t N,
+                                             int64_t group_size, uint16_t* out_bf16, void* stream);
 
 /* ---- persistent expert tier files (host only) -----------------------------------------------
  * The reference persists each projection of each expert as one file `L{l}.e{i}.{gate,up,down}.bin`

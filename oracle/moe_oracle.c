@@ -399,6 +399,56 @@ ORACLE_API void oracle_dequantize_per_row_i8(const int8_t* q, const float* scale
     for (size_t c = 0; c < cols; ++c) out[r * cols + c] = (float)q[r * cols + c] * scales[r];
 }
 
+/* Dense W8A16 quantiser: weight [K, N] row-major, one scale per (group of `group_size` consecutive
+ * rows, column).  src/tensor/quantizer.rs:67-118 (per channel = one group of K rows) and :176-246
+ * (per group).  scale = max(amax/127, 1e-12); q = clamp(round_half_away(w / scale), -127, 127) with
+ * a true division; a NaN quotient becomes 0 (Rust's saturating `as i32`).  `v > max` skips NaNs. */
+ORACLE_API void oracle_absmax_per_group_symmetric(const float* w, size_t K, size_t N, size_t group_size,
+                                                  int8_t* q, float* scales) {
+  if (K == 0 || N == 0 || group_size == 0) return;
+  const size_t groups = (K + group_size - 1) / group_size;
+  for (size_t g = 0; g < groups; ++g) {
+    const size_t lo = g * group_size, hi = (g + 1) * group_size < K ? (g + 1) * group_size : K;
+    for (size_t c = 0; c < N; ++c) {
+      float amax = 0.0f;
+      for (size_t r = lo; r < hi; ++r) {
+        const float v = fabsf(w[r * N + c]);
+        if (v > amax) amax = v;
+      }
+      float sc = amax / 127.0f;
+      if (!(sc >= 1e-12f)) sc = 1e-12f; /* f32::max(1e-12); amax is never NaN here */
+      scales[g * N + c] = sc;
+    }
+  }
+  for (size_t r = 0; r < K; ++r) {
+    const float* srow = scales + (r / group_size) * N;
+    for (size_t c = 0; c < N; ++c) {
+      float v = round_half_away(w[r * N + c] / srow[c]);
+      if (v != v) {
+        q[r * N + c] = 0;
+        continue;
+      }
+      if (v < -127.0f) v = -127.0f;
+      if (v > 127.0f) v = 127.0f;
+      q[r * N + c] = (int8_t)(int32_t)v;
+    }
+  }
+}
+
+/* The reference's materialising dequant: bf16 = high 16 bits of (float)q * scale[group, col]
+ * (truncation).  src/cuda/int8_to_bf16.cu:24-40 (per channel) and :99-117 (per group). */
+ORACLE_API void oracle_int8_to_bf16_per_group(const int8_t* q, const float* scales, size_t K, size_t N,
+                                              size_t group_size, uint16_t* out) {
+  if (group_size == 0) return;
+  for (size_t r = 0; r < K; ++r)
+    for (size_t c = 0; c < N; ++c) {
+      const float f = (float)q[r * N + c] * scales[(r / group_size) * N + c];
+      uint32_t bits;
+      memcpy(&bits, &f, 4);
+      out[r * N + c] = (uint16_t)(bits >> 16);
+    }
+}
+
 /* src/moe/sparse.rs:87-116 */
 ORACLE_API int oracle_combine_selected(const int32_t* indices, const float* weights, int k,
                                        const float* expert_outputs, size_t n_outputs, int d,

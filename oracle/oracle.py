@@ -226,6 +226,29 @@ def dequantize_per_row_i8(q, s):
     return out
 
 
+def absmax_per_group_symmetric(w, group_size=0):
+    """Dense W8A16 quantiser over a [K, N] weight; group_size 0 = one group of K rows (per channel)."""
+    w = np.ascontiguousarray(w, dtype=np.float32)
+    K, N = w.shape
+    g = group_size if group_size > 0 else max(K, 1)
+    groups = (K + g - 1) // g
+    q = np.zeros((K, N), dtype=np.int8)
+    s = np.zeros((groups, N), dtype=np.float32)
+    lib().oracle_absmax_per_group_symmetric(_ptr(w), C.c_size_t(K), C.c_size_t(N), C.c_size_t(g), _ptr(q), _ptr(s))
+    return q, s
+
+
+def int8_to_bf16_per_group(q, s, group_size=0):
+    """bf16 bit patterns (uint16) of the reference's truncating dequant."""
+    q = np.ascontiguousarray(q, dtype=np.int8)
+    s = np.ascontiguousarray(s, dtype=np.float32)
+    K, N = q.shape
+    g = group_size if group_size > 0 else max(K, 1)
+    out = np.zeros((K, N), dtype=np.uint16)
+    lib().oracle_int8_to_bf16_per_group(_ptr(q), _ptr(s), C.c_size_t(K), C.c_size_t(N), C.c_size_t(g), _ptr(out))
+    return out
+
+
 def combine_selected(indices, weights, expert_outputs, d):
     indices = np.ascontiguousarray(indices, dtype=np.int32)
     weights = np.ascontiguousarray(weights, dtype=np.float32)
