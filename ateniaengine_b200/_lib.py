@@ -57,6 +57,7 @@ EXPORTS = [
     "atenia_moe_stack_forward", "atenia_moe_stack_check", "atenia_moe_stack_destroy",
     "atenia_moe_forward_selected", "atenia_tier_detect_dtype", "atenia_tier_read_qint8", "atenia_tier_read_bf16",
     "atenia_tier_read_f32", "atenia_quantize_per_group_i8", "atenia_int8_to_bf16_per_group",
+    "atenia_moe_ep_attach", "atenia_moe_ep_set_token_layout",
 ]
 
 _lib = None
@@ -107,6 +108,8 @@ def lib():
         l.atenia_register_real_moe_layer.argtypes = [C.POINTER(HostMoeLayer)]
         l.atenia_execute_real_moe_layer.argtypes = [C.c_int64, C.c_void_p, C.c_size_t, C.c_void_p]
         l.atenia_moe_ep_get_unique_id.argtypes = [C.c_void_p]
+        l.atenia_moe_ep_attach.argtypes = [C.c_void_p, C.c_void_p]
+        l.atenia_moe_ep_set_token_layout.argtypes = [C.c_void_p, C.c_int]
         for fn in (l.atenia_tier_detect_dtype,):
             fn.argtypes = [C.c_char_p, C.c_int64, C.c_int64]
         l.atenia_tier_read_qint8.argtypes = [C.c_char_p, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p]

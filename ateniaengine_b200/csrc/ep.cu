@@ -21,7 +21,17 @@
 #include "layer.cuh"
 
 namespace atenia {
+
+struct EpComm {
+  ncclComm_t comm = nullptr;  // null once aborted: every layer sharing it then reports ATENIA_ERR_STATE
+};
+
 namespace {
+
+void ep_comm_delete(EpComm* p) {
+  if (p->comm) ncclCommDestroy(p->comm);
+  delete p;
+}
 
 __global__ void counts_kernel(const int32_t* __restrict__ off, int E, int32_t* __restrict__ counts) {
   int e = blockIdx.x * blockDim.x + threadIdx.x;
@@ -57,7 +67,7 @@ int bounded_stream_wait(AteniaMoeLayer* L, cudaStream_t s) {
     double v = e ? std::atof(e) : 60.0;
     return v > 0.0 ? v : 60.0;
   }();
-  ncclComm_t comm = reinterpret_cast<ncclComm_t>(L->comm);
+  ncclComm_t comm = L->ep->comm;
   const auto t0 = std::chrono::steady_clock::now();
   for (;;) {
     cudaError_t q = cudaStreamQuery(s);
@@ -68,7 +78,7 @@ int bounded_stream_wait(AteniaMoeLayer* L, cudaStream_t s) {
     const double waited = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
     if (bad || waited > limit_s) {
       ncclCommAbort(comm);
-      L->comm = nullptr;
+      L->ep->comm = nullptr;
       return ATENIA_ERR_NCCL;
     }
     if (waited > 0.002) std::this_thread::sleep_for(std::chrono::microseconds(50));
@@ -97,7 +107,7 @@ int ep_forward_exchange(AteniaMoeLayer* L, int T, cudaStream_t s) {
   (void)T;
   const AteniaMoeConfig& c = L->cfg;
   const int G = c.ep_world, E = c.num_experts, El = L->e_local, rank = c.ep_rank, d = c.d_model;
-  ncclComm_t comm = reinterpret_cast<ncclComm_t>(L->comm);
+  ncclComm_t comm = L->ep->comm;
   counts_kernel<<<1, 128, 0, s>>>(L->expert_offsets, E, L->d_counts_all + (size_t)rank * E);
   count_launch();
   NCCL_TRY(ncclAllGather(L->d_counts_all + (size_t)rank * E, L->d_counts_all, (size_t)E, ncclInt32, comm, s));
@@ -123,12 +133,27 @@ int ep_forward_exchange(AteniaMoeLayer* L, int T, cudaStream_t s) {
   return exchange(comm, rank, G, L->recv_y, r_off, r_cnt, L->y_perm, s_off, s_cnt, d, s);
 }
 
-void ep_destroy(AteniaMoeLayer* L) {
-  if (L->comm) {
-    ncclCommDestroy(reinterpret_cast<ncclComm_t>(L->comm));
-    L->comm = nullptr;
-  }
+// Replicated tokens (decode): every rank holds the same batch and has routed and sorted it
+// identically.  A rank runs the grouped GEMMs over the groups of its own experts only, which sit at
+// the same rows of the dispatch-ordered buffers on every rank; rows of experts owned elsewhere stay
+// zero.  Summing y_perm over the ranks then assembles all rows on all ranks.  Exactly one rank
+// contributes a non-zero value to any element, so the sum is exact in whatever order NCCL adds, and
+// the combine that follows sees the bytes of the single-GPU run.  No host read: the whole forward is
+// launches on `s` and can be captured into a CUDA graph.
+int ep_forward_replicated(AteniaMoeLayer* L, int n_rows, cudaStream_t s) {
+  if (n_rows <= 0) return ATENIA_OK;
+  const int d = L->cfg.d_model;
+  ATENIA_CUDA_TRY(cudaMemsetAsync(L->y_perm, 0, (size_t)n_rows * d * sizeof(__nv_bfloat16), s));
+  int rc = run_expert_gemms(L, L->tm_x_perm, L->tm_recv_h, L->x_perm, L->recv_h, L->y_perm,
+                            L->expert_offsets + L->e_begin, L->e_local, n_rows, s);
+  if (rc) return rc;
+  NCCL_TRY(ncclAllReduce(L->y_perm, L->y_perm, (size_t)n_rows * d, ncclBfloat16, ncclSum, L->ep->comm, s));
+  return ATENIA_OK;
 }
+
+bool ep_ready(const AteniaMoeLayer* L) { return L->ep && L->ep->comm; }
+
+void ep_destroy(AteniaMoeLayer* L) { L->ep.reset(); }
 
 }  // namespace atenia
 
@@ -175,12 +200,31 @@ int atenia_moe_ep_get_unique_id(void* id_out) {
 int atenia_moe_ep_init(AteniaMoeLayer* L, const void* unique_id) {
   if (!L || !unique_id) return ATENIA_ERR_NULL;
   if (L->cfg.ep_world <= 1) return ATENIA_ERR_STATE;
-  if (L->comm) return ATENIA_OK;
+  if (atenia::ep_ready(L)) return ATENIA_OK;
   ncclUniqueId id;
   memcpy(&id, unique_id, sizeof(id));
   ncclComm_t comm = nullptr;
   if (ncclCommInitRank(&comm, L->cfg.ep_world, id, L->cfg.ep_rank) != ncclSuccess) return ATENIA_ERR_NCCL;
-  L->comm = reinterpret_cast<ncclComm*>(comm);
+  atenia::EpComm* holder = new atenia::EpComm();
+  holder->comm = comm;
+  L->ep = std::shared_ptr<atenia::EpComm>(holder, atenia::ep_comm_delete);
+  return ATENIA_OK;
+}
+
+int atenia_moe_ep_attach(AteniaMoeLayer* L, AteniaMoeLayer* owner) {
+  if (!L || !owner) return ATENIA_ERR_NULL;
+  if (L->cfg.ep_world <= 1 || !atenia::ep_ready(owner)) return ATENIA_ERR_STATE;
+  if (L->cfg.ep_world != owner->cfg.ep_world || L->cfg.ep_rank != owner->cfg.ep_rank || L->device != owner->device)
+    return ATENIA_ERR_SHAPE;
+  L->ep = owner->ep;
+  return ATENIA_OK;
+}
+
+int atenia_moe_ep_set_token_layout(AteniaMoeLayer* L, int layout) {
+  if (!L) return ATENIA_ERR_NULL;
+  if (layout != ATENIA_EP_TOKENS_SHARDED && layout != ATENIA_EP_TOKENS_REPLICATED) return ATENIA_ERR_SHAPE;
+  if (L->cfg.ep_world <= 1) return ATENIA_ERR_STATE;
+  L->ep_replicated = layout == ATENIA_EP_TOKENS_REPLICATED;
   return ATENIA_OK;
 }
 

@@ -1,10 +1,13 @@
 // Internal definition of AteniaMoeLayer (shared by moe_layer.cu, ep.cu, registry.cu).
 #pragma once
+#include <memory>
 #include <vector>
 
 #include "common.cuh"
 
-struct ncclComm;
+namespace atenia {
+struct EpComm;  // ep.cu: an NCCL communicator, destroyed with its last holder
+}
 
 struct AteniaMoeLayer {
   AteniaMoeConfig cfg{};
@@ -72,7 +75,8 @@ struct AteniaMoeLayer {
   CUtensorMap tm_x_perm{}, tm_h{}, tm_h_shared{};
 
   // expert parallelism
-  ncclComm* comm = nullptr;
+  std::shared_ptr<atenia::EpComm> ep;  // layers of one stack may share a communicator (atenia_moe_ep_attach)
+  bool ep_replicated = false;          // every rank holds the same tokens (atenia_moe_ep_set_token_layout)
   int recv_cap = 0;                    // rows of the receive-side buffers
   __nv_bfloat16* recv_x = nullptr;     // [recv_cap, d]
   __nv_bfloat16* recv_h = nullptr;     // [recv_cap, F]
@@ -89,6 +93,8 @@ struct AteniaMoeLayer {
 
 namespace atenia {
 int ep_forward_exchange(AteniaMoeLayer* L, int T, cudaStream_t s);  // ep.cu
+int ep_forward_replicated(AteniaMoeLayer* L, int n_rows, cudaStream_t s);
+bool ep_ready(const AteniaMoeLayer* L);
 void ep_destroy(AteniaMoeLayer* L);
 int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorMap& tm_mid,
                      const __nv_bfloat16* a_ptr, __nv_bfloat16* mid, __nv_bfloat16* out,

@@ -80,7 +80,6 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
     g1.err = L->d_err;
     g1.max_rows = max_rows;
     g1.w8 = q;
-  g1.splitk_ws = L->splitk_ws;
     g1.splitk_ws = L->splitk_ws;
     int rc = tmem ? launch_grouped_gemm_w8_tmem(g1, L->num_sms, s)
                   : pairs ? launch_grouped_gemm_2cta(g1, L->num_sms, s) : launch_grouped_gemm_tcgen05(g1, L->num_sms, s);
@@ -108,7 +107,6 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
     g2.err = L->d_err;
     g2.max_rows = max_rows;
     g2.w8 = q;
-  g2.splitk_ws = L->splitk_ws;
     g2.splitk_ws = L->splitk_ws;
     int rc = tmem ? launch_grouped_gemm_w8_tmem(g2, L->num_sms, s)
                   : pairs ? launch_grouped_gemm_2cta(g2, L->num_sms, s) : launch_grouped_gemm_tcgen05(g2, L->num_sms, s);
@@ -464,15 +462,16 @@ static int forward_impl(AteniaMoeLayer* L, const void* x, int x_dtype, int T, vo
   if (!L) return ATENIA_ERR_NULL;
   if (!L->weights_set) return ATENIA_ERR_STATE;
   if (T < 0) return ATENIA_ERR_SHAPE;
-  if (T == 0 && L->cfg.ep_world == 1) return ATENIA_OK;  // an empty batch has no buffers to check
+  // an empty batch has no buffers to check (token-sharded expert parallelism still joins the exchange)
+  const bool no_exchange = L->cfg.ep_world == 1 || L->ep_replicated;
+  if (T == 0 && no_exchange) return ATENIA_OK;
   if (!x || !out) return ATENIA_ERR_NULL;
   if (T > L->cfg.max_tokens) return ATENIA_ERR_CAPACITY;
   if ((x_dtype != ATENIA_IO_BF16 && x_dtype != ATENIA_IO_F32) ||
       (out_dtype != ATENIA_IO_BF16 && out_dtype != ATENIA_IO_F32))
     return ATENIA_ERR_SHAPE;
-  if (L->cfg.ep_world > 1 && !L->comm) return ATENIA_ERR_STATE;
+  if (L->cfg.ep_world > 1 && !ep_ready(L)) return ATENIA_ERR_STATE;
   g_counters[ATENIA_COUNTER_FORWARD_CALLS] += 1;
-  if (T == 0 && L->cfg.ep_world == 1) return ATENIA_OK;
   const AteniaMoeConfig& c = L->cfg;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int k = c.experts_per_token, n = T * k;
@@ -531,6 +530,8 @@ static int forward_impl(AteniaMoeLayer* L, const void* x, int x_dtype, int T, vo
   if (c.ep_world == 1) {
     rc = run_expert_gemms(L, L->tm_x_perm, L->tm_h, L->x_perm, L->h, L->y_perm, L->expert_offsets,
                           c.num_experts, n, s);
+  } else if (L->ep_replicated) {
+    rc = ep_forward_replicated(L, n, s);
   } else {
     rc = ep_forward_exchange(L, T, s);
   }

@@ -96,7 +96,7 @@ int atenia_moe_stack_create(AteniaMoeLayer* const* layers, int n_layers, int res
       delete S;
       return ATENIA_ERR_NULL;
     }
-    if (!L->weights_set || L->cfg.ep_world != 1) {
+    if (!L->weights_set || (L->cfg.ep_world != 1 && !L->ep_replicated)) {
       delete S;
       return ATENIA_ERR_STATE;
     }
@@ -171,7 +171,8 @@ int atenia_moe_stack_forward(AteniaMoeStack* S, const void* x, int x_dtype, int 
     return run_layers(S, x, x_dtype, T, out, out_dtype, s);
   }
   if (!S->exec) {
-    // Everything a forward does on a single GPU is kernel launches on `s`, so it can be captured.
+    // Everything a forward does here is launches on `s` (kernels, and with replicated-token expert
+    // parallelism one NCCL all-reduce per layer), so it can be captured.
     ATENIA_CUDA_TRY(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
     int rc = run_layers(S, x, x_dtype, T, out, out_dtype, s);
     cudaGraph_t graph = nullptr;

@@ -196,6 +196,15 @@ class RealMoeLayer:
         with torch.cuda.device(self.device):
             _lib.check(_lib.lib().atenia_moe_ep_init(self._h, buf), "atenia_moe_ep_init")
 
+    def ep_attach(self, owner):
+        """Share the NCCL communicator `owner` joined with ep_init (one communicator per model, not per layer)."""
+        _lib.check(_lib.lib().atenia_moe_ep_attach(self._h, owner._h), "atenia_moe_ep_attach")
+
+    def ep_replicated_tokens(self, enable=True):
+        """Expert parallelism over a batch that every rank holds (decode): no token exchange, one
+        all-reduce of the expert outputs, capturable in a CUDA graph."""
+        _lib.check(_lib.lib().atenia_moe_ep_set_token_layout(self._h, 1 if enable else 0), "atenia_moe_ep_set_token_layout")
+
     def forward(self, x, out=None, out_dtype=None, aux=False, sync=False):
         """x: [T, d] CUDA bf16 or f32.  Returns out (and a dict of routing tensors when aux)."""
         assert x.is_cuda and x.dim() == 2 and x.shape[1] == self.config.d_model

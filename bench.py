@@ -141,19 +141,43 @@ def run_stack_bench(args):
     """Decode benchmark: a stack of W8A16 Mixtral-shaped MoE-FFN layers with a residual add between
     layers (attention omitted), Zipf-skewed routing, small batches.  One step = one pass of the batch
     through all layers (replayed from a CUDA graph on a side stream)."""
+    import ctypes as C
+
     import numpy as np
     import torch
 
     from ateniaengine_b200 import _lib, synth
     from ateniaengine_b200.moe import RealMoeStack
 
-    torch.cuda.set_device(0)
-    dev = torch.device("cuda", 0)
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
     shape = synth.SHAPES["mixtral_int8"]
     B = args.tokens or 8
     n_layers = args.layers
-    ws = [synth.make_weights(shape, 5 + l, dev) for l in range(n_layers)]
-    layers = [synth.build_layer(shape, w, max_tokens=max(B, 1)) for w in ws]
+    # expert parallelism for decode: every rank holds the same batch and E / world experts of each layer
+    el = shape.num_experts // world
+    ws = [synth.make_weights(shape, 5 + l, dev, experts=(rank * el, el) if world > 1 else None) for l in range(n_layers)]
+    layers = [synth.build_layer(shape, w, max_tokens=max(B, 1), ep_rank=rank, ep_world=world) for w in ws]
+    if world > 1:
+        nb = _lib.lib().atenia_moe_ep_unique_id_bytes()
+        idt = torch.zeros(nb, dtype=torch.uint8, device=dev)
+        if rank == 0:
+            buf = C.create_string_buffer(nb)
+            _lib.check(_lib.lib().atenia_moe_ep_get_unique_id(buf), "ep_get_unique_id")
+            idt = torch.frombuffer(bytearray(buf.raw), dtype=torch.uint8).to(dev)
+        dist.broadcast(idt, 0)
+        layers[0].ep_init(bytes(idt.cpu().numpy().tobytes()))
+        for l in layers[1:]:
+            l.ep_attach(layers[0])
+        for l in layers:
+            l.ep_replicated_tokens(True)
     stack = RealMoeStack(layers, residual=2)
     x = synth.make_activations(shape, 5, dev, tokens=B, dtype=torch.float32)
     out = torch.empty_like(x)
@@ -174,12 +198,16 @@ def run_stack_bench(args):
         for _ in range(max(args.warmup, 3)):
             stack.forward(x, out=out)
         side.synchronize()
-        sampler = ClockSampler(0)
-        sampler.start()
+        sampler = ClockSampler(local_rank)
+        if rank == 0:
+            sampler.start()
         time.sleep(0.8)
-        for _ in range(3):
+        for _ in range(3):  # every rank replays the same graphs: each one holds a collective per layer
             stack.forward(x, out=out)
         side.synchronize()
+        if dist is not None:
+            dist.barrier()
+            torch.cuda.synchronize()
         t0 = time.perf_counter()
         launches0 = _lib.lib().atenia_moe_counter(1)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -191,19 +219,30 @@ def run_stack_bench(args):
         ms = e0.elapsed_time(e1) / args.steps
         launches = int(_lib.lib().atenia_moe_counter(1) - launches0)
         sampler.window = (t0, time.perf_counter())
-        clocks = sampler.stop()
+        clocks = sampler.stop() if rank == 0 else None
     _lib.check(_lib.lib().atenia_moe_stack_check(stack._h, None), "stack_check")
     assert torch.isfinite(out).all()
+    if dist is not None:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        dist.barrier()
+        dist.destroy_process_group()
+        if rank != 0:
+            return 0
     peaks, peak_src = load_peaks()
     wbytes = sum(t * 3 * shape.d_model * shape.d_ff for t in touched)  # one byte per weight
-    achieved = wbytes / (ms * 1e-3) / 1e9
-    line = {"metric": "moe_ffn_stack_tokens_per_s", "value": B / (ms * 1e-3), "unit": UNIT, "n_gpus": 1,
+    # the rank that owns the most touched experts sets the pace; with an even split each streams 1 / world
+    achieved = wbytes / world / (ms * 1e-3) / 1e9
+    line = {"metric": "moe_ffn_stack_tokens_per_s", "value": B / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "int8 weights, bf16 operands, f32 residual stream (W8A16)",
+            "scaling": "weak" if world == 1 else "strong", "vs_baseline": None, "dtype": "int8 weights, bf16 operands, f32 residual stream (W8A16)",
             "data": "synthetic",
             "config": {"workload": f"mixtral_int8 stack: {n_layers} layers, d_model={shape.d_model} d_ff={shape.d_ff} "
                                    f"experts={shape.num_experts} top_k={shape.top_k}, pre-norm residual blocks x + MoE(rmsnorm(x)), batch={B}",
                        "routing_skew": "zipf(1.1)", "experts_touched_per_layer": touched,
+                       "parallelism": "single GPU" if world == 1 else
+                       f"expert-parallel ep{world}, the batch replicated on every rank, one NCCL all-reduce per layer",
                        "l2_policy": f"inputs larger than L2: {wbytes / 1e6:.0f} MB of expert weights per step"},
             "roofline": {"bound": "hbm", "kernel": "whole step (weights of the touched experts, once per step)",
                          "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
@@ -242,8 +281,6 @@ def main():
     arm_watchdog(float(os.environ.get("ATENIA_BENCH_WATCHDOG_S", "600" if args.impl == "reference" else "300")),
                  "the whole run")
     if args.workload == "mixtral_int8_stack":
-        if int(os.environ.get("RANK", "0")) != 0:
-            return 0
         return run_stack_bench(args)
     args.warmup = max(args.warmup, 3)
 

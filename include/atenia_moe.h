@@ -285,7 +285,8 @@ ATENIA_API AteniaMoeLayer* atenia_get_real_moe_layer(int64_t layer_id);
  * block of a transformer with attention left out, x <- x + layer_l(rmsnorm(x)) with unit gain and
  * eps 1e-5 (without a norm, random SwiGLU layers blow the residual stream up within a few layers).
  * Both require f32 input.  The stack
- * borrows the layers (single GPU, equal d_model, else ATENIA_ERR_DIM_MISMATCH as
+ * borrows the layers (single GPU or expert-parallel with replicated tokens; equal d_model, else
+ * ATENIA_ERR_DIM_MISMATCH as
  * MoeStackError::DModelMismatch); activations between layers are f32 buffers of the stack.  On a
  * non-default stream the sequence is captured once per (T, x, out) into a CUDA graph and replayed. */
 typedef struct AteniaMoeStack AteniaMoeStack;
@@ -308,6 +309,27 @@ ATENIA_API int atenia_moe_ep_get_unique_id(void* id_out);
  * this, atenia_moe_forward routes this rank's tokens, exchanges rows with the ranks that own the
  * selected experts, runs the local experts and exchanges the results back. */
 ATENIA_API int atenia_moe_ep_init(AteniaMoeLayer* layer, const void* unique_id);
+
+/* Let `layer` use the communicator `owner` joined with atenia_moe_ep_init (same ep_rank, ep_world and
+ * device), so that the layers of a model share one NCCL communicator instead of one each.  The
+ * communicator lives until the last layer holding it is destroyed.  After ATENIA_ERR_NCCL (a peer
+ * failed, the communicator was aborted) every layer that shares it returns ATENIA_ERR_STATE. */
+ATENIA_API int atenia_moe_ep_attach(AteniaMoeLayer* layer, AteniaMoeLayer* owner);
+
+/* How tokens are laid out over the ranks of an expert-parallel layer (no counterpart in the
+ * reference, which has no multi-GPU path):
+ *   ATENIA_EP_TOKENS_SHARDED     (default) every rank brings its own tokens; rows travel to the ranks
+ *                                that own the selected experts and back (two all-to-alls and one
+ *                                host read of the row counts per forward)
+ *   ATENIA_EP_TOKENS_REPLICATED  every rank passes the SAME [T, d] batch (decode); each rank runs its
+ *                                own experts over it and the expert outputs are assembled with one
+ *                                all-reduce in which every element has a single non-zero
+ *                                contributor, so every rank returns the bytes of the single-GPU
+ *                                result.  No host read: the forward can be captured in a CUDA graph
+ *                                and such layers can be put in an atenia_moe_stack. */
+#define ATENIA_EP_TOKENS_SHARDED 0
+#define ATENIA_EP_TOKENS_REPLICATED 1
+ATENIA_API int atenia_moe_ep_set_token_layout(AteniaMoeLayer* layer, int layout);
 
 /* The exchange plan one rank derives from the all-gathered count matrix counts_all[world][E]
  * (rows rank p holds for expert e, in p's dispatch order).  Experts are owned contiguously:
