@@ -164,6 +164,10 @@ int encode_tmap_2d_u8(CUtensorMap* out, const void* base, uint64_t rows, uint64_
 // token matrix (box {64, 128}, 128B swizzle); tmap_b0/b1 are int8 maps with the 64-byte swizzle.
 int launch_grouped_gemm_w8_tmem(const GroupedGemmArgs& a, int num_sms, cudaStream_t s);
 constexpr size_t kW8SplitKSlotFloats = 2 * 128 * 128;  // per CTA: two slots of this size
+// W8A16 for large groups (w8_gemm_wide.cu): one widened weight tile per k-block for up to 192 tokens.
+// tmap_a is the bf16 token matrix with box {64, 64} (128B swizzle); tmap_b0/b1 are int8 maps with box
+// {64, 64} and the 64-byte swizzle.
+int launch_grouped_gemm_w8_wide(const GroupedGemmArgs& a, int num_sms, cudaStream_t s);
 // bf16 weights, CTA pairs (tcgen05 cta_group::2): 256-row tiles, each CTA stages half of the weight tile
 int launch_grouped_gemm_2cta(const GroupedGemmArgs& a, int num_sms, cudaStream_t s);
 

@@ -128,7 +128,7 @@ int ep_forward_exchange(AteniaMoeLayer* L, int T, cudaStream_t s) {
   int rc = exchange(comm, rank, G, L->x_perm, s_off, s_cnt, L->recv_x, r_off, r_cnt, d, s);
   if (rc) return rc;
   rc = run_expert_gemms(L, L->tm_recv_x, L->tm_recv_h, L->recv_x, L->recv_h, L->recv_y, L->d_group_offsets,
-                        L->n_groups, (int)ro, s);
+                        L->n_groups, (int)ro, s, &L->tm_recv_x_r64, &L->tm_recv_h_r64);
   if (rc) return rc;
   return exchange(comm, rank, G, L->recv_y, r_off, r_cnt, L->y_perm, s_off, s_cnt, d, s);
 }
@@ -145,7 +145,8 @@ int ep_forward_replicated(AteniaMoeLayer* L, int n_rows, cudaStream_t s) {
   const int d = L->cfg.d_model;
   ATENIA_CUDA_TRY(cudaMemsetAsync(L->y_perm, 0, (size_t)n_rows * d * sizeof(__nv_bfloat16), s));
   int rc = run_expert_gemms(L, L->tm_x_perm, L->tm_recv_h, L->x_perm, L->recv_h, L->y_perm,
-                            L->expert_offsets + L->e_begin, L->e_local, n_rows, s);
+                            L->expert_offsets + L->e_begin, L->e_local, n_rows, s, &L->tm_x_perm_r64,
+                            &L->tm_recv_h_r64);
   if (rc) return rc;
   NCCL_TRY(ncclAllReduce(L->y_perm, L->y_perm, (size_t)n_rows * d, ncclBfloat16, ncclSum, L->ep->comm, s));
   return ATENIA_OK;

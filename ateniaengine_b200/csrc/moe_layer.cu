@@ -48,15 +48,19 @@ int validate_config(const AteniaMoeConfig& c) {
 
 int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorMap& tm_mid,
                      const __nv_bfloat16* a_ptr, __nv_bfloat16* mid, __nv_bfloat16* out,
-                     const int32_t* group_offsets, int num_groups, int max_rows, cudaStream_t s) {
+                     const int32_t* group_offsets, int num_groups, int max_rows, cudaStream_t s,
+                     const CUtensorMap* tm_a64, const CUtensorMap* tm_mid64) {
   const AteniaMoeConfig& c = L->cfg;
   const bool q = c.weight_dtype == ATENIA_W_INT8_ROW;
+  const bool large = max_rows >= 256 * num_groups;
+  // INT8, on request: the wide tensor-memory kernel for large groups
+  const bool wide = q && L->w8_mode == 3 && L->has_r64 && tm_a64 && tm_mid64 && large && !L->use_check_gemm;
   // INT8: the tensor-memory kernel wins while groups are small (its MMA width follows the row count),
   // the shared-memory widening kernel once every group fills several 128-row tiles.
-  const bool tmem = q && (L->w8_mode == 1 || (L->w8_mode == 0 && max_rows < 256 * num_groups));
+  const bool tmem = q && !wide && (L->w8_mode == 1 || ((L->w8_mode == 0 || L->w8_mode == 3) && !large));
   // bf16: 256-row CTA-pair tiles pay off once an average group fills a few of them
   // (INT8 has a pair kernel too, but it measures slower than the single-CTA one: only on request.)
-  const bool pairs = !tmem && (L->pair_mode == 1 || (L->pair_mode == 0 && !q && max_rows >= 512 * num_groups));
+  const bool pairs = !tmem && !wide && (L->pair_mode == 1 || (L->pair_mode == 0 && !q && max_rows >= 512 * num_groups));
   if (L->timing) cudaEventRecord(L->ev[0], s);
   if (L->use_check_gemm) {
     GroupedGemmCheckArgs k1{a_ptr, L->d_p_gate, L->d_p_up, q ? 1 : 0, q ? L->d_sc_gate : nullptr,
@@ -66,9 +70,9 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
     if (rc) return rc;
   } else {
     GroupedGemmArgs g1{};
-    g1.tmap_a = tm_a;
-    g1.tmap_b0 = tmem ? L->d_tm_gate_sw : L->d_tm_gate;
-    g1.tmap_b1 = tmem ? L->d_tm_up_sw : L->d_tm_up;
+    g1.tmap_a = wide ? *tm_a64 : tm_a;
+    g1.tmap_b0 = wide ? L->d_tm_gate_r64 : tmem ? L->d_tm_gate_sw : L->d_tm_gate;
+    g1.tmap_b1 = wide ? L->d_tm_up_r64 : tmem ? L->d_tm_up_sw : L->d_tm_up;
     g1.group_offsets = group_offsets;
     g1.num_groups = num_groups;
     g1.N = c.d_ff;
@@ -81,8 +85,10 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
     g1.max_rows = max_rows;
     g1.w8 = q;
     g1.splitk_ws = L->splitk_ws;
-    int rc = tmem ? launch_grouped_gemm_w8_tmem(g1, L->num_sms, s)
-                  : pairs ? launch_grouped_gemm_2cta(g1, L->num_sms, s) : launch_grouped_gemm_tcgen05(g1, L->num_sms, s);
+    int rc = wide ? launch_grouped_gemm_w8_wide(g1, L->num_sms, s)
+                  : tmem ? launch_grouped_gemm_w8_tmem(g1, L->num_sms, s)
+                         : pairs ? launch_grouped_gemm_2cta(g1, L->num_sms, s)
+                                 : launch_grouped_gemm_tcgen05(g1, L->num_sms, s);
     if (rc) return rc;
   }
   if (L->timing) cudaEventRecord(L->ev[1], s);
@@ -93,8 +99,8 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
     if (rc) return rc;
   } else {
     GroupedGemmArgs g2{};
-    g2.tmap_a = tm_mid;
-    g2.tmap_b0 = tmem ? L->d_tm_down_sw : L->d_tm_down;
+    g2.tmap_a = wide ? *tm_mid64 : tm_mid;
+    g2.tmap_b0 = wide ? L->d_tm_down_r64 : tmem ? L->d_tm_down_sw : L->d_tm_down;
     g2.tmap_b1 = g2.tmap_b0;
     g2.group_offsets = group_offsets;
     g2.num_groups = num_groups;
@@ -108,8 +114,10 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
     g2.max_rows = max_rows;
     g2.w8 = q;
     g2.splitk_ws = L->splitk_ws;
-    int rc = tmem ? launch_grouped_gemm_w8_tmem(g2, L->num_sms, s)
-                  : pairs ? launch_grouped_gemm_2cta(g2, L->num_sms, s) : launch_grouped_gemm_tcgen05(g2, L->num_sms, s);
+    int rc = wide ? launch_grouped_gemm_w8_wide(g2, L->num_sms, s)
+                  : tmem ? launch_grouped_gemm_w8_tmem(g2, L->num_sms, s)
+                         : pairs ? launch_grouped_gemm_2cta(g2, L->num_sms, s)
+                                 : launch_grouped_gemm_tcgen05(g2, L->num_sms, s);
     if (rc) return rc;
   }
   if (L->timing) {
@@ -124,7 +132,8 @@ namespace {
 int run_shared_gemms(AteniaMoeLayer* L, const __nv_bfloat16* xb, int T, cudaStream_t s) {
   const AteniaMoeConfig& c = L->cfg;
   const bool q = c.weight_dtype == ATENIA_W_INT8_ROW;
-  const bool tmem = q && (L->w8_mode == 1 || (L->w8_mode == 0 && T < 256));
+  // (the shared expert keeps the default choice under w8_mode 3)
+  const bool tmem = q && (L->w8_mode == 1 || ((L->w8_mode == 0 || L->w8_mode == 3) && T < 256));
   const bool pairs = !tmem && (L->pair_mode == 1 || (L->pair_mode == 0 && !q && T >= 512));
   if (L->timing) cudaEventRecord(L->ev[3], s);
   if (L->use_check_gemm) {
@@ -262,6 +271,12 @@ int atenia_moe_create(const AteniaMoeConfig* cfg, AteniaMoeLayer** out) {
     TRY_ALLOC(L->d_tm_up_sw, (size_t)L->n_groups);
     TRY_ALLOC(L->d_tm_down_sw, (size_t)L->n_groups);
     TRY_ALLOC(L->d_tm_shared_sw, 3);
+    if (L->w8_mode == 3) {
+      TRY_ALLOC(L->d_tm_gate_r64, (size_t)L->n_groups);
+      TRY_ALLOC(L->d_tm_up_r64, (size_t)L->n_groups);
+      TRY_ALLOC(L->d_tm_down_r64, (size_t)L->n_groups);
+      L->has_r64 = true;
+    }
   }
   TRY_ALLOC(L->d_sc_gate, (size_t)L->n_groups);
   TRY_ALLOC(L->d_sc_up, (size_t)L->n_groups);
@@ -301,6 +316,14 @@ int atenia_moe_create(const AteniaMoeConfig* cfg, AteniaMoeLayer** out) {
     rc = encode_tmap_2d_bf16(&L->tm_recv_x, L->recv_x, (uint64_t)L->recv_cap, d, 128, 64);
     if (!rc) rc = encode_tmap_2d_bf16(&L->tm_recv_h, L->recv_h, (uint64_t)L->recv_cap, F, 128, 64);
   }
+  if (!rc && L->has_r64) {
+    rc = encode_tmap_2d_bf16(&L->tm_x_perm_r64, L->x_perm, R, d, 64, 64);
+    if (!rc && L->h) rc = encode_tmap_2d_bf16(&L->tm_h_r64, L->h, R, F, 64, 64);
+    if (!rc && c.ep_world > 1) {
+      rc = encode_tmap_2d_bf16(&L->tm_recv_x_r64, L->recv_x, (uint64_t)L->recv_cap, d, 64, 64);
+      if (!rc) rc = encode_tmap_2d_bf16(&L->tm_recv_h_r64, L->recv_h, (uint64_t)L->recv_cap, F, 64, 64);
+    }
+  }
   if (rc) {
     atenia_moe_destroy(L);
     return rc;
@@ -320,7 +343,7 @@ int atenia_moe_destroy(AteniaMoeLayer* L) {
                   L->x_bf16,     L->h_shared,    L->y_shared,    L->d_err,          L->d_tm_gate,
                   L->d_tm_up,    L->d_tm_down,   L->d_tm_shared, L->d_sc_gate,      L->d_sc_up,
                   L->d_sc_down,  L->d_sc_shared, L->d_p_gate,    L->d_p_up,         L->d_p_down,
-                  L->d_p_shared, L->d_tm_gate_sw, L->d_tm_up_sw, L->d_tm_down_sw, L->d_tm_shared_sw, L->splitk_ws, L->d_escore, L->logits_ws, L->recv_x,      L->recv_h,      L->recv_y,         L->d_counts_all,
+                  L->d_p_shared, L->d_tm_gate_sw, L->d_tm_up_sw, L->d_tm_down_sw, L->d_tm_shared_sw, L->d_tm_gate_r64, L->d_tm_up_r64, L->d_tm_down_r64, L->splitk_ws, L->d_escore, L->logits_ws, L->recv_x,      L->recv_h,      L->recv_y,         L->d_counts_all,
                   L->d_group_offsets};
   for (void* p : ptrs)
     if (p) cudaFree(p);
@@ -367,7 +390,7 @@ int atenia_moe_set_weights(AteniaMoeLayer* L, const AteniaMoeWeights* w) {
   };
 
   const int G = L->n_groups, El = L->e_local;
-  std::vector<CUtensorMap> tg(G), tu(G), td(G), tgs(G), tus(G), tds(G);
+  std::vector<CUtensorMap> tg(G), tu(G), td(G), tgs(G), tus(G), tds(G), tg6(G), tu6(G), td6(G);
   std::vector<const void*> pg(G), pu(G), pd(G);
   std::vector<const float*> sg(G, nullptr), su(G, nullptr), sd(G, nullptr);
   for (int e = 0; e < El; ++e) {
@@ -380,6 +403,9 @@ int atenia_moe_set_weights(AteniaMoeLayer* L, const AteniaMoeWeights* w) {
     if (!rc && q) rc = encode(&tgs[e], pg[e], F, d, 1);
     if (!rc && q) rc = encode(&tus[e], pu[e], F, d, 1);
     if (!rc && q) rc = encode(&tds[e], pd[e], d, F, 1);
+    if (!rc && L->has_r64) rc = encode_tmap_2d_u8(&tg6[e], pg[e], F, d, 64, 64, 1);
+    if (!rc && L->has_r64) rc = encode_tmap_2d_u8(&tu6[e], pu[e], F, d, 64, 64, 1);
+    if (!rc && L->has_r64) rc = encode_tmap_2d_u8(&td6[e], pd[e], d, F, 64, 64, 1);
     if (rc) return rc;
     if (q) {
       if (!w->s_gate[e] || !w->s_up[e] || !w->s_down[e]) return ATENIA_ERR_NULL;
@@ -396,6 +422,9 @@ int atenia_moe_set_weights(AteniaMoeLayer* L, const AteniaMoeWeights* w) {
     tgs[g] = tgs[g % El];
     tus[g] = tus[g % El];
     tds[g] = tds[g % El];
+    tg6[g] = tg6[g % El];
+    tu6[g] = tu6[g % El];
+    td6[g] = td6[g % El];
     pg[g] = pg[g % El];
     pu[g] = pu[g % El];
     pd[g] = pd[g % El];
@@ -411,6 +440,11 @@ int atenia_moe_set_weights(AteniaMoeLayer* L, const AteniaMoeWeights* w) {
     ATENIA_CUDA_TRY(cudaMemcpy(L->d_tm_gate_sw, tgs.data(), mb, cudaMemcpyHostToDevice));
     ATENIA_CUDA_TRY(cudaMemcpy(L->d_tm_up_sw, tus.data(), mb, cudaMemcpyHostToDevice));
     ATENIA_CUDA_TRY(cudaMemcpy(L->d_tm_down_sw, tds.data(), mb, cudaMemcpyHostToDevice));
+  }
+  if (L->has_r64) {
+    ATENIA_CUDA_TRY(cudaMemcpy(L->d_tm_gate_r64, tg6.data(), mb, cudaMemcpyHostToDevice));
+    ATENIA_CUDA_TRY(cudaMemcpy(L->d_tm_up_r64, tu6.data(), mb, cudaMemcpyHostToDevice));
+    ATENIA_CUDA_TRY(cudaMemcpy(L->d_tm_down_r64, td6.data(), mb, cudaMemcpyHostToDevice));
   }
   ATENIA_CUDA_TRY(cudaMemcpy(L->d_p_gate, pg.data(), pb, cudaMemcpyHostToDevice));
   ATENIA_CUDA_TRY(cudaMemcpy(L->d_p_up, pu.data(), pb, cudaMemcpyHostToDevice));
@@ -529,7 +563,7 @@ static int forward_impl(AteniaMoeLayer* L, const void* x, int x_dtype, int T, vo
 
   if (c.ep_world == 1) {
     rc = run_expert_gemms(L, L->tm_x_perm, L->tm_h, L->x_perm, L->h, L->y_perm, L->expert_offsets,
-                          c.num_experts, n, s);
+                          c.num_experts, n, s, &L->tm_x_perm_r64, &L->tm_h_r64);
   } else if (L->ep_replicated) {
     rc = ep_forward_replicated(L, n, s);
   } else {
