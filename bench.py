@@ -427,6 +427,38 @@ def main():
     gemm1_ms = sum(g1) / len(g1)
     gemm2_ms = sum(g2) / len(g2)
 
+    # ---- end to end at N > 1: every rank copies its own tokens from pinned host memory, runs the
+    # expert-parallel forward and copies its result back; same forwards on every rank, max over ranks
+    e2e_multi = None
+    if args.gpus > 1:
+        hin = torch.empty((T, shape.d_model), dtype=torch.float32).pin_memory()
+        hin.copy_(x.float().cpu())
+        hout = torch.empty_like(hin).pin_memory()
+        xd = torch.empty((T, shape.d_model), dtype=torch.float32, device=dev)
+        od = torch.empty_like(xd)
+
+        def one_step():
+            xd.copy_(hin, non_blocking=True)
+            layer.forward(xd, out=od)
+            hout.copy_(od, non_blocking=True)
+
+        for _ in range(3):
+            one_step()
+        sync_all()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            one_step()
+        torch.cuda.synchronize()
+        dt = (time.perf_counter() - t0) / args.steps
+        layer.check()
+        t = torch.tensor([dt], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dt = float(t.item())
+        nfl = T * shape.d_model
+        e2e_multi = {"value": T * args.gpus / dt, "unit": UNIT, "h2d_bytes_per_step": nfl * 4 * args.gpus,
+                     "d2h_bytes_per_step": nfl * 4 * args.gpus, "ms_per_step": dt * 1e3,
+                     "api": "atenia_moe_forward per rank (expert parallel), pinned host f32 in/out on every rank"}
+
     if rank != 0:
         if dist is not None:
             dist.barrier()
@@ -454,7 +486,7 @@ def main():
                                                  (ms * 1e-3) / 1e12 / peaks["bf16_tflops"]}
 
     # ---- end to end through the operator registry with pinned host buffers (N = 1 only)
-    e2e = None
+    e2e = e2e_multi
     if args.gpus == 1:
         lid = ae.register_resident_moe_layer(layer)
         hin = torch.empty((T, shape.d_model), dtype=torch.float32).pin_memory()
