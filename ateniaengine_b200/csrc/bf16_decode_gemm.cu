@@ -1,0 +1,423 @@
+// Grouped expert GEMM for bf16 weights at decode sizes (groups of at most 128 rows), sm_100a.
+//
+// At a batch of a few tokens the work is streaming the touched experts' weights once; what decides
+// the speed is whether every SM streams the same number of bytes.  The 128-row-tile kernels of
+// grouped_gemm.cu give a batch of one token on a Mixtral layer 112 gate/up tiles and 64 down tiles for
+// 148 SMs.  This kernel cuts the flattened list of (tile, k-block) pairs into one contiguous span per
+// CTA ("stream-K", as w8_gemm.cu does for INT8): partial pieces leave raw f32 accumulators in a
+// two-slot-per-CTA workspace and bf16_splitk_reduce_kernel adds the pieces of a tile in CTA order
+// (deterministic) before the activation and the store.
+//
+// The contraction is computed transposed, D[f, t] = sum_k W[f, k] * X[t, k]: 128 weight rows are the
+// M side of the MMA, the token tile its N side, so the MMA width follows the row count (N = rows
+// rounded up to 16) and the per-lane epilogue handles one output feature.  Both operands come from
+// shared memory (bf16 tiles, 128B swizzle, by TMA).
+//
+//   tile      = up to 128 tokens of one expert x { 128 gate rows + 128 up rows (kSwiGLU) | 256 down rows (kPlain) }
+//   k-block   = 64: two 16 KiB weight tiles + one 16 KiB token tile per stage, 4 stages
+//   TMEM      = two buffers of two 128-column accumulators: the epilogue of a piece overlaps the
+//               main loop of the next
+//   warps     : 0 TMA, 1 MMA + TMEM alloc, 4..11 epilogue (two warps per TMEM lane quarter)
+// All waits are bounded as in grouped_gemm.cu.
+#include "tc_common.cuh"
+
+namespace atenia {
+namespace {
+using namespace tc;
+
+constexpr int DTN = 128;     // token tile (MMA N at most)
+constexpr int DROWS = 128;   // weight rows per A tile (MMA M)
+constexpr int D_STAGES = 4;
+constexpr int D_W_BYTES = DROWS * BK * 2;  // 16 KiB
+constexpr int D_X_BYTES = DTN * BK * 2;    // 16 KiB
+constexpr int D_STAGE_BYTES = 2 * D_W_BYTES + D_X_BYTES;  // 48 KiB
+constexpr int D_THREADS = 384;
+constexpr int D_SMEM_BYTES = D_STAGES * D_STAGE_BYTES + 1024 + 256;
+constexpr int D_TMEM_COLS = 512;
+constexpr int D_SLOT_FLOATS = 2 * DTN * DROWS;  // [accumulator][token][feature]
+static_assert(D_SLOT_FLOATS == (int)kW8SplitKSlotFloats, "the layer sizes one workspace for both stream-K kernels");
+
+struct __align__(8) BarriersDec {
+  uint64_t full[D_STAGES];   // TMA landed (1 arrival + bytes)
+  uint64_t empty[D_STAGES];  // the MMAs that read the stage are done (commit)
+  uint64_t acc_full[2];      // all MMAs of the piece done (commit)
+  uint64_t acc_empty[2];     // 8 epilogue warps drained the buffer
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+// Instruction descriptor: D f32, A = B = bf16, K-major, M = 128, N given at run time.
+__device__ __forceinline__ uint32_t idesc_dec(int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(n >> 3) << 17) | (uint32_t(DROWS >> 4) << 24);
+}
+
+// Work of one CTA: whole tiles dealt round-robin, or (stream-K) one contiguous span of the flattened
+// (tile, k-block) list.  A span has at most one partial piece at its start (slot 0) and one at its end
+// (slot 1).
+struct DecPieces {
+  bool splitk;
+  int num_kb, n_tiles, num_groups, bn_out;
+  const int32_t* off;
+  TileCursor cur;
+  int tile, stride;
+  long long g, g0, g_end;
+  TileCoord tc;
+  int kb0, nkb, slot;  // slot -1: the piece is a whole tile
+
+  __device__ void init(bool sk, int num_kb_, int n_tiles_, int num_groups_, int bn_out_, const int32_t* off_) {
+    splitk = sk;
+    num_kb = num_kb_;
+    n_tiles = n_tiles_;
+    num_groups = num_groups_;
+    bn_out = bn_out_;
+    off = off_;
+    cur.group = 0;
+    cur.base = 0;
+    if (num_groups > 0) cursor_load(cur, off);
+    tile = blockIdx.x;
+    stride = gridDim.x;
+    g = g0 = g_end = 0;
+    if (splitk) {
+      long long total_tiles = 0;
+      for (int gi = 0; gi < num_groups; ++gi)
+        total_tiles += (long long)((off[gi + 1] - off[gi] + BM - 1) / BM) * n_tiles;
+      const long long total = total_tiles * num_kb;
+      const long long span = (total + gridDim.x - 1) / gridDim.x;
+      g0 = g = (long long)blockIdx.x * span;
+      g_end = g0 + span < total ? g0 + span : total;
+    }
+  }
+  __device__ bool next() {
+    if (num_groups <= 0) return false;
+    if (!splitk) {
+      if (!cursor_seek(cur, tile, n_tiles, num_groups, off, tc, bn_out)) return false;
+      tile += stride;
+      kb0 = 0;
+      nkb = num_kb;
+      slot = -1;
+      return true;
+    }
+    if (g >= g_end) return false;
+    const int t = (int)(g / num_kb);
+    kb0 = (int)(g - (long long)t * num_kb);
+    const long long left = g_end - g;
+    nkb = (num_kb - kb0) < left ? (num_kb - kb0) : (int)left;
+    if (!cursor_seek(cur, t, n_tiles, num_groups, off, tc, bn_out)) return false;
+    slot = (nkb == num_kb) ? -1 : (g == g0 ? 0 : 1);
+    g += nkb;
+    return true;
+  }
+  __device__ int rows() const {
+    const int r = tc.row_end - tc.row0;
+    return r > DTN ? DTN : r;
+  }
+};
+
+template <int MODE>
+__global__ void __launch_bounds__(D_THREADS, 1)
+grouped_gemm_bf16_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const CUtensorMap* __restrict__ tmap_w0,
+                                const CUtensorMap* __restrict__ tmap_w1, const int32_t* __restrict__ group_offsets,
+                                int num_groups, int N, int K, __nv_bfloat16* __restrict__ out, DeviceError* err,
+                                int splitk, float* __restrict__ ws) {
+  extern __shared__ uint8_t smem_raw[];
+  constexpr int BN_OUT = (MODE == kSwiGLU) ? DROWS : 2 * DROWS;
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
+  BarriersDec* bars = reinterpret_cast<BarriersDec*>(smem_aligned + D_STAGES * D_STAGE_BYTES);
+  volatile int* abort_flag = &bars->abort_flag;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_kb = (K + BK - 1) / BK;
+  const int n_tiles = (N + BN_OUT - 1) / BN_OUT;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < D_STAGES; ++s) {
+      mbar_init(smem_u32(&bars->full[s]), 1);
+      mbar_init(smem_u32(&bars->empty[s]), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&bars->acc_full[b]), 1);
+      mbar_init(smem_u32(&bars->acc_empty[b]), 8);
+    }
+    bars->abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(&bars->tmem_base)),
+                 "r"(D_TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  DecPieces it;
+  it.init(splitk != 0, num_kb, n_tiles, num_groups, BN_OUT, group_offsets);
+  const TileCoord& tc = it.tc;
+
+  if (warp == 0) {
+    // ================= TMA producer =================
+    if (lane == 0) {
+      uint32_t idx = 0;
+      int last_group = -1;
+      uint32_t armed = 0;
+      bool ok = true;
+      while (ok && it.next()) {
+        if (tc.group != last_group) {
+          tmap_acquire(&tmap_w0[tc.group]);
+          if (MODE == kSwiGLU) tmap_acquire(&tmap_w1[tc.group]);
+          last_group = tc.group;
+        }
+        const CUtensorMap* m0 = &tmap_w0[tc.group];
+        const CUtensorMap* m1 = (MODE == kSwiGLU) ? &tmap_w1[tc.group] : m0;
+        const int n1 = (MODE == kSwiGLU) ? tc.n0 : tc.n0 + DROWS;
+        for (int kb = it.kb0; kb < it.kb0 + it.nkb; ++kb, ++idx) {
+          const int stage = idx % D_STAGES;
+          const uint32_t phase = (idx / D_STAGES) & 1u;
+          if (!mbar_wait(smem_u32(&bars->empty[stage]), phase ^ 1u, abort_flag)) {
+            report_error(err, ATENIA_ERR_DEVICE_TIMEOUT, 2600 + stage);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          const uint32_t full = smem_u32(&bars->full[stage]);
+          const uint32_t sw = smem_base + stage * D_STAGE_BYTES;
+          mbar_expect_tx(full, D_STAGE_BYTES);
+          tma_load_2d(sw, m0, full, kb * BK, tc.n0);
+          tma_load_2d(sw + D_W_BYTES, m1, full, kb * BK, n1);
+          tma_load_2d(sw + 2 * D_W_BYTES, &tmap_x, full, kb * BK, tc.row0);
+          armed |= 1u << stage;
+        }
+      }
+      if (*abort_flag) {
+        const int stage = idx % D_STAGES;
+        const uint32_t phase = (idx / D_STAGES) & 1u;
+        for (int s = 0; s < D_STAGES; ++s) {
+          if (!(armed & (1u << s))) continue;
+          const uint32_t par = (s < stage) ? phase : (phase ^ 1u);
+          for (uint32_t i = 0; i < (1u << 20); ++i)
+            if (mbar_try_wait(smem_u32(&bars->full[s]), par)) break;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ================= MMA issuer =================
+    if (lane == 0) {
+      uint32_t idx = 0;
+      int acc = 0;
+      uint32_t acc_phase[2] = {0, 0};
+      bool ok = true;
+      while (ok && it.next()) {
+        if (!mbar_wait(smem_u32(&bars->acc_empty[acc]), acc_phase[acc] ^ 1u, abort_flag)) {
+          report_error(err, ATENIA_ERR_DEVICE_TIMEOUT, 2700 + acc);
+          *abort_flag = 1;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t idesc = idesc_dec((it.rows() + 15) & ~15);
+        const uint32_t d0 = tmem_base + acc * 2 * DTN, d1 = d0 + DTN;
+        for (int kb = it.kb0; kb < it.kb0 + it.nkb; ++kb, ++idx) {
+          const int stage = idx % D_STAGES;
+          const uint32_t phase = (idx / D_STAGES) & 1u;
+          if (!mbar_wait(smem_u32(&bars->full[stage]), phase, abort_flag)) {
+            report_error(err, ATENIA_ERR_DEVICE_TIMEOUT, 2710 + stage);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sw = smem_base + stage * D_STAGE_BYTES;
+          const uint64_t da0 = make_smem_desc(sw), da1 = make_smem_desc(sw + D_W_BYTES);
+          const uint64_t db = make_smem_desc(sw + 2 * D_W_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint32_t accum = (kb > it.kb0 || k > 0) ? 1u : 0u;
+            // 16 bf16 of K = 32 bytes along a swizzled row = 2 in descriptor address units
+            tc_mma_bf16(d0, da0 + 2 * k, db + 2 * k, idesc, accum);
+            tc_mma_bf16(d1, da1 + 2 * k, db + 2 * k, idesc, accum);
+          }
+          tc_commit(smem_u32(&bars->empty[stage]));
+        }
+        if (ok) tc_commit(smem_u32(&bars->acc_full[acc]));
+        acc_phase[acc] ^= 1u;
+        acc ^= 1;
+      }
+    }
+  } else if (warp >= 4) {
+    // ================= epilogue =================
+    // Lane f of the two accumulators is output feature n0 + f (first weight tile) / the matching row
+    // of the second tile; column t is token row0 + t.  For a fixed token the 32 lanes of a warp write
+    // 64 contiguous bytes.
+    const int quarter = warp & 3;
+    const int f = quarter * 32 + lane;
+    const int half = (warp - 4) >> 2;  // which of the two warps of this lane quarter
+    int acc = 0;
+    uint32_t acc_phase[2] = {0, 0};
+    while (it.next()) {
+      if (!mbar_wait(smem_u32(&bars->acc_full[acc]), acc_phase[acc], abort_flag)) {
+        if (lane == 0) report_error(err, ATENIA_ERR_DEVICE_TIMEOUT, 2900 + acc);
+        *abort_flag = 1;
+        break;
+      }
+      acc_phase[acc] ^= 1u;
+      tc_fence_after();
+      const int rows = it.rows();
+      const uint32_t t0 = tmem_base + (uint32_t(quarter * 32) << 16) + acc * 2 * DTN, t1 = t0 + DTN;
+      if (it.slot >= 0) {
+        // partial piece: raw accumulators to this CTA's workspace slot, [accumulator][token][feature]
+        float* slot = ws + ((size_t)blockIdx.x * 2 + it.slot) * D_SLOT_FLOATS;
+#pragma unroll 1
+        for (int c = half * 16; c < rows; c += 32) {
+          uint32_t a[16], b[16];
+          tc_ld16(t0 + c, a);
+          tc_ld16(t1 + c, b);
+          tc_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            if (c + j < rows) {
+              slot[(size_t)(c + j) * DROWS + f] = __uint_as_float(a[j]);
+              slot[(size_t)(DTN + c + j) * DROWS + f] = __uint_as_float(b[j]);
+            }
+          }
+        }
+      } else if (MODE == kSwiGLU) {
+        const int n = tc.n0 + f;
+        const bool n_ok = n < N;
+        __nv_bfloat16* obase = out + (size_t)tc.row0 * N + n;
+#pragma unroll 1
+        for (int c = half * 16; c < rows; c += 32) {
+          uint32_t g[16], u[16];
+          tc_ld16(t0 + c, g);
+          tc_ld16(t1 + c, u);
+          tc_ld_wait();
+          if (n_ok) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              if (c + j < rows)
+                obase[(size_t)(c + j) * N] = __float2bfloat16(silu_mul(__uint_as_float(g[j]), __uint_as_float(u[j])));
+          }
+        }
+      } else {
+        const int n_lo = tc.n0 + f, n_hi = tc.n0 + DROWS + f;
+        const bool lo_ok = n_lo < N, hi_ok = n_hi < N;
+        __nv_bfloat16* obase = out + (size_t)tc.row0 * N;
+#pragma unroll 1
+        for (int c = half * 16; c < rows; c += 32) {
+          uint32_t a[16], b[16];
+          tc_ld16(t0 + c, a);
+          tc_ld16(t1 + c, b);
+          tc_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            if (c + j < rows) {
+              if (lo_ok) obase[(size_t)(c + j) * N + n_lo] = __float2bfloat16(__uint_as_float(a[j]));
+              if (hi_ok) obase[(size_t)(c + j) * N + n_hi] = __float2bfloat16(__uint_as_float(b[j]));
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bars->acc_empty[acc]));
+      acc ^= 1;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(D_TMEM_COLS)
+                 : "memory");
+  }
+}
+
+// Adds the partial pieces of every tile that stream-K cut across CTAs, in CTA order, then applies the
+// main kernel's activation and store.  One block per tile, one thread per weight row (feature).
+template <int MODE>
+__global__ void __launch_bounds__(DROWS) bf16_splitk_reduce_kernel(const int32_t* __restrict__ group_offsets,
+                                                                    int num_groups, int N, int K,
+                                                                    __nv_bfloat16* __restrict__ out,
+                                                                    const float* __restrict__ ws, int num_ctas) {
+  constexpr int BN_OUT = (MODE == kSwiGLU) ? DROWS : 2 * DROWS;
+  const int num_kb = (K + BK - 1) / BK;
+  const int n_tiles = (N + BN_OUT - 1) / BN_OUT;
+  long long total_tiles = 0;
+  for (int gi = 0; gi < num_groups; ++gi)
+    total_tiles += (long long)((group_offsets[gi + 1] - group_offsets[gi] + BM - 1) / BM) * n_tiles;
+  const long long t = blockIdx.x;
+  if (t >= total_tiles) return;
+  const long long total = total_tiles * num_kb;
+  const long long span = (total + num_ctas - 1) / num_ctas;
+  const int c0 = (int)((t * num_kb) / span), c1 = (int)(((t + 1) * num_kb - 1) / span);
+  if (c0 == c1) return;  // the tile was computed whole by one CTA
+  TileCursor cur;
+  cur.group = 0;
+  cur.base = 0;
+  cursor_load(cur, group_offsets);
+  TileCoord tc;
+  if (!cursor_seek(cur, (int)t, n_tiles, num_groups, group_offsets, tc, BN_OUT)) return;
+  const int f = threadIdx.x;
+  int rows = tc.row_end - tc.row0;
+  if (rows > DTN) rows = DTN;
+  const int n_lo = tc.n0 + f, n_hi = tc.n0 + DROWS + f;
+  const bool ok_a = n_lo < N, ok_b = (MODE == kSwiGLU) ? ok_a : n_hi < N;
+  for (int tok = 0; tok < rows; ++tok) {
+    float a = 0.f, b = 0.f;
+    for (int c = c0; c <= c1; ++c) {
+      const int slot = (t == ((long long)c * span) / num_kb) ? 0 : 1;
+      const float* p = ws + ((size_t)c * 2 + slot) * D_SLOT_FLOATS;
+      a += p[(size_t)tok * DROWS + f];
+      b += p[(size_t)(DTN + tok) * DROWS + f];
+    }
+    __nv_bfloat16* orow = out + (size_t)(tc.row0 + tok) * N;
+    if (MODE == kSwiGLU) {
+      if (ok_a) orow[n_lo] = __float2bfloat16(silu_mul(a, b));
+    } else {
+      if (ok_a) orow[n_lo] = __float2bfloat16(a);
+      if (ok_b) orow[n_hi] = __float2bfloat16(b);
+    }
+  }
+}
+
+template <int MODE>
+int launch_dec_one(const GroupedGemmArgs& a, int num_sms, cudaStream_t s) {
+  static bool attr_set[kMaxDevices] = {};
+  if (first_use_on_current_device(attr_set)) {
+    ATENIA_CUDA_TRY(cudaFuncSetAttribute(grouped_gemm_bf16_decode_kernel<MODE>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, D_SMEM_BYTES));
+  }
+  // stream-K where every group fits one token tile (one workspace slot holds 128 tokens) and the
+  // tiles that can exist are too few to balance the SMs
+  constexpr int BN_OUT = (MODE == kSwiGLU) ? DROWS : 2 * DROWS;
+  const int n_tiles = (a.N + BN_OUT - 1) / BN_OUT;
+  const int active_groups = a.max_rows < a.num_groups ? a.max_rows : a.num_groups;
+  const bool splitk = a.splitk_ws != nullptr && a.max_rows <= DTN && active_groups * n_tiles < 4 * num_sms;
+  grouped_gemm_bf16_decode_kernel<MODE><<<dim3(num_sms), dim3(D_THREADS), D_SMEM_BYTES, s>>>(
+      a.tmap_a, a.tmap_b0, MODE == kSwiGLU ? a.tmap_b1 : a.tmap_b0, a.group_offsets, a.num_groups, a.N, a.K, a.out,
+      a.err, splitk ? 1 : 0, a.splitk_ws);
+  int rc = (int)cudaGetLastError();
+  if (rc || !splitk) return rc;
+  const int max_tiles = a.num_groups * n_tiles;  // every group has at most one token tile here
+  bf16_splitk_reduce_kernel<MODE><<<dim3(max_tiles), dim3(DROWS), 0, s>>>(a.group_offsets, a.num_groups, a.N, a.K, a.out,
+                                                                          a.splitk_ws, num_sms);
+  count_launch();
+  return (int)cudaGetLastError();
+}
+
+}  // namespace
+
+int launch_grouped_gemm_bf16_decode(const GroupedGemmArgs& a, int num_sms, cudaStream_t s) {
+  if (a.num_groups <= 0) return ATENIA_OK;
+  if (a.N % 16 != 0 || a.K % 16 != 0) return ATENIA_ERR_SHAPE;
+  int rc = a.mode == kSwiGLU ? launch_dec_one<kSwiGLU>(a, num_sms, s) : launch_dec_one<kPlain>(a, num_sms, s);
+  count_launch();
+  count_tcgen05_launch();
+  return rc;
+}
+
+}  // namespace atenia

@@ -168,6 +168,10 @@ constexpr size_t kW8SplitKSlotFloats = 2 * 128 * 128;  // per CTA: two slots of 
 // tmap_a is the bf16 token matrix with box {64, 64} (128B swizzle); tmap_b0/b1 are int8 maps with box
 // {64, 64} and the 64-byte swizzle.
 int launch_grouped_gemm_w8_wide(const GroupedGemmArgs& a, int num_sms, cudaStream_t s);
+// bf16 weights, groups of at most 128 rows (bf16_decode_gemm.cu): transposed product with stream-K over
+// the SMs; tmap_a / tmap_b0 / tmap_b1 are the maps of launch_grouped_gemm_tcgen05, splitk_ws as for
+// the INT8 tensor-memory kernel (null: whole tiles only).
+int launch_grouped_gemm_bf16_decode(const GroupedGemmArgs& a, int num_sms, cudaStream_t s);
 // bf16 weights, CTA pairs (tcgen05 cta_group::2): 256-row tiles, each CTA stages half of the weight tile
 int launch_grouped_gemm_2cta(const GroupedGemmArgs& a, int num_sms, cudaStream_t s);
 

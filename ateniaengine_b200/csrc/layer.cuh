@@ -27,6 +27,8 @@ struct AteniaMoeLayer {
   // bf16: 0 = pick per call (CTA-pair kernel once groups average >= 512 rows), 1 = always pairs,
   // 2 = always the single-CTA kernel
   int pair_mode = 0;
+  // bf16, on request (ATENIA_MOE_BF16_DECODE=1): the stream-K decode kernel when a call has <= 128 rows
+  bool bf16_decode = false;
 
   // weights (device)
   float* d_router = nullptr;    // [E, d]

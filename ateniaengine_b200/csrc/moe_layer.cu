@@ -60,7 +60,9 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
   const bool tmem = q && !wide && (L->w8_mode == 1 || ((L->w8_mode == 0 || L->w8_mode == 3) && !large));
   // bf16: 256-row CTA-pair tiles pay off once an average group fills a few of them
   // (INT8 has a pair kernel too, but it measures slower than the single-CTA one: only on request.)
-  const bool pairs = !tmem && !wide && (L->pair_mode == 1 || (L->pair_mode == 0 && !q && max_rows >= 512 * num_groups));
+  // bf16, on request: the stream-K decode kernel while the whole call fits one token tile per group
+  const bool dec = !q && L->bf16_decode && max_rows <= 128 && !L->use_check_gemm;
+  const bool pairs = !tmem && !wide && !dec && (L->pair_mode == 1 || (L->pair_mode == 0 && !q && max_rows >= 512 * num_groups));
   if (L->timing) cudaEventRecord(L->ev[0], s);
   if (L->use_check_gemm) {
     GroupedGemmCheckArgs k1{a_ptr, L->d_p_gate, L->d_p_up, q ? 1 : 0, q ? L->d_sc_gate : nullptr,
@@ -86,6 +88,7 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
     g1.w8 = q;
     g1.splitk_ws = L->splitk_ws;
     int rc = wide ? launch_grouped_gemm_w8_wide(g1, L->num_sms, s)
+                  : dec ? launch_grouped_gemm_bf16_decode(g1, L->num_sms, s)
                   : tmem ? launch_grouped_gemm_w8_tmem(g1, L->num_sms, s)
                          : pairs ? launch_grouped_gemm_2cta(g1, L->num_sms, s)
                                  : launch_grouped_gemm_tcgen05(g1, L->num_sms, s);
@@ -115,6 +118,7 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
     g2.w8 = q;
     g2.splitk_ws = L->splitk_ws;
     int rc = wide ? launch_grouped_gemm_w8_wide(g2, L->num_sms, s)
+                  : dec ? launch_grouped_gemm_bf16_decode(g2, L->num_sms, s)
                   : tmem ? launch_grouped_gemm_w8_tmem(g2, L->num_sms, s)
                          : pairs ? launch_grouped_gemm_2cta(g2, L->num_sms, s)
                                  : launch_grouped_gemm_tcgen05(g2, L->num_sms, s);
@@ -223,6 +227,8 @@ int atenia_moe_create(const AteniaMoeConfig* cfg, AteniaMoeLayer** out) {
   L->use_check_gemm = std::getenv("ATENIA_MOE_CHECK_GEMM") && std::atoi(std::getenv("ATENIA_MOE_CHECK_GEMM")) != 0;
   L->w8_mode = std::getenv("ATENIA_MOE_W8_MODE") ? std::atoi(std::getenv("ATENIA_MOE_W8_MODE")) : 0;
   L->pair_mode = std::getenv("ATENIA_MOE_PAIR_MODE") ? std::atoi(std::getenv("ATENIA_MOE_PAIR_MODE")) : 0;
+  L->bf16_decode = c.weight_dtype == ATENIA_W_BF16 && std::getenv("ATENIA_MOE_BF16_DECODE") &&
+                   std::atoi(std::getenv("ATENIA_MOE_BF16_DECODE")) != 0;
   const size_t Tm = (size_t)c.max_tokens, k = (size_t)c.experts_per_token, E = (size_t)c.num_experts;
   const size_t d = (size_t)c.d_model, F = (size_t)c.d_ff, Fs = (size_t)c.shared_d_ff;
   const size_t R = Tm * k;
@@ -265,6 +271,7 @@ int atenia_moe_create(const AteniaMoeConfig* cfg, AteniaMoeLayer** out) {
   TRY_ALLOC(L->d_tm_up, (size_t)L->n_groups);
   TRY_ALLOC(L->d_tm_down, (size_t)L->n_groups);
   TRY_ALLOC(L->d_tm_shared, 3);
+  if (L->bf16_decode) TRY_ALLOC(L->splitk_ws, (size_t)L->num_sms * 2 * kW8SplitKSlotFloats);
   if (c.weight_dtype == ATENIA_W_INT8_ROW) {
     TRY_ALLOC(L->splitk_ws, (size_t)L->num_sms * 2 * kW8SplitKSlotFloats);
     TRY_ALLOC(L->d_tm_gate_sw, (size_t)L->n_groups);
