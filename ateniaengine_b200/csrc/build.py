@@ -5,7 +5,7 @@ import sys
 from concurrent.futures import ThreadPoolExecutor
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-SOURCES = ["grouped_gemm.cu", "w8_gemm.cu", "w8_gemm_wide.cu", "bf16_decode_gemm.cu", "grouped_gemm_2cta.cu", "router.cu", "dispatch.cu", "combine.cu", "moe_layer.cu", "ep.cu", "registry.cu", "noalloc.cu", "stack.cu", "tier.cu", "dense_int8.cu"]
+SOURCES = ["grouped_gemm.cu", "w8_gemm.cu", "w8_gemm_wide.cu", "bf16_decode_gemm.cu", "grouped_gemm_2cta.cu", "router.cu", "router_dmma.cu", "dispatch.cu", "combine.cu", "moe_layer.cu", "ep.cu", "registry.cu", "noalloc.cu", "stack.cu", "tier.cu", "dense_int8.cu"]
 LIB = os.path.join(HERE, "libatenia_moe.so")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-ccbin", "g++",
@@ -20,7 +20,7 @@ def _stale(out, deps):
 
 
 def build(force=False, verbose=False):
-    headers = [os.path.join(HERE, h) for h in ("common.cuh", "layer.cuh", "tc_common.cuh", "v3_route.cuh")] + [
+    headers = [os.path.join(HERE, h) for h in ("common.cuh", "layer.cuh", "tc_common.cuh", "v3_route.cuh", "route_warp.cuh")] + [
         os.path.join(HERE, "..", "..", "include", "atenia_moe.h")]
     objs = []
     jobs = []

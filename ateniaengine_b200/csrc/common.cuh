@@ -64,8 +64,10 @@ struct RouterArgs {
   float* gate_scale;   // [T] or null
   float* logits;       // [T, E] or null
   DeviceError* err;
+  int variant;         // 0: CUDA-core f64 kernel (router.cu); 1: f64 tensor-core kernel (router_dmma.cu)
 };
 int launch_router(const RouterArgs& a, cudaStream_t s);
+int launch_router_dmma(const RouterArgs& a, cudaStream_t s);  // same contract, E <= 128, k <= 8
 int launch_route_from_logits(const float* logits, int T, int E, int k, int renormalize,
                              int32_t* topk_idx, float* topk_w, DeviceError* err, cudaStream_t s);
 

@@ -29,6 +29,8 @@ struct AteniaMoeLayer {
   int pair_mode = 0;
   // bf16, on request (ATENIA_MOE_BF16_DECODE=1): the stream-K decode kernel when a call has <= 128 rows
   bool bf16_decode = false;
+  // on request (ATENIA_MOE_ROUTER_DMMA=1): router logits on the f64 tensor cores (router_dmma.cu)
+  int router_variant = 0;
 
   // weights (device)
   float* d_router = nullptr;    // [E, d]

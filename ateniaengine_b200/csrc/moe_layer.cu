@@ -227,6 +227,7 @@ int atenia_moe_create(const AteniaMoeConfig* cfg, AteniaMoeLayer** out) {
   L->use_check_gemm = std::getenv("ATENIA_MOE_CHECK_GEMM") && std::atoi(std::getenv("ATENIA_MOE_CHECK_GEMM")) != 0;
   L->w8_mode = std::getenv("ATENIA_MOE_W8_MODE") ? std::atoi(std::getenv("ATENIA_MOE_W8_MODE")) : 0;
   L->pair_mode = std::getenv("ATENIA_MOE_PAIR_MODE") ? std::atoi(std::getenv("ATENIA_MOE_PAIR_MODE")) : 0;
+  L->router_variant = (std::getenv("ATENIA_MOE_ROUTER_DMMA") && std::atoi(std::getenv("ATENIA_MOE_ROUTER_DMMA")) != 0) ? 1 : 0;
   L->bf16_decode = c.weight_dtype == ATENIA_W_BF16 && std::getenv("ATENIA_MOE_BF16_DECODE") &&
                    std::atoi(std::getenv("ATENIA_MOE_BF16_DECODE")) != 0;
   const size_t Tm = (size_t)c.max_tokens, k = (size_t)c.experts_per_token, E = (size_t)c.num_experts;
@@ -535,6 +536,7 @@ static int forward_impl(AteniaMoeLayer* L, const void* x, int x_dtype, int T, vo
   const bool v3 = c.router_mode == ATENIA_ROUTER_V3;
   ra.logits = (aux && aux->logits) ? aux->logits : (v3 ? L->logits_ws : nullptr);
   ra.err = L->d_err;
+  ra.variant = L->router_variant;
   int rc = launch_router(ra, s);
   if (rc) return rc;
   if (v3) {

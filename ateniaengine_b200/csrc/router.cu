@@ -8,12 +8,11 @@
 // reference's router matvec (src/moe/dense.rs:97-115, :333), so they round to the same f32 except
 // when the f64 sums differ in their last bits across summation orders.
 #include "common.cuh"
+#include "route_warp.cuh"
 #include "v3_route.cuh"
 
 namespace atenia {
 namespace {
-
-constexpr int kMaxK = 8;
 
 // softmax + top-k for one token, executed by one thread.  `lg` holds E f32 logits (stride 1).
 // Writes k ascending indices and weights.  Returns 0 or a negative status.  `probs` (E floats) may
@@ -63,98 +62,6 @@ __device__ int route_one(const float* lg, int E, int k, int renormalize, int32_t
   if (!(ssum > 0.0)) return ATENIA_ERR_ROUTING;
   double scale = renormalize ? 1.0 / ssum : 1.0;
   for (int s = 0; s < k; ++s) w_out[s] = (float)((double)probs[idx_out[s]] * scale);
-  return 0;
-}
-
-// Softmax + top-k for one token by one warp.  `lg` holds E f32 logits in shared memory.
-// Follows the reference's sequence: f32 maximum, exp((f64)(v - max)) with the subtraction in f32,
-// the f64 sum accumulated in ascending expert order by one lane, f32 weights, then k rounds of
-// "largest weight, lowest index" and a renormalisation summed in ascending index order.
-template <int EPL>
-__device__ __forceinline__ int route_one_warp(const float* lg, int E, int k, int renormalize, int lane,
-                                              int32_t* idx_out, float* w_out, double* exps /* smem, E */) {
-  float mx = -INFINITY;
-  bool finite = true;
-#pragma unroll
-  for (int j = 0; j < EPL; ++j) {
-    int e = lane + 32 * j;
-    if (e < E) {
-      float v = lg[e];
-      if (!isfinite(v)) finite = false;
-      mx = fmaxf(mx, v);
-    }
-  }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-  if (__any_sync(0xffffffffu, !finite)) return ATENIA_ERR_ROUTING;
-  double ex[EPL];
-#pragma unroll
-  for (int j = 0; j < EPL; ++j) {
-    int e = lane + 32 * j;
-    ex[j] = 0.0;
-    if (e < E) {
-      ex[j] = exp((double)__fsub_rn(lg[e], mx));
-      exps[e] = ex[j];
-    }
-  }
-  __syncwarp();
-  double sum = 0.0;
-  if (lane == 0)
-    for (int e = 0; e < E; ++e) sum += exps[e];
-  sum = __shfl_sync(0xffffffffu, sum, 0);
-  const double inv = sum > 0.0 ? 1.0 / sum : 0.0;
-  float p[EPL];
-  bool taken[EPL];
-#pragma unroll
-  for (int j = 0; j < EPL; ++j) {
-    p[j] = (float)(ex[j] * inv);
-    taken[j] = (lane + 32 * j) >= E;  // slots past E never compete
-  }
-  for (int s = 0; s < k; ++s) {
-    float bw = -1.0f;  // weights are >= 0
-    int bi = 0x7fffffff;
-#pragma unroll
-    for (int j = 0; j < EPL; ++j) {
-      if (!taken[j] && p[j] > bw) {  // ascending j = ascending index: strict > keeps the lower one
-        bw = p[j];
-        bi = lane + 32 * j;
-      }
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      float ow = __shfl_xor_sync(0xffffffffu, bw, o);
-      int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-      if (ow > bw || (ow == bw && oi < bi)) {
-        bw = ow;
-        bi = oi;
-      }
-    }
-#pragma unroll
-    for (int j = 0; j < EPL; ++j)
-      if (lane + 32 * j == bi) taken[j] = true;
-  }
-  // selected experts in ascending order: rank of each selected slot among the selected
-  int m_before = 0;
-  double ssum = 0.0;
-#pragma unroll
-  for (int j = 0; j < EPL; ++j) {
-    bool sel = taken[j] && (lane + 32 * j) < E;
-    unsigned mask = __ballot_sync(0xffffffffu, sel);
-    int rank = m_before + __popc(mask & ((1u << lane) - 1u));
-    if (sel) {
-      idx_out[rank] = lane + 32 * j;
-      exps[rank] = (double)p[j];  // reuse as the selected-weight list (ascending index)
-    }
-    m_before += __popc(mask);
-  }
-  __syncwarp();
-  if (lane == 0)
-    for (int s = 0; s < k; ++s) ssum += exps[s];
-  ssum = __shfl_sync(0xffffffffu, ssum, 0);
-  if (!(ssum > 0.0)) return ATENIA_ERR_ROUTING;
-  const double scale = renormalize ? 1.0 / ssum : 1.0;
-  if (lane < k) w_out[lane] = (float)(exps[lane] * scale);
-  __syncwarp();
   return 0;
 }
 
@@ -444,6 +351,7 @@ int launch_v3_route(const float* logits, const float* e_score_bias, int T, int E
 int launch_router(const RouterArgs& a, cudaStream_t s) {
   if (a.T <= 0) return ATENIA_OK;
   if (a.k > kMaxK || a.E > 128) return ATENIA_ERR_UNSUPPORTED;
+  if (a.variant == 1) return launch_router_dmma(a, s);
   dim3 block(kRWarps * 32);
   // more tokens per CTA for many experts: the router matrix is re-read once per CTA
   if (a.E <= 8) router_kernel<8, 8><<<(a.T + 7) / 8, block, 0, s>>>(a);

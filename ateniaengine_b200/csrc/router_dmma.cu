@@ -1,0 +1,235 @@
+// Router on the f64 tensor cores: logits[t, e] = sum_c W[e, c] * x[t, c] as an m8n8k4 DMMA product,
+// then the same softmax + top-k as router.cu.
+//
+// The reference accumulates the router matvec in f64 (src/moe/dense.rs:97-115, :333) and rounds the
+// sum to f32.  router.cu does that with scalar f64 multiply-adds and is bound by the FP64 pipe of
+// the CUDA cores; for 64 experts it is a fifth of a DeepSeek-shaped forward.  Here the same f64
+// products go through mma.sync.m8n8k4.f64 (there is no tcgen05 form for f64): inputs are the exact
+// f64 values of the bf16 / f32 operands, accumulation is f64, only the order of the additions
+// differs from the serial loop (last bits of a 53-bit sum, far below the rounding to f32).
+//
+// One CTA (8 warps) handles 32 tokens:
+//   * per chunk of 32 values of k the CTA stages x[32, 32] and W_router[E, 32] as f64 in shared memory
+//     (row pitch 36 doubles: the 8 rows x 4 columns a fragment load touches fall in distinct banks);
+//     global loads of the next chunk are in flight during the arithmetic of the current one;
+//   * warps are arranged NW_N x NW_K: a warp owns NTW 8-expert tiles for all four 8-token tiles and
+//     every NW_K-th k-step of the chunk; its accumulators are 4 x NTW x 2 doubles per lane;
+//   * the k-slices are folded through shared memory in warp order (fixed), the bias joins the f64
+//     sum, logits are rounded to f32 and each warp routes four tokens (route_one_warp).
+#include "route_warp.cuh"
+
+namespace atenia {
+namespace {
+
+constexpr int kDW = 8;         // warps per CTA
+constexpr int kDTok = 32;      // tokens per CTA
+constexpr int kDKC = 32;       // k values per chunk
+constexpr int kDLD = kDKC + 4; // shared-memory row pitch in doubles
+
+template <int E_T>
+struct DmmaCfg {
+  static constexpr int NT = E_T / 8;               // 8-expert tiles
+  static constexpr int NW_N = NT < kDW ? NT : kDW; // warps across expert tiles
+  static constexpr int NW_K = kDW / NW_N;          // warps across k-steps
+  static constexpr int NTW = NT / NW_N;            // expert tiles per warp
+  static constexpr int kXs = kDTok * kDLD * 8;
+  static constexpr int kWs = E_T * kDLD * 8;
+  static constexpr int kLoop = kXs + kWs;
+  static constexpr int kAcc = kDTok * (E_T + 1) * 8;
+  static constexpr int kLg = kDTok * E_T * 4;
+  static constexpr int kExps = kDW * E_T * 8;
+  static constexpr int kGate = kDW * kDTok * 8;
+  static constexpr int kSel = kDTok * kMaxK * 8;
+  static constexpr int kTail = kAcc + kLg + kExps + kGate + kSel;
+  static constexpr int kBytes = kLoop > kTail ? kLoop : kTail;
+};
+
+// D[8x8] += A[8x4] * B[4x8].  Lane l holds A[l / 4][l % 4], B[l % 4][l / 4] and D[l / 4][2 (l % 4) + {0, 1}].
+__device__ __forceinline__ void dmma884(double (&c)[2], double a, double b) {
+  asm volatile("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0, %1}, {%2}, {%3}, {%0, %1};"
+               : "+d"(c[0]), "+d"(c[1])
+               : "d"(a), "d"(b));
+}
+
+template <int E_T>
+__global__ void __launch_bounds__(kDW * 32) router_dmma_kernel(RouterArgs a) {
+  using C = DmmaCfg<E_T>;
+  constexpr int NTW = C::NTW;
+  extern __shared__ __align__(16) unsigned char smem[];
+  // main-loop view
+  double (*xs)[kDLD] = reinterpret_cast<double (*)[kDLD]>(smem);
+  double (*ws)[kDLD] = reinterpret_cast<double (*)[kDLD]>(smem + C::kXs);
+  // tail view (after the last __syncthreads of the loop)
+  double (*acc_s)[E_T + 1] = reinterpret_cast<double (*)[E_T + 1]>(smem);
+  float (*lg_s)[E_T] = reinterpret_cast<float (*)[E_T]>(smem + C::kAcc);
+  double (*exps_s)[E_T] = reinterpret_cast<double (*)[E_T]>(smem + C::kAcc + C::kLg);
+  double (*gate_s)[kDTok] = reinterpret_cast<double (*)[kDTok]>(smem + C::kAcc + C::kLg + C::kExps);
+  int32_t (*idx_s)[kMaxK] = reinterpret_cast<int32_t (*)[kMaxK]>(smem + C::kAcc + C::kLg + C::kExps + C::kGate);
+  float (*w_s)[kMaxK] = reinterpret_cast<float (*)[kMaxK]>(smem + C::kAcc + C::kLg + C::kExps + C::kGate +
+                                                          kDTok * kMaxK * 4);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t0 = blockIdx.x * kDTok;
+  const int d = a.d, E = a.E;
+  const int ngrp = warp % C::NW_N, kslice = warp / C::NW_N;
+  const int frow = lane >> 2, fcol = lane & 3;
+
+  double acc[4][NTW][2];
+#pragma unroll
+  for (int mt = 0; mt < 4; ++mt)
+#pragma unroll
+    for (int j = 0; j < NTW; ++j) acc[mt][j][0] = acc[mt][j][1] = 0.0;
+  double gacc = 0.0;  // lane t of warp w: gate dot product of token t over the k values 4w..4w+3 of each chunk
+
+  // staging: thread i moves four consecutive k values of token i / 8 (x) and of expert rows
+  // i / 8 + 32 r (W); eight neighbouring threads cover 32 consecutive k of one row
+  constexpr int WV = (E_T + 31) / 32;
+  const int s_row = threadIdx.x >> 3, s_k = (threadIdx.x & 7) * 4;
+  uint4 xq;
+  float4 wq[WV];
+  auto fetch = [&](int k0) {
+    const int kk = k0 + s_k, tg = t0 + s_row;
+    xq = make_uint4(0, 0, 0, 0);
+    if (tg < a.T && kk < d) {  // d is a multiple of 16: a group of 4 is all in or all out
+      if (a.x_is_f32) {
+        xq = *reinterpret_cast<const uint4*>(static_cast<const float*>(a.x) + (size_t)tg * d + kk);
+      } else {
+        const uint2 u = *reinterpret_cast<const uint2*>(static_cast<const __nv_bfloat16*>(a.x) + (size_t)tg * d + kk);
+        xq.x = u.x;
+        xq.y = u.y;
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < WV; ++r) {
+      const int e = s_row + 32 * r;
+      wq[r] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (e < E && kk < d) wq[r] = __ldg(reinterpret_cast<const float4*>(a.w_router + (size_t)e * d + kk));
+    }
+  };
+  fetch(0);
+  for (int k0 = 0; k0 < d; k0 += kDKC) {
+    __syncthreads();
+    {
+      float v[4];
+      if (a.x_is_f32) {
+        v[0] = __uint_as_float(xq.x); v[1] = __uint_as_float(xq.y);
+        v[2] = __uint_as_float(xq.z); v[3] = __uint_as_float(xq.w);
+      } else {
+        v[0] = bf16lo(xq.x); v[1] = bf16hi(xq.x); v[2] = bf16lo(xq.y); v[3] = bf16hi(xq.y);
+      }
+      double2* px = reinterpret_cast<double2*>(&xs[s_row][s_k]);
+      px[0] = make_double2((double)v[0], (double)v[1]);
+      px[1] = make_double2((double)v[2], (double)v[3]);
+#pragma unroll
+      for (int r = 0; r < WV; ++r) {
+        const int e = s_row + 32 * r;
+        if (e < E_T) {
+          double2* pw = reinterpret_cast<double2*>(&ws[e][s_k]);
+          pw[0] = make_double2((double)wq[r].x, (double)wq[r].y);
+          pw[1] = make_double2((double)wq[r].z, (double)wq[r].w);
+        }
+      }
+    }
+    __syncthreads();
+    if (k0 + kDKC < d) fetch(k0 + kDKC);
+#pragma unroll
+    for (int i = 0; i < kDKC / 4 / C::NW_K; ++i) {
+      const int kk = (kslice + i * C::NW_K) * 4 + fcol;
+      double af[4];
+#pragma unroll
+      for (int mt = 0; mt < 4; ++mt) af[mt] = xs[mt * 8 + frow][kk];
+#pragma unroll
+      for (int j = 0; j < NTW; ++j) {
+        const double bf = ws[(ngrp * NTW + j) * 8 + frow][kk];
+#pragma unroll
+        for (int mt = 0; mt < 4; ++mt) dmma884(acc[mt][j], af[mt], bf);
+      }
+    }
+    if (a.gate_vec) {
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int kc = warp * 4 + c;
+        if (k0 + kc < d) gacc = fma((double)__ldg(a.gate_vec + k0 + kc), xs[lane][kc], gacc);
+      }
+    }
+  }
+  __syncthreads();  // the loop's shared-memory view is dead from here on
+  // fold the k-slices, one after the other; slice 0 initialises
+  for (int ksl = 0; ksl < C::NW_K; ++ksl) {
+    if (kslice == ksl) {
+#pragma unroll
+      for (int mt = 0; mt < 4; ++mt)
+#pragma unroll
+        for (int j = 0; j < NTW; ++j)
+#pragma unroll
+          for (int i = 0; i < 2; ++i) {
+            const int t = mt * 8 + frow, e = (ngrp * NTW + j) * 8 + fcol * 2 + i;
+            if (e < E) acc_s[t][e] = (ksl == 0 ? 0.0 : acc_s[t][e]) + acc[mt][j][i];
+          }
+    }
+    __syncthreads();
+  }
+  if (a.gate_vec) gate_s[warp][lane] = gacc;
+  // logits: bias joins the f64 sum before the rounding to f32
+  for (int i = threadIdx.x; i < kDTok * E; i += blockDim.x) {
+    const int t = i / E, e = i - t * E;
+    double v = acc_s[t][e];
+    if (a.bias) v += (double)a.bias[e];
+    const float f = (float)v;
+    lg_s[t][e] = f;
+    const int tg = t0 + t;
+    if (a.logits && tg < a.T) a.logits[(size_t)tg * E + e] = f;
+  }
+  __syncthreads();
+  if (a.gate_vec && a.gate_scale && threadIdx.x < kDTok) {
+    const int t = threadIdx.x, tg = t0 + t;
+    double v = 0.0;
+    for (int w = 0; w < kDW; ++w) v += gate_s[w][t];
+    if (tg < a.T) a.gate_scale[tg] = (float)(1.0 / (1.0 + exp(-v)));
+  }
+  for (int t = warp; t < kDTok; t += kDW) {
+    const int tg = t0 + t;
+    if (tg >= a.T) continue;
+    int rc = route_one_warp<(E_T + 31) / 32>(lg_s[t], E, a.k, a.renormalize, lane, idx_s[t], w_s[t], exps_s[warp]);
+    if (rc) {
+      if (lane == 0) report_error(a.err, rc, 1003);
+      if (lane < a.k) {  // keep downstream kernels in bounds
+        idx_s[t][lane] = lane;
+        w_s[t][lane] = 0.f;
+      }
+    }
+    __syncwarp();
+    if (lane < a.k) {
+      a.topk_idx[(size_t)tg * a.k + lane] = idx_s[t][lane];
+      a.topk_w[(size_t)tg * a.k + lane] = w_s[t][lane];
+    }
+  }
+}
+
+template <int E_T>
+int launch_one(const RouterArgs& a, cudaStream_t s) {
+  using C = DmmaCfg<E_T>;
+  static bool attr_set[kMaxDevices] = {};
+  if (C::kBytes > 48 * 1024 && first_use_on_current_device(attr_set)) {
+    ATENIA_CUDA_TRY(cudaFuncSetAttribute(router_dmma_kernel<E_T>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kBytes));
+  }
+  router_dmma_kernel<E_T><<<(a.T + kDTok - 1) / kDTok, kDW * 32, C::kBytes, s>>>(a);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace
+
+int launch_router_dmma(const RouterArgs& a, cudaStream_t s) {
+  if (a.T <= 0) return ATENIA_OK;
+  if (a.k > kMaxK || a.E > 128 || a.d % 16 != 0) return ATENIA_ERR_UNSUPPORTED;
+  int rc;
+  if (a.E <= 8) rc = launch_one<8>(a, s);
+  else if (a.E <= 16) rc = launch_one<16>(a, s);
+  else if (a.E <= 32) rc = launch_one<32>(a, s);
+  else if (a.E <= 64) rc = launch_one<64>(a, s);
+  else rc = launch_one<128>(a, s);
+  count_launch();
+  return rc;
+}
+
+}  // namespace atenia
