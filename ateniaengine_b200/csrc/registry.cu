@@ -2,6 +2,7 @@
 // (register_real_moe_layer / execute_real_moe_layer, src/moe/graph_op.rs:221-350).
 // Ids are append-only and stable for the process; one mutex guards the table and is held across a
 // forward, like the reference's registry lock (src/moe/graph_op.rs:304-316).
+#include <cstdlib>
 #include <mutex>
 #include <vector>
 
@@ -17,6 +18,12 @@ struct Registered {
   void* d_in = nullptr;        // [max_tokens, d] f32
   void* d_out = nullptr;
   cudaStream_t stream = nullptr;
+  // copy/compute overlap (on request): second pair of staging buffers, copy streams, events
+  void* d_in2 = nullptr;
+  void* d_out2 = nullptr;
+  cudaStream_t s_h2d = nullptr, s_d2h = nullptr;
+  cudaEvent_t ev_in_ready[2] = {}, ev_in_free[2] = {}, ev_out_ready[2] = {}, ev_out_free[2] = {};
+  bool pipe_ready = false;
 };
 
 std::mutex g_mu;
@@ -59,7 +66,87 @@ void release(Registered& r) {
   if (r.d_in) cudaFree(r.d_in);
   if (r.d_out) cudaFree(r.d_out);
   if (r.stream) cudaStreamDestroy(r.stream);
+  if (r.d_in2) cudaFree(r.d_in2);
+  if (r.d_out2) cudaFree(r.d_out2);
+  if (r.s_h2d) cudaStreamDestroy(r.s_h2d);
+  if (r.s_d2h) cudaStreamDestroy(r.s_d2h);
+  for (int i = 0; i < 2; ++i) {
+    if (r.ev_in_ready[i]) cudaEventDestroy(r.ev_in_ready[i]);
+    if (r.ev_in_free[i]) cudaEventDestroy(r.ev_in_free[i]);
+    if (r.ev_out_ready[i]) cudaEventDestroy(r.ev_out_ready[i]);
+    if (r.ev_out_free[i]) cudaEventDestroy(r.ev_out_free[i]);
+  }
   r = Registered();
+}
+
+// ATENIA_MOE_EXEC_CHUNK=<tokens> (unset or 0: off): execute_real_moe_layer cuts its input into
+// sub-batches of that many tokens and overlaps the host->device copy of sub-batch i+1 and the
+// device->host copy of sub-batch i-1 with the forward of sub-batch i (two staging buffers each way,
+// two copy streams, events).  The forwards themselves stay in order on one stream: the layer has one
+// workspace.  Host buffers must be pinned for the copies to be asynchronous.
+size_t exec_chunk_tokens() {
+  static const size_t v = [] {
+    const char* e = std::getenv("ATENIA_MOE_EXEC_CHUNK");
+    const long n = e ? std::atol(e) : 0;
+    return n > 0 ? (size_t)n : (size_t)0;
+  }();
+  return v;
+}
+
+int ensure_pipe(Registered& r) {
+  if (r.pipe_ready) return ATENIA_OK;
+  const size_t io = (size_t)r.layer->cfg.max_tokens * (size_t)r.layer->cfg.d_model * sizeof(float);
+  ATENIA_CUDA_TRY(cudaMalloc(&r.d_in2, io));
+  ATENIA_CUDA_TRY(cudaMalloc(&r.d_out2, io));
+  ATENIA_CUDA_TRY(cudaStreamCreateWithFlags(&r.s_h2d, cudaStreamNonBlocking));
+  ATENIA_CUDA_TRY(cudaStreamCreateWithFlags(&r.s_d2h, cudaStreamNonBlocking));
+  for (int i = 0; i < 2; ++i) {
+    ATENIA_CUDA_TRY(cudaEventCreateWithFlags(&r.ev_in_ready[i], cudaEventDisableTiming));
+    ATENIA_CUDA_TRY(cudaEventCreateWithFlags(&r.ev_in_free[i], cudaEventDisableTiming));
+    ATENIA_CUDA_TRY(cudaEventCreateWithFlags(&r.ev_out_ready[i], cudaEventDisableTiming));
+    ATENIA_CUDA_TRY(cudaEventCreateWithFlags(&r.ev_out_free[i], cudaEventDisableTiming));
+  }
+  r.pipe_ready = true;
+  return ATENIA_OK;
+}
+
+int execute_pipelined(Registered& r, const float* input, float* output, size_t n, size_t chunk) {
+  int rc = ensure_pipe(r);
+  if (rc) return rc;
+  const size_t d = (size_t)r.layer->cfg.d_model;
+  void* din[2] = {r.d_in, r.d_in2};
+  void* dout[2] = {r.d_out, r.d_out2};
+  size_t i = 0;
+  for (size_t t0 = 0; t0 < n; t0 += chunk, ++i) {
+    const size_t tn = n - t0 < chunk ? n - t0 : chunk;
+    const size_t bytes = tn * d * sizeof(float);
+    const int b = (int)(i & 1);
+    // host -> device, once the forward that last read this input buffer is done
+    if (i >= 2) ATENIA_CUDA_TRY(cudaStreamWaitEvent(r.s_h2d, r.ev_in_free[b], 0));
+    ATENIA_CUDA_TRY(cudaMemcpyAsync(din[b], input + t0 * d, bytes, cudaMemcpyHostToDevice, r.s_h2d));
+    ATENIA_CUDA_TRY(cudaEventRecord(r.ev_in_ready[b], r.s_h2d));
+    // forward, once its input has landed and the copy that last read this output buffer is done
+    ATENIA_CUDA_TRY(cudaStreamWaitEvent(r.stream, r.ev_in_ready[b], 0));
+    if (i >= 2) ATENIA_CUDA_TRY(cudaStreamWaitEvent(r.stream, r.ev_out_free[b], 0));
+    rc = atenia_moe_forward(r.layer, din[b], ATENIA_IO_F32, (int)tn, dout[b], ATENIA_IO_F32, nullptr, r.stream);
+    if (rc) break;
+    ATENIA_CUDA_TRY(cudaEventRecord(r.ev_in_free[b], r.stream));
+    ATENIA_CUDA_TRY(cudaEventRecord(r.ev_out_ready[b], r.stream));
+    // device -> host
+    ATENIA_CUDA_TRY(cudaStreamWaitEvent(r.s_d2h, r.ev_out_ready[b], 0));
+    ATENIA_CUDA_TRY(cudaMemcpyAsync(output + t0 * d, dout[b], bytes, cudaMemcpyDeviceToHost, r.s_d2h));
+    ATENIA_CUDA_TRY(cudaEventRecord(r.ev_out_free[b], r.s_d2h));
+    count_bytes(ATENIA_COUNTER_H2D_BYTES, bytes);
+    count_bytes(ATENIA_COUNTER_D2H_BYTES, bytes);
+  }
+  // everything issued must finish before the buffers are reused or the caller reads its output
+  cudaError_t e1 = cudaStreamSynchronize(r.s_h2d), e2 = cudaStreamSynchronize(r.stream),
+              e3 = cudaStreamSynchronize(r.s_d2h);
+  if (rc) return rc;
+  if (e1 != cudaSuccess) return (int)e1;
+  if (e2 != cudaSuccess) return (int)e2;
+  if (e3 != cudaSuccess) return (int)e3;
+  return atenia_moe_check(r.layer, r.stream);
 }
 
 }  // namespace
@@ -191,6 +278,11 @@ int atenia_execute_real_moe_layer(int64_t layer_id, const float* input, size_t l
   if (!input || !output) return ATENIA_ERR_NULL;
   ATENIA_CUDA_TRY(cudaSetDevice(r.layer->device));
   const size_t n = len / d, cap = (size_t)r.layer->cfg.max_tokens;
+  {
+    size_t chunk = exec_chunk_tokens();
+    if (chunk > cap) chunk = cap;
+    if (chunk > 0 && n > chunk) return execute_pipelined(r, input, output, n, chunk);
+  }
   for (size_t t0 = 0; t0 < n; t0 += cap) {
     const size_t tn = n - t0 < cap ? n - t0 : cap;
     const size_t bytes = tn * d * sizeof(float);
