@@ -58,6 +58,7 @@ EXPORTS = [
     "atenia_moe_forward_selected", "atenia_tier_detect_dtype", "atenia_tier_read_qint8", "atenia_tier_read_bf16",
     "atenia_tier_read_f32", "atenia_quantize_per_group_i8", "atenia_int8_to_bf16_per_group",
     "atenia_moe_ep_attach", "atenia_moe_ep_set_token_layout",
+    "atenia_moe_ep_ipc_bytes", "atenia_moe_ep_ipc_export", "atenia_moe_ep_ipc_import", "atenia_moe_ep_plan_direct",
 ]
 
 _lib = None
@@ -109,6 +110,9 @@ def lib():
         l.atenia_execute_real_moe_layer.argtypes = [C.c_int64, C.c_void_p, C.c_size_t, C.c_void_p]
         l.atenia_moe_ep_get_unique_id.argtypes = [C.c_void_p]
         l.atenia_moe_ep_attach.argtypes = [C.c_void_p, C.c_void_p]
+        l.atenia_moe_ep_ipc_export.argtypes = [C.c_void_p, C.c_void_p]
+        l.atenia_moe_ep_ipc_import.argtypes = [C.c_void_p, C.c_void_p]
+        l.atenia_moe_ep_plan_direct.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]
         l.atenia_moe_ep_set_token_layout.argtypes = [C.c_void_p, C.c_int]
         for fn in (l.atenia_tier_detect_dtype,):
             fn.argtypes = [C.c_char_p, C.c_int64, C.c_int64]

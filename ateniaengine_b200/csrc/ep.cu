@@ -18,6 +18,7 @@
 #include <thread>
 #include <vector>
 
+#include "ep_plan.cuh"
 #include "layer.cuh"
 
 namespace atenia {
@@ -49,6 +50,79 @@ __global__ void group_offsets_kernel(const int32_t* __restrict__ counts_all, int
       run += counts_all[p * E + e_begin + j];
     }
   group_offsets[world * e_local] = run;
+}
+
+// ---- direct exchange: rows stored into peer memory ---------------------------------------------
+__global__ void ep_plan_kernel(const int32_t* __restrict__ counts_all, int world, int E, int rank,
+                               int32_t* __restrict__ dst_base, int32_t* __restrict__ src_base,
+                               int32_t* __restrict__ group_offsets) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) ep_direct_plan(counts_all, world, E, rank, dst_base, src_base, group_offsets);
+}
+
+__device__ __forceinline__ void copy_row_bf16(uint4* __restrict__ drow, const uint4* __restrict__ srow, int nvec) {
+  for (int v = threadIdx.x; v < nvec; v += blockDim.x) drow[v] = srow[v];
+}
+
+// Block i moves dispatch row i (token perm[i] / k, expert topk_idx[perm[i]]) of this rank into the
+// receive buffer of the expert's owner: gather and send in one pass.  A row index outside the
+// owner's buffer is recorded and skipped.
+__global__ void __launch_bounds__(256) ep_scatter_kernel(const void* __restrict__ x, int x_is_f32,
+                                                         const int32_t* __restrict__ perm,
+                                                         const int32_t* __restrict__ topk_idx,
+                                                         const int32_t* __restrict__ expert_offsets,
+                                                         const int32_t* __restrict__ dst_base,
+                                                         __nv_bfloat16* const* __restrict__ peer_recv_x, int n_rows,
+                                                         int k, int d, int E, int e_local, int recv_cap,
+                                                         DeviceError* err) {
+  const int i = blockIdx.x;
+  if (i >= n_rows) return;
+  const int flat = perm[i];
+  const int e = topk_idx[flat];
+  if (e < 0 || e >= E) return;
+  const int row = dst_base[e] + (i - expert_offsets[e]);
+  if (row < 0 || row >= recv_cap) {
+    if (threadIdx.x == 0) report_error(err, ATENIA_ERR_CAPACITY, 3000);
+    return;
+  }
+  const int tok = flat / k;
+  uint4* drow = reinterpret_cast<uint4*>(peer_recv_x[e / e_local] + (size_t)row * d);
+  const int nvec = d / 8;
+  if (x_is_f32) {
+    const float4* srow = reinterpret_cast<const float4*>(static_cast<const float*>(x) + (size_t)tok * d);
+    for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+      const float4 a = srow[2 * v], b = srow[2 * v + 1];
+      drow[v] = make_uint4(pack_bf16x2(a.x, a.y), pack_bf16x2(a.z, a.w), pack_bf16x2(b.x, b.y),
+                           pack_bf16x2(b.z, b.w));
+    }
+  } else {
+    copy_row_bf16(drow, reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(x) + (size_t)tok * d), nvec);
+  }
+}
+
+// Row i of this rank's expert outputs belongs to group g = (source rank p, local expert j) and goes
+// back to row src_base[g] + (i - group_offsets[g]) of rank p's y_perm.
+__global__ void __launch_bounds__(256) ep_return_kernel(const __nv_bfloat16* __restrict__ recv_y,
+                                                        const int32_t* __restrict__ group_offsets,
+                                                        const int32_t* __restrict__ src_base,
+                                                        __nv_bfloat16* const* __restrict__ peer_y_perm, int n_groups,
+                                                        int e_local, int d, int rows_cap, DeviceError* err) {
+  const int total = group_offsets[n_groups];
+  const int nvec = d / 8;
+  for (int i = blockIdx.x; i < total; i += gridDim.x) {
+    int lo = 0, hi = n_groups;  // group_offsets[lo] <= i < group_offsets[hi]
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (group_offsets[mid] <= i) lo = mid;
+      else hi = mid;
+    }
+    const int row = src_base[lo] + (i - group_offsets[lo]);
+    if (row < 0 || row >= rows_cap) {
+      if (threadIdx.x == 0) report_error(err, ATENIA_ERR_CAPACITY, 3001);
+      continue;
+    }
+    copy_row_bf16(reinterpret_cast<uint4*>(peer_y_perm[lo / e_local] + (size_t)row * d),
+                  reinterpret_cast<const uint4*>(recv_y + (size_t)i * d), nvec);
+  }
 }
 
 #define NCCL_TRY(expr)                                 \
@@ -152,9 +226,50 @@ int ep_forward_replicated(AteniaMoeLayer* L, int n_rows, cudaStream_t s) {
   return ATENIA_OK;
 }
 
+// Direct exchange.  Every step is a launch on `s`: the counts travel by all-gather, every rank derives
+// all row positions from them on the device (ep_plan.cuh), rows are stored into the owners' receive
+// buffers by ep_scatter_kernel (which also replaces the local gather), a one-word all-reduce orders
+// those stores before the grouped GEMMs of every rank, ep_return_kernel stores the results into the
+// sources' y_perm and a second all-reduce orders them before the combine.  The collectives are the
+// only cross-GPU synchronisation (no flags, no spinning kernels), a kernel's peer stores are complete
+// when the kernel is, and nothing is read on the host.
+int ep_forward_direct(AteniaMoeLayer* L, const void* x, int x_is_f32, int T, cudaStream_t s) {
+  const AteniaMoeConfig& c = L->cfg;
+  const int G = c.ep_world, E = c.num_experts, El = L->e_local, rank = c.ep_rank, d = c.d_model;
+  const int n = T * c.experts_per_token;
+  ncclComm_t comm = L->ep->comm;
+  counts_kernel<<<1, 128, 0, s>>>(L->expert_offsets, E, L->d_counts_all + (size_t)rank * E);
+  count_launch();
+  NCCL_TRY(ncclAllGather(L->d_counts_all + (size_t)rank * E, L->d_counts_all, (size_t)E, ncclInt32, comm, s));
+  ep_plan_kernel<<<1, 32, 0, s>>>(L->d_counts_all, G, E, rank, L->d_dst_base, L->d_src_base, L->d_group_offsets);
+  count_launch();
+  if (n > 0) {
+    ep_scatter_kernel<<<n, 256, 0, s>>>(x, x_is_f32, L->perm, L->topk_idx, L->expert_offsets, L->d_dst_base,
+                                        L->d_peer_recv_x, n, c.experts_per_token, d, E, El, L->recv_cap, L->d_err);
+    count_launch();
+  }
+  ATENIA_CUDA_TRY(cudaGetLastError());
+  NCCL_TRY(ncclAllReduce(L->d_bar, L->d_bar, 1, ncclInt32, ncclSum, comm, s));
+  // the number of rows received is known on the device only: size by the buffer
+  int rc = run_expert_gemms(L, L->tm_recv_x, L->tm_recv_h, L->recv_x, L->recv_h, L->recv_y, L->d_group_offsets,
+                            L->n_groups, L->recv_cap, s, &L->tm_recv_x_r64, &L->tm_recv_h_r64);
+  if (rc) return rc;
+  ep_return_kernel<<<L->num_sms * 8, 256, 0, s>>>(L->recv_y, L->d_group_offsets, L->d_src_base, L->d_peer_y_perm,
+                                                  L->n_groups, El, d, L->rows_cap, L->d_err);
+  count_launch();
+  ATENIA_CUDA_TRY(cudaGetLastError());
+  NCCL_TRY(ncclAllReduce(L->d_bar, L->d_bar, 1, ncclInt32, ncclSum, comm, s));
+  return ATENIA_OK;
+}
+
 bool ep_ready(const AteniaMoeLayer* L) { return L->ep && L->ep->comm; }
 
-void ep_destroy(AteniaMoeLayer* L) { L->ep.reset(); }
+void ep_destroy(AteniaMoeLayer* L) {
+  for (void* p : L->ipc_opened) cudaIpcCloseMemHandle(p);
+  L->ipc_opened.clear();
+  L->ep_direct = false;
+  L->ep.reset();
+}
 
 }  // namespace atenia
 
@@ -221,10 +336,92 @@ int atenia_moe_ep_attach(AteniaMoeLayer* L, AteniaMoeLayer* owner) {
   return ATENIA_OK;
 }
 
+namespace {
+struct IpcBlob {
+  cudaIpcMemHandle_t recv_x, y_perm;
+  int32_t recv_cap, rows_cap, d_model, pad;  // buffer sizes: every rank must have been created alike
+};
+}  // namespace
+
+int atenia_moe_ep_ipc_bytes(void) { return (int)sizeof(IpcBlob); }
+
+int atenia_moe_ep_ipc_export(AteniaMoeLayer* L, void* blob) {
+  if (!L || !blob) return ATENIA_ERR_NULL;
+  if (L->cfg.ep_world <= 1 || !L->recv_x || !L->y_perm) return ATENIA_ERR_STATE;
+  IpcBlob b;
+  ATENIA_CUDA_TRY(cudaIpcGetMemHandle(&b.recv_x, L->recv_x));
+  ATENIA_CUDA_TRY(cudaIpcGetMemHandle(&b.y_perm, L->y_perm));
+  b.recv_cap = L->recv_cap;
+  b.rows_cap = L->rows_cap;
+  b.d_model = L->cfg.d_model;
+  b.pad = 0;
+  memcpy(blob, &b, sizeof(b));
+  return ATENIA_OK;
+}
+
+int atenia_moe_ep_ipc_import(AteniaMoeLayer* L, const void* blobs) {
+  if (!L || !blobs) return ATENIA_ERR_NULL;
+  const int G = L->cfg.ep_world, rank = L->cfg.ep_rank;
+  if (G <= 1 || !atenia::ep_ready(L) || L->ep_replicated || L->ep_direct) return ATENIA_ERR_STATE;
+  std::vector<__nv_bfloat16*> px(G), py(G);
+  // the sender bounds its stores by its own buffer sizes: they must be the sizes of every peer
+  for (int p = 0; p < G; ++p) {
+    IpcBlob b;
+    memcpy(&b, static_cast<const unsigned char*>(blobs) + (size_t)p * sizeof(IpcBlob), sizeof(b));
+    if (b.recv_cap != L->recv_cap || b.rows_cap != L->rows_cap || b.d_model != L->cfg.d_model) return ATENIA_ERR_SHAPE;
+  }
+  for (int p = 0; p < G; ++p) {
+    if (p == rank) {
+      px[p] = L->recv_x;
+      py[p] = L->y_perm;
+      continue;
+    }
+    IpcBlob b;
+    memcpy(&b, static_cast<const unsigned char*>(blobs) + (size_t)p * sizeof(IpcBlob), sizeof(b));
+    void* a = nullptr;
+    void* y = nullptr;
+    cudaError_t e = cudaIpcOpenMemHandle(&a, b.recv_x, cudaIpcMemLazyEnablePeerAccess);
+    if (e == cudaSuccess) {
+      L->ipc_opened.push_back(a);
+      e = cudaIpcOpenMemHandle(&y, b.y_perm, cudaIpcMemLazyEnablePeerAccess);
+    }
+    if (e != cudaSuccess) {
+      for (void* q : L->ipc_opened) cudaIpcCloseMemHandle(q);
+      L->ipc_opened.clear();
+      return (int)e;
+    }
+    L->ipc_opened.push_back(y);
+    px[p] = static_cast<__nv_bfloat16*>(a);
+    py[p] = static_cast<__nv_bfloat16*>(y);
+  }
+  const size_t pb = (size_t)G * sizeof(void*);
+  if (!L->d_peer_recv_x) ATENIA_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&L->d_peer_recv_x), pb));
+  if (!L->d_peer_y_perm) ATENIA_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&L->d_peer_y_perm), pb));
+  if (!L->d_dst_base) ATENIA_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&L->d_dst_base), (size_t)L->cfg.num_experts * 4));
+  if (!L->d_src_base) ATENIA_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&L->d_src_base), (size_t)L->n_groups * 4));
+  if (!L->d_bar) ATENIA_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&L->d_bar), 4));
+  ATENIA_CUDA_TRY(cudaMemcpy(L->d_peer_recv_x, px.data(), pb, cudaMemcpyHostToDevice));
+  ATENIA_CUDA_TRY(cudaMemcpy(L->d_peer_y_perm, py.data(), pb, cudaMemcpyHostToDevice));
+  ATENIA_CUDA_TRY(cudaMemset(L->d_bar, 0, 4));
+  L->ep_direct = true;
+  return ATENIA_OK;
+}
+
+// Host form of the row placement the direct exchange computes on the device (ep_plan.cuh), exported so
+// that it can be tested without GPUs.  Arrays: dst_base[E], src_base[E], group_offsets[E + 1] (a rank
+// has world * E / world = E groups).
+int atenia_moe_ep_plan_direct(const int32_t* counts_all, int world, int num_experts, int rank, int32_t* dst_base,
+                              int32_t* src_base, int32_t* group_offsets) {
+  if (!counts_all || !dst_base || !src_base || !group_offsets) return ATENIA_ERR_NULL;
+  if (world < 1 || num_experts < 1 || num_experts % world || rank < 0 || rank >= world) return ATENIA_ERR_SHAPE;
+  atenia::ep_direct_plan(counts_all, world, num_experts, rank, dst_base, src_base, group_offsets);
+  return ATENIA_OK;
+}
+
 int atenia_moe_ep_set_token_layout(AteniaMoeLayer* L, int layout) {
   if (!L) return ATENIA_ERR_NULL;
   if (layout != ATENIA_EP_TOKENS_SHARDED && layout != ATENIA_EP_TOKENS_REPLICATED) return ATENIA_ERR_SHAPE;
-  if (L->cfg.ep_world <= 1) return ATENIA_ERR_STATE;
+  if (L->cfg.ep_world <= 1 || L->ep_direct) return ATENIA_ERR_STATE;
   L->ep_replicated = layout == ATENIA_EP_TOKENS_REPLICATED;
   return ATENIA_OK;
 }

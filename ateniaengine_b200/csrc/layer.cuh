@@ -96,6 +96,15 @@ struct AteniaMoeLayer {
   int32_t* h_counts_all = nullptr;     // pinned host copy
   int32_t* d_group_offsets = nullptr;  // [world * e_local + 1]
   CUtensorMap tm_recv_x{}, tm_recv_h{};
+  // direct exchange (atenia_moe_ep_ipc_import): rows are stored straight into the owner's receive
+  // buffer and results straight back into the source's y_perm through peer mappings
+  bool ep_direct = false;
+  __nv_bfloat16** d_peer_recv_x = nullptr;  // device array [world]: every rank's recv_x (own entry: local)
+  __nv_bfloat16** d_peer_y_perm = nullptr;  // device array [world]: every rank's y_perm
+  std::vector<void*> ipc_opened;            // peer mappings to close
+  int32_t* d_dst_base = nullptr;            // [E]
+  int32_t* d_src_base = nullptr;            // [world * e_local]
+  int32_t* d_bar = nullptr;                 // [1] operand of the barrier all-reduce
 
   // timing
   cudaEvent_t ev[8] = {};
@@ -105,6 +114,7 @@ struct AteniaMoeLayer {
 namespace atenia {
 int ep_forward_exchange(AteniaMoeLayer* L, int T, cudaStream_t s);  // ep.cu
 int ep_forward_replicated(AteniaMoeLayer* L, int n_rows, cudaStream_t s);
+int ep_forward_direct(AteniaMoeLayer* L, const void* x, int x_is_f32, int T, cudaStream_t s);
 bool ep_ready(const AteniaMoeLayer* L);
 void ep_destroy(AteniaMoeLayer* L);
 // tm_a64 / tm_mid64: the same two matrices described with 64-row boxes (w8_mode 3), or null

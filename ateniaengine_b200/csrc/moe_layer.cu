@@ -352,7 +352,7 @@ int atenia_moe_destroy(AteniaMoeLayer* L) {
                   L->d_tm_up,    L->d_tm_down,   L->d_tm_shared, L->d_sc_gate,      L->d_sc_up,
                   L->d_sc_down,  L->d_sc_shared, L->d_p_gate,    L->d_p_up,         L->d_p_down,
                   L->d_p_shared, L->d_tm_gate_sw, L->d_tm_up_sw, L->d_tm_down_sw, L->d_tm_shared_sw, L->d_tm_gate_r64, L->d_tm_up_r64, L->d_tm_down_r64, L->splitk_ws, L->d_escore, L->logits_ws, L->recv_x,      L->recv_h,      L->recv_y,         L->d_counts_all,
-                  L->d_group_offsets};
+                  L->d_group_offsets, L->d_peer_recv_x, L->d_peer_y_perm, L->d_dst_base, L->d_src_base, L->d_bar};
   for (void* p : ptrs)
     if (p) cudaFree(p);
   for (void* p : L->owned) cudaFree(p);
@@ -567,7 +567,10 @@ static int forward_impl(AteniaMoeLayer* L, const void* x, int x_dtype, int T, vo
   if (rc) return rc;
 
   const bool need_xb = x_f32 && L->has_shared;
-  rc = launch_gather_rows(x, x_f32, L->perm, n, k, c.d_model, L->x_perm, need_xb ? L->x_bf16 : nullptr, T, s);
+  // the direct expert-parallel exchange gathers rows straight into the owners' buffers
+  const bool direct = c.ep_world > 1 && !L->ep_replicated && L->ep_direct;
+  rc = launch_gather_rows(x, x_f32, L->perm, direct ? 0 : n, k, c.d_model, L->x_perm, need_xb ? L->x_bf16 : nullptr, T,
+                          s);
   if (rc) return rc;
 
   if (c.ep_world == 1) {
@@ -575,6 +578,8 @@ static int forward_impl(AteniaMoeLayer* L, const void* x, int x_dtype, int T, vo
                           c.num_experts, n, s, &L->tm_x_perm_r64, &L->tm_h_r64);
   } else if (L->ep_replicated) {
     rc = ep_forward_replicated(L, n, s);
+  } else if (direct) {
+    rc = ep_forward_direct(L, x, x_f32 ? 1 : 0, T, s);
   } else {
     rc = ep_forward_exchange(L, T, s);
   }

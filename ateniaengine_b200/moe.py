@@ -200,6 +200,20 @@ class RealMoeLayer:
         """Share the NCCL communicator `owner` joined with ep_init (one communicator per model, not per layer)."""
         _lib.check(_lib.lib().atenia_moe_ep_attach(self._h, owner._h), "atenia_moe_ep_attach")
 
+    def ep_ipc_export(self) -> bytes:
+        """Handles to this rank's receive and result buffers, for the direct (peer-store) exchange."""
+        nb = _lib.lib().atenia_moe_ep_ipc_bytes()
+        buf = C.create_string_buffer(nb)
+        _lib.check(_lib.lib().atenia_moe_ep_ipc_export(self._h, buf), "atenia_moe_ep_ipc_export")
+        return bytes(buf.raw)
+
+    def ep_ipc_import(self, blobs_of_all_ranks: bytes):
+        """Map the buffers of all ranks (blobs concatenated in rank order) and switch the layer's
+        forward to the direct exchange."""
+        buf = C.create_string_buffer(blobs_of_all_ranks, len(blobs_of_all_ranks))
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.lib().atenia_moe_ep_ipc_import(self._h, buf), "atenia_moe_ep_ipc_import")
+
     def ep_replicated_tokens(self, enable=True):
         """Expert parallelism over a batch that every rank holds (decode): no token exchange, one
         all-reduce of the expert outputs, capturable in a CUDA graph."""

@@ -374,6 +374,13 @@ def main():
             idt = torch.frombuffer(bytearray(buf.raw), dtype=torch.uint8).to(dev)
         dist.broadcast(idt, 0)
         layer.ep_init(bytes(idt.cpu().numpy().tobytes()))
+        if os.environ.get("ATENIA_BENCH_EP_DIRECT", "0") == "1":
+            # direct exchange: rows stored into the owners' buffers over NVLink peer mappings
+            mine = torch.frombuffer(bytearray(layer.ep_ipc_export()), dtype=torch.uint8).to(dev)
+            blobs = [torch.empty_like(mine) for _ in range(args.gpus)]
+            dist.all_gather(blobs, mine)
+            layer.ep_ipc_import(b"".join(bytes(b.cpu().numpy().tobytes()) for b in blobs))
+            config["parallelism"] = f"expert-parallel ep{args.gpus}, rows stored peer to peer over NVLink, NCCL for counts and ordering"
     out = torch.empty_like(x)
 
     def sync_all():

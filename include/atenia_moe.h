@@ -331,6 +331,27 @@ ATENIA_API int atenia_moe_ep_attach(AteniaMoeLayer* layer, AteniaMoeLayer* owner
 #define ATENIA_EP_TOKENS_REPLICATED 1
 ATENIA_API int atenia_moe_ep_set_token_layout(AteniaMoeLayer* layer, int layout);
 
+/* Direct exchange for token-sharded expert parallelism (no counterpart in the reference).  After
+ * atenia_moe_ep_init every rank exports handles to its receive and result buffers, the host program
+ * gathers the blobs of all ranks (rank order) and every rank imports them.  From then on
+ * atenia_moe_forward stores each routed row straight into the receive buffer of the rank that owns
+ * its expert and each expert output straight back into the source rank's buffer over NVLink; row
+ * positions are derived on the device from all-gathered counts, two one-word all-reduces order the
+ * stores, nothing is read on the host and the results are those of the NCCL send/receive path.
+ * All ranks must be processes on one node whose GPUs have peer access, and their layers must have
+ * been created with the same max_tokens (else ATENIA_ERR_SHAPE at import).  Destroy the layers of all
+ * ranks only after every rank has finished its last forward. */
+ATENIA_API int atenia_moe_ep_ipc_bytes(void);
+ATENIA_API int atenia_moe_ep_ipc_export(AteniaMoeLayer* layer, void* blob_out);
+ATENIA_API int atenia_moe_ep_ipc_import(AteniaMoeLayer* layer, const void* blobs_of_all_ranks);
+
+/* Row placement of the direct exchange for one rank (pure host arithmetic, the same function the
+ * device runs): dst_base[E] = first row, in the owner's receive buffer, of the rows this rank holds
+ * for each expert; group_offsets[E + 1] = first row of each (source rank, local expert) group of this
+ * rank's receive buffer; src_base[E] = first row of that group in its source rank's dispatch order. */
+ATENIA_API int atenia_moe_ep_plan_direct(const int32_t* counts_all, int world, int num_experts, int rank,
+                                         int32_t* dst_base, int32_t* src_base, int32_t* group_offsets);
+
 /* The exchange plan one rank derives from the all-gathered count matrix counts_all[world][E]
  * (rows rank p holds for expert e, in p's dispatch order).  Experts are owned contiguously:
  * expert e lives on rank e / (E / world).  Pure host arithmetic (no CUDA, no NCCL); exported so the

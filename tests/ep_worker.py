@@ -35,7 +35,8 @@ def main():
     w = synth.make_weights(shape, 4, dev, experts=(rank * el, el))
     Tl = T + 5 * rank
     x = synth.make_activations(shape, 40 + rank, dev, tokens=Tl)
-    layer = synth.build_layer(shape, w, max_tokens=Tl, ep_rank=rank, ep_world=world)
+    # one capacity on every rank (the direct exchange requires it)
+    layer = synth.build_layer(shape, w, max_tokens=T + 5 * (world - 1), ep_rank=rank, ep_world=world)
     nb = _lib.lib().atenia_moe_ep_unique_id_bytes()
     idt = torch.zeros(nb, dtype=torch.uint8, device=dev)
     if rank == 0:
@@ -44,6 +45,12 @@ def main():
         idt = torch.frombuffer(bytearray(buf.raw), dtype=torch.uint8).to(dev)
     dist.broadcast(idt, 0)
     layer.ep_init(bytes(idt.cpu().numpy().tobytes()))
+    if len(sys.argv) > 3 and sys.argv[3] == "direct":
+        # direct exchange: rows stored into the owners' buffers over peer mappings
+        mine = torch.frombuffer(bytearray(layer.ep_ipc_export()), dtype=torch.uint8).to(dev)
+        blobs = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(blobs, mine)
+        layer.ep_ipc_import(b"".join(bytes(b.cpu().numpy().tobytes()) for b in blobs))
     outs = []
     for _ in range(2):
         outs.append(layer.forward(x, out_dtype=torch.float32, sync=True))
@@ -65,7 +72,7 @@ def main():
         got = torch.cat(ys)
         ok = torch.equal(ref, got)
         print(f"EP{world} {name} tokens={sizes}: equal={ok} max_abs={float((ref - got).abs().max()):.3e}", flush=True)
-    dist.barrier()
+    dist.barrier()  # peers may still map this rank's buffers until here
     dist.destroy_process_group()
     os._exit(0 if ok else 1)
 

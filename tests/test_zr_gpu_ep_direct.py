@@ -1,0 +1,31 @@
+"""Direct (peer-store) expert-parallel exchange on real GPUs: an N-rank run equals the single-GPU run
+(needs >= 2 GPUs with peer access)."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+# Opt-in in the library (atenia_moe_ep_ipc_import) and here until it has run on hardware:
+# ATENIA_TEST_EP_DIRECT=1.
+pytestmark = [pytest.mark.gpu,
+              pytest.mark.skipif(os.environ.get("ATENIA_TEST_EP_DIRECT", "0") != "1",
+                                 reason="opt-in path: set ATENIA_TEST_EP_DIRECT=1")]
+
+
+@pytest.mark.parametrize("name,port", [("mixtral", 29671), ("deepseek_v2_lite", 29678)])
+def test_direct_exchange_equals_single_gpu(name, port):
+    n = torch.cuda.device_count() if torch.cuda.is_available() else 0
+    if n < 2:
+        pytest.skip("needs at least 2 GPUs")
+    world = min(n, int(os.environ.get("ATENIA_EP_TEST_WORLD", "2")))
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", "ep_worker.py"),
+           name, "301", "direct"]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=240, env=env)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert "equal=True" in r.stdout
