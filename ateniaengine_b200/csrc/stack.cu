@@ -96,7 +96,8 @@ int atenia_moe_stack_create(AteniaMoeLayer* const* layers, int n_layers, int res
       delete S;
       return ATENIA_ERR_NULL;
     }
-    if (!L->weights_set || (L->cfg.ep_world != 1 && !L->ep_replicated)) {
+    // expert-parallel layers qualify when their forward reads nothing on the host
+    if (!L->weights_set || (L->cfg.ep_world != 1 && !L->ep_replicated && !L->ep_direct)) {
       delete S;
       return ATENIA_ERR_STATE;
     }

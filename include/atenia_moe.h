@@ -285,7 +285,8 @@ ATENIA_API AteniaMoeLayer* atenia_get_real_moe_layer(int64_t layer_id);
  * block of a transformer with attention left out, x <- x + layer_l(rmsnorm(x)) with unit gain and
  * eps 1e-5 (without a norm, random SwiGLU layers blow the residual stream up within a few layers).
  * Both require f32 input.  The stack
- * borrows the layers (single GPU or expert-parallel with replicated tokens; equal d_model, else
+ * borrows the layers (single GPU, or expert-parallel with replicated tokens or the direct exchange;
+ * equal d_model, else
  * ATENIA_ERR_DIM_MISMATCH as
  * MoeStackError::DModelMismatch); activations between layers are f32 buffers of the stack.  On a
  * non-default stream the sequence is captured once per (T, x, out) into a CUDA graph and replayed. */
