@@ -345,14 +345,15 @@ int atenia_moe_destroy(AteniaMoeLayer* L) {
   if (!L) return ATENIA_OK;
   cudaDeviceSynchronize();
   ep_destroy(L);
-  void* ptrs[] = {L->d_router,   L->d_bias,      L->d_gate_vec,  L->topk_idx,       L->topk_w,
-                  L->gate_scale, L->perm,        L->inv_perm,    L->expert_offsets, L->shared_offsets,
-                  L->block_counts, L->block_base, L->x_perm,     L->h,              L->y_perm,
-                  L->x_bf16,     L->h_shared,    L->y_shared,    L->d_err,          L->d_tm_gate,
-                  L->d_tm_up,    L->d_tm_down,   L->d_tm_shared, L->d_sc_gate,      L->d_sc_up,
-                  L->d_sc_down,  L->d_sc_shared, L->d_p_gate,    L->d_p_up,         L->d_p_down,
-                  L->d_p_shared, L->d_tm_gate_sw, L->d_tm_up_sw, L->d_tm_down_sw, L->d_tm_shared_sw, L->d_tm_gate_r64, L->d_tm_up_r64, L->d_tm_down_r64, L->splitk_ws, L->d_escore, L->logits_ws, L->recv_x,      L->recv_h,      L->recv_y,         L->d_counts_all,
-                  L->d_group_offsets, L->d_peer_recv_x, L->d_peer_y_perm, L->d_dst_base, L->d_src_base, L->d_bar};
+  void* ptrs[] = {L->d_router, L->d_bias, L->d_gate_vec, L->topk_idx, L->topk_w, L->gate_scale, L->perm,
+                  L->inv_perm, L->expert_offsets, L->shared_offsets, L->block_counts, L->block_base, L->x_perm,
+                  L->h, L->y_perm, L->x_bf16, L->h_shared, L->y_shared, L->d_err, L->d_tm_gate, L->d_tm_up,
+                  L->d_tm_down, L->d_tm_shared, L->d_sc_gate, L->d_sc_up, L->d_sc_down, L->d_sc_shared,
+                  L->d_p_gate, L->d_p_up, L->d_p_down, L->d_p_shared, L->d_tm_gate_sw, L->d_tm_up_sw,
+                  L->d_tm_down_sw, L->d_tm_shared_sw, L->d_tm_gate_r64, L->d_tm_up_r64, L->d_tm_down_r64,
+                  L->splitk_ws, L->d_escore, L->logits_ws, L->recv_x, L->recv_h, L->recv_y, L->d_counts_all,
+                  L->d_group_offsets, L->d_peer_recv_x, L->d_peer_y_perm, L->d_dst_base, L->d_src_base,
+                  L->d_bar};
   for (void* p : ptrs)
     if (p) cudaFree(p);
   for (void* p : L->owned) cudaFree(p);
