@@ -112,7 +112,8 @@ def lib():
         l.atenia_moe_ep_attach.argtypes = [C.c_void_p, C.c_void_p]
         l.atenia_moe_ep_ipc_export.argtypes = [C.c_void_p, C.c_void_p]
         l.atenia_moe_ep_ipc_import.argtypes = [C.c_void_p, C.c_void_p]
-        l.atenia_moe_ep_plan_direct.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]
+        l.atenia_moe_ep_plan_direct.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p,
+                                                C.c_void_p]
         l.atenia_moe_ep_set_token_layout.argtypes = [C.c_void_p, C.c_int]
         for fn in (l.atenia_tier_detect_dtype,):
             fn.argtypes = [C.c_char_p, C.c_int64, C.c_int64]

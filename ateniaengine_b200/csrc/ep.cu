@@ -55,8 +55,9 @@ __global__ void group_offsets_kernel(const int32_t* __restrict__ counts_all, int
 // ---- direct exchange: rows stored into peer memory ---------------------------------------------
 __global__ void ep_plan_kernel(const int32_t* __restrict__ counts_all, int world, int E, int rank,
                                int32_t* __restrict__ dst_base, int32_t* __restrict__ src_base,
-                               int32_t* __restrict__ group_offsets) {
-  if (threadIdx.x == 0 && blockIdx.x == 0) ep_direct_plan(counts_all, world, E, rank, dst_base, src_base, group_offsets);
+                               int32_t* __restrict__ sub_offsets, int32_t* __restrict__ gemm_offsets) {
+  if (threadIdx.x == 0 && blockIdx.x == 0)
+    ep_direct_plan(counts_all, world, E, rank, dst_base, src_base, sub_offsets, gemm_offsets);
 }
 
 __device__ __forceinline__ void copy_row_bf16(uint4* __restrict__ drow, const uint4* __restrict__ srow, int nvec) {
@@ -99,13 +100,13 @@ __global__ void __launch_bounds__(256) ep_scatter_kernel(const void* __restrict_
   }
 }
 
-// Row i of this rank's expert outputs belongs to group g = (source rank p, local expert j) and goes
-// back to row src_base[g] + (i - group_offsets[g]) of rank p's y_perm.
+// Row i of this rank's expert outputs belongs to sub-group g = (local expert j, source rank p) and
+// goes back to row src_base[g] + (i - sub_offsets[g]) of rank p's y_perm.
 __global__ void __launch_bounds__(256) ep_return_kernel(const __nv_bfloat16* __restrict__ recv_y,
                                                         const int32_t* __restrict__ group_offsets,
                                                         const int32_t* __restrict__ src_base,
                                                         __nv_bfloat16* const* __restrict__ peer_y_perm, int n_groups,
-                                                        int e_local, int d, int rows_cap, DeviceError* err) {
+                                                        int world, int d, int rows_cap, DeviceError* err) {
   const int total = group_offsets[n_groups];
   const int nvec = d / 8;
   for (int i = blockIdx.x; i < total; i += gridDim.x) {
@@ -120,7 +121,7 @@ __global__ void __launch_bounds__(256) ep_return_kernel(const __nv_bfloat16* __r
       if (threadIdx.x == 0) report_error(err, ATENIA_ERR_CAPACITY, 3001);
       continue;
     }
-    copy_row_bf16(reinterpret_cast<uint4*>(peer_y_perm[lo / e_local] + (size_t)row * d),
+    copy_row_bf16(reinterpret_cast<uint4*>(peer_y_perm[lo % world] + (size_t)row * d),
                   reinterpret_cast<const uint4*>(recv_y + (size_t)i * d), nvec);
   }
 }
@@ -227,8 +228,9 @@ int ep_forward_replicated(AteniaMoeLayer* L, int n_rows, cudaStream_t s) {
 }
 
 // Direct exchange.  Every step is a launch on `s`: the counts travel by all-gather, every rank derives
-// all row positions from them on the device (ep_plan.cuh), rows are stored into the owners' receive
-// buffers by ep_scatter_kernel (which also replaces the local gather), a one-word all-reduce orders
+// all row positions from them on the device (ep_plan.cuh; the receive buffer is expert-major, so the
+// GEMM has one group per local expert), rows are stored into the owners' receive buffers by
+// ep_scatter_kernel (which also replaces the local gather), a one-word all-reduce orders
 // those stores before the grouped GEMMs of every rank, ep_return_kernel stores the results into the
 // sources' y_perm and a second all-reduce orders them before the combine.  The collectives are the
 // only cross-GPU synchronisation (no flags, no spinning kernels), a kernel's peer stores are complete
@@ -241,7 +243,8 @@ int ep_forward_direct(AteniaMoeLayer* L, const void* x, int x_is_f32, int T, cud
   counts_kernel<<<1, 128, 0, s>>>(L->expert_offsets, E, L->d_counts_all + (size_t)rank * E);
   count_launch();
   NCCL_TRY(ncclAllGather(L->d_counts_all + (size_t)rank * E, L->d_counts_all, (size_t)E, ncclInt32, comm, s));
-  ep_plan_kernel<<<1, 32, 0, s>>>(L->d_counts_all, G, E, rank, L->d_dst_base, L->d_src_base, L->d_group_offsets);
+  ep_plan_kernel<<<1, 32, 0, s>>>(L->d_counts_all, G, E, rank, L->d_dst_base, L->d_src_base, L->d_group_offsets,
+                                  L->d_gemm_offsets);
   count_launch();
   if (n > 0) {
     ep_scatter_kernel<<<n, 256, 0, s>>>(x, x_is_f32, L->perm, L->topk_idx, L->expert_offsets, L->d_dst_base,
@@ -251,11 +254,12 @@ int ep_forward_direct(AteniaMoeLayer* L, const void* x, int x_is_f32, int T, cud
   ATENIA_CUDA_TRY(cudaGetLastError());
   NCCL_TRY(ncclAllReduce(L->d_bar, L->d_bar, 1, ncclInt32, ncclSum, comm, s));
   // the number of rows received is known on the device only: size by the buffer
-  int rc = run_expert_gemms(L, L->tm_recv_x, L->tm_recv_h, L->recv_x, L->recv_h, L->recv_y, L->d_group_offsets,
-                            L->n_groups, L->recv_cap, s, &L->tm_recv_x_r64, &L->tm_recv_h_r64);
+  // one GEMM group per local expert: its rows from all sources are contiguous
+  int rc = run_expert_gemms(L, L->tm_recv_x, L->tm_recv_h, L->recv_x, L->recv_h, L->recv_y, L->d_gemm_offsets, El,
+                            L->recv_cap, s, &L->tm_recv_x_r64, &L->tm_recv_h_r64);
   if (rc) return rc;
   ep_return_kernel<<<L->num_sms * 8, 256, 0, s>>>(L->recv_y, L->d_group_offsets, L->d_src_base, L->d_peer_y_perm,
-                                                  L->n_groups, El, d, L->rows_cap, L->d_err);
+                                                  L->n_groups, G, d, L->rows_cap, L->d_err);
   count_launch();
   ATENIA_CUDA_TRY(cudaGetLastError());
   NCCL_TRY(ncclAllReduce(L->d_bar, L->d_bar, 1, ncclInt32, ncclSum, comm, s));
@@ -399,6 +403,8 @@ int atenia_moe_ep_ipc_import(AteniaMoeLayer* L, const void* blobs) {
   if (!L->d_peer_y_perm) ATENIA_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&L->d_peer_y_perm), pb));
   if (!L->d_dst_base) ATENIA_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&L->d_dst_base), (size_t)L->cfg.num_experts * 4));
   if (!L->d_src_base) ATENIA_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&L->d_src_base), (size_t)L->n_groups * 4));
+  if (!L->d_gemm_offsets)
+    ATENIA_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&L->d_gemm_offsets), (size_t)(L->e_local + 1) * 4));
   if (!L->d_bar) ATENIA_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&L->d_bar), 4));
   ATENIA_CUDA_TRY(cudaMemcpy(L->d_peer_recv_x, px.data(), pb, cudaMemcpyHostToDevice));
   ATENIA_CUDA_TRY(cudaMemcpy(L->d_peer_y_perm, py.data(), pb, cudaMemcpyHostToDevice));
@@ -408,13 +414,13 @@ int atenia_moe_ep_ipc_import(AteniaMoeLayer* L, const void* blobs) {
 }
 
 // Host form of the row placement the direct exchange computes on the device (ep_plan.cuh), exported so
-// that it can be tested without GPUs.  Arrays: dst_base[E], src_base[E], group_offsets[E + 1] (a rank
-// has world * E / world = E groups).
+// that it can be tested without GPUs.  Arrays: dst_base[E], src_base[E], sub_offsets[E + 1] (a rank
+// has E / world * world = E sub-groups), gemm_offsets[E / world + 1].
 int atenia_moe_ep_plan_direct(const int32_t* counts_all, int world, int num_experts, int rank, int32_t* dst_base,
-                              int32_t* src_base, int32_t* group_offsets) {
-  if (!counts_all || !dst_base || !src_base || !group_offsets) return ATENIA_ERR_NULL;
+                              int32_t* src_base, int32_t* sub_offsets, int32_t* gemm_offsets) {
+  if (!counts_all || !dst_base || !src_base || !sub_offsets || !gemm_offsets) return ATENIA_ERR_NULL;
   if (world < 1 || num_experts < 1 || num_experts % world || rank < 0 || rank >= world) return ATENIA_ERR_SHAPE;
-  atenia::ep_direct_plan(counts_all, world, num_experts, rank, dst_base, src_base, group_offsets);
+  atenia::ep_direct_plan(counts_all, world, num_experts, rank, dst_base, src_base, sub_offsets, gemm_offsets);
   return ATENIA_OK;
 }
 

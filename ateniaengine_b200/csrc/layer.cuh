@@ -103,7 +103,8 @@ struct AteniaMoeLayer {
   __nv_bfloat16** d_peer_y_perm = nullptr;  // device array [world]: every rank's y_perm
   std::vector<void*> ipc_opened;            // peer mappings to close
   int32_t* d_dst_base = nullptr;            // [E]
-  int32_t* d_src_base = nullptr;            // [world * e_local]
+  int32_t* d_src_base = nullptr;            // [e_local * world]
+  int32_t* d_gemm_offsets = nullptr;        // [e_local + 1] expert-major group offsets of the receive buffer
   int32_t* d_bar = nullptr;                 // [1] operand of the barrier all-reduce
 
   // timing

@@ -347,11 +347,14 @@ ATENIA_API int atenia_moe_ep_ipc_export(AteniaMoeLayer* layer, void* blob_out);
 ATENIA_API int atenia_moe_ep_ipc_import(AteniaMoeLayer* layer, const void* blobs_of_all_ranks);
 
 /* Row placement of the direct exchange for one rank (pure host arithmetic, the same function the
- * device runs): dst_base[E] = first row, in the owner's receive buffer, of the rows this rank holds
- * for each expert; group_offsets[E + 1] = first row of each (source rank, local expert) group of this
- * rank's receive buffer; src_base[E] = first row of that group in its source rank's dispatch order. */
+ * device runs).  The receive buffer is laid out [local expert][source rank][rows].  dst_base[E] =
+ * first row, in the owner's receive buffer, of the rows this rank holds for each expert;
+ * gemm_offsets[E / world + 1] = first row of each local expert in this rank's receive buffer;
+ * sub_offsets[E + 1] = first row of each (local expert, source rank) slice of it; src_base[E] = first
+ * row of that slice in its source rank's dispatch order. */
 ATENIA_API int atenia_moe_ep_plan_direct(const int32_t* counts_all, int world, int num_experts, int rank,
-                                         int32_t* dst_base, int32_t* src_base, int32_t* group_offsets);
+                                         int32_t* dst_base, int32_t* src_base, int32_t* sub_offsets,
+                                         int32_t* gemm_offsets);
 
 /* The exchange plan one rank derives from the all-gathered count matrix counts_all[world][E]
  * (rows rank p holds for expert e, in p's dispatch order).  Experts are owned contiguously:
