@@ -530,6 +530,21 @@ def main():
                                             "strict mode)"}}
 
     value = T * args.gpus / (ms * 1e-3)
+    if args.gpus > 1:
+        # whole-forward target per rank: the slower of its expert flops at the measured GEMM rate and the
+        # bytes it must send over NVLink (uniform routing: (G-1)/G of its rows, out and back) at the
+        # measured peer-copy rate of this pool
+        G = args.gpus
+        flops = T * shape.top_k * 6.0 * shape.d_model * shape.d_ff + T * 6.0 * shape.d_model * shape.shared_d_ff
+        t_compute = flops / (peaks["bf16_tflops"] * 1e12)
+        link_bytes = 2.0 * T * shape.top_k * (G - 1) / G * shape.d_model * 2
+        nvlink_gbs = 770.0
+        t_link = link_bytes / (nvlink_gbs * 1e9)
+        target = max(t_compute, t_link)
+        roofline["expert_parallel"] = {"t_compute_ms": t_compute * 1e3, "t_nvlink_ms": t_link * 1e3,
+                                       "nvlink_bytes_per_rank_per_direction": link_bytes,
+                                       "nvlink_gbs_per_direction": nvlink_gbs, "target_ms": target * 1e3,
+                                       "frac": target / (ms * 1e-3)}
     line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": dtype_name, "data": "synthetic", "config": config,
