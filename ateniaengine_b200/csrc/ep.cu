@@ -148,6 +148,8 @@ int bounded_stream_wait(AteniaMoeLayer* L, cudaStream_t s) {
     cudaError_t q = cudaStreamQuery(s);
     if (q == cudaSuccess) return ATENIA_OK;
     if (q != cudaErrorNotReady) return (int)q;
+    (void)cudaGetLastError();  // "not ready" is recorded as the last error: clear it, or the next
+                               // launch check of this thread would report it
     ncclResult_t async = ncclSuccess;
     const bool bad = ncclCommGetAsyncError(comm, &async) != ncclSuccess || (async != ncclSuccess && async != ncclInProgress);
     const double waited = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
