@@ -109,6 +109,9 @@ def lib():
         l.atenia_register_real_moe_layer.argtypes = [C.POINTER(HostMoeLayer)]
         l.atenia_execute_real_moe_layer.argtypes = [C.c_int64, C.c_void_p, C.c_size_t, C.c_void_p]
         l.atenia_moe_ep_get_unique_id.argtypes = [C.c_void_p]
+        l.atenia_moe_ep_plan.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int] + [C.c_void_p] * 6
+        l.atenia_moe_counter.argtypes = [C.c_int]
+        l.atenia_moe_status_str.argtypes = [C.c_int]
         l.atenia_moe_ep_attach.argtypes = [C.c_void_p, C.c_void_p]
         l.atenia_moe_ep_ipc_export.argtypes = [C.c_void_p, C.c_void_p]
         l.atenia_moe_ep_ipc_import.argtypes = [C.c_void_p, C.c_void_p]
