@@ -229,7 +229,7 @@ int ep_forward_replicated(AteniaMoeLayer* L, int n_rows, cudaStream_t s) {
   return ATENIA_OK;
 }
 
-// Direct exchange.  Every step is a launch on `s`: the counts travel by all-gather, every rank derives
+// Direct exchange, in two halves (ep_direct_send, ep_direct_finish).  Every step is a launch on `s`: the counts travel by all-gather, every rank derives
 // all row positions from them on the device (ep_plan.cuh; the receive buffer is expert-major, so the
 // GEMM has one group per local expert), rows are stored into the owners' receive buffers by
 // ep_scatter_kernel (which also replaces the local gather), a one-word all-reduce orders
@@ -237,7 +237,7 @@ int ep_forward_replicated(AteniaMoeLayer* L, int n_rows, cudaStream_t s) {
 // sources' y_perm and a second all-reduce orders them before the combine.  The collectives are the
 // only cross-GPU synchronisation (no flags, no spinning kernels), a kernel's peer stores are complete
 // when the kernel is, and nothing is read on the host.
-int ep_forward_direct(AteniaMoeLayer* L, const void* x, int x_is_f32, int T, cudaStream_t s) {
+int ep_direct_send(AteniaMoeLayer* L, const void* x, int x_is_f32, int T, cudaStream_t s) {
   const AteniaMoeConfig& c = L->cfg;
   const int G = c.ep_world, E = c.num_experts, El = L->e_local, rank = c.ep_rank, d = c.d_model;
   const int n = T * c.experts_per_token;
@@ -253,9 +253,17 @@ int ep_forward_direct(AteniaMoeLayer* L, const void* x, int x_is_f32, int T, cud
                                         L->d_peer_recv_x, n, c.experts_per_token, d, E, El, L->recv_cap, L->d_err);
     count_launch();
   }
-  ATENIA_CUDA_TRY(cudaGetLastError());
+  return (int)cudaGetLastError();
+}
+
+// Second half: call after any local work that does not need the routed results (the shared expert),
+// so that it runs while the peers' rows are still arriving.
+int ep_direct_finish(AteniaMoeLayer* L, cudaStream_t s) {
+  const AteniaMoeConfig& c = L->cfg;
+  const int G = c.ep_world, El = L->e_local, d = c.d_model;
+  ncclComm_t comm = L->ep->comm;
   NCCL_TRY(ncclAllReduce(L->d_bar, L->d_bar, 1, ncclInt32, ncclSum, comm, s));
-  // the number of rows received is known on the device only: size by the buffer
+  // the number of rows received is known on the device only: size by the buffer.
   // one GEMM group per local expert: its rows from all sources are contiguous
   int rc = run_expert_gemms(L, L->tm_recv_x, L->tm_recv_h, L->recv_x, L->recv_h, L->recv_y, L->d_gemm_offsets, El,
                             L->recv_cap, s, &L->tm_recv_x_r64, &L->tm_recv_h_r64);

@@ -115,7 +115,8 @@ struct AteniaMoeLayer {
 namespace atenia {
 int ep_forward_exchange(AteniaMoeLayer* L, int T, cudaStream_t s);  // ep.cu
 int ep_forward_replicated(AteniaMoeLayer* L, int n_rows, cudaStream_t s);
-int ep_forward_direct(AteniaMoeLayer* L, const void* x, int x_is_f32, int T, cudaStream_t s);
+int ep_direct_send(AteniaMoeLayer* L, const void* x, int x_is_f32, int T, cudaStream_t s);
+int ep_direct_finish(AteniaMoeLayer* L, cudaStream_t s);
 bool ep_ready(const AteniaMoeLayer* L);
 void ep_destroy(AteniaMoeLayer* L);
 // tm_a64 / tm_mid64: the same two matrices described with 64-row boxes (w8_mode 3), or null

@@ -580,13 +580,20 @@ static int forward_impl(AteniaMoeLayer* L, const void* x, int x_dtype, int T, vo
   } else if (L->ep_replicated) {
     rc = ep_forward_replicated(L, n, s);
   } else if (direct) {
-    rc = ep_forward_direct(L, x, x_f32 ? 1 : 0, T, s);
+    // rows leave for their owners, the shared expert runs on the local tokens while the peers' rows
+    // arrive, then the routed experts
+    rc = ep_direct_send(L, x, x_f32 ? 1 : 0, T, s);
+    if (!rc && L->has_shared && T > 0) {
+      const __nv_bfloat16* xb = x_f32 ? L->x_bf16 : static_cast<const __nv_bfloat16*>(x);
+      rc = run_shared_gemms(L, xb, T, s);
+    }
+    if (!rc) rc = ep_direct_finish(L, s);
   } else {
     rc = ep_forward_exchange(L, T, s);
   }
   if (rc) return rc;
 
-  if (L->has_shared && T > 0) {
+  if (L->has_shared && T > 0 && !direct) {
     const __nv_bfloat16* xb = x_f32 ? L->x_bf16 : static_cast<const __nv_bfloat16*>(x);
     rc = run_shared_gemms(L, xb, T, s);
     if (rc) return rc;
