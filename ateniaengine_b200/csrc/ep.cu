@@ -60,56 +60,67 @@ __global__ void ep_plan_kernel(const int32_t* __restrict__ counts_all, int world
     ep_direct_plan(counts_all, world, E, rank, dst_base, src_base, sub_offsets, gemm_offsets);
 }
 
-__device__ __forceinline__ void copy_row_bf16(uint4* __restrict__ drow, const uint4* __restrict__ srow, int nvec) {
-  for (int v = threadIdx.x; v < nvec; v += blockDim.x) drow[v] = srow[v];
+// One warp moves one row: 16-byte vectors, four loads in flight per lane before the stores.
+__device__ __forceinline__ void warp_copy_row_bf16(uint4* __restrict__ drow, const uint4* __restrict__ srow, int nvec,
+                                                   int lane) {
+  for (int v = lane; v < nvec; v += 128) {
+    uint4 t[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (v + 32 * j < nvec) t[j] = srow[v + 32 * j];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (v + 32 * j < nvec) drow[v + 32 * j] = t[j];
+  }
 }
 
-// Block i moves dispatch row i (token perm[i] / k, expert topk_idx[perm[i]]) of this rank into the
-// receive buffer of the expert's owner: gather and send in one pass.  A row index outside the
-// owner's buffer is recorded and skipped.
-__global__ void __launch_bounds__(256) ep_scatter_kernel(const void* __restrict__ x, int x_is_f32,
-                                                         const int32_t* __restrict__ perm,
-                                                         const int32_t* __restrict__ topk_idx,
-                                                         const int32_t* __restrict__ expert_offsets,
-                                                         const int32_t* __restrict__ dst_base,
-                                                         __nv_bfloat16* const* __restrict__ peer_recv_x, int n_rows,
-                                                         int k, int d, int E, int e_local, int recv_cap,
-                                                         DeviceError* err) {
-  const int i = blockIdx.x;
-  if (i >= n_rows) return;
-  const int flat = perm[i];
-  const int e = topk_idx[flat];
-  if (e < 0 || e >= E) return;
-  const int row = dst_base[e] + (i - expert_offsets[e]);
-  if (row < 0 || row >= recv_cap) {
-    if (threadIdx.x == 0) report_error(err, ATENIA_ERR_CAPACITY, 3000);
-    return;
-  }
-  const int tok = flat / k;
-  uint4* drow = reinterpret_cast<uint4*>(peer_recv_x[e / e_local] + (size_t)row * d);
+constexpr int kEpRowWarps = 8;  // warps (rows in flight) per block of the two row-moving kernels
+
+// Warp w of the grid moves dispatch rows w, w + W, ... (token perm[i] / k, expert topk_idx[perm[i]])
+// of this rank into the receive buffer of the expert's owner: gather and send in one pass.  A row
+// index outside the owner's buffer is recorded and skipped.
+__global__ void __launch_bounds__(kEpRowWarps * 32) ep_scatter_kernel(
+    const void* __restrict__ x, int x_is_f32, const int32_t* __restrict__ perm, const int32_t* __restrict__ topk_idx,
+    const int32_t* __restrict__ expert_offsets, const int32_t* __restrict__ dst_base,
+    __nv_bfloat16* const* __restrict__ peer_recv_x, int n_rows, int k, int d, int E, int e_local, int recv_cap,
+    DeviceError* err) {
+  const int lane = threadIdx.x & 31;
   const int nvec = d / 8;
-  if (x_is_f32) {
-    const float4* srow = reinterpret_cast<const float4*>(static_cast<const float*>(x) + (size_t)tok * d);
-    for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
-      const float4 a = srow[2 * v], b = srow[2 * v + 1];
-      drow[v] = make_uint4(pack_bf16x2(a.x, a.y), pack_bf16x2(a.z, a.w), pack_bf16x2(b.x, b.y),
-                           pack_bf16x2(b.z, b.w));
+  for (int i = blockIdx.x * kEpRowWarps + (threadIdx.x >> 5); i < n_rows; i += gridDim.x * kEpRowWarps) {
+    const int flat = perm[i];
+    const int e = topk_idx[flat];
+    if (e < 0 || e >= E) continue;
+    const int row = dst_base[e] + (i - expert_offsets[e]);
+    if (row < 0 || row >= recv_cap) {
+      if (lane == 0) report_error(err, ATENIA_ERR_CAPACITY, 3000);
+      continue;
     }
-  } else {
-    copy_row_bf16(drow, reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(x) + (size_t)tok * d), nvec);
+    const int tok = flat / k;
+    uint4* drow = reinterpret_cast<uint4*>(peer_recv_x[e / e_local] + (size_t)row * d);
+    if (x_is_f32) {
+      const float4* srow = reinterpret_cast<const float4*>(static_cast<const float*>(x) + (size_t)tok * d);
+      for (int v = lane; v < nvec; v += 32) {
+        const float4 a = srow[2 * v], b = srow[2 * v + 1];
+        drow[v] = make_uint4(pack_bf16x2(a.x, a.y), pack_bf16x2(a.z, a.w), pack_bf16x2(b.x, b.y),
+                             pack_bf16x2(b.z, b.w));
+      }
+    } else {
+      warp_copy_row_bf16(drow, reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(x) + (size_t)tok * d),
+                         nvec, lane);
+    }
   }
 }
 
 // Row i of this rank's expert outputs belongs to sub-group g = (local expert j, source rank p) and
-// goes back to row src_base[g] + (i - sub_offsets[g]) of rank p's y_perm.
-__global__ void __launch_bounds__(256) ep_return_kernel(const __nv_bfloat16* __restrict__ recv_y,
-                                                        const int32_t* __restrict__ group_offsets,
-                                                        const int32_t* __restrict__ src_base,
-                                                        __nv_bfloat16* const* __restrict__ peer_y_perm, int n_groups,
-                                                        int world, int d, int rows_cap, DeviceError* err) {
+// goes back to row src_base[g] + (i - sub_offsets[g]) of rank p's y_perm.  One warp per row.
+__global__ void __launch_bounds__(kEpRowWarps * 32) ep_return_kernel(
+    const __nv_bfloat16* __restrict__ recv_y, const int32_t* __restrict__ group_offsets,
+    const int32_t* __restrict__ src_base, __nv_bfloat16* const* __restrict__ peer_y_perm, int n_groups, int world,
+    int d, int rows_cap, DeviceError* err) {
   const int total = group_offsets[n_groups];
+  const int lane = threadIdx.x & 31;
   const int nvec = d / 8;
-  for (int i = blockIdx.x; i < total; i += gridDim.x) {
+  for (int i = blockIdx.x * kEpRowWarps + (threadIdx.x >> 5); i < total; i += gridDim.x * kEpRowWarps) {
     int lo = 0, hi = n_groups;  // group_offsets[lo] <= i < group_offsets[hi]
     while (hi - lo > 1) {
       const int mid = (lo + hi) >> 1;
@@ -118,11 +129,11 @@ __global__ void __launch_bounds__(256) ep_return_kernel(const __nv_bfloat16* __r
     }
     const int row = src_base[lo] + (i - group_offsets[lo]);
     if (row < 0 || row >= rows_cap) {
-      if (threadIdx.x == 0) report_error(err, ATENIA_ERR_CAPACITY, 3001);
+      if (lane == 0) report_error(err, ATENIA_ERR_CAPACITY, 3001);
       continue;
     }
-    copy_row_bf16(reinterpret_cast<uint4*>(peer_y_perm[lo % world] + (size_t)row * d),
-                  reinterpret_cast<const uint4*>(recv_y + (size_t)i * d), nvec);
+    warp_copy_row_bf16(reinterpret_cast<uint4*>(peer_y_perm[lo % world] + (size_t)row * d),
+                       reinterpret_cast<const uint4*>(recv_y + (size_t)i * d), nvec, lane);
   }
 }
 
@@ -249,8 +260,11 @@ int ep_direct_send(AteniaMoeLayer* L, const void* x, int x_is_f32, int T, cudaSt
                                   L->d_gemm_offsets);
   count_launch();
   if (n > 0) {
-    ep_scatter_kernel<<<n, 256, 0, s>>>(x, x_is_f32, L->perm, L->topk_idx, L->expert_offsets, L->d_dst_base,
-                                        L->d_peer_recv_x, n, c.experts_per_token, d, E, El, L->recv_cap, L->d_err);
+    const int blocks = (n + kEpRowWarps - 1) / kEpRowWarps;
+    const int cap = L->num_sms * 16;
+    ep_scatter_kernel<<<blocks < cap ? blocks : cap, kEpRowWarps * 32, 0, s>>>(
+        x, x_is_f32, L->perm, L->topk_idx, L->expert_offsets, L->d_dst_base, L->d_peer_recv_x, n,
+        c.experts_per_token, d, E, El, L->recv_cap, L->d_err);
     count_launch();
   }
   return (int)cudaGetLastError();
@@ -268,7 +282,7 @@ int ep_direct_finish(AteniaMoeLayer* L, cudaStream_t s) {
   int rc = run_expert_gemms(L, L->tm_recv_x, L->tm_recv_h, L->recv_x, L->recv_h, L->recv_y, L->d_gemm_offsets, El,
                             L->recv_cap, s, &L->tm_recv_x_r64, &L->tm_recv_h_r64);
   if (rc) return rc;
-  ep_return_kernel<<<L->num_sms * 8, 256, 0, s>>>(L->recv_y, L->d_group_offsets, L->d_src_base, L->d_peer_y_perm,
+  ep_return_kernel<<<L->num_sms * 16, kEpRowWarps * 32, 0, s>>>(L->recv_y, L->d_group_offsets, L->d_src_base, L->d_peer_y_perm,
                                                   L->n_groups, G, d, L->rows_cap, L->d_err);
   count_launch();
   ATENIA_CUDA_TRY(cudaGetLastError());
