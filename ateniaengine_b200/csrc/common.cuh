@@ -165,6 +165,8 @@ int encode_tmap_2d_u8(CUtensorMap* out, const void* base, uint64_t rows, uint64_
 // W8A16 grouped GEMM with the weights as the tensor-memory operand (w8_gemm.cu).  tmap_a is the bf16
 // token matrix (box {64, 128}, 128B swizzle); tmap_b0/b1 are int8 maps with the 64-byte swizzle.
 int launch_grouped_gemm_w8_tmem(const GroupedGemmArgs& a, int num_sms, cudaStream_t s);
+// Same contract; the widening warps take alternate k-blocks (w8_gemm_alt.cu).
+int launch_grouped_gemm_w8_alt(const GroupedGemmArgs& a, int num_sms, cudaStream_t s);
 constexpr size_t kW8SplitKSlotFloats = 2 * 128 * 128;  // per CTA: two slots of this size
 // W8A16 for large groups (w8_gemm_wide.cu): one widened weight tile per k-block for up to 192 tokens.
 // tmap_a is the bf16 token matrix with box {64, 64} (128B swizzle); tmap_b0/b1 are int8 maps with box

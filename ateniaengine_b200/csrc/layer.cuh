@@ -22,7 +22,8 @@ struct AteniaMoeLayer {
   const float* residual = nullptr;  // set by a stack around one forward: added by the combine kernel
   // INT8: 0 = pick per call (tensor-memory operand kernel for small batches, shared-memory widening
   // for large ones), 1 = always the tensor-memory kernel, 2 = always shared-memory widening,
-  // 3 = as 0 but the wide tensor-memory kernel (w8_gemm_wide.cu) for large batches
+  // 3 = as 0 but the wide tensor-memory kernel (w8_gemm_wide.cu) for large batches,
+  // 4 = as 0 but the tensor-memory kernel with alternating widening groups (w8_gemm_alt.cu)
   int w8_mode = 0;
   // bf16: 0 = pick per call (CTA-pair kernel once groups average >= 512 rows), 1 = always pairs,
   // 2 = always the single-CTA kernel

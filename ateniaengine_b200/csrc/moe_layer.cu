@@ -57,7 +57,9 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
   const bool wide = q && L->w8_mode == 3 && L->has_r64 && tm_a64 && tm_mid64 && large && !L->use_check_gemm;
   // INT8: the tensor-memory kernel wins while groups are small (its MMA width follows the row count),
   // the shared-memory widening kernel once every group fills several 128-row tiles.
-  const bool tmem = q && !wide && (L->w8_mode == 1 || ((L->w8_mode == 0 || L->w8_mode == 3) && !large));
+  const bool w8_auto = L->w8_mode == 0 || L->w8_mode == 3 || L->w8_mode == 4;
+  const bool tmem = q && !wide && (L->w8_mode == 1 || (w8_auto && !large));
+  const bool alt = tmem && L->w8_mode == 4;  // on request: the variant with alternating widening groups
   // bf16: 256-row CTA-pair tiles pay off once an average group fills a few of them
   // (INT8 has a pair kernel too, but it measures slower than the single-CTA one: only on request.)
   // bf16, on request: the stream-K decode kernel while the whole call fits one token tile per group
@@ -89,6 +91,7 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
     g1.splitk_ws = L->splitk_ws;
     int rc = wide ? launch_grouped_gemm_w8_wide(g1, L->num_sms, s)
                   : dec ? launch_grouped_gemm_bf16_decode(g1, L->num_sms, s)
+                  : alt ? launch_grouped_gemm_w8_alt(g1, L->num_sms, s)
                   : tmem ? launch_grouped_gemm_w8_tmem(g1, L->num_sms, s)
                          : pairs ? launch_grouped_gemm_2cta(g1, L->num_sms, s)
                                  : launch_grouped_gemm_tcgen05(g1, L->num_sms, s);
@@ -119,6 +122,7 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
     g2.splitk_ws = L->splitk_ws;
     int rc = wide ? launch_grouped_gemm_w8_wide(g2, L->num_sms, s)
                   : dec ? launch_grouped_gemm_bf16_decode(g2, L->num_sms, s)
+                  : alt ? launch_grouped_gemm_w8_alt(g2, L->num_sms, s)
                   : tmem ? launch_grouped_gemm_w8_tmem(g2, L->num_sms, s)
                          : pairs ? launch_grouped_gemm_2cta(g2, L->num_sms, s)
                                  : launch_grouped_gemm_tcgen05(g2, L->num_sms, s);
@@ -137,7 +141,9 @@ int run_shared_gemms(AteniaMoeLayer* L, const __nv_bfloat16* xb, int T, cudaStre
   const AteniaMoeConfig& c = L->cfg;
   const bool q = c.weight_dtype == ATENIA_W_INT8_ROW;
   // (the shared expert keeps the default choice under w8_mode 3)
-  const bool tmem = q && (L->w8_mode == 1 || ((L->w8_mode == 0 || L->w8_mode == 3) && T < 256));
+  const bool w8_auto = L->w8_mode == 0 || L->w8_mode == 3 || L->w8_mode == 4;
+  const bool tmem = q && (L->w8_mode == 1 || (w8_auto && T < 256));
+  const bool alt = tmem && L->w8_mode == 4;
   const bool pairs = !tmem && (L->pair_mode == 1 || (L->pair_mode == 0 && !q && T >= 512));
   if (L->timing) cudaEventRecord(L->ev[3], s);
   if (L->use_check_gemm) {
@@ -169,8 +175,9 @@ int run_shared_gemms(AteniaMoeLayer* L, const __nv_bfloat16* xb, int T, cudaStre
   g1.max_rows = T;
   g1.w8 = q;
   g1.splitk_ws = L->splitk_ws;
-  rc = tmem ? launch_grouped_gemm_w8_tmem(g1, L->num_sms, s)
-            : pairs ? launch_grouped_gemm_2cta(g1, L->num_sms, s) : launch_grouped_gemm_tcgen05(g1, L->num_sms, s);
+  rc = alt ? launch_grouped_gemm_w8_alt(g1, L->num_sms, s)
+           : tmem ? launch_grouped_gemm_w8_tmem(g1, L->num_sms, s)
+                  : pairs ? launch_grouped_gemm_2cta(g1, L->num_sms, s) : launch_grouped_gemm_tcgen05(g1, L->num_sms, s);
   if (rc) return rc;
   if (L->timing) cudaEventRecord(L->ev[4], s);
   GroupedGemmArgs g2{};
@@ -188,8 +195,9 @@ int run_shared_gemms(AteniaMoeLayer* L, const __nv_bfloat16* xb, int T, cudaStre
   g2.max_rows = T;
   g2.w8 = q;
   g2.splitk_ws = L->splitk_ws;
-  rc = tmem ? launch_grouped_gemm_w8_tmem(g2, L->num_sms, s)
-            : pairs ? launch_grouped_gemm_2cta(g2, L->num_sms, s) : launch_grouped_gemm_tcgen05(g2, L->num_sms, s);
+  rc = alt ? launch_grouped_gemm_w8_alt(g2, L->num_sms, s)
+           : tmem ? launch_grouped_gemm_w8_tmem(g2, L->num_sms, s)
+                  : pairs ? launch_grouped_gemm_2cta(g2, L->num_sms, s) : launch_grouped_gemm_tcgen05(g2, L->num_sms, s);
   if (rc) return rc;
   if (L->timing) {
     cudaEventRecord(L->ev[5], s);

@@ -37,6 +37,8 @@ class Bar:
 
 
 class Sim:
+    acc_bufs = 2  # 1 models w8_gemm_alt.cu: same widening protocol, single accumulator buffer
+
     def __init__(self, tiles, seed):
         self.rng = random.Random(seed)
         self.tiles = tiles  # list of (num_kb, nbox)
@@ -120,7 +122,7 @@ class Sim:
                 self.acc_full[acc].arrive()
             self.at(max(self.mma_queue_done - self.t, 0.0) + 1e-6, tile_done)
             acc_phase[acc] ^= 1
-            acc ^= 1
+            acc = (acc + 1) % self.acc_bufs
         self.finished += 1
 
     def widen(self, group, quarter):
@@ -173,7 +175,7 @@ class Sim:
             assert a["tile"] == tile_no, "accumulator overwritten while the epilogue was reading it"
             a["drained"] += 1
             self.acc_empty[acc].arrive()
-            acc ^= 1
+            acc = (acc + 1) % self.acc_bufs
         self.finished += 1
 
     def run(self):
@@ -225,6 +227,15 @@ class Sim:
 def test_protocol_has_no_deadlock_or_hazard(tiles):
     for seed in range(12):
         Sim(tiles, seed).run()
+
+
+@pytest.mark.parametrize("tiles", [[(1, 1)], [(7, 1), (3, 1)], [(64, 1)] * 2, [(2, 1)] * 7, [(224, 1)]])
+def test_alternating_groups_with_a_single_accumulator(tiles):
+    """The decode variant (w8_gemm_alt.cu): stream-K pieces of any length, one accumulator buffer."""
+    class Single(Sim):
+        acc_bufs = 1
+    for seed in range(8):
+        Single(tiles, seed).run()
 
 
 def test_model_detects_a_wrong_arrival_count():
