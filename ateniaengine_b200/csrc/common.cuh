@@ -64,10 +64,17 @@ struct RouterArgs {
   float* gate_scale;   // [T] or null
   float* logits;       // [T, E] or null
   DeviceError* err;
-  int variant;         // 0: CUDA-core f64 kernel (router.cu); 1: f64 tensor-core kernel (router_dmma.cu)
+  int variant;         // 0: CUDA-core f64 kernel (router.cu); 1: f64 tensor-core kernel (router_dmma.cu);
+                       // 2: split-k kernel for small batches (router_splitk.cu) when T <= sk_tokens
+  double* sk_part;     // variant 2 workspace (router_splitk_workspace), else null
+  double* sk_gate;
+  unsigned int* sk_counters;
+  int sk_tokens;       // largest batch the workspace serves
 };
 int launch_router(const RouterArgs& a, cudaStream_t s);
 int launch_router_dmma(const RouterArgs& a, cudaStream_t s);  // same contract, E <= 128, k <= 8
+int launch_router_splitk(const RouterArgs& a, cudaStream_t s);  // same contract, T <= a.sk_tokens
+void router_splitk_workspace(int tokens, int d, int E, size_t* part_doubles, size_t* gate_doubles, size_t* counters);
 int launch_route_from_logits(const float* logits, int T, int E, int k, int renormalize,
                              int32_t* topk_idx, float* topk_w, DeviceError* err, cudaStream_t s);
 

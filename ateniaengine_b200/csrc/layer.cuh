@@ -31,7 +31,12 @@ struct AteniaMoeLayer {
   // bf16, on request (ATENIA_MOE_BF16_DECODE=1): the stream-K decode kernel when a call has <= 128 rows
   bool bf16_decode = false;
   // on request (ATENIA_MOE_ROUTER_DMMA=1): router logits on the f64 tensor cores (router_dmma.cu)
+  // ... or (ATENIA_MOE_ROUTER_SPLITK=1) the split-k router for batches of at most sk_tokens (router_splitk.cu)
   int router_variant = 0;
+  double* sk_part = nullptr;
+  double* sk_gate = nullptr;
+  unsigned int* sk_counters = nullptr;
+  int sk_tokens = 0;
 
   // weights (device)
   float* d_router = nullptr;    // [E, d]

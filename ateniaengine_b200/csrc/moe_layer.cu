@@ -236,6 +236,9 @@ int atenia_moe_create(const AteniaMoeConfig* cfg, AteniaMoeLayer** out) {
   L->w8_mode = std::getenv("ATENIA_MOE_W8_MODE") ? std::atoi(std::getenv("ATENIA_MOE_W8_MODE")) : 0;
   L->pair_mode = std::getenv("ATENIA_MOE_PAIR_MODE") ? std::atoi(std::getenv("ATENIA_MOE_PAIR_MODE")) : 0;
   L->router_variant = (std::getenv("ATENIA_MOE_ROUTER_DMMA") && std::atoi(std::getenv("ATENIA_MOE_ROUTER_DMMA")) != 0) ? 1 : 0;
+  if (L->router_variant == 0 && std::getenv("ATENIA_MOE_ROUTER_SPLITK") &&
+      std::atoi(std::getenv("ATENIA_MOE_ROUTER_SPLITK")) != 0)
+    L->router_variant = 2;
   L->bf16_decode = c.weight_dtype == ATENIA_W_BF16 && std::getenv("ATENIA_MOE_BF16_DECODE") &&
                    std::atoi(std::getenv("ATENIA_MOE_BF16_DECODE")) != 0;
   const size_t Tm = (size_t)c.max_tokens, k = (size_t)c.experts_per_token, E = (size_t)c.num_experts;
@@ -281,6 +284,18 @@ int atenia_moe_create(const AteniaMoeConfig* cfg, AteniaMoeLayer** out) {
   TRY_ALLOC(L->d_tm_down, (size_t)L->n_groups);
   TRY_ALLOC(L->d_tm_shared, 3);
   if (L->bf16_decode) TRY_ALLOC(L->splitk_ws, (size_t)L->num_sms * 2 * kW8SplitKSlotFloats);
+  if (L->router_variant == 2) {
+    L->sk_tokens = c.max_tokens < 1024 ? c.max_tokens : 1024;
+    size_t np = 0, ng = 0, nc = 0;
+    router_splitk_workspace(L->sk_tokens, c.d_model, c.num_experts, &np, &ng, &nc);
+    TRY_ALLOC(L->sk_part, np);
+    TRY_ALLOC(L->sk_gate, ng);
+    TRY_ALLOC(L->sk_counters, nc);
+    if (cudaMemset(L->sk_counters, 0, nc * sizeof(unsigned int)) != cudaSuccess) {
+      atenia_moe_destroy(L);
+      return ATENIA_ERR_STATE;
+    }
+  }
   if (c.weight_dtype == ATENIA_W_INT8_ROW) {
     TRY_ALLOC(L->splitk_ws, (size_t)L->num_sms * 2 * kW8SplitKSlotFloats);
     TRY_ALLOC(L->d_tm_gate_sw, (size_t)L->n_groups);
@@ -361,7 +376,7 @@ int atenia_moe_destroy(AteniaMoeLayer* L) {
                   L->d_tm_down_sw, L->d_tm_shared_sw, L->d_tm_gate_r64, L->d_tm_up_r64, L->d_tm_down_r64,
                   L->splitk_ws, L->d_escore, L->logits_ws, L->recv_x, L->recv_h, L->recv_y, L->d_counts_all,
                   L->d_group_offsets, L->d_peer_recv_x, L->d_peer_y_perm, L->d_dst_base, L->d_src_base,
-                  L->d_gemm_offsets, L->d_bar};
+                  L->d_gemm_offsets, L->d_bar, L->sk_part, L->sk_gate, L->sk_counters};
   for (void* p : ptrs)
     if (p) cudaFree(p);
   for (void* p : L->owned) cudaFree(p);
@@ -546,6 +561,10 @@ static int forward_impl(AteniaMoeLayer* L, const void* x, int x_dtype, int T, vo
   ra.logits = (aux && aux->logits) ? aux->logits : (v3 ? L->logits_ws : nullptr);
   ra.err = L->d_err;
   ra.variant = L->router_variant;
+  ra.sk_part = L->sk_part;
+  ra.sk_gate = L->sk_gate;
+  ra.sk_counters = L->sk_counters;
+  ra.sk_tokens = L->sk_tokens;
   int rc = launch_router(ra, s);
   if (rc) return rc;
   if (v3) {

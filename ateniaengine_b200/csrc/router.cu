@@ -352,6 +352,7 @@ int launch_router(const RouterArgs& a, cudaStream_t s) {
   if (a.T <= 0) return ATENIA_OK;
   if (a.k > kMaxK || a.E > 128) return ATENIA_ERR_UNSUPPORTED;
   if (a.variant == 1) return launch_router_dmma(a, s);
+  if (a.variant == 2 && a.T <= a.sk_tokens) return launch_router_splitk(a, s);
   dim3 block(kRWarps * 32);
   // more tokens per CTA for many experts: the router matrix is re-read once per CTA
   if (a.E <= 8) router_kernel<8, 8><<<(a.T + 7) / 8, block, 0, s>>>(a);

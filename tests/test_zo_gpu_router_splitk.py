@@ -1,0 +1,45 @@
+"""ATENIA_MOE_ROUTER_SPLITK=1: the split-k router for small batches against the oracle and the default
+router, repeated calls (its counters reset themselves) and the hand-over to the default router above
+1024 tokens."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from tests.test_gpu_parity import TOL_BF16, _run_parity, _synth, dev  # noqa: F401
+
+# Opt-in in the library and here until it has run on hardware: ATENIA_TEST_ROUTER_SPLITK=1.
+pytestmark = [pytest.mark.gpu,
+              pytest.mark.skipif(os.environ.get("ATENIA_TEST_ROUTER_SPLITK", "0") != "1",
+                                 reason="opt-in kernel: set ATENIA_TEST_ROUTER_SPLITK=1")]
+
+
+@pytest.mark.parametrize("name,d_model,T", [("mixtral", 512, 1), ("mixtral", 528, 13), ("qwen_moe", 512, 64),
+                                             ("deepseek_v2_lite", 1024, 200), ("mixtral", 512, 1500)])
+def test_layer_parity_with_the_splitk_router(dev, monkeypatch, name, d_model, T):
+    monkeypatch.setenv("ATENIA_MOE_ROUTER_SPLITK", "1")
+    synth = _synth()
+    base = synth.SHAPES[name]
+    shape = synth.small(base, d_model=d_model, d_ff=384, shared_d_ff=256 if base.shared_d_ff else 0)
+    _run_parity(dev, shape, T, TOL_BF16, seed=T, sample=256)
+
+
+@pytest.mark.parametrize("E,k", [(8, 2), (60, 4), (64, 6), (128, 8)])
+def test_same_routing_as_the_default_router_and_repeatable(dev, monkeypatch, E, k):
+    synth = _synth()
+    shape = synth.MoeShape("r", 4096, 64, E, k, True)
+    w = synth.make_weights(shape, 3, dev)
+    x = synth.make_activations(shape, 3, dev, tokens=37)
+    _, a = synth.build_layer(shape, w, max_tokens=64).forward(x, out_dtype=torch.float32, aux=True, sync=True)
+    monkeypatch.setenv("ATENIA_MOE_ROUTER_SPLITK", "1")
+    layer = synth.build_layer(shape, w, max_tokens=64)
+    outs = [layer.forward(x, out_dtype=torch.float32, aux=True, sync=True) for _ in range(3)]
+    for _, b in outs:
+        la, lb = a["logits"].cpu().numpy(), b["logits"].cpu().numpy()
+        assert np.abs(la - lb).max() <= 1e-6 and (la != lb).mean() < 1e-2
+        assert (a["topk_idx"].cpu().numpy() == b["topk_idx"].cpu().numpy()).all(axis=1).mean() >= 0.97
+    assert torch.equal(outs[0][1]["logits"], outs[2][1]["logits"]) and torch.equal(outs[0][0], outs[2][0])
+    # fewer tokens than the last call: only the counters of the first token blocks are touched
+    y1 = layer.forward(x[:3], out_dtype=torch.float32, sync=True)
+    assert torch.equal(y1, outs[0][0][:3])
