@@ -14,4 +14,12 @@ from .moe import (  # noqa: F401
     quantize_per_row_i8,
     quantize_per_group_i8,
     int8_to_bf16_per_group,
+    execute_real_moe_layer_with,
+    NumericPolicy,
+    numeric_policy,
+    set_numeric_policy,
+    clear_numeric_policy_override,
+    auto_expert_cache_capacity,
+    plan_residency,
+    workspace_bytes,
 )

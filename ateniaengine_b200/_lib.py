@@ -9,6 +9,9 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "csrc", "libatenia_moe.so")
 
 IO_BF16, IO_F32 = 0, 1
+CONVENTION_LAYER, CONVENTION_ATENIA, CONVENTION_HF_QWEN = -1, 0, 1
+POLICY_CERTIFIED, POLICY_STRICT, POLICY_FAST = 0, 1, 2
+ERR_POLICY = -15
 W_BF16, W_INT8_ROW = 0, 1
 
 ERR_LAYER_NOT_FOUND = -5
@@ -38,6 +41,13 @@ class MoeAux(C.Structure):
                 ("perm", C.c_void_p), ("expert_offsets", C.c_void_p)]
 
 
+class ResidencyPlan(C.Structure):
+    _fields_ = [("min_ep_world", C.c_int32), ("experts_per_rank", C.c_int32),
+                ("resident_experts_per_layer", C.c_int32), ("reserved", C.c_int32),
+                ("bytes_per_expert", C.c_uint64), ("fixed_bytes_per_rank", C.c_uint64),
+                ("bytes_per_rank", C.c_uint64)]
+
+
 class HostMoeLayer(C.Structure):
     _fields_ = [
         ("config", MoeConfig), ("w_router", C.c_void_p),
@@ -59,6 +69,11 @@ EXPORTS = [
     "atenia_tier_read_f32", "atenia_quantize_per_group_i8", "atenia_int8_to_bf16_per_group",
     "atenia_moe_ep_attach", "atenia_moe_ep_set_token_layout",
     "atenia_moe_ep_ipc_bytes", "atenia_moe_ep_ipc_export", "atenia_moe_ep_ipc_import", "atenia_moe_ep_plan_direct",
+    "atenia_moe_forward_with", "atenia_execute_real_moe_layer_with",
+    "atenia_numeric_policy_from_str", "atenia_numeric_policy_str", "atenia_numeric_policy",
+    "atenia_numeric_policy_is_explicit", "atenia_set_numeric_policy", "atenia_clear_numeric_policy_override",
+    "atenia_numeric_policy_ffn_uses_f32", "atenia_numeric_policy_ffn_uses_cuda", "atenia_numeric_policy_gate",
+    "atenia_moe_plan_residency", "atenia_auto_expert_cache_capacity", "atenia_moe_workspace_bytes",
 ]
 
 _lib = None
@@ -131,6 +146,24 @@ def lib():
         l.atenia_moe_dispatch_noalloc.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p,
                                                   C.c_void_p, C.c_void_p]
         l.atenia_moe_ep_init.argtypes = [C.c_void_p, C.c_void_p]
+        l.atenia_moe_forward_with.argtypes = fwd + [C.c_int]
+        l.atenia_execute_real_moe_layer_with.argtypes = [C.c_int64, C.c_void_p, C.c_size_t, C.c_void_p, C.c_int]
+        l.atenia_numeric_policy_from_str.argtypes = [C.c_char_p]
+        l.atenia_numeric_policy_str.argtypes = [C.c_int]
+        l.atenia_numeric_policy_str.restype = C.c_char_p
+        l.atenia_numeric_policy.argtypes = []
+        l.atenia_numeric_policy_is_explicit.argtypes = []
+        l.atenia_set_numeric_policy.argtypes = [C.c_int]
+        l.atenia_clear_numeric_policy_override.argtypes = []
+        l.atenia_clear_numeric_policy_override.restype = None
+        l.atenia_numeric_policy_ffn_uses_f32.argtypes = [C.c_int]
+        l.atenia_numeric_policy_ffn_uses_cuda.argtypes = [C.c_int]
+        l.atenia_numeric_policy_gate.argtypes = []
+        l.atenia_moe_plan_residency.argtypes = [C.POINTER(MoeConfig), C.c_int, C.c_uint64, C.POINTER(ResidencyPlan)]
+        l.atenia_auto_expert_cache_capacity.argtypes = [C.c_uint64] * 4
+        l.atenia_auto_expert_cache_capacity.restype = C.c_uint64
+        l.atenia_moe_workspace_bytes.argtypes = [C.POINTER(MoeConfig)]
+        l.atenia_moe_workspace_bytes.restype = C.c_uint64
         _lib = l
     return _lib
 

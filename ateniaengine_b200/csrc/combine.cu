@@ -27,6 +27,7 @@ __global__ void __launch_bounds__(256) combine_kernel(CombineArgs a) {
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] = 0.f;
     for (int s = 0; s < a.k; ++s) {
+      if (rows[s] < 0) continue;  // entry without a row (invalid expert id, reported by the dispatch)
       const uint4 y = *reinterpret_cast<const uint4*>(a.y_rows + (size_t)rows[s] * a.d + v * 8);
       const uint32_t p[4] = {y.x, y.y, y.z, y.w};
 #pragma unroll

@@ -100,9 +100,10 @@ struct DispatchArgs {
 constexpr int kDispatchChunk = 256;  // flat entries per block
 int launch_dispatch(const DispatchArgs& a, cudaStream_t s);
 
-// x_perm[r, :] = bf16(x[perm[r] / k, :]); optionally x_bf16 = bf16(x) when x is f32.
-int launch_gather_rows(const void* x, int x_is_f32, const int32_t* perm, int n_rows, int k, int d,
-                       __nv_bfloat16* x_perm, __nv_bfloat16* x_bf16, int T, cudaStream_t s);
+// x_perm[r, :] = bf16(x[perm[r] / k, :]) for r < *placed (device: expert_offsets[E], the rows the
+// placement wrote); optionally x_bf16 = bf16(x) when x is f32.
+int launch_gather_rows(const void* x, int x_is_f32, const int32_t* perm, const int32_t* placed, int n_rows, int k,
+                       int d, __nv_bfloat16* x_perm, __nv_bfloat16* x_bf16, int T, cudaStream_t s);
 
 // ---- combine ---------------------------------------------------------------------------------
 struct CombineArgs {

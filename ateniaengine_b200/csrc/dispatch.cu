@@ -88,12 +88,17 @@ __global__ void __launch_bounds__(kDispatchChunk) place_kernel(DispatchArgs a) {
     const int pos = a.expert_offsets[e] + a.block_base[(size_t)blockIdx.x * a.E + e] + before + rank_in_warp;
     a.perm[pos] = i;
     a.inv_perm[i] = pos;
+  } else if (i < a.n) {
+    a.inv_perm[i] = -1;  // an entry with an invalid expert id has no row: the combine skips it
   }
 }
 
-// One block per destination row; 16-byte vectors.
+// One block per destination row; 16-byte vectors.  `placed` points at expert_offsets[E], the number
+// of rows the placement actually wrote: entries with an invalid expert id get no row, so perm beyond
+// that count holds whatever an earlier call left there and must not be followed.
 __global__ void __launch_bounds__(256) gather_rows_kernel(const void* __restrict__ x, int x_is_f32,
-                                                           const int32_t* __restrict__ perm, int n_rows, int k,
+                                                           const int32_t* __restrict__ perm,
+                                                           const int32_t* __restrict__ placed, int n_rows, int k,
                                                            int d, __nv_bfloat16* __restrict__ x_perm,
                                                            __nv_bfloat16* __restrict__ x_bf16, int T) {
   const int r = blockIdx.x;
@@ -101,7 +106,9 @@ __global__ void __launch_bounds__(256) gather_rows_kernel(const void* __restrict
   int src_t, dst_r;
   __nv_bfloat16* dst;
   if (!copy_row) {
+    if (r >= *placed) return;
     src_t = perm[r] / k;
+    if (src_t < 0 || src_t >= T) return;
     dst_r = r;
     dst = x_perm;
   } else {
@@ -143,11 +150,11 @@ int launch_dispatch(const DispatchArgs& a, cudaStream_t s) {
   return (int)cudaGetLastError();
 }
 
-int launch_gather_rows(const void* x, int x_is_f32, const int32_t* perm, int n_rows, int k, int d,
-                       __nv_bfloat16* x_perm, __nv_bfloat16* x_bf16, int T, cudaStream_t s) {
+int launch_gather_rows(const void* x, int x_is_f32, const int32_t* perm, const int32_t* placed, int n_rows, int k,
+                       int d, __nv_bfloat16* x_perm, __nv_bfloat16* x_bf16, int T, cudaStream_t s) {
   const int extra = x_bf16 ? T : 0;
   if (n_rows + extra <= 0) return ATENIA_OK;
-  gather_rows_kernel<<<n_rows + extra, 256, 0, s>>>(x, x_is_f32, perm, n_rows, k, d, x_perm, x_bf16, T);
+  gather_rows_kernel<<<n_rows + extra, 256, 0, s>>>(x, x_is_f32, perm, placed, n_rows, k, d, x_perm, x_bf16, T);
   count_launch();
   return (int)cudaGetLastError();
 }

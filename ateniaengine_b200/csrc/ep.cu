@@ -86,8 +86,11 @@ __global__ void __launch_bounds__(kEpRowWarps * 32) ep_scatter_kernel(
     DeviceError* err) {
   const int lane = threadIdx.x & 31;
   const int nvec = d / 8;
-  for (int i = blockIdx.x * kEpRowWarps + (threadIdx.x >> 5); i < n_rows; i += gridDim.x * kEpRowWarps) {
+  // entries with an invalid expert id were given no row: perm beyond the placed count is stale
+  const int placed = expert_offsets[E] < n_rows ? expert_offsets[E] : n_rows;
+  for (int i = blockIdx.x * kEpRowWarps + (threadIdx.x >> 5); i < placed; i += gridDim.x * kEpRowWarps) {
     const int flat = perm[i];
+    if (flat < 0 || flat >= n_rows) continue;
     const int e = topk_idx[flat];
     if (e < 0 || e >= E) continue;
     const int row = dst_base[e] + (i - expert_offsets[e]);
@@ -148,6 +151,7 @@ __global__ void __launch_bounds__(kEpRowWarps * 32) ep_return_kernel(
 // error or when the deadline (ATENIA_MOE_EP_TIMEOUT_S, default 60 s) passes the communicator is
 // aborted, which also ends NCCL kernels still waiting on the device, and ATENIA_ERR_NCCL is returned.
 int bounded_stream_wait(AteniaMoeLayer* L, cudaStream_t s) {
+  if (!L->ep || !L->ep->comm) return ATENIA_ERR_STATE;
   static const double limit_s = [] {
     const char* e = std::getenv("ATENIA_MOE_EP_TIMEOUT_S");
     double v = e ? std::atof(e) : 60.0;
@@ -291,6 +295,8 @@ int ep_direct_finish(AteniaMoeLayer* L, cudaStream_t s) {
 }
 
 bool ep_ready(const AteniaMoeLayer* L) { return L->ep && L->ep->comm; }
+
+int ep_bounded_wait(AteniaMoeLayer* L, cudaStream_t s) { return bounded_stream_wait(L, s); }
 
 void ep_destroy(AteniaMoeLayer* L) {
   for (void* p : L->ipc_opened) cudaIpcCloseMemHandle(p);

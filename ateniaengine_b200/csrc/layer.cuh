@@ -44,7 +44,9 @@ struct AteniaMoeLayer {
   float* d_gate_vec = nullptr;  // [d]
   float* d_escore = nullptr;    // [E] V3 e_score_correction_bias (zeros if none given)
   float* logits_ws = nullptr;   // [max_tokens, E] V3: logits between the router and the V3 selection
-  bool has_bias = false, has_gate_vec = false, has_shared = false;
+  bool has_bias = false, has_shared = false;
+  bool gate_vec_bound = false;  // a shared gate vector was given with the weights
+  bool has_gate_vec = false;    // ... and the layer's own convention uses it
   CUtensorMap* d_tm_gate = nullptr;  // [n_groups]
   CUtensorMap* d_tm_up = nullptr;
   CUtensorMap* d_tm_down = nullptr;
@@ -124,6 +126,10 @@ int ep_forward_replicated(AteniaMoeLayer* L, int n_rows, cudaStream_t s);
 int ep_direct_send(AteniaMoeLayer* L, const void* x, int x_is_f32, int T, cudaStream_t s);
 int ep_direct_finish(AteniaMoeLayer* L, cudaStream_t s);
 bool ep_ready(const AteniaMoeLayer* L);
+// Wait for `s` with the expert-parallel deadline (ATENIA_MOE_EP_TIMEOUT_S): polls the stream and the
+// communicator; on a failed peer or a passed deadline aborts the communicator and returns
+// ATENIA_ERR_NCCL, so a collective whose peer never arrives cannot block the host for ever.
+int ep_bounded_wait(AteniaMoeLayer* L, cudaStream_t s);
 void ep_destroy(AteniaMoeLayer* L);
 // tm_a64 / tm_mid64: the same two matrices described with 64-row boxes (w8_mode 3), or null
 int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorMap& tm_mid,

@@ -410,8 +410,10 @@ int atenia_moe_set_weights(AteniaMoeLayer* L, const AteniaMoeWeights* w) {
     else
       ATENIA_CUDA_TRY(cudaMemset(L->d_escore, 0, E * sizeof(float)));
   }
-  L->has_gate_vec = w->shared_gate_vec != nullptr && c.shared_gated && L->has_shared;
-  if (L->has_gate_vec)
+  // kept whenever given: a call may ask for the gated convention of a layer configured ungated
+  L->gate_vec_bound = w->shared_gate_vec != nullptr && L->has_shared;
+  L->has_gate_vec = L->gate_vec_bound && c.shared_gated;
+  if (L->gate_vec_bound)
     ATENIA_CUDA_TRY(cudaMemcpy(L->d_gate_vec, w->shared_gate_vec, d * sizeof(float), cudaMemcpyDeviceToDevice));
 
   // INT8 matrices are borrowed as they are: their tensor maps describe bytes and the grouped GEMM
@@ -510,11 +512,21 @@ int atenia_moe_set_weights(AteniaMoeLayer* L, const AteniaMoeWeights* w) {
 }
 
 static int forward_impl(AteniaMoeLayer* L, const void* x, int x_dtype, int T, void* out, int out_dtype,
-                        const AteniaMoeAux* aux, void* stream, const int32_t* sel_idx, const float* sel_w);
+                        const AteniaMoeAux* aux, void* stream, const int32_t* sel_idx, const float* sel_w,
+                        int convention = ATENIA_CONVENTION_LAYER);
 
 int atenia_moe_forward(AteniaMoeLayer* L, const void* x, int x_dtype, int T, void* out, int out_dtype,
                        const AteniaMoeAux* aux, void* stream) {
   return forward_impl(L, x, x_dtype, T, out, out_dtype, aux, stream, nullptr, nullptr);
+}
+
+int atenia_moe_forward_with(AteniaMoeLayer* L, const void* x, int x_dtype, int T, void* out, int out_dtype,
+                            const AteniaMoeAux* aux, void* stream, int convention) {
+  if (convention != ATENIA_CONVENTION_LAYER && convention != ATENIA_CONVENTION_ATENIA &&
+      convention != ATENIA_CONVENTION_HF_QWEN)
+    return ATENIA_ERR_SHAPE;
+  if (L && convention != ATENIA_CONVENTION_LAYER && L->cfg.router_mode == ATENIA_ROUTER_V3) return ATENIA_ERR_UNSUPPORTED;
+  return forward_impl(L, x, x_dtype, T, out, out_dtype, aux, stream, nullptr, nullptr, convention);
 }
 
 int atenia_moe_forward_selected(AteniaMoeLayer* L, const void* x, int x_dtype, int T, const int32_t* topk_idx,
@@ -524,14 +536,15 @@ int atenia_moe_forward_selected(AteniaMoeLayer* L, const void* x, int x_dtype, i
 }
 
 static int forward_impl(AteniaMoeLayer* L, const void* x, int x_dtype, int T, void* out, int out_dtype,
-                        const AteniaMoeAux* aux, void* stream, const int32_t* sel_idx, const float* sel_w) {
+                        const AteniaMoeAux* aux, void* stream, const int32_t* sel_idx, const float* sel_w,
+                        int convention) {
   if (!L) return ATENIA_ERR_NULL;
   if (!L->weights_set) return ATENIA_ERR_STATE;
   if (T < 0) return ATENIA_ERR_SHAPE;
   // an empty batch has no buffers to check (token-sharded expert parallelism still joins the exchange)
   const bool no_exchange = L->cfg.ep_world == 1 || L->ep_replicated;
   if (T == 0 && no_exchange) return ATENIA_OK;
-  if (!x || !out) return ATENIA_ERR_NULL;
+  if (T > 0 && (!x || !out)) return ATENIA_ERR_NULL;  // an empty rank may pass NULL and still joins the exchange
   if (T > L->cfg.max_tokens) return ATENIA_ERR_CAPACITY;
   if ((x_dtype != ATENIA_IO_BF16 && x_dtype != ATENIA_IO_F32) ||
       (out_dtype != ATENIA_IO_BF16 && out_dtype != ATENIA_IO_F32))
@@ -542,21 +555,26 @@ static int forward_impl(AteniaMoeLayer* L, const void* x, int x_dtype, int T, vo
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int k = c.experts_per_token, n = T * k;
   const bool x_f32 = x_dtype == ATENIA_IO_F32;
+  // the convention of this call (RealMoeLayer::forward_with): Atenia renormalises and ignores the gate;
+  // HuggingFaceQwen keeps the raw weights and gates the shared expert when a gate vector is bound
+  const int renorm = convention == ATENIA_CONVENTION_LAYER ? c.renormalize : (convention == ATENIA_CONVENTION_ATENIA ? 1 : 0);
+  const bool gated = convention == ATENIA_CONVENTION_LAYER ? L->has_gate_vec
+                                                           : (convention == ATENIA_CONVENTION_HF_QWEN && L->gate_vec_bound);
 
   RouterArgs ra{};
   ra.x = x;
   ra.x_is_f32 = x_f32;
   ra.w_router = L->d_router;
   ra.bias = L->has_bias ? L->d_bias : nullptr;
-  ra.gate_vec = L->has_gate_vec ? L->d_gate_vec : nullptr;
+  ra.gate_vec = gated ? L->d_gate_vec : nullptr;
   ra.T = T;
   ra.d = c.d_model;
   ra.E = c.num_experts;
   ra.k = k;
-  ra.renormalize = c.renormalize;
+  ra.renormalize = renorm;
   ra.topk_idx = L->topk_idx;
   ra.topk_w = L->topk_w;
-  ra.gate_scale = L->has_gate_vec ? L->gate_scale : nullptr;
+  ra.gate_scale = gated ? L->gate_scale : nullptr;
   const bool v3 = c.router_mode == ATENIA_ROUTER_V3;
   ra.logits = (aux && aux->logits) ? aux->logits : (v3 ? L->logits_ws : nullptr);
   ra.err = L->d_err;
@@ -597,8 +615,8 @@ static int forward_impl(AteniaMoeLayer* L, const void* x, int x_dtype, int T, vo
   const bool need_xb = x_f32 && L->has_shared;
   // the direct expert-parallel exchange gathers rows straight into the owners' buffers
   const bool direct = c.ep_world > 1 && !L->ep_replicated && L->ep_direct;
-  rc = launch_gather_rows(x, x_f32, L->perm, direct ? 0 : n, k, c.d_model, L->x_perm, need_xb ? L->x_bf16 : nullptr, T,
-                          s);
+  rc = launch_gather_rows(x, x_f32, L->perm, L->expert_offsets + c.num_experts, direct ? 0 : n, k, c.d_model,
+                          L->x_perm, need_xb ? L->x_bf16 : nullptr, T, s);
   if (rc) return rc;
 
   if (c.ep_world == 1) {
@@ -631,7 +649,7 @@ static int forward_impl(AteniaMoeLayer* L, const void* x, int x_dtype, int T, vo
   ca.inv_perm = L->inv_perm;
   ca.topk_w = L->topk_w;
   ca.y_shared = L->has_shared ? L->y_shared : nullptr;
-  ca.gate_scale = L->has_gate_vec ? L->gate_scale : nullptr;
+  ca.gate_scale = gated ? L->gate_scale : nullptr;
   ca.residual = L->residual;
   ca.out = out;
   ca.out_is_f32 = out_dtype == ATENIA_IO_F32;
@@ -657,7 +675,13 @@ static int forward_impl(AteniaMoeLayer* L, const void* x, int x_dtype, int T, vo
 int atenia_moe_check(AteniaMoeLayer* L, void* stream) {
   if (!L) return ATENIA_ERR_NULL;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  ATENIA_CUDA_TRY(cudaStreamSynchronize(s));
+  if (L->cfg.ep_world > 1 && ep_ready(L)) {
+    // every expert-parallel forward holds collectives: wait with the deadline, not for ever
+    int wrc = ep_bounded_wait(L, s);
+    if (wrc) return wrc;
+  } else {
+    ATENIA_CUDA_TRY(cudaStreamSynchronize(s));
+  }
   DeviceError he{};
   ATENIA_CUDA_TRY(cudaMemcpy(&he, L->d_err, sizeof(he), cudaMemcpyDeviceToHost));
   if (he.code != 0) {
@@ -729,6 +753,8 @@ const char* atenia_moe_status_str(int status) {
     case ATENIA_ERR_DRIVER: return "tensor-map encode or driver entry point unavailable";
     case ATENIA_ERR_IO: return "a tier file is missing or could not be read";
     case ATENIA_ERR_TIER_FORMAT: return "tier file length matches none of its encodings (or not the one asked for)";
+    case ATENIA_ERR_POLICY:
+      return "the selected numeric policy (certified / strict) keeps the MoE block on the host's CPU arms";
     case ATENIA_ERR_SCRATCH_LIMIT:
       return "request exceeds the fixed scratch of atenia_moe_dispatch_noalloc (T*k <= 65536, E <= 128)";
     default: break;

@@ -27,11 +27,13 @@ constexpr int kNoAllocWords = 2 * kNoAllocBlocks * kNoAllocMaxExperts;  // count
 
 static __device__ __align__(256) int32_t g_dispatch_scratch[kNoAllocWords];
 
-constexpr int kMaxDevices = 64;
 std::mutex g_setup_mu;
-int32_t* g_scratch_addr[kMaxDevices] = {};
+int32_t* g_scratch_addr[kMaxDevices] = {};  // kMaxDevices: common.cuh
 
-// Device address of the scratch array on the current device; looked up on the first call per device.
+// Device address of the scratch array on the current device; looked up on the first call per device
+// and kept for the life of the process.  A cudaDeviceReset (or any other teardown of the device's
+// primary context) invalidates the kept address: a process that resets a device must not call this
+// entry point on that device afterwards.
 int scratch_for_current_device(int32_t** out) {
   int dev = -1;
   ATENIA_CUDA_TRY(cudaGetDevice(&dev));

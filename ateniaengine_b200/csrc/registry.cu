@@ -110,7 +110,7 @@ int ensure_pipe(Registered& r) {
   return ATENIA_OK;
 }
 
-int execute_pipelined(Registered& r, const float* input, float* output, size_t n, size_t chunk) {
+int execute_pipelined(Registered& r, const float* input, float* output, size_t n, size_t chunk, int convention) {
   int rc = ensure_pipe(r);
   if (rc) return rc;
   const size_t d = (size_t)r.layer->cfg.d_model;
@@ -128,7 +128,8 @@ int execute_pipelined(Registered& r, const float* input, float* output, size_t n
     // forward, once its input has landed and the copy that last read this output buffer is done
     ATENIA_CUDA_TRY(cudaStreamWaitEvent(r.stream, r.ev_in_ready[b], 0));
     if (i >= 2) ATENIA_CUDA_TRY(cudaStreamWaitEvent(r.stream, r.ev_out_free[b], 0));
-    rc = atenia_moe_forward(r.layer, din[b], ATENIA_IO_F32, (int)tn, dout[b], ATENIA_IO_F32, nullptr, r.stream);
+    rc = atenia_moe_forward_with(r.layer, din[b], ATENIA_IO_F32, (int)tn, dout[b], ATENIA_IO_F32, nullptr, r.stream,
+                                 convention);
     if (rc) break;
     ATENIA_CUDA_TRY(cudaEventRecord(r.ev_in_free[b], r.stream));
     ATENIA_CUDA_TRY(cudaEventRecord(r.ev_out_ready[b], r.stream));
@@ -216,7 +217,7 @@ int64_t atenia_register_real_moe_layer(const AteniaHostMoeLayer* h) {
     if (!rc) rc = upload_matrix(h->shared_w_up, Fs, d, q, reg, &w.shared_w_up, &w.shared_s_up, staging);
     if (!rc) rc = upload_matrix(h->shared_w_down, d, Fs, q, reg, &w.shared_w_down, &w.shared_s_down, staging);
     if (rc) return fail(rc);
-    if (h->shared_gate_vec && cfg.shared_gated) {
+    if (h->shared_gate_vec) {  // kept even when the layer's own convention is ungated (execute_..._with)
       ce = cudaMalloc(reinterpret_cast<void**>(&d_gate_vec), d * sizeof(float));
       if (ce == cudaSuccess) ce = cudaMemcpy(d_gate_vec, h->shared_gate_vec, d * sizeof(float), cudaMemcpyHostToDevice);
       if (ce != cudaSuccess) return fail((int)ce);
@@ -269,6 +270,19 @@ int64_t atenia_register_resident_moe_layer(AteniaMoeLayer* layer) {
 }
 
 int atenia_execute_real_moe_layer(int64_t layer_id, const float* input, size_t len, float* output) {
+  return atenia_execute_real_moe_layer_with(layer_id, input, len, output, ATENIA_CONVENTION_LAYER);
+}
+
+int atenia_execute_real_moe_layer_with(int64_t layer_id, const float* input, size_t len, float* output,
+                                       int convention) {
+  {
+    // a host that selected the certified or strict numeric policy runs its own CPU arm
+    const int prc = atenia_numeric_policy_gate();
+    if (prc) return prc;
+  }
+  if (convention != ATENIA_CONVENTION_LAYER && convention != ATENIA_CONVENTION_ATENIA &&
+      convention != ATENIA_CONVENTION_HF_QWEN)
+    return ATENIA_ERR_SHAPE;
   std::lock_guard<std::mutex> lk(g_mu);
   if (layer_id < 0 || (size_t)layer_id >= g_layers.size() || !g_layers[(size_t)layer_id].layer)
     return ATENIA_ERR_LAYER_NOT_FOUND;
@@ -281,13 +295,14 @@ int atenia_execute_real_moe_layer(int64_t layer_id, const float* input, size_t l
   {
     size_t chunk = exec_chunk_tokens();
     if (chunk > cap) chunk = cap;
-    if (chunk > 0 && n > chunk) return execute_pipelined(r, input, output, n, chunk);
+    if (chunk > 0 && n > chunk) return execute_pipelined(r, input, output, n, chunk, convention);
   }
   for (size_t t0 = 0; t0 < n; t0 += cap) {
     const size_t tn = n - t0 < cap ? n - t0 : cap;
     const size_t bytes = tn * d * sizeof(float);
     ATENIA_CUDA_TRY(cudaMemcpyAsync(r.d_in, input + t0 * d, bytes, cudaMemcpyHostToDevice, r.stream));
-    int rc = atenia_moe_forward(r.layer, r.d_in, ATENIA_IO_F32, (int)tn, r.d_out, ATENIA_IO_F32, nullptr, r.stream);
+    int rc = atenia_moe_forward_with(r.layer, r.d_in, ATENIA_IO_F32, (int)tn, r.d_out, ATENIA_IO_F32, nullptr,
+                                     r.stream, convention);
     if (rc) return rc;
     ATENIA_CUDA_TRY(cudaMemcpyAsync(output + t0 * d, r.d_out, bytes, cudaMemcpyDeviceToHost, r.stream));
     count_bytes(ATENIA_COUNTER_H2D_BYTES, bytes);

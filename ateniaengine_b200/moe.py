@@ -246,7 +246,27 @@ class RealMoeLayer:
                           C.byref(auxs) if auxs is not None else None, st), "atenia_moe_forward")
         return (out, aux_t) if aux else out
 
-    forward_auto = forward
+    def forward_with(self, x, convention, out=None, out_dtype=None, sync=False):
+        """RealMoeLayer::forward_with: the block under an explicit MoeExecutionConvention for this call
+        (Atenia: renormalised weights, ungated shared expert; HuggingFaceQwen: raw weights, shared
+        expert scaled by sigmoid(gate . x) when the layer was given a gate vector)."""
+        assert x.is_cuda and x.dim() == 2 and x.shape[1] == self.config.d_model
+        x = x.contiguous()
+        T = x.shape[0]
+        if out is None:
+            out = torch.empty((T, self.config.d_model), dtype=out_dtype or x.dtype, device=x.device)
+        with torch.cuda.device(x.device):
+            st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+            _lib.check(_lib.lib().atenia_moe_forward_with(self._h, _ptr(x), _io_dtype(x), T, _ptr(out), _io_dtype(out),
+                                                          None, st, int(convention.value)), "atenia_moe_forward_with")
+            if sync:
+                _lib.check(_lib.lib().atenia_moe_check(self._h, st), "atenia_moe_forward_with")
+        return out
+
+    def forward_auto(self, x, **kw):
+        """RealMoeLayer::forward_auto: HuggingFaceQwen when a shared gate vector is present, else Atenia
+        (resolve_convention); the convention the constructor resolved when none was given."""
+        return self.forward(x, **kw)
 
     def forward_selected(self, x, topk_idx, topk_w, out_dtype=None, sync=True):
         """The block with a caller-supplied selection (the graph primitives MoeDynamicDispatch /
@@ -345,13 +365,20 @@ def register_resident_moe_layer(layer):
     return int(lid)
 
 
-def execute_real_moe_layer(layer_id, input, out=None):
-    """Flat host f32 [n * d_model] -> [n * d_model], the graph op's contract."""
+def execute_real_moe_layer(layer_id, input, out=None, convention=None):
+    """Flat host f32 [n * d_model] -> [n * d_model], the graph op's contract.  `convention` (a
+    MoeExecutionConvention) makes it execute_real_moe_layer_with."""
     inp = np.ascontiguousarray(input, dtype=np.float32).reshape(-1)
     if out is None:
         out = np.empty_like(inp)
-    rc = _lib.lib().atenia_execute_real_moe_layer(int(layer_id), C.c_void_p(inp.ctypes.data), inp.size,
-                                                  C.c_void_p(out.ctypes.data))
+    if convention is None:
+        rc = _lib.lib().atenia_execute_real_moe_layer(int(layer_id), C.c_void_p(inp.ctypes.data), inp.size,
+                                                      C.c_void_p(out.ctypes.data))
+    else:
+        rc = _lib.lib().atenia_execute_real_moe_layer_with(int(layer_id), C.c_void_p(inp.ctypes.data), inp.size,
+                                                           C.c_void_p(out.ctypes.data), int(convention.value))
+    if rc == _lib.ERR_POLICY:
+        raise MoeLayerError("NumericPolicy", rc, "the selected numeric policy keeps the block on the CPU arms")
     if rc == _lib.ERR_LAYER_NOT_FOUND:
         raise MoeLayerError("LayerNotFound", rc, f"layer_id {layer_id}")
     if rc == _lib.ERR_DIM_MISMATCH:
@@ -359,6 +386,71 @@ def execute_real_moe_layer(layer_id, input, out=None):
     if rc != 0:
         raise MoeLayerError("Status", rc, _lib.lib().atenia_moe_status_str(C.c_int(rc)).decode())
     return out
+
+
+def execute_real_moe_layer_with(layer_id, input, convention, out=None):
+    """execute_real_moe_layer_with (src/moe/graph_op.rs:352-364)."""
+    return execute_real_moe_layer(layer_id, input, out=out, convention=convention)
+
+
+class NumericPolicy(enum.Enum):
+    """NumericPolicy (src/moe/numeric_policy.rs:37-47).  The library is the Fast arm."""
+    Certified = 0
+    Strict = 1
+    Fast = 2
+
+    def as_str(self):
+        return _lib.lib().atenia_numeric_policy_str(self.value).decode()
+
+    @staticmethod
+    def from_str(name):
+        v = _lib.lib().atenia_numeric_policy_from_str(name.encode())
+        return None if v < 0 else NumericPolicy(v)
+
+    def ffn_uses_f32(self):
+        return bool(_lib.lib().atenia_numeric_policy_ffn_uses_f32(self.value))
+
+    def ffn_uses_cuda(self):
+        return bool(_lib.lib().atenia_numeric_policy_ffn_uses_cuda(self.value))
+
+
+def numeric_policy():
+    return NumericPolicy(_lib.lib().atenia_numeric_policy())
+
+
+def set_numeric_policy(p):
+    _lib.check(_lib.lib().atenia_set_numeric_policy(p.value), "set_numeric_policy")
+
+
+def clear_numeric_policy_override():
+    _lib.lib().atenia_clear_numeric_policy_override()
+
+
+def auto_expert_cache_capacity(ram_budget_bytes, n_layers, per_expert_bytes, num_experts):
+    """auto_expert_cache_capacity (src/moe/residency.rs:201-211)."""
+    return int(_lib.lib().atenia_auto_expert_cache_capacity(int(ram_budget_bytes), int(n_layers),
+                                                            int(per_expert_bytes), int(num_experts)))
+
+
+def _plan_config(config, shared_d_ff, int8, max_tokens, ep_world=1):
+    return _lib.MoeConfig(config.num_experts, config.experts_per_token, config.d_model, config.d_ff, int(shared_d_ff),
+                          1, 0, W_INT8_ROW if int8 else W_BF16, int(max_tokens), 0, int(ep_world))
+
+
+def plan_residency(config, n_layers, hbm_budget_bytes, shared_d_ff=0, int8=False, max_tokens=4096):
+    """Smallest expert-parallel world (1, 2, 4, 8) in which `n_layers` layers of `config` are resident
+    within `hbm_budget_bytes` per GPU.  Returns (status, plan dict); status -3 (capacity) when even
+    8 ranks do not hold the model."""
+    cfg = _plan_config(config, shared_d_ff, int8, max_tokens)
+    plan = _lib.ResidencyPlan()
+    rc = _lib.lib().atenia_moe_plan_residency(C.byref(cfg), int(n_layers), int(hbm_budget_bytes), C.byref(plan))
+    return rc, {n: getattr(plan, n) for n, _ in _lib.ResidencyPlan._fields_ if n != "reserved"}
+
+
+def workspace_bytes(config, shared_d_ff=0, int8=False, max_tokens=4096, ep_world=1):
+    """Device bytes a RealMoeLayer of this configuration allocates besides its weights."""
+    cfg = _plan_config(config, shared_d_ff, int8, max_tokens, ep_world)
+    return int(_lib.lib().atenia_moe_workspace_bytes(C.byref(cfg)))
 
 
 def execute_real_moe_layer_ptr(layer_id, in_ptr, n_floats, out_ptr):

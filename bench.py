@@ -116,7 +116,7 @@ def cpu_oracle_rate(shape, w, x_host, max_seconds, threads=0, accum=None, ol=Non
     """tokens/s of the CPU oracle (all host threads) on a bounded token sample; `accum` picks the
     reference's accumulation mode (default f64, its certified path; ACC_F32 is its strict path)."""
     from oracle import oracle as orc
-    from tests.helpers import oracle_layer
+    from oracle.from_synth import oracle_layer
 
     if ol is None:
         ol = oracle_layer(shape, w)
@@ -317,7 +317,7 @@ def main():
         w = synth.make_weights(shape, 2, dev)
         x = synth.make_activations(shape, 2, dev, tokens=min(T, 512)).float().cpu().numpy()
         from oracle import oracle as orc
-        from tests.helpers import oracle_layer
+        from oracle.from_synth import oracle_layer
         ol = oracle_layer(shape, w)
         del w
         cores = orc.max_threads()

@@ -21,6 +21,10 @@
  *                                        src/cuda/int8_to_bf16.cu:42-73, :119-150
  *                                                                  atenia_int8_to_bf16_per_group
  *   RealMoeStack::forward                src/moe/stack.rs:197-210  atenia_moe_stack_forward
+ *   RealMoeLayer::forward_with           src/moe/layer.rs:405-431  atenia_moe_forward_with
+ *   execute_real_moe_layer_with          src/moe/graph_op.rs:352-364  atenia_execute_real_moe_layer_with
+ *   NumericPolicy, numeric_policy()      src/moe/numeric_policy.rs:37-127  atenia_numeric_policy*
+ *   auto_expert_cache_capacity           src/moe/residency.rs:201-211  atenia_moe_plan_residency
  *
  * Conventions follow the reference's existing CUDA FFI (the .cu files under src/cuda): plain `extern "C"` functions,
  * `int` status (0 = ok, > 0 = a cudaError_t value, < 0 = argument / shape / state errors listed
@@ -62,6 +66,7 @@ extern "C" {
 #define ATENIA_ERR_IO (-13)             /* a tier file is missing or could not be read */
 #define ATENIA_ERR_TIER_FORMAT (-14)    /* a tier file's length matches none of its encodings (or not the one asked for) */
 #define ATENIA_ERR_SCRATCH_LIMIT (-12)  /* request larger than the fixed scratch of atenia_moe_dispatch_noalloc */
+#define ATENIA_ERR_POLICY (-15)         /* the numeric policy the host selected keeps the block on its CPU arms */
 
 /* ---- enums -------------------------------------------------------------------------------- */
 #define ATENIA_IO_BF16 0 /* activations as bf16 (high half of an f32, src/tensor/tensor.rs:294-308) */
@@ -146,6 +151,22 @@ ATENIA_API int atenia_moe_set_weights(AteniaMoeLayer* layer, const AteniaMoeWeig
 ATENIA_API int atenia_moe_forward(AteniaMoeLayer* layer, const void* x, int x_dtype, int T, void* out,
                                   int out_dtype, const AteniaMoeAux* aux, void* stream);
 
+/* Execution conventions (MoeExecutionConvention, src/moe/layer.rs:37-43) for the calls that take one:
+ *   ATENIA_CONVENTION_LAYER    the convention in the layer's config (renormalize, shared_gated)
+ *   ATENIA_CONVENTION_ATENIA   selected weights renormalised, shared expert added ungated
+ *   ATENIA_CONVENTION_HF_QWEN  raw selected weights, shared expert scaled by sigmoid(g . x) when a
+ *                              gate vector was bound with the weights, by 1 otherwise */
+#define ATENIA_CONVENTION_LAYER (-1)
+#define ATENIA_CONVENTION_ATENIA 0
+#define ATENIA_CONVENTION_HF_QWEN 1
+
+/* atenia_moe_forward under an explicit convention for this call only (RealMoeLayer::forward_with,
+ * src/moe/layer.rs:405-431).  The gate vector is kept by atenia_moe_set_weights whenever one is given,
+ * whatever config.shared_gated says, so both conventions can be asked of one layer.  Softmax routers
+ * only (ATENIA_ERR_UNSUPPORTED for ATENIA_ROUTER_V3, whose normalisation flag is part of its config). */
+ATENIA_API int atenia_moe_forward_with(AteniaMoeLayer* layer, const void* x, int x_dtype, int T, void* out,
+                                       int out_dtype, const AteniaMoeAux* aux, void* stream, int convention);
+
 /* The block with the selection supplied by the caller instead of the router: topk_idx [T, k] (device,
  * int32, expert ids in [0, E), need not be sorted) and topk_w [T, k] (device, f32) are used as they
  * are; everything after routing is unchanged (out = sum_s w[t,s] * expert_{idx[t,s]}(x_t), slots in
@@ -153,7 +174,9 @@ ATENIA_API int atenia_moe_forward(AteniaMoeLayer* layer, const void* x, int x_dt
  * graph primitives MoeDynamicDispatch / ConditionalExpert / MoeSparseCombine
  * (src/moe/graph_op.rs:84-188, src/amg/graph.rs:5406-5566), whose selection tensor is the flat
  * [idx0, w0, idx1, w1, ...] list; the router primitives MoeRouterSoftmax / MoeTopK are
- * atenia_moe_route_from_logits.  An id outside [0, E) records ATENIA_ERR_ROUTING. */
+ * atenia_moe_route_from_logits.  An id outside [0, E) records ATENIA_ERR_ROUTING (returned by the next
+ * atenia_moe_check); such an entry gets no row and contributes nothing, and no read leaves the
+ * caller's buffers. */
 ATENIA_API int atenia_moe_forward_selected(AteniaMoeLayer* layer, const void* x, int x_dtype, int T,
                                            const int32_t* topk_idx, const float* topk_w, void* out,
                                            int out_dtype, void* stream);
@@ -185,12 +208,16 @@ ATENIA_API int atenia_moe_route_from_logits(AteniaMoeLayer* layer, const float* 
  * atenia_moe_route_from_logits.  Scratch is a fixed 256 KiB array inside the library, present on
  * every GPU that loads it; hence the limits T*k <= ATENIA_NOALLOC_MAX_ENTRIES and
  * E <= ATENIA_NOALLOC_MAX_EXPERTS, beyond which the call returns ATENIA_ERR_SCRATCH_LIMIT and does
- * nothing.  Entries whose expert id is out of range are skipped.  Asynchronous on `stream`; the
- * library calls no cudaMalloc / cudaFree / allocating routine here.
- * The first call on each device looks up the array's device address; make that first call
- * outside any stream capture.  All calls on one GPU share the array: two calls whose kernels can
- * overlap on that GPU (different streams without ordering, or different host threads) race on it;
- * order them on one stream or with events. */
+ * nothing.  Entries whose expert id is out of range get no row: their inv_perm entry is -1 and
+ * perm[expert_offsets[E] .. T*k) is left unwritten.  topk_idx, perm, inv_perm and expert_offsets
+ * must live on the CURRENT device (the scratch used is the current device's).  Asynchronous on
+ * `stream`; the library calls no cudaMalloc / cudaFree / allocating routine here.
+ * The first call on each device looks up the array's device address and keeps it for the life of
+ * the process; make that first call outside any stream capture, and do not call this entry point
+ * on a device after resetting it (cudaDeviceReset): the kept address would be stale.  All calls on
+ * one GPU share the array: two calls whose kernels can overlap on that GPU (different streams
+ * without ordering, or different host threads) race on it; order them on one stream or with
+ * events. */
 #define ATENIA_NOALLOC_MAX_ENTRIES 65536
 #define ATENIA_NOALLOC_MAX_EXPERTS 128
 ATENIA_API int atenia_moe_dispatch_noalloc(const int32_t* topk_idx, int T, int k, int E, int32_t* perm,
@@ -274,9 +301,73 @@ ATENIA_API int64_t atenia_register_resident_moe_layer(AteniaMoeLayer* layer);
 ATENIA_API int atenia_execute_real_moe_layer(int64_t layer_id, const float* input, size_t len,
                                              float* output);
 
+/* execute_real_moe_layer_with (src/moe/graph_op.rs:352-364): the same call under an explicit
+ * ATENIA_CONVENTION_* for this call only. */
+ATENIA_API int atenia_execute_real_moe_layer_with(int64_t layer_id, const float* input, size_t len, float* output,
+                                                  int convention);
+
 /* The device layer behind a registry id (NULL if unknown), for callers that keep activations on the
  * device. */
 ATENIA_API AteniaMoeLayer* atenia_get_real_moe_layer(int64_t layer_id);
+
+/* ---- numeric policy (src/moe/numeric_policy.rs:37-127) -------------------------------------------
+ * The reference picks the arithmetic of its expert matvec from ATENIA_NUMERIC_POLICY =
+ * {certified | f64, strict | f32, fast} (read once; default and any unknown value: certified), with
+ * an in-process override (set_numeric_policy / clear_numeric_policy_override).  Only `fast` sends the
+ * expert contraction to the GPU (ffn_uses_cuda, hook at src/moe/dense.rs:159-168); certified (f64
+ * accumulation) and strict (f32) stay on the reference's own CPU arms; the router accumulates in f64
+ * under every policy, as it does here.  This library is the `fast` arm and nothing else: it has no
+ * CPU code.  These functions restate the switch so that a host binds one source of truth:
+ *   atenia_numeric_policy()            the active policy (override, else environment, else certified)
+ *   atenia_numeric_policy_is_explicit  1 when an override is set or the variable names a policy
+ *   atenia_numeric_policy_gate()       ATENIA_OK when the library may serve the call: the active policy
+ *                                      is fast, or the host never selected one (calling the library
+ *                                      is then the selection); ATENIA_ERR_POLICY when the host
+ *                                      explicitly selected certified or strict
+ * The operator entry points atenia_execute_real_moe_layer[_with] apply the gate before anything else
+ * (the host then runs its own CPU arm, exactly as matvec_policy does); the device-level calls
+ * (atenia_moe_forward and friends) are explicit requests for the GPU and are not gated. */
+#define ATENIA_POLICY_CERTIFIED 0
+#define ATENIA_POLICY_STRICT 1
+#define ATENIA_POLICY_FAST 2
+ATENIA_API int atenia_numeric_policy_from_str(const char* name); /* ATENIA_POLICY_* or ATENIA_ERR_SHAPE */
+ATENIA_API const char* atenia_numeric_policy_str(int policy);
+ATENIA_API int atenia_numeric_policy(void);
+ATENIA_API int atenia_numeric_policy_is_explicit(void);
+ATENIA_API int atenia_set_numeric_policy(int policy);
+ATENIA_API void atenia_clear_numeric_policy_override(void);
+ATENIA_API int atenia_numeric_policy_ffn_uses_f32(int policy);
+ATENIA_API int atenia_numeric_policy_ffn_uses_cuda(int policy);
+ATENIA_API int atenia_numeric_policy_gate(void);
+
+/* ---- expert residency planner ---------------------------------------------------------------------
+ * The reference keeps experts in a RAM / NVMe tier behind a per-layer LRU cache whose capacity is
+ * clamp(budget / (n_layers * bytes_per_expert), 1, E) (auto_expert_cache_capacity,
+ * src/moe/residency.rs:201-211; resolved per model at src/moe/runtime.rs:559-584).  Here the tier is
+ * HBM and a layer is either fully resident on its rank or sharded over more ranks, so the planner
+ * answers: for `n_layers` layers of this configuration (max_tokens included: the workspace counts)
+ * and `hbm_budget_bytes` per GPU (e.g. what cudaMemGetInfo reports free), which is the smallest
+ * ep_world in {1, 2, 4, 8} dividing E in which every rank holds its E / ep_world experts of every
+ * layer?  Returns ATENIA_OK with the plan, or ATENIA_ERR_CAPACITY when even 8 ranks do not hold the
+ * model (the plan then describes the largest world tried; resident_experts_per_layer < experts_per_rank
+ * is the reference's capacity rule applied to the budget left after the fixed costs).  Host arithmetic
+ * only; cfg.ep_rank / cfg.ep_world are ignored. */
+typedef struct AteniaResidencyPlan {
+  int32_t min_ep_world;               /* smallest world that fits (or the largest tried on failure) */
+  int32_t experts_per_rank;           /* E / min_ep_world */
+  int32_t resident_experts_per_layer; /* experts of each layer the budget holds per rank in that world */
+  int32_t reserved;
+  uint64_t bytes_per_expert;          /* 3*F*d bytes (bf16: x2) plus (2F+d) f32 scales for int8 */
+  uint64_t fixed_bytes_per_rank;      /* shared experts + router + workspace, all layers */
+  uint64_t bytes_per_rank;            /* fixed + experts_per_rank * bytes_per_expert * n_layers */
+} AteniaResidencyPlan;
+ATENIA_API int atenia_moe_plan_residency(const AteniaMoeConfig* cfg, int n_layers, uint64_t hbm_budget_bytes,
+                                         AteniaResidencyPlan* plan);
+/* auto_expert_cache_capacity itself (src/moe/residency.rs:201-211). */
+ATENIA_API uint64_t atenia_auto_expert_cache_capacity(uint64_t budget_bytes, uint64_t n_layers,
+                                                      uint64_t per_expert_bytes, uint64_t num_experts);
+/* Device bytes atenia_moe_create allocates for this configuration (0 for an invalid one). */
+ATENIA_API uint64_t atenia_moe_workspace_bytes(const AteniaMoeConfig* cfg);
 
 /* ---- layer stack ------------------------------------------------------------------------------
  * RealMoeStack::forward (src/moe/stack.rs:197-210): x <- layer_l(x) for l = 0..n-1, every layer with

@@ -1,8 +1,23 @@
-"""Dense W8A16 quantiser and truncating dequant on the GPU, bit for bit against the oracle."""
+"""Dense W8A16 quantiser and truncating dequant on the GPU, bit for bit against the oracle.
+
+NaN results (0 * inf on a column whose scale overflowed) are compared as NaNs: the sign and payload
+of a NaN a multiply produces differ between x86 (0xFFC0 after truncation) and CUDA (0x7FFF), and
+neither the reference's kernel nor its CPU code defines one.  Every other value is compared by bits.
+"""
 import numpy as np
 import pytest
 
 pytestmark = pytest.mark.gpu
+
+
+def assert_bf16_bits_equal(got_u16, ref_u16):
+    """Bit equality of bf16 patterns, with any NaN equal to any NaN."""
+    got_u16 = np.asarray(got_u16, dtype=np.uint16)
+    ref_u16 = np.asarray(ref_u16, dtype=np.uint16)
+    nan_got = ((got_u16 & 0x7F80) == 0x7F80) & ((got_u16 & 0x007F) != 0)
+    nan_ref = ((ref_u16 & 0x7F80) == 0x7F80) & ((ref_u16 & 0x007F) != 0)
+    np.testing.assert_array_equal(nan_got, nan_ref)
+    np.testing.assert_array_equal(got_u16[~nan_ref], ref_u16[~nan_ref])
 
 
 @pytest.mark.parametrize("K,N,g", [(4, 1, 0), (8, 3, 0), (256, 7, 128), (200, 7, 128), (77, 19, 32),
@@ -25,7 +40,9 @@ def test_quantiser_and_dequant_match_oracle(K, N, g):
     np.testing.assert_array_equal(q.cpu().numpy(), q_ref)
     out = int8_to_bf16_per_group(q, s, g)
     ref = orc.int8_to_bf16_per_group(q_ref, s_ref, g)
-    np.testing.assert_array_equal(out.view(torch.int16).cpu().numpy().view(np.uint16), ref)
+    assert_bf16_bits_equal(out.view(torch.int16).cpu().numpy().view(np.uint16), ref)
+    if K >= 8 and N >= 3:
+        assert np.isnan(w.numpy()).any() and np.isinf(w.numpy()).any()  # the special values stay in the case
 
 
 def test_misaligned_views_take_the_scalar_path():
@@ -49,8 +66,8 @@ def test_misaligned_views_take_the_scalar_path():
     q_ref, s_ref = orc.absmax_per_group_symmetric(w[1:].numpy().reshape(K, N), g)
     np.testing.assert_array_equal(q[1:].cpu().numpy().reshape(K, N), q_ref)
     np.testing.assert_array_equal(s[1:].cpu().numpy().reshape(-1, N), s_ref)
-    np.testing.assert_array_equal(out[1:].cpu().numpy().view(np.uint16).reshape(K, N),
-                                  orc.int8_to_bf16_per_group(q_ref, s_ref, g))
+    assert_bf16_bits_equal(out[1:].cpu().numpy().view(np.uint16).reshape(K, N),
+                           orc.int8_to_bf16_per_group(q_ref, s_ref, g))
 
 
 def test_argument_errors_and_empty():

@@ -9,8 +9,11 @@ scratch from a larger call does not leak into a smaller one, and that requests b
 scratch are refused.  It is collected last so that a run that stops at the first failure has already
 run every other test; it also passes when run alone in a fresh process.
 """
+import numpy as np
 import pytest
 import torch
+
+from oracle import oracle as orc
 
 pytestmark = pytest.mark.gpu
 
@@ -38,6 +41,11 @@ def test_noalloc_dispatch_matches_layer_dispatch_twice_in_a_row():
         assert torch.equal(off, off_ref)
         assert torch.equal(perm, perm_ref)
         assert torch.equal(inv, inv_ref)
+        # and against the CPU statement of the same order, which shares no code with the library
+        o_off, o_perm, o_inv = orc.dispatch_permutation(idx.cpu().numpy(), E)
+        np.testing.assert_array_equal(off.cpu().numpy(), o_off)
+        np.testing.assert_array_equal(perm.cpu().numpy(), o_perm)
+        np.testing.assert_array_equal(inv.cpu().numpy(), o_inv)
 
 
 def test_noalloc_dispatch_refuses_requests_beyond_its_scratch():
