@@ -64,8 +64,8 @@ struct RouterArgs {
   float* gate_scale;   // [T] or null
   float* logits;       // [T, E] or null
   DeviceError* err;
-  int variant;         // 0: CUDA-core f64 kernel (router.cu); 1: f64 tensor-core kernel (router_dmma.cu);
-                       // 2: split-k kernel for small batches (router_splitk.cu) when T <= sk_tokens
+  int variant;         // -1: by size; 0: CUDA-core f64 kernel (router.cu); 1: f64 tensor-core kernel
+                       // (router_dmma.cu); 2: split-k kernel (router_splitk.cu) when T <= sk_tokens
   double* sk_part;     // variant 2 workspace (router_splitk_workspace), else null
   double* sk_gate;
   unsigned int* sk_counters;

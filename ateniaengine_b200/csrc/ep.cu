@@ -219,10 +219,15 @@ int ep_forward_exchange(AteniaMoeLayer* L, int T, cudaStream_t s) {
   if (ro > L->recv_cap) return ATENIA_ERR_CAPACITY;
   int rc = exchange(comm, rank, G, L->x_perm, s_off, s_cnt, L->recv_x, r_off, r_cnt, d, s);
   if (rc) return rc;
+  if (L->timing) cudaEventRecord(L->ph[2], s);
+  L->last_recv_rows = (int)ro;
   rc = run_expert_gemms(L, L->tm_recv_x, L->tm_recv_h, L->recv_x, L->recv_h, L->recv_y, L->d_group_offsets,
                         L->n_groups, (int)ro, s, &L->tm_recv_x_r64, &L->tm_recv_h_r64);
   if (rc) return rc;
-  return exchange(comm, rank, G, L->recv_y, r_off, r_cnt, L->y_perm, s_off, s_cnt, d, s);
+  if (L->timing) cudaEventRecord(L->ph[3], s);
+  rc = exchange(comm, rank, G, L->recv_y, r_off, r_cnt, L->y_perm, s_off, s_cnt, d, s);
+  if (L->timing) cudaEventRecord(L->ph[4], s);
+  return rc;
 }
 
 // Replicated tokens (decode): every rank holds the same batch and has routed and sorted it
@@ -236,11 +241,14 @@ int ep_forward_replicated(AteniaMoeLayer* L, int n_rows, cudaStream_t s) {
   if (n_rows <= 0) return ATENIA_OK;
   const int d = L->cfg.d_model;
   ATENIA_CUDA_TRY(cudaMemsetAsync(L->y_perm, 0, (size_t)n_rows * d * sizeof(__nv_bfloat16), s));
+  if (L->timing) cudaEventRecord(L->ph[2], s);
   int rc = run_expert_gemms(L, L->tm_x_perm, L->tm_recv_h, L->x_perm, L->recv_h, L->y_perm,
                             L->expert_offsets + L->e_begin, L->e_local, n_rows, s, &L->tm_x_perm_r64,
                             &L->tm_recv_h_r64);
   if (rc) return rc;
+  if (L->timing) cudaEventRecord(L->ph[3], s);
   NCCL_TRY(ncclAllReduce(L->y_perm, L->y_perm, (size_t)n_rows * d, ncclBfloat16, ncclSum, L->ep->comm, s));
+  if (L->timing) cudaEventRecord(L->ph[4], s);
   return ATENIA_OK;
 }
 
@@ -281,16 +289,19 @@ int ep_direct_finish(AteniaMoeLayer* L, cudaStream_t s) {
   const int G = c.ep_world, El = L->e_local, d = c.d_model;
   ncclComm_t comm = L->ep->comm;
   NCCL_TRY(ncclAllReduce(L->d_bar, L->d_bar, 1, ncclInt32, ncclSum, comm, s));
+  if (L->timing) cudaEventRecord(L->ph[2], s);
   // the number of rows received is known on the device only: size by the buffer.
   // one GEMM group per local expert: its rows from all sources are contiguous
   int rc = run_expert_gemms(L, L->tm_recv_x, L->tm_recv_h, L->recv_x, L->recv_h, L->recv_y, L->d_gemm_offsets, El,
                             L->recv_cap, s, &L->tm_recv_x_r64, &L->tm_recv_h_r64);
   if (rc) return rc;
+  if (L->timing) cudaEventRecord(L->ph[3], s);
   ep_return_kernel<<<L->num_sms * 16, kEpRowWarps * 32, 0, s>>>(L->recv_y, L->d_group_offsets, L->d_src_base, L->d_peer_y_perm,
                                                   L->n_groups, G, d, L->rows_cap, L->d_err);
   count_launch();
   ATENIA_CUDA_TRY(cudaGetLastError());
   NCCL_TRY(ncclAllReduce(L->d_bar, L->d_bar, 1, ncclInt32, ncclSum, comm, s));
+  if (L->timing) cudaEventRecord(L->ph[4], s);
   return ATENIA_OK;
 }
 

@@ -30,9 +30,9 @@ struct AteniaMoeLayer {
   int pair_mode = 0;
   // bf16, on request (ATENIA_MOE_BF16_DECODE=1): the stream-K decode kernel when a call has <= 128 rows
   bool bf16_decode = false;
-  // on request (ATENIA_MOE_ROUTER_DMMA=1): router logits on the f64 tensor cores (router_dmma.cu)
-  // ... or (ATENIA_MOE_ROUTER_SPLITK=1) the split-k router for batches of at most sk_tokens (router_splitk.cu)
-  int router_variant = 0;
+  // router kernel: -1 by size, 0 CUDA cores (router.cu), 1 f64 tensor cores (router_dmma.cu),
+  // 2 split-k for batches of at most sk_tokens (router_splitk.cu); see atenia_moe_create
+  int router_variant = -1;
   double* sk_part = nullptr;
   double* sk_gate = nullptr;
   unsigned int* sk_counters = nullptr;
@@ -97,6 +97,7 @@ struct AteniaMoeLayer {
   std::shared_ptr<atenia::EpComm> ep;  // layers of one stack may share a communicator (atenia_moe_ep_attach)
   bool ep_replicated = false;          // every rank holds the same tokens (atenia_moe_ep_set_token_layout)
   int recv_cap = 0;                    // rows of the receive-side buffers
+  int last_recv_rows = -1;             // rows this rank's experts received in the last token-sharded forward
   __nv_bfloat16* recv_x = nullptr;     // [recv_cap, d]
   __nv_bfloat16* recv_h = nullptr;     // [recv_cap, F]
   __nv_bfloat16* recv_y = nullptr;     // [recv_cap, d]
@@ -118,6 +119,11 @@ struct AteniaMoeLayer {
   // timing
   cudaEvent_t ev[8] = {};
   bool ev_valid[4] = {false, false, false, false};
+  // phase marks of one forward (recorded only while timing is enabled): 0 start, 1 routed and sorted
+  // (rows gathered), 2 rows at their experts (after the dispatch exchange), 3 expert GEMMs done,
+  // 4 results back (after the return exchange), 5 end
+  cudaEvent_t ph[6] = {};
+  bool ph_valid = false;
 };
 
 namespace atenia {

@@ -3,6 +3,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <new>
+#include <string>
 
 #include "layer.cuh"
 #include "v3_route.cuh"
@@ -235,10 +236,15 @@ int atenia_moe_create(const AteniaMoeConfig* cfg, AteniaMoeLayer** out) {
   L->use_check_gemm = std::getenv("ATENIA_MOE_CHECK_GEMM") && std::atoi(std::getenv("ATENIA_MOE_CHECK_GEMM")) != 0;
   L->w8_mode = std::getenv("ATENIA_MOE_W8_MODE") ? std::atoi(std::getenv("ATENIA_MOE_W8_MODE")) : 0;
   L->pair_mode = std::getenv("ATENIA_MOE_PAIR_MODE") ? std::atoi(std::getenv("ATENIA_MOE_PAIR_MODE")) : 0;
-  L->router_variant = (std::getenv("ATENIA_MOE_ROUTER_DMMA") && std::atoi(std::getenv("ATENIA_MOE_ROUTER_DMMA")) != 0) ? 1 : 0;
-  if (L->router_variant == 0 && std::getenv("ATENIA_MOE_ROUTER_SPLITK") &&
-      std::atoi(std::getenv("ATENIA_MOE_ROUTER_SPLITK")) != 0)
-    L->router_variant = 2;
+  // Router kernel: by default the split-k kernel for batches of at most 128 tokens (many CTAs share one
+  // token block's dot products), the f64 tensor-core kernel for 32 experts and more, the CUDA-core
+  // kernel otherwise.  ATENIA_MOE_ROUTER = scalar | dmma | splitk pins one (tests, A/B runs); a pinned
+  // split-k serves batches up to 1024 tokens and hands larger ones to the CUDA-core kernel.
+  {
+    const char* rv = std::getenv("ATENIA_MOE_ROUTER");
+    const std::string r(rv ? rv : "");
+    L->router_variant = r == "scalar" ? 0 : r == "dmma" ? 1 : r == "splitk" ? 2 : -1;
+  }
   L->bf16_decode = c.weight_dtype == ATENIA_W_BF16 && std::getenv("ATENIA_MOE_BF16_DECODE") &&
                    std::atoi(std::getenv("ATENIA_MOE_BF16_DECODE")) != 0;
   const size_t Tm = (size_t)c.max_tokens, k = (size_t)c.experts_per_token, E = (size_t)c.num_experts;
@@ -284,8 +290,11 @@ int atenia_moe_create(const AteniaMoeConfig* cfg, AteniaMoeLayer** out) {
   TRY_ALLOC(L->d_tm_down, (size_t)L->n_groups);
   TRY_ALLOC(L->d_tm_shared, 3);
   if (L->bf16_decode) TRY_ALLOC(L->splitk_ws, (size_t)L->num_sms * 2 * kW8SplitKSlotFloats);
-  if (L->router_variant == 2) {
-    L->sk_tokens = c.max_tokens < 1024 ? c.max_tokens : 1024;
+  {
+    const int sk_cap = L->router_variant == 2 ? 1024 : (L->router_variant == -1 ? 128 : 0);
+    L->sk_tokens = c.max_tokens < sk_cap ? c.max_tokens : sk_cap;
+  }
+  if (L->sk_tokens > 0) {
     size_t np = 0, ng = 0, nc = 0;
     router_splitk_workspace(L->sk_tokens, c.d_model, c.num_experts, &np, &ng, &nc);
     TRY_ALLOC(L->sk_part, np);
@@ -360,6 +369,7 @@ int atenia_moe_create(const AteniaMoeConfig* cfg, AteniaMoeLayer** out) {
     return rc;
   }
   for (int i = 0; i < 8; ++i) cudaEventCreate(&L->ev[i]);
+  for (int i = 0; i < 6; ++i) cudaEventCreate(&L->ph[i]);
   *out = L;
   return ATENIA_OK;
 }
@@ -383,6 +393,8 @@ int atenia_moe_destroy(AteniaMoeLayer* L) {
   if (L->h_counts_all) cudaFreeHost(L->h_counts_all);
   for (int i = 0; i < 8; ++i)
     if (L->ev[i]) cudaEventDestroy(L->ev[i]);
+  for (int i = 0; i < 6; ++i)
+    if (L->ph[i]) cudaEventDestroy(L->ph[i]);
   delete L;
   return ATENIA_OK;
 }
@@ -561,6 +573,7 @@ static int forward_impl(AteniaMoeLayer* L, const void* x, int x_dtype, int T, vo
   const bool gated = convention == ATENIA_CONVENTION_LAYER ? L->has_gate_vec
                                                            : (convention == ATENIA_CONVENTION_HF_QWEN && L->gate_vec_bound);
 
+  if (L->timing) cudaEventRecord(L->ph[0], s);
   RouterArgs ra{};
   ra.x = x;
   ra.x_is_f32 = x_f32;
@@ -618,8 +631,10 @@ static int forward_impl(AteniaMoeLayer* L, const void* x, int x_dtype, int T, vo
   rc = launch_gather_rows(x, x_f32, L->perm, L->expert_offsets + c.num_experts, direct ? 0 : n, k, c.d_model,
                           L->x_perm, need_xb ? L->x_bf16 : nullptr, T, s);
   if (rc) return rc;
+  if (L->timing) cudaEventRecord(L->ph[1], s);
 
   if (c.ep_world == 1) {
+    if (L->timing) cudaEventRecord(L->ph[2], s);
     rc = run_expert_gemms(L, L->tm_x_perm, L->tm_h, L->x_perm, L->h, L->y_perm, L->expert_offsets,
                           c.num_experts, n, s, &L->tm_x_perm_r64, &L->tm_h_r64);
   } else if (L->ep_replicated) {
@@ -637,6 +652,10 @@ static int forward_impl(AteniaMoeLayer* L, const void* x, int x_dtype, int T, vo
     rc = ep_forward_exchange(L, T, s);
   }
   if (rc) return rc;
+  if (L->timing && c.ep_world == 1) {
+    cudaEventRecord(L->ph[3], s);  // one GPU: no exchange either way
+    cudaEventRecord(L->ph[4], s);
+  }
 
   if (L->has_shared && T > 0 && !direct) {
     const __nv_bfloat16* xb = x_f32 ? L->x_bf16 : static_cast<const __nv_bfloat16*>(x);
@@ -658,6 +677,10 @@ static int forward_impl(AteniaMoeLayer* L, const void* x, int x_dtype, int T, vo
   ca.d = c.d_model;
   rc = launch_combine(ca, s);
   if (rc) return rc;
+  if (L->timing) {
+    cudaEventRecord(L->ph[5], s);
+    L->ph_valid = true;
+  }
 
   if (aux) {
     if (aux->topk_idx)
@@ -772,7 +795,18 @@ int atenia_moe_enable_timing(AteniaMoeLayer* L, int enable) {
   if (!L) return ATENIA_ERR_NULL;
   L->timing = enable != 0;
   for (bool& v : L->ev_valid) v = false;
+  L->ph_valid = false;
   return ATENIA_OK;
+}
+
+int atenia_moe_last_recv_rows(AteniaMoeLayer* L) { return L ? L->last_recv_rows : -1; }
+
+float atenia_moe_last_phase_ms(AteniaMoeLayer* L, int which) {
+  if (!L || which < 0 || which > 5 || !L->ph_valid) return -1.0f;
+  float ms = -1.0f;
+  const int a = which == 5 ? 0 : which, b = which == 5 ? 5 : which + 1;
+  if (cudaEventElapsedTime(&ms, L->ph[a], L->ph[b]) != cudaSuccess) return -1.0f;
+  return ms;
 }
 
 float atenia_moe_last_gemm_ms(AteniaMoeLayer* L, int which) {

@@ -8,26 +8,28 @@
 // f64 values of the bf16 / f32 operands, accumulation is f64, only the order of the additions
 // differs from the serial loop (last bits of a 53-bit sum, far below the rounding to f32).
 //
-// One CTA (8 warps) handles 32 tokens:
-//   * per chunk of 32 values of k the CTA stages x[32, 32] and W_router[E, 32] as f64 in shared memory
+// One CTA (8 warps) handles 8 MT tokens (MT = 4, 2 or 1 eight-token tiles, by batch size):
+//   * per chunk of 32 values of k the CTA stages x[8 MT, 32] and W_router[E, 32] as f64 in shared memory
 //     (row pitch 36 doubles: the 8 rows x 4 columns a fragment load touches fall in distinct banks);
 //     global loads of the next chunk are in flight during the arithmetic of the current one;
-//   * warps are arranged NW_N x NW_K: a warp owns NTW 8-expert tiles for all four 8-token tiles and
-//     every NW_K-th k-step of the chunk; its accumulators are 4 x NTW x 2 doubles per lane;
+//   * warps are arranged NW_N x NW_K: a warp owns NTW 8-expert tiles for all MT 8-token tiles and
+//     every NW_K-th k-step of the chunk; its accumulators are MT x NTW x 2 doubles per lane;
 //   * the k-slices are folded through shared memory in warp order (fixed), the bias joins the f64
-//     sum, logits are rounded to f32 and each warp routes four tokens (route_one_warp).
+//     sum, logits are rounded to f32 and the warps route the tokens (route_one_warp).
 #include "route_warp.cuh"
 
 namespace atenia {
 namespace {
 
 constexpr int kDW = 8;         // warps per CTA
-constexpr int kDTok = 32;      // tokens per CTA
 constexpr int kDKC = 32;       // k values per chunk
 constexpr int kDLD = kDKC + 4; // shared-memory row pitch in doubles
 
-template <int E_T>
+// MT: 8-token tiles per CTA (kDTok = 8 MT tokens).  Large batches take 4 (an expert fragment feeds four
+// products); smaller ones take 2 or 1 so that the grid still covers the SMs.
+template <int E_T, int MT>
 struct DmmaCfg {
+  static constexpr int kDTok = 8 * MT;
   static constexpr int NT = E_T / 8;               // 8-expert tiles
   static constexpr int NW_N = NT < kDW ? NT : kDW; // warps across expert tiles
   static constexpr int NW_K = kDW / NW_N;          // warps across k-steps
@@ -51,10 +53,11 @@ __device__ __forceinline__ void dmma884(double (&c)[2], double a, double b) {
                : "d"(a), "d"(b));
 }
 
-template <int E_T>
+template <int E_T, int MT>
 __global__ void __launch_bounds__(kDW * 32) router_dmma_kernel(RouterArgs a) {
-  using C = DmmaCfg<E_T>;
+  using C = DmmaCfg<E_T, MT>;
   constexpr int NTW = C::NTW;
+  constexpr int kDTok = C::kDTok;
   extern __shared__ __align__(16) unsigned char smem[];
   // main-loop view
   double (*xs)[kDLD] = reinterpret_cast<double (*)[kDLD]>(smem);
@@ -74,9 +77,9 @@ __global__ void __launch_bounds__(kDW * 32) router_dmma_kernel(RouterArgs a) {
   const int ngrp = warp % C::NW_N, kslice = warp / C::NW_N;
   const int frow = lane >> 2, fcol = lane & 3;
 
-  double acc[4][NTW][2];
+  double acc[MT][NTW][2];
 #pragma unroll
-  for (int mt = 0; mt < 4; ++mt)
+  for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
     for (int j = 0; j < NTW; ++j) acc[mt][j][0] = acc[mt][j][1] = 0.0;
   double gacc = 0.0;  // lane t of warp w: gate dot product of token t over the k values 4w..4w+3 of each chunk
@@ -90,7 +93,7 @@ __global__ void __launch_bounds__(kDW * 32) router_dmma_kernel(RouterArgs a) {
   auto fetch = [&](int k0) {
     const int kk = k0 + s_k, tg = t0 + s_row;
     xq = make_uint4(0, 0, 0, 0);
-    if (tg < a.T && kk < d) {  // d is a multiple of 16: a group of 4 is all in or all out
+    if (s_row < kDTok && tg < a.T && kk < d) {  // d is a multiple of 16: a group of 4 is all in or all out
       if (a.x_is_f32) {
         xq = *reinterpret_cast<const uint4*>(static_cast<const float*>(a.x) + (size_t)tg * d + kk);
       } else {
@@ -117,9 +120,11 @@ __global__ void __launch_bounds__(kDW * 32) router_dmma_kernel(RouterArgs a) {
       } else {
         v[0] = bf16lo(xq.x); v[1] = bf16hi(xq.x); v[2] = bf16lo(xq.y); v[3] = bf16hi(xq.y);
       }
-      double2* px = reinterpret_cast<double2*>(&xs[s_row][s_k]);
-      px[0] = make_double2((double)v[0], (double)v[1]);
-      px[1] = make_double2((double)v[2], (double)v[3]);
+      if (s_row < kDTok) {
+        double2* px = reinterpret_cast<double2*>(&xs[s_row][s_k]);
+        px[0] = make_double2((double)v[0], (double)v[1]);
+        px[1] = make_double2((double)v[2], (double)v[3]);
+      }
 #pragma unroll
       for (int r = 0; r < WV; ++r) {
         const int e = s_row + 32 * r;
@@ -135,21 +140,21 @@ __global__ void __launch_bounds__(kDW * 32) router_dmma_kernel(RouterArgs a) {
 #pragma unroll
     for (int i = 0; i < kDKC / 4 / C::NW_K; ++i) {
       const int kk = (kslice + i * C::NW_K) * 4 + fcol;
-      double af[4];
+      double af[MT];
 #pragma unroll
-      for (int mt = 0; mt < 4; ++mt) af[mt] = xs[mt * 8 + frow][kk];
+      for (int mt = 0; mt < MT; ++mt) af[mt] = xs[mt * 8 + frow][kk];
 #pragma unroll
       for (int j = 0; j < NTW; ++j) {
         const double bf = ws[(ngrp * NTW + j) * 8 + frow][kk];
 #pragma unroll
-        for (int mt = 0; mt < 4; ++mt) dmma884(acc[mt][j], af[mt], bf);
+        for (int mt = 0; mt < MT; ++mt) dmma884(acc[mt][j], af[mt], bf);
       }
     }
     if (a.gate_vec) {
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         const int kc = warp * 4 + c;
-        if (k0 + kc < d) gacc = fma((double)__ldg(a.gate_vec + k0 + kc), xs[lane][kc], gacc);
+        if (lane < kDTok && k0 + kc < d) gacc = fma((double)__ldg(a.gate_vec + k0 + kc), xs[lane][kc], gacc);
       }
     }
   }
@@ -158,7 +163,7 @@ __global__ void __launch_bounds__(kDW * 32) router_dmma_kernel(RouterArgs a) {
   for (int ksl = 0; ksl < C::NW_K; ++ksl) {
     if (kslice == ksl) {
 #pragma unroll
-      for (int mt = 0; mt < 4; ++mt)
+      for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
         for (int j = 0; j < NTW; ++j)
 #pragma unroll
@@ -169,7 +174,7 @@ __global__ void __launch_bounds__(kDW * 32) router_dmma_kernel(RouterArgs a) {
     }
     __syncthreads();
   }
-  if (a.gate_vec) gate_s[warp][lane] = gacc;
+  if (a.gate_vec && lane < kDTok) gate_s[warp][lane] = gacc;
   // logits: bias joins the f64 sum before the rounding to f32
   for (int i = threadIdx.x; i < kDTok * E; i += blockDim.x) {
     const int t = i / E, e = i - t * E;
@@ -206,15 +211,23 @@ __global__ void __launch_bounds__(kDW * 32) router_dmma_kernel(RouterArgs a) {
   }
 }
 
-template <int E_T>
-int launch_one(const RouterArgs& a, cudaStream_t s) {
-  using C = DmmaCfg<E_T>;
+template <int E_T, int MT>
+int launch_mt(const RouterArgs& a, cudaStream_t s) {
+  using C = DmmaCfg<E_T, MT>;
   static bool attr_set[kMaxDevices] = {};
   if (C::kBytes > 48 * 1024 && first_use_on_current_device(attr_set)) {
-    ATENIA_CUDA_TRY(cudaFuncSetAttribute(router_dmma_kernel<E_T>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kBytes));
+    ATENIA_CUDA_TRY(cudaFuncSetAttribute(router_dmma_kernel<E_T, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kBytes));
   }
-  router_dmma_kernel<E_T><<<(a.T + kDTok - 1) / kDTok, kDW * 32, C::kBytes, s>>>(a);
+  router_dmma_kernel<E_T, MT><<<(a.T + C::kDTok - 1) / C::kDTok, kDW * 32, C::kBytes, s>>>(a);
   return (int)cudaGetLastError();
+}
+
+template <int E_T>
+int launch_one(const RouterArgs& a, cudaStream_t s) {
+  // tokens per CTA by batch size: the grid should cover the SMs a few times over
+  if (a.T >= 4096) return launch_mt<E_T, 4>(a, s);
+  if (a.T >= 1024) return launch_mt<E_T, 2>(a, s);
+  return launch_mt<E_T, 1>(a, s);
 }
 
 }  // namespace

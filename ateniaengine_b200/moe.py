@@ -315,6 +315,13 @@ class RealMoeLayer:
     def last_gemm_ms(self, which):
         return float(_lib.lib().atenia_moe_last_gemm_ms(self._h, which))
 
+    def last_phase_ms(self, which):
+        """0 route+permute+gather, 1 rows out (EP), 2 routed GEMMs, 3 rows back (EP), 4 shared+combine, 5 all."""
+        return float(_lib.lib().atenia_moe_last_phase_ms(self._h, which))
+
+    def last_recv_rows(self):
+        return int(_lib.lib().atenia_moe_last_recv_rows(self._h))
+
 
 # ---- operator registry (host buffers) ---------------------------------------------------------
 

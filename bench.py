@@ -34,13 +34,12 @@ METRIC = "moe_layer_tokens_per_s"
 UNIT = "tokens/s"
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the routed gate/up kernel, from the ncu
-# capture summarised under profiles/ (scaled to this workload by rows where the capture was smaller).
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the routed gate/up + SwiGLU kernel the
+# workload selects, from one-pass ncu captures of this command (kernel name -> bytes).
 NCU_TRAFFIC_BYTES = {
-    # profiles/grouped_gemm_tcgen05_mixtral_t4096_dram.md: 1.95 GB read + 227.5 MB written
-    "mixtral:4096": 2.18e9,
-    # profiles/grouped_gemm_tcgen05_mixtral_t512.md: 1.904 GB read + 29.9 MB written
-    "mixtral:512": 1.934e9,
+    # single-CTA kernel: 1.95 GB read + 227.5 MB written at 4096 tokens; 1.904 GB + 29.9 MB at 512
+    "mixtral:4096:grouped_gemm_tcgen05_kernel": 2.18e9,
+    "mixtral:512:grouped_gemm_tcgen05_kernel": 1.934e9,
 }
 
 
@@ -266,6 +265,193 @@ def arm_watchdog(seconds, what):
     return t
 
 
+def host_threads():
+    """Host cores this process may use.  torchrun exports OMP_NUM_THREADS=1 to its ranks; the CPU arm
+    must not inherit that, so the count is passed to the oracle explicitly."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
+def layer_roofline(shape, T, touched, peaks, int8):
+    """Whole-forward target on one GPU: the slower of the expert flops at the measured tensor peak and
+    the bytes that must cross HBM (weights of the experts that got a row, router, activations in and
+    out) at the measured copy rate."""
+    d, F, Fs, E, k = shape.d_model, shape.d_ff, shape.shared_d_ff, shape.num_experts, shape.top_k
+    flops = T * (k * 6.0 * d * F + 6.0 * d * Fs + 2.0 * d * E)
+    b = 1 if int8 else 2
+    wbytes = touched * 3.0 * d * F * b + 3.0 * d * Fs * b + E * d * 4.0
+    if int8:
+        wbytes += touched * (2 * F + d) * 4.0 + (2 * Fs + d) * 4.0 * (1 if Fs else 0)
+    abytes = 2.0 * T * d * 2
+    t_c = flops / (peaks["bf16_tflops"] * 1e12)
+    t_h = (wbytes + abytes) / (peaks["hbm_gbs"] * 1e9)
+    return {"flops": flops, "hbm_bytes": wbytes + abytes, "t_tensor_ms": t_c * 1e3, "t_hbm_ms": t_h * 1e3,
+            "bound": "tensor" if t_c >= t_h else "hbm", "target_ms": max(t_c, t_h) * 1e3}
+
+
+class EpGroup:
+    """torch.distributed plumbing of one benchmark process (one rank per GPU)."""
+
+    def __init__(self, gpus):
+        import torch
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+        torch.cuda.set_device(self.local_rank)
+        self.dev = torch.device("cuda", self.local_rank)
+        self.dist = None
+        if gpus > 1:
+            import torch.distributed as dist
+            dist.init_process_group("nccl", device_id=self.dev)
+            self.dist = dist
+
+    def sync(self):
+        import torch
+        torch.cuda.synchronize()
+        if self.dist is not None:
+            self.dist.barrier()
+            torch.cuda.synchronize()
+
+    def max_over_ranks(self, v):
+        import torch
+        if self.dist is None:
+            return float(v)
+        t = torch.tensor([float(v)], device=self.dev)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def gather_floats(self, vals):
+        """[world, len(vals)] list of every rank's values."""
+        import torch
+        t = torch.tensor([float(v) for v in vals], device=self.dev)
+        if self.dist is None:
+            return [t.tolist()]
+        out = [torch.empty_like(t) for _ in range(self.world)]
+        self.dist.all_gather(out, t)
+        return [o.tolist() for o in out]
+
+    def join_ep(self, layer, direct=False):
+        import ctypes as C
+
+        import torch
+        from ateniaengine_b200 import _lib
+        nb = _lib.lib().atenia_moe_ep_unique_id_bytes()
+        idt = torch.zeros(nb, dtype=torch.uint8, device=self.dev)
+        if self.rank == 0:
+            buf = C.create_string_buffer(nb)
+            _lib.check(_lib.lib().atenia_moe_ep_get_unique_id(buf), "ep_get_unique_id")
+            idt = torch.frombuffer(bytearray(buf.raw), dtype=torch.uint8).to(self.dev)
+        self.dist.broadcast(idt, 0)
+        layer.ep_init(bytes(idt.cpu().numpy().tobytes()))
+        if direct:
+            mine = torch.frombuffer(bytearray(layer.ep_ipc_export()), dtype=torch.uint8).to(self.dev)
+            blobs = [torch.empty_like(mine) for _ in range(self.world)]
+            self.dist.all_gather(blobs, mine)
+            layer.ep_ipc_import(b"".join(bytes(b.cpu().numpy().tobytes()) for b in blobs))
+
+    def close(self):
+        if self.dist is not None:
+            self.dist.barrier()
+            self.dist.destroy_process_group()
+
+
+def time_steps(grp, fn, steps):
+    """ms per step of `steps` calls of fn, CUDA events on the current stream, barrier + device sync on
+    both sides, max over ranks."""
+    import torch
+    grp.sync()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    grp.sync()
+    return grp.max_over_ranks(e0.elapsed_time(e1) / steps)
+
+
+def measure_record(grp, name, T_total, args, peaks, seed=2, direct=False):
+    """One extra workload measured like the headline one (warm-up, K steps, CUDA events, max over
+    ranks): tokens/s of the whole job and the fraction of the single-GPU-equivalent roofline.  At N > 1
+    the batch of T_total tokens is split over the ranks (strong scaling) and rank 0 also times the
+    unsharded layer on the whole batch in the same run."""
+    import torch
+    from ateniaengine_b200 import synth
+    shape = synth.SHAPES[name]
+    G = grp.world if grp.dist is not None else 1
+    T = T_total // G
+    el = shape.num_experts // G
+    w = synth.make_weights(shape, seed, grp.dev, experts=(grp.rank * el, el) if G > 1 else None)
+    x = synth.make_activations(shape, seed + grp.rank, grp.dev, tokens=T)
+    layer = synth.build_layer(shape, w, max_tokens=T, ep_rank=grp.rank if G > 1 else 0, ep_world=G)
+    if G > 1:
+        grp.join_ep(layer, direct=direct)
+    out = torch.empty_like(x)
+    fn = lambda: layer.forward(x, out=out)
+    for _ in range(args.warmup):
+        fn()
+    layer.check()
+    layer.enable_timing(True)
+    ms = time_steps(grp, fn, args.steps)
+    layer.check()
+    phases = [layer.last_phase_ms(i) for i in range(6)]
+    recv_rows = layer.last_recv_rows() if G > 1 and not direct else T * shape.top_k
+    layer.enable_timing(False)
+    _, aux = layer.forward(x, aux=True, sync=True)
+    touched = int(torch.unique(aux["topk_idx"]).numel())
+    per_rank = grp.gather_floats([recv_rows] + phases)
+    rec = {"workload": f"{shape.name}: d_model={shape.d_model} d_ff={shape.d_ff} experts={shape.num_experts} "
+                       f"top_k={shape.top_k} shared_d_ff={shape.shared_d_ff}",
+           "tokens_per_step": T * G, "n_gpus": G, "scaling": "strong" if G > 1 else "single GPU",
+           "dtype": "int8 weights, bf16 activations (W8A16)" if shape.int8 else "bf16",
+           "ms_per_step": ms, "tokens_per_s": T * G / (ms * 1e-3)}
+    rl = layer_roofline(shape, T * G, shape.num_experts if G > 1 else touched, peaks, shape.int8)
+    rec["roofline"] = {"bound": rl["bound"], "target_ms_one_gpu": rl["target_ms"], "t_tensor_ms": rl["t_tensor_ms"],
+                       "t_hbm_ms": rl["t_hbm_ms"], "frac": rl["target_ms"] / G / ms,
+                       "note": "target = slower of expert flops at the measured bf16 peak and touched weight + "
+                               "activation bytes at the measured HBM rate, divided by the GPU count"}
+    slow = max(range(len(per_rank)), key=lambda r: per_rank[r][0])
+    names = ("route_permute_gather", "rows_out", "routed_gemms", "rows_back", "shared_combine", "forward")
+    rec["phases_ms_slowest_rank"] = {n: per_rank[slow][1 + i] for i, n in enumerate(names)}
+    if G > 1:
+        rows = [r[0] for r in per_rank]
+        rec["rows_received_per_rank"] = {"max": max(rows), "mean": sum(rows) / len(rows),
+                                         "imbalance_max_over_mean": max(rows) / max(sum(rows) / len(rows), 1.0)}
+        rec["exchange"] = "peer stores over NVLink (direct)" if direct else "NCCL send/recv groups"
+        # the same batch on one GPU, timed by rank 0 in this very run (the others wait at the barrier)
+        single = None
+        if grp.rank == 0:
+            wf = synth.make_weights(shape, seed, grp.dev)
+            xs = [synth.make_activations(shape, seed + r, grp.dev, tokens=T) for r in range(G)]
+            xf = torch.cat(xs)
+            full = synth.build_layer(shape, wf, max_tokens=T * G)
+            of = torch.empty_like(xf)
+            for _ in range(args.warmup):
+                full.forward(xf, out=of)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(args.steps):
+                full.forward(xf, out=of)
+            e1.record()
+            torch.cuda.synchronize()
+            single = e0.elapsed_time(e1) / args.steps
+            full.check()
+            # the sharded run must give the unsharded run's rows (same rows, same experts, same order)
+            rec["max_abs_diff_vs_one_gpu_rank0_rows"] = float((of[:T].float() - out.float()).abs().max())
+            full.close()
+            del wf, xf, of
+        grp.sync()
+        if grp.rank == 0:
+            rec["one_gpu_ms_same_run"] = single
+            rec["speedup_vs_one_gpu_same_run"] = single / ms
+    layer.close()
+    del w, x, out
+    torch.cuda.empty_cache()
+    return rec
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -277,8 +463,10 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--layers", type=int, default=32, help="layers of the mixtral_int8_stack workload")
+    ap.add_argument("--windows", type=int, default=25, help="further K-step windows timed after the first (0: none)")
+    ap.add_argument("--no-records", action="store_true", help="skip the extra workloads of the default line")
     args = ap.parse_args()
-    arm_watchdog(float(os.environ.get("ATENIA_BENCH_WATCHDOG_S", "600" if args.impl == "reference" else "300")),
+    arm_watchdog(float(os.environ.get("ATENIA_BENCH_WATCHDOG_S", "600" if args.impl == "reference" else "420")),
                  "the whole run")
     if args.workload == "mixtral_int8_stack":
         return run_stack_bench(args)
@@ -286,7 +474,6 @@ def main():
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if world != args.gpus and world > 1:
         args.gpus = world
 
@@ -316,24 +503,23 @@ def main():
             return 0
         w = synth.make_weights(shape, 2, dev)
         x = synth.make_activations(shape, 2, dev, tokens=min(T, 512)).float().cpu().numpy()
-        from oracle import oracle as orc
         from oracle.from_synth import oracle_layer
         ol = oracle_layer(shape, w)
         del w
-        cores = orc.max_threads()
+        cores = host_threads()  # all host cores, whatever OMP_NUM_THREADS the launcher exported
         # size one step to about 2 s of CPU work; the sizing run and one more step are the warm-up
         # (CPU steps have no clocks or caches to settle beyond that)
         n0 = min(x.shape[0], max(cores, 4))
         t = time.perf_counter()
-        ol.forward(x[:n0])
+        ol.forward(x[:n0], nthreads=cores)
         rate0 = n0 / (time.perf_counter() - t)
         # about 2 s per step, less when many steps are asked for: the whole run stays near two minutes
         per_step_s = min(2.0, 120.0 / (args.steps + 1))
         n = int(min(x.shape[0], max(1, rate0 * per_step_s)))
-        ol.forward(x[:n])
+        ol.forward(x[:n], nthreads=cores)
         t = time.perf_counter()
         for _ in range(args.steps):
-            ol.forward(x[:n])
+            ol.forward(x[:n], nthreads=cores)
         dt = time.perf_counter() - t
         val = n * args.steps / dt
         line = {"metric": METRIC, "value": val, "unit": UNIT, "impl": "reference", "n_gpus": args.gpus,
@@ -349,90 +535,60 @@ def main():
         return 0
 
     # ------------------------------------------------------------------ our arm (GPU)
-    import ctypes as C
-
     import ateniaengine_b200 as ae
     from ateniaengine_b200 import _lib
 
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    dist = None
-    if args.gpus > 1:
-        import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=dev)
+    grp = EpGroup(args.gpus)
+    dev, dist = grp.dev, grp.dist
+    local_rank = grp.local_rank
+    direct = args.gpus > 1 and os.environ.get("ATENIA_BENCH_EP_DIRECT", "0") == "1"
     E = shape.num_experts
     el = E // args.gpus
     w = synth.make_weights(shape, 2, dev, experts=(rank * el, el))
     x = synth.make_activations(shape, 2 + rank, dev, tokens=T)
     layer = synth.build_layer(shape, w, max_tokens=T, ep_rank=rank, ep_world=args.gpus)
     if args.gpus > 1:
-        nb = _lib.lib().atenia_moe_ep_unique_id_bytes()
-        idt = torch.zeros(nb, dtype=torch.uint8, device=dev)
-        if rank == 0:
-            buf = C.create_string_buffer(nb)
-            _lib.check(_lib.lib().atenia_moe_ep_get_unique_id(buf), "ep_get_unique_id")
-            idt = torch.frombuffer(bytearray(buf.raw), dtype=torch.uint8).to(dev)
-        dist.broadcast(idt, 0)
-        layer.ep_init(bytes(idt.cpu().numpy().tobytes()))
-        if os.environ.get("ATENIA_BENCH_EP_DIRECT", "0") == "1":
-            # direct exchange: rows stored into the owners' buffers over NVLink peer mappings
-            mine = torch.frombuffer(bytearray(layer.ep_ipc_export()), dtype=torch.uint8).to(dev)
-            blobs = [torch.empty_like(mine) for _ in range(args.gpus)]
-            dist.all_gather(blobs, mine)
-            layer.ep_ipc_import(b"".join(bytes(b.cpu().numpy().tobytes()) for b in blobs))
-            config["parallelism"] = f"expert-parallel ep{args.gpus}, rows stored peer to peer over NVLink, NCCL for counts and ordering"
+        grp.join_ep(layer, direct=direct)
+        if direct:
+            config["parallelism"] = (f"expert-parallel ep{args.gpus}, rows stored peer to peer over NVLink, "
+                                     "NCCL for counts and ordering")
     out = torch.empty_like(x)
-
-    def sync_all():
-        torch.cuda.synchronize()
-        if dist is not None:
-            dist.barrier()
-            torch.cuda.synchronize()
+    fwd = lambda: layer.forward(x, out=out)
 
     for _ in range(args.warmup):
-        layer.forward(x, out=out)
+        fwd()
     layer.check()
-    sync_all()
+    grp.sync()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
     time.sleep(0.8)  # nvidia-smi needs a moment before its first reading
-    # every rank runs the same forwards: under expert parallelism each one is a set of collectives
+    # every rank runs the same forwards: under expert parallelism each one is a set of collectives.
+    # The library's CUDA events (grouped GEMMs, phases) are recorded inside the timed forwards: the
+    # figures below are those of the last timed step, not of a separate pass.
+    layer.enable_timing(True)
     for _ in range(args.warmup):
-        layer.forward(x, out=out)
-    sync_all()
+        fwd()
     t_load0 = time.perf_counter()
     launches0 = _lib.lib().atenia_moe_counter(1)
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    ev0.record()
-    for _ in range(args.steps):
-        layer.forward(x, out=out)
-    ev1.record()
-    sync_all()
-    ms = ev0.elapsed_time(ev1) / args.steps
+    ms = time_steps(grp, fwd, args.steps)
     launches = int(_lib.lib().atenia_moe_counter(1) - launches0)
     layer.check()
-    # keep the sampler running over the kernel-timing pass too: short timed regions give few samples
-    if dist is not None:
-        t = torch.tensor([ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
-
-    # ---- dominant kernel: routed gate/up + SwiGLU grouped GEMM, CUDA events on the launching stream
-    layer.enable_timing(True)
-    g1, g2 = [], []
-    for _ in range(args.steps):
-        layer.forward(x, out=out)
-        torch.cuda.synchronize()
-        g1.append(layer.last_gemm_ms(0))
-        g2.append(layer.last_gemm_ms(1))
+    gemm1_ms, gemm2_ms = layer.last_gemm_ms(0), layer.last_gemm_ms(1)
+    phases = [layer.last_phase_ms(i) for i in range(6)]
+    recv_rows = layer.last_recv_rows() if args.gpus > 1 and not direct else T * shape.top_k
+    # further windows of exactly K steps, back to back: the first window is a burst after an idle
+    # moment, the median window is what a loaded GPU sustains (clocks settle under the power cap)
+    win = []
+    for _ in range(max(args.windows, 0)):
+        win.append(time_steps(grp, fwd, args.steps))
     layer.enable_timing(False)
-    # the clock record covers the timed region and the kernel-timing pass that follows it
     if rank == 0:
         sampler.window = (t_load0, time.perf_counter())
     clocks = sampler.stop() if rank == 0 else None
-    gemm1_ms = sum(g1) / len(g1)
-    gemm2_ms = sum(g2) / len(g2)
+    per_rank = grp.gather_floats([recv_rows, gemm1_ms, gemm2_ms] + phases)
+    _, aux = layer.forward(x, aux=True, sync=True)
+    touched = int(torch.unique(aux["topk_idx"]).numel())
 
     # ---- end to end at N > 1: every rank copies its own tokens from pinned host memory, runs the
     # expert-parallel forward and copies its result back; same forwards on every rank, max over ranks
@@ -451,46 +607,90 @@ def main():
 
         for _ in range(3):
             one_step()
-        sync_all()
+        grp.sync()
         t0 = time.perf_counter()
         for _ in range(args.steps):
             one_step()
         torch.cuda.synchronize()
         dt = (time.perf_counter() - t0) / args.steps
         layer.check()
-        t = torch.tensor([dt], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        dt = float(t.item())
+        dt = grp.max_over_ranks(dt)
         nfl = T * shape.d_model
         e2e_multi = {"value": T * args.gpus / dt, "unit": UNIT, "h2d_bytes_per_step": nfl * 4 * args.gpus,
                      "d2h_bytes_per_step": nfl * 4 * args.gpus, "ms_per_step": dt * 1e3,
                      "api": "atenia_moe_forward per rank (expert parallel), pinned host f32 in/out on every rank"}
 
+    peaks, peak_src = load_peaks()
+
+    # ---- N > 1: a sample of rank 0's rows against the CPU oracle, outside the timed regions
+    parity = None
+    if args.gpus > 1 and not shape.int8:
+        if rank == 0:
+            from oracle.from_synth import oracle_layer, rel_l2
+            wf = synth.make_weights(shape, 2, dev)
+            ol = oracle_layer(shape, wf)
+            del wf
+            torch.cuda.empty_cache()
+            ns = min(32, T)
+            ref = ol.forward(x[:ns].float().cpu().numpy(), nthreads=host_threads())
+            parity = {"tokens": ns, "rel_l2_vs_cpu_oracle": rel_l2(out[:ns].float().cpu().numpy(), ref), "bar": 1e-2}
+            del ol
+        grp.sync()
+
+    # ---- extra records of the line: the other named workloads, each measured like the headline
+    records = {}
+    if not args.no_records and args.workload == "mixtral" and not args.tokens:
+        # release the headline layer first (N = 1 keeps it for the e2e leg below)
+        if args.gpus == 1:
+            records["w8a16_mixtral_4096"] = measure_record(grp, "mixtral_int8", 4096, args, peaks, seed=5)
+            records["deepseek_v2_lite_ep"] = measure_record(grp, "deepseek_v2_lite", 8192, args, peaks, seed=4)
+            records["qwen15_moe_2048"] = measure_record(grp, "qwen_moe", 2048, args, peaks, seed=3)
+        else:
+            records["deepseek_v2_lite_ep"] = measure_record(grp, "deepseek_v2_lite", 8192, args, peaks, seed=4,
+                                                            direct=direct)
+
     if rank != 0:
-        if dist is not None:
-            dist.barrier()
-            dist.destroy_process_group()
+        grp.close()
         return 0
 
-    peaks, peak_src = load_peaks()
-    rows = T * shape.top_k  # rows this rank's experts process under uniform sharding
-    flops1 = 4.0 * rows * shape.d_model * shape.d_ff  # gate and up: 2 * 2 * rows * d * F
-    achieved = flops1 / (gemm1_ms * 1e-3) / 1e12
-    groups = (shape.num_experts // args.gpus) * (args.gpus if args.gpus > 1 else 1)
+    slow = max(range(len(per_rank)), key=lambda r: per_rank[r][0])
+    rows_slow = per_rank[slow][0]
+    g1_slow, g2_slow = per_rank[slow][1], per_rank[slow][2]
+    groups = (shape.num_experts // args.gpus) * (args.gpus if args.gpus > 1 and not direct else 1)
     if shape.int8:
-        kname = "grouped_gemm_w8_tmem_kernel<kSwiGLU>" if rows < 256 * groups else "grouped_gemm_tcgen05_kernel<kSwiGLU, W8>"
+        kname = "grouped_gemm_w8_tmem_kernel" if rows_slow < 256 * groups else "grouped_gemm_tcgen05_kernel"
     else:
-        kname = "grouped_gemm_2cta_kernel<kSwiGLU>" if rows >= 512 * groups else "grouped_gemm_tcgen05_kernel<kSwiGLU>"
-    roofline = {"bound": "tensor", "kernel": kname + " (routed gate/up + SwiGLU)",
+        kname = "grouped_gemm_2cta_kernel" if rows_slow >= 512 * groups else "grouped_gemm_tcgen05_kernel"
+    # dominant kernel: the routed gate/up + SwiGLU grouped GEMM of the rank with the most rows
+    flops1 = 4.0 * rows_slow * shape.d_model * shape.d_ff  # gate and up: 2 * 2 * rows * d * F
+    achieved = flops1 / (g1_slow * 1e-3) / 1e12
+    rl = layer_roofline(shape, T, touched if args.gpus == 1 else shape.num_experts // args.gpus, peaks, shape.int8)
+    names = ("route_permute_gather", "rows_out", "routed_gemms", "rows_back", "shared_combine", "forward")
+    roofline = {"bound": "tensor", "kernel": kname + "<kSwiGLU> (routed gate/up + SwiGLU)",
                 "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                 "frac": achieved / peaks["bf16_tflops"], "peak_source": f"{peak_src} (burst cuBLAS bf16)",
                 "frac_of_sustained_peak": achieved / peaks["bf16_tflops_sustained"],
-                "traffic": NCU_TRAFFIC_BYTES.get(f"{shape.name}:{T}"),
-                "launch_ms": gemm1_ms, "down_gemm_ms": gemm2_ms,
-                "down_gemm_tflops": 2.0 * rows * shape.d_model * shape.d_ff / (gemm2_ms * 1e-3) / 1e12,
+                "traffic": NCU_TRAFFIC_BYTES.get(f"{shape.name}:{T}:{kname}") if args.gpus == 1 else None,
+                "rows": rows_slow, "launch_ms": g1_slow, "down_gemm_ms": g2_slow,
+                "down_gemm_tflops": 2.0 * rows_slow * shape.d_model * shape.d_ff / (g2_slow * 1e-3) / 1e12,
+                "timed_inside": "the last step of the timed region (events on the launching stream)",
+                "phases_ms": {n: per_rank[slow][3 + i] for i, n in enumerate(names)},
                 "layer_frac_of_tensor_roofline": (T * shape.top_k * 6.0 * shape.d_model * shape.d_ff +
                                                   T * 6.0 * shape.d_model * shape.shared_d_ff) /
                                                  (ms * 1e-3) / 1e12 / peaks["bf16_tflops"]}
+    if args.gpus == 1:
+        roofline["layer"] = {"bound": rl["bound"], "target_ms": rl["target_ms"], "frac": rl["target_ms"] / ms}
+    windows = None
+    if win:
+        med = statistics.median(win)
+        windows = {"count": len(win), "steps_each": args.steps, "ms_per_step_median": med, "ms_per_step_min": min(win),
+                   "ms_per_step_max": max(win), "tokens_per_s_median": T * args.gpus / (med * 1e-3),
+                   "first_window_ms_per_step": ms,
+                   "layer_frac_of_sustained_tensor_peak": (T * shape.top_k * 6.0 * shape.d_model * shape.d_ff +
+                                                           T * 6.0 * shape.d_model * shape.shared_d_ff) /
+                                                          (med * 1e-3) / 1e12 / peaks["bf16_tflops_sustained"],
+                   "note": "value / ms_per_step are the first window after warm-up (a burst); these windows "
+                           "follow it back to back, so their median is the sustained figure under the power cap"}
 
     # ---- end to end through the operator registry with pinned host buffers (N = 1 only)
     e2e = e2e_multi
@@ -520,8 +720,9 @@ def main():
     if args.gpus == 1 and not args.no_cpu_baseline:
         xs = x[: min(T, 512)].float().cpu().numpy()
         from oracle import oracle as orc
-        rate, cores, n, ol = cpu_oracle_rate(shape, w, xs, args.cpu_seconds * 0.6)
-        rate32, _, n32, _ = cpu_oracle_rate(shape, w, xs, args.cpu_seconds * 0.4, accum=orc.ACC_F32, ol=ol)
+        cores = host_threads()
+        rate, cores, n, ol = cpu_oracle_rate(shape, w, xs, args.cpu_seconds * 0.6, threads=cores)
+        rate32, _, n32, _ = cpu_oracle_rate(shape, w, xs, args.cpu_seconds * 0.4, threads=cores, accum=orc.ACC_F32, ol=ol)
         cpu = {"value": rate, "unit": UNIT, "cores": cores, "kind": "port",
                "sample": f"{n} of the step's {T} tokens, CPU oracle (C restatement of the reference's per-token "
                          f"f64 path), {cores} OpenMP threads",
@@ -531,29 +732,33 @@ def main():
 
     value = T * args.gpus / (ms * 1e-3)
     if args.gpus > 1:
-        # whole-forward target per rank: the slower of its expert flops at the measured GEMM rate and the
-        # bytes it must send over NVLink (uniform routing: (G-1)/G of its rows, out and back) at the
-        # measured peer-copy rate of this pool
+        # whole-forward target of the rank with the most rows: the slower of its expert flops at the
+        # measured GEMM rate and the bytes it must move over NVLink (rows it receives from the other
+        # ranks, there and back) at the measured peer-copy rate of this pool
         G = args.gpus
-        flops = T * shape.top_k * 6.0 * shape.d_model * shape.d_ff + T * 6.0 * shape.d_model * shape.shared_d_ff
+        rows = [r[0] for r in per_rank]
+        flops = rows_slow * 6.0 * shape.d_model * shape.d_ff + T * 6.0 * shape.d_model * shape.shared_d_ff
         t_compute = flops / (peaks["bf16_tflops"] * 1e12)
-        link_bytes = 2.0 * T * shape.top_k * (G - 1) / G * shape.d_model * 2
+        link_bytes = rows_slow * (G - 1) / G * shape.d_model * 2
         nvlink_gbs = 770.0
         t_link = link_bytes / (nvlink_gbs * 1e9)
         target = max(t_compute, t_link)
-        roofline["expert_parallel"] = {"t_compute_ms": t_compute * 1e3, "t_nvlink_ms": t_link * 1e3,
-                                       "nvlink_bytes_per_rank_per_direction": link_bytes,
-                                       "nvlink_gbs_per_direction": nvlink_gbs, "target_ms": target * 1e3,
-                                       "frac": target / (ms * 1e-3)}
+        roofline["expert_parallel"] = {
+            "rows_received_per_rank": rows, "rows_max": max(rows), "rows_mean": sum(rows) / len(rows),
+            "imbalance_max_over_mean": max(rows) / max(sum(rows) / len(rows), 1.0),
+            "efficiency_bound_from_imbalance": (sum(rows) / len(rows)) / max(rows),
+            "slowest_rank": slow, "t_compute_ms": t_compute * 1e3, "t_nvlink_ms": t_link * 1e3,
+            "nvlink_bytes_in_per_phase": link_bytes, "nvlink_gbs_per_direction": nvlink_gbs,
+            "target_ms": target * 1e3, "frac": target / (ms * 1e-3),
+            "note": "every rank routes its own tokens; the rank that owns the most popular experts sets the step"}
     line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": dtype_name, "data": "synthetic", "config": config,
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks, "gpu_launches": launches,
-            "tensor_core_launches_per_step": 2 + (2 if shape.shared_d_ff else 0)}
+            "tensor_core_launches_per_step": 2 + (2 if shape.shared_d_ff else 0),
+            "windows": windows, "records": records or None, "parity": parity}
     print(json.dumps(line))
-    if dist is not None:
-        dist.barrier()
-        dist.destroy_process_group()
+    grp.close()
     return 0
 
 

@@ -475,6 +475,14 @@ ATENIA_API uint64_t atenia_moe_counter(int which);
  * if nothing was recorded.  Enabling timing adds event records to every forward. */
 ATENIA_API int atenia_moe_enable_timing(AteniaMoeLayer* layer, int enable);
 ATENIA_API float atenia_moe_last_gemm_ms(AteniaMoeLayer* layer, int which);
+/* Phases of the most recent forward, from the same events: 0 = routing, permutation and row gather,
+ * 1 = rows to the ranks of their experts (expert parallelism; 0 on one GPU), 2 = routed expert GEMMs,
+ * 3 = results back to their source ranks (expert parallelism), 4 = shared expert and combine,
+ * 5 = the whole forward.  Milliseconds, negative if nothing was recorded. */
+ATENIA_API float atenia_moe_last_phase_ms(AteniaMoeLayer* layer, int which);
+/* Rows the experts of this rank received in the most recent token-sharded expert-parallel forward
+ * (known on the host because that path reads the row counts); -1 if none. */
+ATENIA_API int atenia_moe_last_recv_rows(AteniaMoeLayer* layer);
 
 #ifdef __cplusplus
 }

@@ -247,10 +247,10 @@ def test_forward_with_caller_selection(dev):
     # bf16-rounded weights (MoeDenseExpert::forward, src/moe/dense.rs:253-270)
     up16 = lambda t: t.float().cpu().numpy()
     xs = x.float().cpu().numpy()
-    for e, y in ((3, y1), (41, y2)):
+    for e, ye in ((3, y1), (41, y2)):
         ref = np.stack([orc.expert_forward(up16(w["gate"][e]), up16(w["up"][e]), up16(w["down"][e]), xs[t])
                         for t in range(90)])
-        assert rel_l2(y.cpu().numpy(), ref) <= TOL_BF16
+        assert rel_l2(ye.cpu().numpy(), ref) <= TOL_BF16
     # and the weighted pair against combine_selected over the concatenated expert outputs
     # (src/moe/sparse.rs:87-116)
     e3 = np.stack([orc.expert_forward(up16(w["gate"][3]), up16(w["up"][3]), up16(w["down"][3]), xs[t]) for t in range(8)])

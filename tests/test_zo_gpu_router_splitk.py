@@ -1,4 +1,4 @@
-"""ATENIA_MOE_ROUTER_SPLITK=1: the split-k router for small batches against the oracle and the default
+"""ATENIA_MOE_ROUTER=splitk: the split-k router for small batches against the oracle and the default
 router, repeated calls (its counters reset themselves) and the hand-over to the default router above
 1024 tokens."""
 import os
@@ -9,16 +9,13 @@ import torch
 
 from tests.test_gpu_parity import TOL_BF16, _run_parity, _synth, dev  # noqa: F401
 
-# Opt-in in the library and here until it has run on hardware: ATENIA_TEST_ROUTER_SPLITK=1.
-pytestmark = [pytest.mark.gpu,
-              pytest.mark.skipif(os.environ.get("ATENIA_TEST_ROUTER_SPLITK", "0") != "1",
-                                 reason="opt-in kernel: set ATENIA_TEST_ROUTER_SPLITK=1")]
+pytestmark = pytest.mark.gpu
 
 
 @pytest.mark.parametrize("name,d_model,T", [("mixtral", 512, 1), ("mixtral", 528, 13), ("qwen_moe", 512, 64),
                                              ("deepseek_v2_lite", 1024, 200), ("mixtral", 512, 1500)])
 def test_layer_parity_with_the_splitk_router(dev, monkeypatch, name, d_model, T):
-    monkeypatch.setenv("ATENIA_MOE_ROUTER_SPLITK", "1")
+    monkeypatch.setenv("ATENIA_MOE_ROUTER", "splitk")
     synth = _synth()
     base = synth.SHAPES[name]
     shape = synth.small(base, d_model=d_model, d_ff=384, shared_d_ff=256 if base.shared_d_ff else 0)
@@ -31,8 +28,9 @@ def test_same_routing_as_the_default_router_and_repeatable(dev, monkeypatch, E, 
     shape = synth.MoeShape("r", 4096, 64, E, k, True)
     w = synth.make_weights(shape, 3, dev)
     x = synth.make_activations(shape, 3, dev, tokens=37)
+    monkeypatch.setenv("ATENIA_MOE_ROUTER", "scalar")
     _, a = synth.build_layer(shape, w, max_tokens=64).forward(x, out_dtype=torch.float32, aux=True, sync=True)
-    monkeypatch.setenv("ATENIA_MOE_ROUTER_SPLITK", "1")
+    monkeypatch.setenv("ATENIA_MOE_ROUTER", "splitk")
     layer = synth.build_layer(shape, w, max_tokens=64)
     outs = [layer.forward(x, out_dtype=torch.float32, aux=True, sync=True) for _ in range(3)]
     for _, b in outs:

@@ -8,11 +8,7 @@ import torch
 from tests.helpers import oracle_layer, rel_l2
 from tests.test_gpu_parity import TOL_BF16, _synth, dev  # noqa: F401
 
-# New host-side views over entry points that have their own GPU tests; opt-in until they have run on
-# hardware once: ATENIA_TEST_GRAPH_OPS=1.
-pytestmark = [pytest.mark.gpu,
-              pytest.mark.skipif(os.environ.get("ATENIA_TEST_GRAPH_OPS", "0") != "1",
-                                 reason="set ATENIA_TEST_GRAPH_OPS=1")]
+pytestmark = pytest.mark.gpu
 
 
 def test_router_topk_then_dispatch_equals_the_fused_forward(dev):

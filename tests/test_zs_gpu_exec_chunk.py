@@ -7,10 +7,7 @@ import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
-# Opt-in in the library and here until it has run on hardware: ATENIA_TEST_EXEC_CHUNK=1.
-pytestmark = [pytest.mark.gpu,
-              pytest.mark.skipif(os.environ.get("ATENIA_TEST_EXEC_CHUNK", "0") != "1",
-                                 reason="opt-in path: set ATENIA_TEST_EXEC_CHUNK=1")]
+pytestmark = pytest.mark.gpu
 
 
 @pytest.mark.parametrize("chunk,tokens", [(64, 64), (64, 65), (100, 1000), (256, 777), (4096, 300)])

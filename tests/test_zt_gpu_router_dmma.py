@@ -1,4 +1,4 @@
-"""ATENIA_MOE_ROUTER_DMMA=1: router logits on the f64 tensor cores against the oracle and against the
+"""ATENIA_MOE_ROUTER=dmma: router logits on the f64 tensor cores against the oracle and against the
 default router."""
 import os
 
@@ -8,17 +8,14 @@ import torch
 
 from tests.test_gpu_parity import TOL_BF16, _run_parity, _synth, dev  # noqa: F401
 
-# The kernel is opt-in in the library and so are its tests until it has been brought up on hardware:
-# ATENIA_TEST_ROUTER_DMMA=1 runs them.
-pytestmark = [pytest.mark.gpu,
-              pytest.mark.skipif(os.environ.get("ATENIA_TEST_ROUTER_DMMA", "0") != "1",
-                                 reason="opt-in kernel: set ATENIA_TEST_ROUTER_DMMA=1")]
+pytestmark = pytest.mark.gpu
 
 
 @pytest.mark.parametrize("name,d_model,T", [("mixtral", 512, 1), ("mixtral", 528, 77), ("qwen_moe", 512, 300),
-                                             ("deepseek_v2_lite", 512, 515), ("mixtral", 1024, 4096)])
+                                             ("deepseek_v2_lite", 512, 515), ("deepseek_v2_lite", 512, 1500),
+                                             ("mixtral", 1024, 4096)])
 def test_layer_parity_with_the_dmma_router(dev, monkeypatch, name, d_model, T):
-    monkeypatch.setenv("ATENIA_MOE_ROUTER_DMMA", "1")
+    monkeypatch.setenv("ATENIA_MOE_ROUTER", "dmma")
     synth = _synth()
     base = synth.SHAPES[name]
     shape = synth.small(base, d_model=d_model, d_ff=384, shared_d_ff=256 if base.shared_d_ff else 0)
@@ -31,8 +28,9 @@ def test_same_routing_as_the_default_router(dev, monkeypatch, E, k):
     shape = synth.MoeShape("r", 256, 64, E, k, True)
     w = synth.make_weights(shape, 3, dev)
     x = synth.make_activations(shape, 3, dev, tokens=999)
+    monkeypatch.setenv("ATENIA_MOE_ROUTER", "scalar")
     _, a = synth.build_layer(shape, w, max_tokens=999).forward(x, out_dtype=torch.float32, aux=True, sync=True)
-    monkeypatch.setenv("ATENIA_MOE_ROUTER_DMMA", "1")
+    monkeypatch.setenv("ATENIA_MOE_ROUTER", "dmma")
     _, b = synth.build_layer(shape, w, max_tokens=999).forward(x, out_dtype=torch.float32, aux=True, sync=True)
     # f64 sums in a different order: the f32 logits agree except for rare last-bit roundings
     la, lb = a["logits"].cpu().numpy(), b["logits"].cpu().numpy()
