@@ -73,7 +73,7 @@ EXPORTS = [
     "atenia_numeric_policy_from_str", "atenia_numeric_policy_str", "atenia_numeric_policy",
     "atenia_numeric_policy_is_explicit", "atenia_set_numeric_policy", "atenia_clear_numeric_policy_override",
     "atenia_numeric_policy_ffn_uses_f32", "atenia_numeric_policy_ffn_uses_cuda", "atenia_numeric_policy_gate",
-    "atenia_moe_last_phase_ms", "atenia_moe_last_recv_rows", "atenia_moe_plan_residency", "atenia_auto_expert_cache_capacity", "atenia_moe_workspace_bytes",
+    "atenia_moe_block_forward", "atenia_moe_stack_set_norm", "atenia_moe_last_phase_ms", "atenia_moe_last_recv_rows", "atenia_moe_plan_residency", "atenia_auto_expert_cache_capacity", "atenia_moe_workspace_bytes",
 ]
 
 _lib = None
@@ -146,6 +146,9 @@ def lib():
         l.atenia_moe_dispatch_noalloc.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p,
                                                   C.c_void_p, C.c_void_p]
         l.atenia_moe_ep_init.argtypes = [C.c_void_p, C.c_void_p]
+        l.atenia_moe_block_forward.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_int, C.c_void_p,
+                                               C.c_void_p]
+        l.atenia_moe_stack_set_norm.argtypes = [C.c_void_p, C.POINTER(C.c_void_p), C.c_float]
         l.atenia_moe_last_phase_ms.restype = C.c_float
         l.atenia_moe_last_phase_ms.argtypes = [C.c_void_p, C.c_int]
         l.atenia_moe_last_recv_rows.argtypes = [C.c_void_p]

@@ -167,3 +167,45 @@ def bind_layer(tensors, layer_id, names=None):
         if sg is not None:
             shared_gate = np.asarray(tensors[sg], dtype=np.float32).reshape(-1)
     return {"router": router, "gate": gate, "up": up, "down": down, "shared": shared, "shared_gate": shared_gate}
+
+
+def to_device_layer(bound, top_k, device, convention=None, renormalize=None, max_tokens=4096, int8=False):
+    """Upload a layer bound by `bind_layer` and create the device layer: matrices rounded to bf16 (or
+    quantised per row to int8 on the GPU, the reference's tier quantiser), router and gate vector kept
+    f32.  The kernels need d_ff and the shared width to be multiples of 16: narrower experts are
+    zero-padded, which changes nothing (a zero gate/up row gives h = 0 and the matching zero column of
+    the down projection ignores it)."""
+    import torch
+
+    from .moe import MoeLayerConfig, RealMoeLayer, quantize_per_row_i8
+
+    def pad16(a, axis):
+        n = a.shape[axis]
+        m = (n + 15) // 16 * 16
+        if m == n:
+            return a
+        pad = [(0, 0)] * a.ndim
+        pad[axis] = (0, m - n)
+        return np.pad(a, pad)
+
+    def up(a):
+        t = torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).to(device)
+        if int8:
+            return quantize_per_row_i8(t)
+        return t.to(torch.bfloat16), None
+
+    E, d = bound["router"].shape
+    mats = {k: [up(pad16(a, 0 if k != "down" else 1)) for a in bound[k]] for k in ("gate", "up", "down")}
+    shared = shared_scales = None
+    if bound["shared"] is not None:
+        sh = [up(pad16(bound["shared"][0], 0)), up(pad16(bound["shared"][1], 0)), up(pad16(bound["shared"][2], 1))]
+        shared = [m for m, _ in sh]
+        shared_scales = [s for _, s in sh] if int8 else None
+    f32 = lambda a: None if a is None else torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).to(device)
+    cfg = MoeLayerConfig(E, int(top_k), shared is not None, d, mats["gate"][0][0].shape[0])
+    scales = {k: [s for _, s in mats[k]] for k in mats} if int8 else None
+    return RealMoeLayer(cfg, f32(bound["router"]), [m for m, _ in mats["gate"]], [m for m, _ in mats["up"]],
+                        [m for m, _ in mats["down"]], shared=shared, shared_gate=f32(bound["shared_gate"]),
+                        scales=scales, shared_scales=shared_scales, convention=convention, renormalize=renormalize,
+                        max_tokens=max_tokens)
+

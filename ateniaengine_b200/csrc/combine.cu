@@ -12,24 +12,41 @@
 namespace atenia {
 namespace {
 
+// One block per token, one 16-byte vector of the row per thread and step.  K is the top-k count (a
+// compile-time bound so that the k row loads of a vector are all issued before the first is used);
+// the arithmetic order does not depend on it.
+template <int K>
 __global__ void __launch_bounds__(256) combine_kernel(CombineArgs a) {
   const int t = blockIdx.x;
   const int nvec = a.d / 8;
-  int rows[8];
-  float w[8];
-  for (int s = 0; s < a.k; ++s) {
-    rows[s] = a.inv_perm[(size_t)t * a.k + s];
-    w[s] = a.topk_w[(size_t)t * a.k + s];
+  int rows[K];
+  float w[K];
+#pragma unroll
+  for (int s = 0; s < K; ++s) {
+    rows[s] = s < a.k ? a.inv_perm[(size_t)t * a.k + s] : -1;
+    w[s] = s < a.k ? a.topk_w[(size_t)t * a.k + s] : 0.f;
   }
   const float scale = a.gate_scale ? a.gate_scale[t] : 1.0f;
   for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+    uint4 y[K];
+#pragma unroll
+    for (int s = 0; s < K; ++s)
+      if (rows[s] >= 0) y[s] = *reinterpret_cast<const uint4*>(a.y_rows + (size_t)rows[s] * a.d + v * 8);
+    uint4 ysh = make_uint4(0, 0, 0, 0);
+    if (a.y_shared) ysh = *reinterpret_cast<const uint4*>(a.y_shared + (size_t)t * a.d + v * 8);
+    float4 r0 = make_float4(0.f, 0.f, 0.f, 0.f), r1 = r0;
+    if (a.residual) {
+      const float4* r = reinterpret_cast<const float4*>(a.residual + (size_t)t * a.d + v * 8);
+      r0 = r[0];
+      r1 = r[1];
+    }
     float acc[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-    for (int s = 0; s < a.k; ++s) {
-      if (rows[s] < 0) continue;  // entry without a row (invalid expert id, reported by the dispatch)
-      const uint4 y = *reinterpret_cast<const uint4*>(a.y_rows + (size_t)rows[s] * a.d + v * 8);
-      const uint32_t p[4] = {y.x, y.y, y.z, y.w};
+#pragma unroll
+    for (int s = 0; s < K; ++s) {
+      if (rows[s] < 0) continue;  // slot past k, or an entry without a row (invalid expert id, reported by the dispatch)
+      const uint32_t p[4] = {y[s].x, y[s].y, y[s].z, y[s].w};
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         acc[2 * j] = __fadd_rn(acc[2 * j], __fmul_rn(w[s], bf16lo(p[j])));
@@ -37,8 +54,7 @@ __global__ void __launch_bounds__(256) combine_kernel(CombineArgs a) {
       }
     }
     if (a.y_shared) {
-      const uint4 y = *reinterpret_cast<const uint4*>(a.y_shared + (size_t)t * a.d + v * 8);
-      const uint32_t p[4] = {y.x, y.y, y.z, y.w};
+      const uint32_t p[4] = {ysh.x, ysh.y, ysh.z, ysh.w};
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         acc[2 * j] = __fadd_rn(acc[2 * j], __fmul_rn(scale, bf16lo(p[j])));
@@ -46,8 +62,6 @@ __global__ void __launch_bounds__(256) combine_kernel(CombineArgs a) {
       }
     }
     if (a.residual) {
-      const float4* r = reinterpret_cast<const float4*>(a.residual + (size_t)t * a.d + v * 8);
-      const float4 r0 = r[0], r1 = r[1];
       acc[0] = __fadd_rn(acc[0], r0.x); acc[1] = __fadd_rn(acc[1], r0.y);
       acc[2] = __fadd_rn(acc[2], r0.z); acc[3] = __fadd_rn(acc[3], r0.w);
       acc[4] = __fadd_rn(acc[4], r1.x); acc[5] = __fadd_rn(acc[5], r1.y);
@@ -103,7 +117,13 @@ __global__ void f32_to_bf16_kernel(const float* __restrict__ src, __nv_bfloat16*
 
 int launch_combine(const CombineArgs& a, cudaStream_t s) {
   if (a.T <= 0) return ATENIA_OK;
-  combine_kernel<<<a.T, 256, 0, s>>>(a);
+  // d / 8 vectors per token: narrow rows take narrower blocks
+  const int nvec = a.d / 8;
+  const int threads = nvec >= 256 ? 256 : nvec >= 128 ? 128 : 64;
+  if (a.k <= 2) combine_kernel<2><<<a.T, threads, 0, s>>>(a);
+  else if (a.k <= 4) combine_kernel<4><<<a.T, threads, 0, s>>>(a);
+  else if (a.k <= 6) combine_kernel<6><<<a.T, threads, 0, s>>>(a);
+  else combine_kernel<8><<<a.T, threads, 0, s>>>(a);
   count_launch();
   return (int)cudaGetLastError();
 }

@@ -88,8 +88,8 @@ struct DispatchArgs {
   const int32_t* topk_idx;  // [n] flat (t*k + s) -> expert
   int n;                    // T * k
   int E;
-  int32_t* block_counts;  // [nblk, E]
-  int32_t* block_base;    // [nblk, E]
+  int32_t* block_counts;  // [E, nblk] entries of each expert per block of kDispatchChunk entries
+  int32_t* block_base;    // [E, nblk] exclusive scan of block_counts over the blocks
   int32_t* expert_offsets;  // [E + 1]
   int32_t* perm;            // [n]
   int32_t* inv_perm;        // [n]
@@ -162,6 +162,8 @@ struct GroupedGemmCheckArgs {
 int launch_grouped_gemm_check(const GroupedGemmCheckArgs& a, cudaStream_t s);
 
 int launch_f32_to_bf16(const float* src, __nv_bfloat16* dst, int64_t n, cudaStream_t s);
+// y = (x * inv_rms(x)) * gamma per row (stack.cu); gamma may be null (unit gain)
+int launch_rmsnorm_rows(const float* x, const float* gamma, float eps, float* y, int T, int d, cudaStream_t s);
 
 // Tensor-map encoding through the driver entry point (no link-time dependency on libcuda).
 int encode_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols,
@@ -173,8 +175,6 @@ int encode_tmap_2d_u8(CUtensorMap* out, const void* base, uint64_t rows, uint64_
 // W8A16 grouped GEMM with the weights as the tensor-memory operand (w8_gemm.cu).  tmap_a is the bf16
 // token matrix (box {64, 128}, 128B swizzle); tmap_b0/b1 are int8 maps with the 64-byte swizzle.
 int launch_grouped_gemm_w8_tmem(const GroupedGemmArgs& a, int num_sms, cudaStream_t s);
-// Same contract; the widening warps take alternate k-blocks (w8_gemm_alt.cu).
-int launch_grouped_gemm_w8_alt(const GroupedGemmArgs& a, int num_sms, cudaStream_t s);
 constexpr size_t kW8SplitKSlotFloats = 2 * 128 * 128;  // per CTA: two slots of this size
 // W8A16 for large groups (w8_gemm_wide.cu): one widened weight tile per k-block for up to 192 tokens.
 // tmap_a is the bf16 token matrix with box {64, 64} (128B swizzle); tmap_b0/b1 are int8 maps with box

@@ -27,26 +27,39 @@ __global__ void __launch_bounds__(kDispatchChunk) count_kernel(DispatchArgs a) {
     }
   }
   __syncthreads();
-  for (int e = threadIdx.x; e < a.E; e += blockDim.x) a.block_counts[(size_t)blockIdx.x * a.E + e] = hist[e];
+  // counts are kept expert-major, [E][gridDim.x]: the scan then reads consecutive blocks of one expert
+  for (int e = threadIdx.x; e < a.E; e += blockDim.x) a.block_counts[(size_t)e * gridDim.x + blockIdx.x] = hist[e];
 }
 
-// One block.  Warp w scans experts w, w + nwarps, ... over the blocks; then thread 0 scans experts.
+// One block.  Warp w scans experts w, w + nwarps, ... over the blocks (32 blocks per step, the loads of
+// up to eight steps issued before the first is consumed); then thread 0 scans experts.
 __global__ void __launch_bounds__(1024) scan_kernel(DispatchArgs a, int nblk) {
   __shared__ int totals[kMaxE];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  constexpr int kBatch = 8;
   for (int e = warp; e < a.E; e += nwarps) {
+    const int32_t* cnt = a.block_counts + (size_t)e * nblk;
+    int32_t* base = a.block_base + (size_t)e * nblk;
     int running = 0;
-    for (int b0 = 0; b0 < nblk; b0 += 32) {
-      int b = b0 + lane;
-      int c = b < nblk ? a.block_counts[(size_t)b * a.E + e] : 0;
-      int incl = c;
+    for (int b0 = 0; b0 < nblk; b0 += 32 * kBatch) {
+      int c[kBatch];
 #pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        int v = __shfl_up_sync(0xffffffffu, incl, o);
-        if (lane >= o) incl += v;
+      for (int j = 0; j < kBatch; ++j) {
+        const int b = b0 + 32 * j + lane;
+        c[j] = b < nblk ? cnt[b] : 0;
       }
-      if (b < nblk) a.block_base[(size_t)b * a.E + e] = running + incl - c;
-      running += __shfl_sync(0xffffffffu, incl, 31);
+#pragma unroll
+      for (int j = 0; j < kBatch; ++j) {
+        const int b = b0 + 32 * j + lane;
+        int incl = c[j];
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          int v = __shfl_up_sync(0xffffffffu, incl, o);
+          if (lane >= o) incl += v;
+        }
+        if (b < nblk) base[b] = running + incl - c[j];
+        running += __shfl_sync(0xffffffffu, incl, 31);
+      }
     }
     if (lane == 0) totals[e] = running;
   }
@@ -85,7 +98,7 @@ __global__ void __launch_bounds__(kDispatchChunk) place_kernel(DispatchArgs a) {
   if (e >= 0) {
     int before = 0;
     for (int w = 0; w < warp; ++w) before += warp_cnt[w][e];
-    const int pos = a.expert_offsets[e] + a.block_base[(size_t)blockIdx.x * a.E + e] + before + rank_in_warp;
+    const int pos = a.expert_offsets[e] + a.block_base[(size_t)e * gridDim.x + blockIdx.x] + before + rank_in_warp;
     a.perm[pos] = i;
     a.inv_perm[i] = pos;
   } else if (i < a.n) {
@@ -93,42 +106,66 @@ __global__ void __launch_bounds__(kDispatchChunk) place_kernel(DispatchArgs a) {
   }
 }
 
-// One block per destination row; 16-byte vectors.  `placed` points at expert_offsets[E], the number
-// of rows the placement actually wrote: entries with an invalid expert id get no row, so perm beyond
-// that count holds whatever an earlier call left there and must not be followed.
-__global__ void __launch_bounds__(256) gather_rows_kernel(const void* __restrict__ x, int x_is_f32,
-                                                           const int32_t* __restrict__ perm,
-                                                           const int32_t* __restrict__ placed, int n_rows, int k,
-                                                           int d, __nv_bfloat16* __restrict__ x_perm,
-                                                           __nv_bfloat16* __restrict__ x_bf16, int T) {
-  const int r = blockIdx.x;
-  const bool copy_row = r >= n_rows;  // blocks past n_rows convert x itself (f32 input, shared expert)
-  int src_t, dst_r;
-  __nv_bfloat16* dst;
-  if (!copy_row) {
-    if (r >= *placed) return;
-    src_t = perm[r] / k;
-    if (src_t < 0 || src_t >= T) return;
-    dst_r = r;
-    dst = x_perm;
-  } else {
-    src_t = r - n_rows;
-    if (src_t >= T) return;
-    dst_r = src_t;
-    dst = x_bf16;
-  }
-  uint4* drow = reinterpret_cast<uint4*>(dst + (size_t)dst_r * d);
+// Row gather: x_perm[r, :] = bf16(x[perm[r] / k, :]).  One warp per destination row, eight rows per
+// block in flight and a grid that loops; every lane keeps four 16-byte vectors in flight.  `placed`
+// points at expert_offsets[E], the number of rows the placement actually wrote: entries with an
+// invalid expert id get no row, so perm beyond that count holds whatever an earlier call left there
+// and must not be followed.  Rows n_rows .. n_rows + T - 1 of the index space convert x itself
+// (f32 input with a shared expert: x_bf16 = bf16(x)).
+constexpr int kGatherWarps = 8;
+
+__global__ void __launch_bounds__(kGatherWarps * 32) gather_rows_kernel(const void* __restrict__ x, int x_is_f32,
+                                                                         const int32_t* __restrict__ perm,
+                                                                         const int32_t* __restrict__ placed,
+                                                                         int n_rows, int k, int d,
+                                                                         __nv_bfloat16* __restrict__ x_perm,
+                                                                         __nv_bfloat16* __restrict__ x_bf16, int T,
+                                                                         int total_rows) {
+  const int lane = threadIdx.x & 31;
   const int nvec = d / 8;
-  if (x_is_f32) {
-    const float4* srow = reinterpret_cast<const float4*>(static_cast<const float*>(x) + (size_t)src_t * d);
-    for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
-      float4 a = srow[2 * v], b = srow[2 * v + 1];
-      drow[v] = make_uint4(pack_bf16x2(a.x, a.y), pack_bf16x2(a.z, a.w), pack_bf16x2(b.x, b.y),
-                           pack_bf16x2(b.z, b.w));
+  const int n_placed = n_rows > 0 ? *placed : 0;
+  for (int r = blockIdx.x * kGatherWarps + (threadIdx.x >> 5); r < total_rows; r += gridDim.x * kGatherWarps) {
+    int src_t, dst_r;
+    __nv_bfloat16* dst;
+    if (r < n_rows) {
+      if (r >= n_placed) continue;
+      src_t = perm[r] / k;
+      if (src_t < 0 || src_t >= T) continue;
+      dst_r = r;
+      dst = x_perm;
+    } else {
+      src_t = r - n_rows;
+      dst_r = src_t;
+      dst = x_bf16;
     }
-  } else {
-    const uint4* srow = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(x) + (size_t)src_t * d);
-    for (int v = threadIdx.x; v < nvec; v += blockDim.x) drow[v] = srow[v];
+    uint4* drow = reinterpret_cast<uint4*>(dst + (size_t)dst_r * d);
+    if (x_is_f32) {
+      const float4* srow = reinterpret_cast<const float4*>(static_cast<const float*>(x) + (size_t)src_t * d);
+      for (int v = lane; v < nvec; v += 64) {
+        float4 a0 = srow[2 * v], b0 = srow[2 * v + 1], a1, b1;
+        const bool two = v + 32 < nvec;
+        if (two) {
+          a1 = srow[2 * (v + 32)];
+          b1 = srow[2 * (v + 32) + 1];
+        }
+        drow[v] = make_uint4(pack_bf16x2(a0.x, a0.y), pack_bf16x2(a0.z, a0.w), pack_bf16x2(b0.x, b0.y),
+                             pack_bf16x2(b0.z, b0.w));
+        if (two)
+          drow[v + 32] = make_uint4(pack_bf16x2(a1.x, a1.y), pack_bf16x2(a1.z, a1.w), pack_bf16x2(b1.x, b1.y),
+                                    pack_bf16x2(b1.z, b1.w));
+      }
+    } else {
+      const uint4* srow = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(x) + (size_t)src_t * d);
+      for (int v = lane; v < nvec; v += 128) {
+        uint4 t[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (v + 32 * j < nvec) t[j] = srow[v + 32 * j];
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (v + 32 * j < nvec) drow[v + 32 * j] = t[j];
+      }
+    }
   }
 }
 
@@ -153,8 +190,13 @@ int launch_dispatch(const DispatchArgs& a, cudaStream_t s) {
 int launch_gather_rows(const void* x, int x_is_f32, const int32_t* perm, const int32_t* placed, int n_rows, int k,
                        int d, __nv_bfloat16* x_perm, __nv_bfloat16* x_bf16, int T, cudaStream_t s) {
   const int extra = x_bf16 ? T : 0;
-  if (n_rows + extra <= 0) return ATENIA_OK;
-  gather_rows_kernel<<<n_rows + extra, 256, 0, s>>>(x, x_is_f32, perm, placed, n_rows, k, d, x_perm, x_bf16, T);
+  const int total = n_rows + extra;
+  if (total <= 0) return ATENIA_OK;
+  // enough blocks to keep every SM's memory pipeline full; the kernel loops over the rest
+  const int want = (total + kGatherWarps - 1) / kGatherWarps;
+  const int cap = 148 * 8;
+  gather_rows_kernel<<<want < cap ? want : cap, kGatherWarps * 32, 0, s>>>(x, x_is_f32, perm, placed, n_rows, k, d, x_perm,
+                                                                          x_bf16, T, total);
   count_launch();
   return (int)cudaGetLastError();
 }

@@ -56,8 +56,9 @@ __global__ void group_offsets_kernel(const int32_t* __restrict__ counts_all, int
 __global__ void ep_plan_kernel(const int32_t* __restrict__ counts_all, int world, int E, int rank,
                                int32_t* __restrict__ dst_base, int32_t* __restrict__ src_base,
                                int32_t* __restrict__ sub_offsets, int32_t* __restrict__ gemm_offsets) {
-  if (threadIdx.x == 0 && blockIdx.x == 0)
-    ep_direct_plan(counts_all, world, E, rank, dst_base, src_base, sub_offsets, gemm_offsets);
+  // one thread per plan entry (E <= 128): the entries are independent prefix sums over the count matrix
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < E) ep_direct_plan_entry(counts_all, world, E, rank, i, dst_base, src_base, sub_offsets, gemm_offsets);
 }
 
 // One warp moves one row: 16-byte vectors, four loads in flight per lane before the stores.
@@ -268,7 +269,7 @@ int ep_direct_send(AteniaMoeLayer* L, const void* x, int x_is_f32, int T, cudaSt
   counts_kernel<<<1, 128, 0, s>>>(L->expert_offsets, E, L->d_counts_all + (size_t)rank * E);
   count_launch();
   NCCL_TRY(ncclAllGather(L->d_counts_all + (size_t)rank * E, L->d_counts_all, (size_t)E, ncclInt32, comm, s));
-  ep_plan_kernel<<<1, 32, 0, s>>>(L->d_counts_all, G, E, rank, L->d_dst_base, L->d_src_base, L->d_group_offsets,
+  ep_plan_kernel<<<1, 128, 0, s>>>(L->d_counts_all, G, E, rank, L->d_dst_base, L->d_src_base, L->d_group_offsets,
                                   L->d_gemm_offsets);
   count_launch();
   if (n > 0) {

@@ -21,33 +21,47 @@ namespace atenia {
 //   sub_offsets[j*world + p]  first row of the rows rank p sent for local expert j (El * world + 1 entries)
 //   src_base[j*world + p]     first row of those rows in rank p's dispatch-ordered buffers, where the
 //                             results go back to
+// Entry i in [0, E) of the plan: dst_base[i], and the slice (j, p) = (i / world, i % world) of this
+// rank's receive buffer (E = El * world, so one index covers both).  Entries are independent: the
+// device computes them with one thread each, the host in a loop.
+ATENIA_HD inline void ep_direct_plan_entry(const int32_t* counts_all, int world, int E, int rank, int i,
+                                           int32_t* dst_base, int32_t* src_base, int32_t* sub_offsets,
+                                           int32_t* gemm_offsets) {
+  const int El = E / world;
+  {
+    const int owner = i / El;
+    int run = 0;
+    for (int e = owner * El; e < i; ++e)
+      for (int p = 0; p < world; ++p) run += counts_all[p * E + e];
+    int before = 0;
+    for (int p = 0; p < rank; ++p) before += counts_all[p * E + i];
+    dst_base[i] = run + before;
+  }
+  {
+    const int j = i / world, p = i - j * world;
+    const int e = rank * El + j;
+    int run = 0;
+    for (int jj = 0; jj < j; ++jj)
+      for (int pp = 0; pp < world; ++pp) run += counts_all[pp * E + rank * El + jj];
+    int within = 0;
+    for (int pp = 0; pp < p; ++pp) within += counts_all[pp * E + e];
+    int src = 0;
+    for (int e2 = 0; e2 < e; ++e2) src += counts_all[p * E + e2];
+    sub_offsets[i] = run + within;
+    src_base[i] = src;
+    if (p == 0) gemm_offsets[j] = run;
+    if (i == E - 1) {
+      const int total = run + within + counts_all[p * E + e];
+      gemm_offsets[El] = total;
+      sub_offsets[E] = total;
+    }
+  }
+}
+
 ATENIA_HD inline void ep_direct_plan(const int32_t* counts_all, int world, int E, int rank, int32_t* dst_base,
                                      int32_t* src_base, int32_t* sub_offsets, int32_t* gemm_offsets) {
-  const int El = E / world;
-  for (int r = 0; r < world; ++r) {
-    int run = 0;
-    for (int j = 0; j < El; ++j) {
-      const int e = r * El + j;
-      int before = 0;
-      for (int p = 0; p < rank; ++p) before += counts_all[p * E + e];
-      dst_base[e] = run + before;
-      for (int p = 0; p < world; ++p) run += counts_all[p * E + e];
-    }
-  }
-  int run = 0;
-  for (int j = 0; j < El; ++j) {
-    const int e = rank * El + j;
-    gemm_offsets[j] = run;
-    for (int p = 0; p < world; ++p) {
-      int src = 0;
-      for (int e2 = 0; e2 < e; ++e2) src += counts_all[p * E + e2];
-      sub_offsets[j * world + p] = run;
-      src_base[j * world + p] = src;
-      run += counts_all[p * E + e];
-    }
-  }
-  gemm_offsets[El] = run;
-  sub_offsets[El * world] = run;
+  for (int i = 0; i < E; ++i)
+    ep_direct_plan_entry(counts_all, world, E, rank, i, dst_base, src_base, sub_offsets, gemm_offsets);
 }
 
 }  // namespace atenia

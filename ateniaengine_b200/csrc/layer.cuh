@@ -20,16 +20,17 @@ struct AteniaMoeLayer {
   bool use_check_gemm = false;  // diagnostic: CUDA-core contraction instead of tcgen05
   bool timing = false;
   const float* residual = nullptr;  // set by a stack around one forward: added by the combine kernel
-  // INT8: 0 = pick per call (tensor-memory operand kernel for small batches, shared-memory widening
-  // for large ones), 1 = always the tensor-memory kernel, 2 = always shared-memory widening,
-  // 3 = as 0 but the wide tensor-memory kernel (w8_gemm_wide.cu) for large batches,
-  // 4 = as 0 but the tensor-memory kernel with alternating widening groups (w8_gemm_alt.cu)
+  float* block_normed = nullptr;    // [max_tokens, d] f32, allocated by the first atenia_moe_block_forward
+  // INT8: 0 = pick per call (tensor-memory operand kernel of w8_gemm.cu for small groups, the wide
+  // tensor-memory kernel of w8_gemm_wide.cu for large ones), 1 = always the small-group kernel,
+  // 2 = always shared-memory widening (grouped_gemm.cu), 3 = as 0
   int w8_mode = 0;
   // bf16: 0 = pick per call (CTA-pair kernel once groups average >= 512 rows), 1 = always pairs,
   // 2 = always the single-CTA kernel
   int pair_mode = 0;
-  // bf16, on request (ATENIA_MOE_BF16_DECODE=1): the stream-K decode kernel when a call has <= 128 rows
-  bool bf16_decode = false;
+  // bf16 stream-K decode kernel: -1 = calls of at most 32 rows, 1 = every call of at most 128 rows
+  // (ATENIA_MOE_BF16_DECODE=1), 0 = never (=0, or INT8 weights)
+  int bf16_decode = -1;
   // router kernel: -1 by size, 0 CUDA cores (router.cu), 1 f64 tensor cores (router_dmma.cu),
   // 2 split-k for batches of at most sk_tokens (router_splitk.cu); see atenia_moe_create
   int router_variant = -1;

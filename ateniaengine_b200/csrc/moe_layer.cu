@@ -54,17 +54,18 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
   const AteniaMoeConfig& c = L->cfg;
   const bool q = c.weight_dtype == ATENIA_W_INT8_ROW;
   const bool large = max_rows >= 256 * num_groups;
-  // INT8, on request: the wide tensor-memory kernel for large groups
-  const bool wide = q && L->w8_mode == 3 && L->has_r64 && tm_a64 && tm_mid64 && large && !L->use_check_gemm;
-  // INT8: the tensor-memory kernel wins while groups are small (its MMA width follows the row count),
-  // the shared-memory widening kernel once every group fills several 128-row tiles.
-  const bool w8_auto = L->w8_mode == 0 || L->w8_mode == 3 || L->w8_mode == 4;
-  const bool tmem = q && !wide && (L->w8_mode == 1 || (w8_auto && !large));
-  const bool alt = tmem && L->w8_mode == 4;  // on request: the variant with alternating widening groups
-  // bf16: 256-row CTA-pair tiles pay off once an average group fills a few of them
-  // (INT8 has a pair kernel too, but it measures slower than the single-CTA one: only on request.)
-  // bf16, on request: the stream-K decode kernel while the whole call fits one token tile per group
-  const bool dec = !q && L->bf16_decode && max_rows <= 128 && !L->use_check_gemm;
+  // INT8: the tensor-memory kernel of w8_gemm.cu while groups are small (its MMA width follows the row
+  // count), the wide tensor-memory kernel (one widened weight tile per 192 tokens) once every group
+  // fills several tiles.  w8_mode 1 / 2 pin the small-group kernel / the shared-memory widening kernel of
+  // grouped_gemm.cu (tests, A/B runs).
+  const bool wide_ok = q && L->has_r64 && tm_a64 && tm_mid64 && !L->use_check_gemm;
+  const bool wide = wide_ok && large && (L->w8_mode == 0 || L->w8_mode == 3);
+  const bool tmem = q && !wide && (L->w8_mode == 1 || ((L->w8_mode == 0 || L->w8_mode == 3) && !large));
+  // bf16: 256-row CTA-pair tiles pay off once an average group fills a few of them; a call of at most
+  // 32 rows (decode) takes the stream-K kernel of bf16_decode_gemm.cu, which spreads the few tiles
+  // there are over all SMs (bf16_decode 1 / 0 pins it on for every call of at most 128 rows / off).
+  const bool dec = !q && !L->use_check_gemm && L->splitk_ws &&
+                   (L->bf16_decode == 1 ? max_rows <= 128 : (L->bf16_decode < 0 && max_rows <= 32));
   const bool pairs = !tmem && !wide && !dec && (L->pair_mode == 1 || (L->pair_mode == 0 && !q && max_rows >= 512 * num_groups));
   if (L->timing) cudaEventRecord(L->ev[0], s);
   if (L->use_check_gemm) {
@@ -92,7 +93,6 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
     g1.splitk_ws = L->splitk_ws;
     int rc = wide ? launch_grouped_gemm_w8_wide(g1, L->num_sms, s)
                   : dec ? launch_grouped_gemm_bf16_decode(g1, L->num_sms, s)
-                  : alt ? launch_grouped_gemm_w8_alt(g1, L->num_sms, s)
                   : tmem ? launch_grouped_gemm_w8_tmem(g1, L->num_sms, s)
                          : pairs ? launch_grouped_gemm_2cta(g1, L->num_sms, s)
                                  : launch_grouped_gemm_tcgen05(g1, L->num_sms, s);
@@ -123,7 +123,6 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
     g2.splitk_ws = L->splitk_ws;
     int rc = wide ? launch_grouped_gemm_w8_wide(g2, L->num_sms, s)
                   : dec ? launch_grouped_gemm_bf16_decode(g2, L->num_sms, s)
-                  : alt ? launch_grouped_gemm_w8_alt(g2, L->num_sms, s)
                   : tmem ? launch_grouped_gemm_w8_tmem(g2, L->num_sms, s)
                          : pairs ? launch_grouped_gemm_2cta(g2, L->num_sms, s)
                                  : launch_grouped_gemm_tcgen05(g2, L->num_sms, s);
@@ -141,10 +140,9 @@ namespace {
 int run_shared_gemms(AteniaMoeLayer* L, const __nv_bfloat16* xb, int T, cudaStream_t s) {
   const AteniaMoeConfig& c = L->cfg;
   const bool q = c.weight_dtype == ATENIA_W_INT8_ROW;
-  // (the shared expert keeps the default choice under w8_mode 3)
-  const bool w8_auto = L->w8_mode == 0 || L->w8_mode == 3 || L->w8_mode == 4;
-  const bool tmem = q && (L->w8_mode == 1 || (w8_auto && T < 256));
-  const bool alt = tmem && L->w8_mode == 4;
+  // (the shared expert is one group: INT8 takes the small-group kernel below 256 tokens and the
+  // shared-memory widening kernel above)
+  const bool tmem = q && (L->w8_mode == 1 || (L->w8_mode != 2 && T < 256));
   const bool pairs = !tmem && (L->pair_mode == 1 || (L->pair_mode == 0 && !q && T >= 512));
   if (L->timing) cudaEventRecord(L->ev[3], s);
   if (L->use_check_gemm) {
@@ -176,8 +174,7 @@ int run_shared_gemms(AteniaMoeLayer* L, const __nv_bfloat16* xb, int T, cudaStre
   g1.max_rows = T;
   g1.w8 = q;
   g1.splitk_ws = L->splitk_ws;
-  rc = alt ? launch_grouped_gemm_w8_alt(g1, L->num_sms, s)
-           : tmem ? launch_grouped_gemm_w8_tmem(g1, L->num_sms, s)
+  rc = tmem ? launch_grouped_gemm_w8_tmem(g1, L->num_sms, s)
                   : pairs ? launch_grouped_gemm_2cta(g1, L->num_sms, s) : launch_grouped_gemm_tcgen05(g1, L->num_sms, s);
   if (rc) return rc;
   if (L->timing) cudaEventRecord(L->ev[4], s);
@@ -196,8 +193,7 @@ int run_shared_gemms(AteniaMoeLayer* L, const __nv_bfloat16* xb, int T, cudaStre
   g2.max_rows = T;
   g2.w8 = q;
   g2.splitk_ws = L->splitk_ws;
-  rc = alt ? launch_grouped_gemm_w8_alt(g2, L->num_sms, s)
-           : tmem ? launch_grouped_gemm_w8_tmem(g2, L->num_sms, s)
+  rc = tmem ? launch_grouped_gemm_w8_tmem(g2, L->num_sms, s)
                   : pairs ? launch_grouped_gemm_2cta(g2, L->num_sms, s) : launch_grouped_gemm_tcgen05(g2, L->num_sms, s);
   if (rc) return rc;
   if (L->timing) {
@@ -245,8 +241,9 @@ int atenia_moe_create(const AteniaMoeConfig* cfg, AteniaMoeLayer** out) {
     const std::string r(rv ? rv : "");
     L->router_variant = r == "scalar" ? 0 : r == "dmma" ? 1 : r == "splitk" ? 2 : -1;
   }
-  L->bf16_decode = c.weight_dtype == ATENIA_W_BF16 && std::getenv("ATENIA_MOE_BF16_DECODE") &&
-                   std::atoi(std::getenv("ATENIA_MOE_BF16_DECODE")) != 0;
+  L->bf16_decode = c.weight_dtype != ATENIA_W_BF16 ? 0
+                   : std::getenv("ATENIA_MOE_BF16_DECODE") ? (std::atoi(std::getenv("ATENIA_MOE_BF16_DECODE")) != 0 ? 1 : 0)
+                                                           : -1;
   const size_t Tm = (size_t)c.max_tokens, k = (size_t)c.experts_per_token, E = (size_t)c.num_experts;
   const size_t d = (size_t)c.d_model, F = (size_t)c.d_ff, Fs = (size_t)c.shared_d_ff;
   const size_t R = Tm * k;
@@ -289,7 +286,7 @@ int atenia_moe_create(const AteniaMoeConfig* cfg, AteniaMoeLayer** out) {
   TRY_ALLOC(L->d_tm_up, (size_t)L->n_groups);
   TRY_ALLOC(L->d_tm_down, (size_t)L->n_groups);
   TRY_ALLOC(L->d_tm_shared, 3);
-  if (L->bf16_decode) TRY_ALLOC(L->splitk_ws, (size_t)L->num_sms * 2 * kW8SplitKSlotFloats);
+  if (L->bf16_decode != 0) TRY_ALLOC(L->splitk_ws, (size_t)L->num_sms * 2 * kW8SplitKSlotFloats);
   {
     const int sk_cap = L->router_variant == 2 ? 1024 : (L->router_variant == -1 ? 128 : 0);
     L->sk_tokens = c.max_tokens < sk_cap ? c.max_tokens : sk_cap;
@@ -311,7 +308,7 @@ int atenia_moe_create(const AteniaMoeConfig* cfg, AteniaMoeLayer** out) {
     TRY_ALLOC(L->d_tm_up_sw, (size_t)L->n_groups);
     TRY_ALLOC(L->d_tm_down_sw, (size_t)L->n_groups);
     TRY_ALLOC(L->d_tm_shared_sw, 3);
-    if (L->w8_mode == 3) {
+    if (L->w8_mode == 0 || L->w8_mode == 3) {
       TRY_ALLOC(L->d_tm_gate_r64, (size_t)L->n_groups);
       TRY_ALLOC(L->d_tm_up_r64, (size_t)L->n_groups);
       TRY_ALLOC(L->d_tm_down_r64, (size_t)L->n_groups);
@@ -386,7 +383,7 @@ int atenia_moe_destroy(AteniaMoeLayer* L) {
                   L->d_tm_down_sw, L->d_tm_shared_sw, L->d_tm_gate_r64, L->d_tm_up_r64, L->d_tm_down_r64,
                   L->splitk_ws, L->d_escore, L->logits_ws, L->recv_x, L->recv_h, L->recv_y, L->d_counts_all,
                   L->d_group_offsets, L->d_peer_recv_x, L->d_peer_y_perm, L->d_dst_base, L->d_src_base,
-                  L->d_gemm_offsets, L->d_bar, L->sk_part, L->sk_gate, L->sk_counters};
+                  L->d_gemm_offsets, L->d_bar, L->sk_part, L->sk_gate, L->sk_counters, L->block_normed};
   for (void* p : ptrs)
     if (p) cudaFree(p);
   for (void* p : L->owned) cudaFree(p);
@@ -693,6 +690,26 @@ static int forward_impl(AteniaMoeLayer* L, const void* x, int x_dtype, int T, vo
                                       cudaMemcpyDeviceToDevice, s));
   }
   return ATENIA_OK;
+}
+
+int atenia_moe_block_forward(AteniaMoeLayer* L, const float* x, const float* gamma, float eps, int T, float* out,
+                             void* stream) {
+  if (!L) return ATENIA_ERR_NULL;
+  if (!L->weights_set) return ATENIA_ERR_STATE;
+  if (T < 0 || !(eps >= 0.f)) return ATENIA_ERR_SHAPE;
+  if (T > L->cfg.max_tokens) return ATENIA_ERR_CAPACITY;
+  if (T > 0 && (!x || !out)) return ATENIA_ERR_NULL;
+  if (!L->block_normed) {
+    ATENIA_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&L->block_normed),
+                               (size_t)L->cfg.max_tokens * (size_t)L->cfg.d_model * sizeof(float)));
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int rc = launch_rmsnorm_rows(x, gamma, eps, L->block_normed, T, L->cfg.d_model, s);
+  if (rc) return rc;
+  L->residual = x;  // added last by the combine kernel: out = x + MoE(h)
+  rc = forward_impl(L, L->block_normed, ATENIA_IO_F32, T, out, ATENIA_IO_F32, nullptr, stream, nullptr, nullptr);
+  L->residual = nullptr;
+  return rc;
 }
 
 int atenia_moe_check(AteniaMoeLayer* L, void* stream) {

@@ -16,6 +16,8 @@
 //     every NW_K-th k-step of the chunk; its accumulators are MT x NTW x 2 doubles per lane;
 //   * the k-slices are folded through shared memory in warp order (fixed), the bias joins the f64
 //     sum, logits are rounded to f32 and the warps route the tokens (route_one_warp).
+#include <cstdlib>
+
 #include "route_warp.cuh"
 
 namespace atenia {
@@ -224,9 +226,15 @@ int launch_mt(const RouterArgs& a, cudaStream_t s) {
 
 template <int E_T>
 int launch_one(const RouterArgs& a, cudaStream_t s) {
-  // tokens per CTA by batch size: the grid should cover the SMs a few times over
-  if (a.T >= 4096) return launch_mt<E_T, 4>(a, s);
-  if (a.T >= 1024) return launch_mt<E_T, 2>(a, s);
+  // tokens per CTA by batch size: several CTAs per SM hide the latency of a CTA's chunk pipeline, so
+  // the grid should cover the SMs a few times over (ATENIA_MOE_ROUTER_MT = 1 | 2 | 4 pins it: A/B runs)
+  static const int pinned = [] {
+    const char* e = std::getenv("ATENIA_MOE_ROUTER_MT");
+    return e ? std::atoi(e) : 0;
+  }();
+  const int mt = pinned == 1 || pinned == 2 || pinned == 4 ? pinned : (a.T >= 16384 ? 4 : a.T >= 4096 ? 2 : 1);
+  if (mt == 4) return launch_mt<E_T, 4>(a, s);
+  if (mt == 2) return launch_mt<E_T, 2>(a, s);
   return launch_mt<E_T, 1>(a, s);
 }
 

@@ -13,6 +13,8 @@ struct AteniaMoeStack {
   bool residual = false;
   bool prenorm = false;       // residual == 2: x <- x + layer(rmsnorm(x))
   float* normed = nullptr;    // [max_tokens, d] f32
+  std::vector<const float*> gammas;  // per layer device [d] gain of the norm, or empty = unit gain
+  float eps = 1e-5f;
   int d_model = 0;
   int max_tokens = 0;
   float* buf[2] = {nullptr, nullptr};  // ping-pong [max_tokens, d] f32
@@ -27,13 +29,19 @@ struct AteniaMoeStack {
 
 namespace {
 
-// y[t, :] = x[t, :] / sqrt(mean(x[t, :]^2) + 1e-5): RMSNorm with unit gain, one block per row.
-__global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const float* __restrict__ x, float* __restrict__ y, int d) {
+// y[t, :] = (x[t, :] * inv_rms) * gamma with inv_rms = 1 / sqrt(mean(x[t, :]^2) + eps): the post-attention
+// RMSNorm and its gain as the reference applies them before the MoE block (rms_norm,
+// src/nn/normalization.rs:8-37, then broadcast_mul by gamma, src/moe/full_forward.rs:239-242): f32
+// throughout, the normalised value rounded before the gain multiplies it.  The reference adds the
+// squares in index order; here they are added by a block reduction, which can move inv_rms by an ulp.
+// gamma == nullptr means unit gain.  One block per row.
+__global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ gamma,
+                                                            float eps, float* __restrict__ y, int d) {
   __shared__ float red[8];
   __shared__ float s_inv;
   const float* row = x + (size_t)blockIdx.x * d;
   float ss = 0.f;
-  for (int c = threadIdx.x; c < d; c += blockDim.x) ss += row[c] * row[c];
+  for (int c = threadIdx.x; c < d; c += blockDim.x) ss = __fmaf_rn(row[c], row[c], ss);
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
@@ -41,12 +49,29 @@ __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const float* __restri
   if (threadIdx.x == 0) {
     float t = 0.f;
     for (int i = 0; i < 8; ++i) t += red[i];
-    s_inv = rsqrtf(t / (float)d + 1e-5f);
+    const float mean_sq = __fdiv_rn(t, (float)d);
+    s_inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean_sq, eps)));
   }
   __syncthreads();
   const float inv = s_inv;
-  for (int c = threadIdx.x; c < d; c += blockDim.x) y[(size_t)blockIdx.x * d + c] = row[c] * inv;
+  for (int c = threadIdx.x; c < d; c += blockDim.x) {
+    const float n = __fmul_rn(row[c], inv);
+    y[(size_t)blockIdx.x * d + c] = gamma ? __fmul_rn(n, gamma[c]) : n;
+  }
 }
+
+}  // namespace
+
+namespace atenia {
+int launch_rmsnorm_rows(const float* x, const float* gamma, float eps, float* y, int T, int d, cudaStream_t s) {
+  if (T <= 0) return ATENIA_OK;
+  rmsnorm_rows_kernel<<<T, 256, 0, s>>>(x, gamma, eps, y, d);
+  count_launch();
+  return (int)cudaGetLastError();
+}
+}  // namespace atenia
+
+namespace {
 
 int run_layers(AteniaMoeStack* S, const void* x, int x_dtype, int T, void* out, int out_dtype, cudaStream_t s) {
   const int n = (int)S->layers.size();
@@ -65,8 +90,9 @@ int run_layers(AteniaMoeStack* S, const void* x, int x_dtype, int T, void* out, 
     }
     const void* in = cur;
     if (S->prenorm) {
-      rmsnorm_rows_kernel<<<T, 256, 0, s>>>(static_cast<const float*>(cur), S->normed, S->d_model);
-      atenia::count_launch();
+      const float* g = S->gammas.empty() ? nullptr : S->gammas[(size_t)l];
+      int nrc = atenia::launch_rmsnorm_rows(static_cast<const float*>(cur), g, S->eps, S->normed, T, S->d_model, s);
+      if (nrc) return nrc;
       in = S->normed;
     }
     L->residual = res;
@@ -131,6 +157,21 @@ int atenia_moe_stack_create(AteniaMoeLayer* const* layers, int n_layers, int res
   const char* g = std::getenv("ATENIA_MOE_STACK_GRAPH");
   S->use_graph = !(g && std::atoi(g) == 0);
   *out = S;
+  return ATENIA_OK;
+}
+
+int atenia_moe_stack_set_norm(AteniaMoeStack* S, const float* const* gammas, float eps) {
+  if (!S) return ATENIA_ERR_NULL;
+  if (!S->prenorm) return ATENIA_ERR_STATE;
+  if (!(eps >= 0.f)) return ATENIA_ERR_SHAPE;
+  S->gammas.clear();
+  if (gammas) S->gammas.assign(gammas, gammas + S->layers.size());
+  S->eps = eps;
+  if (S->exec) {  // a captured graph holds the old arguments
+    cudaGraphExecDestroy(S->exec);
+    S->exec = nullptr;
+  }
+  S->g_warm = false;
   return ATENIA_OK;
 }
 

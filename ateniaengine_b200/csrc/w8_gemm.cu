@@ -3,7 +3,7 @@
 // The contraction is computed transposed, D[f, t] = sum_k W[f, k] * X[t, k]: 128 weight rows are
 // the M side of the MMA, a tile of up to 128 tokens is the N side.  The int8 weight tile arrives by
 // TMA (one byte per weight through HBM, L2 and shared memory), each of 256 threads widens one weight
-// row of the k-block to bf16 in registers (exact: |q| <= 127) and stores it with tcgen05.st into
+// row of a k-block to bf16 in registers (exact: |q| <= 127) and stores it with tcgen05.st into
 // tensor memory, and tcgen05.mma reads A from tensor memory and B (the bf16 token tile, 128B-swizzled
 // by TMA) from shared memory.  The widened weights never touch shared memory, which is the scarce
 // resource of this kernel: per k-block the shared-memory traffic is 80 KiB instead of the 128 KiB of
@@ -16,8 +16,15 @@
 //               [256,512) four stages of the widened weight tiles (2 x 32 columns each)
 //   MMA       = M128 x N x K16 with N = the tile's token count rounded up to 16: a decode batch does
 //               not pay for 128 columns
-//   warps     : 0 TMA, 1 MMA + TMEM alloc, 4..11 widen (4..7 tile 0, 8..11 tile 1), 12..19 epilogue
-//               (two warps per TMEM lane quarter, each taking every other 16-token chunk)
+//   warps     : 0 TMA, 1 MMA + TMEM alloc, 4..7 widen both weight tiles of the even k-blocks, 8..11 of the
+//               odd ones, 12..19 epilogue (two warps per TMEM lane quarter, each taking every other
+//               16-token chunk)
+//
+// The two groups of widening warps take ALTERNATE k-blocks: a warp's chain wait -> ld.shared -> widen ->
+// tcgen05.st -> wait::st -> arrive then has two k-block periods to complete, and two k-blocks are in
+// flight.  (With every warp serving every k-block, that chain, not HBM, set the k-block period at decode
+// sizes, where the MMA of a k-block is a few dozen cycles: measured on B200, a Mixtral-shaped layer at
+// 8 / 64 tokens takes 0.309 / 0.531 ms this way against 0.318 / 0.549 ms.)
 //
 // The accumulator is single-buffered (TMEM is full); the TMA ring and the widening run ahead into the
 // next tile while the epilogue drains.  All waits are bounded as in grouped_gemm.cu.
@@ -43,8 +50,8 @@ constexpr int A_TILE_COLS = BK / 2;  // 64 bf16 per row = 32 columns of 32 bits
 
 struct __align__(8) BarriersW8 {
   uint64_t full[S_STAGES];    // TMA landed (1 arrival + bytes)
-  uint64_t empty[S_STAGES];   // 8 widening warps read the int8 tiles + MMA commit read the token tile
-  uint64_t a_full[T_STAGES];  // widened tiles stored to TMEM (8 widening warps)
+  uint64_t empty[S_STAGES];   // 4 widening warps (one group) read the int8 tiles + MMA commit read the token tile
+  uint64_t a_full[T_STAGES];  // widened tiles stored to TMEM (4 widening warps: one group)
   uint64_t a_empty[T_STAGES]; // MMAs that read them are done (commit)
   uint64_t acc_full;          // all MMAs of the tile done (commit)
   uint64_t acc_empty;         // 8 epilogue warps drained the accumulators
@@ -144,10 +151,10 @@ grouped_gemm_w8_tmem_kernel(const __grid_constant__ CUtensorMap tmap_x, const CU
   if (threadIdx.x == 0) {
     for (int s = 0; s < S_STAGES; ++s) {
       mbar_init(smem_u32(&bars->full[s]), 1);
-      mbar_init(smem_u32(&bars->empty[s]), 9);
+      mbar_init(smem_u32(&bars->empty[s]), 5);
     }
     for (int c = 0; c < T_STAGES; ++c) {
-      mbar_init(smem_u32(&bars->a_full[c]), 8);
+      mbar_init(smem_u32(&bars->a_full[c]), 4);
       mbar_init(smem_u32(&bars->a_empty[c]), 1);
     }
     mbar_init(smem_u32(&bars->acc_full), 1);
@@ -269,16 +276,17 @@ grouped_gemm_w8_tmem_kernel(const __grid_constant__ CUtensorMap tmap_x, const CU
     }
   } else if (warp >= 4 && warp < 12) {
     // ================= int8 -> bf16 widening into tensor memory =================
-    // Warp w handles weight tile (w - 4) / 4 and the 32 rows of TMEM lane quarter w % 4; each thread
-    // owns one weight row of the k-block: 64 int8 = four 16-byte pieces.  The TMA box is 64B-swizzled
-    // (piece index XOR (row / 2) mod 4), which makes the 32 row-strided reads of a warp conflict-free.
-    const int which = (warp - 4) >> 2;
+    // Group (warp - 4) / 4 takes the k-blocks of its parity and widens both weight tiles of them; warp
+    // quarter w % 4 owns TMEM lanes [32q, 32q + 32); a thread widens one row of each tile: 64 int8 =
+    // four 16-byte pieces.  The TMA box is 64B-swizzled (piece index XOR (row / 2) mod 4), which makes
+    // the 32 row-strided reads of a warp conflict-free.
+    const uint32_t group = (warp - 4) >> 2;
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
-    // Software pipeline: the TMEM store of k-block i is left in flight while k-block i+1 is read and
-    // widened; its completion is awaited (and the barriers signalled) just before the next store.
-    int stage = 0, tstage = 0;
-    uint32_t phase = 0, tphase = 0;
+    const int sw = (row >> 1) & 3;
+    // The TMEM stores of one k-block stay in flight while this group's next k-block is read and
+    // widened; their completion is awaited (and the barriers signalled) just before the next store.
+    uint32_t idx = 0;  // k-blocks of this CTA so far, both groups counted
     int pend_stage = -1, pend_tstage = -1;
     bool ok = true;
     auto retire = [&]() {
@@ -292,27 +300,32 @@ grouped_gemm_w8_tmem_kernel(const __grid_constant__ CUtensorMap tmap_x, const CU
       }
       pend_stage = -1;
     };
+    auto widen_row = [&](const uint8_t* q, uint32_t (&v)[32]) {
+      uint4 p[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) p[c] = *reinterpret_cast<const uint4*>(q + ((c ^ sw) << 4));
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        widen4(p[c].x, v[8 * c + 0], v[8 * c + 1]);
+        widen4(p[c].y, v[8 * c + 2], v[8 * c + 3]);
+        widen4(p[c].z, v[8 * c + 4], v[8 * c + 5]);
+        widen4(p[c].w, v[8 * c + 6], v[8 * c + 7]);
+      }
+    };
     while (ok && it.next()) {
-      for (int kb = it.kb0; kb < it.kb0 + it.nkb; ++kb) {
+      for (int kb = it.kb0; kb < it.kb0 + it.nkb; ++kb, ++idx) {
+        if ((idx & 1u) != group) continue;
+        const int stage = idx % S_STAGES, tstage = idx % T_STAGES;
+        const uint32_t phase = (idx / S_STAGES) & 1u, tphase = (idx / T_STAGES) & 1u;
         if (!mbar_wait(smem_u32(&bars->full[stage]), phase, abort_flag)) {
           if (lane == 0) report_error(err, ATENIA_ERR_DEVICE_TIMEOUT, 800 + warp);
           *abort_flag = 1;
           ok = false;
           break;
         }
-        const uint8_t* q = smem_aligned + stage * S_STAGE_BYTES + which * WQ_TILE_BYTES + row * BK;
-        const int sw = (row >> 1) & 3;
-        uint4 p[4];
-#pragma unroll
-        for (int c = 0; c < 4; ++c) p[c] = *reinterpret_cast<const uint4*>(q + ((c ^ sw) << 4));
+        const uint8_t* q0 = smem_aligned + stage * S_STAGE_BYTES + row * BK;
         uint32_t v[32];
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          widen4(p[c].x, v[8 * c + 0], v[8 * c + 1]);
-          widen4(p[c].y, v[8 * c + 2], v[8 * c + 3]);
-          widen4(p[c].z, v[8 * c + 4], v[8 * c + 5]);
-          widen4(p[c].w, v[8 * c + 6], v[8 * c + 7]);
-        }
+        widen_row(q0, v);
         retire();
         if (!mbar_wait(smem_u32(&bars->a_empty[tstage]), tphase ^ 1u, abort_flag)) {
           if (lane == 0) report_error(err, ATENIA_ERR_DEVICE_TIMEOUT, 820 + warp);
@@ -321,19 +334,12 @@ grouped_gemm_w8_tmem_kernel(const __grid_constant__ CUtensorMap tmap_x, const CU
           break;
         }
         tc_fence_after();
-        const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + A_RING_COL +
-                               tstage * 2 * A_TILE_COLS + which * A_TILE_COLS;
+        const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + A_RING_COL + tstage * 2 * A_TILE_COLS;
         tc_st32(taddr, v);
+        widen_row(q0 + WQ_TILE_BYTES, v);  // the store above read its registers when it was issued
+        tc_st32(taddr + A_TILE_COLS, v);
         pend_stage = stage;
         pend_tstage = tstage;
-        if (++stage == S_STAGES) {
-          stage = 0;
-          phase ^= 1u;
-        }
-        if (++tstage == T_STAGES) {
-          tstage = 0;
-          tphase ^= 1u;
-        }
       }
     }
     retire();

@@ -263,6 +263,24 @@ class RealMoeLayer:
                 _lib.check(_lib.lib().atenia_moe_check(self._h, st), "atenia_moe_forward_with")
         return out
 
+    def block_forward(self, x, gamma=None, eps=1e-5, out=None, sync=False):
+        """The decoder-layer step around the block: x + MoE(rms_norm(x, eps) * gamma)
+        (src/moe/full_forward.rs:239-252).  x: CUDA f32 [T, d]; gamma: CUDA f32 [d] or None."""
+        assert x.is_cuda and x.dtype == torch.float32 and x.dim() == 2 and x.shape[1] == self.config.d_model
+        x = x.contiguous()
+        if gamma is not None:
+            assert gamma.is_cuda and gamma.dtype == torch.float32 and gamma.numel() == self.config.d_model
+            gamma = gamma.contiguous()
+        if out is None:
+            out = torch.empty_like(x)
+        with torch.cuda.device(x.device):
+            st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+            _lib.check(_lib.lib().atenia_moe_block_forward(self._h, _ptr(x), _ptr(gamma), float(eps), x.shape[0],
+                                                           _ptr(out), st), "atenia_moe_block_forward")
+            if sync:
+                _lib.check(_lib.lib().atenia_moe_check(self._h, st), "atenia_moe_block_forward")
+        return out
+
     def forward_auto(self, x, **kw):
         """RealMoeLayer::forward_auto: HuggingFaceQwen when a shared gate vector is present, else Atenia
         (resolve_convention); the convention the constructor resolved when none was given."""
@@ -512,6 +530,16 @@ class RealMoeStack:
             if sync:
                 _lib.check(_lib.lib().atenia_moe_stack_check(self._h, st), "atenia_moe_stack_check")
         return out
+
+    def set_norm(self, gammas=None, eps=1e-5):
+        """Gains (one CUDA f32 [d] tensor per layer, or None for unit gain) and epsilon of the pre-norm of
+        a residual=2 stack."""
+        arr = None
+        if gammas is not None:
+            assert len(gammas) == len(self.layers)
+            self._gammas = [None if g is None else g.contiguous() for g in gammas]
+            arr = (C.c_void_p * len(gammas))(*[None if g is None else g.data_ptr() for g in self._gammas])
+        _lib.check(_lib.lib().atenia_moe_stack_set_norm(self._h, arr, float(eps)), "atenia_moe_stack_set_norm")
 
     def close(self):
         if getattr(self, "_h", None) is not None and self._h.value:

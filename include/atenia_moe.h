@@ -167,6 +167,17 @@ ATENIA_API int atenia_moe_forward(AteniaMoeLayer* layer, const void* x, int x_dt
 ATENIA_API int atenia_moe_forward_with(AteniaMoeLayer* layer, const void* x, int x_dtype, int T, void* out,
                                        int out_dtype, const AteniaMoeAux* aux, void* stream, int convention);
 
+/* The step either side of the block in a decoder layer (src/moe/full_forward.rs:239-252):
+ *   h = rms_norm(x, eps) * gamma;  out = x + MoE(h)
+ * x, out: device f32 [T, d]; gamma: device f32 [d] (NULL = unit gain).  rms_norm follows
+ * src/nn/normalization.rs:8-37 in f32 (x * (1 / sqrt(mean(x^2) + eps)), then the gain); the residual
+ * is added in the combine kernel's epilogue, after the shared expert, as one f32 add per element.
+ * The normalised rows pass through an f32 buffer of the layer ([max_tokens, d]) that the FIRST call
+ * allocates (make that call outside any stream capture).  With T == 0 under token-sharded expert
+ * parallelism x and out may be NULL. */
+ATENIA_API int atenia_moe_block_forward(AteniaMoeLayer* layer, const float* x, const float* gamma, float eps, int T,
+                                        float* out, void* stream);
+
 /* The block with the selection supplied by the caller instead of the router: topk_idx [T, k] (device,
  * int32, expert ids in [0, E), need not be sorted) and topk_w [T, k] (device, f32) are used as they
  * are; everything after routing is unchanged (out = sum_s w[t,s] * expert_{idx[t,s]}(x_t), slots in
@@ -373,8 +384,9 @@ ATENIA_API uint64_t atenia_moe_workspace_bytes(const AteniaMoeConfig* cfg);
  * RealMoeStack::forward (src/moe/stack.rs:197-210): x <- layer_l(x) for l = 0..n-1, every layer with
  * its own convention, no norm.  `residual` = 1 computes x <- x + layer_l(x) instead (the reference
  * stack has no residual; the 32-layer decode benchmark does); `residual` = 2 computes the pre-norm
- * block of a transformer with attention left out, x <- x + layer_l(rmsnorm(x)) with unit gain and
- * eps 1e-5 (without a norm, random SwiGLU layers blow the residual stream up within a few layers).
+ * block of a transformer with attention left out, x <- x + layer_l(rmsnorm(x) * gamma_l) (unit gain and
+ * eps 1e-5 unless atenia_moe_stack_set_norm says otherwise; without a norm, random SwiGLU layers blow
+ * the residual stream up within a few layers).
  * Both require f32 input.  The stack
  * borrows the layers (single GPU, or expert-parallel with replicated tokens or the direct exchange;
  * equal d_model, else
@@ -386,6 +398,10 @@ ATENIA_API int atenia_moe_stack_create(AteniaMoeLayer* const* layers, int n_laye
                                        AteniaMoeStack** out);
 ATENIA_API int atenia_moe_stack_forward(AteniaMoeStack* stack, const void* x, int x_dtype, int T, void* out,
                                         int out_dtype, void* stream);
+/* Gains and epsilon of the pre-norm of a `residual` = 2 stack: `gammas` is a HOST array of n_layers
+ * DEVICE pointers to f32 [d] vectors (an entry, or the whole array, may be NULL = unit gain); the
+ * vectors are borrowed.  ATENIA_ERR_STATE for a stack without a pre-norm. */
+ATENIA_API int atenia_moe_stack_set_norm(AteniaMoeStack* stack, const float* const* gammas, float eps);
 /* Waits for the stream and returns the first error any layer's kernels recorded. */
 ATENIA_API int atenia_moe_stack_check(AteniaMoeStack* stack, void* stream);
 ATENIA_API int atenia_moe_stack_destroy(AteniaMoeStack* stack);

@@ -577,3 +577,23 @@ ORACLE_API int oracle_max_threads(void) {
   return 1;
 #endif
 }
+
+/* Post-attention RMSNorm and its gain, as applied before the MoE block: rms_norm
+ * (src/nn/normalization.rs:8-37: f32 sum of squares in index order, mean over the row, 1 / sqrt(mean +
+ * eps), x * inv_rms) followed by broadcast_mul with gamma (src/moe/full_forward.rs:239-242).
+ * gamma may be NULL (unit gain). */
+ORACLE_API void oracle_rms_norm_gamma(const float* x, int T, int d, const float* gamma, float eps, float* out) {
+  for (int t = 0; t < T; ++t) {
+    const float* row = x + (size_t)t * d;
+    float sum_sq = 0.0f;
+    for (int i = 0; i < d; ++i) sum_sq += row[i] * row[i];
+    const float cols = d > 1 ? (float)d : 1.0f;
+    const float mean_sq = sum_sq / cols;
+    const float inv_rms = 1.0f / sqrtf(mean_sq + eps);
+    for (int i = 0; i < d; ++i) {
+      const float n = row[i] * inv_rms;
+      out[(size_t)t * d + i] = gamma ? n * gamma[i] : n;
+    }
+  }
+}
+

@@ -297,3 +297,14 @@ def expert_forward(w_gate, w_up, w_down, x, accum=ACC_F64):
     lib().oracle_expert_forward_f32(_ptr(w_gate), _ptr(w_up), _ptr(w_down), C.c_int(d), C.c_int(F),
                                     C.c_int(accum), _ptr(x), _ptr(y))
     return y
+
+
+def rms_norm_gamma(x, gamma=None, eps=1e-5):
+    """rms_norm(x, eps) * gamma over the last dimension of a [T, d] f32 array."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    T, d = x.shape
+    g = None if gamma is None else np.ascontiguousarray(gamma, dtype=np.float32).reshape(-1)
+    out = np.empty_like(x)
+    lib().oracle_rms_norm_gamma(_ptr(x), C.c_int(T), C.c_int(d), _ptr(g), C.c_float(eps), _ptr(out))
+    return out
+

@@ -37,7 +37,7 @@ class Bar:
 
 
 class Sim:
-    acc_bufs = 2  # 1 models w8_gemm_alt.cu: same widening protocol, single accumulator buffer
+    acc_bufs = 2  # 1 models w8_gemm.cu: same widening protocol, single accumulator buffer
 
     def __init__(self, tiles, seed):
         self.rng = random.Random(seed)
@@ -231,7 +231,7 @@ def test_protocol_has_no_deadlock_or_hazard(tiles):
 
 @pytest.mark.parametrize("tiles", [[(1, 1)], [(7, 1), (3, 1)], [(64, 1)] * 2, [(2, 1)] * 7, [(224, 1)]])
 def test_alternating_groups_with_a_single_accumulator(tiles):
-    """The decode variant (w8_gemm_alt.cu): stream-K pieces of any length, one accumulator buffer."""
+    """The decode variant (w8_gemm.cu): stream-K pieces of any length, one accumulator buffer."""
     class Single(Sim):
         acc_bufs = 1
     for seed in range(8):

@@ -8,11 +8,7 @@ import torch
 from tests.helpers import rel_l2
 from tests.test_gpu_parity import TOL_BF16, _run_parity, _synth, dev  # noqa: F401
 
-# The kernel is opt-in in the library and so are its tests until it has been brought up on hardware:
-# ATENIA_TEST_BF16_DECODE=1 runs them.
-pytestmark = [pytest.mark.gpu,
-              pytest.mark.skipif(os.environ.get("ATENIA_TEST_BF16_DECODE", "0") != "1",
-                                 reason="opt-in kernel: set ATENIA_TEST_BF16_DECODE=1")]
+pytestmark = pytest.mark.gpu
 
 
 @pytest.mark.parametrize("name,d_model,d_ff,shared,T", [
@@ -32,6 +28,7 @@ def test_decode_kernel_agrees_with_default_kernels(dev, monkeypatch):
     shape = synth.small(synth.SHAPES["mixtral"], d_model=1024, d_ff=2048)
     w = synth.make_weights(shape, 23, dev)
     x = synth.make_activations(shape, 23, dev, tokens=64)
+    monkeypatch.setenv("ATENIA_MOE_BF16_DECODE", "0")  # the 128-row-tile kernels as the other side
     base = synth.build_layer(shape, w, max_tokens=200)
     monkeypatch.setenv("ATENIA_MOE_BF16_DECODE", "1")
     layer = synth.build_layer(shape, w, max_tokens=200)

@@ -9,11 +9,7 @@ from tests.test_gpu_parity import TOL_W8A16, _run_parity, _synth, dev  # noqa: F
 
 import os
 
-# The kernel is opt-in in the library (ATENIA_MOE_W8_MODE=3) and so are its tests until it has been
-# brought up on hardware: ATENIA_TEST_W8_WIDE=1 runs them.
-pytestmark = [pytest.mark.gpu,
-              pytest.mark.skipif(os.environ.get("ATENIA_TEST_W8_WIDE", "0") != "1",
-                                 reason="opt-in kernel: set ATENIA_TEST_W8_WIDE=1")]
+pytestmark = pytest.mark.gpu
 
 
 @pytest.mark.parametrize("d_model,d_ff,T", [(512, 768, 700), (512, 768, 2600), (528, 400, 1500), (1024, 2048, 4096)])
@@ -31,6 +27,7 @@ def test_wide_kernel_agrees_with_default_kernels(dev, monkeypatch):
     shape = synth.small(synth.SHAPES["mixtral_int8"], d_model=512, d_ff=768)
     w = synth.make_weights(shape, 21, dev)
     x = synth.make_activations(shape, 21, dev, tokens=3000)
+    monkeypatch.setenv("ATENIA_MOE_W8_MODE", "2")  # the shared-memory widening kernel as the other side
     a = synth.build_layer(shape, w, max_tokens=3000).forward(x, out_dtype=torch.float32, sync=True)
     monkeypatch.setenv("ATENIA_MOE_W8_MODE", "3")
     layer = synth.build_layer(shape, w, max_tokens=3000)
