@@ -180,6 +180,9 @@ constexpr size_t kW8SplitKSlotFloats = 2 * 128 * 128;  // per CTA: two slots of 
 // tmap_a is the bf16 token matrix with box {64, 64} (128B swizzle); tmap_b0/b1 are int8 maps with box
 // {64, 64} and the 64-byte swizzle.
 int launch_grouped_gemm_w8_wide(const GroupedGemmArgs& a, int num_sms, cudaStream_t s);
+// W8A16 for large groups (w8_gemm_m256.cu): 256-row token tiles, the widened weight tile shared by two
+// M128 MMAs.  Tensor maps as for launch_grouped_gemm_tcgen05 with w8 set.
+int launch_grouped_gemm_w8_m256(const GroupedGemmArgs& a, int num_sms, cudaStream_t s);
 // bf16 weights, groups of at most 128 rows (bf16_decode_gemm.cu): transposed product with stream-K over
 // the SMs; tmap_a / tmap_b0 / tmap_b1 are the maps of launch_grouped_gemm_tcgen05, splitk_ws as for
 // the INT8 tensor-memory kernel (null: whole tiles only).

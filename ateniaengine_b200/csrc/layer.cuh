@@ -23,12 +23,12 @@ struct AteniaMoeLayer {
   float* block_normed = nullptr;    // [max_tokens, d] f32, allocated by the first atenia_moe_block_forward
   // INT8: 0 = pick per call (tensor-memory operand kernel of w8_gemm.cu for small groups, the wide
   // tensor-memory kernel of w8_gemm_wide.cu for large ones), 1 = always the small-group kernel,
-  // 2 = always shared-memory widening (grouped_gemm.cu), 3 = as 0
+  // 2 = always shared-memory widening (grouped_gemm.cu), 3 = as 0, 4 = w8_gemm_m256.cu for large groups
   int w8_mode = 0;
   // bf16: 0 = pick per call (CTA-pair kernel once groups average >= 512 rows), 1 = always pairs,
   // 2 = always the single-CTA kernel
   int pair_mode = 0;
-  // bf16 stream-K decode kernel: -1 = calls of at most 32 rows, 1 = every call of at most 128 rows
+  // bf16 stream-K decode kernel: -1 = calls of at most 16 rows, 1 = every call of at most 128 rows
   // (ATENIA_MOE_BF16_DECODE=1), 0 = never (=0, or INT8 weights)
   int bf16_decode = -1;
   // router kernel: -1 by size, 0 CUDA cores (router.cu), 1 f64 tensor cores (router_dmma.cu),

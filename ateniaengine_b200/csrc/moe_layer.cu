@@ -60,13 +60,15 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
   // grouped_gemm.cu (tests, A/B runs).
   const bool wide_ok = q && L->has_r64 && tm_a64 && tm_mid64 && !L->use_check_gemm;
   const bool wide = wide_ok && large && (L->w8_mode == 0 || L->w8_mode == 3);
-  const bool tmem = q && !wide && (L->w8_mode == 1 || ((L->w8_mode == 0 || L->w8_mode == 3) && !large));
+  // w8_mode 4: the 256-row-tile kernel of w8_gemm_m256.cu for large groups
+  const bool m256 = q && large && L->w8_mode == 4 && !L->use_check_gemm;
+  const bool tmem = q && !wide && !m256 && (L->w8_mode == 1 || (L->w8_mode != 2 && !large));
   // bf16: 256-row CTA-pair tiles pay off once an average group fills a few of them; a call of at most
-  // 32 rows (decode) takes the stream-K kernel of bf16_decode_gemm.cu, which spreads the few tiles
+  // 16 rows (decode) takes the stream-K kernel of bf16_decode_gemm.cu, which spreads the few tiles
   // there are over all SMs (bf16_decode 1 / 0 pins it on for every call of at most 128 rows / off).
   const bool dec = !q && !L->use_check_gemm && L->splitk_ws &&
-                   (L->bf16_decode == 1 ? max_rows <= 128 : (L->bf16_decode < 0 && max_rows <= 32));
-  const bool pairs = !tmem && !wide && !dec && (L->pair_mode == 1 || (L->pair_mode == 0 && !q && max_rows >= 512 * num_groups));
+                   (L->bf16_decode == 1 ? max_rows <= 128 : (L->bf16_decode < 0 && max_rows <= 16));
+  const bool pairs = !tmem && !wide && !m256 && !dec && (L->pair_mode == 1 || (L->pair_mode == 0 && !q && max_rows >= 512 * num_groups));
   if (L->timing) cudaEventRecord(L->ev[0], s);
   if (L->use_check_gemm) {
     GroupedGemmCheckArgs k1{a_ptr, L->d_p_gate, L->d_p_up, q ? 1 : 0, q ? L->d_sc_gate : nullptr,
@@ -92,6 +94,7 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
     g1.w8 = q;
     g1.splitk_ws = L->splitk_ws;
     int rc = wide ? launch_grouped_gemm_w8_wide(g1, L->num_sms, s)
+                  : m256 ? launch_grouped_gemm_w8_m256(g1, L->num_sms, s)
                   : dec ? launch_grouped_gemm_bf16_decode(g1, L->num_sms, s)
                   : tmem ? launch_grouped_gemm_w8_tmem(g1, L->num_sms, s)
                          : pairs ? launch_grouped_gemm_2cta(g1, L->num_sms, s)
@@ -122,6 +125,7 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
     g2.w8 = q;
     g2.splitk_ws = L->splitk_ws;
     int rc = wide ? launch_grouped_gemm_w8_wide(g2, L->num_sms, s)
+                  : m256 ? launch_grouped_gemm_w8_m256(g2, L->num_sms, s)
                   : dec ? launch_grouped_gemm_bf16_decode(g2, L->num_sms, s)
                   : tmem ? launch_grouped_gemm_w8_tmem(g2, L->num_sms, s)
                          : pairs ? launch_grouped_gemm_2cta(g2, L->num_sms, s)

@@ -353,7 +353,7 @@ int launch_router(const RouterArgs& a, cudaStream_t s) {
   if (a.k > kMaxK || a.E > 128) return ATENIA_ERR_UNSUPPORTED;
   // variant -1: choose by size (see atenia_moe_create)
   if ((a.variant == 2 || a.variant == -1) && a.T <= a.sk_tokens && a.sk_part) return launch_router_splitk(a, s);
-  if (a.variant == 1 || (a.variant == -1 && a.E > 16 && a.d % 16 == 0)) return launch_router_dmma(a, s);
+  if (a.variant == 1 || (a.variant == -1 && a.d % 16 == 0)) return launch_router_dmma(a, s);
   dim3 block(kRWarps * 32);
   // more tokens per CTA for many experts: the router matrix is re-read once per CTA
   if (a.E <= 8) router_kernel<8, 8><<<(a.T + 7) / 8, block, 0, s>>>(a);

@@ -39,5 +39,7 @@ def test_same_routing_as_the_default_router_and_repeatable(dev, monkeypatch, E, 
         assert (a["topk_idx"].cpu().numpy() == b["topk_idx"].cpu().numpy()).all(axis=1).mean() >= 0.97
     assert torch.equal(outs[0][1]["logits"], outs[2][1]["logits"]) and torch.equal(outs[0][0], outs[2][0])
     # fewer tokens than the last call: only the counters of the first token blocks are touched
-    y1 = layer.forward(x[:3], out_dtype=torch.float32, sync=True)
-    assert torch.equal(y1, outs[0][0][:3])
+    y1, a1 = layer.forward(x[:3], out_dtype=torch.float32, aux=True, sync=True)
+    assert torch.equal(a1["logits"], outs[0][1]["logits"][:3]) and torch.equal(a1["topk_idx"], outs[0][1]["topk_idx"][:3])
+    # (three tokens take the decode GEMM kernel, thirty-seven the tile kernels: outputs agree to rounding)
+    assert (y1 - outs[0][0][:3]).abs().max() <= 2e-3 * outs[0][0].abs().max()
