@@ -223,7 +223,7 @@ int ep_forward_exchange(AteniaMoeLayer* L, int T, cudaStream_t s) {
   if (L->timing) cudaEventRecord(L->ph[2], s);
   L->last_recv_rows = (int)ro;
   rc = run_expert_gemms(L, L->tm_recv_x, L->tm_recv_h, L->recv_x, L->recv_h, L->recv_y, L->d_group_offsets,
-                        L->n_groups, (int)ro, s, &L->tm_recv_x_r64, &L->tm_recv_h_r64);
+                        L->n_groups, (int)ro, s);
   if (rc) return rc;
   if (L->timing) cudaEventRecord(L->ph[3], s);
   rc = exchange(comm, rank, G, L->recv_y, r_off, r_cnt, L->y_perm, s_off, s_cnt, d, s);
@@ -244,8 +244,7 @@ int ep_forward_replicated(AteniaMoeLayer* L, int n_rows, cudaStream_t s) {
   ATENIA_CUDA_TRY(cudaMemsetAsync(L->y_perm, 0, (size_t)n_rows * d * sizeof(__nv_bfloat16), s));
   if (L->timing) cudaEventRecord(L->ph[2], s);
   int rc = run_expert_gemms(L, L->tm_x_perm, L->tm_recv_h, L->x_perm, L->recv_h, L->y_perm,
-                            L->expert_offsets + L->e_begin, L->e_local, n_rows, s, &L->tm_x_perm_r64,
-                            &L->tm_recv_h_r64);
+                            L->expert_offsets + L->e_begin, L->e_local, n_rows, s);
   if (rc) return rc;
   if (L->timing) cudaEventRecord(L->ph[3], s);
   NCCL_TRY(ncclAllReduce(L->y_perm, L->y_perm, (size_t)n_rows * d, ncclBfloat16, ncclSum, L->ep->comm, s));
@@ -294,7 +293,7 @@ int ep_direct_finish(AteniaMoeLayer* L, cudaStream_t s) {
   // the number of rows received is known on the device only: size by the buffer.
   // one GEMM group per local expert: its rows from all sources are contiguous
   int rc = run_expert_gemms(L, L->tm_recv_x, L->tm_recv_h, L->recv_x, L->recv_h, L->recv_y, L->d_gemm_offsets, El,
-                            L->recv_cap, s, &L->tm_recv_x_r64, &L->tm_recv_h_r64);
+                            L->recv_cap, s);
   if (rc) return rc;
   if (L->timing) cudaEventRecord(L->ph[3], s);
   ep_return_kernel<<<L->num_sms * 16, kEpRowWarps * 32, 0, s>>>(L->recv_y, L->d_group_offsets, L->d_src_base, L->d_peer_y_perm,

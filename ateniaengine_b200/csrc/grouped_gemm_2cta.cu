@@ -304,324 +304,6 @@ grouped_gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const CUten
   }
 }
 
-// ---- W8A16 variant ------------------------------------------------------------------------------
-// Same pairing; each CTA receives its half of the weight tile as int8 (8 KiB per k-block), four
-// warps widen it to bf16 into a second ring (exact, see widen4) and the leader's MMA reads both
-// CTAs' widened halves.  Pairing halves the widening work per unit of math, which is what limits the
-// single-CTA shared-memory widening kernel.
-constexpr int W8P_STAGES = 5;   // TMA ring: A bf16 16 KiB + int8 half tile 8 KiB
-constexpr int W8P_CONV = 4;     // ring of widened bf16 half tiles, 16 KiB each
-constexpr int QH_BYTES2 = (BN2 / 2) * BK;  // 8 KiB
-constexpr int W8P_STAGE_BYTES = A_BYTES2 + QH_BYTES2;
-constexpr int W8P_CONV_WARPS = 16;
-constexpr int W8P_THREADS = 192 + W8P_CONV_WARPS * 32;  // + warps 6..21: widening
-constexpr int W8P_SMEM = W8P_STAGES * W8P_STAGE_BYTES + W8P_CONV * BH_BYTES2 + 1024 + 256;
-
-struct __align__(8) BarriersW8P {
-  uint64_t full[W8P_STAGES];       // leader: token tiles of both CTAs landed
-  uint64_t qfull[W8P_STAGES];      // local: this CTA's int8 half tile landed
-  uint64_t empty[W8P_STAGES];      // local: MMA done with A (commit) + the widening warps done with int8
-  uint64_t conv_full[W8P_CONV];    // leader: widened halves of both CTAs ready (all widening warps of both)
-  uint64_t conv_empty[W8P_CONV];   // local: MMAs that read the widened tile are done (commit)
-  uint64_t acc_full[ACC_BUFS2];
-  uint64_t acc_empty[ACC_BUFS2];
-  uint32_t tmem_base;
-  int abort_flag;
-};
-
-template <int MODE>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(W8P_THREADS, 1)
-grouped_gemm_2cta_w8_kernel(const __grid_constant__ CUtensorMap tmap_a, const CUtensorMap* __restrict__ tmap_b0,
-                            const CUtensorMap* __restrict__ tmap_b1, const int32_t* __restrict__ group_offsets,
-                            int num_groups, int N, int K, __nv_bfloat16* __restrict__ out,
-                            const float* const* __restrict__ scale0, const float* const* __restrict__ scale1,
-                            DeviceError* err) {
-  extern __shared__ uint8_t smem_raw[];
-  constexpr int BN_OUT = (MODE == kSwiGLU) ? BN2 / 2 : BN2;
-  constexpr uint32_t CONV_OFF = W8P_STAGES * W8P_STAGE_BYTES;
-  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  uint8_t* smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
-  BarriersW8P* bars = reinterpret_cast<BarriersW8P*>(smem_aligned + CONV_OFF + W8P_CONV * BH_BYTES2);
-  volatile int* abort_flag = &bars->abort_flag;
-
-  const int warp = threadIdx.x >> 5;
-  const int lane = threadIdx.x & 31;
-  const uint32_t rank = cluster_ctarank();
-  const bool leader = rank == 0;
-  const int pair = blockIdx.x >> 1;
-  const int num_pairs = gridDim.x >> 1;
-  const int num_kb = (K + BK - 1) / BK;
-  const int n_tiles = (N + BN_OUT - 1) / BN_OUT;
-
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < W8P_STAGES; ++s) {
-      mbar_init(smem_u32(&bars->full[s]), 1);
-      mbar_init(smem_u32(&bars->qfull[s]), 1);
-      mbar_init(smem_u32(&bars->empty[s]), 1 + W8P_CONV_WARPS);
-    }
-    for (int c = 0; c < W8P_CONV; ++c) {
-      mbar_init(smem_u32(&bars->conv_full[c]), 2 * W8P_CONV_WARPS);
-      mbar_init(smem_u32(&bars->conv_empty[c]), 1);
-    }
-    for (int b = 0; b < ACC_BUFS2; ++b) {
-      mbar_init(smem_u32(&bars->acc_full[b]), 1);
-      mbar_init(smem_u32(&bars->acc_empty[b]), 8);
-    }
-    bars->abort_flag = 0;
-    fence_barrier_init();
-  }
-  if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
-                     smem_u32(&bars->tmem_base)),
-                 "r"(TMEM_COLS2)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
-  }
-  tc_fence_before();
-  __syncthreads();
-  cluster_sync_all();
-  tc_fence_after();
-  const uint32_t tmem_base = bars->tmem_base;
-
-  TileCursor cur;
-  cur.group = 0;
-  cur.base = 0;
-  if (num_groups > 0) cursor_load(cur, group_offsets, PAIR_ROWS);
-  TileCoord tc;
-
-  if (warp == 0) {
-    // ================= TMA producer (both CTAs) =================
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      int last_group = -1;
-      bool ok = true;
-      for (int tile = pair; ok && cursor_seek(cur, tile, n_tiles, num_groups, group_offsets, tc, BN_OUT, PAIR_ROWS);
-           tile += num_pairs) {
-        const CUtensorMap* mb;
-        int nb;
-        if (MODE == kSwiGLU) {
-          mb = leader ? &tmap_b0[tc.group] : &tmap_b1[tc.group];
-          nb = tc.n0;
-        } else {
-          mb = &tmap_b0[tc.group];
-          nb = tc.n0 + (leader ? 0 : BN2 / 2);
-        }
-        if (tc.group != last_group) {
-          tmap_acquire(mb);
-          last_group = tc.group;
-        }
-        const int my_row0 = tc.row0 + (int)rank * BM;
-        for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(smem_u32(&bars->empty[stage]), phase ^ 1u, abort_flag)) {
-            report_error(err, ATENIA_ERR_DEVICE_TIMEOUT, 1500 + stage);
-            *abort_flag = 1;
-            ok = false;
-            break;
-          }
-          const uint32_t full_local = smem_u32(&bars->full[stage]);
-          const uint32_t qfull = smem_u32(&bars->qfull[stage]);
-          const uint32_t sa = smem_base + stage * W8P_STAGE_BYTES;
-          if (leader) mbar_expect_tx(full_local, 2 * A_BYTES2);
-          tma_load_2d_pair(sa, &tmap_a, mapa(full_local, 0), kb * BK, my_row0);
-          mbar_expect_tx(qfull, QH_BYTES2);
-          tma_load_2d(sa + A_BYTES2, mb, qfull, kb * BK, nb);
-          if (++stage == W8P_STAGES) {
-            stage = 0;
-            phase ^= 1u;
-          }
-        }
-      }
-    }
-  } else if (warp == 1) {
-    // ================= MMA issuer (leader CTA only) =================
-    if (leader && lane == 0) {
-      int stage = 0, cstage = 0;
-      uint32_t phase = 0, cphase = 0;
-      uint32_t acc_phase[ACC_BUFS2] = {0, 0};
-      int it = 0;
-      bool ok = true;
-      for (int tile = pair; ok && cursor_seek(cur, tile, n_tiles, num_groups, group_offsets, tc, BN_OUT, PAIR_ROWS);
-           tile += num_pairs, ++it) {
-        const int acc = it & 1;
-        if (!mbar_wait(smem_u32(&bars->acc_empty[acc]), acc_phase[acc] ^ 1u, abort_flag)) {
-          report_error(err, ATENIA_ERR_DEVICE_TIMEOUT, 1600 + acc);
-          *abort_flag = 1;
-          break;
-        }
-        acc_phase[acc] ^= 1u;
-        tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * BN2;
-        for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(smem_u32(&bars->full[stage]), phase, abort_flag) ||
-              !mbar_wait(smem_u32(&bars->conv_full[cstage]), cphase, abort_flag)) {
-            report_error(err, ATENIA_ERR_DEVICE_TIMEOUT, 1700 + stage);
-            *abort_flag = 1;
-            ok = false;
-            break;
-          }
-          tc_fence_after();
-          const uint64_t da = make_smem_desc(smem_base + stage * W8P_STAGE_BYTES);
-          const uint64_t db = make_smem_desc(smem_base + CONV_OFF + cstage * BH_BYTES2);
-#pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k)
-            tc_mma_bf16_pair(d_tmem, da + 2 * k, db + 2 * k, kInstrDesc2, (kb > 0 || k > 0) ? 1u : 0u);
-          tc_commit_pair(smem_u32(&bars->empty[stage]));
-          tc_commit_pair(smem_u32(&bars->conv_empty[cstage]));
-          if (++stage == W8P_STAGES) {
-            stage = 0;
-            phase ^= 1u;
-          }
-          if (++cstage == W8P_CONV) {
-            cstage = 0;
-            cphase ^= 1u;
-          }
-        }
-        if (ok) tc_commit_pair(smem_u32(&bars->acc_full[acc]));
-      }
-    }
-  } else if (warp >= 6) {
-    // ================= int8 -> bf16 widening of this CTA's half tile (warps 6..) =================
-    // 128 rows x 64 int8 per k-block = 512 16-byte pieces; thread t takes (row = (t >> 2) + 8 W i, c = t & 3)
-    // for W widening warps.  Each warp is latency-bound on its own load-widen-store chain, so many
-    // warps with one piece each beat few warps with several.
-    const int ct = threadIdx.x - 192;
-    int stage = 0, cstage = 0;
-    uint32_t phase = 0, cphase = 0;
-    bool ok = true;
-    for (int tile = pair; ok && cursor_seek(cur, tile, n_tiles, num_groups, group_offsets, tc, BN_OUT, PAIR_ROWS);
-         tile += num_pairs) {
-      for (int kb = 0; kb < num_kb; ++kb) {
-        if (!mbar_wait(smem_u32(&bars->qfull[stage]), phase, abort_flag) ||
-            !mbar_wait(smem_u32(&bars->conv_empty[cstage]), cphase ^ 1u, abort_flag)) {
-          if (lane == 0) report_error(err, ATENIA_ERR_DEVICE_TIMEOUT, 1800 + warp);
-          *abort_flag = 1;
-          ok = false;
-          break;
-        }
-        const uint8_t* q = smem_aligned + stage * W8P_STAGE_BYTES + A_BYTES2;
-        uint8_t* b = smem_aligned + CONV_OFF + cstage * BH_BYTES2;
-        const int c = ct & 3;
-#pragma unroll
-        for (int i = 0; i < (BN2 / 2) / (W8P_CONV_WARPS * 8); ++i) {
-          const int row = (ct >> 2) + W8P_CONV_WARPS * 8 * i;
-          const uint4 v = *reinterpret_cast<const uint4*>(q + row * BK + c * 16);
-          uint4 o0, o1;
-          widen4(v.x, o0.x, o0.y);
-          widen4(v.y, o0.z, o0.w);
-          widen4(v.z, o1.x, o1.y);
-          widen4(v.w, o1.z, o1.w);
-          uint8_t* line = b + row * 128;
-          *reinterpret_cast<uint4*>(line + (((2 * c) ^ (row & 7)) << 4)) = o0;
-          *reinterpret_cast<uint4*>(line + (((2 * c + 1) ^ (row & 7)) << 4)) = o1;
-        }
-        fence_proxy_async();
-        __syncwarp();
-        if (lane == 0) {
-          mbar_arrive_remote(mapa(smem_u32(&bars->conv_full[cstage]), 0));
-          mbar_arrive(smem_u32(&bars->empty[stage]));
-        }
-        if (++stage == W8P_STAGES) {
-          stage = 0;
-          phase ^= 1u;
-        }
-        if (++cstage == W8P_CONV) {
-          cstage = 0;
-          cphase ^= 1u;
-        }
-      }
-    }
-  } else {
-    // ================= epilogue (warps 2..5 of both CTAs) =================
-    const int quarter = warp & 3;
-    const int row_in_tile = quarter * 32 + lane;
-    uint32_t acc_phase[ACC_BUFS2] = {0, 0};
-    int it = 0;
-    for (int tile = pair; cursor_seek(cur, tile, n_tiles, num_groups, group_offsets, tc, BN_OUT, PAIR_ROWS);
-         tile += num_pairs, ++it) {
-      const int acc = it & 1;
-      if (!mbar_wait(smem_u32(&bars->acc_full[acc]), acc_phase[acc], abort_flag)) {
-        if (lane == 0) report_error(err, ATENIA_ERR_DEVICE_TIMEOUT, 1900 + acc);
-        *abort_flag = 1;
-        break;
-      }
-      acc_phase[acc] ^= 1u;
-      tc_fence_after();
-      const int grow = tc.row0 + (int)rank * BM + row_in_tile;
-      const bool row_ok = grow < tc.row_end;
-      const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN2;
-      __nv_bfloat16* orow = out + (size_t)grow * N;
-      const float* sc0 = scale0[tc.group];
-      if (MODE == kSwiGLU) {
-        const float* sc1 = scale1[tc.group];
-#pragma unroll 1
-        for (int c = 0; c < BN_OUT; c += 16) {
-          uint32_t g[16], u[16];
-          tc_ld16(taddr + c, g);
-          tc_ld16(taddr + BN_OUT + c, u);
-          tc_ld_wait();
-          const int n = tc.n0 + c;
-          if (row_ok && n < N) {
-            uint32_t p[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const float g0 = __uint_as_float(g[2 * j]) * sc0[n + 2 * j], g1 = __uint_as_float(g[2 * j + 1]) * sc0[n + 2 * j + 1];
-              const float u0 = __uint_as_float(u[2 * j]) * sc1[n + 2 * j], u1 = __uint_as_float(u[2 * j + 1]) * sc1[n + 2 * j + 1];
-              p[j] = pack_bf16x2(silu_mul(g0, u0), silu_mul(g1, u1));
-            }
-            uint4* dst = reinterpret_cast<uint4*>(orow + n);
-            dst[0] = make_uint4(p[0], p[1], p[2], p[3]);
-            dst[1] = make_uint4(p[4], p[5], p[6], p[7]);
-          }
-        }
-      } else {
-#pragma unroll 1
-        for (int c = 0; c < BN_OUT; c += 16) {
-          uint32_t v[16];
-          tc_ld16(taddr + c, v);
-          tc_ld_wait();
-          const int n = tc.n0 + c;
-          if (row_ok && n < N) {
-            uint32_t p[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j)
-              p[j] = pack_bf16x2(__uint_as_float(v[2 * j]) * sc0[n + 2 * j], __uint_as_float(v[2 * j + 1]) * sc0[n + 2 * j + 1]);
-            uint4* dst = reinterpret_cast<uint4*>(orow + n);
-            dst[0] = make_uint4(p[0], p[1], p[2], p[3]);
-            dst[1] = make_uint4(p[4], p[5], p[6], p[7]);
-          }
-        }
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive_remote(mapa(smem_u32(&bars->acc_empty[acc]), 0));
-    }
-  }
-
-  tc_fence_before();
-  __syncthreads();
-  cluster_sync_all();
-  if (warp == 1) {
-    __syncwarp();
-    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS2)
-                 : "memory");
-  }
-}
-
-template <int MODE>
-int launch_2cta_w8_one(const GroupedGemmArgs& a, int num_sms, cudaStream_t s) {
-  static bool attr_set[kMaxDevices] = {};
-  if (first_use_on_current_device(attr_set)) {
-    ATENIA_CUDA_TRY(cudaFuncSetAttribute(grouped_gemm_2cta_w8_kernel<MODE>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, W8P_SMEM));
-  }
-  const int grid = num_sms & ~1;
-  grouped_gemm_2cta_w8_kernel<MODE><<<dim3(grid), dim3(W8P_THREADS), W8P_SMEM, s>>>(
-      a.tmap_a, a.tmap_b0, MODE == kSwiGLU ? a.tmap_b1 : a.tmap_b0, a.group_offsets, a.num_groups, a.N, a.K, a.out,
-      a.scale0, a.scale1, a.err);
-  return (int)cudaGetLastError();
-}
-
 template <int MODE>
 int launch_2cta_one(const GroupedGemmArgs& a, int num_sms, cudaStream_t s) {
   static bool attr_set[kMaxDevices] = {};
@@ -641,13 +323,8 @@ int launch_2cta_one(const GroupedGemmArgs& a, int num_sms, cudaStream_t s) {
 int launch_grouped_gemm_2cta(const GroupedGemmArgs& a, int num_sms, cudaStream_t s) {
   if (a.num_groups <= 0) return ATENIA_OK;
   if (a.N % 16 != 0 || a.K % 16 != 0) return ATENIA_ERR_SHAPE;
-  int rc;
-  if (a.w8) {
-    if (!a.scale0 || (a.mode == kSwiGLU && !a.scale1)) return ATENIA_ERR_NULL;
-    rc = a.mode == kSwiGLU ? launch_2cta_w8_one<kSwiGLU>(a, num_sms, s) : launch_2cta_w8_one<kPlain>(a, num_sms, s);
-  } else {
-    rc = a.mode == kSwiGLU ? launch_2cta_one<kSwiGLU>(a, num_sms, s) : launch_2cta_one<kPlain>(a, num_sms, s);
-  }
+  if (a.w8) return ATENIA_ERR_UNSUPPORTED;  // INT8 weights: w8_gemm.cu / w8_gemm_m256.cu
+  int rc = a.mode == kSwiGLU ? launch_2cta_one<kSwiGLU>(a, num_sms, s) : launch_2cta_one<kPlain>(a, num_sms, s);
   count_launch();
   count_tcgen05_launch();
   return rc;

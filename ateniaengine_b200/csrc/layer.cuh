@@ -21,9 +21,9 @@ struct AteniaMoeLayer {
   bool timing = false;
   const float* residual = nullptr;  // set by a stack around one forward: added by the combine kernel
   float* block_normed = nullptr;    // [max_tokens, d] f32, allocated by the first atenia_moe_block_forward
-  // INT8: 0 = pick per call (tensor-memory operand kernel of w8_gemm.cu for small groups, the wide
-  // tensor-memory kernel of w8_gemm_wide.cu for large ones), 1 = always the small-group kernel,
-  // 2 = always shared-memory widening (grouped_gemm.cu), 3 = as 0, 4 = w8_gemm_m256.cu for large groups
+  // INT8: 0 = pick per call (tensor-memory operand kernel of w8_gemm.cu for small groups, the 256-row
+  // tile kernel of w8_gemm_m256.cu for large ones), 1 = always the small-group kernel,
+  // 2 = always the 128-row shared-memory widening kernel (grouped_gemm.cu)
   int w8_mode = 0;
   // bf16: 0 = pick per call (CTA-pair kernel once groups average >= 512 rows), 1 = always pairs,
   // 2 = always the single-CTA kernel
@@ -57,10 +57,6 @@ struct AteniaMoeLayer {
   CUtensorMap* d_tm_up_sw = nullptr;
   CUtensorMap* d_tm_down_sw = nullptr;
   CUtensorMap* d_tm_shared_sw = nullptr;
-  // w8_mode 3 only: the routed matrices once more with 64-row boxes (64-byte swizzle)
-  CUtensorMap* d_tm_gate_r64 = nullptr;
-  CUtensorMap* d_tm_up_r64 = nullptr;
-  CUtensorMap* d_tm_down_r64 = nullptr;
   const float** d_sc_gate = nullptr;   // [n_groups] device pointers (INT8) or null
   const float** d_sc_up = nullptr;
   const float** d_sc_down = nullptr;
@@ -91,8 +87,6 @@ struct AteniaMoeLayer {
   atenia::DeviceError* d_err = nullptr;
   float* splitk_ws = nullptr;  // INT8: stream-K partial sums, 2 slots per SM
   CUtensorMap tm_x_perm{}, tm_h{}, tm_h_shared{};
-  CUtensorMap tm_x_perm_r64{}, tm_h_r64{}, tm_recv_x_r64{}, tm_recv_h_r64{};  // w8_mode 3: 64-row boxes
-  bool has_r64 = false;
 
   // expert parallelism
   std::shared_ptr<atenia::EpComm> ep;  // layers of one stack may share a communicator (atenia_moe_ep_attach)
@@ -138,9 +132,7 @@ bool ep_ready(const AteniaMoeLayer* L);
 // ATENIA_ERR_NCCL, so a collective whose peer never arrives cannot block the host for ever.
 int ep_bounded_wait(AteniaMoeLayer* L, cudaStream_t s);
 void ep_destroy(AteniaMoeLayer* L);
-// tm_a64 / tm_mid64: the same two matrices described with 64-row boxes (w8_mode 3), or null
 int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorMap& tm_mid,
                      const __nv_bfloat16* a_ptr, __nv_bfloat16* mid, __nv_bfloat16* out,
-                     const int32_t* group_offsets, int num_groups, int max_rows, cudaStream_t s,
-                     const CUtensorMap* tm_a64 = nullptr, const CUtensorMap* tm_mid64 = nullptr);
+                     const int32_t* group_offsets, int num_groups, int max_rows, cudaStream_t s);
 }  // namespace atenia

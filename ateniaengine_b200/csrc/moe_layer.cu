@@ -49,26 +49,23 @@ int validate_config(const AteniaMoeConfig& c) {
 
 int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorMap& tm_mid,
                      const __nv_bfloat16* a_ptr, __nv_bfloat16* mid, __nv_bfloat16* out,
-                     const int32_t* group_offsets, int num_groups, int max_rows, cudaStream_t s,
-                     const CUtensorMap* tm_a64, const CUtensorMap* tm_mid64) {
+                     const int32_t* group_offsets, int num_groups, int max_rows, cudaStream_t s) {
   const AteniaMoeConfig& c = L->cfg;
   const bool q = c.weight_dtype == ATENIA_W_INT8_ROW;
   const bool large = max_rows >= 256 * num_groups;
   // INT8: the tensor-memory kernel of w8_gemm.cu while groups are small (its MMA width follows the row
-  // count), the wide tensor-memory kernel (one widened weight tile per 192 tokens) once every group
-  // fills several tiles.  w8_mode 1 / 2 pin the small-group kernel / the shared-memory widening kernel of
-  // grouped_gemm.cu (tests, A/B runs).
-  const bool wide_ok = q && L->has_r64 && tm_a64 && tm_mid64 && !L->use_check_gemm;
-  const bool wide = wide_ok && large && (L->w8_mode == 0 || L->w8_mode == 3);
-  // w8_mode 4: the 256-row-tile kernel of w8_gemm_m256.cu for large groups
-  const bool m256 = q && large && L->w8_mode == 4 && !L->use_check_gemm;
-  const bool tmem = q && !wide && !m256 && (L->w8_mode == 1 || (L->w8_mode != 2 && !large));
+  // count), the 256-row-tile kernel of w8_gemm_m256.cu once every group fills a tile (measured on B200,
+  // Mixtral shape: 1.07 / 1.61 / 2.51 ms at 1024 / 2048 / 4096 tokens against 1.27 / - / 3.56 ms of the
+  // 128-row shared-memory widening kernel).  w8_mode 1 / 2 pin the small-group kernel / the 128-row
+  // shared-memory widening kernel of grouped_gemm.cu (tests, A/B runs).
+  const bool m256 = q && large && L->w8_mode != 1 && L->w8_mode != 2 && !L->use_check_gemm;
+  const bool tmem = q && !m256 && (L->w8_mode == 1 || (L->w8_mode != 2 && !large));
   // bf16: 256-row CTA-pair tiles pay off once an average group fills a few of them; a call of at most
   // 16 rows (decode) takes the stream-K kernel of bf16_decode_gemm.cu, which spreads the few tiles
   // there are over all SMs (bf16_decode 1 / 0 pins it on for every call of at most 128 rows / off).
   const bool dec = !q && !L->use_check_gemm && L->splitk_ws &&
                    (L->bf16_decode == 1 ? max_rows <= 128 : (L->bf16_decode < 0 && max_rows <= 16));
-  const bool pairs = !tmem && !wide && !m256 && !dec && (L->pair_mode == 1 || (L->pair_mode == 0 && !q && max_rows >= 512 * num_groups));
+  const bool pairs = !q && !dec && (L->pair_mode == 1 || (L->pair_mode == 0 && max_rows >= 512 * num_groups));
   if (L->timing) cudaEventRecord(L->ev[0], s);
   if (L->use_check_gemm) {
     GroupedGemmCheckArgs k1{a_ptr, L->d_p_gate, L->d_p_up, q ? 1 : 0, q ? L->d_sc_gate : nullptr,
@@ -78,9 +75,9 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
     if (rc) return rc;
   } else {
     GroupedGemmArgs g1{};
-    g1.tmap_a = wide ? *tm_a64 : tm_a;
-    g1.tmap_b0 = wide ? L->d_tm_gate_r64 : tmem ? L->d_tm_gate_sw : L->d_tm_gate;
-    g1.tmap_b1 = wide ? L->d_tm_up_r64 : tmem ? L->d_tm_up_sw : L->d_tm_up;
+    g1.tmap_a = tm_a;
+    g1.tmap_b0 = tmem ? L->d_tm_gate_sw : L->d_tm_gate;
+    g1.tmap_b1 = tmem ? L->d_tm_up_sw : L->d_tm_up;
     g1.group_offsets = group_offsets;
     g1.num_groups = num_groups;
     g1.N = c.d_ff;
@@ -93,8 +90,7 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
     g1.max_rows = max_rows;
     g1.w8 = q;
     g1.splitk_ws = L->splitk_ws;
-    int rc = wide ? launch_grouped_gemm_w8_wide(g1, L->num_sms, s)
-                  : m256 ? launch_grouped_gemm_w8_m256(g1, L->num_sms, s)
+    int rc = m256 ? launch_grouped_gemm_w8_m256(g1, L->num_sms, s)
                   : dec ? launch_grouped_gemm_bf16_decode(g1, L->num_sms, s)
                   : tmem ? launch_grouped_gemm_w8_tmem(g1, L->num_sms, s)
                          : pairs ? launch_grouped_gemm_2cta(g1, L->num_sms, s)
@@ -109,8 +105,8 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
     if (rc) return rc;
   } else {
     GroupedGemmArgs g2{};
-    g2.tmap_a = wide ? *tm_mid64 : tm_mid;
-    g2.tmap_b0 = wide ? L->d_tm_down_r64 : tmem ? L->d_tm_down_sw : L->d_tm_down;
+    g2.tmap_a = tm_mid;
+    g2.tmap_b0 = tmem ? L->d_tm_down_sw : L->d_tm_down;
     g2.tmap_b1 = g2.tmap_b0;
     g2.group_offsets = group_offsets;
     g2.num_groups = num_groups;
@@ -124,8 +120,7 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
     g2.max_rows = max_rows;
     g2.w8 = q;
     g2.splitk_ws = L->splitk_ws;
-    int rc = wide ? launch_grouped_gemm_w8_wide(g2, L->num_sms, s)
-                  : m256 ? launch_grouped_gemm_w8_m256(g2, L->num_sms, s)
+    int rc = m256 ? launch_grouped_gemm_w8_m256(g2, L->num_sms, s)
                   : dec ? launch_grouped_gemm_bf16_decode(g2, L->num_sms, s)
                   : tmem ? launch_grouped_gemm_w8_tmem(g2, L->num_sms, s)
                          : pairs ? launch_grouped_gemm_2cta(g2, L->num_sms, s)
@@ -145,9 +140,10 @@ int run_shared_gemms(AteniaMoeLayer* L, const __nv_bfloat16* xb, int T, cudaStre
   const AteniaMoeConfig& c = L->cfg;
   const bool q = c.weight_dtype == ATENIA_W_INT8_ROW;
   // (the shared expert is one group: INT8 takes the small-group kernel below 256 tokens and the
-  // shared-memory widening kernel above)
-  const bool tmem = q && (L->w8_mode == 1 || (L->w8_mode != 2 && T < 256));
-  const bool pairs = !tmem && (L->pair_mode == 1 || (L->pair_mode == 0 && !q && T >= 512));
+  // 256-row-tile kernel above)
+  const bool m256 = q && T >= 256 && L->w8_mode != 1 && L->w8_mode != 2 && !L->use_check_gemm;
+  const bool tmem = q && !m256 && (L->w8_mode == 1 || (L->w8_mode != 2 && T < 256));
+  const bool pairs = !q && (L->pair_mode == 1 || (L->pair_mode == 0 && T >= 512));
   if (L->timing) cudaEventRecord(L->ev[3], s);
   if (L->use_check_gemm) {
     GroupedGemmCheckArgs k1{xb, L->d_p_shared, L->d_p_shared + 1, q ? 1 : 0, q ? L->d_sc_shared : nullptr,
@@ -178,7 +174,8 @@ int run_shared_gemms(AteniaMoeLayer* L, const __nv_bfloat16* xb, int T, cudaStre
   g1.max_rows = T;
   g1.w8 = q;
   g1.splitk_ws = L->splitk_ws;
-  rc = tmem ? launch_grouped_gemm_w8_tmem(g1, L->num_sms, s)
+  rc = m256 ? launch_grouped_gemm_w8_m256(g1, L->num_sms, s)
+       : tmem ? launch_grouped_gemm_w8_tmem(g1, L->num_sms, s)
                   : pairs ? launch_grouped_gemm_2cta(g1, L->num_sms, s) : launch_grouped_gemm_tcgen05(g1, L->num_sms, s);
   if (rc) return rc;
   if (L->timing) cudaEventRecord(L->ev[4], s);
@@ -197,7 +194,8 @@ int run_shared_gemms(AteniaMoeLayer* L, const __nv_bfloat16* xb, int T, cudaStre
   g2.max_rows = T;
   g2.w8 = q;
   g2.splitk_ws = L->splitk_ws;
-  rc = tmem ? launch_grouped_gemm_w8_tmem(g2, L->num_sms, s)
+  rc = m256 ? launch_grouped_gemm_w8_m256(g2, L->num_sms, s)
+       : tmem ? launch_grouped_gemm_w8_tmem(g2, L->num_sms, s)
                   : pairs ? launch_grouped_gemm_2cta(g2, L->num_sms, s) : launch_grouped_gemm_tcgen05(g2, L->num_sms, s);
   if (rc) return rc;
   if (L->timing) {
@@ -312,12 +310,6 @@ int atenia_moe_create(const AteniaMoeConfig* cfg, AteniaMoeLayer** out) {
     TRY_ALLOC(L->d_tm_up_sw, (size_t)L->n_groups);
     TRY_ALLOC(L->d_tm_down_sw, (size_t)L->n_groups);
     TRY_ALLOC(L->d_tm_shared_sw, 3);
-    if (L->w8_mode == 0 || L->w8_mode == 3) {
-      TRY_ALLOC(L->d_tm_gate_r64, (size_t)L->n_groups);
-      TRY_ALLOC(L->d_tm_up_r64, (size_t)L->n_groups);
-      TRY_ALLOC(L->d_tm_down_r64, (size_t)L->n_groups);
-      L->has_r64 = true;
-    }
   }
   TRY_ALLOC(L->d_sc_gate, (size_t)L->n_groups);
   TRY_ALLOC(L->d_sc_up, (size_t)L->n_groups);
@@ -357,14 +349,6 @@ int atenia_moe_create(const AteniaMoeConfig* cfg, AteniaMoeLayer** out) {
     rc = encode_tmap_2d_bf16(&L->tm_recv_x, L->recv_x, (uint64_t)L->recv_cap, d, 128, 64);
     if (!rc) rc = encode_tmap_2d_bf16(&L->tm_recv_h, L->recv_h, (uint64_t)L->recv_cap, F, 128, 64);
   }
-  if (!rc && L->has_r64) {
-    rc = encode_tmap_2d_bf16(&L->tm_x_perm_r64, L->x_perm, R, d, 64, 64);
-    if (!rc && L->h) rc = encode_tmap_2d_bf16(&L->tm_h_r64, L->h, R, F, 64, 64);
-    if (!rc && c.ep_world > 1) {
-      rc = encode_tmap_2d_bf16(&L->tm_recv_x_r64, L->recv_x, (uint64_t)L->recv_cap, d, 64, 64);
-      if (!rc) rc = encode_tmap_2d_bf16(&L->tm_recv_h_r64, L->recv_h, (uint64_t)L->recv_cap, F, 64, 64);
-    }
-  }
   if (rc) {
     atenia_moe_destroy(L);
     return rc;
@@ -384,7 +368,7 @@ int atenia_moe_destroy(AteniaMoeLayer* L) {
                   L->h, L->y_perm, L->x_bf16, L->h_shared, L->y_shared, L->d_err, L->d_tm_gate, L->d_tm_up,
                   L->d_tm_down, L->d_tm_shared, L->d_sc_gate, L->d_sc_up, L->d_sc_down, L->d_sc_shared,
                   L->d_p_gate, L->d_p_up, L->d_p_down, L->d_p_shared, L->d_tm_gate_sw, L->d_tm_up_sw,
-                  L->d_tm_down_sw, L->d_tm_shared_sw, L->d_tm_gate_r64, L->d_tm_up_r64, L->d_tm_down_r64,
+                  L->d_tm_down_sw, L->d_tm_shared_sw,
                   L->splitk_ws, L->d_escore, L->logits_ws, L->recv_x, L->recv_h, L->recv_y, L->d_counts_all,
                   L->d_group_offsets, L->d_peer_recv_x, L->d_peer_y_perm, L->d_dst_base, L->d_src_base,
                   L->d_gemm_offsets, L->d_bar, L->sk_part, L->sk_gate, L->sk_counters, L->block_normed};
@@ -437,7 +421,7 @@ int atenia_moe_set_weights(AteniaMoeLayer* L, const AteniaMoeWeights* w) {
   };
 
   const int G = L->n_groups, El = L->e_local;
-  std::vector<CUtensorMap> tg(G), tu(G), td(G), tgs(G), tus(G), tds(G), tg6(G), tu6(G), td6(G);
+  std::vector<CUtensorMap> tg(G), tu(G), td(G), tgs(G), tus(G), tds(G);
   std::vector<const void*> pg(G), pu(G), pd(G);
   std::vector<const float*> sg(G, nullptr), su(G, nullptr), sd(G, nullptr);
   for (int e = 0; e < El; ++e) {
@@ -450,9 +434,6 @@ int atenia_moe_set_weights(AteniaMoeLayer* L, const AteniaMoeWeights* w) {
     if (!rc && q) rc = encode(&tgs[e], pg[e], F, d, 1);
     if (!rc && q) rc = encode(&tus[e], pu[e], F, d, 1);
     if (!rc && q) rc = encode(&tds[e], pd[e], d, F, 1);
-    if (!rc && L->has_r64) rc = encode_tmap_2d_u8(&tg6[e], pg[e], F, d, 64, 64, 1);
-    if (!rc && L->has_r64) rc = encode_tmap_2d_u8(&tu6[e], pu[e], F, d, 64, 64, 1);
-    if (!rc && L->has_r64) rc = encode_tmap_2d_u8(&td6[e], pd[e], d, F, 64, 64, 1);
     if (rc) return rc;
     if (q) {
       if (!w->s_gate[e] || !w->s_up[e] || !w->s_down[e]) return ATENIA_ERR_NULL;
@@ -469,9 +450,6 @@ int atenia_moe_set_weights(AteniaMoeLayer* L, const AteniaMoeWeights* w) {
     tgs[g] = tgs[g % El];
     tus[g] = tus[g % El];
     tds[g] = tds[g % El];
-    tg6[g] = tg6[g % El];
-    tu6[g] = tu6[g % El];
-    td6[g] = td6[g % El];
     pg[g] = pg[g % El];
     pu[g] = pu[g % El];
     pd[g] = pd[g % El];
@@ -487,11 +465,6 @@ int atenia_moe_set_weights(AteniaMoeLayer* L, const AteniaMoeWeights* w) {
     ATENIA_CUDA_TRY(cudaMemcpy(L->d_tm_gate_sw, tgs.data(), mb, cudaMemcpyHostToDevice));
     ATENIA_CUDA_TRY(cudaMemcpy(L->d_tm_up_sw, tus.data(), mb, cudaMemcpyHostToDevice));
     ATENIA_CUDA_TRY(cudaMemcpy(L->d_tm_down_sw, tds.data(), mb, cudaMemcpyHostToDevice));
-  }
-  if (L->has_r64) {
-    ATENIA_CUDA_TRY(cudaMemcpy(L->d_tm_gate_r64, tg6.data(), mb, cudaMemcpyHostToDevice));
-    ATENIA_CUDA_TRY(cudaMemcpy(L->d_tm_up_r64, tu6.data(), mb, cudaMemcpyHostToDevice));
-    ATENIA_CUDA_TRY(cudaMemcpy(L->d_tm_down_r64, td6.data(), mb, cudaMemcpyHostToDevice));
   }
   ATENIA_CUDA_TRY(cudaMemcpy(L->d_p_gate, pg.data(), pb, cudaMemcpyHostToDevice));
   ATENIA_CUDA_TRY(cudaMemcpy(L->d_p_up, pu.data(), pb, cudaMemcpyHostToDevice));
@@ -637,7 +610,7 @@ static int forward_impl(AteniaMoeLayer* L, const void* x, int x_dtype, int T, vo
   if (c.ep_world == 1) {
     if (L->timing) cudaEventRecord(L->ph[2], s);
     rc = run_expert_gemms(L, L->tm_x_perm, L->tm_h, L->x_perm, L->h, L->y_perm, L->expert_offsets,
-                          c.num_experts, n, s, &L->tm_x_perm_r64, &L->tm_h_r64);
+                          c.num_experts, n, s);
   } else if (L->ep_replicated) {
     rc = ep_forward_replicated(L, n, s);
   } else if (direct) {

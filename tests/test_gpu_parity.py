@@ -150,13 +150,12 @@ def test_w8a16_structure(dev):
         _run_parity(dev, shape, T, TOL_W8A16, seed=T)
 
 
-@pytest.mark.parametrize("mode,pair", [("1", "2"), ("2", "2"), ("2", "1")])
-def test_w8a16_every_kernel(dev, monkeypatch, mode, pair):
-    """ATENIA_MOE_W8_MODE pins the INT8 kernel family (1: weights widened into tensor memory,
-    2: widened into shared memory) and ATENIA_MOE_PAIR_MODE the single-CTA (2) or CTA-pair (1) form
-    of the latter; each must meet the bar at small and large group sizes."""
+@pytest.mark.parametrize("mode", ["0", "1", "2"])
+def test_w8a16_every_kernel(dev, monkeypatch, mode):
+    """ATENIA_MOE_W8_MODE pins the INT8 kernel family (0: by size -- weights widened into tensor memory
+    for small groups, 256-row tiles widened into shared memory for large ones; 1: always the former;
+    2: 128-row tiles widened into shared memory); each must meet the bar at small and large group sizes."""
     monkeypatch.setenv("ATENIA_MOE_W8_MODE", mode)
-    monkeypatch.setenv("ATENIA_MOE_PAIR_MODE", pair)
     synth = _synth()
     shape = synth.small(synth.SHAPES["mixtral_int8"], d_model=512, d_ff=768)
     for T in (3, 700):
