@@ -162,11 +162,13 @@ def test_w8a16_every_kernel(dev, monkeypatch, mode):
         _run_parity(dev, shape, T, TOL_W8A16, seed=T)
 
 
-def test_w8a16_with_shared_expert(dev):
+@pytest.mark.parametrize("T", [200, 700])
+def test_w8a16_with_shared_expert(dev, T):
+    """Below 256 tokens the shared expert takes the small-group INT8 kernel, above it the 256-row-tile one."""
     synth = _synth()
     from dataclasses import replace
     shape = replace(synth.small(synth.SHAPES["qwen_moe"], d_model=512, d_ff=384, shared_d_ff=768), int8=True)
-    _run_parity(dev, shape, 200, TOL_W8A16)
+    _run_parity(dev, shape, T, TOL_W8A16)
 
 
 def test_all_tokens_on_one_expert_and_empty_experts(dev):
