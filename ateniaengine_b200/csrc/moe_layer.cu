@@ -63,8 +63,11 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
   // bf16: 256-row CTA-pair tiles pay off once an average group fills a few of them; a call of at most
   // 16 rows (decode) takes the stream-K kernel of bf16_decode_gemm.cu, which spreads the few tiles
   // there are over all SMs (bf16_decode 1 / 0 pins it on for every call of at most 128 rows / off).
+  // (bf16_decode 2: also for ragged mid-size groups, fewer than 256 rows per group on average -- A/B runs)
   const bool dec = !q && !L->use_check_gemm && L->splitk_ws &&
-                   (L->bf16_decode == 1 ? max_rows <= 128 : (L->bf16_decode < 0 && max_rows <= 16));
+                   (L->bf16_decode == 1 ? max_rows <= 128
+                    : L->bf16_decode == 2 ? max_rows < 256 * num_groups
+                                          : (L->bf16_decode < 0 && max_rows <= 16));
   const bool pairs = !q && !dec && (L->pair_mode == 1 || (L->pair_mode == 0 && max_rows >= 512 * num_groups));
   if (L->timing) cudaEventRecord(L->ev[0], s);
   if (L->use_check_gemm) {
@@ -244,7 +247,7 @@ int atenia_moe_create(const AteniaMoeConfig* cfg, AteniaMoeLayer** out) {
     L->router_variant = r == "scalar" ? 0 : r == "dmma" ? 1 : r == "splitk" ? 2 : -1;
   }
   L->bf16_decode = c.weight_dtype != ATENIA_W_BF16 ? 0
-                   : std::getenv("ATENIA_MOE_BF16_DECODE") ? (std::atoi(std::getenv("ATENIA_MOE_BF16_DECODE")) != 0 ? 1 : 0)
+                   : std::getenv("ATENIA_MOE_BF16_DECODE") ? std::atoi(std::getenv("ATENIA_MOE_BF16_DECODE"))
                                                            : -1;
   const size_t Tm = (size_t)c.max_tokens, k = (size_t)c.experts_per_token, E = (size_t)c.num_experts;
   const size_t d = (size_t)c.d_model, F = (size_t)c.d_ff, Fs = (size_t)c.shared_d_ff;
@@ -355,6 +358,15 @@ int atenia_moe_create(const AteniaMoeConfig* cfg, AteniaMoeLayer** out) {
   }
   for (int i = 0; i < 8; ++i) cudaEventCreate(&L->ev[i]);
   for (int i = 0; i < 6; ++i) cudaEventCreate(&L->ph[i]);
+  if (c.ep_world > 1 && L->has_shared) {
+    e = cudaStreamCreateWithFlags(&L->aux_stream, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&L->ev_fork, cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&L->ev_join, cudaEventDisableTiming);
+    if (e != cudaSuccess) {
+      atenia_moe_destroy(L);
+      return (int)e;
+    }
+  }
   *out = L;
   return ATENIA_OK;
 }
@@ -380,6 +392,9 @@ int atenia_moe_destroy(AteniaMoeLayer* L) {
     if (L->ev[i]) cudaEventDestroy(L->ev[i]);
   for (int i = 0; i < 6; ++i)
     if (L->ph[i]) cudaEventDestroy(L->ph[i]);
+  if (L->ev_fork) cudaEventDestroy(L->ev_fork);
+  if (L->ev_join) cudaEventDestroy(L->ev_join);
+  if (L->aux_stream) cudaStreamDestroy(L->aux_stream);
   delete L;
   return ATENIA_OK;
 }
@@ -607,6 +622,19 @@ static int forward_impl(AteniaMoeLayer* L, const void* x, int x_dtype, int T, vo
   if (rc) return rc;
   if (L->timing) cudaEventRecord(L->ph[1], s);
 
+  // Under token-sharded expert parallelism the shared expert runs on the layer's second stream, beside
+  // the exchange and the routed experts: it reads only this rank's tokens (x, or the bf16 copy the
+  // gather launch just made) and writes buffers nothing else touches before the combine.
+  const bool shared_aside = L->has_shared && T > 0 && c.ep_world > 1 && !L->ep_replicated && L->aux_stream;
+  if (shared_aside) {
+    const __nv_bfloat16* xb = x_f32 ? L->x_bf16 : static_cast<const __nv_bfloat16*>(x);
+    ATENIA_CUDA_TRY(cudaEventRecord(L->ev_fork, s));
+    ATENIA_CUDA_TRY(cudaStreamWaitEvent(L->aux_stream, L->ev_fork, 0));
+    rc = run_shared_gemms(L, xb, T, L->aux_stream);
+    if (rc) return rc;
+    ATENIA_CUDA_TRY(cudaEventRecord(L->ev_join, L->aux_stream));
+  }
+
   if (c.ep_world == 1) {
     if (L->timing) cudaEventRecord(L->ph[2], s);
     rc = run_expert_gemms(L, L->tm_x_perm, L->tm_h, L->x_perm, L->h, L->y_perm, L->expert_offsets,
@@ -614,13 +642,8 @@ static int forward_impl(AteniaMoeLayer* L, const void* x, int x_dtype, int T, vo
   } else if (L->ep_replicated) {
     rc = ep_forward_replicated(L, n, s);
   } else if (direct) {
-    // rows leave for their owners, the shared expert runs on the local tokens while the peers' rows
-    // arrive, then the routed experts
+    // rows leave for their owners, then the routed experts
     rc = ep_direct_send(L, x, x_f32 ? 1 : 0, T, s);
-    if (!rc && L->has_shared && T > 0) {
-      const __nv_bfloat16* xb = x_f32 ? L->x_bf16 : static_cast<const __nv_bfloat16*>(x);
-      rc = run_shared_gemms(L, xb, T, s);
-    }
     if (!rc) rc = ep_direct_finish(L, s);
   } else {
     rc = ep_forward_exchange(L, T, s);
@@ -631,7 +654,9 @@ static int forward_impl(AteniaMoeLayer* L, const void* x, int x_dtype, int T, vo
     cudaEventRecord(L->ph[4], s);
   }
 
-  if (L->has_shared && T > 0 && !direct) {
+  if (shared_aside) {
+    ATENIA_CUDA_TRY(cudaStreamWaitEvent(s, L->ev_join, 0));
+  } else if (L->has_shared && T > 0) {
     const __nv_bfloat16* xb = x_f32 ? L->x_bf16 : static_cast<const __nv_bfloat16*>(x);
     rc = run_shared_gemms(L, xb, T, s);
     if (rc) return rc;
@@ -793,7 +818,16 @@ int atenia_moe_enable_timing(AteniaMoeLayer* L, int enable) {
   return ATENIA_OK;
 }
 
-int atenia_moe_last_recv_rows(AteniaMoeLayer* L) { return L ? L->last_recv_rows : -1; }
+int atenia_moe_last_recv_rows(AteniaMoeLayer* L) {
+  if (!L) return -1;
+  if (L->ep_direct && L->d_gemm_offsets) {
+    // the direct exchange keeps the count on the device: fetch it (synchronous; diagnostics only)
+    int32_t v = -1;
+    if (cudaMemcpy(&v, L->d_gemm_offsets + L->e_local, sizeof(v), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    return v;
+  }
+  return L->last_recv_rows;
+}
 
 float atenia_moe_last_phase_ms(AteniaMoeLayer* L, int which) {
   if (!L || which < 0 || which > 5 || !L->ph_valid) return -1.0f;

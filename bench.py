@@ -350,6 +350,7 @@ class EpGroup:
             blobs = [torch.empty_like(mine) for _ in range(self.world)]
             self.dist.all_gather(blobs, mine)
             layer.ep_ipc_import(b"".join(bytes(b.cpu().numpy().tobytes()) for b in blobs))
+        return direct
 
     def close(self):
         if self.dist is not None:
@@ -396,7 +397,7 @@ def measure_record(grp, name, T_total, args, peaks, seed=2, direct=False):
     ms = time_steps(grp, fn, args.steps)
     layer.check()
     phases = [layer.last_phase_ms(i) for i in range(6)]
-    recv_rows = layer.last_recv_rows() if G > 1 and not direct else T * shape.top_k
+    recv_rows = layer.last_recv_rows() if G > 1 else T * shape.top_k
     layer.enable_timing(False)
     _, aux = layer.forward(x, aux=True, sync=True)
     touched = int(torch.unique(aux["topk_idx"]).numel())
@@ -489,7 +490,7 @@ def main():
                           f"top_k={shape.top_k} shared_d_ff={shape.shared_d_ff} tokens_per_rank={T}",
               "tokens_per_step": T * max(args.gpus, 1),
               "routing_skew": shape.bias,
-              "parallelism": "single GPU" if args.gpus == 1 else f"expert-parallel ep{args.gpus}, NCCL all-to-all",
+              "parallelism": "single GPU" if args.gpus == 1 else f"expert-parallel ep{args.gpus}, NCCL send/recv all-to-all",
               "l2_policy": "inputs larger than L2: every step streams the expert weights "
                            f"({3 * shape.d_model * shape.d_ff * shape.num_experts * (1 if shape.int8 else 2) / 1e6:.0f} MB)"}
 
@@ -541,7 +542,9 @@ def main():
     grp = EpGroup(args.gpus)
     dev, dist = grp.dev, grp.dist
     local_rank = grp.local_rank
-    direct = args.gpus > 1 and os.environ.get("ATENIA_BENCH_EP_DIRECT", "0") == "1"
+    # rows travel by the library's own peer-store kernels over NVLink (the direct exchange);
+    # ATENIA_BENCH_EP_DIRECT=0 times the NCCL send/recv exchange instead
+    direct = args.gpus > 1 and os.environ.get("ATENIA_BENCH_EP_DIRECT", "1") != "0"
     E = shape.num_experts
     el = E // args.gpus
     w = synth.make_weights(shape, 2, dev, experts=(rank * el, el))
@@ -576,7 +579,7 @@ def main():
     layer.check()
     gemm1_ms, gemm2_ms = layer.last_gemm_ms(0), layer.last_gemm_ms(1)
     phases = [layer.last_phase_ms(i) for i in range(6)]
-    recv_rows = layer.last_recv_rows() if args.gpus > 1 and not direct else T * shape.top_k
+    recv_rows = layer.last_recv_rows() if args.gpus > 1 else T * shape.top_k
     # further windows of exactly K steps, back to back: the first window is a burst after an idle
     # moment, the median window is what a loaded GPU sustains (clocks settle under the power cap)
     win = []

@@ -496,8 +496,9 @@ ATENIA_API float atenia_moe_last_gemm_ms(AteniaMoeLayer* layer, int which);
  * 3 = results back to their source ranks (expert parallelism), 4 = shared expert and combine,
  * 5 = the whole forward.  Milliseconds, negative if nothing was recorded. */
 ATENIA_API float atenia_moe_last_phase_ms(AteniaMoeLayer* layer, int which);
-/* Rows the experts of this rank received in the most recent token-sharded expert-parallel forward
- * (known on the host because that path reads the row counts); -1 if none. */
+/* Rows the experts of this rank received in the most recent token-sharded expert-parallel forward; -1 if
+ * none.  Under the direct exchange the count lives on the device and this call copies it back
+ * (synchronous: call it outside timed regions, after the forward has completed). */
 ATENIA_API int atenia_moe_last_recv_rows(AteniaMoeLayer* layer);
 
 #ifdef __cplusplus

@@ -9,11 +9,7 @@ import torch
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
-# Opt-in in the library (atenia_moe_ep_ipc_import) and here until it has run on hardware:
-# ATENIA_TEST_EP_DIRECT=1.
-pytestmark = [pytest.mark.gpu,
-              pytest.mark.skipif(os.environ.get("ATENIA_TEST_EP_DIRECT", "0") != "1",
-                                 reason="opt-in path: set ATENIA_TEST_EP_DIRECT=1")]
+pytestmark = pytest.mark.gpu
 
 
 @pytest.mark.parametrize("name,port", [("mixtral", 29671), ("deepseek_v2_lite", 29678)])

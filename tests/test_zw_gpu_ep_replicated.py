@@ -7,10 +7,7 @@ import sys
 import pytest
 import torch
 
-# Opt-in until it has run on hardware once: ATENIA_TEST_EP_REPLICATED=1.
-pytestmark = [pytest.mark.gpu,
-              pytest.mark.skipif(os.environ.get("ATENIA_TEST_EP_REPLICATED", "0") != "1",
-                                 reason="set ATENIA_TEST_EP_REPLICATED=1")]
+pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
