@@ -160,6 +160,10 @@ struct GroupedGemmCheckArgs {
   int max_rows;
 };
 int launch_grouped_gemm_check(const GroupedGemmCheckArgs& a, cudaStream_t s);
+// The same contraction for calls of at most four rows in all (decode at batch 1-2): a CUDA-core
+// matrix-vector kernel that streams the touched experts' weights once (decode_gemv.cu).
+int launch_grouped_gemv(const GroupedGemmCheckArgs& a, cudaStream_t s);
+constexpr int kGemvMaxRows = 4;
 
 int launch_f32_to_bf16(const float* src, __nv_bfloat16* dst, int64_t n, cudaStream_t s);
 // y = (x * inv_rms(x)) * gamma per row (stack.cu); gamma may be null (unit gain)

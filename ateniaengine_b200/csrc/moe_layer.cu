@@ -69,12 +69,15 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
                     : L->bf16_decode == 2 ? max_rows < 256 * num_groups
                                           : (L->bf16_decode < 0 && max_rows <= 16));
   const bool pairs = !q && !dec && (L->pair_mode == 1 || (L->pair_mode == 0 && max_rows >= 512 * num_groups));
+  // a call of at most four rows in all (decode at batch 1-2) is a stream over the touched experts'
+  // weights: the CUDA-core matrix-vector kernel (ATENIA_MOE_GEMV=0 keeps the tensor-core kernels: A/B runs)
+  const bool gemv = L->use_gemv && max_rows <= kGemvMaxRows && !L->use_check_gemm;
   if (L->timing) cudaEventRecord(L->ev[0], s);
-  if (L->use_check_gemm) {
+  if (L->use_check_gemm || gemv) {
     GroupedGemmCheckArgs k1{a_ptr, L->d_p_gate, L->d_p_up, q ? 1 : 0, q ? L->d_sc_gate : nullptr,
                             q ? L->d_sc_up : nullptr, group_offsets, num_groups, c.d_ff, c.d_model,
                             kSwiGLU, mid, max_rows};
-    int rc = launch_grouped_gemm_check(k1, s);
+    int rc = gemv ? launch_grouped_gemv(k1, s) : launch_grouped_gemm_check(k1, s);
     if (rc) return rc;
   } else {
     GroupedGemmArgs g1{};
@@ -101,10 +104,10 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
     if (rc) return rc;
   }
   if (L->timing) cudaEventRecord(L->ev[1], s);
-  if (L->use_check_gemm) {
+  if (L->use_check_gemm || gemv) {
     GroupedGemmCheckArgs k2{mid, L->d_p_down, nullptr, q ? 1 : 0, q ? L->d_sc_down : nullptr, nullptr,
                             group_offsets, num_groups, c.d_model, c.d_ff, kPlain, out, max_rows};
-    int rc = launch_grouped_gemm_check(k2, s);
+    int rc = gemv ? launch_grouped_gemv(k2, s) : launch_grouped_gemm_check(k2, s);
     if (rc) return rc;
   } else {
     GroupedGemmArgs g2{};
@@ -147,17 +150,23 @@ int run_shared_gemms(AteniaMoeLayer* L, const __nv_bfloat16* xb, int T, cudaStre
   const bool m256 = q && T >= 256 && L->w8_mode != 1 && L->w8_mode != 2 && !L->use_check_gemm;
   const bool tmem = q && !m256 && (L->w8_mode == 1 || (L->w8_mode != 2 && T < 256));
   const bool pairs = !q && (L->pair_mode == 1 || (L->pair_mode == 0 && T >= 512));
+  const bool gemv = L->use_gemv && T <= kGemvMaxRows && !L->use_check_gemm;
   if (L->timing) cudaEventRecord(L->ev[3], s);
-  if (L->use_check_gemm) {
+  if (L->use_check_gemm || gemv) {
     GroupedGemmCheckArgs k1{xb, L->d_p_shared, L->d_p_shared + 1, q ? 1 : 0, q ? L->d_sc_shared : nullptr,
                             q ? L->d_sc_shared + 1 : nullptr, L->shared_offsets, 1, c.shared_d_ff, c.d_model,
                             kSwiGLU, L->h_shared, T};
-    int rc = launch_grouped_gemm_check(k1, s);
+    int rc = gemv ? launch_grouped_gemv(k1, s) : launch_grouped_gemm_check(k1, s);
     if (rc) return rc;
+    if (L->timing) cudaEventRecord(L->ev[4], s);
     GroupedGemmCheckArgs k2{L->h_shared, L->d_p_shared + 2, nullptr, q ? 1 : 0, q ? L->d_sc_shared + 2 : nullptr,
                             nullptr, L->shared_offsets, 1, c.d_model, c.shared_d_ff, kPlain, L->y_shared, T};
-    rc = launch_grouped_gemm_check(k2, s);
+    rc = gemv ? launch_grouped_gemv(k2, s) : launch_grouped_gemm_check(k2, s);
     if (rc) return rc;
+    if (L->timing) {
+      cudaEventRecord(L->ev[5], s);
+      L->ev_valid[2] = L->ev_valid[3] = true;
+    }
     return ATENIA_OK;
   }
   GroupedGemmArgs g1{};
@@ -237,6 +246,7 @@ int atenia_moe_create(const AteniaMoeConfig* cfg, AteniaMoeLayer** out) {
   L->use_check_gemm = std::getenv("ATENIA_MOE_CHECK_GEMM") && std::atoi(std::getenv("ATENIA_MOE_CHECK_GEMM")) != 0;
   L->w8_mode = std::getenv("ATENIA_MOE_W8_MODE") ? std::atoi(std::getenv("ATENIA_MOE_W8_MODE")) : 0;
   L->pair_mode = std::getenv("ATENIA_MOE_PAIR_MODE") ? std::atoi(std::getenv("ATENIA_MOE_PAIR_MODE")) : 0;
+  L->use_gemv = std::getenv("ATENIA_MOE_GEMV") && std::atoi(std::getenv("ATENIA_MOE_GEMV")) != 0;
   // Router kernel: by default the split-k kernel for batches of at most 128 tokens (many CTAs share one
   // token block's dot products), the f64 tensor-core kernel for 32 experts and more, the CUDA-core
   // kernel otherwise.  ATENIA_MOE_ROUTER = scalar | dmma | splitk pins one (tests, A/B runs); a pinned
