@@ -63,11 +63,8 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
   // bf16: 256-row CTA-pair tiles pay off once an average group fills a few of them; a call of at most
   // 16 rows (decode) takes the stream-K kernel of bf16_decode_gemm.cu, which spreads the few tiles
   // there are over all SMs (bf16_decode 1 / 0 pins it on for every call of at most 128 rows / off).
-  // (bf16_decode 2: also for ragged mid-size groups, fewer than 256 rows per group on average -- A/B runs)
   const bool dec = !q && !L->use_check_gemm && L->splitk_ws &&
-                   (L->bf16_decode == 1 ? max_rows <= 128
-                    : L->bf16_decode == 2 ? max_rows < 256 * num_groups
-                                          : (L->bf16_decode < 0 && max_rows <= 16));
+                   (L->bf16_decode == 1 ? max_rows <= 128 : (L->bf16_decode < 0 && max_rows <= 16));
   const bool pairs = !q && !dec && (L->pair_mode == 1 || (L->pair_mode == 0 && max_rows >= 512 * num_groups));
   // a call of at most four rows in all (decode at batch 1-2) is a stream over the touched experts'
   // weights: the CUDA-core matrix-vector kernel (ATENIA_MOE_GEMV=0 keeps the tensor-core kernels: A/B runs)
@@ -257,7 +254,7 @@ int atenia_moe_create(const AteniaMoeConfig* cfg, AteniaMoeLayer** out) {
     L->router_variant = r == "scalar" ? 0 : r == "dmma" ? 1 : r == "splitk" ? 2 : -1;
   }
   L->bf16_decode = c.weight_dtype != ATENIA_W_BF16 ? 0
-                   : std::getenv("ATENIA_MOE_BF16_DECODE") ? std::atoi(std::getenv("ATENIA_MOE_BF16_DECODE"))
+                   : std::getenv("ATENIA_MOE_BF16_DECODE") ? (std::atoi(std::getenv("ATENIA_MOE_BF16_DECODE")) != 0 ? 1 : 0)
                                                            : -1;
   const size_t Tm = (size_t)c.max_tokens, k = (size_t)c.experts_per_token, E = (size_t)c.num_experts;
   const size_t d = (size_t)c.d_model, F = (size_t)c.d_ff, Fs = (size_t)c.shared_d_ff;
