@@ -180,6 +180,10 @@ int encode_tmap_2d_u8(CUtensorMap* out, const void* base, uint64_t rows, uint64_
 // token matrix (box {64, 128}, 128B swizzle); tmap_b0/b1 are int8 maps with the 64-byte swizzle.
 int launch_grouped_gemm_w8_tmem(const GroupedGemmArgs& a, int num_sms, cudaStream_t s);
 constexpr size_t kW8SplitKSlotFloats = 2 * 128 * 128;  // per CTA: two slots of this size
+// W8A16 for small groups with the weights widened into shared memory (w8_decode_gemm.cu): transposed
+// product, stream-K.  tmap_a is the bf16 token matrix (box {64, 128}, 128B swizzle); tmap_b0/b1 are the
+// UNSWIZZLED int8 maps (box {64, 128}); splitk_ws as for the tensor-memory kernel.
+int launch_grouped_gemm_w8_decode(const GroupedGemmArgs& a, int num_sms, cudaStream_t s);
 // W8A16 for large groups (w8_gemm_m256.cu): 256-row token tiles, the widened weight tile shared by two
 // M128 MMAs.  Tensor maps as for launch_grouped_gemm_tcgen05 with w8 set.
 int launch_grouped_gemm_w8_m256(const GroupedGemmArgs& a, int num_sms, cudaStream_t s);

@@ -60,6 +60,8 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
   // shared-memory widening kernel of grouped_gemm.cu (tests, A/B runs).
   const bool m256 = q && large && L->w8_mode != 1 && L->w8_mode != 2 && !L->use_check_gemm;
   const bool tmem = q && !m256 && (L->w8_mode == 1 || (L->w8_mode != 2 && !large));
+  // w8_mode 5: small groups through the shared-memory widening decode kernel (w8_decode_gemm.cu) -- A/B runs
+  const bool w8dec = tmem && L->w8_mode == 5 && max_rows <= 128 * num_groups;
   // bf16: 256-row CTA-pair tiles pay off once an average group fills a few of them; a call of at most
   // 16 rows (decode) takes the stream-K kernel of bf16_decode_gemm.cu, which spreads the few tiles
   // there are over all SMs (bf16_decode 1 / 0 pins it on for every call of at most 128 rows / off).
@@ -79,8 +81,8 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
   } else {
     GroupedGemmArgs g1{};
     g1.tmap_a = tm_a;
-    g1.tmap_b0 = tmem ? L->d_tm_gate_sw : L->d_tm_gate;
-    g1.tmap_b1 = tmem ? L->d_tm_up_sw : L->d_tm_up;
+    g1.tmap_b0 = (tmem && !w8dec) ? L->d_tm_gate_sw : L->d_tm_gate;
+    g1.tmap_b1 = (tmem && !w8dec) ? L->d_tm_up_sw : L->d_tm_up;
     g1.group_offsets = group_offsets;
     g1.num_groups = num_groups;
     g1.N = c.d_ff;
@@ -94,6 +96,7 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
     g1.w8 = q;
     g1.splitk_ws = L->splitk_ws;
     int rc = m256 ? launch_grouped_gemm_w8_m256(g1, L->num_sms, s)
+                  : w8dec ? launch_grouped_gemm_w8_decode(g1, L->num_sms, s)
                   : dec ? launch_grouped_gemm_bf16_decode(g1, L->num_sms, s)
                   : tmem ? launch_grouped_gemm_w8_tmem(g1, L->num_sms, s)
                          : pairs ? launch_grouped_gemm_2cta(g1, L->num_sms, s)
@@ -109,7 +112,7 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
   } else {
     GroupedGemmArgs g2{};
     g2.tmap_a = tm_mid;
-    g2.tmap_b0 = tmem ? L->d_tm_down_sw : L->d_tm_down;
+    g2.tmap_b0 = (tmem && !w8dec) ? L->d_tm_down_sw : L->d_tm_down;
     g2.tmap_b1 = g2.tmap_b0;
     g2.group_offsets = group_offsets;
     g2.num_groups = num_groups;
@@ -124,6 +127,7 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
     g2.w8 = q;
     g2.splitk_ws = L->splitk_ws;
     int rc = m256 ? launch_grouped_gemm_w8_m256(g2, L->num_sms, s)
+                  : w8dec ? launch_grouped_gemm_w8_decode(g2, L->num_sms, s)
                   : dec ? launch_grouped_gemm_bf16_decode(g2, L->num_sms, s)
                   : tmem ? launch_grouped_gemm_w8_tmem(g2, L->num_sms, s)
                          : pairs ? launch_grouped_gemm_2cta(g2, L->num_sms, s)
