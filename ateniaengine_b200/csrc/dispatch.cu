@@ -106,6 +106,59 @@ __global__ void __launch_bounds__(kDispatchChunk) place_kernel(DispatchArgs a) {
   }
 }
 
+// Small batches (at most 1024 entries, i.e. decode): histogram, scan and stable placement in ONE block,
+// one thread per entry -- the same permutation as the three launches above without their launch gaps.
+constexpr int kSmallDispatchMax = 1024;
+
+__global__ void __launch_bounds__(kSmallDispatchMax) dispatch_small_kernel(DispatchArgs a) {
+  __shared__ int warp_cnt[kSmallDispatchMax / 32][kMaxE];  // entries of expert e in warp w, then their base
+  __shared__ int offsets[kMaxE + 1];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  for (int j = threadIdx.x; j < nwarps * kMaxE; j += blockDim.x) (&warp_cnt[0][0])[j] = 0;
+  __syncthreads();
+  const int i = threadIdx.x;
+  int e = -1;
+  if (i < a.n) {
+    e = a.topk_idx[i];
+    if (e < 0 || e >= a.E) {
+      report_error(a.err, ATENIA_ERR_ROUTING, 2001);
+      e = -1;
+    }
+  }
+  const unsigned peers = __match_any_sync(0xffffffffu, e);
+  const int rank_in_warp = __popc(peers & ((1u << lane) - 1u));
+  if (e >= 0 && rank_in_warp == 0) warp_cnt[warp][e] = __popc(peers);
+  __syncthreads();
+  // thread e: exclusive scan of its expert's counts over the warps (entry order), total into offsets
+  if (threadIdx.x < a.E) {
+    int run = 0;
+    for (int w = 0; w < nwarps; ++w) {
+      const int c = warp_cnt[w][threadIdx.x];
+      warp_cnt[w][threadIdx.x] = run;
+      run += c;
+    }
+    offsets[threadIdx.x + 1] = run;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    offsets[0] = 0;
+    for (int x = 0; x < a.E; ++x) offsets[x + 1] += offsets[x];
+    if (a.extra_offsets) {
+      a.extra_offsets[0] = 0;
+      a.extra_offsets[1] = a.T;
+    }
+  }
+  __syncthreads();
+  for (int x = threadIdx.x; x <= a.E; x += blockDim.x) a.expert_offsets[x] = offsets[x];
+  if (e >= 0) {
+    const int pos = offsets[e] + warp_cnt[warp][e] + rank_in_warp;
+    a.perm[pos] = i;
+    a.inv_perm[i] = pos;
+  } else if (i < a.n) {
+    a.inv_perm[i] = -1;
+  }
+}
+
 // Row gather: x_perm[r, :] = bf16(x[perm[r] / k, :]).  One warp per destination row, eight rows per
 // block in flight and a grid that loops; every lane keeps four 16-byte vectors in flight.  `placed`
 // points at expert_offsets[E], the number of rows the placement actually wrote: entries with an
@@ -173,6 +226,12 @@ __global__ void __launch_bounds__(kGatherWarps * 32) gather_rows_kernel(const vo
 
 int launch_dispatch(const DispatchArgs& a, cudaStream_t s) {
   if (a.E > kMaxE) return ATENIA_ERR_UNSUPPORTED;
+  if (a.n > 0 && a.n <= kSmallDispatchMax) {
+    const int threads = ((a.n + 31) / 32 * 32) < a.E ? ((a.E + 31) / 32 * 32) : ((a.n + 31) / 32 * 32);
+    dispatch_small_kernel<<<1, threads, 0, s>>>(a);
+    count_launch();
+    return (int)cudaGetLastError();
+  }
   const int nblk = (a.n + kDispatchChunk - 1) / kDispatchChunk;
   if (nblk > 0) {
     count_kernel<<<nblk, kDispatchChunk, 0, s>>>(a);

@@ -112,9 +112,9 @@ struct AteniaMoeLayer {
   int32_t* d_gemm_offsets = nullptr;        // [e_local + 1] expert-major group offsets of the receive buffer
   int32_t* d_bar = nullptr;                 // [1] operand of the barrier all-reduce
 
-  // expert parallelism with a shared expert: the shared expert needs nothing from the peers, so its
-  // GEMMs run on a second stream while rows travel and the routed experts work (fork after routing,
-  // join before the combine)
+  // the shared expert needs only the call's tokens: its GEMMs run on a second stream beside the routing
+  // phase and, under expert parallelism, the exchanges (fork at the start, join before the combine)
+  bool shared_aside = true;
   cudaStream_t aux_stream = nullptr;
   cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
 

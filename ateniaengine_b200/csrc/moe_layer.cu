@@ -247,6 +247,7 @@ int atenia_moe_create(const AteniaMoeConfig* cfg, AteniaMoeLayer** out) {
   L->use_check_gemm = std::getenv("ATENIA_MOE_CHECK_GEMM") && std::atoi(std::getenv("ATENIA_MOE_CHECK_GEMM")) != 0;
   L->w8_mode = std::getenv("ATENIA_MOE_W8_MODE") ? std::atoi(std::getenv("ATENIA_MOE_W8_MODE")) : 0;
   L->pair_mode = std::getenv("ATENIA_MOE_PAIR_MODE") ? std::atoi(std::getenv("ATENIA_MOE_PAIR_MODE")) : 0;
+  L->shared_aside = !(std::getenv("ATENIA_MOE_SHARED_ASIDE") && std::atoi(std::getenv("ATENIA_MOE_SHARED_ASIDE")) == 0);
   L->use_gemv = std::getenv("ATENIA_MOE_GEMV") && std::atoi(std::getenv("ATENIA_MOE_GEMV")) != 0;
   // Router kernel: by default the split-k kernel for batches of at most 128 tokens (many CTAs share one
   // token block's dot products), the f64 tensor-core kernel for 32 experts and more, the CUDA-core
@@ -369,7 +370,7 @@ int atenia_moe_create(const AteniaMoeConfig* cfg, AteniaMoeLayer** out) {
   }
   for (int i = 0; i < 8; ++i) cudaEventCreate(&L->ev[i]);
   for (int i = 0; i < 6; ++i) cudaEventCreate(&L->ph[i]);
-  if (c.ep_world > 1 && L->has_shared) {
+  if (L->has_shared) {
     e = cudaStreamCreateWithFlags(&L->aux_stream, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&L->ev_fork, cudaEventDisableTiming);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&L->ev_join, cudaEventDisableTiming);
@@ -567,6 +568,7 @@ static int forward_impl(AteniaMoeLayer* L, const void* x, int x_dtype, int T, vo
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int k = c.experts_per_token, n = T * k;
   const bool x_f32 = x_dtype == ATENIA_IO_F32;
+  int rc0 = ATENIA_OK;
   // the convention of this call (RealMoeLayer::forward_with): Atenia renormalises and ignores the gate;
   // HuggingFaceQwen keeps the raw weights and gates the shared expert when a gate vector is bound
   const int renorm = convention == ATENIA_CONVENTION_LAYER ? c.renormalize : (convention == ATENIA_CONVENTION_ATENIA ? 1 : 0);
@@ -574,6 +576,25 @@ static int forward_impl(AteniaMoeLayer* L, const void* x, int x_dtype, int T, vo
                                                            : (convention == ATENIA_CONVENTION_HF_QWEN && L->gate_vec_bound);
 
   if (L->timing) cudaEventRecord(L->ph[0], s);
+  // The shared expert needs only this call's tokens, so its GEMMs run on the layer's second stream from
+  // the start of the forward, beside the routing phase (an FP64-bound router, an HBM-bound gather: the
+  // tensor cores are idle there) and, under expert parallelism, beside the exchanges; the combine waits
+  // for them.  f32 input is converted to bf16 first.  Tiny batches keep the one-stream order (the two
+  // event hops would cost more than the overlap gives); ATENIA_MOE_SHARED_ASIDE=0 turns it off.
+  const bool shared_aside = L->has_shared && T >= 64 && L->aux_stream && L->shared_aside;
+  if (shared_aside) {
+    const __nv_bfloat16* xb = static_cast<const __nv_bfloat16*>(x);
+    if (x_f32) {
+      rc0 = launch_f32_to_bf16(static_cast<const float*>(x), L->x_bf16, (int64_t)T * c.d_model, s);
+      if (rc0) return rc0;
+      xb = L->x_bf16;
+    }
+    ATENIA_CUDA_TRY(cudaEventRecord(L->ev_fork, s));
+    ATENIA_CUDA_TRY(cudaStreamWaitEvent(L->aux_stream, L->ev_fork, 0));
+    rc0 = run_shared_gemms(L, xb, T, L->aux_stream);
+    if (rc0) return rc0;
+    ATENIA_CUDA_TRY(cudaEventRecord(L->ev_join, L->aux_stream));
+  }
   RouterArgs ra{};
   ra.x = x;
   ra.x_is_f32 = x_f32;
@@ -625,26 +646,13 @@ static int forward_impl(AteniaMoeLayer* L, const void* x, int x_dtype, int T, vo
   rc = launch_dispatch(da, s);
   if (rc) return rc;
 
-  const bool need_xb = x_f32 && L->has_shared;
+  const bool need_xb = x_f32 && L->has_shared && !shared_aside;  // (aside: converted at the start already)
   // the direct expert-parallel exchange gathers rows straight into the owners' buffers
   const bool direct = c.ep_world > 1 && !L->ep_replicated && L->ep_direct;
   rc = launch_gather_rows(x, x_f32, L->perm, L->expert_offsets + c.num_experts, direct ? 0 : n, k, c.d_model,
                           L->x_perm, need_xb ? L->x_bf16 : nullptr, T, s);
   if (rc) return rc;
   if (L->timing) cudaEventRecord(L->ph[1], s);
-
-  // Under token-sharded expert parallelism the shared expert runs on the layer's second stream, beside
-  // the exchange and the routed experts: it reads only this rank's tokens (x, or the bf16 copy the
-  // gather launch just made) and writes buffers nothing else touches before the combine.
-  const bool shared_aside = L->has_shared && T > 0 && c.ep_world > 1 && !L->ep_replicated && L->aux_stream;
-  if (shared_aside) {
-    const __nv_bfloat16* xb = x_f32 ? L->x_bf16 : static_cast<const __nv_bfloat16*>(x);
-    ATENIA_CUDA_TRY(cudaEventRecord(L->ev_fork, s));
-    ATENIA_CUDA_TRY(cudaStreamWaitEvent(L->aux_stream, L->ev_fork, 0));
-    rc = run_shared_gemms(L, xb, T, L->aux_stream);
-    if (rc) return rc;
-    ATENIA_CUDA_TRY(cudaEventRecord(L->ev_join, L->aux_stream));
-  }
 
   if (c.ep_world == 1) {
     if (L->timing) cudaEventRecord(L->ph[2], s);

@@ -213,45 +213,52 @@ __global__ void __launch_bounds__(kDW * 32) router_dmma_kernel(RouterArgs a) {
   }
 }
 
-// ---- few experts (E <= 16): operands streamed from global memory straight into fragments -----------
-// With one or two 8-expert tiles the staged kernel above does a handful of products per chunk and is
-// bound by its two block-wide barriers per chunk.  Here nothing is staged and the main loop has no
-// barrier: warp w of the CTA owns the k-range [w KW, (w+1) KW) of the dot products of the CTA's 8 MT
-// tokens.  The summation index of an m8n8k4 product is free to be permuted as long as A and B agree,
-// so lane (r, c) = (lane / 4, lane % 4) loads EIGHT consecutive k of token row r (16 bytes of bf16)
-// and of expert row r of each tile (32 bytes of f32) at k = base + 8 c, and step j of eight uses
-// element j of every lane's vectors: the four lanes of a row cover 32 consecutive k, global loads are
-// whole sectors, every operand element is converted to f64 once per CTA.  The vectors of the next 32 k
-// are in flight while the current ones are multiplied.  The eight warps' partial sums are added
-// through shared memory in warp order (fixed), then bias, rounding and routing as above.
+// ---- operands streamed from global memory straight into fragments (few experts, or few tokens) ------
+// With one or two 8-expert tiles, or with a batch too small to fill the GPU with 32-token CTAs, the staged
+// kernel above is bound by its two block-wide barriers per 32-k chunk and by the latency of one chunk in
+// flight.  Here nothing is staged and the main loop has no barrier.  The eight warps of a CTA are
+// arranged NW_N x NW_K as above: a warp owns NTW 8-expert tiles and the k-range [kslice KW, (kslice+1) KW)
+// of the dot products of the CTA's 8 MT tokens.  The summation index of an m8n8k4 product is free to be
+// permuted as long as A and B agree, so lane (r, c) = (lane / 4, lane % 4) loads EIGHT consecutive k of
+// token row r (16 bytes of bf16) and of expert row r of each of its tiles (32 bytes of f32) at
+// k = base + 8 c, and step j of eight uses element j of every lane's vectors: the four lanes of a row
+// cover 32 consecutive k, global loads are whole sectors (the warps of one k-slice read the same token
+// vectors: the first brings them into L1).  The vectors of the next 32 k are in flight while the current
+// ones are multiplied.  Partial sums of the k-slices are added through shared memory in slice order
+// (fixed), then bias, rounding and routing as above.
 template <int E_T, int MT>
 __global__ void __launch_bounds__(kDW * 32) router_dmma_direct_kernel(RouterArgs a, int kw) {
   constexpr int NT = E_T / 8;
+  constexpr int NW_N = NT < kDW ? NT : kDW;
+  constexpr int NW_K = kDW / NW_N;
+  constexpr int NTW = NT / NW_N;
   constexpr int kTok = 8 * MT;
-  __shared__ double part_s[kDW][MT][NT][32][2];
-  __shared__ double gpart_s[kDW][kTok];
+  __shared__ double part_s[kDW][MT][NTW][32][2];
+  __shared__ double gpart_s[NW_K][kTok];
   __shared__ float lg_s[kTok][E_T];
   __shared__ double exps_s[kDW][E_T];
   __shared__ int32_t idx_s[kTok][kMaxK];
   __shared__ float w_s[kTok][kMaxK];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int ngrp = warp % NW_N, kslice = warp / NW_N;
   const int r = lane >> 2, c = lane & 3;
   const int t0 = blockIdx.x * kTok;
   const int d = a.d, E = a.E;
-  const int k_begin = warp * kw, k_end = (k_begin + kw < d) ? k_begin + kw : d;
+  const int k_begin = kslice * kw < d ? kslice * kw : d, k_end = (k_begin + kw < d) ? k_begin + kw : d;
+  const bool do_gate = a.gate_vec != nullptr && ngrp == 0;  // one warp per k-slice takes the gate dot product
 
-  double acc[MT][NT][2];
+  double acc[MT][NTW][2];
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt) acc[mt][nt][0] = acc[mt][nt][1] = 0.0;
+    for (int j = 0; j < NTW; ++j) acc[mt][j][0] = acc[mt][j][1] = 0.0;
   double gacc[MT];
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt) gacc[mt] = 0.0;
 
   // raw vectors of one step: x as bf16 uses xq[mt][0] only, as f32 both; W always two float4
   uint4 xq[MT][2];
-  float4 wq[NT][2];
+  float4 wq[NTW][2];
   float4 gq[2];
   auto fetch = [&](int kb) {
     const int k = kb + c * 8;
@@ -272,17 +279,17 @@ __global__ void __launch_bounds__(kDW * 32) router_dmma_direct_kernel(RouterArgs
       }
     }
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-      const int e = nt * 8 + r;
-      wq[nt][0] = wq[nt][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int j = 0; j < NTW; ++j) {
+      const int e = (ngrp * NTW + j) * 8 + r;
+      wq[j][0] = wq[j][1] = make_float4(0.f, 0.f, 0.f, 0.f);
       if (k_ok && e < E) {
         const float4* p = reinterpret_cast<const float4*>(a.w_router + (size_t)e * d + k);
-        wq[nt][0] = __ldg(p);
-        wq[nt][1] = __ldg(p + 1);
+        wq[j][0] = __ldg(p);
+        wq[j][1] = __ldg(p + 1);
       }
     }
     gq[0] = gq[1] = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (a.gate_vec && k_ok) {
+    if (do_gate && k_ok) {
       const float4* p = reinterpret_cast<const float4*>(a.gate_vec + k);
       gq[0] = __ldg(p);
       gq[1] = __ldg(p + 1);
@@ -290,7 +297,7 @@ __global__ void __launch_bounds__(kDW * 32) router_dmma_direct_kernel(RouterArgs
   };
   if (k_begin < k_end) fetch(k_begin);
   for (int kb = k_begin; kb < k_end; kb += 32) {
-    double xd[MT][8], wd[NT][8];
+    double xd[MT][8], wd[NTW][8];
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt) {
       if (a.x_is_f32) {
@@ -308,13 +315,13 @@ __global__ void __launch_bounds__(kDW * 32) router_dmma_direct_kernel(RouterArgs
       }
     }
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-      const float f[8] = {wq[nt][0].x, wq[nt][0].y, wq[nt][0].z, wq[nt][0].w,
-                          wq[nt][1].x, wq[nt][1].y, wq[nt][1].z, wq[nt][1].w};
+    for (int jt = 0; jt < NTW; ++jt) {
+      const float f[8] = {wq[jt][0].x, wq[jt][0].y, wq[jt][0].z, wq[jt][0].w,
+                          wq[jt][1].x, wq[jt][1].y, wq[jt][1].z, wq[jt][1].w};
 #pragma unroll
-      for (int j = 0; j < 8; ++j) wd[nt][j] = (double)f[j];
+      for (int j = 0; j < 8; ++j) wd[jt][j] = (double)f[j];
     }
-    if (a.gate_vec) {
+    if (do_gate) {
       const float g[8] = {gq[0].x, gq[0].y, gq[0].z, gq[0].w, gq[1].x, gq[1].y, gq[1].z, gq[1].w};
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt)
@@ -325,38 +332,39 @@ __global__ void __launch_bounds__(kDW * 32) router_dmma_direct_kernel(RouterArgs
 #pragma unroll
     for (int j = 0; j < 8; ++j)
 #pragma unroll
-      for (int nt = 0; nt < NT; ++nt)
+      for (int jt = 0; jt < NTW; ++jt)
 #pragma unroll
-        for (int mt = 0; mt < MT; ++mt) dmma884(acc[mt][nt], xd[mt][j], wd[nt][j]);
+        for (int mt = 0; mt < MT; ++mt) dmma884(acc[mt][jt], xd[mt][j], wd[jt][j]);
   }
-  // partial sums of this warp's k-range: C[row r][columns 2c, 2c + 1] of every tile
+  // partial sums of this warp's k-range: C[row r][columns 2c, 2c + 1] of every tile it owns
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-      part_s[warp][mt][nt][lane][0] = acc[mt][nt][0];
-      part_s[warp][mt][nt][lane][1] = acc[mt][nt][1];
+    for (int jt = 0; jt < NTW; ++jt) {
+      part_s[warp][mt][jt][lane][0] = acc[mt][jt][0];
+      part_s[warp][mt][jt][lane][1] = acc[mt][jt][1];
     }
-  if (a.gate_vec) {
+  if (do_gate) {
     // the four lanes of a row hold the four k-quarters of the gate dot product: fold them (fixed tree)
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt) {
       double v = gacc[mt];
       v += __shfl_xor_sync(0xffffffffu, v, 1);
       v += __shfl_xor_sync(0xffffffffu, v, 2);
-      if (c == 0) gpart_s[warp][mt * 8 + r] = v;
+      if (c == 0) gpart_s[kslice][mt * 8 + r] = v;
     }
   }
   __syncthreads();
-  // logits: the warps' partial sums in warp order, then the bias, then the rounding to f32
+  // logits: the k-slices' partial sums in slice order, then the bias, then the rounding to f32
   for (int i = threadIdx.x; i < kTok * E_T; i += blockDim.x) {
     const int t = i / E_T, e = i - t * E_T;
     if (e >= E) continue;
     const int mt = t >> 3, rr = t & 7, nt = e >> 3, col = e & 7;
+    const int og = nt / NTW, jt = nt - og * NTW;
     const int src_lane = rr * 4 + (col >> 1), which = col & 1;
     double v = 0.0;
 #pragma unroll
-    for (int w = 0; w < kDW; ++w) v += part_s[w][mt][nt][src_lane][which];
+    for (int ks = 0; ks < NW_K; ++ks) v += part_s[ks * NW_N + og][mt][jt][src_lane][which];
     if (a.bias) v += (double)a.bias[e];
     const float f = (float)v;
     lg_s[t][e] = f;
@@ -366,14 +374,14 @@ __global__ void __launch_bounds__(kDW * 32) router_dmma_direct_kernel(RouterArgs
   if (a.gate_vec && a.gate_scale && threadIdx.x < kTok) {
     const int t = threadIdx.x, tg = t0 + t;
     double v = 0.0;
-    for (int w = 0; w < kDW; ++w) v += gpart_s[w][t];
+    for (int ks = 0; ks < NW_K; ++ks) v += gpart_s[ks][t];
     if (tg < a.T) a.gate_scale[tg] = (float)(1.0 / (1.0 + exp(-v)));
   }
   __syncthreads();
   for (int t = warp; t < kTok; t += kDW) {
     const int tg = t0 + t;
     if (tg >= a.T) continue;
-    int rc = route_one_warp<1>(lg_s[t], E, a.k, a.renormalize, lane, idx_s[t], w_s[t], exps_s[warp]);
+    int rc = route_one_warp<(E_T + 31) / 32>(lg_s[t], E, a.k, a.renormalize, lane, idx_s[t], w_s[t], exps_s[warp]);
     if (rc) {
       if (lane == 0) report_error(a.err, rc, 1005);
       if (lane < a.k) {  // keep downstream kernels in bounds
@@ -391,9 +399,11 @@ __global__ void __launch_bounds__(kDW * 32) router_dmma_direct_kernel(RouterArgs
 
 template <int E_T>
 int launch_direct(const RouterArgs& a, cudaStream_t s) {
-  // k-range of a warp: d over the eight warps, rounded up to whole 32-k steps
-  const int kw = ((a.d + kDW - 1) / kDW + 31) / 32 * 32;
-  if (a.T >= 8192) {
+  constexpr int NT = E_T / 8;
+  constexpr int NW_K = kDW / (NT < kDW ? NT : kDW);
+  // k-range of a k-slice: d over the slices, rounded up to whole 32-k steps
+  const int kw = ((a.d + NW_K - 1) / NW_K + 31) / 32 * 32;
+  if (a.T >= 8192 || (E_T > 16 && a.T >= 2048)) {
     router_dmma_direct_kernel<E_T, 2><<<(a.T + 15) / 16, kDW * 32, 0, s>>>(a, kw);
   } else {
     router_dmma_direct_kernel<E_T, 1><<<(a.T + 7) / 8, kDW * 32, 0, s>>>(a, kw);
@@ -432,11 +442,19 @@ int launch_router_dmma(const RouterArgs& a, cudaStream_t s) {
   if (a.T <= 0) return ATENIA_OK;
   if (a.k > kMaxK || a.E > 128 || a.d % 16 != 0) return ATENIA_ERR_UNSUPPORTED;
   int rc;
+  // few experts: always the barrier-free kernel; many experts: the barrier-free kernel while the batch
+  // is too small to fill the GPU with the staged kernel's 32-token CTAs (ATENIA_MOE_ROUTER_DIRECT_MAX
+  // moves the hand-over: A/B runs)
+  static const int direct_max = [] {
+    const char* e = std::getenv("ATENIA_MOE_ROUTER_DIRECT_MAX");
+    return e ? std::atoi(e) : 4095;
+  }();
+  const bool direct = a.T <= direct_max;
   if (a.E <= 8) rc = launch_direct<8>(a, s);
   else if (a.E <= 16) rc = launch_direct<16>(a, s);
-  else if (a.E <= 32) rc = launch_one<32>(a, s);
-  else if (a.E <= 64) rc = launch_one<64>(a, s);
-  else rc = launch_one<128>(a, s);
+  else if (a.E <= 32) rc = direct ? launch_direct<32>(a, s) : launch_one<32>(a, s);
+  else if (a.E <= 64) rc = direct ? launch_direct<64>(a, s) : launch_one<64>(a, s);
+  else rc = direct ? launch_direct<128>(a, s) : launch_one<128>(a, s);
   count_launch();
   return rc;
 }

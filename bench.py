@@ -338,6 +338,9 @@ class EpGroup:
         return [o.tolist() for o in out]
 
     def join_ep(self, layer, direct=False):
+        """Joins the layer to the expert-parallel group; with `direct` also maps the peers' buffers for the
+        peer-store exchange.  Returns True when every rank has the direct exchange set up, False when the
+        layer is on the NCCL send/receive exchange."""
         import ctypes as C
 
         import torch
@@ -350,12 +353,32 @@ class EpGroup:
             idt = torch.frombuffer(bytearray(buf.raw), dtype=torch.uint8).to(self.dev)
         self.dist.broadcast(idt, 0)
         layer.ep_init(bytes(idt.cpu().numpy().tobytes()))
-        if direct:
-            mine = torch.frombuffer(bytearray(layer.ep_ipc_export()), dtype=torch.uint8).to(self.dev)
-            blobs = [torch.empty_like(mine) for _ in range(self.world)]
-            self.dist.all_gather(blobs, mine)
+        if not direct:
+            return False
+        mine = torch.frombuffer(bytearray(layer.ep_ipc_export()), dtype=torch.uint8).to(self.dev)
+        blobs = [torch.empty_like(mine) for _ in range(self.world)]
+        self.dist.all_gather(blobs, mine)
+        ok = 1.0
+        try:
             layer.ep_ipc_import(b"".join(bytes(b.cpu().numpy().tobytes()) for b in blobs))
-        return direct
+        except Exception as e:  # no peer access between these GPUs, or IPC refused
+            sys.stderr.write(f"bench.py: rank {self.rank}: direct exchange unavailable ({e})\n")
+            ok = 0.0
+        t = torch.tensor([ok], device=self.dev)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MIN)
+        return bool(t.item() > 0.5)
+
+    def make_ep_layer(self, shape, w, max_tokens, direct):
+        """An expert-parallel layer of this rank with the direct exchange if every rank can have it, else
+        (all ranks together) a fresh layer on the NCCL exchange."""
+        from ateniaengine_b200 import synth
+        layer = synth.build_layer(shape, w, max_tokens=max_tokens, ep_rank=self.rank, ep_world=self.world)
+        if self.join_ep(layer, direct=direct) or not direct:
+            return layer, direct
+        layer.close()
+        layer = synth.build_layer(shape, w, max_tokens=max_tokens, ep_rank=self.rank, ep_world=self.world)
+        self.join_ep(layer, direct=False)
+        return layer, False
 
     def close(self):
         if self.dist is not None:
@@ -390,9 +413,10 @@ def measure_record(grp, name, T_total, args, peaks, seed=2, direct=False):
     el = shape.num_experts // G
     w = synth.make_weights(shape, seed, grp.dev, experts=(grp.rank * el, el) if G > 1 else None)
     x = synth.make_activations(shape, seed + grp.rank, grp.dev, tokens=T)
-    layer = synth.build_layer(shape, w, max_tokens=T, ep_rank=grp.rank if G > 1 else 0, ep_world=G)
     if G > 1:
-        grp.join_ep(layer, direct=direct)
+        layer, direct = grp.make_ep_layer(shape, w, T, direct)
+    else:
+        layer = synth.build_layer(shape, w, max_tokens=T)
     out = torch.empty_like(x)
     fn = lambda: layer.forward(x, out=out)
     for _ in range(args.warmup):
@@ -554,9 +578,11 @@ def main():
     el = E // args.gpus
     w = synth.make_weights(shape, 2, dev, experts=(rank * el, el))
     x = synth.make_activations(shape, 2 + rank, dev, tokens=T)
-    layer = synth.build_layer(shape, w, max_tokens=T, ep_rank=rank, ep_world=args.gpus)
     if args.gpus > 1:
-        grp.join_ep(layer, direct=direct)
+        layer, direct = grp.make_ep_layer(shape, w, T, direct)
+    else:
+        layer = synth.build_layer(shape, w, max_tokens=T)
+    if args.gpus > 1:
         if direct:
             config["parallelism"] = (f"expert-parallel ep{args.gpus}, rows stored peer to peer over NVLink, "
                                      "NCCL for counts and ordering")
