@@ -5,7 +5,7 @@ import sys
 from concurrent.futures import ThreadPoolExecutor
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-SOURCES = ["grouped_gemm.cu", "w8_gemm.cu", "w8_gemm_m256.cu", "w8_decode_gemm.cu", "bf16_decode_gemm.cu", "decode_gemv.cu", "grouped_gemm_2cta.cu", "router.cu", "router_dmma.cu", "router_splitk.cu", "dispatch.cu", "combine.cu", "moe_layer.cu", "ep.cu", "registry.cu", "noalloc.cu", "planner.cu", "stack.cu", "tier.cu", "dense_int8.cu"]
+SOURCES = ["grouped_gemm.cu", "w8_gemm.cu", "w8_gemm_m256.cu", "bf16_decode_gemm.cu", "decode_gemv.cu", "grouped_gemm_2cta.cu", "router.cu", "router_dmma.cu", "router_splitk.cu", "dispatch.cu", "combine.cu", "moe_layer.cu", "ep.cu", "registry.cu", "noalloc.cu", "planner.cu", "stack.cu", "tier.cu", "dense_int8.cu"]
 LIB = os.path.join(HERE, "libatenia_moe.so")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-ccbin", "g++",

@@ -160,10 +160,11 @@ struct GroupedGemmCheckArgs {
   int max_rows;
 };
 int launch_grouped_gemm_check(const GroupedGemmCheckArgs& a, cudaStream_t s);
-// The same contraction for calls of at most four rows in all (decode at batch 1-2): a CUDA-core
-// matrix-vector kernel that streams the touched experts' weights once (decode_gemv.cu).
+// The same contraction for calls of at most two rows in all (decode at batch 1): a CUDA-core
+// matrix-vector kernel that streams the touched experts' weights once (decode_gemv.cu; it handles up to
+// four rows per group, but from three rows on the tensor-core kernels are as fast).
 int launch_grouped_gemv(const GroupedGemmCheckArgs& a, cudaStream_t s);
-constexpr int kGemvMaxRows = 4;
+constexpr int kGemvMaxRows = 2;
 
 int launch_f32_to_bf16(const float* src, __nv_bfloat16* dst, int64_t n, cudaStream_t s);
 // y = (x * inv_rms(x)) * gamma per row (stack.cu); gamma may be null (unit gain)
@@ -180,10 +181,6 @@ int encode_tmap_2d_u8(CUtensorMap* out, const void* base, uint64_t rows, uint64_
 // token matrix (box {64, 128}, 128B swizzle); tmap_b0/b1 are int8 maps with the 64-byte swizzle.
 int launch_grouped_gemm_w8_tmem(const GroupedGemmArgs& a, int num_sms, cudaStream_t s);
 constexpr size_t kW8SplitKSlotFloats = 2 * 128 * 128;  // per CTA: two slots of this size
-// W8A16 for small groups with the weights widened into shared memory (w8_decode_gemm.cu): transposed
-// product, stream-K.  tmap_a is the bf16 token matrix (box {64, 128}, 128B swizzle); tmap_b0/b1 are the
-// UNSWIZZLED int8 maps (box {64, 128}); splitk_ws as for the tensor-memory kernel.
-int launch_grouped_gemm_w8_decode(const GroupedGemmArgs& a, int num_sms, cudaStream_t s);
 // W8A16 for large groups (w8_gemm_m256.cu): 256-row token tiles, the widened weight tile shared by two
 // M128 MMAs.  Tensor maps as for launch_grouped_gemm_tcgen05 with w8 set.
 int launch_grouped_gemm_w8_m256(const GroupedGemmArgs& a, int num_sms, cudaStream_t s);

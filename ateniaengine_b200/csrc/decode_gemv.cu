@@ -1,6 +1,6 @@
-// Expert products for a handful of rows (decode at batch 1-2): a CUDA-core matrix-vector kernel.
+// Expert products for one or two rows (decode at batch 1): a CUDA-core matrix-vector kernel.
 //
-// With at most four rows in the whole call the work is reading the touched experts' weights once:
+// With a row or two in the whole call the work is reading the touched experts' weights once:
 // 2 F d + d F weights per expert for a few flops each.  A tensor-core tile of 128 weight rows spends
 // its time on staging (and, for INT8, on the widening chain) rather than on the stream; here every
 // warp streams whole weight rows with 16-byte loads, four rows (two of each matrix) in flight per
@@ -151,7 +151,10 @@ __global__ void __launch_bounds__(kGvWarps * 32) grouped_gemv_kernel(GroupedGemm
 }  // namespace
 
 // Same arguments as the CUDA-core checking contraction (raw matrix pointers per group); the call must
-// have at most kGvMaxRows rows in total (a.max_rows), so that every group has at most that many.
+// have at most kGvMaxRows rows in total (a.max_rows), so that every group has at most that many.  The
+// layer sends calls of at most kGemvMaxRows = 2 rows here: measured on B200 (Mixtral shape, one token)
+// bf16 0.189 -> 0.183 ms, INT8 0.174 -> 0.166 ms, a DeepSeek-shaped layer with its shared expert
+// 0.182 -> 0.156 ms; with four rows the tensor-core decode kernels are as fast or faster.
 int launch_grouped_gemv(const GroupedGemmCheckArgs& a, cudaStream_t s) {
   if (a.num_groups <= 0 || a.max_rows <= 0) return ATENIA_OK;
   if (a.max_rows > kGvMaxRows || a.K % 16 != 0) return ATENIA_ERR_SHAPE;

@@ -60,16 +60,14 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
   // shared-memory widening kernel of grouped_gemm.cu (tests, A/B runs).
   const bool m256 = q && large && L->w8_mode != 1 && L->w8_mode != 2 && !L->use_check_gemm;
   const bool tmem = q && !m256 && (L->w8_mode == 1 || (L->w8_mode != 2 && !large));
-  // w8_mode 5: small groups through the shared-memory widening decode kernel (w8_decode_gemm.cu) -- A/B runs
-  const bool w8dec = tmem && L->w8_mode == 5 && max_rows <= 128 * num_groups;
   // bf16: 256-row CTA-pair tiles pay off once an average group fills a few of them; a call of at most
   // 16 rows (decode) takes the stream-K kernel of bf16_decode_gemm.cu, which spreads the few tiles
   // there are over all SMs (bf16_decode 1 / 0 pins it on for every call of at most 128 rows / off).
   const bool dec = !q && !L->use_check_gemm && L->splitk_ws &&
                    (L->bf16_decode == 1 ? max_rows <= 128 : (L->bf16_decode < 0 && max_rows <= 16));
   const bool pairs = !q && !dec && (L->pair_mode == 1 || (L->pair_mode == 0 && max_rows >= 512 * num_groups));
-  // a call of at most four rows in all (decode at batch 1-2) is a stream over the touched experts'
-  // weights: the CUDA-core matrix-vector kernel (ATENIA_MOE_GEMV=0 keeps the tensor-core kernels: A/B runs)
+  // a call of at most two rows in all (decode at batch 1) is a stream over the touched experts' weights:
+  // the CUDA-core matrix-vector kernel (ATENIA_MOE_GEMV=0 keeps the tensor-core kernels: A/B runs)
   const bool gemv = L->use_gemv && max_rows <= kGemvMaxRows && !L->use_check_gemm;
   if (L->timing) cudaEventRecord(L->ev[0], s);
   if (L->use_check_gemm || gemv) {
@@ -81,8 +79,8 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
   } else {
     GroupedGemmArgs g1{};
     g1.tmap_a = tm_a;
-    g1.tmap_b0 = (tmem && !w8dec) ? L->d_tm_gate_sw : L->d_tm_gate;
-    g1.tmap_b1 = (tmem && !w8dec) ? L->d_tm_up_sw : L->d_tm_up;
+    g1.tmap_b0 = tmem ? L->d_tm_gate_sw : L->d_tm_gate;
+    g1.tmap_b1 = tmem ? L->d_tm_up_sw : L->d_tm_up;
     g1.group_offsets = group_offsets;
     g1.num_groups = num_groups;
     g1.N = c.d_ff;
@@ -96,7 +94,6 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
     g1.w8 = q;
     g1.splitk_ws = L->splitk_ws;
     int rc = m256 ? launch_grouped_gemm_w8_m256(g1, L->num_sms, s)
-                  : w8dec ? launch_grouped_gemm_w8_decode(g1, L->num_sms, s)
                   : dec ? launch_grouped_gemm_bf16_decode(g1, L->num_sms, s)
                   : tmem ? launch_grouped_gemm_w8_tmem(g1, L->num_sms, s)
                          : pairs ? launch_grouped_gemm_2cta(g1, L->num_sms, s)
@@ -112,7 +109,7 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
   } else {
     GroupedGemmArgs g2{};
     g2.tmap_a = tm_mid;
-    g2.tmap_b0 = (tmem && !w8dec) ? L->d_tm_down_sw : L->d_tm_down;
+    g2.tmap_b0 = tmem ? L->d_tm_down_sw : L->d_tm_down;
     g2.tmap_b1 = g2.tmap_b0;
     g2.group_offsets = group_offsets;
     g2.num_groups = num_groups;
@@ -127,7 +124,6 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
     g2.w8 = q;
     g2.splitk_ws = L->splitk_ws;
     int rc = m256 ? launch_grouped_gemm_w8_m256(g2, L->num_sms, s)
-                  : w8dec ? launch_grouped_gemm_w8_decode(g2, L->num_sms, s)
                   : dec ? launch_grouped_gemm_bf16_decode(g2, L->num_sms, s)
                   : tmem ? launch_grouped_gemm_w8_tmem(g2, L->num_sms, s)
                          : pairs ? launch_grouped_gemm_2cta(g2, L->num_sms, s)
@@ -248,7 +244,7 @@ int atenia_moe_create(const AteniaMoeConfig* cfg, AteniaMoeLayer** out) {
   L->w8_mode = std::getenv("ATENIA_MOE_W8_MODE") ? std::atoi(std::getenv("ATENIA_MOE_W8_MODE")) : 0;
   L->pair_mode = std::getenv("ATENIA_MOE_PAIR_MODE") ? std::atoi(std::getenv("ATENIA_MOE_PAIR_MODE")) : 0;
   L->shared_aside = !(std::getenv("ATENIA_MOE_SHARED_ASIDE") && std::atoi(std::getenv("ATENIA_MOE_SHARED_ASIDE")) == 0);
-  L->use_gemv = std::getenv("ATENIA_MOE_GEMV") && std::atoi(std::getenv("ATENIA_MOE_GEMV")) != 0;
+  L->use_gemv = !(std::getenv("ATENIA_MOE_GEMV") && std::atoi(std::getenv("ATENIA_MOE_GEMV")) == 0);
   // Router kernel: by default the split-k kernel for batches of at most 128 tokens (many CTAs share one
   // token block's dot products), the f64 tensor-core kernel for 32 experts and more, the CUDA-core
   // kernel otherwise.  ATENIA_MOE_ROUTER = scalar | dmma | splitk pins one (tests, A/B runs); a pinned
