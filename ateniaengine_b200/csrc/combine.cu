@@ -128,6 +128,17 @@ int launch_combine(const CombineArgs& a, cudaStream_t s) {
   return (int)cudaGetLastError();
 }
 
+__global__ void set_pair_kernel(int32_t* p, int32_t a, int32_t b) {
+  p[0] = a;
+  p[1] = b;
+}
+
+int launch_set_pair(int32_t* p, int32_t a, int32_t b, cudaStream_t s) {
+  set_pair_kernel<<<1, 1, 0, s>>>(p, a, b);
+  count_launch();
+  return (int)cudaGetLastError();
+}
+
 int launch_f32_to_bf16(const float* src, __nv_bfloat16* dst, int64_t n, cudaStream_t s) {
   if (n <= 0) return ATENIA_OK;
   int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);

@@ -167,6 +167,8 @@ int launch_grouped_gemv(const GroupedGemmCheckArgs& a, cudaStream_t s);
 constexpr int kGemvMaxRows = 2;
 
 int launch_f32_to_bf16(const float* src, __nv_bfloat16* dst, int64_t n, cudaStream_t s);
+// p[0] = a, p[1] = b on the stream (the one-group offsets of the shared expert's GEMMs)
+int launch_set_pair(int32_t* p, int32_t a, int32_t b, cudaStream_t s);
 // y = (x * inv_rms(x)) * gamma per row (stack.cu); gamma may be null (unit gain)
 int launch_rmsnorm_rows(const float* x, const float* gamma, float eps, float* y, int T, int d, cudaStream_t s);
 

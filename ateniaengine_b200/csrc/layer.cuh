@@ -86,7 +86,8 @@ struct AteniaMoeLayer {
   __nv_bfloat16* h_shared = nullptr;  // [max_tokens, Fs]
   __nv_bfloat16* y_shared = nullptr;  // [max_tokens, d]
   atenia::DeviceError* d_err = nullptr;
-  float* splitk_ws = nullptr;  // INT8: stream-K partial sums, 2 slots per SM
+  float* splitk_ws = nullptr;  // stream-K partial sums of the decode kernels, 2 slots per SM
+  float* splitk_ws_shared = nullptr;  // the same for the shared expert's launches (INT8 with a shared expert)
   CUtensorMap tm_x_perm{}, tm_h{}, tm_h_shared{};
 
   // expert parallelism

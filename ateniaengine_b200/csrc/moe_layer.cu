@@ -182,7 +182,7 @@ int run_shared_gemms(AteniaMoeLayer* L, const __nv_bfloat16* xb, int T, cudaStre
   g1.err = L->d_err;
   g1.max_rows = T;
   g1.w8 = q;
-  g1.splitk_ws = L->splitk_ws;
+  g1.splitk_ws = L->splitk_ws_shared;  // its own: these launches may run beside the routed GEMMs
   rc = m256 ? launch_grouped_gemm_w8_m256(g1, L->num_sms, s)
        : tmem ? launch_grouped_gemm_w8_tmem(g1, L->num_sms, s)
                   : pairs ? launch_grouped_gemm_2cta(g1, L->num_sms, s) : launch_grouped_gemm_tcgen05(g1, L->num_sms, s);
@@ -202,7 +202,7 @@ int run_shared_gemms(AteniaMoeLayer* L, const __nv_bfloat16* xb, int T, cudaStre
   g2.err = L->d_err;
   g2.max_rows = T;
   g2.w8 = q;
-  g2.splitk_ws = L->splitk_ws;
+  g2.splitk_ws = L->splitk_ws_shared;
   rc = m256 ? launch_grouped_gemm_w8_m256(g2, L->num_sms, s)
        : tmem ? launch_grouped_gemm_w8_tmem(g2, L->num_sms, s)
                   : pairs ? launch_grouped_gemm_2cta(g2, L->num_sms, s) : launch_grouped_gemm_tcgen05(g2, L->num_sms, s);
@@ -299,7 +299,8 @@ int atenia_moe_create(const AteniaMoeConfig* cfg, AteniaMoeLayer** out) {
   TRY_ALLOC(L->d_tm_up, (size_t)L->n_groups);
   TRY_ALLOC(L->d_tm_down, (size_t)L->n_groups);
   TRY_ALLOC(L->d_tm_shared, 3);
-  if (L->bf16_decode != 0) TRY_ALLOC(L->splitk_ws, (size_t)L->num_sms * 2 * kW8SplitKSlotFloats);
+  if (L->bf16_decode != 0 || c.weight_dtype == ATENIA_W_INT8_ROW)
+    TRY_ALLOC(L->splitk_ws, (size_t)L->num_sms * 2 * kW8SplitKSlotFloats);
   {
     const int sk_cap = L->router_variant == 2 ? 1024 : (L->router_variant == -1 ? 128 : 0);
     L->sk_tokens = c.max_tokens < sk_cap ? c.max_tokens : sk_cap;
@@ -316,7 +317,7 @@ int atenia_moe_create(const AteniaMoeConfig* cfg, AteniaMoeLayer** out) {
     }
   }
   if (c.weight_dtype == ATENIA_W_INT8_ROW) {
-    TRY_ALLOC(L->splitk_ws, (size_t)L->num_sms * 2 * kW8SplitKSlotFloats);
+    if (L->has_shared) TRY_ALLOC(L->splitk_ws_shared, (size_t)L->num_sms * 2 * kW8SplitKSlotFloats);
     TRY_ALLOC(L->d_tm_gate_sw, (size_t)L->n_groups);
     TRY_ALLOC(L->d_tm_up_sw, (size_t)L->n_groups);
     TRY_ALLOC(L->d_tm_down_sw, (size_t)L->n_groups);
@@ -389,7 +390,7 @@ int atenia_moe_destroy(AteniaMoeLayer* L) {
                   L->d_tm_down, L->d_tm_shared, L->d_sc_gate, L->d_sc_up, L->d_sc_down, L->d_sc_shared,
                   L->d_p_gate, L->d_p_up, L->d_p_down, L->d_p_shared, L->d_tm_gate_sw, L->d_tm_up_sw,
                   L->d_tm_down_sw, L->d_tm_shared_sw,
-                  L->splitk_ws, L->d_escore, L->logits_ws, L->recv_x, L->recv_h, L->recv_y, L->d_counts_all,
+                  L->splitk_ws, L->splitk_ws_shared, L->d_escore, L->logits_ws, L->recv_x, L->recv_h, L->recv_y, L->d_counts_all,
                   L->d_group_offsets, L->d_peer_recv_x, L->d_peer_y_perm, L->d_dst_base, L->d_src_base,
                   L->d_gemm_offsets, L->d_bar, L->sk_part, L->sk_gate, L->sk_counters, L->block_normed};
   for (void* p : ptrs)
@@ -587,6 +588,9 @@ static int forward_impl(AteniaMoeLayer* L, const void* x, int x_dtype, int T, vo
     }
     ATENIA_CUDA_TRY(cudaEventRecord(L->ev_fork, s));
     ATENIA_CUDA_TRY(cudaStreamWaitEvent(L->aux_stream, L->ev_fork, 0));
+    // (the dispatch kernels, which write the one-group offsets {0, T} otherwise, run later on `s`)
+    rc0 = launch_set_pair(L->shared_offsets, 0, T, L->aux_stream);
+    if (rc0) return rc0;
     rc0 = run_shared_gemms(L, xb, T, L->aux_stream);
     if (rc0) return rc0;
     ATENIA_CUDA_TRY(cudaEventRecord(L->ev_join, L->aux_stream));
@@ -636,7 +640,7 @@ static int forward_impl(AteniaMoeLayer* L, const void* x, int x_dtype, int T, vo
   da.expert_offsets = L->expert_offsets;
   da.perm = L->perm;
   da.inv_perm = L->inv_perm;
-  da.extra_offsets = L->shared_offsets;
+  da.extra_offsets = shared_aside ? nullptr : L->shared_offsets;
   da.T = T;
   da.err = L->d_err;
   rc = launch_dispatch(da, s);

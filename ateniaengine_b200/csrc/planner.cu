@@ -96,8 +96,9 @@ uint64_t layer_workspace_bytes(const AteniaMoeConfig& c, int world) {
   t.add(groups * tm);
   t.add(groups * tm);
   t.add(3 * tm);
+  t.add((uint64_t)148 * 2 * kW8SplitKSlotFloats * 4);  // stream-K partial sums, one pair of slots per SM
   if (q) {
-    t.add((uint64_t)148 * 2 * kW8SplitKSlotFloats * 4);  // stream-K partial sums, one pair of slots per SM
+    if (Fs) t.add((uint64_t)148 * 2 * kW8SplitKSlotFloats * 4);  // the same for the shared expert's launches
     t.add(groups * tm);
     t.add(groups * tm);
     t.add(groups * tm);
