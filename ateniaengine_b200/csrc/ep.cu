@@ -77,6 +77,111 @@ __device__ __forceinline__ void warp_copy_row_bf16(uint4* __restrict__ drow, con
 
 constexpr int kEpRowWarps = 8;  // warps (rows in flight) per block of the two row-moving kernels
 
+// ---- flag synchronisation -------------------------------------------------------------------------
+// Every rank owns a sync buffer that all ranks map: words [phase][source rank] hold the epoch (forward
+// number) up to which that source has finished the phase -- 0: its expert counts are stored here,
+// 1: its rows are stored in this rank's receive buffer, 2: its results are stored in this rank's y_perm --
+// followed by the count matrix [world][E].  A rank publishes with a system-scope fence and a release
+// store into every peer's buffer; a rank consumes by polling its OWN buffer (local memory) with acquire
+// loads.  Every poll is bounded in time and in iterations: a peer that never arrives costs
+// ATENIA_ERR_DEVICE_TIMEOUT and a sticky "gave up" word that makes the later waits of this layer return
+// at once; the kernels then run on stale but in-range counts (every index is range-checked).
+constexpr int kEpMaxWorld = 16;
+constexpr int kEpSyncFlagWords = 4 * kEpMaxWorld;  // epochs [3][kEpMaxWorld] + spare; the counts follow
+constexpr size_t kEpSyncBytes = (size_t)2 << 20;   // a whole allocation granule: nothing else shares the mapping
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// true once *flag has reached `epoch`; false after limit_ns (or the matching number of polls)
+__device__ bool wait_epoch(const uint32_t* flag, uint32_t epoch, uint64_t limit_ns) {
+  const uint64_t t0 = globaltimer_ns();
+  const uint64_t max_polls = limit_ns / 64 + 1024;
+  for (uint64_t polls = 0; polls < max_polls; ++polls) {
+    if ((int32_t)(ld_acquire_sys(flag) - epoch) >= 0) return true;
+    __nanosleep(polls < 256 ? 32 : 256);
+    if ((polls & 255) == 255 && globaltimer_ns() - t0 > limit_ns) return false;
+  }
+  return false;
+}
+
+// lanes 0 .. world-1 of the calling block wait for their source's epoch of `phase`
+__device__ void wait_phase(const uint32_t* my_sync, uint32_t* state, int phase, int world, uint64_t limit_ns,
+                           DeviceError* err) {
+  if ((int)threadIdx.x >= world) return;
+  if (state[3] != 0) {  // an earlier wait of this layer gave up: the exchange is out of step for good
+    report_error(err, ATENIA_ERR_STATE, 3110 + phase);
+    return;
+  }
+  if (!wait_epoch(my_sync + phase * kEpMaxWorld + threadIdx.x, state[0], limit_ns)) {
+    state[3] = 1;
+    report_error(err, ATENIA_ERR_DEVICE_TIMEOUT, 3100 + phase);
+  }
+}
+
+// End of a row-moving kernel: when the last block of the grid has finished, tell every rank that this
+// rank's stores of `phase` are done.  Every thread fences its own peer stores; the block counter is
+// the usual release (fence, then add) / acquire (add, then fence) pair.
+__device__ void grid_done_publish(uint32_t* const* peer_sync, uint32_t* state, int phase, int world, int rank) {
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned prev = atomicAdd(&state[phase], 1u);
+    if (prev == gridDim.x - 1) {
+      state[phase] = 0;  // the next launch of this kernel follows in stream order
+      __threadfence_system();
+      const uint32_t epoch = state[0];
+      for (int p = 0; p < world; ++p) st_release_sys(peer_sync[p] + phase * kEpMaxWorld + rank, epoch);
+    }
+  }
+}
+
+// Start of a forward: next epoch; this rank's row counts per expert into every rank's count matrix.
+__global__ void ep_counts_publish_kernel(const int32_t* __restrict__ off, int E, int world, int rank,
+                                         uint32_t* const* __restrict__ peer_sync, uint32_t* state) {
+  __shared__ uint32_t epoch_s;
+  if (threadIdx.x == 0) {
+    epoch_s = state[0] + 1;
+    state[0] = epoch_s;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < world * E; i += blockDim.x) {
+    const int p = i / E, e = i - p * E;
+    reinterpret_cast<int32_t*>(peer_sync[p] + kEpSyncFlagWords)[rank * E + e] = off[e + 1] - off[e];
+  }
+  __threadfence_system();
+  __syncthreads();
+  if ((int)threadIdx.x < world) st_release_sys(peer_sync[threadIdx.x] + rank, epoch_s);
+}
+
+// Row placement once every rank's counts of this forward have arrived (one block; E <= 128 threads work).
+__global__ void ep_plan_flags_kernel(const uint32_t* my_sync, uint32_t* state, int world, int E, int rank,
+                                     uint64_t limit_ns, int32_t* __restrict__ dst_base, int32_t* __restrict__ src_base,
+                                     int32_t* __restrict__ sub_offsets, int32_t* __restrict__ gemm_offsets,
+                                     DeviceError* err) {
+  wait_phase(my_sync, state, 0, world, limit_ns, err);
+  __syncthreads();
+  const int32_t* counts_all = reinterpret_cast<const int32_t*>(my_sync + kEpSyncFlagWords);
+  const int i = threadIdx.x;
+  if (i < E) ep_direct_plan_entry(counts_all, world, E, rank, i, dst_base, src_base, sub_offsets, gemm_offsets);
+}
+
+__global__ void ep_wait_kernel(const uint32_t* my_sync, uint32_t* state, int phase, int world, uint64_t limit_ns,
+                               DeviceError* err) {
+  wait_phase(my_sync, state, phase, world, limit_ns, err);
+}
+
 // Warp w of the grid moves dispatch rows w, w + W, ... (token perm[i] / k, expert topk_idx[perm[i]])
 // of this rank into the receive buffer of the expert's owner: gather and send in one pass.  A row
 // index outside the owner's buffer is recorded and skipped.
@@ -84,7 +189,7 @@ __global__ void __launch_bounds__(kEpRowWarps * 32) ep_scatter_kernel(
     const void* __restrict__ x, int x_is_f32, const int32_t* __restrict__ perm, const int32_t* __restrict__ topk_idx,
     const int32_t* __restrict__ expert_offsets, const int32_t* __restrict__ dst_base,
     __nv_bfloat16* const* __restrict__ peer_recv_x, int n_rows, int k, int d, int E, int e_local, int recv_cap,
-    DeviceError* err) {
+    DeviceError* err, uint32_t* const* __restrict__ peer_sync, uint32_t* state, int world, int rank) {
   const int lane = threadIdx.x & 31;
   const int nvec = d / 8;
   // entries with an invalid expert id were given no row: perm beyond the placed count is stale
@@ -113,6 +218,7 @@ __global__ void __launch_bounds__(kEpRowWarps * 32) ep_scatter_kernel(
                          nvec, lane);
     }
   }
+  if (peer_sync) grid_done_publish(peer_sync, state, 1, world, rank);
 }
 
 // Row i of this rank's expert outputs belongs to sub-group g = (local expert j, source rank p) and
@@ -120,7 +226,7 @@ __global__ void __launch_bounds__(kEpRowWarps * 32) ep_scatter_kernel(
 __global__ void __launch_bounds__(kEpRowWarps * 32) ep_return_kernel(
     const __nv_bfloat16* __restrict__ recv_y, const int32_t* __restrict__ group_offsets,
     const int32_t* __restrict__ src_base, __nv_bfloat16* const* __restrict__ peer_y_perm, int n_groups, int world,
-    int d, int rows_cap, DeviceError* err) {
+    int d, int rows_cap, DeviceError* err, uint32_t* const* __restrict__ peer_sync, uint32_t* state, int rank) {
   const int total = group_offsets[n_groups];
   const int lane = threadIdx.x & 31;
   const int nvec = d / 8;
@@ -139,6 +245,7 @@ __global__ void __launch_bounds__(kEpRowWarps * 32) ep_return_kernel(
     warp_copy_row_bf16(reinterpret_cast<uint4*>(peer_y_perm[lo % world] + (size_t)row * d),
                        reinterpret_cast<const uint4*>(recv_y + (size_t)i * d), nvec, lane);
   }
+  if (peer_sync) grid_done_publish(peer_sync, state, 2, world, rank);
 }
 
 #define NCCL_TRY(expr)                                 \
@@ -265,18 +372,28 @@ int ep_direct_send(AteniaMoeLayer* L, const void* x, int x_is_f32, int T, cudaSt
   const int G = c.ep_world, E = c.num_experts, El = L->e_local, rank = c.ep_rank, d = c.d_model;
   const int n = T * c.experts_per_token;
   ncclComm_t comm = L->ep->comm;
-  counts_kernel<<<1, 128, 0, s>>>(L->expert_offsets, E, L->d_counts_all + (size_t)rank * E);
-  count_launch();
-  NCCL_TRY(ncclAllGather(L->d_counts_all + (size_t)rank * E, L->d_counts_all, (size_t)E, ncclInt32, comm, s));
-  ep_plan_kernel<<<1, 128, 0, s>>>(L->d_counts_all, G, E, rank, L->d_dst_base, L->d_src_base, L->d_group_offsets,
-                                  L->d_gemm_offsets);
-  count_launch();
-  if (n > 0) {
-    const int blocks = (n + kEpRowWarps - 1) / kEpRowWarps;
+  const bool flags = L->ep_flags;
+  if (flags) {
+    ep_counts_publish_kernel<<<1, 128, 0, s>>>(L->expert_offsets, E, G, rank, L->d_peer_sync, L->d_ep_state);
+    count_launch();
+    ep_plan_flags_kernel<<<1, 128, 0, s>>>(L->d_sync, L->d_ep_state, G, E, rank, L->ep_flag_limit_ns, L->d_dst_base,
+                                           L->d_src_base, L->d_group_offsets, L->d_gemm_offsets, L->d_err);
+    count_launch();
+  } else {
+    counts_kernel<<<1, 128, 0, s>>>(L->expert_offsets, E, L->d_counts_all + (size_t)rank * E);
+    count_launch();
+    NCCL_TRY(ncclAllGather(L->d_counts_all + (size_t)rank * E, L->d_counts_all, (size_t)E, ncclInt32, comm, s));
+    ep_plan_kernel<<<1, 128, 0, s>>>(L->d_counts_all, G, E, rank, L->d_dst_base, L->d_src_base, L->d_group_offsets,
+                                    L->d_gemm_offsets);
+    count_launch();
+  }
+  if (n > 0 || flags) {  // (with flags the kernel also publishes "my rows are out", rows or no rows)
+    const int blocks = n > 0 ? (n + kEpRowWarps - 1) / kEpRowWarps : 1;
     const int cap = L->num_sms * 16;
     ep_scatter_kernel<<<blocks < cap ? blocks : cap, kEpRowWarps * 32, 0, s>>>(
         x, x_is_f32, L->perm, L->topk_idx, L->expert_offsets, L->d_dst_base, L->d_peer_recv_x, n,
-        c.experts_per_token, d, E, El, L->recv_cap, L->d_err);
+        c.experts_per_token, d, E, El, L->recv_cap, L->d_err, flags ? L->d_peer_sync : nullptr, L->d_ep_state, G,
+        rank);
     count_launch();
   }
   return (int)cudaGetLastError();
@@ -288,7 +405,13 @@ int ep_direct_finish(AteniaMoeLayer* L, cudaStream_t s) {
   const AteniaMoeConfig& c = L->cfg;
   const int G = c.ep_world, El = L->e_local, d = c.d_model;
   ncclComm_t comm = L->ep->comm;
-  NCCL_TRY(ncclAllReduce(L->d_bar, L->d_bar, 1, ncclInt32, ncclSum, comm, s));
+  const bool flags = L->ep_flags;
+  if (flags) {
+    ep_wait_kernel<<<1, 32, 0, s>>>(L->d_sync, L->d_ep_state, 1, G, L->ep_flag_limit_ns, L->d_err);
+    count_launch();
+  } else {
+    NCCL_TRY(ncclAllReduce(L->d_bar, L->d_bar, 1, ncclInt32, ncclSum, comm, s));
+  }
   if (L->timing) cudaEventRecord(L->ph[2], s);
   // the number of rows received is known on the device only: size by the buffer.
   // one GEMM group per local expert: its rows from all sources are contiguous
@@ -297,10 +420,16 @@ int ep_direct_finish(AteniaMoeLayer* L, cudaStream_t s) {
   if (rc) return rc;
   if (L->timing) cudaEventRecord(L->ph[3], s);
   ep_return_kernel<<<L->num_sms * 16, kEpRowWarps * 32, 0, s>>>(L->recv_y, L->d_group_offsets, L->d_src_base, L->d_peer_y_perm,
-                                                  L->n_groups, G, d, L->rows_cap, L->d_err);
+                                                  L->n_groups, G, d, L->rows_cap, L->d_err,
+                                                  flags ? L->d_peer_sync : nullptr, L->d_ep_state, c.ep_rank);
   count_launch();
   ATENIA_CUDA_TRY(cudaGetLastError());
-  NCCL_TRY(ncclAllReduce(L->d_bar, L->d_bar, 1, ncclInt32, ncclSum, comm, s));
+  if (flags) {
+    ep_wait_kernel<<<1, 32, 0, s>>>(L->d_sync, L->d_ep_state, 2, G, L->ep_flag_limit_ns, L->d_err);
+    count_launch();
+  } else {
+    NCCL_TRY(ncclAllReduce(L->d_bar, L->d_bar, 1, ncclInt32, ncclSum, comm, s));
+  }
   if (L->timing) cudaEventRecord(L->ph[4], s);
   return ATENIA_OK;
 }
@@ -383,7 +512,7 @@ int atenia_moe_ep_attach(AteniaMoeLayer* L, AteniaMoeLayer* owner) {
 
 namespace {
 struct IpcBlob {
-  cudaIpcMemHandle_t recv_x, y_perm;
+  cudaIpcMemHandle_t recv_x, y_perm, sync;
   int32_t recv_cap, rows_cap, d_model, pad;  // buffer sizes: every rank must have been created alike
 };
 }  // namespace
@@ -396,6 +525,15 @@ int atenia_moe_ep_ipc_export(AteniaMoeLayer* L, void* blob) {
   IpcBlob b;
   ATENIA_CUDA_TRY(cudaIpcGetMemHandle(&b.recv_x, L->recv_x));
   ATENIA_CUDA_TRY(cudaIpcGetMemHandle(&b.y_perm, L->y_perm));
+  if (!L->d_sync) {
+    if ((size_t)atenia::kEpSyncFlagWords * 4 + (size_t)L->cfg.ep_world * L->cfg.num_experts * 4 > atenia::kEpSyncBytes ||
+        L->cfg.ep_world > atenia::kEpMaxWorld)
+      return ATENIA_ERR_UNSUPPORTED;
+    ATENIA_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&L->d_sync), atenia::kEpSyncBytes));
+    ATENIA_CUDA_TRY(cudaMemset(L->d_sync, 0, atenia::kEpSyncBytes));
+    ATENIA_CUDA_TRY(cudaDeviceSynchronize());  // zero before any peer can store into it
+  }
+  ATENIA_CUDA_TRY(cudaIpcGetMemHandle(&b.sync, L->d_sync));
   b.recv_cap = L->recv_cap;
   b.rows_cap = L->rows_cap;
   b.d_model = L->cfg.d_model;
@@ -408,7 +546,9 @@ int atenia_moe_ep_ipc_import(AteniaMoeLayer* L, const void* blobs) {
   if (!L || !blobs) return ATENIA_ERR_NULL;
   const int G = L->cfg.ep_world, rank = L->cfg.ep_rank;
   if (G <= 1 || !atenia::ep_ready(L) || L->ep_replicated || L->ep_direct) return ATENIA_ERR_STATE;
+  if (!L->d_sync) return ATENIA_ERR_STATE;  // (allocated by this layer's export)
   std::vector<__nv_bfloat16*> px(G), py(G);
+  std::vector<uint32_t*> ps(G);
   // the sender bounds its stores by its own buffer sizes: they must be the sizes of every peer
   for (int p = 0; p < G; ++p) {
     IpcBlob b;
@@ -419,25 +559,32 @@ int atenia_moe_ep_ipc_import(AteniaMoeLayer* L, const void* blobs) {
     if (p == rank) {
       px[p] = L->recv_x;
       py[p] = L->y_perm;
+      ps[p] = L->d_sync;
       continue;
     }
     IpcBlob b;
     memcpy(&b, static_cast<const unsigned char*>(blobs) + (size_t)p * sizeof(IpcBlob), sizeof(b));
     void* a = nullptr;
     void* y = nullptr;
+    void* z = nullptr;
     cudaError_t e = cudaIpcOpenMemHandle(&a, b.recv_x, cudaIpcMemLazyEnablePeerAccess);
     if (e == cudaSuccess) {
       L->ipc_opened.push_back(a);
       e = cudaIpcOpenMemHandle(&y, b.y_perm, cudaIpcMemLazyEnablePeerAccess);
+    }
+    if (e == cudaSuccess) {
+      L->ipc_opened.push_back(y);
+      e = cudaIpcOpenMemHandle(&z, b.sync, cudaIpcMemLazyEnablePeerAccess);
     }
     if (e != cudaSuccess) {
       for (void* q : L->ipc_opened) cudaIpcCloseMemHandle(q);
       L->ipc_opened.clear();
       return (int)e;
     }
-    L->ipc_opened.push_back(y);
+    L->ipc_opened.push_back(z);
     px[p] = static_cast<__nv_bfloat16*>(a);
     py[p] = static_cast<__nv_bfloat16*>(y);
+    ps[p] = static_cast<uint32_t*>(z);
   }
   const size_t pb = (size_t)G * sizeof(void*);
   if (!L->d_peer_recv_x) ATENIA_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&L->d_peer_recv_x), pb));
@@ -447,6 +594,19 @@ int atenia_moe_ep_ipc_import(AteniaMoeLayer* L, const void* blobs) {
   if (!L->d_gemm_offsets)
     ATENIA_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&L->d_gemm_offsets), (size_t)(L->e_local + 1) * 4));
   if (!L->d_bar) ATENIA_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&L->d_bar), 4));
+  if (!L->d_peer_sync) ATENIA_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&L->d_peer_sync), pb));
+  if (!L->d_ep_state) ATENIA_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&L->d_ep_state), 16));
+  ATENIA_CUDA_TRY(cudaMemcpy(L->d_peer_sync, ps.data(), pb, cudaMemcpyHostToDevice));
+  ATENIA_CUDA_TRY(cudaMemset(L->d_ep_state, 0, 16));
+  {
+    // ATENIA_MOE_EP_FLAGS=1: counts and completion epochs through the peers' sync buffers instead of one
+    // all-gather and two one-word all-reduces per forward; ATENIA_MOE_EP_FLAG_TIMEOUT_MS bounds a wait
+    const char* f = std::getenv("ATENIA_MOE_EP_FLAGS");
+    L->ep_flags = f && std::atoi(f) != 0;
+    const char* t = std::getenv("ATENIA_MOE_EP_FLAG_TIMEOUT_MS");
+    const long ms = t ? std::atol(t) : 20000;
+    L->ep_flag_limit_ns = (uint64_t)(ms < 1 ? 1 : ms) * 1000000ull;
+  }
   ATENIA_CUDA_TRY(cudaMemcpy(L->d_peer_recv_x, px.data(), pb, cudaMemcpyHostToDevice));
   ATENIA_CUDA_TRY(cudaMemcpy(L->d_peer_y_perm, py.data(), pb, cudaMemcpyHostToDevice));
   ATENIA_CUDA_TRY(cudaMemset(L->d_bar, 0, 4));

@@ -112,6 +112,13 @@ struct AteniaMoeLayer {
   int32_t* d_src_base = nullptr;            // [e_local * world]
   int32_t* d_gemm_offsets = nullptr;        // [e_local + 1] expert-major group offsets of the receive buffer
   int32_t* d_bar = nullptr;                 // [1] operand of the barrier all-reduce
+  // flag synchronisation of the direct exchange (ATENIA_MOE_EP_FLAGS=1): counts and "my stores are done"
+  // epochs are stored into the peers' sync buffers instead of travelling through three collectives
+  bool ep_flags = false;
+  uint32_t* d_sync = nullptr;        // this rank's sync buffer (own 2 MiB allocation): epochs, then counts [world, E]
+  uint32_t** d_peer_sync = nullptr;  // device array [world]: every rank's sync buffer
+  uint32_t* d_ep_state = nullptr;    // private: [0] epoch of the current forward, [1],[2] finished-block counters, [3] gave up
+  uint64_t ep_flag_limit_ns = 20000000000ull;
 
   // the shared expert needs only the call's tokens: its GEMMs run on a second stream beside the routing
   // phase and, under expert parallelism, the exchanges (fork at the start, join before the combine)

@@ -392,7 +392,7 @@ int atenia_moe_destroy(AteniaMoeLayer* L) {
                   L->d_tm_down_sw, L->d_tm_shared_sw,
                   L->splitk_ws, L->splitk_ws_shared, L->d_escore, L->logits_ws, L->recv_x, L->recv_h, L->recv_y, L->d_counts_all,
                   L->d_group_offsets, L->d_peer_recv_x, L->d_peer_y_perm, L->d_dst_base, L->d_src_base,
-                  L->d_gemm_offsets, L->d_bar, L->sk_part, L->sk_gate, L->sk_counters, L->block_normed};
+                  L->d_gemm_offsets, L->d_bar, L->d_sync, L->d_peer_sync, L->d_ep_state, L->sk_part, L->sk_gate, L->sk_counters, L->block_normed};
   for (void* p : ptrs)
     if (p) cudaFree(p);
   for (void* p : L->owned) cudaFree(p);

@@ -8,14 +8,11 @@
 // f64 values of the bf16 / f32 operands, accumulation is f64, only the order of the additions
 // differs from the serial loop (last bits of a 53-bit sum, far below the rounding to f32).
 //
-// One CTA (8 warps) handles 8 MT tokens (MT = 4, 2 or 1 eight-token tiles, by batch size):
-//   * per chunk of 32 values of k the CTA stages x[8 MT, 32] and W_router[E, 32] as f64 in shared memory
-//     (row pitch 36 doubles: the 8 rows x 4 columns a fragment load touches fall in distinct banks);
-//     global loads of the next chunk are in flight during the arithmetic of the current one;
-//   * warps are arranged NW_N x NW_K: a warp owns NTW 8-expert tiles for all MT 8-token tiles and
-//     every NW_K-th k-step of the chunk; its accumulators are MT x NTW x 2 doubles per lane;
-//   * the k-slices are folded through shared memory in warp order (fixed), the bias joins the f64
-//     sum, logits are rounded to f32 and the warps route the tokens (route_one_warp).
+// Operands are streamed from global memory straight into the fragments: nothing is staged in shared
+// memory and the main loop has no barrier.  (An earlier form that staged x and the router matrix as f64
+// in shared memory, 32 tokens per CTA, was bound by its two block-wide barriers per 32-k chunk; measured
+// on B200 it was never faster -- DeepSeek-V2-Lite shape, whole forward: 512 tokens 0.310 vs 0.302 ms,
+// 2048 tokens 0.437 vs 0.426 ms, 8192 tokens 1.103 vs 1.100 ms -- and was removed.)
 #include <cstdlib>
 
 #include "route_warp.cuh"
@@ -23,30 +20,7 @@
 namespace atenia {
 namespace {
 
-constexpr int kDW = 8;         // warps per CTA
-constexpr int kDKC = 32;       // k values per chunk
-constexpr int kDLD = kDKC + 4; // shared-memory row pitch in doubles
-
-// MT: 8-token tiles per CTA (kDTok = 8 MT tokens).  Large batches take 4 (an expert fragment feeds four
-// products); smaller ones take 2 or 1 so that the grid still covers the SMs.
-template <int E_T, int MT>
-struct DmmaCfg {
-  static constexpr int kDTok = 8 * MT;
-  static constexpr int NT = E_T / 8;               // 8-expert tiles
-  static constexpr int NW_N = NT < kDW ? NT : kDW; // warps across expert tiles
-  static constexpr int NW_K = kDW / NW_N;          // warps across k-steps
-  static constexpr int NTW = NT / NW_N;            // expert tiles per warp
-  static constexpr int kXs = kDTok * kDLD * 8;
-  static constexpr int kWs = E_T * kDLD * 8;
-  static constexpr int kLoop = kXs + kWs;
-  static constexpr int kAcc = kDTok * (E_T + 1) * 8;
-  static constexpr int kLg = kDTok * E_T * 4;
-  static constexpr int kExps = kDW * E_T * 8;
-  static constexpr int kGate = kDW * kDTok * 8;
-  static constexpr int kSel = kDTok * kMaxK * 8;
-  static constexpr int kTail = kAcc + kLg + kExps + kGate + kSel;
-  static constexpr int kBytes = kLoop > kTail ? kLoop : kTail;
-};
+constexpr int kDW = 8;  // warps per CTA
 
 // D[8x8] += A[8x4] * B[4x8].  Lane l holds A[l / 4][l % 4], B[l % 4][l / 4] and D[l / 4][2 (l % 4) + {0, 1}].
 __device__ __forceinline__ void dmma884(double (&c)[2], double a, double b) {
@@ -55,169 +29,8 @@ __device__ __forceinline__ void dmma884(double (&c)[2], double a, double b) {
                : "d"(a), "d"(b));
 }
 
-template <int E_T, int MT>
-__global__ void __launch_bounds__(kDW * 32) router_dmma_kernel(RouterArgs a) {
-  using C = DmmaCfg<E_T, MT>;
-  constexpr int NTW = C::NTW;
-  constexpr int kDTok = C::kDTok;
-  extern __shared__ __align__(16) unsigned char smem[];
-  // main-loop view
-  double (*xs)[kDLD] = reinterpret_cast<double (*)[kDLD]>(smem);
-  double (*ws)[kDLD] = reinterpret_cast<double (*)[kDLD]>(smem + C::kXs);
-  // tail view (after the last __syncthreads of the loop)
-  double (*acc_s)[E_T + 1] = reinterpret_cast<double (*)[E_T + 1]>(smem);
-  float (*lg_s)[E_T] = reinterpret_cast<float (*)[E_T]>(smem + C::kAcc);
-  double (*exps_s)[E_T] = reinterpret_cast<double (*)[E_T]>(smem + C::kAcc + C::kLg);
-  double (*gate_s)[kDTok] = reinterpret_cast<double (*)[kDTok]>(smem + C::kAcc + C::kLg + C::kExps);
-  int32_t (*idx_s)[kMaxK] = reinterpret_cast<int32_t (*)[kMaxK]>(smem + C::kAcc + C::kLg + C::kExps + C::kGate);
-  float (*w_s)[kMaxK] = reinterpret_cast<float (*)[kMaxK]>(smem + C::kAcc + C::kLg + C::kExps + C::kGate +
-                                                          kDTok * kMaxK * 4);
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t0 = blockIdx.x * kDTok;
-  const int d = a.d, E = a.E;
-  const int ngrp = warp % C::NW_N, kslice = warp / C::NW_N;
-  const int frow = lane >> 2, fcol = lane & 3;
-
-  double acc[MT][NTW][2];
-#pragma unroll
-  for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-    for (int j = 0; j < NTW; ++j) acc[mt][j][0] = acc[mt][j][1] = 0.0;
-  double gacc = 0.0;  // lane t of warp w: gate dot product of token t over the k values 4w..4w+3 of each chunk
-
-  // staging: thread i moves four consecutive k values of token i / 8 (x) and of expert rows
-  // i / 8 + 32 r (W); eight neighbouring threads cover 32 consecutive k of one row
-  constexpr int WV = (E_T + 31) / 32;
-  const int s_row = threadIdx.x >> 3, s_k = (threadIdx.x & 7) * 4;
-  uint4 xq;
-  float4 wq[WV];
-  auto fetch = [&](int k0) {
-    const int kk = k0 + s_k, tg = t0 + s_row;
-    xq = make_uint4(0, 0, 0, 0);
-    if (s_row < kDTok && tg < a.T && kk < d) {  // d is a multiple of 16: a group of 4 is all in or all out
-      if (a.x_is_f32) {
-        xq = *reinterpret_cast<const uint4*>(static_cast<const float*>(a.x) + (size_t)tg * d + kk);
-      } else {
-        const uint2 u = *reinterpret_cast<const uint2*>(static_cast<const __nv_bfloat16*>(a.x) + (size_t)tg * d + kk);
-        xq.x = u.x;
-        xq.y = u.y;
-      }
-    }
-#pragma unroll
-    for (int r = 0; r < WV; ++r) {
-      const int e = s_row + 32 * r;
-      wq[r] = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (e < E && kk < d) wq[r] = __ldg(reinterpret_cast<const float4*>(a.w_router + (size_t)e * d + kk));
-    }
-  };
-  fetch(0);
-  for (int k0 = 0; k0 < d; k0 += kDKC) {
-    __syncthreads();
-    {
-      float v[4];
-      if (a.x_is_f32) {
-        v[0] = __uint_as_float(xq.x); v[1] = __uint_as_float(xq.y);
-        v[2] = __uint_as_float(xq.z); v[3] = __uint_as_float(xq.w);
-      } else {
-        v[0] = bf16lo(xq.x); v[1] = bf16hi(xq.x); v[2] = bf16lo(xq.y); v[3] = bf16hi(xq.y);
-      }
-      if (s_row < kDTok) {
-        double2* px = reinterpret_cast<double2*>(&xs[s_row][s_k]);
-        px[0] = make_double2((double)v[0], (double)v[1]);
-        px[1] = make_double2((double)v[2], (double)v[3]);
-      }
-#pragma unroll
-      for (int r = 0; r < WV; ++r) {
-        const int e = s_row + 32 * r;
-        if (e < E_T) {
-          double2* pw = reinterpret_cast<double2*>(&ws[e][s_k]);
-          pw[0] = make_double2((double)wq[r].x, (double)wq[r].y);
-          pw[1] = make_double2((double)wq[r].z, (double)wq[r].w);
-        }
-      }
-    }
-    __syncthreads();
-    if (k0 + kDKC < d) fetch(k0 + kDKC);
-#pragma unroll
-    for (int i = 0; i < kDKC / 4 / C::NW_K; ++i) {
-      const int kk = (kslice + i * C::NW_K) * 4 + fcol;
-      double af[MT];
-#pragma unroll
-      for (int mt = 0; mt < MT; ++mt) af[mt] = xs[mt * 8 + frow][kk];
-#pragma unroll
-      for (int j = 0; j < NTW; ++j) {
-        const double bf = ws[(ngrp * NTW + j) * 8 + frow][kk];
-#pragma unroll
-        for (int mt = 0; mt < MT; ++mt) dmma884(acc[mt][j], af[mt], bf);
-      }
-    }
-    if (a.gate_vec) {
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        const int kc = warp * 4 + c;
-        if (lane < kDTok && k0 + kc < d) gacc = fma((double)__ldg(a.gate_vec + k0 + kc), xs[lane][kc], gacc);
-      }
-    }
-  }
-  __syncthreads();  // the loop's shared-memory view is dead from here on
-  // fold the k-slices, one after the other; slice 0 initialises
-  for (int ksl = 0; ksl < C::NW_K; ++ksl) {
-    if (kslice == ksl) {
-#pragma unroll
-      for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-        for (int j = 0; j < NTW; ++j)
-#pragma unroll
-          for (int i = 0; i < 2; ++i) {
-            const int t = mt * 8 + frow, e = (ngrp * NTW + j) * 8 + fcol * 2 + i;
-            if (e < E) acc_s[t][e] = (ksl == 0 ? 0.0 : acc_s[t][e]) + acc[mt][j][i];
-          }
-    }
-    __syncthreads();
-  }
-  if (a.gate_vec && lane < kDTok) gate_s[warp][lane] = gacc;
-  // logits: bias joins the f64 sum before the rounding to f32
-  for (int i = threadIdx.x; i < kDTok * E; i += blockDim.x) {
-    const int t = i / E, e = i - t * E;
-    double v = acc_s[t][e];
-    if (a.bias) v += (double)a.bias[e];
-    const float f = (float)v;
-    lg_s[t][e] = f;
-    const int tg = t0 + t;
-    if (a.logits && tg < a.T) a.logits[(size_t)tg * E + e] = f;
-  }
-  __syncthreads();
-  if (a.gate_vec && a.gate_scale && threadIdx.x < kDTok) {
-    const int t = threadIdx.x, tg = t0 + t;
-    double v = 0.0;
-    for (int w = 0; w < kDW; ++w) v += gate_s[w][t];
-    if (tg < a.T) a.gate_scale[tg] = (float)(1.0 / (1.0 + exp(-v)));
-  }
-  for (int t = warp; t < kDTok; t += kDW) {
-    const int tg = t0 + t;
-    if (tg >= a.T) continue;
-    int rc = route_one_warp<(E_T + 31) / 32>(lg_s[t], E, a.k, a.renormalize, lane, idx_s[t], w_s[t], exps_s[warp]);
-    if (rc) {
-      if (lane == 0) report_error(a.err, rc, 1003);
-      if (lane < a.k) {  // keep downstream kernels in bounds
-        idx_s[t][lane] = lane;
-        w_s[t][lane] = 0.f;
-      }
-    }
-    __syncwarp();
-    if (lane < a.k) {
-      a.topk_idx[(size_t)tg * a.k + lane] = idx_s[t][lane];
-      a.topk_w[(size_t)tg * a.k + lane] = w_s[t][lane];
-    }
-  }
-}
-
-// ---- operands streamed from global memory straight into fragments (few experts, or few tokens) ------
-// With one or two 8-expert tiles, or with a batch too small to fill the GPU with 32-token CTAs, the staged
-// kernel above is bound by its two block-wide barriers per 32-k chunk and by the latency of one chunk in
-// flight.  Here nothing is staged and the main loop has no barrier.  The eight warps of a CTA are
-// arranged NW_N x NW_K as above: a warp owns NTW 8-expert tiles and the k-range [kslice KW, (kslice+1) KW)
+// The eight warps of a CTA are arranged NW_N x NW_K (NW_N = min(8, E_T / 8) across the 8-expert tiles,
+// the rest across k): a warp owns NTW 8-expert tiles and the k-range [kslice KW, (kslice+1) KW)
 // of the dot products of the CTA's 8 MT tokens.  The summation index of an m8n8k4 product is free to be
 // permuted as long as A and B agree, so lane (r, c) = (lane / 4, lane % 4) loads EIGHT consecutive k of
 // token row r (16 bytes of bf16) and of expert row r of each of its tiles (32 bytes of f32) at
@@ -225,7 +38,7 @@ __global__ void __launch_bounds__(kDW * 32) router_dmma_kernel(RouterArgs a) {
 // cover 32 consecutive k, global loads are whole sectors (the warps of one k-slice read the same token
 // vectors: the first brings them into L1).  The vectors of the next 32 k are in flight while the current
 // ones are multiplied.  Partial sums of the k-slices are added through shared memory in slice order
-// (fixed), then bias, rounding and routing as above.
+// (fixed), then the bias, the rounding to f32 and the routing of each token by one warp (route_one_warp).
 template <int E_T, int MT>
 __global__ void __launch_bounds__(kDW * 32) router_dmma_direct_kernel(RouterArgs a, int kw) {
   constexpr int NT = E_T / 8;
@@ -411,50 +224,17 @@ int launch_direct(const RouterArgs& a, cudaStream_t s) {
   return (int)cudaGetLastError();
 }
 
-template <int E_T, int MT>
-int launch_mt(const RouterArgs& a, cudaStream_t s) {
-  using C = DmmaCfg<E_T, MT>;
-  static bool attr_set[kMaxDevices] = {};
-  if (C::kBytes > 48 * 1024 && first_use_on_current_device(attr_set)) {
-    ATENIA_CUDA_TRY(cudaFuncSetAttribute(router_dmma_kernel<E_T, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kBytes));
-  }
-  router_dmma_kernel<E_T, MT><<<(a.T + C::kDTok - 1) / C::kDTok, kDW * 32, C::kBytes, s>>>(a);
-  return (int)cudaGetLastError();
-}
-
-template <int E_T>
-int launch_one(const RouterArgs& a, cudaStream_t s) {
-  // tokens per CTA by batch size: several CTAs per SM hide the latency of a CTA's chunk pipeline, so
-  // the grid should cover the SMs a few times over (ATENIA_MOE_ROUTER_MT = 1 | 2 | 4 pins it: A/B runs)
-  static const int pinned = [] {
-    const char* e = std::getenv("ATENIA_MOE_ROUTER_MT");
-    return e ? std::atoi(e) : 0;
-  }();
-  const int mt = pinned == 1 || pinned == 2 || pinned == 4 ? pinned : (a.T >= 4096 ? 4 : a.T >= 1024 ? 2 : 1);
-  if (mt == 4) return launch_mt<E_T, 4>(a, s);
-  if (mt == 2) return launch_mt<E_T, 2>(a, s);
-  return launch_mt<E_T, 1>(a, s);
-}
-
 }  // namespace
 
 int launch_router_dmma(const RouterArgs& a, cudaStream_t s) {
   if (a.T <= 0) return ATENIA_OK;
   if (a.k > kMaxK || a.E > 128 || a.d % 16 != 0) return ATENIA_ERR_UNSUPPORTED;
   int rc;
-  // few experts: always the barrier-free kernel; many experts: the barrier-free kernel while the batch
-  // is too small to fill the GPU with the staged kernel's 32-token CTAs (ATENIA_MOE_ROUTER_DIRECT_MAX
-  // moves the hand-over: A/B runs)
-  static const int direct_max = [] {
-    const char* e = std::getenv("ATENIA_MOE_ROUTER_DIRECT_MAX");
-    return e ? std::atoi(e) : 4095;
-  }();
-  const bool direct = a.T <= direct_max;
   if (a.E <= 8) rc = launch_direct<8>(a, s);
   else if (a.E <= 16) rc = launch_direct<16>(a, s);
-  else if (a.E <= 32) rc = direct ? launch_direct<32>(a, s) : launch_one<32>(a, s);
-  else if (a.E <= 64) rc = direct ? launch_direct<64>(a, s) : launch_one<64>(a, s);
-  else rc = direct ? launch_direct<128>(a, s) : launch_one<128>(a, s);
+  else if (a.E <= 32) rc = launch_direct<32>(a, s);
+  else if (a.E <= 64) rc = launch_direct<64>(a, s);
+  else rc = launch_direct<128>(a, s);
   count_launch();
   return rc;
 }

@@ -448,7 +448,10 @@ def measure_record(grp, name, T_total, args, peaks, seed=2, direct=False):
         rows = [r[0] for r in per_rank]
         rec["rows_received_per_rank"] = {"max": max(rows), "mean": sum(rows) / len(rows),
                                          "imbalance_max_over_mean": max(rows) / max(sum(rows) / len(rows), 1.0)}
-        rec["exchange"] = "peer stores over NVLink (direct)" if direct else "NCCL send/recv groups"
+        flags = os.environ.get("ATENIA_MOE_EP_FLAGS", "0") not in ("", "0")
+        rec["exchange"] = (("peer stores over NVLink (direct), " + ("ordered by flags in peer memory" if flags
+                                                                       else "NCCL for counts and ordering"))
+                           if direct else "NCCL send/recv groups")
         # the same batch on one GPU, timed by rank 0 in this very run (the others wait at the barrier)
         single = None
         if grp.rank == 0:
@@ -584,8 +587,10 @@ def main():
         layer = synth.build_layer(shape, w, max_tokens=T)
     if args.gpus > 1:
         if direct:
+            flags = os.environ.get("ATENIA_MOE_EP_FLAGS", "0") not in ("", "0")
             config["parallelism"] = (f"expert-parallel ep{args.gpus}, rows stored peer to peer over NVLink, "
-                                     "NCCL for counts and ordering")
+                                     + ("counts and ordering by flags in peer memory" if flags
+                                        else "NCCL for counts and ordering"))
     out = torch.empty_like(x)
     fwd = lambda: layer.forward(x, out=out)
 

@@ -4,7 +4,10 @@ Both ranks run one expert-parallel forward.  Then rank 1 stays out of the next o
 nothing of its own is in flight) and rank 0 calls it alone.  Rank 0's collectives cannot complete, so
 its bounded host wait must run out (ATENIA_MOE_EP_TIMEOUT_S), abort the communicator and return
 ATENIA_ERR_NCCL; afterwards the layer reports ATENIA_ERR_STATE instead of hanging.  No GPU fault is
-involved: the waiting NCCL kernel is ended by ncclCommAbort."""
+involved: the waiting NCCL kernel is ended by ncclCommAbort.  With layout "flags" (direct exchange,
+ATENIA_MOE_EP_FLAGS=1) there is no collective: rank 0's kernels poll flags that rank 1 never sets, the
+bounded poll runs out (ATENIA_MOE_EP_FLAG_TIMEOUT_MS), the forward reports ATENIA_ERR_DEVICE_TIMEOUT and
+the next one ATENIA_ERR_STATE; the kernels return normally and the context stays usable."""
 import ctypes as C
 import os
 import sys
@@ -25,7 +28,7 @@ def main():
     from ateniaengine_b200 import _lib, synth
     from ateniaengine_b200._lib import AteniaError
 
-    layout = sys.argv[1]  # sharded | replicated
+    layout = sys.argv[1]  # sharded | replicated | flags (direct exchange synchronised by flags in peer memory)
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
@@ -45,6 +48,11 @@ def main():
     layer.ep_init(bytes(idt.numpy().tobytes()))
     if layout == "replicated":
         layer.ep_replicated_tokens(True)
+    if layout == "flags":
+        mine = torch.frombuffer(bytearray(layer.ep_ipc_export()), dtype=torch.uint8).clone()
+        blobs = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(blobs, mine)
+        layer.ep_ipc_import(b"".join(bytes(b.numpy().tobytes()) for b in blobs))
     out = layer.forward(x, out_dtype=torch.float32, sync=True)  # a healthy step on both ranks
     assert torch.isfinite(out).all()
     dist.barrier()
@@ -62,7 +70,8 @@ def main():
             layer.forward(x, out_dtype=torch.float32, sync=True)
         except AteniaError as e:
             after = e.status
-        ok = status == -10 and after == -4 and waited < 60.0
+        # (with flags the wait that runs out is a kernel's bounded poll: ATENIA_ERR_DEVICE_TIMEOUT)
+        ok = status == (-8 if layout == "flags" else -10) and after == -4 and waited < 60.0
         print(f"{layout}: status={status} after={after} waited={waited:.1f}s ok={ok}", flush=True)
     dist.barrier()  # rank 1 has waited here, idle, all along
     os._exit(0 if ok else 1)

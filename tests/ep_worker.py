@@ -55,6 +55,11 @@ def main():
     for _ in range(2):
         outs.append(layer.forward(x, out_dtype=torch.float32, sync=True))
     assert torch.equal(outs[0], outs[1])
+    # a run of forwards with nothing between them (the exchange buffers of one are reused by the next)
+    for _ in range(12):
+        last = layer.forward(x, out_dtype=torch.float32, sync=False)
+    layer.check()
+    assert torch.equal(outs[0], last)
     sizes = [T + 5 * r for r in range(world)]
     xs = [torch.empty((n, shape.d_model), dtype=x.dtype, device=dev) for n in sizes]
     ys = [torch.empty((n, shape.d_model), dtype=torch.float32, device=dev) for n in sizes]

@@ -12,13 +12,17 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-@pytest.mark.parametrize("layout", ["sharded", "replicated"])
+@pytest.mark.parametrize("layout", ["sharded", "replicated", "flags"])
 def test_missing_peer_ends_with_an_error_status(layout):
     n = torch.cuda.device_count() if torch.cuda.is_available() else 0
     if n < 2:
         pytest.skip("needs at least 2 GPUs")
+    if layout == "flags" and not os.environ.get("ATENIA_TEST_EP_FLAGS"):
+        pytest.skip("flag-synchronised exchange: opt-in until it has run on hardware")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", ATENIA_MOE_EP_TIMEOUT_S="4")
-    port = 29691 + (0 if layout == "sharded" else 5)
+    if layout == "flags":
+        env.update(ATENIA_MOE_EP_FLAGS="1", ATENIA_MOE_EP_FLAG_TIMEOUT_MS="1500")
+    port = 29691 + {"sharded": 0, "replicated": 5, "flags": 9}[layout]
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
            "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", "ep_timeout_worker.py"), layout]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env)
