@@ -680,6 +680,9 @@ def main():
         else:
             records["deepseek_v2_lite_ep"] = measure_record(grp, "deepseek_v2_lite", 8192, args, peaks, seed=4,
                                                             direct=direct)
+            if args.gpus == 2:  # the Qwen-shaped layer is named for 1 and 2 GPUs (60 experts: 30 per rank)
+                records["qwen15_moe_2048_ep"] = measure_record(grp, "qwen_moe", 2048, args, peaks, seed=3,
+                                                               direct=direct)
 
     # further windows of exactly K steps of the headline workload, back to back, after everything else:
     # the first window above is a burst after an idle moment, the median of these is what a loaded GPU
