@@ -18,7 +18,8 @@ struct AteniaMoeLayer {
   int n_groups = 0;  // GEMM groups per launch: e_local (single GPU) or ep_world * e_local
   bool weights_set = false;
   bool use_check_gemm = false;  // diagnostic: CUDA-core contraction instead of tcgen05
-  bool use_gemv = true;         // calls of at most four rows: the matrix-vector kernel (decode_gemv.cu)
+  bool use_gemv = true;         // small calls take the matrix-vector kernel (decode_gemv.cu)
+  int gemv_rows = 2;   // calls of at most this many rows take it
   bool timing = false;
   const float* residual = nullptr;  // set by a stack around one forward: added by the combine kernel
   float* block_normed = nullptr;    // [max_tokens, d] f32, allocated by the first atenia_moe_block_forward

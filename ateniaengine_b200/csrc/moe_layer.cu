@@ -68,7 +68,7 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
   const bool pairs = !q && !dec && (L->pair_mode == 1 || (L->pair_mode == 0 && max_rows >= 512 * num_groups));
   // a call of at most two rows in all (decode at batch 1) is a stream over the touched experts' weights:
   // the CUDA-core matrix-vector kernel (ATENIA_MOE_GEMV=0 keeps the tensor-core kernels: A/B runs)
-  const bool gemv = L->use_gemv && max_rows <= kGemvMaxRows && !L->use_check_gemm;
+  const bool gemv = L->use_gemv && max_rows <= L->gemv_rows && !L->use_check_gemm;
   if (L->timing) cudaEventRecord(L->ev[0], s);
   if (L->use_check_gemm || gemv) {
     GroupedGemmCheckArgs k1{a_ptr, L->d_p_gate, L->d_p_up, q ? 1 : 0, q ? L->d_sc_gate : nullptr,
@@ -147,7 +147,7 @@ int run_shared_gemms(AteniaMoeLayer* L, const __nv_bfloat16* xb, int T, cudaStre
   const bool m256 = q && T >= 256 && L->w8_mode != 1 && L->w8_mode != 2 && !L->use_check_gemm;
   const bool tmem = q && !m256 && (L->w8_mode == 1 || (L->w8_mode != 2 && T < 256));
   const bool pairs = !q && (L->pair_mode == 1 || (L->pair_mode == 0 && T >= 512));
-  const bool gemv = L->use_gemv && T <= kGemvMaxRows && !L->use_check_gemm;
+  const bool gemv = L->use_gemv && T <= L->gemv_rows && !L->use_check_gemm;
   if (L->timing) cudaEventRecord(L->ev[3], s);
   if (L->use_check_gemm || gemv) {
     GroupedGemmCheckArgs k1{xb, L->d_p_shared, L->d_p_shared + 1, q ? 1 : 0, q ? L->d_sc_shared : nullptr,
@@ -245,6 +245,12 @@ int atenia_moe_create(const AteniaMoeConfig* cfg, AteniaMoeLayer** out) {
   L->pair_mode = std::getenv("ATENIA_MOE_PAIR_MODE") ? std::atoi(std::getenv("ATENIA_MOE_PAIR_MODE")) : 0;
   L->shared_aside = !(std::getenv("ATENIA_MOE_SHARED_ASIDE") && std::atoi(std::getenv("ATENIA_MOE_SHARED_ASIDE")) == 0);
   L->use_gemv = !(std::getenv("ATENIA_MOE_GEMV") && std::atoi(std::getenv("ATENIA_MOE_GEMV")) == 0);
+  {
+    // ATENIA_MOE_GEMV_ROWS moves the hand-over to the tensor-core kernels (1 .. 4 rows: A/B runs)
+    const char* e = std::getenv("ATENIA_MOE_GEMV_ROWS");
+    const int r = e ? std::atoi(e) : kGemvMaxRows;
+    L->gemv_rows = r < 1 ? 1 : (r > 4 ? 4 : r);
+  }
   // Router kernel: by default the split-k kernel for batches of at most 128 tokens (many CTAs share one
   // token block's dot products), the f64 tensor-core kernel for 32 experts and more, the CUDA-core
   // kernel otherwise.  ATENIA_MOE_ROUTER = scalar | dmma | splitk pins one (tests, A/B runs); a pinned

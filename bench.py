@@ -386,17 +386,22 @@ class EpGroup:
             self.dist.destroy_process_group()
 
 
-def time_steps(grp, fn, steps):
+def time_steps(grp, fn, steps, host=None):
     """ms per step of `steps` calls of fn, CUDA events on the current stream, barrier + device sync on
-    both sides, max over ranks."""
+    both sides, max over ranks.  `host` (a list) receives this rank's wall-clock ms per step spent ISSUING
+    the calls: when it is close to the device figure the step is bound by the host's launch rate."""
     import torch
     grp.sync()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
+    t0 = time.perf_counter()
     for _ in range(steps):
         fn()
+    t1 = time.perf_counter()
     e1.record()
     grp.sync()
+    if host is not None:
+        host.append((t1 - t0) * 1e3 / steps)
     return grp.max_over_ranks(e0.elapsed_time(e1) / steps)
 
 
@@ -423,7 +428,8 @@ def measure_record(grp, name, T_total, args, peaks, seed=2, direct=False):
         fn()
     layer.check()
     layer.enable_timing(True)
-    ms = time_steps(grp, fn, args.steps)
+    host = []
+    ms = time_steps(grp, fn, args.steps, host)
     layer.check()
     phases = [layer.last_phase_ms(i) for i in range(6)]
     recv_rows = layer.last_recv_rows() if G > 1 else T * shape.top_k
@@ -435,7 +441,8 @@ def measure_record(grp, name, T_total, args, peaks, seed=2, direct=False):
                        f"top_k={shape.top_k} shared_d_ff={shape.shared_d_ff}",
            "tokens_per_step": T * G, "n_gpus": G, "scaling": "strong" if G > 1 else "single GPU",
            "dtype": "int8 weights, bf16 activations (W8A16)" if shape.int8 else "bf16",
-           "ms_per_step": ms, "tokens_per_s": T * G / (ms * 1e-3)}
+           "ms_per_step": ms, "tokens_per_s": T * G / (ms * 1e-3),
+           "host_issue_ms_per_step": grp.max_over_ranks(host[0])}
     rl = layer_roofline(shape, T * G, shape.num_experts if G > 1 else touched, peaks, shape.int8)
     rec["roofline"] = {"bound": rl["bound"], "target_ms_one_gpu": rl["target_ms"], "t_tensor_ms": rl["t_tensor_ms"],
                        "t_hbm_ms": rl["t_hbm_ms"], "frac": rl["target_ms"] / G / ms,
@@ -476,9 +483,33 @@ def measure_record(grp, name, T_total, args, peaks, seed=2, direct=False):
             full.close()
             del wf, xf, of
         grp.sync()
+        # the same forward replayed as one CUDA graph (a one-layer stack on a side stream): the direct
+        # exchange reads nothing on the host, so kernels, collectives and the second stream's fork and
+        # join are all captured, and the host issues one launch per step
+        gms = None
+        if direct:
+            from ateniaengine_b200.moe import RealMoeStack
+            st1 = RealMoeStack([layer], residual=False)
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                gfn = lambda: st1.forward(x, out=out)
+                for _ in range(max(args.warmup, 3)):  # eager, capture, replays
+                    gfn()
+                layer.check()
+                gms = time_steps(grp, gfn, args.steps)
+                layer.check()
+            torch.cuda.current_stream().wait_stream(side)
+            st1.close()
         if grp.rank == 0:
             rec["one_gpu_ms_same_run"] = single
             rec["speedup_vs_one_gpu_same_run"] = single / ms
+            if gms is not None:
+                rec["graph_replay"] = {"ms_per_step": gms, "tokens_per_s": T * G / (gms * 1e-3),
+                                       "speedup_vs_one_gpu_same_run": single / gms,
+                                       "frac": rl["target_ms"] / G / gms,
+                                       "note": "the same forward replayed as one CUDA graph through a "
+                                               "one-layer atenia_moe_stack: one host launch per step"}
     layer.close()
     del w, x, out
     torch.cuda.empty_cache()
