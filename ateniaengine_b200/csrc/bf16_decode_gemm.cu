@@ -1,4 +1,5 @@
-// Grouped expert GEMM for bf16 weights at decode sizes (groups of at most 128 rows), sm_100a.
+// Grouped expert GEMM at decode sizes, sm_100a: bf16 weights (groups of at most 128 rows) and INT8
+// weights multiplied as integers (calls of at most 128 rows).
 //
 // At a batch of a few tokens the work is streaming the touched experts' weights once; what decides
 // the speed is whether every SM streams the same number of bytes.  The 128-row-tile kernels of
@@ -19,6 +20,20 @@
 //               main loop of the next
 //   warps     : 0 TMA, 1 MMA + TMEM alloc, 4..11 epilogue (two warps per TMEM lane quarter)
 // All waits are bounded as in grouped_gemm.cu.
+//
+// INT8 form (template parameter I8).  Widening int8 codes to bf16 costs two to three instructions per
+// weight, and at decode sizes those instructions, not HBM, set the pace of the widening kernels (w8_gemm.cu,
+// decode_gemv.cu: 44 - 52 % of the copy rate).  Here no weight is ever widened: the MMA is
+// tcgen05.mma.kind::i8 on the codes as they lie in memory, and the bf16 ACTIVATIONS are turned into
+// integers instead -- a handful of rows per call.  quantize_digits_kernel writes every token row as four
+// planes of balanced base-128 digits of X = rint(x 2^(26 - e)), e = the row's exponent (|x| < 2^e):
+//   x = 2^(e - 26) (d0 + 128 d1 + 128^2 d2 + 128^3 d3),   d_i in [-64, 63]
+// (exact for every element within 2^-19 of the row's largest; below that the element is rounded to
+// 2^-27 of the largest, far finer than the bf16 product it replaces).  The four planes of a token tile
+// are four column blocks of ONE MMA (N = 4 x tokens rounded to 16), the int32 accumulators are exact,
+// and the epilogue folds them, v = a0 + 128 (a1 + 128 (a2 + 128 a3)), and multiplies by the weight
+// row's scale and the token's 2^(e - 26).  Per k-block of 128 codes a stage holds two 16 KiB weight tiles
+// and at most 16 KiB of digits; token tiles are 32 rows.
 #include "tc_common.cuh"
 
 namespace atenia {
@@ -50,13 +65,29 @@ struct __align__(8) BarriersDec {
 __device__ __forceinline__ uint32_t idesc_dec(int n) {
   return (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(n >> 3) << 17) | (uint32_t(DROWS >> 4) << 24);
 }
+// The same for kind::i8: D s32 (format 2), A = B = signed 8-bit (format 1).
+__device__ __forceinline__ uint32_t idesc_dec_i8(int n) {
+  return (2u << 4) | (1u << 7) | (1u << 10) | (uint32_t(n >> 3) << 17) | (uint32_t(DROWS >> 4) << 24);
+}
+__device__ __forceinline__ void tc_mma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+constexpr int ITOK = 32;        // INT8 form: token tile (four digit planes = 128 MMA columns)
+constexpr int IBK = 128;        // INT8 form: codes per k-block (128 bytes of a row, as for bf16)
+constexpr int kDigitPlanes = 4;
 
 // Work of one CTA: whole tiles dealt round-robin, or (stream-K) one contiguous span of the flattened
 // (tile, k-block) list.  A span has at most one partial piece at its start (slot 0) and one at its end
 // (slot 1).
 struct DecPieces {
   bool splitk;
-  int num_kb, n_tiles, num_groups, bn_out;
+  int num_kb, n_tiles, num_groups, bn_out, tile_rows;
   const int32_t* off;
   TileCursor cur;
   int tile, stride;
@@ -64,8 +95,10 @@ struct DecPieces {
   TileCoord tc;
   int kb0, nkb, slot;  // slot -1: the piece is a whole tile
 
-  __device__ void init(bool sk, int num_kb_, int n_tiles_, int num_groups_, int bn_out_, const int32_t* off_) {
+  __device__ void init(bool sk, int num_kb_, int n_tiles_, int num_groups_, int bn_out_, const int32_t* off_,
+                       int tile_rows_) {
     splitk = sk;
+    tile_rows = tile_rows_;
     num_kb = num_kb_;
     n_tiles = n_tiles_;
     num_groups = num_groups_;
@@ -73,14 +106,14 @@ struct DecPieces {
     off = off_;
     cur.group = 0;
     cur.base = 0;
-    if (num_groups > 0) cursor_load(cur, off);
+    if (num_groups > 0) cursor_load(cur, off, tile_rows);
     tile = blockIdx.x;
     stride = gridDim.x;
     g = g0 = g_end = 0;
     if (splitk) {
       long long total_tiles = 0;
       for (int gi = 0; gi < num_groups; ++gi)
-        total_tiles += (long long)((off[gi + 1] - off[gi] + BM - 1) / BM) * n_tiles;
+        total_tiles += (long long)((off[gi + 1] - off[gi] + tile_rows - 1) / tile_rows) * n_tiles;
       const long long total = total_tiles * num_kb;
       const long long span = (total + gridDim.x - 1) / gridDim.x;
       g0 = g = (long long)blockIdx.x * span;
@@ -90,7 +123,7 @@ struct DecPieces {
   __device__ bool next() {
     if (num_groups <= 0) return false;
     if (!splitk) {
-      if (!cursor_seek(cur, tile, n_tiles, num_groups, off, tc, bn_out)) return false;
+      if (!cursor_seek(cur, tile, n_tiles, num_groups, off, tc, bn_out, tile_rows)) return false;
       tile += stride;
       kb0 = 0;
       nkb = num_kb;
@@ -102,25 +135,32 @@ struct DecPieces {
     kb0 = (int)(g - (long long)t * num_kb);
     const long long left = g_end - g;
     nkb = (num_kb - kb0) < left ? (num_kb - kb0) : (int)left;
-    if (!cursor_seek(cur, t, n_tiles, num_groups, off, tc, bn_out)) return false;
+    if (!cursor_seek(cur, t, n_tiles, num_groups, off, tc, bn_out, tile_rows)) return false;
     slot = (nkb == num_kb) ? -1 : (g == g0 ? 0 : 1);
     g += nkb;
     return true;
   }
   __device__ int rows() const {
     const int r = tc.row_end - tc.row0;
-    return r > DTN ? DTN : r;
+    return r > tile_rows ? tile_rows : r;
   }
 };
 
-template <int MODE>
+// I8: tmap_x is the digit-plane map (uint8, box {128, 16}; plane p of row r at row p * plane_rows + r),
+// tmap_w0 / tmap_w1 are int8 maps with box {128, 128} and the 128-byte swizzle, scale0 / scale1 the
+// weight rows' scales per group and tok_scale the token rows' 2^(e - 26).
+template <int MODE, bool I8>
 __global__ void __launch_bounds__(D_THREADS, 1)
-grouped_gemm_bf16_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const CUtensorMap* __restrict__ tmap_w0,
-                                const CUtensorMap* __restrict__ tmap_w1, const int32_t* __restrict__ group_offsets,
-                                int num_groups, int N, int K, __nv_bfloat16* __restrict__ out, DeviceError* err,
-                                int splitk, float* __restrict__ ws) {
+grouped_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const CUtensorMap* __restrict__ tmap_w0,
+                           const CUtensorMap* __restrict__ tmap_w1, const int32_t* __restrict__ group_offsets,
+                           int num_groups, int N, int K, __nv_bfloat16* __restrict__ out, DeviceError* err,
+                           int splitk, float* __restrict__ ws, const float* const* __restrict__ scale0,
+                           const float* const* __restrict__ scale1, const float* __restrict__ tok_scale,
+                           int plane_rows) {
   extern __shared__ uint8_t smem_raw[];
   constexpr int BN_OUT = (MODE == kSwiGLU) ? DROWS : 2 * DROWS;
+  constexpr int BKE = I8 ? IBK : BK;        // k elements per k-block
+  constexpr int TROWS = I8 ? ITOK : DTN;    // token rows per tile
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
   BarriersDec* bars = reinterpret_cast<BarriersDec*>(smem_aligned + D_STAGES * D_STAGE_BYTES);
@@ -128,7 +168,7 @@ grouped_gemm_bf16_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, cons
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int num_kb = (K + BK - 1) / BK;
+  const int num_kb = (K + BKE - 1) / BKE;
   const int n_tiles = (N + BN_OUT - 1) / BN_OUT;
 
   if (threadIdx.x == 0) {
@@ -156,7 +196,7 @@ grouped_gemm_bf16_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, cons
   const uint32_t tmem_base = bars->tmem_base;
 
   DecPieces it;
-  it.init(splitk != 0, num_kb, n_tiles, num_groups, BN_OUT, group_offsets);
+  it.init(splitk != 0, num_kb, n_tiles, num_groups, BN_OUT, group_offsets, TROWS);
   const TileCoord& tc = it.tc;
 
   if (warp == 0) {
@@ -186,10 +226,22 @@ grouped_gemm_bf16_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, cons
           }
           const uint32_t full = smem_u32(&bars->full[stage]);
           const uint32_t sw = smem_base + stage * D_STAGE_BYTES;
-          mbar_expect_tx(full, D_STAGE_BYTES);
-          tma_load_2d(sw, m0, full, kb * BK, tc.n0);
-          tma_load_2d(sw + D_W_BYTES, m1, full, kb * BK, n1);
-          tma_load_2d(sw + 2 * D_W_BYTES, &tmap_x, full, kb * BK, tc.row0);
+          if (I8) {
+            // the four digit planes of the tile's tokens, 16 rows per copy: MMA column p * tokp + t
+            const int tokp = (it.rows() + 15) & ~15;
+            mbar_expect_tx(full, 2 * D_W_BYTES + kDigitPlanes * tokp * 128);
+            tma_load_2d(sw, m0, full, kb * BKE, tc.n0);
+            tma_load_2d(sw + D_W_BYTES, m1, full, kb * BKE, n1);
+            for (int p = 0; p < kDigitPlanes; ++p)
+              for (int c = 0; c < tokp; c += 16)
+                tma_load_2d(sw + 2 * D_W_BYTES + (p * tokp + c) * 128, &tmap_x, full, kb * BKE,
+                            p * plane_rows + tc.row0 + c);
+          } else {
+            mbar_expect_tx(full, D_STAGE_BYTES);
+            tma_load_2d(sw, m0, full, kb * BK, tc.n0);
+            tma_load_2d(sw + D_W_BYTES, m1, full, kb * BK, n1);
+            tma_load_2d(sw + 2 * D_W_BYTES, &tmap_x, full, kb * BK, tc.row0);
+          }
           armed |= 1u << stage;
         }
       }
@@ -218,7 +270,8 @@ grouped_gemm_bf16_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, cons
           break;
         }
         tc_fence_after();
-        const uint32_t idesc = idesc_dec((it.rows() + 15) & ~15);
+        const int tokp = (it.rows() + 15) & ~15;
+        const uint32_t idesc = I8 ? idesc_dec_i8(kDigitPlanes * tokp) : idesc_dec(tokp);
         const uint32_t d0 = tmem_base + acc * 2 * DTN, d1 = d0 + DTN;
         for (int kb = it.kb0; kb < it.kb0 + it.nkb; ++kb, ++idx) {
           const int stage = idx % D_STAGES;
@@ -236,9 +289,14 @@ grouped_gemm_bf16_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, cons
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
             const uint32_t accum = (kb > it.kb0 || k > 0) ? 1u : 0u;
-            // 16 bf16 of K = 32 bytes along a swizzled row = 2 in descriptor address units
-            tc_mma_bf16(d0, da0 + 2 * k, db + 2 * k, idesc, accum);
-            tc_mma_bf16(d1, da1 + 2 * k, db + 2 * k, idesc, accum);
+            // 16 bf16 (32 int8) of K = 32 bytes along a swizzled row = 2 in descriptor address units
+            if (I8) {
+              tc_mma_i8(d0, da0 + 2 * k, db + 2 * k, idesc, accum);
+              tc_mma_i8(d1, da1 + 2 * k, db + 2 * k, idesc, accum);
+            } else {
+              tc_mma_bf16(d0, da0 + 2 * k, db + 2 * k, idesc, accum);
+              tc_mma_bf16(d1, da1 + 2 * k, db + 2 * k, idesc, accum);
+            }
           }
           tc_commit(smem_u32(&bars->empty[stage]));
         }
@@ -267,7 +325,60 @@ grouped_gemm_bf16_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, cons
       tc_fence_after();
       const int rows = it.rows();
       const uint32_t t0 = tmem_base + (uint32_t(quarter * 32) << 16) + acc * 2 * DTN, t1 = t0 + DTN;
-      if (it.slot >= 0) {
+      if (I8) {
+        // INT8 form: column p * tokp + t of an accumulator is digit plane p of token t (int32, exact)
+        const int tokp = (rows + 15) & ~15;
+        auto fold16 = [&](uint32_t t, int c, float (&v)[16]) {
+          uint32_t a[16];
+          tc_ld16(t + 3 * tokp + c, a);
+          tc_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = (float)(int32_t)a[j];
+#pragma unroll
+          for (int p = 2; p >= 0; --p) {
+            tc_ld16(t + p * tokp + c, a);
+            tc_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = fmaf(v[j], 128.0f, (float)(int32_t)a[j]);
+          }
+        };
+        const int n_lo = tc.n0 + f, n_hi = tc.n0 + DROWS + f;
+        const bool lo_ok = n_lo < N, hi_ok = (MODE == kSwiGLU) ? lo_ok : n_hi < N;
+        float sa = 0.f, sb = 0.f;  // weight-row scales of this lane's two accumulator rows
+        if (it.slot < 0) {
+          if (lo_ok) sa = scale0[tc.group][n_lo];
+          if (MODE == kSwiGLU) {
+            if (lo_ok) sb = scale1[tc.group][n_lo];
+          } else if (hi_ok) {
+            sb = scale0[tc.group][n_hi];
+          }
+        }
+        float* slot = it.slot >= 0 ? ws + ((size_t)blockIdx.x * 2 + it.slot) * D_SLOT_FLOATS : nullptr;
+        __nv_bfloat16* obase = out + (size_t)tc.row0 * N;
+#pragma unroll 1
+        for (int c = half * 16; c < rows; c += 32) {
+          float va[16], vb[16];
+          fold16(t0, c, va);
+          fold16(t1, c, vb);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            if (c + j >= rows) continue;
+            if (slot) {  // partial piece: folded, unscaled sums, [accumulator][token][feature]
+              slot[(size_t)(c + j) * DROWS + f] = va[j];
+              slot[(size_t)(DTN + c + j) * DROWS + f] = vb[j];
+              continue;
+            }
+            const float ts = tok_scale[tc.row0 + c + j];
+            const float a = va[j] * sa * ts, b = vb[j] * sb * ts;
+            if (MODE == kSwiGLU) {
+              if (lo_ok) obase[(size_t)(c + j) * N + n_lo] = __float2bfloat16(silu_mul(a, b));
+            } else {
+              if (lo_ok) obase[(size_t)(c + j) * N + n_lo] = __float2bfloat16(a);
+              if (hi_ok) obase[(size_t)(c + j) * N + n_hi] = __float2bfloat16(b);
+            }
+          }
+        }
+      } else if (it.slot >= 0) {
         // partial piece: raw accumulators to this CTA's workspace slot, [accumulator][token][feature]
         float* slot = ws + ((size_t)blockIdx.x * 2 + it.slot) * D_SLOT_FLOATS;
 #pragma unroll 1
@@ -338,17 +449,22 @@ grouped_gemm_bf16_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, cons
 
 // Adds the partial pieces of every tile that stream-K cut across CTAs, in CTA order, then applies the
 // main kernel's activation and store.  One block per tile, one thread per weight row (feature).
-template <int MODE>
-__global__ void __launch_bounds__(DROWS) bf16_splitk_reduce_kernel(const int32_t* __restrict__ group_offsets,
-                                                                    int num_groups, int N, int K,
-                                                                    __nv_bfloat16* __restrict__ out,
-                                                                    const float* __restrict__ ws, int num_ctas) {
+template <int MODE, bool I8>
+__global__ void __launch_bounds__(DROWS) decode_splitk_reduce_kernel(const int32_t* __restrict__ group_offsets,
+                                                                      int num_groups, int N, int K,
+                                                                      __nv_bfloat16* __restrict__ out,
+                                                                      const float* __restrict__ ws, int num_ctas,
+                                                                      const float* const* __restrict__ scale0,
+                                                                      const float* const* __restrict__ scale1,
+                                                                      const float* __restrict__ tok_scale) {
   constexpr int BN_OUT = (MODE == kSwiGLU) ? DROWS : 2 * DROWS;
-  const int num_kb = (K + BK - 1) / BK;
+  constexpr int BKE = I8 ? IBK : BK;
+  constexpr int TROWS = I8 ? ITOK : DTN;
+  const int num_kb = (K + BKE - 1) / BKE;
   const int n_tiles = (N + BN_OUT - 1) / BN_OUT;
   long long total_tiles = 0;
   for (int gi = 0; gi < num_groups; ++gi)
-    total_tiles += (long long)((group_offsets[gi + 1] - group_offsets[gi] + BM - 1) / BM) * n_tiles;
+    total_tiles += (long long)((group_offsets[gi + 1] - group_offsets[gi] + TROWS - 1) / TROWS) * n_tiles;
   const long long t = blockIdx.x;
   if (t >= total_tiles) return;
   const long long total = total_tiles * num_kb;
@@ -358,14 +474,19 @@ __global__ void __launch_bounds__(DROWS) bf16_splitk_reduce_kernel(const int32_t
   TileCursor cur;
   cur.group = 0;
   cur.base = 0;
-  cursor_load(cur, group_offsets);
+  cursor_load(cur, group_offsets, TROWS);
   TileCoord tc;
-  if (!cursor_seek(cur, (int)t, n_tiles, num_groups, group_offsets, tc, BN_OUT)) return;
+  if (!cursor_seek(cur, (int)t, n_tiles, num_groups, group_offsets, tc, BN_OUT, TROWS)) return;
   const int f = threadIdx.x;
   int rows = tc.row_end - tc.row0;
-  if (rows > DTN) rows = DTN;
+  if (rows > TROWS) rows = TROWS;
   const int n_lo = tc.n0 + f, n_hi = tc.n0 + DROWS + f;
   const bool ok_a = n_lo < N, ok_b = (MODE == kSwiGLU) ? ok_a : n_hi < N;
+  float sa = 1.f, sb = 1.f;
+  if (I8) {
+    sa = ok_a ? scale0[tc.group][n_lo] : 0.f;
+    sb = (MODE == kSwiGLU) ? (ok_a ? scale1[tc.group][n_lo] : 0.f) : (ok_b ? scale0[tc.group][n_hi] : 0.f);
+  }
   for (int tok = 0; tok < rows; ++tok) {
     float a = 0.f, b = 0.f;
     for (int c = c0; c <= c1; ++c) {
@@ -373,6 +494,11 @@ __global__ void __launch_bounds__(DROWS) bf16_splitk_reduce_kernel(const int32_t
       const float* p = ws + ((size_t)c * 2 + slot) * D_SLOT_FLOATS;
       a += p[(size_t)tok * DROWS + f];
       b += p[(size_t)(DTN + tok) * DROWS + f];
+    }
+    if (I8) {
+      const float ts = tok_scale[tc.row0 + tok];
+      a = a * sa * ts;
+      b = b * sb * ts;
     }
     __nv_bfloat16* orow = out + (size_t)(tc.row0 + tok) * N;
     if (MODE == kSwiGLU) {
@@ -384,29 +510,100 @@ __global__ void __launch_bounds__(DROWS) bf16_splitk_reduce_kernel(const int32_t
   }
 }
 
-template <int MODE>
+template <int MODE, bool I8>
 int launch_dec_one(const GroupedGemmArgs& a, int num_sms, cudaStream_t s) {
   static bool attr_set[kMaxDevices] = {};
   if (first_use_on_current_device(attr_set)) {
-    ATENIA_CUDA_TRY(cudaFuncSetAttribute(grouped_gemm_bf16_decode_kernel<MODE>,
+    ATENIA_CUDA_TRY(cudaFuncSetAttribute(grouped_gemm_decode_kernel<MODE, I8>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, D_SMEM_BYTES));
   }
-  // stream-K where every group fits one token tile (one workspace slot holds 128 tokens) and the
-  // tiles that can exist are too few to balance the SMs
+  // stream-K where a workspace slot can hold every piece (bf16: every group fits one 128-token tile;
+  // INT8: tiles are 32 tokens) and the tiles that can exist are too few to balance the SMs
   constexpr int BN_OUT = (MODE == kSwiGLU) ? DROWS : 2 * DROWS;
+  constexpr int TROWS = I8 ? ITOK : DTN;
   const int n_tiles = (a.N + BN_OUT - 1) / BN_OUT;
   const int active_groups = a.max_rows < a.num_groups ? a.max_rows : a.num_groups;
-  const bool splitk = a.splitk_ws != nullptr && a.max_rows <= DTN && active_groups * n_tiles < 4 * num_sms;
-  grouped_gemm_bf16_decode_kernel<MODE><<<dim3(num_sms), dim3(D_THREADS), D_SMEM_BYTES, s>>>(
+  const int max_tok_tiles = I8 ? active_groups + a.max_rows / TROWS : active_groups;
+  const bool splitk = a.splitk_ws != nullptr && a.max_rows <= DTN && max_tok_tiles * n_tiles < 4 * num_sms;
+  grouped_gemm_decode_kernel<MODE, I8><<<dim3(num_sms), dim3(D_THREADS), D_SMEM_BYTES, s>>>(
       a.tmap_a, a.tmap_b0, MODE == kSwiGLU ? a.tmap_b1 : a.tmap_b0, a.group_offsets, a.num_groups, a.N, a.K, a.out,
-      a.err, splitk ? 1 : 0, a.splitk_ws);
+      a.err, splitk ? 1 : 0, a.splitk_ws, a.scale0, a.scale1, a.tok_scale, a.plane_rows);
   int rc = (int)cudaGetLastError();
   if (rc || !splitk) return rc;
-  const int max_tiles = a.num_groups * n_tiles;  // every group has at most one token tile here
-  bf16_splitk_reduce_kernel<MODE><<<dim3(max_tiles), dim3(DROWS), 0, s>>>(a.group_offsets, a.num_groups, a.N, a.K, a.out,
-                                                                          a.splitk_ws, num_sms);
+  decode_splitk_reduce_kernel<MODE, I8><<<dim3(max_tok_tiles * n_tiles), dim3(DROWS), 0, s>>>(
+      a.group_offsets, a.num_groups, a.N, a.K, a.out, a.splitk_ws, num_sms, a.scale0, a.scale1, a.tok_scale);
   count_launch();
   return (int)cudaGetLastError();
+}
+
+// One block per token row: the row's exponent, then its four digit planes (see the head of this file).
+__global__ void __launch_bounds__(256) quantize_digits_kernel(const __nv_bfloat16* __restrict__ x,
+                                                              const int32_t* __restrict__ n_rows_dev, int n_rows,
+                                                              int K, int plane_rows, int8_t* __restrict__ planes,
+                                                              float* __restrict__ tok_scale) {
+  const int row = blockIdx.x;
+  // rows the dispatch did not place (invalid expert ids) hold nothing: skip them
+  const int placed = n_rows_dev ? (*n_rows_dev < n_rows ? *n_rows_dev : n_rows) : n_rows;
+  if (row >= placed) return;
+  __shared__ float red[8];
+  __shared__ float mul_s;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * K);
+  const int nvec = K / 8;
+  float amax = 0.f;
+  bool bad = false;
+  for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+    const uint4 q = xr[v];
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float a = fabsf(bf16lo(w[i])), b = fabsf(bf16hi(w[i]));
+      bad = bad || !(a <= 3.0e38f) || !(b <= 3.0e38f);  // inf or NaN
+      amax = fmaxf(amax, fmaxf(a, b));
+    }
+  }
+  if (bad) amax = __int_as_float(0x7f800000);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float m = red[0];
+    for (int i = 1; i < 8; ++i) m = fmaxf(m, red[i]);
+    float mul = 0.f, ts = 0.f;
+    if (!(m <= 3.0e38f)) {
+      ts = __int_as_float(0x7fc00000);  // a non-finite activation makes the token's outputs NaN
+    } else if (m > 0.f) {
+      int e = ilogbf(m) + 1;  // m < 2^e
+      if (e < -100) e = -100;
+      mul = ldexpf(1.0f, 26 - e);
+      ts = ldexpf(1.0f, e - 26);
+    }
+    mul_s = mul;
+    tok_scale[row] = ts;
+  }
+  __syncthreads();
+  const float mul = mul_s;
+  const size_t plane = (size_t)plane_rows * K;
+  int8_t* prow = planes + (size_t)row * K;
+  for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+    const uint4 q = xr[v];
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+    uint32_t d[kDigitPlanes][2] = {};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float xv = (i & 1) ? bf16hi(w[i >> 1]) : bf16lo(w[i >> 1]);
+      int X = __float2int_rn(xv * mul);  // |X| <= 2^26
+#pragma unroll
+      for (int p = 0; p < kDigitPlanes; ++p) {
+        const int dg = ((X + 64) & 127) - 64;  // balanced digit in [-64, 63]
+        X = (X - dg) >> 7;
+        d[p][i >> 2] |= (uint32_t)(dg & 0xff) << (8 * (i & 3));
+      }
+    }
+#pragma unroll
+    for (int p = 0; p < kDigitPlanes; ++p)
+      *reinterpret_cast<uint2*>(prow + p * plane + (size_t)v * 8) = make_uint2(d[p][0], d[p][1]);
+  }
 }
 
 }  // namespace
@@ -414,10 +611,29 @@ int launch_dec_one(const GroupedGemmArgs& a, int num_sms, cudaStream_t s) {
 int launch_grouped_gemm_bf16_decode(const GroupedGemmArgs& a, int num_sms, cudaStream_t s) {
   if (a.num_groups <= 0) return ATENIA_OK;
   if (a.N % 16 != 0 || a.K % 16 != 0) return ATENIA_ERR_SHAPE;
-  int rc = a.mode == kSwiGLU ? launch_dec_one<kSwiGLU>(a, num_sms, s) : launch_dec_one<kPlain>(a, num_sms, s);
+  int rc = a.mode == kSwiGLU ? launch_dec_one<kSwiGLU, false>(a, num_sms, s) : launch_dec_one<kPlain, false>(a, num_sms, s);
   count_launch();
   count_tcgen05_launch();
   return rc;
+}
+
+int launch_grouped_gemm_w8_i8_decode(const GroupedGemmArgs& a, int num_sms, cudaStream_t s) {
+  if (a.num_groups <= 0) return ATENIA_OK;
+  if (a.N % 16 != 0 || a.K % 16 != 0 || a.max_rows > kI8DecodeMaxRows) return ATENIA_ERR_SHAPE;
+  if (!a.scale0 || (a.mode == kSwiGLU && !a.scale1) || !a.tok_scale || a.plane_rows < a.max_rows) return ATENIA_ERR_NULL;
+  int rc = a.mode == kSwiGLU ? launch_dec_one<kSwiGLU, true>(a, num_sms, s) : launch_dec_one<kPlain, true>(a, num_sms, s);
+  count_launch();
+  count_tcgen05_launch();
+  return rc;
+}
+
+int launch_quantize_digits(const __nv_bfloat16* x, const int32_t* n_rows_dev, int n_rows, int K, int plane_rows,
+                           int8_t* planes, float* tok_scale, cudaStream_t s) {
+  if (n_rows <= 0) return ATENIA_OK;
+  if (K % 16 != 0 || n_rows > plane_rows) return ATENIA_ERR_SHAPE;
+  quantize_digits_kernel<<<n_rows, 256, 0, s>>>(x, n_rows_dev, n_rows, K, plane_rows, planes, tok_scale);
+  count_launch();
+  return (int)cudaGetLastError();
 }
 
 }  // namespace atenia

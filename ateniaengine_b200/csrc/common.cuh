@@ -142,6 +142,9 @@ struct GroupedGemmArgs {
   int max_rows;  // upper bound on total rows (sizes nothing; used by the checking kernel's grid)
   int w8;        // B matrices are int8 (tensor maps of bytes), widened to bf16 inside the kernel
   float* splitk_ws;  // W8 tensor-memory kernel: workspace for stream-K partial sums (null: whole tiles only)
+  // integer-MMA decode kernel only: 2^(e - 26) per token row and the row count of one digit plane
+  const float* tok_scale;
+  int plane_rows;
 };
 int launch_grouped_gemm_tcgen05(const GroupedGemmArgs& a, int num_sms, cudaStream_t s);
 
@@ -178,7 +181,7 @@ int encode_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t rows, uint6
 // int8 matrix [rows, cols]; unswizzled box, or 64-byte swizzle for the row-per-thread reads of the
 // TMEM-operand kernel
 int encode_tmap_2d_u8(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
-                      uint32_t box_cols, int swizzle64);
+                      uint32_t box_cols, int swizzle64);  // swizzle64: 0 none, 1 64-byte, 2 128-byte
 // W8A16 grouped GEMM with the weights as the tensor-memory operand (w8_gemm.cu).  tmap_a is the bf16
 // token matrix (box {64, 128}, 128B swizzle); tmap_b0/b1 are int8 maps with the 64-byte swizzle.
 int launch_grouped_gemm_w8_tmem(const GroupedGemmArgs& a, int num_sms, cudaStream_t s);
@@ -190,6 +193,16 @@ int launch_grouped_gemm_w8_m256(const GroupedGemmArgs& a, int num_sms, cudaStrea
 // the SMs; tmap_a / tmap_b0 / tmap_b1 are the maps of launch_grouped_gemm_tcgen05, splitk_ws as for
 // the INT8 tensor-memory kernel (null: whole tiles only).
 int launch_grouped_gemm_bf16_decode(const GroupedGemmArgs& a, int num_sms, cudaStream_t s);
+// INT8 weights, calls of at most kI8DecodeMaxRows rows (same file): the codes are multiplied as integers
+// (tcgen05 kind::i8) with the token rows split into four planes of base-128 digits by
+// launch_quantize_digits.  tmap_a is the digit-plane map (uint8, box {128, 16}, 128B swizzle; plane p of
+// row r at row p * plane_rows + r), tmap_b0 / tmap_b1 int8 maps with box {128, 128} and the 128B swizzle.
+constexpr int kI8DecodeMaxRows = 128;
+int launch_grouped_gemm_w8_i8_decode(const GroupedGemmArgs& a, int num_sms, cudaStream_t s);
+// planes [4][plane_rows][K] int8 and tok_scale [plane_rows] from bf16 rows x [n_rows, K]; n_rows_dev
+// (device, may be null) bounds the rows that hold data
+int launch_quantize_digits(const __nv_bfloat16* x, const int32_t* n_rows_dev, int n_rows, int K, int plane_rows,
+                           int8_t* planes, float* tok_scale, cudaStream_t s);
 // bf16 weights, CTA pairs (tcgen05 cta_group::2): 256-row tiles, each CTA stages half of the weight tile
 int launch_grouped_gemm_2cta(const GroupedGemmArgs& a, int num_sms, cudaStream_t s);
 

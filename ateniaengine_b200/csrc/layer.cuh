@@ -88,6 +88,17 @@ struct AteniaMoeLayer {
   __nv_bfloat16* y_shared = nullptr;  // [max_tokens, d]
   atenia::DeviceError* d_err = nullptr;
   float* splitk_ws = nullptr;  // stream-K partial sums of the decode kernels, 2 slots per SM
+  // INT8, integer-MMA decode kernel: weight maps (box {128, 128}, 128B swizzle), digit planes [4][128][K] of
+  // the token rows and of the intermediate rows with their row scales, and the planes' tensor maps
+  bool w8_i8 = false;
+  CUtensorMap* d_tm_gate_i8 = nullptr;
+  CUtensorMap* d_tm_up_i8 = nullptr;
+  CUtensorMap* d_tm_down_i8 = nullptr;
+  int8_t* dq_x = nullptr;
+  int8_t* dq_h = nullptr;
+  float* dq_ts_x = nullptr;
+  float* dq_ts_h = nullptr;
+  CUtensorMap tm_dq_x{}, tm_dq_h{};
   float* splitk_ws_shared = nullptr;  // the same for the shared expert's launches (INT8 with a shared expert)
   CUtensorMap tm_x_perm{}, tm_h{}, tm_h_shared{};
 

@@ -69,7 +69,58 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
   // a call of at most two rows in all (decode at batch 1) is a stream over the touched experts' weights:
   // the CUDA-core matrix-vector kernel (ATENIA_MOE_GEMV=0 keeps the tensor-core kernels: A/B runs)
   const bool gemv = L->use_gemv && max_rows <= L->gemv_rows && !L->use_check_gemm;
+  // INT8, calls of at most 128 rows: the codes multiplied as integers against digit planes of the token
+  // rows (bf16_decode_gemm.cu, I8 form) -- no widening, the kernel streams at the HBM rate
+  const bool i8dec = q && L->w8_i8 && L->dq_x && max_rows <= kI8DecodeMaxRows && !L->use_check_gemm && !gemv &&
+                     L->w8_mode == 0;
   if (L->timing) cudaEventRecord(L->ev[0], s);
+  if (i8dec) {
+    int rc = launch_quantize_digits(a_ptr, group_offsets + num_groups, max_rows, c.d_model, kI8DecodeMaxRows, L->dq_x,
+                                    L->dq_ts_x, s);
+    if (rc) return rc;
+    GroupedGemmArgs g1{};
+    g1.tmap_a = L->tm_dq_x;
+    g1.tmap_b0 = L->d_tm_gate_i8;
+    g1.tmap_b1 = L->d_tm_up_i8;
+    g1.group_offsets = group_offsets;
+    g1.num_groups = num_groups;
+    g1.N = c.d_ff;
+    g1.K = c.d_model;
+    g1.mode = kSwiGLU;
+    g1.out = mid;
+    g1.scale0 = L->d_sc_gate;
+    g1.scale1 = L->d_sc_up;
+    g1.err = L->d_err;
+    g1.max_rows = max_rows;
+    g1.w8 = 1;
+    g1.splitk_ws = L->splitk_ws;
+    g1.tok_scale = L->dq_ts_x;
+    g1.plane_rows = kI8DecodeMaxRows;
+    rc = launch_grouped_gemm_w8_i8_decode(g1, L->num_sms, s);
+    if (rc) return rc;
+    if (L->timing) cudaEventRecord(L->ev[1], s);
+    rc = launch_quantize_digits(mid, group_offsets + num_groups, max_rows, c.d_ff, kI8DecodeMaxRows, L->dq_h, L->dq_ts_h,
+                                s);
+    if (rc) return rc;
+    GroupedGemmArgs g2 = g1;
+    g2.tmap_a = L->tm_dq_h;
+    g2.tmap_b0 = L->d_tm_down_i8;
+    g2.tmap_b1 = g2.tmap_b0;
+    g2.N = c.d_model;
+    g2.K = c.d_ff;
+    g2.mode = kPlain;
+    g2.out = out;
+    g2.scale0 = L->d_sc_down;
+    g2.scale1 = nullptr;
+    g2.tok_scale = L->dq_ts_h;
+    rc = launch_grouped_gemm_w8_i8_decode(g2, L->num_sms, s);
+    if (rc) return rc;
+    if (L->timing) {
+      cudaEventRecord(L->ev[2], s);
+      L->ev_valid[0] = L->ev_valid[1] = true;
+    }
+    return ATENIA_OK;
+  }
   if (L->use_check_gemm || gemv) {
     GroupedGemmCheckArgs k1{a_ptr, L->d_p_gate, L->d_p_up, q ? 1 : 0, q ? L->d_sc_gate : nullptr,
                             q ? L->d_sc_up : nullptr, group_offsets, num_groups, c.d_ff, c.d_model,
@@ -245,6 +296,8 @@ int atenia_moe_create(const AteniaMoeConfig* cfg, AteniaMoeLayer** out) {
   L->pair_mode = std::getenv("ATENIA_MOE_PAIR_MODE") ? std::atoi(std::getenv("ATENIA_MOE_PAIR_MODE")) : 0;
   L->shared_aside = !(std::getenv("ATENIA_MOE_SHARED_ASIDE") && std::atoi(std::getenv("ATENIA_MOE_SHARED_ASIDE")) == 0);
   L->use_gemv = !(std::getenv("ATENIA_MOE_GEMV") && std::atoi(std::getenv("ATENIA_MOE_GEMV")) == 0);
+  // ATENIA_MOE_W8_I8=1: INT8 calls of at most 128 rows through the integer-MMA decode kernel
+  L->w8_i8 = std::getenv("ATENIA_MOE_W8_I8") && std::atoi(std::getenv("ATENIA_MOE_W8_I8")) != 0;
   {
     // ATENIA_MOE_GEMV_ROWS moves the hand-over to the tensor-core kernels (1 .. 4 rows: A/B runs)
     const char* e = std::getenv("ATENIA_MOE_GEMV_ROWS");
@@ -324,6 +377,14 @@ int atenia_moe_create(const AteniaMoeConfig* cfg, AteniaMoeLayer** out) {
   }
   if (c.weight_dtype == ATENIA_W_INT8_ROW) {
     if (L->has_shared) TRY_ALLOC(L->splitk_ws_shared, (size_t)L->num_sms * 2 * kW8SplitKSlotFloats);
+    // integer-MMA decode kernel: int8 weight maps with the 128-byte swizzle, digit planes of up to 128 token rows
+    TRY_ALLOC(L->d_tm_gate_i8, (size_t)L->n_groups);
+    TRY_ALLOC(L->d_tm_up_i8, (size_t)L->n_groups);
+    TRY_ALLOC(L->d_tm_down_i8, (size_t)L->n_groups);
+    TRY_ALLOC(L->dq_x, (size_t)4 * kI8DecodeMaxRows * c.d_model);
+    TRY_ALLOC(L->dq_h, (size_t)4 * kI8DecodeMaxRows * c.d_ff);
+    TRY_ALLOC(L->dq_ts_x, (size_t)kI8DecodeMaxRows);
+    TRY_ALLOC(L->dq_ts_h, (size_t)kI8DecodeMaxRows);
     TRY_ALLOC(L->d_tm_gate_sw, (size_t)L->n_groups);
     TRY_ALLOC(L->d_tm_up_sw, (size_t)L->n_groups);
     TRY_ALLOC(L->d_tm_down_sw, (size_t)L->n_groups);
@@ -362,6 +423,8 @@ int atenia_moe_create(const AteniaMoeConfig* cfg, AteniaMoeLayer** out) {
   }
   rc = encode_tmap_2d_bf16(&L->tm_x_perm, L->x_perm, R, d, 128, 64);
   if (!rc && L->h) rc = encode_tmap_2d_bf16(&L->tm_h, L->h, R, F, 128, 64);
+  if (!rc && L->dq_x) rc = encode_tmap_2d_u8(&L->tm_dq_x, L->dq_x, (uint64_t)4 * kI8DecodeMaxRows, d, 16, 128, 2);
+  if (!rc && L->dq_h) rc = encode_tmap_2d_u8(&L->tm_dq_h, L->dq_h, (uint64_t)4 * kI8DecodeMaxRows, F, 16, 128, 2);
   if (!rc && L->has_shared) rc = encode_tmap_2d_bf16(&L->tm_h_shared, L->h_shared, Tm, Fs, 128, 64);
   if (!rc && c.ep_world > 1) {
     rc = encode_tmap_2d_bf16(&L->tm_recv_x, L->recv_x, (uint64_t)L->recv_cap, d, 128, 64);
@@ -396,7 +459,8 @@ int atenia_moe_destroy(AteniaMoeLayer* L) {
                   L->d_tm_down, L->d_tm_shared, L->d_sc_gate, L->d_sc_up, L->d_sc_down, L->d_sc_shared,
                   L->d_p_gate, L->d_p_up, L->d_p_down, L->d_p_shared, L->d_tm_gate_sw, L->d_tm_up_sw,
                   L->d_tm_down_sw, L->d_tm_shared_sw,
-                  L->splitk_ws, L->splitk_ws_shared, L->d_escore, L->logits_ws, L->recv_x, L->recv_h, L->recv_y, L->d_counts_all,
+                  L->splitk_ws, L->splitk_ws_shared, L->d_tm_gate_i8, L->d_tm_up_i8, L->d_tm_down_i8, L->dq_x, L->dq_h,
+                  L->dq_ts_x, L->dq_ts_h, L->d_escore, L->logits_ws, L->recv_x, L->recv_h, L->recv_y, L->d_counts_all,
                   L->d_group_offsets, L->d_peer_recv_x, L->d_peer_y_perm, L->d_dst_base, L->d_src_base,
                   L->d_gemm_offsets, L->d_bar, L->d_sync, L->d_peer_sync, L->d_ep_state, L->sk_part, L->sk_gate, L->sk_counters, L->block_normed};
   for (void* p : ptrs)
@@ -451,7 +515,7 @@ int atenia_moe_set_weights(AteniaMoeLayer* L, const AteniaMoeWeights* w) {
   };
 
   const int G = L->n_groups, El = L->e_local;
-  std::vector<CUtensorMap> tg(G), tu(G), td(G), tgs(G), tus(G), tds(G);
+  std::vector<CUtensorMap> tg(G), tu(G), td(G), tgs(G), tus(G), tds(G), tgi(G), tui(G), tdi(G);
   std::vector<const void*> pg(G), pu(G), pd(G);
   std::vector<const float*> sg(G, nullptr), su(G, nullptr), sd(G, nullptr);
   for (int e = 0; e < El; ++e) {
@@ -464,6 +528,10 @@ int atenia_moe_set_weights(AteniaMoeLayer* L, const AteniaMoeWeights* w) {
     if (!rc && q) rc = encode(&tgs[e], pg[e], F, d, 1);
     if (!rc && q) rc = encode(&tus[e], pu[e], F, d, 1);
     if (!rc && q) rc = encode(&tds[e], pd[e], d, F, 1);
+    // integer-MMA decode kernel: 128 codes of 128 rows per box, 128-byte swizzle
+    if (!rc && q) rc = encode_tmap_2d_u8(&tgi[e], pg[e], F, d, 128, 128, 2);
+    if (!rc && q) rc = encode_tmap_2d_u8(&tui[e], pu[e], F, d, 128, 128, 2);
+    if (!rc && q) rc = encode_tmap_2d_u8(&tdi[e], pd[e], d, F, 128, 128, 2);
     if (rc) return rc;
     if (q) {
       if (!w->s_gate[e] || !w->s_up[e] || !w->s_down[e]) return ATENIA_ERR_NULL;
@@ -480,6 +548,9 @@ int atenia_moe_set_weights(AteniaMoeLayer* L, const AteniaMoeWeights* w) {
     tgs[g] = tgs[g % El];
     tus[g] = tus[g % El];
     tds[g] = tds[g % El];
+    tgi[g] = tgi[g % El];
+    tui[g] = tui[g % El];
+    tdi[g] = tdi[g % El];
     pg[g] = pg[g % El];
     pu[g] = pu[g % El];
     pd[g] = pd[g % El];
@@ -495,6 +566,9 @@ int atenia_moe_set_weights(AteniaMoeLayer* L, const AteniaMoeWeights* w) {
     ATENIA_CUDA_TRY(cudaMemcpy(L->d_tm_gate_sw, tgs.data(), mb, cudaMemcpyHostToDevice));
     ATENIA_CUDA_TRY(cudaMemcpy(L->d_tm_up_sw, tus.data(), mb, cudaMemcpyHostToDevice));
     ATENIA_CUDA_TRY(cudaMemcpy(L->d_tm_down_sw, tds.data(), mb, cudaMemcpyHostToDevice));
+    ATENIA_CUDA_TRY(cudaMemcpy(L->d_tm_gate_i8, tgi.data(), mb, cudaMemcpyHostToDevice));
+    ATENIA_CUDA_TRY(cudaMemcpy(L->d_tm_up_i8, tui.data(), mb, cudaMemcpyHostToDevice));
+    ATENIA_CUDA_TRY(cudaMemcpy(L->d_tm_down_i8, tdi.data(), mb, cudaMemcpyHostToDevice));
   }
   ATENIA_CUDA_TRY(cudaMemcpy(L->d_p_gate, pg.data(), pb, cudaMemcpyHostToDevice));
   ATENIA_CUDA_TRY(cudaMemcpy(L->d_p_up, pu.data(), pb, cudaMemcpyHostToDevice));

@@ -99,6 +99,11 @@ uint64_t layer_workspace_bytes(const AteniaMoeConfig& c, int world) {
   t.add((uint64_t)148 * 2 * kW8SplitKSlotFloats * 4);  // stream-K partial sums, one pair of slots per SM
   if (q) {
     if (Fs) t.add((uint64_t)148 * 2 * kW8SplitKSlotFloats * 4);  // the same for the shared expert's launches
+    for (int i = 0; i < 3; ++i) t.add(groups * tm);               // weight maps of the integer-MMA decode kernel
+    t.add((uint64_t)4 * kI8DecodeMaxRows * d);                    // digit planes of the token rows
+    t.add((uint64_t)4 * kI8DecodeMaxRows * F);                    // and of the intermediate rows
+    t.add((uint64_t)kI8DecodeMaxRows * 4);
+    t.add((uint64_t)kI8DecodeMaxRows * 4);
     t.add(groups * tm);
     t.add(groups * tm);
     t.add(groups * tm);
