@@ -197,7 +197,8 @@ int launch_grouped_gemm_bf16_decode(const GroupedGemmArgs& a, int num_sms, cudaS
 // (tcgen05 kind::i8) with the token rows split into four planes of base-128 digits by
 // launch_quantize_digits.  tmap_a is the digit-plane map (uint8, box {128, 16}, 128B swizzle; plane p of
 // row r at row p * plane_rows + r), tmap_b0 / tmap_b1 int8 maps with box {128, 128} and the 128B swizzle.
-constexpr int kI8DecodeMaxRows = 128;
+constexpr int kI8DecodeMaxRows = 512;      // largest call (rows of one digit plane) a layer may be set up for
+constexpr int kI8DecodeDefaultRows = 128;  // ... and what a layer takes unless told otherwise
 int launch_grouped_gemm_w8_i8_decode(const GroupedGemmArgs& a, int num_sms, cudaStream_t s);
 // planes [4][plane_rows][K] int8 and tok_scale [plane_rows] from bf16 rows x [n_rows, K]; n_rows_dev
 // (device, may be null) bounds the rows that hold data

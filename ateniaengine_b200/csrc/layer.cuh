@@ -90,7 +90,8 @@ struct AteniaMoeLayer {
   float* splitk_ws = nullptr;  // stream-K partial sums of the decode kernels, 2 slots per SM
   // INT8, integer-MMA decode kernel: weight maps (box {128, 128}, 128B swizzle), digit planes [4][128][K] of
   // the token rows and of the intermediate rows with their row scales, and the planes' tensor maps
-  bool w8_i8 = false;
+  bool w8_i8 = true;
+  int i8_rows = 128;  // rows of one digit plane = the largest call the kernel takes
   CUtensorMap* d_tm_gate_i8 = nullptr;
   CUtensorMap* d_tm_up_i8 = nullptr;
   CUtensorMap* d_tm_down_i8 = nullptr;

@@ -68,14 +68,16 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
   const bool pairs = !q && !dec && (L->pair_mode == 1 || (L->pair_mode == 0 && max_rows >= 512 * num_groups));
   // a call of at most two rows in all (decode at batch 1) is a stream over the touched experts' weights:
   // the CUDA-core matrix-vector kernel (ATENIA_MOE_GEMV=0 keeps the tensor-core kernels: A/B runs)
-  const bool gemv = L->use_gemv && max_rows <= L->gemv_rows && !L->use_check_gemm;
-  // INT8, calls of at most 128 rows: the codes multiplied as integers against digit planes of the token
-  // rows (bf16_decode_gemm.cu, I8 form) -- no widening, the kernel streams at the HBM rate
-  const bool i8dec = q && L->w8_i8 && L->dq_x && max_rows <= kI8DecodeMaxRows && !L->use_check_gemm && !gemv &&
-                     L->w8_mode == 0;
+  // INT8, calls of at most i8_rows rows (decode): the codes multiplied as integers against digit planes of
+  // the token rows (bf16_decode_gemm.cu, I8 form) -- nothing is widened and the kernel streams weights like
+  // the bf16 one.  Measured on B200, Mixtral shape, 1 / 8 / 64 tokens: 0.145 / 0.221 / 0.390 ms against
+  // 0.160 (matrix-vector kernel) / 0.300 / 0.525 ms (tensor-memory kernel).  ATENIA_MOE_W8_I8=0 or a pinned
+  // w8_mode keep the widening kernels (tests, A/B runs).
+  const bool i8dec = q && L->w8_i8 && L->dq_x && max_rows <= L->i8_rows && !L->use_check_gemm && L->w8_mode == 0;
+  const bool gemv = L->use_gemv && max_rows <= L->gemv_rows && !L->use_check_gemm && !i8dec;
   if (L->timing) cudaEventRecord(L->ev[0], s);
   if (i8dec) {
-    int rc = launch_quantize_digits(a_ptr, group_offsets + num_groups, max_rows, c.d_model, kI8DecodeMaxRows, L->dq_x,
+    int rc = launch_quantize_digits(a_ptr, group_offsets + num_groups, max_rows, c.d_model, L->i8_rows, L->dq_x,
                                     L->dq_ts_x, s);
     if (rc) return rc;
     GroupedGemmArgs g1{};
@@ -95,12 +97,11 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
     g1.w8 = 1;
     g1.splitk_ws = L->splitk_ws;
     g1.tok_scale = L->dq_ts_x;
-    g1.plane_rows = kI8DecodeMaxRows;
+    g1.plane_rows = L->i8_rows;
     rc = launch_grouped_gemm_w8_i8_decode(g1, L->num_sms, s);
     if (rc) return rc;
     if (L->timing) cudaEventRecord(L->ev[1], s);
-    rc = launch_quantize_digits(mid, group_offsets + num_groups, max_rows, c.d_ff, kI8DecodeMaxRows, L->dq_h, L->dq_ts_h,
-                                s);
+    rc = launch_quantize_digits(mid, group_offsets + num_groups, max_rows, c.d_ff, L->i8_rows, L->dq_h, L->dq_ts_h, s);
     if (rc) return rc;
     GroupedGemmArgs g2 = g1;
     g2.tmap_a = L->tm_dq_h;
@@ -296,8 +297,10 @@ int atenia_moe_create(const AteniaMoeConfig* cfg, AteniaMoeLayer** out) {
   L->pair_mode = std::getenv("ATENIA_MOE_PAIR_MODE") ? std::atoi(std::getenv("ATENIA_MOE_PAIR_MODE")) : 0;
   L->shared_aside = !(std::getenv("ATENIA_MOE_SHARED_ASIDE") && std::atoi(std::getenv("ATENIA_MOE_SHARED_ASIDE")) == 0);
   L->use_gemv = !(std::getenv("ATENIA_MOE_GEMV") && std::atoi(std::getenv("ATENIA_MOE_GEMV")) == 0);
-  // ATENIA_MOE_W8_I8=1: INT8 calls of at most 128 rows through the integer-MMA decode kernel
-  L->w8_i8 = std::getenv("ATENIA_MOE_W8_I8") && std::atoi(std::getenv("ATENIA_MOE_W8_I8")) != 0;
+  // ATENIA_MOE_W8_I8=0: INT8 decode calls keep the widening kernels; ATENIA_MOE_W8_I8_ROWS moves the row
+  // count up to which the integer-MMA decode kernel is taken (16 .. kI8DecodeMaxRows; A/B runs)
+  L->w8_i8 = !(std::getenv("ATENIA_MOE_W8_I8") && std::atoi(std::getenv("ATENIA_MOE_W8_I8")) == 0);
+
   {
     // ATENIA_MOE_GEMV_ROWS moves the hand-over to the tensor-core kernels (1 .. 4 rows: A/B runs)
     const char* e = std::getenv("ATENIA_MOE_GEMV_ROWS");
@@ -377,14 +380,21 @@ int atenia_moe_create(const AteniaMoeConfig* cfg, AteniaMoeLayer** out) {
   }
   if (c.weight_dtype == ATENIA_W_INT8_ROW) {
     if (L->has_shared) TRY_ALLOC(L->splitk_ws_shared, (size_t)L->num_sms * 2 * kW8SplitKSlotFloats);
-    // integer-MMA decode kernel: int8 weight maps with the 128-byte swizzle, digit planes of up to 128 token rows
+    // integer-MMA decode kernel: int8 weight maps with the 128-byte swizzle, digit planes of the token rows
+  {
+    const char* e = std::getenv("ATENIA_MOE_W8_I8_ROWS");
+    int r = e ? std::atoi(e) : kI8DecodeDefaultRows;
+    r = r < 16 ? 16 : (r > kI8DecodeMaxRows ? kI8DecodeMaxRows : r);
+    const int cap = (int)((R + 15) / 16 * 16);  // never more planes than the layer has rows
+    L->i8_rows = r < cap ? r : cap;
+  }
     TRY_ALLOC(L->d_tm_gate_i8, (size_t)L->n_groups);
     TRY_ALLOC(L->d_tm_up_i8, (size_t)L->n_groups);
     TRY_ALLOC(L->d_tm_down_i8, (size_t)L->n_groups);
-    TRY_ALLOC(L->dq_x, (size_t)4 * kI8DecodeMaxRows * c.d_model);
-    TRY_ALLOC(L->dq_h, (size_t)4 * kI8DecodeMaxRows * c.d_ff);
-    TRY_ALLOC(L->dq_ts_x, (size_t)kI8DecodeMaxRows);
-    TRY_ALLOC(L->dq_ts_h, (size_t)kI8DecodeMaxRows);
+    TRY_ALLOC(L->dq_x, (size_t)4 * L->i8_rows * c.d_model);
+    TRY_ALLOC(L->dq_h, (size_t)4 * L->i8_rows * c.d_ff);
+    TRY_ALLOC(L->dq_ts_x, (size_t)L->i8_rows);
+    TRY_ALLOC(L->dq_ts_h, (size_t)L->i8_rows);
     TRY_ALLOC(L->d_tm_gate_sw, (size_t)L->n_groups);
     TRY_ALLOC(L->d_tm_up_sw, (size_t)L->n_groups);
     TRY_ALLOC(L->d_tm_down_sw, (size_t)L->n_groups);
@@ -423,8 +433,8 @@ int atenia_moe_create(const AteniaMoeConfig* cfg, AteniaMoeLayer** out) {
   }
   rc = encode_tmap_2d_bf16(&L->tm_x_perm, L->x_perm, R, d, 128, 64);
   if (!rc && L->h) rc = encode_tmap_2d_bf16(&L->tm_h, L->h, R, F, 128, 64);
-  if (!rc && L->dq_x) rc = encode_tmap_2d_u8(&L->tm_dq_x, L->dq_x, (uint64_t)4 * kI8DecodeMaxRows, d, 16, 128, 2);
-  if (!rc && L->dq_h) rc = encode_tmap_2d_u8(&L->tm_dq_h, L->dq_h, (uint64_t)4 * kI8DecodeMaxRows, F, 16, 128, 2);
+  if (!rc && L->dq_x) rc = encode_tmap_2d_u8(&L->tm_dq_x, L->dq_x, (uint64_t)4 * L->i8_rows, d, 16, 128, 2);
+  if (!rc && L->dq_h) rc = encode_tmap_2d_u8(&L->tm_dq_h, L->dq_h, (uint64_t)4 * L->i8_rows, F, 16, 128, 2);
   if (!rc && L->has_shared) rc = encode_tmap_2d_bf16(&L->tm_h_shared, L->h_shared, Tm, Fs, 128, 64);
   if (!rc && c.ep_world > 1) {
     rc = encode_tmap_2d_bf16(&L->tm_recv_x, L->recv_x, (uint64_t)L->recv_cap, d, 128, 64);

@@ -15,6 +15,7 @@
 // the router is f64 under every policy.  This library IS the Fast arm.  The functions below restate
 // the switch (same strings, same precedence: in-process override, then the environment read once,
 // then Certified) so that a host can ask whether the library serves the active policy.
+#include <algorithm>
 #include <atomic>
 #include <cctype>
 #include <cstdlib>
@@ -100,10 +101,11 @@ uint64_t layer_workspace_bytes(const AteniaMoeConfig& c, int world) {
   if (q) {
     if (Fs) t.add((uint64_t)148 * 2 * kW8SplitKSlotFloats * 4);  // the same for the shared expert's launches
     for (int i = 0; i < 3; ++i) t.add(groups * tm);               // weight maps of the integer-MMA decode kernel
-    t.add((uint64_t)4 * kI8DecodeMaxRows * d);                    // digit planes of the token rows
-    t.add((uint64_t)4 * kI8DecodeMaxRows * F);                    // and of the intermediate rows
-    t.add((uint64_t)kI8DecodeMaxRows * 4);
-    t.add((uint64_t)kI8DecodeMaxRows * 4);
+    const uint64_t pr = std::min<uint64_t>(kI8DecodeDefaultRows, (R + 15) / 16 * 16);
+    t.add(4 * pr * d);                                            // digit planes of the token rows
+    t.add(4 * pr * F);                                            // and of the intermediate rows
+    t.add(pr * 4);
+    t.add(pr * 4);
     t.add(groups * tm);
     t.add(groups * tm);
     t.add(groups * tm);

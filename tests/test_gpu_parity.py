@@ -152,9 +152,10 @@ def test_w8a16_structure(dev):
 
 @pytest.mark.parametrize("mode", ["0", "1", "2"])
 def test_w8a16_every_kernel(dev, monkeypatch, mode):
-    """ATENIA_MOE_W8_MODE pins the INT8 kernel family (0: by size -- weights widened into tensor memory
-    for small groups, 256-row tiles widened into shared memory for large ones; 1: always the former;
-    2: 128-row tiles widened into shared memory); each must meet the bar at small and large group sizes."""
+    """ATENIA_MOE_W8_MODE pins the INT8 kernel family (0: by size -- the integer-MMA decode kernel up to
+    128 rows, weights widened into tensor memory for small groups, 256-row tiles widened into shared memory
+    for large ones; 1: always the tensor-memory kernel; 2: 128-row tiles widened into shared memory); each
+    must meet the bar at small and large group sizes."""
     monkeypatch.setenv("ATENIA_MOE_W8_MODE", mode)
     synth = _synth()
     shape = synth.small(synth.SHAPES["mixtral_int8"], d_model=512, d_ff=768)
