@@ -448,9 +448,11 @@ grouped_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const CUt
 }
 
 // Adds the partial pieces of every tile that stream-K cut across CTAs, in CTA order, then applies the
-// main kernel's activation and store.  One block per tile, one thread per weight row (feature).
+// main kernel's activation and store.  One block per tile; thread (f, y) takes weight row (feature) f and
+// every kReduceTokLanes-th token, so that the dependent loads of one thread are few.
+constexpr int kReduceTokLanes = 8;
 template <int MODE, bool I8>
-__global__ void __launch_bounds__(DROWS) decode_splitk_reduce_kernel(const int32_t* __restrict__ group_offsets,
+__global__ void __launch_bounds__(DROWS * kReduceTokLanes) decode_splitk_reduce_kernel(const int32_t* __restrict__ group_offsets,
                                                                       int num_groups, int N, int K,
                                                                       __nv_bfloat16* __restrict__ out,
                                                                       const float* __restrict__ ws, int num_ctas,
@@ -487,7 +489,7 @@ __global__ void __launch_bounds__(DROWS) decode_splitk_reduce_kernel(const int32
     sa = ok_a ? scale0[tc.group][n_lo] : 0.f;
     sb = (MODE == kSwiGLU) ? (ok_a ? scale1[tc.group][n_lo] : 0.f) : (ok_b ? scale0[tc.group][n_hi] : 0.f);
   }
-  for (int tok = 0; tok < rows; ++tok) {
+  for (int tok = threadIdx.y; tok < rows; tok += kReduceTokLanes) {
     float a = 0.f, b = 0.f;
     for (int c = c0; c <= c1; ++c) {
       const int slot = (t == ((long long)c * span) / num_kb) ? 0 : 1;
@@ -530,80 +532,104 @@ int launch_dec_one(const GroupedGemmArgs& a, int num_sms, cudaStream_t s) {
       a.err, splitk ? 1 : 0, a.splitk_ws, a.scale0, a.scale1, a.tok_scale, a.plane_rows);
   int rc = (int)cudaGetLastError();
   if (rc || !splitk) return rc;
-  decode_splitk_reduce_kernel<MODE, I8><<<dim3(max_tok_tiles * n_tiles), dim3(DROWS), 0, s>>>(
+  decode_splitk_reduce_kernel<MODE, I8><<<dim3(max_tok_tiles * n_tiles), dim3(DROWS, kReduceTokLanes), 0, s>>>(
       a.group_offsets, a.num_groups, a.N, a.K, a.out, a.splitk_ws, num_sms, a.scale0, a.scale1, a.tok_scale);
   count_launch();
   return (int)cudaGetLastError();
 }
 
 // One block per token row: the row's exponent, then its four digit planes (see the head of this file).
-__global__ void __launch_bounds__(256) quantize_digits_kernel(const __nv_bfloat16* __restrict__ x,
-                                                              const int32_t* __restrict__ n_rows_dev, int n_rows,
-                                                              int K, int plane_rows, int8_t* __restrict__ planes,
-                                                              float* __restrict__ tok_scale) {
+// The row is read once: a thread keeps its (up to kQVecs) 16-byte vectors in registers between the two
+// passes; longer rows read the rest again.
+constexpr int kQThreads = 1024;
+constexpr int kQVecs = 2;  // 8 bf16 each: rows of up to 16 384 elements stay in registers
+
+__device__ __forceinline__ void digits_of_vector(const uint4& q, float mul, int8_t* __restrict__ prow, size_t plane,
+                                                 int v) {
+  const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+  uint32_t d[kDigitPlanes][2] = {};
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float xv = (i & 1) ? bf16hi(w[i >> 1]) : bf16lo(w[i >> 1]);
+    int X = __float2int_rn(xv * mul);  // |X| <= 2^26
+#pragma unroll
+    for (int p = 0; p < kDigitPlanes; ++p) {
+      const int dg = ((X + 64) & 127) - 64;  // balanced digit in [-64, 63]
+      X = (X - dg) >> 7;
+      d[p][i >> 2] |= (uint32_t)(dg & 0xff) << (8 * (i & 3));
+    }
+  }
+#pragma unroll
+  for (int p = 0; p < kDigitPlanes; ++p)
+    *reinterpret_cast<uint2*>(prow + p * plane + (size_t)v * 8) = make_uint2(d[p][0], d[p][1]);
+}
+
+__device__ __forceinline__ void amax_of_vector(const uint4& q, float& amax, bool& bad) {
+  const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float a = fabsf(bf16lo(w[i])), b = fabsf(bf16hi(w[i]));
+    bad = bad || !(a <= 3.0e38f) || !(b <= 3.0e38f);  // inf or NaN
+    amax = fmaxf(amax, fmaxf(a, b));
+  }
+}
+
+__global__ void __launch_bounds__(kQThreads) quantize_digits_kernel(const __nv_bfloat16* __restrict__ x,
+                                                                    const int32_t* __restrict__ n_rows_dev, int n_rows,
+                                                                    int K, int plane_rows, int8_t* __restrict__ planes,
+                                                                    float* __restrict__ tok_scale) {
   const int row = blockIdx.x;
   // rows the dispatch did not place (invalid expert ids) hold nothing: skip them
   const int placed = n_rows_dev ? (*n_rows_dev < n_rows ? *n_rows_dev : n_rows) : n_rows;
   if (row >= placed) return;
-  __shared__ float red[8];
+  __shared__ float red[kQThreads / 32];
   __shared__ float mul_s;
   const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * K);
   const int nvec = K / 8;
+  uint4 keep[kQVecs];
   float amax = 0.f;
   bool bad = false;
-  for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
-    const uint4 q = xr[v];
-    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float a = fabsf(bf16lo(w[i])), b = fabsf(bf16hi(w[i]));
-      bad = bad || !(a <= 3.0e38f) || !(b <= 3.0e38f);  // inf or NaN
-      amax = fmaxf(amax, fmaxf(a, b));
-    }
+  for (int j = 0; j < kQVecs; ++j) {
+    const int v = threadIdx.x + j * kQThreads;
+    keep[j] = v < nvec ? xr[v] : make_uint4(0, 0, 0, 0);
   }
+#pragma unroll
+  for (int j = 0; j < kQVecs; ++j) amax_of_vector(keep[j], amax, bad);
+  for (int v = threadIdx.x + kQVecs * kQThreads; v < nvec; v += kQThreads) amax_of_vector(xr[v], amax, bad);
   if (bad) amax = __int_as_float(0x7f800000);
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
   __syncthreads();
-  if (threadIdx.x == 0) {
-    float m = red[0];
-    for (int i = 1; i < 8; ++i) m = fmaxf(m, red[i]);
-    float mul = 0.f, ts = 0.f;
-    if (!(m <= 3.0e38f)) {
-      ts = __int_as_float(0x7fc00000);  // a non-finite activation makes the token's outputs NaN
-    } else if (m > 0.f) {
-      int e = ilogbf(m) + 1;  // m < 2^e
-      if (e < -100) e = -100;
-      mul = ldexpf(1.0f, 26 - e);
-      ts = ldexpf(1.0f, e - 26);
+  if (threadIdx.x < 32) {
+    float m = red[threadIdx.x];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if (threadIdx.x == 0) {
+      float mul = 0.f, ts = 0.f;
+      if (!(m <= 3.0e38f)) {
+        ts = __int_as_float(0x7fc00000);  // a non-finite activation makes the token's outputs NaN
+      } else if (m > 0.f) {
+        int e = ilogbf(m) + 1;  // m < 2^e
+        if (e < -100) e = -100;
+        mul = ldexpf(1.0f, 26 - e);
+        ts = ldexpf(1.0f, e - 26);
+      }
+      mul_s = mul;
+      tok_scale[row] = ts;
     }
-    mul_s = mul;
-    tok_scale[row] = ts;
   }
   __syncthreads();
   const float mul = mul_s;
   const size_t plane = (size_t)plane_rows * K;
   int8_t* prow = planes + (size_t)row * K;
-  for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
-    const uint4 q = xr[v];
-    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-    uint32_t d[kDigitPlanes][2] = {};
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const float xv = (i & 1) ? bf16hi(w[i >> 1]) : bf16lo(w[i >> 1]);
-      int X = __float2int_rn(xv * mul);  // |X| <= 2^26
-#pragma unroll
-      for (int p = 0; p < kDigitPlanes; ++p) {
-        const int dg = ((X + 64) & 127) - 64;  // balanced digit in [-64, 63]
-        X = (X - dg) >> 7;
-        d[p][i >> 2] |= (uint32_t)(dg & 0xff) << (8 * (i & 3));
-      }
-    }
-#pragma unroll
-    for (int p = 0; p < kDigitPlanes; ++p)
-      *reinterpret_cast<uint2*>(prow + p * plane + (size_t)v * 8) = make_uint2(d[p][0], d[p][1]);
+  for (int j = 0; j < kQVecs; ++j) {
+    const int v = threadIdx.x + j * kQThreads;
+    if (v < nvec) digits_of_vector(keep[j], mul, prow, plane, v);
   }
+  for (int v = threadIdx.x + kQVecs * kQThreads; v < nvec; v += kQThreads) digits_of_vector(xr[v], mul, prow, plane, v);
 }
 
 }  // namespace
@@ -631,7 +657,7 @@ int launch_quantize_digits(const __nv_bfloat16* x, const int32_t* n_rows_dev, in
                            int8_t* planes, float* tok_scale, cudaStream_t s) {
   if (n_rows <= 0) return ATENIA_OK;
   if (K % 16 != 0 || n_rows > plane_rows) return ATENIA_ERR_SHAPE;
-  quantize_digits_kernel<<<n_rows, 256, 0, s>>>(x, n_rows_dev, n_rows, K, plane_rows, planes, tok_scale);
+  quantize_digits_kernel<<<n_rows, kQThreads, 0, s>>>(x, n_rows_dev, n_rows, K, plane_rows, planes, tok_scale);
   count_launch();
   return (int)cudaGetLastError();
 }

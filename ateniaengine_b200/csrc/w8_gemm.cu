@@ -442,7 +442,7 @@ grouped_gemm_w8_tmem_kernel(const __grid_constant__ CUtensorMap tmap_x, const CU
 // same scale / activation / store as the main kernel's epilogue.  One block per tile, one thread per
 // weight row (feature).
 template <int MODE>
-__global__ void __launch_bounds__(WROWS) w8_splitk_reduce_kernel(const int32_t* __restrict__ group_offsets,
+__global__ void __launch_bounds__(WROWS * 8) w8_splitk_reduce_kernel(const int32_t* __restrict__ group_offsets,
                                                                   int num_groups, int N, int K,
                                                                   __nv_bfloat16* __restrict__ out,
                                                                   const float* const* __restrict__ scale0,
@@ -483,7 +483,8 @@ __global__ void __launch_bounds__(WROWS) w8_splitk_reduce_kernel(const int32_t* 
     s_a = ok_a ? sc0[n_lo] : 0.f;
     s_b = ok_b ? sc0[n_hi] : 0.f;
   }
-  for (int tok = 0; tok < rows; ++tok) {
+  // (thread (f, y) takes every blockDim.y-th token: few dependent loads per thread)
+  for (int tok = threadIdx.y; tok < rows; tok += blockDim.y) {
     float a = 0.f, b = 0.f;
     for (int c = c0; c <= c1; ++c) {
       const int slot = (t == ((long long)c * span) / num_kb) ? 0 : 1;
@@ -522,7 +523,7 @@ int launch_w8_one(const GroupedGemmArgs& a, int num_sms, cudaStream_t s) {
   constexpr int BN_OUT = (MODE == kSwiGLU) ? WROWS : 2 * WROWS;
   const int n_tiles = (a.N + BN_OUT - 1) / BN_OUT;
   const int max_tiles = a.num_groups * n_tiles;  // every group has at most one token tile here
-  w8_splitk_reduce_kernel<MODE><<<dim3(max_tiles), dim3(WROWS), 0, s>>>(a.group_offsets, a.num_groups, a.N, a.K, a.out,
+  w8_splitk_reduce_kernel<MODE><<<dim3(max_tiles), dim3(WROWS, 8), 0, s>>>(a.group_offsets, a.num_groups, a.N, a.K, a.out,
                                                                          a.scale0, a.scale1, a.splitk_ws, num_sms);
   count_launch();
   return (int)cudaGetLastError();
