@@ -149,7 +149,13 @@ struct DecPieces {
 // I8: tmap_x is the digit-plane map (uint8, box {128, 16}; plane p of row r at row p * plane_rows + r),
 // tmap_w0 / tmap_w1 are int8 maps with box {128, 128} and the 128-byte swizzle, scale0 / scale1 the
 // weight rows' scales per group and tok_scale the token rows' 2^(e - 26).
-template <int MODE, bool I8>
+//
+// WIDE (bf16 only): token tiles of up to 256 rows -- one tile for most experts of a many-expert layer at a
+// few thousand tokens, where 128-row tiles leave a second, nearly empty tile per expert that streams the
+// expert's weights through shared memory again.  The two accumulators then fill tensor memory (no second
+// buffer: the epilogue of a tile is not overlapped), the ring is 3 stages of 64 KiB, the token rows arrive in
+// 64-row copies (tmap_x has a 64-row box) and there is no stream-K.
+template <int MODE, bool I8, bool WIDE = false>
 __global__ void __launch_bounds__(D_THREADS, 1)
 grouped_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const CUtensorMap* __restrict__ tmap_w0,
                            const CUtensorMap* __restrict__ tmap_w1, const int32_t* __restrict__ group_offsets,
@@ -159,8 +165,13 @@ grouped_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const CUt
                            int plane_rows) {
   extern __shared__ uint8_t smem_raw[];
   constexpr int BN_OUT = (MODE == kSwiGLU) ? DROWS : 2 * DROWS;
-  constexpr int BKE = I8 ? IBK : BK;        // k elements per k-block
-  constexpr int TROWS = I8 ? ITOK : DTN;    // token rows per tile
+  static_assert(!(I8 && WIDE), "the wide form is bf16 only");
+  constexpr int BKE = I8 ? IBK : BK;                         // k elements per k-block
+  constexpr int TROWS = I8 ? ITOK : (WIDE ? 2 * DTN : DTN);  // token rows per tile
+  constexpr int ACOLS = WIDE ? 2 * DTN : DTN;                // tensor-memory columns of one accumulator
+  constexpr int STAGES = WIDE ? 3 : D_STAGES;
+  constexpr int STAGE_BYTES = WIDE ? 2 * D_W_BYTES + 2 * D_X_BYTES : D_STAGE_BYTES;  // 64 KiB : 48 KiB
+  static_assert(STAGES * STAGE_BYTES <= D_STAGES * D_STAGE_BYTES, "one shared-memory size for all forms");
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
   BarriersDec* bars = reinterpret_cast<BarriersDec*>(smem_aligned + D_STAGES * D_STAGE_BYTES);
@@ -172,7 +183,7 @@ grouped_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const CUt
   const int n_tiles = (N + BN_OUT - 1) / BN_OUT;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < D_STAGES; ++s) {
+    for (int s = 0; s < STAGES; ++s) {
       mbar_init(smem_u32(&bars->full[s]), 1);
       mbar_init(smem_u32(&bars->empty[s]), 1);
     }
@@ -216,8 +227,8 @@ grouped_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const CUt
         const CUtensorMap* m1 = (MODE == kSwiGLU) ? &tmap_w1[tc.group] : m0;
         const int n1 = (MODE == kSwiGLU) ? tc.n0 : tc.n0 + DROWS;
         for (int kb = it.kb0; kb < it.kb0 + it.nkb; ++kb, ++idx) {
-          const int stage = idx % D_STAGES;
-          const uint32_t phase = (idx / D_STAGES) & 1u;
+          const int stage = idx % STAGES;
+          const uint32_t phase = (idx / STAGES) & 1u;
           if (!mbar_wait(smem_u32(&bars->empty[stage]), phase ^ 1u, abort_flag)) {
             report_error(err, ATENIA_ERR_DEVICE_TIMEOUT, 2600 + stage);
             *abort_flag = 1;
@@ -225,7 +236,7 @@ grouped_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const CUt
             break;
           }
           const uint32_t full = smem_u32(&bars->full[stage]);
-          const uint32_t sw = smem_base + stage * D_STAGE_BYTES;
+          const uint32_t sw = smem_base + stage * STAGE_BYTES;
           if (I8) {
             // the four digit planes of the tile's tokens, 16 rows per copy: MMA column p * tokp + t
             const int tokp = (it.rows() + 15) & ~15;
@@ -236,6 +247,15 @@ grouped_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const CUt
               for (int c = 0; c < tokp; c += 16)
                 tma_load_2d(sw + 2 * D_W_BYTES + (p * tokp + c) * 128, &tmap_x, full, kb * BKE,
                             p * plane_rows + tc.row0 + c);
+          } else if (WIDE) {
+            // the tile's token rows in copies of 64 (a copy that runs past the group's rows brings rows of
+            // the next group: columns the epilogue never stores)
+            const int nbox = (it.rows() + 63) / 64;
+            mbar_expect_tx(full, 2 * D_W_BYTES + nbox * 64 * 128);
+            tma_load_2d(sw, m0, full, kb * BK, tc.n0);
+            tma_load_2d(sw + D_W_BYTES, m1, full, kb * BK, n1);
+            for (int b = 0; b < nbox; ++b)
+              tma_load_2d(sw + 2 * D_W_BYTES + b * 64 * 128, &tmap_x, full, kb * BK, tc.row0 + 64 * b);
           } else {
             mbar_expect_tx(full, D_STAGE_BYTES);
             tma_load_2d(sw, m0, full, kb * BK, tc.n0);
@@ -246,9 +266,9 @@ grouped_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const CUt
         }
       }
       if (*abort_flag) {
-        const int stage = idx % D_STAGES;
-        const uint32_t phase = (idx / D_STAGES) & 1u;
-        for (int s = 0; s < D_STAGES; ++s) {
+        const int stage = idx % STAGES;
+        const uint32_t phase = (idx / STAGES) & 1u;
+        for (int s = 0; s < STAGES; ++s) {
           if (!(armed & (1u << s))) continue;
           const uint32_t par = (s < stage) ? phase : (phase ^ 1u);
           for (uint32_t i = 0; i < (1u << 20); ++i)
@@ -272,10 +292,10 @@ grouped_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const CUt
         tc_fence_after();
         const int tokp = (it.rows() + 15) & ~15;
         const uint32_t idesc = I8 ? idesc_dec_i8(kDigitPlanes * tokp) : idesc_dec(tokp);
-        const uint32_t d0 = tmem_base + acc * 2 * DTN, d1 = d0 + DTN;
+        const uint32_t d0 = tmem_base + acc * 2 * ACOLS, d1 = d0 + ACOLS;
         for (int kb = it.kb0; kb < it.kb0 + it.nkb; ++kb, ++idx) {
-          const int stage = idx % D_STAGES;
-          const uint32_t phase = (idx / D_STAGES) & 1u;
+          const int stage = idx % STAGES;
+          const uint32_t phase = (idx / STAGES) & 1u;
           if (!mbar_wait(smem_u32(&bars->full[stage]), phase, abort_flag)) {
             report_error(err, ATENIA_ERR_DEVICE_TIMEOUT, 2710 + stage);
             *abort_flag = 1;
@@ -283,7 +303,7 @@ grouped_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const CUt
             break;
           }
           tc_fence_after();
-          const uint32_t sw = smem_base + stage * D_STAGE_BYTES;
+          const uint32_t sw = smem_base + stage * STAGE_BYTES;
           const uint64_t da0 = make_smem_desc(sw), da1 = make_smem_desc(sw + D_W_BYTES);
           const uint64_t db = make_smem_desc(sw + 2 * D_W_BYTES);
 #pragma unroll
@@ -302,7 +322,7 @@ grouped_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const CUt
         }
         if (ok) tc_commit(smem_u32(&bars->acc_full[acc]));
         acc_phase[acc] ^= 1u;
-        acc ^= 1;
+        if (!WIDE) acc ^= 1;  // (wide: the one buffer again, once the epilogue has drained it)
       }
     }
   } else if (warp >= 4) {
@@ -324,7 +344,7 @@ grouped_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const CUt
       acc_phase[acc] ^= 1u;
       tc_fence_after();
       const int rows = it.rows();
-      const uint32_t t0 = tmem_base + (uint32_t(quarter * 32) << 16) + acc * 2 * DTN, t1 = t0 + DTN;
+      const uint32_t t0 = tmem_base + (uint32_t(quarter * 32) << 16) + acc * 2 * ACOLS, t1 = t0 + ACOLS;
       if (I8) {
         // INT8 form: column p * tokp + t of an accumulator is digit plane p of token t (int32, exact)
         const int tokp = (rows + 15) & ~15;
@@ -434,7 +454,7 @@ grouped_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const CUt
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bars->acc_empty[acc]));
-      acc ^= 1;
+      if (!WIDE) acc ^= 1;
     }
   }
 
@@ -512,11 +532,11 @@ __global__ void __launch_bounds__(DROWS * kReduceTokLanes) decode_splitk_reduce_
   }
 }
 
-template <int MODE, bool I8>
+template <int MODE, bool I8, bool WIDE = false>
 int launch_dec_one(const GroupedGemmArgs& a, int num_sms, cudaStream_t s) {
   static bool attr_set[kMaxDevices] = {};
   if (first_use_on_current_device(attr_set)) {
-    ATENIA_CUDA_TRY(cudaFuncSetAttribute(grouped_gemm_decode_kernel<MODE, I8>,
+    ATENIA_CUDA_TRY(cudaFuncSetAttribute(grouped_gemm_decode_kernel<MODE, I8, WIDE>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, D_SMEM_BYTES));
   }
   // stream-K where a workspace slot can hold every piece (bf16: every group fits one 128-token tile;
@@ -526,8 +546,8 @@ int launch_dec_one(const GroupedGemmArgs& a, int num_sms, cudaStream_t s) {
   const int n_tiles = (a.N + BN_OUT - 1) / BN_OUT;
   const int active_groups = a.max_rows < a.num_groups ? a.max_rows : a.num_groups;
   const int max_tok_tiles = I8 ? active_groups + a.max_rows / TROWS : active_groups;
-  const bool splitk = a.splitk_ws != nullptr && (I8 || a.max_rows <= DTN) && max_tok_tiles * n_tiles < 4 * num_sms;
-  grouped_gemm_decode_kernel<MODE, I8><<<dim3(num_sms), dim3(D_THREADS), D_SMEM_BYTES, s>>>(
+  const bool splitk = !WIDE && a.splitk_ws != nullptr && (I8 || a.max_rows <= DTN) && max_tok_tiles * n_tiles < 4 * num_sms;
+  grouped_gemm_decode_kernel<MODE, I8, WIDE><<<dim3(num_sms), dim3(D_THREADS), D_SMEM_BYTES, s>>>(
       a.tmap_a, a.tmap_b0, MODE == kSwiGLU ? a.tmap_b1 : a.tmap_b0, a.group_offsets, a.num_groups, a.N, a.K, a.out,
       a.err, splitk ? 1 : 0, a.splitk_ws, a.scale0, a.scale1, a.tok_scale, a.plane_rows);
   int rc = (int)cudaGetLastError();
@@ -638,6 +658,16 @@ int launch_grouped_gemm_bf16_decode(const GroupedGemmArgs& a, int num_sms, cudaS
   if (a.num_groups <= 0) return ATENIA_OK;
   if (a.N % 16 != 0 || a.K % 16 != 0) return ATENIA_ERR_SHAPE;
   int rc = a.mode == kSwiGLU ? launch_dec_one<kSwiGLU, false>(a, num_sms, s) : launch_dec_one<kPlain, false>(a, num_sms, s);
+  count_launch();
+  count_tcgen05_launch();
+  return rc;
+}
+
+int launch_grouped_gemm_bf16_wide(const GroupedGemmArgs& a, int num_sms, cudaStream_t s) {
+  if (a.num_groups <= 0) return ATENIA_OK;
+  if (a.N % 16 != 0 || a.K % 16 != 0) return ATENIA_ERR_SHAPE;
+  int rc = a.mode == kSwiGLU ? launch_dec_one<kSwiGLU, false, true>(a, num_sms, s)
+                             : launch_dec_one<kPlain, false, true>(a, num_sms, s);
   count_launch();
   count_tcgen05_launch();
   return rc;
