@@ -212,60 +212,71 @@ grouped_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const CUt
 
   if (warp == 0) {
     // ================= TMA producer =================
-    if (lane == 0) {
+    // All lanes of the warp walk the same piece list.  Lane 0 waits for the stage and arms its barrier;
+    // then lane c issues copy c of the stage (0 and 1: the two weight tiles, 2 and up: the token rows), so
+    // that the issue latencies of a stage's copies overlap instead of adding up in one thread (a stage of
+    // the INT8 form has up to ten copies, of the wide form up to six).
+    {
       uint32_t idx = 0;
       int last_group = -1;
       uint32_t armed = 0;
       bool ok = true;
       while (ok && it.next()) {
-        if (tc.group != last_group) {
-          tmap_acquire(&tmap_w0[tc.group]);
-          if (MODE == kSwiGLU) tmap_acquire(&tmap_w1[tc.group]);
-          last_group = tc.group;
-        }
         const CUtensorMap* m0 = &tmap_w0[tc.group];
         const CUtensorMap* m1 = (MODE == kSwiGLU) ? &tmap_w1[tc.group] : m0;
+        if (tc.group != last_group) {
+          if (lane == 0) tmap_acquire(m0);
+          if (lane == 1) tmap_acquire(m1);
+          last_group = tc.group;
+        }
         const int n1 = (MODE == kSwiGLU) ? tc.n0 : tc.n0 + DROWS;
+        // copies of token rows per stage, and the stage's bytes
+        const int tokp = (it.rows() + 15) & ~15;
+        const int cpp = tokp / 16;  // INT8: copies per digit plane (16 rows each)
+        const int n_x = I8 ? kDigitPlanes * cpp : (WIDE ? (it.rows() + 63) / 64 : 1);
+        const uint32_t bytes = I8 ? 2 * D_W_BYTES + kDigitPlanes * tokp * 128
+                                  : (WIDE ? 2 * D_W_BYTES + n_x * 64 * 128 : (uint32_t)D_STAGE_BYTES);
         for (int kb = it.kb0; kb < it.kb0 + it.nkb; ++kb, ++idx) {
           const int stage = idx % STAGES;
           const uint32_t phase = (idx / STAGES) & 1u;
-          if (!mbar_wait(smem_u32(&bars->empty[stage]), phase ^ 1u, abort_flag)) {
-            report_error(err, ATENIA_ERR_DEVICE_TIMEOUT, 2600 + stage);
-            *abort_flag = 1;
+          int got = 1;
+          if (lane == 0) got = mbar_wait(smem_u32(&bars->empty[stage]), phase ^ 1u, abort_flag) ? 1 : 0;
+          got = __shfl_sync(0xffffffffu, got, 0);
+          if (!got) {
+            if (lane == 0) {
+              report_error(err, ATENIA_ERR_DEVICE_TIMEOUT, 2600 + stage);
+              *abort_flag = 1;
+            }
             ok = false;
             break;
           }
           const uint32_t full = smem_u32(&bars->full[stage]);
           const uint32_t sw = smem_base + stage * STAGE_BYTES;
-          if (I8) {
-            // the four digit planes of the tile's tokens, 16 rows per copy: MMA column p * tokp + t
-            const int tokp = (it.rows() + 15) & ~15;
-            mbar_expect_tx(full, 2 * D_W_BYTES + kDigitPlanes * tokp * 128);
+          if (lane == 0) mbar_expect_tx(full, bytes);
+          __syncwarp();
+          if (lane == 0) {
             tma_load_2d(sw, m0, full, kb * BKE, tc.n0);
+          } else if (lane == 1) {
             tma_load_2d(sw + D_W_BYTES, m1, full, kb * BKE, n1);
-            for (int p = 0; p < kDigitPlanes; ++p)
-              for (int c = 0; c < tokp; c += 16)
-                tma_load_2d(sw + 2 * D_W_BYTES + (p * tokp + c) * 128, &tmap_x, full, kb * BKE,
-                            p * plane_rows + tc.row0 + c);
-          } else if (WIDE) {
-            // the tile's token rows in copies of 64 (a copy that runs past the group's rows brings rows of
-            // the next group: columns the epilogue never stores)
-            const int nbox = (it.rows() + 63) / 64;
-            mbar_expect_tx(full, 2 * D_W_BYTES + nbox * 64 * 128);
-            tma_load_2d(sw, m0, full, kb * BK, tc.n0);
-            tma_load_2d(sw + D_W_BYTES, m1, full, kb * BK, n1);
-            for (int b = 0; b < nbox; ++b)
-              tma_load_2d(sw + 2 * D_W_BYTES + b * 64 * 128, &tmap_x, full, kb * BK, tc.row0 + 64 * b);
-          } else {
-            mbar_expect_tx(full, D_STAGE_BYTES);
-            tma_load_2d(sw, m0, full, kb * BK, tc.n0);
-            tma_load_2d(sw + D_W_BYTES, m1, full, kb * BK, n1);
-            tma_load_2d(sw + 2 * D_W_BYTES, &tmap_x, full, kb * BK, tc.row0);
+          } else if (lane - 2 < n_x) {
+            const int c = lane - 2;
+            if (I8) {
+              // digit plane p, token rows 16 cc .. 16 cc + 15 of the tile: MMA columns p * tokp + 16 cc ...
+              const int p = c / cpp, cc = (c - p * cpp) * 16;
+              tma_load_2d(sw + 2 * D_W_BYTES + (p * tokp + cc) * 128, &tmap_x, full, kb * BKE,
+                          p * plane_rows + tc.row0 + cc);
+            } else if (WIDE) {
+              // 64 token rows per copy (a copy that runs past the group's rows brings rows of the next
+              // group: columns the epilogue never stores)
+              tma_load_2d(sw + 2 * D_W_BYTES + c * 64 * 128, &tmap_x, full, kb * BKE, tc.row0 + 64 * c);
+            } else {
+              tma_load_2d(sw + 2 * D_W_BYTES, &tmap_x, full, kb * BKE, tc.row0);
+            }
           }
           armed |= 1u << stage;
         }
       }
-      if (*abort_flag) {
+      if (lane == 0 && *abort_flag) {
         const int stage = idx % STAGES;
         const uint32_t phase = (idx / STAGES) & 1u;
         for (int s = 0; s < STAGES; ++s) {
