@@ -605,7 +605,7 @@ __device__ __forceinline__ void amax_of_vector(const uint4& q, float& amax, bool
   }
 }
 
-__global__ void __launch_bounds__(kQThreads) quantize_digits_kernel(const __nv_bfloat16* __restrict__ x,
+__global__ void __launch_bounds__(kQThreads) quantize_digits_kernel(DigitSource src,
                                                                     const int32_t* __restrict__ n_rows_dev, int n_rows,
                                                                     int K, int plane_rows, int8_t* __restrict__ planes,
                                                                     float* __restrict__ tok_scale) {
@@ -613,9 +613,21 @@ __global__ void __launch_bounds__(kQThreads) quantize_digits_kernel(const __nv_b
   // rows the dispatch did not place (invalid expert ids) hold nothing: skip them
   const int placed = n_rows_dev ? (*n_rows_dev < n_rows ? *n_rows_dev : n_rows) : n_rows;
   if (row >= placed) return;
+  // dispatch row `row` is token perm[row] / k of the caller's batch (gather and digits in one pass)
+  const int srow = src.perm ? src.perm[row] / src.k : row;
+  if (srow < 0 || srow >= src.n_src_rows) return;
   __shared__ float red[kQThreads / 32];
   __shared__ float mul_s;
-  const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * K);
+  // vector v of the row: eight consecutive elements as bf16 (f32 input is rounded to nearest even first,
+  // as the row gather does)
+  auto load_vec = [&](int v) -> uint4 {
+    if (src.x_is_f32) {
+      const float4* p = reinterpret_cast<const float4*>(static_cast<const float*>(src.x) + (size_t)srow * K) + 2 * v;
+      const float4 a = p[0], b = p[1];
+      return make_uint4(pack_bf16x2(a.x, a.y), pack_bf16x2(a.z, a.w), pack_bf16x2(b.x, b.y), pack_bf16x2(b.z, b.w));
+    }
+    return reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(src.x) + (size_t)srow * K)[v];
+  };
   const int nvec = K / 8;
   uint4 keep[kQVecs];
   float amax = 0.f;
@@ -623,11 +635,11 @@ __global__ void __launch_bounds__(kQThreads) quantize_digits_kernel(const __nv_b
 #pragma unroll
   for (int j = 0; j < kQVecs; ++j) {
     const int v = threadIdx.x + j * kQThreads;
-    keep[j] = v < nvec ? xr[v] : make_uint4(0, 0, 0, 0);
+    keep[j] = v < nvec ? load_vec(v) : make_uint4(0, 0, 0, 0);
   }
 #pragma unroll
   for (int j = 0; j < kQVecs; ++j) amax_of_vector(keep[j], amax, bad);
-  for (int v = threadIdx.x + kQVecs * kQThreads; v < nvec; v += kQThreads) amax_of_vector(xr[v], amax, bad);
+  for (int v = threadIdx.x + kQVecs * kQThreads; v < nvec; v += kQThreads) amax_of_vector(load_vec(v), amax, bad);
   if (bad) amax = __int_as_float(0x7f800000);
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
@@ -660,7 +672,8 @@ __global__ void __launch_bounds__(kQThreads) quantize_digits_kernel(const __nv_b
     const int v = threadIdx.x + j * kQThreads;
     if (v < nvec) digits_of_vector(keep[j], mul, prow, plane, v);
   }
-  for (int v = threadIdx.x + kQVecs * kQThreads; v < nvec; v += kQThreads) digits_of_vector(xr[v], mul, prow, plane, v);
+  for (int v = threadIdx.x + kQVecs * kQThreads; v < nvec; v += kQThreads)
+    digits_of_vector(load_vec(v), mul, prow, plane, v);
 }
 
 }  // namespace
@@ -694,11 +707,11 @@ int launch_grouped_gemm_w8_i8_decode(const GroupedGemmArgs& a, int num_sms, cuda
   return rc;
 }
 
-int launch_quantize_digits(const __nv_bfloat16* x, const int32_t* n_rows_dev, int n_rows, int K, int plane_rows,
+int launch_quantize_digits(const DigitSource& src, const int32_t* n_rows_dev, int n_rows, int K, int plane_rows,
                            int8_t* planes, float* tok_scale, cudaStream_t s) {
   if (n_rows <= 0) return ATENIA_OK;
-  if (K % 16 != 0 || n_rows > plane_rows) return ATENIA_ERR_SHAPE;
-  quantize_digits_kernel<<<n_rows, kQThreads, 0, s>>>(x, n_rows_dev, n_rows, K, plane_rows, planes, tok_scale);
+  if (K % 16 != 0 || n_rows > plane_rows || !src.x || (src.perm && src.k < 1)) return ATENIA_ERR_SHAPE;
+  quantize_digits_kernel<<<n_rows, kQThreads, 0, s>>>(src, n_rows_dev, n_rows, K, plane_rows, planes, tok_scale);
   count_launch();
   return (int)cudaGetLastError();
 }

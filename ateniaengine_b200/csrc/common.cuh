@@ -203,9 +203,17 @@ int launch_grouped_gemm_bf16_wide(const GroupedGemmArgs& a, int num_sms, cudaStr
 constexpr int kI8DecodeMaxRows = 512;      // largest call (rows of one digit plane) a layer may be set up for
 constexpr int kI8DecodeDefaultRows = 128;  // ... and what a layer takes unless told otherwise
 int launch_grouped_gemm_w8_i8_decode(const GroupedGemmArgs& a, int num_sms, cudaStream_t s);
-// planes [4][plane_rows][K] int8 and tok_scale [plane_rows] from bf16 rows x [n_rows, K]; n_rows_dev
-// (device, may be null) bounds the rows that hold data
-int launch_quantize_digits(const __nv_bfloat16* x, const int32_t* n_rows_dev, int n_rows, int K, int plane_rows,
+// planes [4][plane_rows][K] int8 and tok_scale [plane_rows] of n_rows rows; n_rows_dev (device, may be null)
+// bounds the rows that hold data.  Row r comes from row r of src.x, or -- with src.perm, the dispatch
+// permutation -- from token row perm[r] / k of the caller's batch (the row gather and the digits in one pass).
+struct DigitSource {
+  const void* x;        // [n_src_rows, K], bf16 or f32
+  int x_is_f32;
+  const int32_t* perm;  // null: no gather
+  int k;
+  int n_src_rows;
+};
+int launch_quantize_digits(const DigitSource& src, const int32_t* n_rows_dev, int n_rows, int K, int plane_rows,
                            int8_t* planes, float* tok_scale, cudaStream_t s);
 // bf16 weights, CTA pairs (tcgen05 cta_group::2): 256-row tiles, each CTA stages half of the weight tile
 int launch_grouped_gemm_2cta(const GroupedGemmArgs& a, int num_sms, cudaStream_t s);

@@ -102,6 +102,8 @@ struct AteniaMoeLayer {
   float* dq_ts_x = nullptr;
   float* dq_ts_h = nullptr;
   CUtensorMap tm_dq_x{}, tm_dq_h{};
+  atenia::DigitSource i8_src{};  // the caller's batch and the permutation, when the digit kernel does the row gather
+  bool i8_src_set = false;
   float* splitk_ws_shared = nullptr;  // the same for the shared expert's launches (INT8 with a shared expert)
   CUtensorMap tm_x_perm{}, tm_h{}, tm_h_shared{};
 

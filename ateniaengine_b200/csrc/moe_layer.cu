@@ -80,9 +80,13 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
   const bool i8dec = q && L->w8_i8 && L->dq_x && max_rows <= L->i8_rows && !L->use_check_gemm && L->w8_mode == 0;
   const bool gemv = L->use_gemv && max_rows <= L->gemv_rows && !L->use_check_gemm && !i8dec;
   if (L->timing) cudaEventRecord(L->ev[0], s);
+  // (set by the forward when it left the row gather to the digit kernel; consumed here)
+  const bool gather_here = L->i8_src_set && a_ptr == L->x_perm;
+  L->i8_src_set = false;
   if (i8dec) {
-    int rc = launch_quantize_digits(a_ptr, group_offsets + num_groups, max_rows, c.d_model, L->i8_rows, L->dq_x,
-                                    L->dq_ts_x, s);
+    const DigitSource own{a_ptr, 0, nullptr, 1, max_rows};
+    int rc = launch_quantize_digits(gather_here ? L->i8_src : own, group_offsets + num_groups, max_rows, c.d_model,
+                                    L->i8_rows, L->dq_x, L->dq_ts_x, s);
     if (rc) return rc;
     GroupedGemmArgs g1{};
     g1.tmap_a = L->tm_dq_x;
@@ -105,7 +109,9 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
     rc = launch_grouped_gemm_w8_i8_decode(g1, L->num_sms, s);
     if (rc) return rc;
     if (L->timing) cudaEventRecord(L->ev[1], s);
-    rc = launch_quantize_digits(mid, group_offsets + num_groups, max_rows, c.d_ff, L->i8_rows, L->dq_h, L->dq_ts_h, s);
+    const DigitSource mid_rows{mid, 0, nullptr, 1, max_rows};
+    rc = launch_quantize_digits(mid_rows, group_offsets + num_groups, max_rows, c.d_ff, L->i8_rows, L->dq_h, L->dq_ts_h,
+                                s);
     if (rc) return rc;
     GroupedGemmArgs g2 = g1;
     g2.tmap_a = L->tm_dq_h;
@@ -748,9 +754,14 @@ static int forward_impl(AteniaMoeLayer* L, const void* x, int x_dtype, int T, vo
   const bool need_xb = x_f32 && L->has_shared && !shared_aside;  // (aside: converted at the start already)
   // the direct expert-parallel exchange gathers rows straight into the owners' buffers
   const bool direct = c.ep_world > 1 && !L->ep_replicated && L->ep_direct;
-  rc = launch_gather_rows(x, x_f32, L->perm, L->expert_offsets + c.num_experts, direct ? 0 : n, k, c.d_model,
-                          L->x_perm, need_xb ? L->x_bf16 : nullptr, T, s);
+  // an INT8 decode call (integer-MMA kernel) never reads x_perm: its digit kernel gathers the rows itself
+  const bool i8_gather = c.weight_dtype == ATENIA_W_INT8_ROW && L->w8_i8 && L->dq_x && n <= L->i8_rows &&
+                         !L->use_check_gemm && L->w8_mode == 0 && (c.ep_world == 1 || L->ep_replicated);
+  rc = launch_gather_rows(x, x_f32, L->perm, L->expert_offsets + c.num_experts, (direct || i8_gather) ? 0 : n, k,
+                          c.d_model, L->x_perm, need_xb ? L->x_bf16 : nullptr, T, s);
   if (rc) return rc;
+  L->i8_src = DigitSource{x, x_f32 ? 1 : 0, L->perm, k, T};
+  L->i8_src_set = i8_gather;
   if (L->timing) cudaEventRecord(L->ph[1], s);
 
   if (c.ep_world == 1) {
