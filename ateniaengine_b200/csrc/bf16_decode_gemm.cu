@@ -20,6 +20,11 @@
 //               main loop of the next
 //   warps     : 0 TMA, 1 MMA + TMEM alloc, 4..11 epilogue (two warps per TMEM lane quarter)
 // All waits are bounded as in grouped_gemm.cu.
+// (A form of this kernel with 256-row token tiles for groups of a few hundred rows -- one tile per expert
+// instead of a full and a nearly empty 128-row tile -- was measured on B200 against the 128-row-tile kernel
+// of grouped_gemm.cu: Qwen1.5-MoE shape 2048 tokens 0.400 vs 0.416 ms, Mixtral shape 512 tokens 0.603 vs
+// 0.640 ms, but Mixtral 1024 tokens 0.993 vs 0.899 ms and DeepSeek-V2-Lite 4096 tokens 0.743 vs 0.649 ms;
+// it was removed.)
 //
 // INT8 form (template parameter I8).  Widening int8 codes to bf16 costs two to three instructions per
 // weight, and at decode sizes those instructions, not HBM, set the pace of the widening kernels (w8_gemm.cu,
@@ -149,13 +154,7 @@ struct DecPieces {
 // I8: tmap_x is the digit-plane map (uint8, box {128, 16}; plane p of row r at row p * plane_rows + r),
 // tmap_w0 / tmap_w1 are int8 maps with box {128, 128} and the 128-byte swizzle, scale0 / scale1 the
 // weight rows' scales per group and tok_scale the token rows' 2^(e - 26).
-//
-// WIDE (bf16 only): token tiles of up to 256 rows -- one tile for most experts of a many-expert layer at a
-// few thousand tokens, where 128-row tiles leave a second, nearly empty tile per expert that streams the
-// expert's weights through shared memory again.  The two accumulators then fill tensor memory (no second
-// buffer: the epilogue of a tile is not overlapped), the ring is 3 stages of 64 KiB, the token rows arrive in
-// 64-row copies (tmap_x has a 64-row box) and there is no stream-K.
-template <int MODE, bool I8, bool WIDE = false>
+template <int MODE, bool I8>
 __global__ void __launch_bounds__(D_THREADS, 1)
 grouped_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const CUtensorMap* __restrict__ tmap_w0,
                            const CUtensorMap* __restrict__ tmap_w1, const int32_t* __restrict__ group_offsets,
@@ -165,13 +164,11 @@ grouped_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const CUt
                            int plane_rows) {
   extern __shared__ uint8_t smem_raw[];
   constexpr int BN_OUT = (MODE == kSwiGLU) ? DROWS : 2 * DROWS;
-  static_assert(!(I8 && WIDE), "the wide form is bf16 only");
-  constexpr int BKE = I8 ? IBK : BK;                         // k elements per k-block
-  constexpr int TROWS = I8 ? ITOK : (WIDE ? 2 * DTN : DTN);  // token rows per tile
-  constexpr int ACOLS = WIDE ? 2 * DTN : DTN;                // tensor-memory columns of one accumulator
-  constexpr int STAGES = WIDE ? 3 : D_STAGES;
-  constexpr int STAGE_BYTES = WIDE ? 2 * D_W_BYTES + 2 * D_X_BYTES : D_STAGE_BYTES;  // 64 KiB : 48 KiB
-  static_assert(STAGES * STAGE_BYTES <= D_STAGES * D_STAGE_BYTES, "one shared-memory size for all forms");
+  constexpr int BKE = I8 ? IBK : BK;      // k elements per k-block
+  constexpr int TROWS = I8 ? ITOK : DTN;  // token rows per tile
+  constexpr int ACOLS = DTN;              // tensor-memory columns of one accumulator
+  constexpr int STAGES = D_STAGES;
+  constexpr int STAGE_BYTES = D_STAGE_BYTES;
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
   BarriersDec* bars = reinterpret_cast<BarriersDec*>(smem_aligned + D_STAGES * D_STAGE_BYTES);
@@ -215,7 +212,7 @@ grouped_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const CUt
     // All lanes of the warp walk the same piece list.  Lane 0 waits for the stage and arms its barrier;
     // then lane c issues copy c of the stage (0 and 1: the two weight tiles, 2 and up: the token rows), so
     // that the issue latencies of a stage's copies overlap instead of adding up in one thread (a stage of
-    // the INT8 form has up to ten copies, of the wide form up to six).
+    // the INT8 form has up to ten copies).  Measured: no different from one issuing thread.
     {
       uint32_t idx = 0;
       int last_group = -1;
@@ -233,9 +230,8 @@ grouped_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const CUt
         // copies of token rows per stage, and the stage's bytes
         const int tokp = (it.rows() + 15) & ~15;
         const int cpp = tokp / 16;  // INT8: copies per digit plane (16 rows each)
-        const int n_x = I8 ? kDigitPlanes * cpp : (WIDE ? (it.rows() + 63) / 64 : 1);
-        const uint32_t bytes = I8 ? 2 * D_W_BYTES + kDigitPlanes * tokp * 128
-                                  : (WIDE ? 2 * D_W_BYTES + n_x * 64 * 128 : (uint32_t)D_STAGE_BYTES);
+        const int n_x = I8 ? kDigitPlanes * cpp : 1;
+        const uint32_t bytes = I8 ? 2 * D_W_BYTES + kDigitPlanes * tokp * 128 : (uint32_t)D_STAGE_BYTES;
         for (int kb = it.kb0; kb < it.kb0 + it.nkb; ++kb, ++idx) {
           const int stage = idx % STAGES;
           const uint32_t phase = (idx / STAGES) & 1u;
@@ -265,10 +261,6 @@ grouped_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const CUt
               const int p = c / cpp, cc = (c - p * cpp) * 16;
               tma_load_2d(sw + 2 * D_W_BYTES + (p * tokp + cc) * 128, &tmap_x, full, kb * BKE,
                           p * plane_rows + tc.row0 + cc);
-            } else if (WIDE) {
-              // 64 token rows per copy (a copy that runs past the group's rows brings rows of the next
-              // group: columns the epilogue never stores)
-              tma_load_2d(sw + 2 * D_W_BYTES + c * 64 * 128, &tmap_x, full, kb * BKE, tc.row0 + 64 * c);
             } else {
               tma_load_2d(sw + 2 * D_W_BYTES, &tmap_x, full, kb * BKE, tc.row0);
             }
@@ -333,7 +325,7 @@ grouped_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const CUt
         }
         if (ok) tc_commit(smem_u32(&bars->acc_full[acc]));
         acc_phase[acc] ^= 1u;
-        if (!WIDE) acc ^= 1;  // (wide: the one buffer again, once the epilogue has drained it)
+        acc ^= 1;
       }
     }
   } else if (warp >= 4) {
@@ -465,7 +457,7 @@ grouped_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const CUt
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bars->acc_empty[acc]));
-      if (!WIDE) acc ^= 1;
+      acc ^= 1;
     }
   }
 
@@ -543,11 +535,11 @@ __global__ void __launch_bounds__(DROWS * kReduceTokLanes) decode_splitk_reduce_
   }
 }
 
-template <int MODE, bool I8, bool WIDE = false>
+template <int MODE, bool I8>
 int launch_dec_one(const GroupedGemmArgs& a, int num_sms, cudaStream_t s) {
   static bool attr_set[kMaxDevices] = {};
   if (first_use_on_current_device(attr_set)) {
-    ATENIA_CUDA_TRY(cudaFuncSetAttribute(grouped_gemm_decode_kernel<MODE, I8, WIDE>,
+    ATENIA_CUDA_TRY(cudaFuncSetAttribute(grouped_gemm_decode_kernel<MODE, I8>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, D_SMEM_BYTES));
   }
   // stream-K where a workspace slot can hold every piece (bf16: every group fits one 128-token tile;
@@ -557,8 +549,8 @@ int launch_dec_one(const GroupedGemmArgs& a, int num_sms, cudaStream_t s) {
   const int n_tiles = (a.N + BN_OUT - 1) / BN_OUT;
   const int active_groups = a.max_rows < a.num_groups ? a.max_rows : a.num_groups;
   const int max_tok_tiles = I8 ? active_groups + a.max_rows / TROWS : active_groups;
-  const bool splitk = !WIDE && a.splitk_ws != nullptr && (I8 || a.max_rows <= DTN) && max_tok_tiles * n_tiles < 4 * num_sms;
-  grouped_gemm_decode_kernel<MODE, I8, WIDE><<<dim3(num_sms), dim3(D_THREADS), D_SMEM_BYTES, s>>>(
+  const bool splitk = a.splitk_ws != nullptr && (I8 || a.max_rows <= DTN) && max_tok_tiles * n_tiles < 4 * num_sms;
+  grouped_gemm_decode_kernel<MODE, I8><<<dim3(num_sms), dim3(D_THREADS), D_SMEM_BYTES, s>>>(
       a.tmap_a, a.tmap_b0, MODE == kSwiGLU ? a.tmap_b1 : a.tmap_b0, a.group_offsets, a.num_groups, a.N, a.K, a.out,
       a.err, splitk ? 1 : 0, a.splitk_ws, a.scale0, a.scale1, a.tok_scale, a.plane_rows);
   int rc = (int)cudaGetLastError();
@@ -682,16 +674,6 @@ int launch_grouped_gemm_bf16_decode(const GroupedGemmArgs& a, int num_sms, cudaS
   if (a.num_groups <= 0) return ATENIA_OK;
   if (a.N % 16 != 0 || a.K % 16 != 0) return ATENIA_ERR_SHAPE;
   int rc = a.mode == kSwiGLU ? launch_dec_one<kSwiGLU, false>(a, num_sms, s) : launch_dec_one<kPlain, false>(a, num_sms, s);
-  count_launch();
-  count_tcgen05_launch();
-  return rc;
-}
-
-int launch_grouped_gemm_bf16_wide(const GroupedGemmArgs& a, int num_sms, cudaStream_t s) {
-  if (a.num_groups <= 0) return ATENIA_OK;
-  if (a.N % 16 != 0 || a.K % 16 != 0) return ATENIA_ERR_SHAPE;
-  int rc = a.mode == kSwiGLU ? launch_dec_one<kSwiGLU, false, true>(a, num_sms, s)
-                             : launch_dec_one<kPlain, false, true>(a, num_sms, s);
   count_launch();
   count_tcgen05_launch();
   return rc;

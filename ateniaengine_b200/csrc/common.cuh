@@ -193,9 +193,6 @@ int launch_grouped_gemm_w8_m256(const GroupedGemmArgs& a, int num_sms, cudaStrea
 // the SMs; tmap_a / tmap_b0 / tmap_b1 are the maps of launch_grouped_gemm_tcgen05, splitk_ws as for
 // the INT8 tensor-memory kernel (null: whole tiles only).
 int launch_grouped_gemm_bf16_decode(const GroupedGemmArgs& a, int num_sms, cudaStream_t s);
-// bf16 weights, groups of a few hundred rows (same file, WIDE form): the same transposed product with
-// token tiles of up to 256 rows.  tmap_a must have a 64-row box (box {64, 64}); no stream-K.
-int launch_grouped_gemm_bf16_wide(const GroupedGemmArgs& a, int num_sms, cudaStream_t s);
 // INT8 weights, calls of at most kI8DecodeMaxRows rows (same file): the codes are multiplied as integers
 // (tcgen05 kind::i8) with the token rows split into four planes of base-128 digits by
 // launch_quantize_digits.  tmap_a is the digit-plane map (uint8, box {128, 16}, 128B swizzle; plane p of

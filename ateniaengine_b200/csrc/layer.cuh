@@ -90,8 +90,6 @@ struct AteniaMoeLayer {
   float* splitk_ws = nullptr;  // stream-K partial sums of the decode kernels, 2 slots per SM
   // INT8, integer-MMA decode kernel: weight maps (box {128, 128}, 128B swizzle), digit planes [4][128][K] of
   // the token rows and of the intermediate rows with their row scales, and the planes' tensor maps
-  bool bf16_wide = false;  // bf16 groups of a few hundred rows: 256-row token tiles (bf16_decode_gemm.cu, WIDE form)
-  CUtensorMap tm_x_perm64{}, tm_h64{};  // the dispatch buffers with a 64-row box
   bool w8_i8 = true;
   int i8_rows = 128;  // rows of one digit plane = the largest call the kernel takes
   CUtensorMap* d_tm_gate_i8 = nullptr;

@@ -66,10 +66,6 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
   const bool dec = !q && !L->use_check_gemm && L->splitk_ws &&
                    (L->bf16_decode == 1 ? max_rows <= 128 : (L->bf16_decode < 0 && max_rows <= 16));
   const bool pairs = !q && !dec && (L->pair_mode == 1 || (L->pair_mode == 0 && max_rows >= 512 * num_groups));
-  // bf16, groups of a few hundred rows at most (many experts, or a medium batch): the transposed product
-  // with token tiles of up to 256 rows -- an expert's weights pass through shared memory once instead of
-  // once per 128-row tile (ATENIA_MOE_BF16_WIDE=1; only on the layer's own dispatch buffers)
-  const bool wide = !q && !dec && !pairs && L->bf16_wide && !L->use_check_gemm && a_ptr == L->x_perm && mid == L->h;
   // a call of at most two rows in all (decode at batch 1) is a stream over the touched experts' weights:
   // the CUDA-core matrix-vector kernel (ATENIA_MOE_GEMV=0 keeps the tensor-core kernels: A/B runs)
   // INT8, calls of at most i8_rows rows (decode): the codes multiplied as integers against digit planes of
@@ -140,7 +136,7 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
     if (rc) return rc;
   } else {
     GroupedGemmArgs g1{};
-    g1.tmap_a = wide ? L->tm_x_perm64 : tm_a;
+    g1.tmap_a = tm_a;
     g1.tmap_b0 = tmem ? L->d_tm_gate_sw : L->d_tm_gate;
     g1.tmap_b1 = tmem ? L->d_tm_up_sw : L->d_tm_up;
     g1.group_offsets = group_offsets;
@@ -156,7 +152,6 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
     g1.w8 = q;
     g1.splitk_ws = L->splitk_ws;
     int rc = m256 ? launch_grouped_gemm_w8_m256(g1, L->num_sms, s)
-                  : wide ? launch_grouped_gemm_bf16_wide(g1, L->num_sms, s)
                   : dec ? launch_grouped_gemm_bf16_decode(g1, L->num_sms, s)
                   : tmem ? launch_grouped_gemm_w8_tmem(g1, L->num_sms, s)
                          : pairs ? launch_grouped_gemm_2cta(g1, L->num_sms, s)
@@ -171,7 +166,7 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
     if (rc) return rc;
   } else {
     GroupedGemmArgs g2{};
-    g2.tmap_a = wide ? L->tm_h64 : tm_mid;
+    g2.tmap_a = tm_mid;
     g2.tmap_b0 = tmem ? L->d_tm_down_sw : L->d_tm_down;
     g2.tmap_b1 = g2.tmap_b0;
     g2.group_offsets = group_offsets;
@@ -187,7 +182,6 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
     g2.w8 = q;
     g2.splitk_ws = L->splitk_ws;
     int rc = m256 ? launch_grouped_gemm_w8_m256(g2, L->num_sms, s)
-                  : wide ? launch_grouped_gemm_bf16_wide(g2, L->num_sms, s)
                   : dec ? launch_grouped_gemm_bf16_decode(g2, L->num_sms, s)
                   : tmem ? launch_grouped_gemm_w8_tmem(g2, L->num_sms, s)
                          : pairs ? launch_grouped_gemm_2cta(g2, L->num_sms, s)
@@ -309,7 +303,6 @@ int atenia_moe_create(const AteniaMoeConfig* cfg, AteniaMoeLayer** out) {
   L->pair_mode = std::getenv("ATENIA_MOE_PAIR_MODE") ? std::atoi(std::getenv("ATENIA_MOE_PAIR_MODE")) : 0;
   L->shared_aside = !(std::getenv("ATENIA_MOE_SHARED_ASIDE") && std::atoi(std::getenv("ATENIA_MOE_SHARED_ASIDE")) == 0);
   L->use_gemv = !(std::getenv("ATENIA_MOE_GEMV") && std::atoi(std::getenv("ATENIA_MOE_GEMV")) == 0);
-  L->bf16_wide = std::getenv("ATENIA_MOE_BF16_WIDE") && std::atoi(std::getenv("ATENIA_MOE_BF16_WIDE")) != 0;
   // ATENIA_MOE_W8_I8=0: INT8 decode calls keep the widening kernels; ATENIA_MOE_W8_I8_ROWS moves the row
   // count up to which the integer-MMA decode kernel is taken (16 .. kI8DecodeMaxRows; A/B runs)
   L->w8_i8 = !(std::getenv("ATENIA_MOE_W8_I8") && std::atoi(std::getenv("ATENIA_MOE_W8_I8")) == 0);
@@ -446,8 +439,6 @@ int atenia_moe_create(const AteniaMoeConfig* cfg, AteniaMoeLayer** out) {
   }
   rc = encode_tmap_2d_bf16(&L->tm_x_perm, L->x_perm, R, d, 128, 64);
   if (!rc && L->h) rc = encode_tmap_2d_bf16(&L->tm_h, L->h, R, F, 128, 64);
-  if (!rc) rc = encode_tmap_2d_bf16(&L->tm_x_perm64, L->x_perm, R, d, 64, 64);
-  if (!rc && L->h) rc = encode_tmap_2d_bf16(&L->tm_h64, L->h, R, F, 64, 64);
   if (!rc && L->dq_x) rc = encode_tmap_2d_u8(&L->tm_dq_x, L->dq_x, (uint64_t)4 * L->i8_rows, d, 16, 128, 2);
   if (!rc && L->dq_h) rc = encode_tmap_2d_u8(&L->tm_dq_h, L->dq_h, (uint64_t)4 * L->i8_rows, F, 16, 128, 2);
   if (!rc && L->has_shared) rc = encode_tmap_2d_bf16(&L->tm_h_shared, L->h_shared, Tm, Fs, 128, 64);
