@@ -17,8 +17,6 @@ def test_missing_peer_ends_with_an_error_status(layout):
     n = torch.cuda.device_count() if torch.cuda.is_available() else 0
     if n < 2:
         pytest.skip("needs at least 2 GPUs")
-    if layout == "flags" and not os.environ.get("ATENIA_TEST_EP_FLAGS"):
-        pytest.skip("flag-synchronised exchange: opt-in until it has run on hardware")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", ATENIA_MOE_EP_TIMEOUT_S="4")
     if layout == "flags":
         env.update(ATENIA_MOE_EP_FLAGS="1", ATENIA_MOE_EP_FLAG_TIMEOUT_MS="1500")

@@ -18,8 +18,6 @@ def test_direct_exchange_equals_single_gpu(name, port, flags):
     n = torch.cuda.device_count() if torch.cuda.is_available() else 0
     if n < 2:
         pytest.skip("needs at least 2 GPUs")
-    if flags and not os.environ.get("ATENIA_TEST_EP_FLAGS"):
-        pytest.skip("flag-synchronised exchange: opt-in until it has run on hardware")
     world = min(n, int(os.environ.get("ATENIA_EP_TEST_WORLD", "2")))
     # flags = 1: counts and completion epochs through the peers' memory instead of three collectives
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", ATENIA_MOE_EP_FLAGS=str(flags))
