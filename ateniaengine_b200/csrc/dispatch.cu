@@ -159,6 +159,75 @@ __global__ void __launch_bounds__(kSmallDispatchMax) dispatch_small_kernel(Dispa
   }
 }
 
+// Medium batches (at most 8192 entries): the same in ONE block that walks the entries in chunks of 1024 --
+// a histogram pass (shared-memory atomics; the order of additions does not matter for counts), the scan,
+// then per chunk the stable placement of dispatch_small_kernel on top of the counts of the chunks before.
+constexpr int kMediumDispatchMax = 8192;
+
+__global__ void __launch_bounds__(kSmallDispatchMax) dispatch_medium_kernel(DispatchArgs a) {
+  __shared__ int warp_cnt[kSmallDispatchMax / 32][kMaxE];  // current chunk: entries of expert e in warp w, then their base
+  __shared__ int offsets[kMaxE + 1];
+  __shared__ int hist[kMaxE];     // pass 1: entries per expert; pass 2: entries of the current chunk per expert
+  __shared__ int running[kMaxE];  // entries per expert placed by earlier chunks
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr int kWarps = kSmallDispatchMax / 32;
+  if (threadIdx.x < kMaxE) {
+    hist[threadIdx.x] = 0;
+    running[threadIdx.x] = 0;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < a.n; i += blockDim.x) {
+    const int e = a.topk_idx[i];
+    if (e >= 0 && e < a.E) atomicAdd(&hist[e], 1);
+    else report_error(a.err, ATENIA_ERR_ROUTING, 2002);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    offsets[0] = 0;
+    for (int x = 0; x < a.E; ++x) offsets[x + 1] = offsets[x] + hist[x];
+    if (a.extra_offsets) {
+      a.extra_offsets[0] = 0;
+      a.extra_offsets[1] = a.T;
+    }
+  }
+  __syncthreads();
+  for (int x = threadIdx.x; x <= a.E; x += blockDim.x) a.expert_offsets[x] = offsets[x];
+  for (int c0 = 0; c0 < a.n; c0 += kSmallDispatchMax) {
+    for (int j = threadIdx.x; j < kWarps * kMaxE; j += blockDim.x) (&warp_cnt[0][0])[j] = 0;
+    __syncthreads();
+    const int i = c0 + threadIdx.x;
+    int e = -1;
+    if (i < a.n) {
+      e = a.topk_idx[i];
+      if (e < 0 || e >= a.E) e = -1;  // (reported by the histogram pass)
+    }
+    const unsigned peers = __match_any_sync(0xffffffffu, e);
+    const int rank_in_warp = __popc(peers & ((1u << lane) - 1u));
+    if (e >= 0 && rank_in_warp == 0) warp_cnt[warp][e] = __popc(peers);
+    __syncthreads();
+    if (threadIdx.x < a.E) {
+      int run = 0;
+      for (int w = 0; w < kWarps; ++w) {
+        const int c = warp_cnt[w][threadIdx.x];
+        warp_cnt[w][threadIdx.x] = run;
+        run += c;
+      }
+      hist[threadIdx.x] = run;
+    }
+    __syncthreads();
+    if (e >= 0) {
+      const int pos = offsets[e] + running[e] + warp_cnt[warp][e] + rank_in_warp;
+      a.perm[pos] = i;
+      a.inv_perm[i] = pos;
+    } else if (i < a.n) {
+      a.inv_perm[i] = -1;
+    }
+    __syncthreads();
+    if (threadIdx.x < a.E) running[threadIdx.x] += hist[threadIdx.x];
+    // (the zeroing at the top of the next chunk is followed by a barrier before running[] is read again)
+  }
+}
+
 // Row gather: x_perm[r, :] = bf16(x[perm[r] / k, :]).  One warp per destination row, eight rows per
 // block in flight and a grid that loops; every lane keeps four 16-byte vectors in flight.  `placed`
 // points at expert_offsets[E], the number of rows the placement actually wrote: entries with an
@@ -229,6 +298,11 @@ int launch_dispatch(const DispatchArgs& a, cudaStream_t s) {
   if (a.n > 0 && a.n <= kSmallDispatchMax) {
     const int threads = ((a.n + 31) / 32 * 32) < a.E ? ((a.E + 31) / 32 * 32) : ((a.n + 31) / 32 * 32);
     dispatch_small_kernel<<<1, threads, 0, s>>>(a);
+    count_launch();
+    return (int)cudaGetLastError();
+  }
+  if (a.n > kSmallDispatchMax && a.n <= kMediumDispatchMax) {
+    dispatch_medium_kernel<<<1, kSmallDispatchMax, 0, s>>>(a);
     count_launch();
     return (int)cudaGetLastError();
   }
