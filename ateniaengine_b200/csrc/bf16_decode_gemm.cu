@@ -549,7 +549,9 @@ int launch_dec_one(const GroupedGemmArgs& a, int num_sms, cudaStream_t s) {
   const int n_tiles = (a.N + BN_OUT - 1) / BN_OUT;
   const int active_groups = a.max_rows < a.num_groups ? a.max_rows : a.num_groups;
   const int max_tok_tiles = I8 ? active_groups + a.max_rows / TROWS : active_groups;
-  const bool splitk = a.splitk_ws != nullptr && (I8 || a.max_rows <= DTN) && max_tok_tiles * n_tiles < 4 * num_sms;
+  // (up to eight rounds of whole tiles: below that the idle SMs of the last round cost more than the
+  // reduce pass -- Mixtral shape, 8 tokens, INT8 gate/up product: 448 tiles on 148 SMs are 3.03 rounds)
+  const bool splitk = a.splitk_ws != nullptr && (I8 || a.max_rows <= DTN) && max_tok_tiles * n_tiles < 8 * num_sms;
   grouped_gemm_decode_kernel<MODE, I8><<<dim3(num_sms), dim3(D_THREADS), D_SMEM_BYTES, s>>>(
       a.tmap_a, a.tmap_b0, MODE == kSwiGLU ? a.tmap_b1 : a.tmap_b0, a.group_offsets, a.num_groups, a.N, a.K, a.out,
       a.err, splitk ? 1 : 0, a.splitk_ws, a.scale0, a.scale1, a.tok_scale, a.plane_rows);

@@ -33,31 +33,66 @@ namespace {
 // RMSNorm and its gain as the reference applies them before the MoE block (rms_norm,
 // src/nn/normalization.rs:8-37, then broadcast_mul by gamma, src/moe/full_forward.rs:239-242): f32
 // throughout, the normalised value rounded before the gain multiplies it.  The reference adds the
-// squares in index order; here they are added by a block reduction, which can move inv_rms by an ulp.
-// gamma == nullptr means unit gain.  One block per row.
-__global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ gamma,
-                                                            float eps, float* __restrict__ y, int d) {
-  __shared__ float red[8];
+// squares in index order; here they are added by a block reduction (fixed order), which can move inv_rms
+// by an ulp.  gamma == nullptr means unit gain.  One block of 1024 threads per row; a thread keeps its (up
+// to two) float4 vectors in registers between the two passes, so a row of up to 8192 elements is read once.
+constexpr int kNormThreads = 1024;
+constexpr int kNormVecs = 2;
+
+__global__ void __launch_bounds__(kNormThreads) rmsnorm_rows_kernel(const float* __restrict__ x,
+                                                                     const float* __restrict__ gamma, float eps,
+                                                                     float* __restrict__ y, int d) {
+  __shared__ float red[kNormThreads / 32];
   __shared__ float s_inv;
   const float* row = x + (size_t)blockIdx.x * d;
+  float* yrow = y + (size_t)blockIdx.x * d;
+  // 16-byte vectors when every row starts on a 16-byte boundary
+  const bool vec = (d & 3) == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) == 0;
+  const int nvec = vec ? d / 4 : 0;
+  float4 keep[kNormVecs];
   float ss = 0.f;
-  for (int c = threadIdx.x; c < d; c += blockDim.x) ss = __fmaf_rn(row[c], row[c], ss);
+#pragma unroll
+  for (int j = 0; j < kNormVecs; ++j) {
+    const int v = threadIdx.x + j * kNormThreads;
+    keep[j] = v < nvec ? reinterpret_cast<const float4*>(row)[v] : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+#pragma unroll
+  for (int j = 0; j < kNormVecs; ++j) {
+    ss = __fmaf_rn(keep[j].x, keep[j].x, ss);
+    ss = __fmaf_rn(keep[j].y, keep[j].y, ss);
+    ss = __fmaf_rn(keep[j].z, keep[j].z, ss);
+    ss = __fmaf_rn(keep[j].w, keep[j].w, ss);
+  }
+  // what the registers do not hold: the tail of a long row, or all of a row whose length is not a multiple of 4
+  for (int c = (vec ? 4 * kNormVecs * kNormThreads : 0) + threadIdx.x; c < d; c += kNormThreads)
+    ss = __fmaf_rn(row[c], row[c], ss);
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
   __syncthreads();
-  if (threadIdx.x == 0) {
-    float t = 0.f;
-    for (int i = 0; i < 8; ++i) t += red[i];
-    const float mean_sq = __fdiv_rn(t, (float)d);
-    s_inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean_sq, eps)));
+  if (threadIdx.x < 32) {
+    float t = red[threadIdx.x];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    if (threadIdx.x == 0) {
+      const float mean_sq = __fdiv_rn(t, (float)d);
+      s_inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean_sq, eps)));
+    }
   }
   __syncthreads();
   const float inv = s_inv;
-  for (int c = threadIdx.x; c < d; c += blockDim.x) {
-    const float n = __fmul_rn(row[c], inv);
-    y[(size_t)blockIdx.x * d + c] = gamma ? __fmul_rn(n, gamma[c]) : n;
+  auto norm1 = [&](float xv, int c) {
+    const float n = __fmul_rn(xv, inv);
+    return gamma ? __fmul_rn(n, gamma[c]) : n;
+  };
+#pragma unroll
+  for (int j = 0; j < kNormVecs; ++j) {
+    const int v = threadIdx.x + j * kNormThreads;
+    if (v < nvec)
+      reinterpret_cast<float4*>(yrow)[v] = make_float4(norm1(keep[j].x, 4 * v), norm1(keep[j].y, 4 * v + 1),
+                                                       norm1(keep[j].z, 4 * v + 2), norm1(keep[j].w, 4 * v + 3));
   }
+  for (int c = (vec ? 4 * kNormVecs * kNormThreads : 0) + threadIdx.x; c < d; c += kNormThreads) yrow[c] = norm1(row[c], c);
 }
 
 }  // namespace
@@ -65,7 +100,7 @@ __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const float* __restri
 namespace atenia {
 int launch_rmsnorm_rows(const float* x, const float* gamma, float eps, float* y, int T, int d, cudaStream_t s) {
   if (T <= 0) return ATENIA_OK;
-  rmsnorm_rows_kernel<<<T, 256, 0, s>>>(x, gamma, eps, y, d);
+  rmsnorm_rows_kernel<<<T, kNormThreads, 0, s>>>(x, gamma, eps, y, d);
   count_launch();
   return (int)cudaGetLastError();
 }
