@@ -474,8 +474,9 @@ grouped_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const CUt
 // main kernel's activation and store.  One block per tile; thread (f, y) takes weight row (feature) f and
 // every kReduceTokLanes-th token, so that the dependent loads of one thread are few.
 constexpr int kReduceTokLanes = 8;
+constexpr int kReduceMaxGroups = 256;
 template <int MODE, bool I8>
-__global__ void __launch_bounds__(DROWS * kReduceTokLanes) decode_splitk_reduce_kernel(const int32_t* __restrict__ group_offsets,
+__global__ void __launch_bounds__(DROWS * kReduceTokLanes) decode_splitk_reduce_kernel(const int32_t* __restrict__ group_offsets_g,
                                                                       int num_groups, int N, int K,
                                                                       __nv_bfloat16* __restrict__ out,
                                                                       const float* __restrict__ ws, int num_ctas,
@@ -487,6 +488,15 @@ __global__ void __launch_bounds__(DROWS * kReduceTokLanes) decode_splitk_reduce_
   constexpr int TROWS = I8 ? ITOK : DTN;
   const int num_kb = (K + BKE - 1) / BKE;
   const int n_tiles = (N + BN_OUT - 1) / BN_OUT;
+  // the group offsets once, side by side, into shared memory: the walks below are chains of dependent reads
+  __shared__ int32_t off_s[kReduceMaxGroups + 1];
+  const bool in_smem = num_groups <= kReduceMaxGroups;
+  if (in_smem) {
+    for (int i = threadIdx.y * DROWS + threadIdx.x; i <= num_groups; i += DROWS * kReduceTokLanes)
+      off_s[i] = group_offsets_g[i];
+    __syncthreads();
+  }
+  const int32_t* group_offsets = in_smem ? off_s : group_offsets_g;
   long long total_tiles = 0;
   for (int gi = 0; gi < num_groups; ++gi)
     total_tiles += (long long)((group_offsets[gi + 1] - group_offsets[gi] + TROWS - 1) / TROWS) * n_tiles;
