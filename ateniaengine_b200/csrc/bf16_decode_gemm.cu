@@ -99,6 +99,8 @@ struct DecPieces {
   long long g, g0, g_end;
   TileCoord tc;
   int kb0, nkb, slot;  // slot -1: the piece is a whole tile
+  int tile_id;         // stream-K: index of the piece's tile in the flattened tile list
+  long long span;      // stream-K: k-blocks per CTA
 
   __device__ void init(bool sk, int num_kb_, int n_tiles_, int num_groups_, int bn_out_, const int32_t* off_,
                        int tile_rows_) {
@@ -115,12 +117,14 @@ struct DecPieces {
     tile = blockIdx.x;
     stride = gridDim.x;
     g = g0 = g_end = 0;
+    tile_id = 0;
+    span = 1;
     if (splitk) {
       long long total_tiles = 0;
       for (int gi = 0; gi < num_groups; ++gi)
         total_tiles += (long long)((off[gi + 1] - off[gi] + tile_rows - 1) / tile_rows) * n_tiles;
       const long long total = total_tiles * num_kb;
-      const long long span = (total + gridDim.x - 1) / gridDim.x;
+      span = (total + gridDim.x - 1) / gridDim.x;
       g0 = g = (long long)blockIdx.x * span;
       g_end = g0 + span < total ? g0 + span : total;
     }
@@ -137,6 +141,7 @@ struct DecPieces {
     }
     if (g >= g_end) return false;
     const int t = (int)(g / num_kb);
+    tile_id = t;
     kb0 = (int)(g - (long long)t * num_kb);
     const long long left = g_end - g;
     nkb = (num_kb - kb0) < left ? (num_kb - kb0) : (int)left;
@@ -161,7 +166,7 @@ grouped_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const CUt
                            int num_groups, int N, int K, __nv_bfloat16* __restrict__ out, DeviceError* err,
                            int splitk, float* __restrict__ ws, const float* const* __restrict__ scale0,
                            const float* const* __restrict__ scale1, const float* __restrict__ tok_scale,
-                           int plane_rows) {
+                           int plane_rows, unsigned int* __restrict__ tile_cnt) {
   extern __shared__ uint8_t smem_raw[];
   constexpr int BN_OUT = (MODE == kSwiGLU) ? DROWS : 2 * DROWS;
   constexpr int BKE = I8 ? IBK : BK;      // k elements per k-block
@@ -458,6 +463,58 @@ grouped_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const CUt
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bars->acc_empty[acc]));
       acc ^= 1;
+      // ---- fix-up of a tile that stream-K cut across CTAs, without a second kernel.  Every piece of such
+      // a tile is partial and every CTA's warp with this warp's role (lane quarter, token half) has written
+      // the same portion of its slot.  A counter per (tile, role) counts those warps; the one that arrives
+      // last adds the portions of all pieces in CTA order (fixed, whoever is last) and finishes them as
+      // the whole-tile epilogue would.  Nothing waits for anything: a warp that is not last just goes on.
+      if (tile_cnt != nullptr && it.slot >= 0) {
+        const long long tkb = (long long)it.tile_id * num_kb;
+        const int c0 = (int)(tkb / it.span), c1 = (int)((tkb + num_kb - 1) / it.span);
+        __threadfence();  // this thread's slot stores, before the count
+        __syncwarp();
+        int last = 0;
+        if (lane == 0) {
+          unsigned int* cnt = tile_cnt + (size_t)it.tile_id * 8 + (warp - 4);
+          last = atomicAdd(cnt, 1u) == (unsigned)(c1 - c0) ? 1 : 0;
+          if (last) *cnt = 0u;  // ready for the next launch (and for graph replay)
+        }
+        last = __shfl_sync(0xffffffffu, last, 0);
+        if (last) {
+          __threadfence();  // the other pieces' stores, after the count
+          const int n_lo = tc.n0 + f, n_hi = tc.n0 + DROWS + f;
+          const bool lo_ok = n_lo < N, hi_ok = (MODE == kSwiGLU) ? lo_ok : n_hi < N;
+          float sa = 1.f, sb = 1.f;
+          if (I8) {
+            sa = lo_ok ? scale0[tc.group][n_lo] : 0.f;
+            sb = (MODE == kSwiGLU) ? (lo_ok ? scale1[tc.group][n_lo] : 0.f) : (hi_ok ? scale0[tc.group][n_hi] : 0.f);
+          }
+          __nv_bfloat16* obase = out + (size_t)tc.row0 * N;
+#pragma unroll 1
+          for (int c = half * 16; c < rows; c += 32) {
+            for (int j = 0; j < 16 && c + j < rows; ++j) {
+              float a = 0.f, b = 0.f;
+              for (int cc = c0; cc <= c1; ++cc) {
+                const int sl = (it.tile_id == (int)(((long long)cc * it.span) / num_kb)) ? 0 : 1;
+                const float* p = ws + ((size_t)cc * 2 + sl) * D_SLOT_FLOATS;
+                a += __ldcg(p + (size_t)(c + j) * DROWS + f);
+                b += __ldcg(p + (size_t)(DTN + c + j) * DROWS + f);
+              }
+              if (I8) {
+                const float ts = tok_scale[tc.row0 + c + j];
+                a = a * sa * ts;
+                b = b * sb * ts;
+              }
+              if (MODE == kSwiGLU) {
+                if (lo_ok) obase[(size_t)(c + j) * N + n_lo] = __float2bfloat16(silu_mul(a, b));
+              } else {
+                if (lo_ok) obase[(size_t)(c + j) * N + n_lo] = __float2bfloat16(a);
+                if (hi_ok) obase[(size_t)(c + j) * N + n_hi] = __float2bfloat16(b);
+              }
+            }
+          }
+        }
+      }
     }
   }
 
@@ -545,6 +602,8 @@ __global__ void __launch_bounds__(DROWS * kReduceTokLanes) decode_splitk_reduce_
   }
 }
 
+constexpr int kFixupMaxRows = 32;  // rows (tokens x top-k) up to which the kernel adds split tiles itself
+
 template <int MODE, bool I8>
 int launch_dec_one(const GroupedGemmArgs& a, int num_sms, cudaStream_t s) {
   static bool attr_set[kMaxDevices] = {};
@@ -562,11 +621,17 @@ int launch_dec_one(const GroupedGemmArgs& a, int num_sms, cudaStream_t s) {
   // (up to eight rounds of whole tiles: below that the idle SMs of the last round cost more than the
   // reduce pass -- Mixtral shape, 8 tokens, INT8 gate/up product: 448 tiles on 148 SMs are 3.03 rounds)
   const bool splitk = a.splitk_ws != nullptr && (I8 || a.max_rows <= DTN) && max_tok_tiles * n_tiles < 8 * num_sms;
+  // With tile counters the kernel finishes the split tiles itself.  That saves the second launch, and pays
+  // for calls of a few rows (Mixtral INT8 shape, 1 token: 0.136 against 0.146 ms per layer); from about a
+  // hundred rows on the last warp's serial sum costs what the launch saved, so the reduce kernel stays.
+  const bool fixup = splitk && a.splitk_cnt != nullptr && a.max_rows <= kFixupMaxRows &&
+                     max_tok_tiles * n_tiles <= kSplitKMaxTiles;
   grouped_gemm_decode_kernel<MODE, I8><<<dim3(num_sms), dim3(D_THREADS), D_SMEM_BYTES, s>>>(
       a.tmap_a, a.tmap_b0, MODE == kSwiGLU ? a.tmap_b1 : a.tmap_b0, a.group_offsets, a.num_groups, a.N, a.K, a.out,
-      a.err, splitk ? 1 : 0, a.splitk_ws, a.scale0, a.scale1, a.tok_scale, a.plane_rows);
+      a.err, splitk ? 1 : 0, a.splitk_ws, a.scale0, a.scale1, a.tok_scale, a.plane_rows,
+      fixup ? a.splitk_cnt : nullptr);
   int rc = (int)cudaGetLastError();
-  if (rc || !splitk) return rc;
+  if (rc || !splitk || fixup) return rc;
   decode_splitk_reduce_kernel<MODE, I8><<<dim3(max_tok_tiles * n_tiles), dim3(DROWS, kReduceTokLanes), 0, s>>>(
       a.group_offsets, a.num_groups, a.N, a.K, a.out, a.splitk_ws, num_sms, a.scale0, a.scale1, a.tok_scale);
   count_launch();

@@ -142,6 +142,9 @@ struct GroupedGemmArgs {
   int max_rows;  // upper bound on total rows (sizes nothing; used by the checking kernel's grid)
   int w8;        // B matrices are int8 (tensor maps of bytes), widened to bf16 inside the kernel
   float* splitk_ws;  // W8 tensor-memory kernel: workspace for stream-K partial sums (null: whole tiles only)
+  // stream-K decode kernels: zeroed counters [kSplitKMaxTiles * 8] with which the kernel finishes the split
+  // tiles itself (null: a second kernel adds the pieces)
+  unsigned int* splitk_cnt;
   // integer-MMA decode kernel only: 2^(e - 26) per token row and the row count of one digit plane
   const float* tok_scale;
   int plane_rows;
@@ -186,6 +189,7 @@ int encode_tmap_2d_u8(CUtensorMap* out, const void* base, uint64_t rows, uint64_
 // token matrix (box {64, 128}, 128B swizzle); tmap_b0/b1 are int8 maps with the 64-byte swizzle.
 int launch_grouped_gemm_w8_tmem(const GroupedGemmArgs& a, int num_sms, cudaStream_t s);
 constexpr size_t kW8SplitKSlotFloats = 2 * 128 * 128;  // per CTA: two slots of this size
+constexpr int kSplitKMaxTiles = 8 * 160;               // tiles a stream-K launch can have (eight rounds of the SMs)
 // W8A16 for large groups (w8_gemm_m256.cu): 256-row token tiles, the widened weight tile shared by two
 // M128 MMAs.  Tensor maps as for launch_grouped_gemm_tcgen05 with w8 set.
 int launch_grouped_gemm_w8_m256(const GroupedGemmArgs& a, int num_sms, cudaStream_t s);

@@ -88,6 +88,7 @@ struct AteniaMoeLayer {
   __nv_bfloat16* y_shared = nullptr;  // [max_tokens, d]
   atenia::DeviceError* d_err = nullptr;
   float* splitk_ws = nullptr;  // stream-K partial sums of the decode kernels, 2 slots per SM
+  unsigned int* splitk_cnt = nullptr;  // [kSplitKMaxTiles * 8] arrival counters of split tiles (zero between launches)
   // INT8, integer-MMA decode kernel: weight maps (box {128, 128}, 128B swizzle), digit planes [4][128][K] of
   // the token rows and of the intermediate rows with their row scales, and the planes' tensor maps
   bool w8_i8 = true;

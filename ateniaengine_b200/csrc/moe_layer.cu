@@ -100,6 +100,7 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
     g1.max_rows = max_rows;
     g1.w8 = 1;
     g1.splitk_ws = L->splitk_ws;
+    g1.splitk_cnt = L->splitk_cnt;
     g1.tok_scale = L->dq_ts_x;
     g1.plane_rows = L->i8_rows;
     rc = launch_grouped_gemm_w8_i8_decode(g1, L->num_sms, s);
@@ -151,6 +152,7 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
     g1.max_rows = max_rows;
     g1.w8 = q;
     g1.splitk_ws = L->splitk_ws;
+    g1.splitk_cnt = L->splitk_cnt;
     int rc = m256 ? launch_grouped_gemm_w8_m256(g1, L->num_sms, s)
                   : dec ? launch_grouped_gemm_bf16_decode(g1, L->num_sms, s)
                   : tmem ? launch_grouped_gemm_w8_tmem(g1, L->num_sms, s)
@@ -181,6 +183,7 @@ int run_expert_gemms(AteniaMoeLayer* L, const CUtensorMap& tm_a, const CUtensorM
     g2.max_rows = max_rows;
     g2.w8 = q;
     g2.splitk_ws = L->splitk_ws;
+    g2.splitk_cnt = L->splitk_cnt;
     int rc = m256 ? launch_grouped_gemm_w8_m256(g2, L->num_sms, s)
                   : dec ? launch_grouped_gemm_bf16_decode(g2, L->num_sms, s)
                   : tmem ? launch_grouped_gemm_w8_tmem(g2, L->num_sms, s)
@@ -367,8 +370,17 @@ int atenia_moe_create(const AteniaMoeConfig* cfg, AteniaMoeLayer** out) {
   TRY_ALLOC(L->d_tm_up, (size_t)L->n_groups);
   TRY_ALLOC(L->d_tm_down, (size_t)L->n_groups);
   TRY_ALLOC(L->d_tm_shared, 3);
-  if (L->bf16_decode != 0 || c.weight_dtype == ATENIA_W_INT8_ROW)
+  if (L->bf16_decode != 0 || c.weight_dtype == ATENIA_W_INT8_ROW) {
     TRY_ALLOC(L->splitk_ws, (size_t)L->num_sms * 2 * kW8SplitKSlotFloats);
+    // ATENIA_MOE_SPLITK_FIXUP=0: a second kernel adds the pieces of split tiles (A/B runs)
+    if (!(std::getenv("ATENIA_MOE_SPLITK_FIXUP") && std::atoi(std::getenv("ATENIA_MOE_SPLITK_FIXUP")) == 0)) {
+      TRY_ALLOC(L->splitk_cnt, (size_t)kSplitKMaxTiles * 8);
+      if (cudaMemset(L->splitk_cnt, 0, (size_t)kSplitKMaxTiles * 8 * sizeof(unsigned int)) != cudaSuccess) {
+        atenia_moe_destroy(L);
+        return ATENIA_ERR_STATE;
+      }
+    }
+  }
   {
     const int sk_cap = L->router_variant == 2 ? 1024 : (L->router_variant == -1 ? 128 : 0);
     L->sk_tokens = c.max_tokens < sk_cap ? c.max_tokens : sk_cap;
@@ -475,7 +487,7 @@ int atenia_moe_destroy(AteniaMoeLayer* L) {
                   L->d_tm_down, L->d_tm_shared, L->d_sc_gate, L->d_sc_up, L->d_sc_down, L->d_sc_shared,
                   L->d_p_gate, L->d_p_up, L->d_p_down, L->d_p_shared, L->d_tm_gate_sw, L->d_tm_up_sw,
                   L->d_tm_down_sw, L->d_tm_shared_sw,
-                  L->splitk_ws, L->splitk_ws_shared, L->d_tm_gate_i8, L->d_tm_up_i8, L->d_tm_down_i8, L->dq_x, L->dq_h,
+                  L->splitk_ws, L->splitk_cnt, L->splitk_ws_shared, L->d_tm_gate_i8, L->d_tm_up_i8, L->d_tm_down_i8, L->dq_x, L->dq_h,
                   L->dq_ts_x, L->dq_ts_h, L->d_escore, L->logits_ws, L->recv_x, L->recv_h, L->recv_y, L->d_counts_all,
                   L->d_group_offsets, L->d_peer_recv_x, L->d_peer_y_perm, L->d_dst_base, L->d_src_base,
                   L->d_gemm_offsets, L->d_bar, L->d_sync, L->d_peer_sync, L->d_ep_state, L->sk_part, L->sk_gate, L->sk_counters, L->block_normed};

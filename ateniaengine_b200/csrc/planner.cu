@@ -98,6 +98,7 @@ uint64_t layer_workspace_bytes(const AteniaMoeConfig& c, int world) {
   t.add(groups * tm);
   t.add(3 * tm);
   t.add((uint64_t)148 * 2 * kW8SplitKSlotFloats * 4);  // stream-K partial sums, one pair of slots per SM
+  t.add((uint64_t)kSplitKMaxTiles * 8 * 4);            // arrival counters of split tiles
   if (q) {
     if (Fs) t.add((uint64_t)148 * 2 * kW8SplitKSlotFloats * 4);  // the same for the shared expert's launches
     for (int i = 0; i < 3; ++i) t.add(groups * tm);               // weight maps of the integer-MMA decode kernel
