@@ -14,13 +14,14 @@
 // on B200 it was never faster -- DeepSeek-V2-Lite shape, whole forward: 512 tokens 0.310 vs 0.302 ms,
 // 2048 tokens 0.437 vs 0.426 ms, 8192 tokens 1.103 vs 1.100 ms -- and was removed.)
 #include <cstdlib>
+#include <type_traits>
 
 #include "route_warp.cuh"
 
 namespace atenia {
 namespace {
 
-constexpr int kDW = 8;  // warps per CTA
+constexpr int kDW = 8;  // warps per CTA (16 in the form for small batches)
 
 // D[8x8] += A[8x4] * B[4x8].  Lane l holds A[l / 4][l % 4], B[l % 4][l / 4] and D[l / 4][2 (l % 4) + {0, 1}].
 __device__ __forceinline__ void dmma884(double (&c)[2], double a, double b) {
@@ -29,27 +30,67 @@ __device__ __forceinline__ void dmma884(double (&c)[2], double a, double b) {
                : "d"(a), "d"(b));
 }
 
-// The eight warps of a CTA are arranged NW_N x NW_K (NW_N = min(8, E_T / 8) across the 8-expert tiles,
+template <int I>
+using Int = std::integral_constant<int, I>;
+
+// N consecutive 32-bit words (N = 4 or 8) from a 16-byte aligned address
+template <int N, bool LDG>
+__device__ __forceinline__ void ld_words(uint32_t (&w)[N], const void* p) {
+#pragma unroll
+  for (int i = 0; i < N / 4; ++i) {
+    const uint4 v = LDG ? __ldg(static_cast<const uint4*>(p) + i) : static_cast<const uint4*>(p)[i];
+    w[4 * i] = v.x;
+    w[4 * i + 1] = v.y;
+    w[4 * i + 2] = v.z;
+    w[4 * i + 3] = v.w;
+  }
+}
+template <int N>
+__device__ __forceinline__ void zero_words(uint32_t (&w)[N]) {
+#pragma unroll
+  for (int i = 0; i < N; ++i) w[i] = 0u;
+}
+// element j (a constant after unrolling) of a lane's eight consecutive x values held as raw words
+template <bool XF, int N>
+__device__ __forceinline__ double x_elem(const uint32_t (&w)[N], int j) {
+  if (XF) return (double)__uint_as_float(w[j]);
+  return (double)((j & 1) ? bf16hi(w[j >> 1]) : bf16lo(w[j >> 1]));
+}
+
+// The WARPS warps of a CTA are arranged NW_N x NW_K (NW_N = (E_T / 8) / NTW across the 8-expert tiles,
 // the rest across k): a warp owns NTW 8-expert tiles and the k-range [kslice KW, (kslice+1) KW)
 // of the dot products of the CTA's 8 MT tokens.  The summation index of an m8n8k4 product is free to be
 // permuted as long as A and B agree, so lane (r, c) = (lane / 4, lane % 4) loads EIGHT consecutive k of
 // token row r (16 bytes of bf16) and of expert row r of each of its tiles (32 bytes of f32) at
-// k = base + 8 c, and step j of eight uses element j of every lane's vectors: the four lanes of a row
+// k = base + 8 c, and step j of eight uses element j of every lane's values: the four lanes of a row
 // cover 32 consecutive k, global loads are whole sectors (the warps of one k-slice read the same token
-// vectors: the first brings them into L1).  The vectors of the next 32 k are in flight while the current
-// ones are multiplied.  Partial sums of the k-slices are added through shared memory in slice order
-// (fixed), then the bias, the rounding to f32 and the routing of each token by one warp (route_one_warp).
-template <int E_T, int MT>
-__global__ void __launch_bounds__(kDW * 32) router_dmma_direct_kernel(RouterArgs a, int kw) {
+// values: the first brings them into L1).  The raw words of the next 32 k are in flight, in a second set
+// of registers, while the current ones are converted and multiplied.
+//
+// A value is converted to f64 each time a warp uses it: a warp that owns NTW tiles and MT token tiles
+// converts MT + NTW values per MT * NTW products, and the conversion unit is as scarce as the f64 tensor
+// pipe.  With one tile per warp (NTW = 1, MT = 2: 1.5 conversions per product) the conversions set the
+// pace; two tiles per warp (1.0) leave the tensor pipe as the busier unit.  Measured on B200, routing
+// phase (router + dispatch + gather) of a DeepSeek-V2-Lite-shaped layer, 8192 tokens: 0.195 ms with one
+// tile per warp, 0.171 ms with two; four tiles per warp (0.75 conversions per product) measured 0.163 ms
+// alone but need 42 KB of shared memory for the partial sums, which no longer fits on an SM beside a CTA
+// of the expert GEMMs (the shared expert runs there at the same time).  m16n8k4 products instead of
+// m8n8k4 changed nothing.
+//
+// Partial sums of the k-slices are added through shared memory in slice order (fixed), then the bias, the
+// rounding to f32 and the routing of each token by one warp (route_one_warp).
+template <int E_T, int MT, int NTW, bool XF, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32) router_dmma_direct_kernel(RouterArgs a, int kw) {
   constexpr int NT = E_T / 8;
-  constexpr int NW_N = NT < kDW ? NT : kDW;
-  constexpr int NW_K = kDW / NW_N;
-  constexpr int NTW = NT / NW_N;
+  constexpr int NW_N = NT / NTW;
+  constexpr int NW_K = WARPS / NW_N;
+  static_assert(NW_N >= 1 && NW_N * NTW == NT && NW_N * NW_K == WARPS, "warp arrangement");
   constexpr int kTok = 8 * MT;
-  __shared__ double part_s[kDW][MT][NTW][32][2];
+  constexpr int XW = XF ? 8 : 4;  // 32-bit words of a lane's eight x values
+  __shared__ double part_s[WARPS][MT][NTW][32][2];
   __shared__ double gpart_s[NW_K][kTok];
   __shared__ float lg_s[kTok][E_T];
-  __shared__ double exps_s[kDW][E_T];
+  __shared__ double exps_s[WARPS][E_T];
   __shared__ int32_t idx_s[kTok][kMaxK];
   __shared__ float w_s[kTok][kMaxK];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -69,85 +110,61 @@ __global__ void __launch_bounds__(kDW * 32) router_dmma_direct_kernel(RouterArgs
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt) gacc[mt] = 0.0;
 
-  // raw vectors of one step: x as bf16 uses xq[mt][0] only, as f32 both; W always two float4
-  uint4 xq[MT][2];
-  float4 wq[NTW][2];
-  float4 gq[2];
-  auto fetch = [&](int kb) {
+  // raw words of two steps
+  uint32_t xq[2][MT][XW];
+  uint32_t wq[2][NTW][8];
+  uint32_t gq[2][8];
+  auto fetch = [&](auto BUF, int kb) {
+    constexpr int b = decltype(BUF)::value;
     const int k = kb + c * 8;
-    const bool k_ok = k < k_end;  // d and kw are multiples of 8: a vector is all in or all out
+    const bool k_ok = k < k_end;  // d and kw are multiples of 8: a lane's values are all in or all out
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt) {
       const int tg = t0 + mt * 8 + r;
-      xq[mt][0] = make_uint4(0, 0, 0, 0);
-      xq[mt][1] = make_uint4(0, 0, 0, 0);
+      zero_words(xq[b][mt]);
       if (k_ok && tg < a.T) {
-        if (a.x_is_f32) {
-          const uint4* p = reinterpret_cast<const uint4*>(static_cast<const float*>(a.x) + (size_t)tg * d + k);
-          xq[mt][0] = p[0];
-          xq[mt][1] = p[1];
-        } else {
-          xq[mt][0] = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(a.x) + (size_t)tg * d + k);
-        }
+        if (XF) ld_words<XW, false>(xq[b][mt], static_cast<const float*>(a.x) + (size_t)tg * d + k);
+        else ld_words<XW, false>(xq[b][mt], static_cast<const __nv_bfloat16*>(a.x) + (size_t)tg * d + k);
       }
     }
 #pragma unroll
     for (int j = 0; j < NTW; ++j) {
       const int e = (ngrp * NTW + j) * 8 + r;
-      wq[j][0] = wq[j][1] = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (k_ok && e < E) {
-        const float4* p = reinterpret_cast<const float4*>(a.w_router + (size_t)e * d + k);
-        wq[j][0] = __ldg(p);
-        wq[j][1] = __ldg(p + 1);
-      }
+      zero_words(wq[b][j]);
+      if (k_ok && e < E) ld_words<8, true>(wq[b][j], a.w_router + (size_t)e * d + k);
     }
-    gq[0] = gq[1] = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (do_gate && k_ok) {
-      const float4* p = reinterpret_cast<const float4*>(a.gate_vec + k);
-      gq[0] = __ldg(p);
-      gq[1] = __ldg(p + 1);
+    zero_words(gq[b]);
+    if (do_gate && k_ok) ld_words<8, true>(gq[b], a.gate_vec + k);
+  };
+  auto multiply = [&](auto BUF) {
+    constexpr int b = decltype(BUF)::value;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      double xv[MT];
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) xv[mt] = x_elem<XF>(xq[b][mt], j);
+      if (do_gate) {
+        const double g = (double)__uint_as_float(gq[b][j]);
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) gacc[mt] = fma(g, xv[mt], gacc[mt]);
+      }
+#pragma unroll
+      for (int jt = 0; jt < NTW; ++jt) {
+        const double wv = (double)__uint_as_float(wq[b][jt][j]);
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) dmma884(acc[mt][jt], xv[mt], wv);
+      }
     }
   };
-  if (k_begin < k_end) fetch(k_begin);
-  for (int kb = k_begin; kb < k_end; kb += 32) {
-    double xd[MT][8], wd[NTW][8];
-#pragma unroll
-    for (int mt = 0; mt < MT; ++mt) {
-      if (a.x_is_f32) {
-        const uint32_t u[8] = {xq[mt][0].x, xq[mt][0].y, xq[mt][0].z, xq[mt][0].w,
-                               xq[mt][1].x, xq[mt][1].y, xq[mt][1].z, xq[mt][1].w};
-#pragma unroll
-        for (int j = 0; j < 8; ++j) xd[mt][j] = (double)__uint_as_float(u[j]);
-      } else {
-        const uint32_t u[4] = {xq[mt][0].x, xq[mt][0].y, xq[mt][0].z, xq[mt][0].w};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          xd[mt][2 * j] = (double)bf16lo(u[j]);
-          xd[mt][2 * j + 1] = (double)bf16hi(u[j]);
-        }
-      }
+  if (k_begin < k_end) fetch(Int<0>{}, k_begin);
+  for (int kb = k_begin; kb < k_end; kb += 64) {
+    const bool more = kb + 32 < k_end;
+    if (more) fetch(Int<1>{}, kb + 32);
+    multiply(Int<0>{});
+    if (more) {
+      if (kb + 64 < k_end) fetch(Int<0>{}, kb + 64);
+      multiply(Int<1>{});
     }
-#pragma unroll
-    for (int jt = 0; jt < NTW; ++jt) {
-      const float f[8] = {wq[jt][0].x, wq[jt][0].y, wq[jt][0].z, wq[jt][0].w,
-                          wq[jt][1].x, wq[jt][1].y, wq[jt][1].z, wq[jt][1].w};
-#pragma unroll
-      for (int j = 0; j < 8; ++j) wd[jt][j] = (double)f[j];
-    }
-    if (do_gate) {
-      const float g[8] = {gq[0].x, gq[0].y, gq[0].z, gq[0].w, gq[1].x, gq[1].y, gq[1].z, gq[1].w};
-#pragma unroll
-      for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-        for (int j = 0; j < 8; ++j) gacc[mt] = fma((double)g[j], xd[mt][j], gacc[mt]);
-    }
-    if (kb + 32 < k_end) fetch(kb + 32);
-#pragma unroll
-    for (int j = 0; j < 8; ++j)
-#pragma unroll
-      for (int jt = 0; jt < NTW; ++jt)
-#pragma unroll
-        for (int mt = 0; mt < MT; ++mt) dmma884(acc[mt][jt], xd[mt][j], wd[jt][j]);
   }
   // partial sums of this warp's k-range: C[row r][columns 2c, 2c + 1] of every tile it owns
 #pragma unroll
@@ -191,7 +208,7 @@ __global__ void __launch_bounds__(kDW * 32) router_dmma_direct_kernel(RouterArgs
     if (tg < a.T) a.gate_scale[tg] = (float)(1.0 / (1.0 + exp(-v)));
   }
   __syncthreads();
-  for (int t = warp; t < kTok; t += kDW) {
+  for (int t = warp; t < kTok; t += WARPS) {
     const int tg = t0 + t;
     if (tg >= a.T) continue;
     int rc = route_one_warp<(E_T + 31) / 32>(lg_s[t], E, a.k, a.renormalize, lane, idx_s[t], w_s[t], exps_s[warp]);
@@ -210,18 +227,30 @@ __global__ void __launch_bounds__(kDW * 32) router_dmma_direct_kernel(RouterArgs
   }
 }
 
+template <int E_T, int MT, int NTW, int WARPS>
+int launch_form(const RouterArgs& a, cudaStream_t s) {
+  constexpr int NW_K = WARPS / ((E_T / 8) / NTW);
+  constexpr int kTok = 8 * MT;
+  // k-range of a k-slice: d over the slices, rounded up to whole 32-k steps
+  const int kw = ((a.d + NW_K - 1) / NW_K + 31) / 32 * 32;
+  const int grid = (a.T + kTok - 1) / kTok;
+  if (a.x_is_f32) router_dmma_direct_kernel<E_T, MT, NTW, true, WARPS><<<grid, WARPS * 32, 0, s>>>(a, kw);
+  else router_dmma_direct_kernel<E_T, MT, NTW, false, WARPS><<<grid, WARPS * 32, 0, s>>>(a, kw);
+  return (int)cudaGetLastError();
+}
+
+// Two forms.  A batch whose 8-token CTAs fit the SMs in one round is bound by the latency of its
+// dependent load -> multiply steps, not by a pipe: 16 warps per CTA cut the k-range, and with it the
+// number of steps, of every warp in half (DeepSeek-V2-Lite shape, 1024 tokens: router 41 -> 22 us).
+// Larger batches take 16 tokens and 8 warps per CTA, 2 to 3 CTAs per SM.
+constexpr int kSmallBatchCtas = 148;
+
 template <int E_T>
 int launch_direct(const RouterArgs& a, cudaStream_t s) {
   constexpr int NT = E_T / 8;
-  constexpr int NW_K = kDW / (NT < kDW ? NT : kDW);
-  // k-range of a k-slice: d over the slices, rounded up to whole 32-k steps
-  const int kw = ((a.d + NW_K - 1) / NW_K + 31) / 32 * 32;
-  if (a.T >= 8192 || (E_T > 16 && a.T >= 2048)) {
-    router_dmma_direct_kernel<E_T, 2><<<(a.T + 15) / 16, kDW * 32, 0, s>>>(a, kw);
-  } else {
-    router_dmma_direct_kernel<E_T, 1><<<(a.T + 7) / 8, kDW * 32, 0, s>>>(a, kw);
-  }
-  return (int)cudaGetLastError();
+  constexpr int NTW = NT < 2 ? NT : 2;
+  if ((a.T + 7) / 8 <= kSmallBatchCtas) return launch_form<E_T, 1, NTW, 2 * kDW>(a, s);
+  return launch_form<E_T, 2, NTW, kDW>(a, s);
 }
 
 }  // namespace
