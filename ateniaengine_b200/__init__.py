@@ -20,6 +20,7 @@ from .moe import (  # noqa: F401
     set_numeric_policy,
     clear_numeric_policy_override,
     auto_expert_cache_capacity,
+    plan_exec_pieces,
     plan_residency,
     workspace_bytes,
 )

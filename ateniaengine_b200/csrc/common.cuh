@@ -1,5 +1,6 @@
 // Shared declarations of the MoE library's translation units (sm_100a only).
 #pragma once
+#include <vector>
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -218,5 +219,18 @@ int launch_quantize_digits(const DigitSource& src, const int32_t* n_rows_dev, in
                            int8_t* planes, float* tok_scale, cudaStream_t s);
 // bf16 weights, CTA pairs (tcgen05 cta_group::2): 256-row tiles, each CTA stages half of the weight tile
 int launch_grouped_gemm_2cta(const GroupedGemmArgs& a, int num_sms, cudaStream_t s);
+
+// Sub-batch sizes for the host-buffer operator (planner.cu): n tokens in pieces of at most cap tokens,
+// chosen with a cost model of the copies and the forward; one piece means "do not overlap".  `fit`
+// (optional) carries what the operator measured in its earlier calls: forward(T) = a + b T milliseconds
+// and the copy time of a token.
+struct ExecFit {
+  double a_ms = 0.0, b_ms = 0.0, copy_token_ms = 0.0;
+  bool valid = false;
+};
+std::vector<uint64_t> plan_exec_pieces(const AteniaMoeConfig& c, uint64_t n, uint64_t cap, const ExecFit* fit);
+double model_exec_ms(const AteniaMoeConfig& c, const std::vector<uint64_t>& pieces, const ExecFit* fit);
+void update_exec_fit(const AteniaMoeConfig& c, const uint64_t* tokens, const float* forward_ms, int n_pieces,
+                     uint64_t copy_tokens, float copy_ms, ExecFit* fit);
 
 }  // namespace atenia

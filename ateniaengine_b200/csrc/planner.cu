@@ -16,6 +16,7 @@
 // the switch (same strings, same precedence: in-process override, then the environment read once,
 // then Certified) so that a host can ask whether the library serves the active policy.
 #include <algorithm>
+#include <vector>
 #include <atomic>
 #include <cctype>
 #include <cstdlib>
@@ -125,6 +126,186 @@ uint64_t layer_workspace_bytes(const AteniaMoeConfig& c, int world) {
     t.add((groups + 1) * 4);
   }
   return t.total;
+}
+
+
+// ---- sub-batch schedule of the host-buffer operator -------------------------------------------------
+// execute_real_moe_layer copies a batch in, runs it and copies the result out.  Cut into pieces, the copy
+// in of piece i+1 and the copy out of piece i-1 overlap the forward of piece i (two staging buffers each
+// way); what stays exposed is the first copy in and the last copy out, and every piece streams the expert
+// weights again.  Which cut is best depends on whether the layer is slower than the PCIe link or faster,
+// so it is chosen with a model: a forward of T tokens costs the touched expert weights at the HBM rate
+// plus T times the flops of a token at the rate the grouped GEMMs sustain, a copy costs its bytes at the
+// rate of a pinned host buffer.  Measured on B200 (Mixtral shape, 4096 tokens, host f32 buffers): one pass
+// 4.68 ms, two halves 3.99 - 4.05 ms, quarters 4.32 ms, pieces of 768 / 2560 / 768 tokens 3.51 ms; a
+// DeepSeek-V2-Lite-shaped layer at 8192 tokens is slower over PCIe than on the GPU and wants equal pieces
+// (halves 2.55 ms, the three-piece cut above 2.82 ms).
+constexpr double kModelHbmBytesPerMs = 6.5e9;     // streamed weights
+constexpr double kModelFlopsPerMsBf16 = 1.5e12;   // grouped bf16 GEMMs beside the weight stream (1.7e12 fits a Mixtral-shaped layer, 1.3e12 a DeepSeek-shaped one)
+constexpr double kModelFlopsPerMsInt8 = 1.2e12;   // W8A16: the widening kernels
+constexpr double kModelPcieBytesPerMs = 53.0e6;   // pinned host memory, either direction
+constexpr double kModelPieceOverheadMs = 0.06;    // routing, dispatch, combine, launch gaps of one forward
+constexpr uint64_t kModelMinPiece = 256;          // smaller pieces: the line forward(T) = a + b T no longer holds
+
+struct ExecModel {
+  double expert_ms, shared_ms, token_ms, copy_token_ms;
+  uint64_t E, k;
+  bool fitted;         // forward(T) = fit_a + fit_b T from the operator's own timings
+  double fit_a, fit_b;
+};
+
+ExecModel exec_model(const AteniaMoeConfig& c) {
+  const double d = c.d_model, F = c.d_ff, Fs = c.shared_d_ff;
+  const bool q = c.weight_dtype == ATENIA_W_INT8_ROW;
+  const double wb = q ? 1.0 : 2.0;
+  ExecModel m;
+  m.expert_ms = 3.0 * F * d * wb / kModelHbmBytesPerMs;
+  m.shared_ms = 3.0 * Fs * d * wb / kModelHbmBytesPerMs;
+  m.token_ms = (c.experts_per_token * 6.0 * d * F + 6.0 * d * Fs) / (q ? kModelFlopsPerMsInt8 : kModelFlopsPerMsBf16);
+  m.copy_token_ms = d * 4.0 / kModelPcieBytesPerMs;
+  m.E = (uint64_t)c.num_experts;
+  m.k = (uint64_t)c.experts_per_token;
+  m.fitted = false;
+  m.fit_a = m.fit_b = 0.0;
+  return m;
+}
+
+double model_forward_ms(const ExecModel& m, uint64_t T) {
+  if (m.fitted) return m.fit_a + m.fit_b * (double)T;
+  const uint64_t touched = std::min<uint64_t>(m.E, T * m.k);
+  return kModelPieceOverheadMs + (double)touched * m.expert_ms + m.shared_ms + (double)T * m.token_ms;
+}
+
+// End of the last copy out when `pieces` run through the two-buffer pipeline of execute_pipelined.
+double model_pipeline_ms(const ExecModel& m, const std::vector<uint64_t>& pieces) {
+  double h = 0.0, c = 0.0, o = 0.0;
+  std::vector<double> fwd_done, out_done;
+  for (size_t i = 0; i < pieces.size(); ++i) {
+    const double copy = (double)pieces[i] * m.copy_token_ms;
+    double hs = h;
+    if (i >= 2) hs = std::max(hs, fwd_done[i - 2]);  // the input buffer is free again
+    h = hs + copy;
+    double cs = std::max(c, h);
+    if (i >= 2) cs = std::max(cs, out_done[i - 2]);  // the output buffer is free again
+    c = cs + model_forward_ms(m, pieces[i]);
+    fwd_done.push_back(c);
+    o = std::max(o, c) + copy;
+    out_done.push_back(o);
+  }
+  return o;
+}
+
+// Pieces of a batch of n tokens, none above cap: p pieces, the two end ones of `end` tokens and the rest
+// equal, over p = 1 .. 8 and end in steps of n / 32 (multiples of 64 tokens).  One piece means no overlap.
+std::vector<uint64_t> plan_exec_pieces(const AteniaMoeConfig& c, uint64_t n, uint64_t cap, const ExecFit* fit) {
+  std::vector<uint64_t> best;
+  if (n == 0 || cap == 0) return best;
+  ExecModel m = exec_model(c);
+  if (fit && fit->valid) {
+    m.fitted = true;
+    m.fit_a = fit->a_ms;
+    m.fit_b = fit->b_ms;
+    m.copy_token_ms = fit->copy_token_ms;
+  }
+  double best_ms = 0.0;
+  auto consider = [&](const std::vector<uint64_t>& pieces) {
+    uint64_t sum = 0;
+    for (uint64_t v : pieces) {
+      if (v == 0 || v > cap) return;
+      if (pieces.size() > 1 && v < kModelMinPiece) return;
+      sum += v;
+    }
+    if (sum != n) return;
+    const double ms = model_pipeline_ms(m, pieces);
+    if (best.empty() || ms < best_ms * 0.99) {  // (more pieces must earn at least a percent)
+      best = pieces;
+      best_ms = ms;
+    }
+  };
+  const uint64_t p_min = (n + cap - 1) / cap;
+  for (uint64_t p = p_min; p <= p_min + 7; ++p) {
+    if (p == 1) {
+      consider({n});
+      continue;
+    }
+    if (n < kModelMinPiece * p) break;
+    const uint64_t step = std::max<uint64_t>(64, n / 32 / 64 * 64);
+    if (p == 2) {
+      consider({(n + 1) / 2, n / 2});
+      continue;
+    }
+    for (uint64_t end = step; 2 * end < n; end += step) {
+      const uint64_t mid_total = n - 2 * end, mids = p - 2;
+      if (mid_total < mids) break;
+      std::vector<uint64_t> pieces;
+      pieces.push_back(end);
+      for (uint64_t j = 0; j < mids; ++j) pieces.push_back(mid_total / mids + (j < mid_total % mids ? 1 : 0));
+      pieces.push_back(end);
+      consider(pieces);
+    }
+  }
+  return best;
+}
+
+// Modelled duration of a call cut into `pieces` (the operator compares its current cut with a new one).
+double model_exec_ms(const AteniaMoeConfig& c, const std::vector<uint64_t>& pieces, const ExecFit* fit) {
+  ExecModel m = exec_model(c);
+  if (fit && fit->valid) {
+    m.fitted = true;
+    m.fit_a = fit->a_ms;
+    m.fit_b = fit->b_ms;
+    m.copy_token_ms = fit->copy_token_ms;
+  }
+  return model_pipeline_ms(m, pieces);
+}
+
+// The operator's own timings of one pipelined call refine the model: piece i of tokens[i] tokens took
+// forward_ms[i] on the device, and copying copy_tokens tokens took copy_ms.  Two piece sizes give the line
+// forward(T) = a + b T; one size scales the analytical model to it.  Half of each new value is taken.
+void update_exec_fit(const AteniaMoeConfig& c, const uint64_t* tokens, const float* forward_ms, int n_pieces,
+                     uint64_t copy_tokens, float copy_ms, ExecFit* fit) {
+  if (!fit || n_pieces <= 0) return;
+  double st = 0, sm = 0, stt = 0, stm = 0;
+  int used = 0;
+  for (int i = 0; i < n_pieces; ++i) {
+    if (!(forward_ms[i] > 0.f) || tokens[i] == 0) continue;
+    const double t = (double)tokens[i], ms = forward_ms[i];
+    st += t;
+    sm += ms;
+    stt += t * t;
+    stm += t * ms;
+    ++used;
+  }
+  if (used == 0) return;
+  const ExecModel m = exec_model(c);
+  double a, b;
+  const double den = used * stt - st * st;
+  if (used >= 2 && den > 1e-6 * stt) {
+    b = (used * stm - st * sm) / den;
+    a = (sm - b * st) / used;
+  } else {
+    a = b = -1.0;
+  }
+  if (!(a > 0.0) || !(b > 0.0)) {
+    // one size (or a degenerate line): keep the model's shape, match its level
+    const double mean_t = st / used;
+    const double pred = model_forward_ms(m, (uint64_t)mean_t);
+    const double scale = (sm / used) / pred;
+    b = m.token_ms * scale;
+    a = (pred - m.token_ms * mean_t) * scale;
+  }
+  double cp = fit->valid ? fit->copy_token_ms : m.copy_token_ms;
+  if (copy_tokens > 0 && copy_ms > 0.f) cp = (double)copy_ms / (double)copy_tokens;
+  if (fit->valid) {
+    fit->a_ms = 0.5 * (fit->a_ms + a);
+    fit->b_ms = 0.5 * (fit->b_ms + b);
+    fit->copy_token_ms = 0.5 * (fit->copy_token_ms + cp);
+  } else {
+    fit->a_ms = a;
+    fit->b_ms = b;
+    fit->copy_token_ms = cp;
+    fit->valid = true;
+  }
 }
 
 }  // namespace atenia
@@ -268,6 +449,15 @@ int atenia_numeric_policy_gate(void) {
   // silently; a host that said nothing chose this library by calling it.
   if (!atenia_numeric_policy_is_explicit()) return ATENIA_OK;
   return atenia_numeric_policy_ffn_uses_cuda(atenia_numeric_policy()) ? ATENIA_OK : ATENIA_ERR_POLICY;
+}
+
+int atenia_moe_plan_exec_pieces(const AteniaMoeConfig* cfg, uint64_t n_tokens, uint64_t* pieces_out, int max_pieces) {
+  if (!cfg || !pieces_out) return ATENIA_ERR_NULL;
+  if (max_pieces <= 0 || cfg->max_tokens <= 0 || cfg->d_model <= 0 || cfg->num_experts <= 0) return ATENIA_ERR_SHAPE;
+  const std::vector<uint64_t> pieces = plan_exec_pieces(*cfg, n_tokens, (uint64_t)cfg->max_tokens, nullptr);
+  if ((int)pieces.size() > max_pieces) return ATENIA_ERR_CAPACITY;
+  for (size_t i = 0; i < pieces.size(); ++i) pieces_out[i] = pieces[i];
+  return (int)pieces.size();
 }
 
 }  // extern "C"

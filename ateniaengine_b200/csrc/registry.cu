@@ -24,6 +24,14 @@ struct Registered {
   cudaStream_t s_h2d = nullptr, s_d2h = nullptr;
   cudaEvent_t ev_in_ready[2] = {}, ev_in_free[2] = {}, ev_out_ready[2] = {}, ev_out_free[2] = {};
   bool pipe_ready = false;
+  // timings of the pipelined calls (forward of each piece, one copy in) that refine the sub-batch plan
+  static constexpr int kMaxTimed = 8;
+  cudaEvent_t ev_f0[kMaxTimed] = {}, ev_f1[kMaxTimed] = {}, ev_c0 = nullptr, ev_c1 = nullptr;
+  ExecFit fit;
+  // the cut of the last pipelined call: kept for a batch of the same size unless a new one is modelled
+  // at least 3 % faster (timing noise must not make the cut flip from call to call)
+  size_t last_n = 0;
+  std::vector<uint64_t> last_pieces;
 };
 
 std::mutex g_mu;
@@ -76,6 +84,12 @@ void release(Registered& r) {
     if (r.ev_out_ready[i]) cudaEventDestroy(r.ev_out_ready[i]);
     if (r.ev_out_free[i]) cudaEventDestroy(r.ev_out_free[i]);
   }
+  for (int i = 0; i < Registered::kMaxTimed; ++i) {
+    if (r.ev_f0[i]) cudaEventDestroy(r.ev_f0[i]);
+    if (r.ev_f1[i]) cudaEventDestroy(r.ev_f1[i]);
+  }
+  if (r.ev_c0) cudaEventDestroy(r.ev_c0);
+  if (r.ev_c1) cudaEventDestroy(r.ev_c1);
   r = Registered();
 }
 
@@ -83,10 +97,10 @@ void release(Registered& r) {
 // sub-batch i+1 and the device->host copy of sub-batch i-1 with the forward of sub-batch i (two staging
 // buffers each way, two copy streams, events).  The forwards themselves stay in order on one stream: the
 // layer has one workspace.  Host buffers must be pinned for the copies to be asynchronous.
-// By default a batch of 2048 tokens or more runs as two halves (smaller sub-batches lose more in the
-// expert GEMMs, which re-stream the weights per sub-batch, than the overlap gains: measured on B200 with
-// a Mixtral-shaped layer at 4096 tokens, one pass 4.68 ms, halves 4.05 ms, quarters 4.32 ms, eighths 5.9 ms).
-// ATENIA_MOE_EXEC_CHUNK=<tokens> sets the sub-batch size, 0 turns the overlap off.
+// The cut comes from plan_exec_pieces (planner.cu): a layer that is slower than the PCIe link gets a short
+// piece at each end and the bulk in the middle, a layer that is faster gets equal pieces, a small batch
+// stays whole.  The first call plans with the analytical model; every pipelined call times the forward of
+// each of its pieces and one copy in, and the next call plans with the line fitted to those timings.  ATENIA_MOE_EXEC_CHUNK=<tokens> pins one sub-batch size for all, 0 turns the overlap off.
 long exec_chunk_setting() {
   static const long v = [] {
     const char* e = std::getenv("ATENIA_MOE_EXEC_CHUNK");
@@ -97,17 +111,26 @@ long exec_chunk_setting() {
   return v;
 }
 
-size_t exec_chunk_for(size_t n, size_t cap) {
+// sub-batch sizes of one call (fewer than two: no overlap, one pass per max_tokens)
+std::vector<size_t> exec_schedule(Registered& r, size_t n, size_t cap) {
+  const AteniaMoeConfig& cfg = r.layer->cfg;
+  std::vector<size_t> out;
   const long set = exec_chunk_setting();
-  size_t chunk;
-  if (set >= 0) {
-    chunk = (size_t)set;
-  } else {
-    if (n < 2048) return 0;
-    chunk = (n + 1) / 2;
-    if (chunk < 1024) chunk = 1024;
+  if (set == 0) return out;
+  if (set < 0) {
+    std::vector<uint64_t> plan = plan_exec_pieces(cfg, (uint64_t)n, (uint64_t)cap, &r.fit);
+    if (r.last_n == n && !r.last_pieces.empty() && plan != r.last_pieces &&
+        model_exec_ms(cfg, plan, &r.fit) > 0.97 * model_exec_ms(cfg, r.last_pieces, &r.fit))
+      plan = r.last_pieces;
+    r.last_n = n;
+    r.last_pieces = plan;
+    for (uint64_t v : plan) out.push_back((size_t)v);
+    return out;
   }
-  return chunk > cap ? cap : chunk;
+  const size_t chunk = (size_t)set > cap ? cap : (size_t)set;
+  if (n <= chunk) return out;
+  for (size_t t0 = 0; t0 < n; t0 += chunk) out.push_back(n - t0 < chunk ? n - t0 : chunk);
+  return out;
 }
 
 int ensure_pipe(Registered& r) {
@@ -123,31 +146,47 @@ int ensure_pipe(Registered& r) {
     ATENIA_CUDA_TRY(cudaEventCreateWithFlags(&r.ev_out_ready[i], cudaEventDisableTiming));
     ATENIA_CUDA_TRY(cudaEventCreateWithFlags(&r.ev_out_free[i], cudaEventDisableTiming));
   }
+  for (int i = 0; i < Registered::kMaxTimed; ++i) {
+    ATENIA_CUDA_TRY(cudaEventCreate(&r.ev_f0[i]));
+    ATENIA_CUDA_TRY(cudaEventCreate(&r.ev_f1[i]));
+  }
+  ATENIA_CUDA_TRY(cudaEventCreate(&r.ev_c0));
+  ATENIA_CUDA_TRY(cudaEventCreate(&r.ev_c1));
   r.pipe_ready = true;
   return ATENIA_OK;
 }
 
-int execute_pipelined(Registered& r, const float* input, float* output, size_t n, size_t chunk, int convention) {
+int execute_pipelined(Registered& r, const float* input, float* output, const std::vector<size_t>& pieces,
+                      int convention) {
   int rc = ensure_pipe(r);
   if (rc) return rc;
   const size_t d = (size_t)r.layer->cfg.d_model;
   void* din[2] = {r.d_in, r.d_in2};
   void* dout[2] = {r.d_out, r.d_out2};
-  size_t i = 0;
-  for (size_t t0 = 0; t0 < n; t0 += chunk, ++i) {
-    const size_t tn = n - t0 < chunk ? n - t0 : chunk;
+  // the copy in that is timed: the largest piece's (it overlaps a forward, as most copies of a call do)
+  size_t timed_copy = 0;
+  for (size_t i = 1; i < pieces.size(); ++i)
+    if (pieces[i] > pieces[timed_copy]) timed_copy = i;
+  size_t t0 = 0;
+  for (size_t i = 0; i < pieces.size(); t0 += pieces[i], ++i) {
+    const size_t tn = pieces[i];
     const size_t bytes = tn * d * sizeof(float);
     const int b = (int)(i & 1);
     // host -> device, once the forward that last read this input buffer is done
     if (i >= 2) ATENIA_CUDA_TRY(cudaStreamWaitEvent(r.s_h2d, r.ev_in_free[b], 0));
+    const bool time_copy = i == timed_copy;
+    if (time_copy) ATENIA_CUDA_TRY(cudaEventRecord(r.ev_c0, r.s_h2d));
     ATENIA_CUDA_TRY(cudaMemcpyAsync(din[b], input + t0 * d, bytes, cudaMemcpyHostToDevice, r.s_h2d));
+    if (time_copy) ATENIA_CUDA_TRY(cudaEventRecord(r.ev_c1, r.s_h2d));
     ATENIA_CUDA_TRY(cudaEventRecord(r.ev_in_ready[b], r.s_h2d));
     // forward, once its input has landed and the copy that last read this output buffer is done
     ATENIA_CUDA_TRY(cudaStreamWaitEvent(r.stream, r.ev_in_ready[b], 0));
     if (i >= 2) ATENIA_CUDA_TRY(cudaStreamWaitEvent(r.stream, r.ev_out_free[b], 0));
+    if (i < (size_t)Registered::kMaxTimed) ATENIA_CUDA_TRY(cudaEventRecord(r.ev_f0[i], r.stream));
     rc = atenia_moe_forward_with(r.layer, din[b], ATENIA_IO_F32, (int)tn, dout[b], ATENIA_IO_F32, nullptr, r.stream,
                                  convention);
     if (rc) break;
+    if (i < (size_t)Registered::kMaxTimed) ATENIA_CUDA_TRY(cudaEventRecord(r.ev_f1[i], r.stream));
     ATENIA_CUDA_TRY(cudaEventRecord(r.ev_in_free[b], r.stream));
     ATENIA_CUDA_TRY(cudaEventRecord(r.ev_out_ready[b], r.stream));
     // device -> host
@@ -164,6 +203,19 @@ int execute_pipelined(Registered& r, const float* input, float* output, size_t n
   if (e1 != cudaSuccess) return (int)e1;
   if (e2 != cudaSuccess) return (int)e2;
   if (e3 != cudaSuccess) return (int)e3;
+  {
+    // what this call took refines the plan of the next one
+    uint64_t tok[Registered::kMaxTimed];
+    float ms[Registered::kMaxTimed];
+    int np = 0;
+    for (size_t i = 0; i < pieces.size() && i < (size_t)Registered::kMaxTimed; ++i, ++np) {
+      tok[np] = pieces[i];
+      if (cudaEventElapsedTime(&ms[np], r.ev_f0[i], r.ev_f1[i]) != cudaSuccess) ms[np] = 0.f;
+    }
+    float cms = 0.f;
+    if (cudaEventElapsedTime(&cms, r.ev_c0, r.ev_c1) != cudaSuccess) cms = 0.f;
+    update_exec_fit(r.layer->cfg, tok, ms, np, pieces[timed_copy], cms, &r.fit);
+  }
   return atenia_moe_check(r.layer, r.stream);
 }
 
@@ -310,8 +362,8 @@ int atenia_execute_real_moe_layer_with(int64_t layer_id, const float* input, siz
   ATENIA_CUDA_TRY(cudaSetDevice(r.layer->device));
   const size_t n = len / d, cap = (size_t)r.layer->cfg.max_tokens;
   {
-    const size_t chunk = exec_chunk_for(n, cap);
-    if (chunk > 0 && n > chunk) return execute_pipelined(r, input, output, n, chunk, convention);
+    const std::vector<size_t> pieces = exec_schedule(r, n, cap);
+    if (pieces.size() > 1) return execute_pipelined(r, input, output, pieces, convention);
   }
   for (size_t t0 = 0; t0 < n; t0 += cap) {
     const size_t tn = n - t0 < cap ? n - t0 : cap;

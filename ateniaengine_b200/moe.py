@@ -478,6 +478,17 @@ def workspace_bytes(config, shared_d_ff=0, int8=False, max_tokens=4096, ep_world
     return int(_lib.lib().atenia_moe_workspace_bytes(C.byref(cfg)))
 
 
+def plan_exec_pieces(config, n_tokens, shared_d_ff=0, int8=False, max_tokens=4096):
+    """Sub-batch sizes execute_real_moe_layer uses for a batch of `n_tokens` (their sum is n_tokens;
+    one piece: the batch runs whole, without copy / compute overlap)."""
+    cfg = _plan_config(config, shared_d_ff, int8, max_tokens)
+    buf = (C.c_uint64 * 64)()
+    n = _lib.lib().atenia_moe_plan_exec_pieces(C.byref(cfg), int(n_tokens), buf, 64)
+    if n < 0:
+        raise _lib.AteniaError(n, "atenia_moe_plan_exec_pieces")
+    return [int(buf[i]) for i in range(n)]
+
+
 def execute_real_moe_layer_ptr(layer_id, in_ptr, n_floats, out_ptr):
     """Same call on raw host pointers (e.g. pinned buffers); returns the status."""
     return _lib.lib().atenia_execute_real_moe_layer(int(layer_id), C.c_void_p(in_ptr), n_floats,

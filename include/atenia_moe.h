@@ -379,6 +379,16 @@ ATENIA_API uint64_t atenia_auto_expert_cache_capacity(uint64_t budget_bytes, uin
                                                       uint64_t per_expert_bytes, uint64_t num_experts);
 /* Device bytes atenia_moe_create allocates for this configuration (0 for an invalid one). */
 ATENIA_API uint64_t atenia_moe_workspace_bytes(const AteniaMoeConfig* cfg);
+/* Sub-batches of atenia_execute_real_moe_layer for a batch of n_tokens (no counterpart in the
+ * reference, whose operator computes where the data already is: src/moe/graph_op.rs:327-350).  The
+ * operator here copies host buffers over PCIe and cuts a large batch into pieces so that the copies
+ * of neighbouring pieces overlap a piece's forward; the cut is chosen with a cost model (weights
+ * streamed per piece, flops per token, PCIe bytes per token): short end pieces around a large middle
+ * one when the layer is slower than the link, equal pieces when it is faster, one piece (no overlap)
+ * for a small batch.  Writes the piece sizes (their sum is n_tokens, none above cfg->max_tokens) and
+ * returns their number; ATENIA_ERR_CAPACITY if max_pieces is too small.  Host arithmetic only. */
+ATENIA_API int atenia_moe_plan_exec_pieces(const AteniaMoeConfig* cfg, uint64_t n_tokens, uint64_t* pieces_out,
+                                           int max_pieces);
 
 /* ---- layer stack ------------------------------------------------------------------------------
  * RealMoeStack::forward (src/moe/stack.rs:197-210): x <- layer_l(x) for l = 0..n-1, every layer with
