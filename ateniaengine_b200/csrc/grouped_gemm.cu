@@ -73,11 +73,13 @@ struct __align__(8) SharedBarriers {
 template <int MODE, bool W8>
 __global__ void __launch_bounds__(W8 ? W8_NUM_THREADS : NUM_THREADS, 1)
 grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const CUtensorMap* __restrict__ tmap_b0,
-                            const CUtensorMap* __restrict__ tmap_b1, const int32_t* __restrict__ group_offsets,
+                            const CUtensorMap* __restrict__ tmap_b1, const int32_t* __restrict__ group_offsets_g,
                             int num_groups, int N, int K, __nv_bfloat16* __restrict__ out,
                             const float* const* __restrict__ scale0, const float* const* __restrict__ scale1,
                             DeviceError* err) {
   extern __shared__ uint8_t smem_raw[];
+  __shared__ int32_t goff_s[kMaxGroupsShared + 1];
+  const int32_t* group_offsets = stage_group_offsets(group_offsets_g, num_groups, goff_s);
   constexpr int BN_OUT = (MODE == kSwiGLU) ? BN / 2 : BN;
   // 1024-byte alignment is required by the 128B swizzle atoms.
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;

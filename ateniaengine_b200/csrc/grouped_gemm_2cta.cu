@@ -93,9 +93,11 @@ __device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
 template <int MODE>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS2, 1)
 grouped_gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const CUtensorMap* __restrict__ tmap_b0,
-                         const CUtensorMap* __restrict__ tmap_b1, const int32_t* __restrict__ group_offsets,
+                         const CUtensorMap* __restrict__ tmap_b1, const int32_t* __restrict__ group_offsets_g,
                          int num_groups, int N, int K, __nv_bfloat16* __restrict__ out, DeviceError* err) {
   extern __shared__ uint8_t smem_raw[];
+  __shared__ int32_t goff_s[kMaxGroupsShared + 1];
+  const int32_t* group_offsets = stage_group_offsets(group_offsets_g, num_groups, goff_s);
   constexpr int BN_OUT = (MODE == kSwiGLU) ? BN2 / 2 : BN2;
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));

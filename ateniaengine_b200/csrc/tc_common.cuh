@@ -145,6 +145,18 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
 }
 
 // ---- tile walk ---------------------------------------------------------------------------------
+// The producer, the MMA issuer and the epilogue warps of a CTA each walk the group offsets at every tile
+// change (a persistent CTA's next tile is a grid width further on: with 60 experts of 20 tiles that is
+// seven groups, two dependent loads each).  From global memory that walk costs microseconds per tile and
+// the ring runs dry meanwhile, so kernels with many groups copy the offsets into shared memory first.
+constexpr int kMaxGroupsShared = 256;
+__device__ __forceinline__ const int32_t* stage_group_offsets(const int32_t* __restrict__ off_global, int num_groups,
+                                                              int32_t* off_shared) {
+  if (num_groups > kMaxGroupsShared) return off_global;
+  for (int i = threadIdx.x; i <= num_groups; i += blockDim.x) off_shared[i] = off_global[i];
+  return off_shared;  // (valid after the caller's next block-wide barrier)
+}
+
 struct TileCursor {
   int group;      // current group
   int base;       // first tile index of the current group
