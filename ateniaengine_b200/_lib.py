@@ -74,7 +74,7 @@ EXPORTS = [
     "atenia_numeric_policy_is_explicit", "atenia_set_numeric_policy", "atenia_clear_numeric_policy_override",
     "atenia_numeric_policy_ffn_uses_f32", "atenia_numeric_policy_ffn_uses_cuda", "atenia_numeric_policy_gate",
     "atenia_moe_block_forward", "atenia_moe_stack_set_norm", "atenia_moe_last_phase_ms", "atenia_moe_last_recv_rows", "atenia_moe_plan_residency", "atenia_auto_expert_cache_capacity", "atenia_moe_workspace_bytes",
-    "atenia_moe_plan_exec_pieces",
+    "atenia_moe_plan_exec_pieces", "atenia_moe_plan_exec_pieces_measured",
 ]
 
 _lib = None
@@ -172,6 +172,8 @@ def lib():
         l.atenia_moe_workspace_bytes.argtypes = [C.POINTER(MoeConfig)]
         l.atenia_moe_workspace_bytes.restype = C.c_uint64
         l.atenia_moe_plan_exec_pieces.argtypes = [C.POINTER(MoeConfig), C.c_uint64, C.POINTER(C.c_uint64), C.c_int]
+        l.atenia_moe_plan_exec_pieces_measured.argtypes = [C.POINTER(MoeConfig), C.c_uint64, C.c_double, C.c_double,
+                                                            C.c_double, C.POINTER(C.c_uint64), C.c_int]
         _lib = l
     return _lib
 

@@ -452,9 +452,21 @@ int atenia_numeric_policy_gate(void) {
 }
 
 int atenia_moe_plan_exec_pieces(const AteniaMoeConfig* cfg, uint64_t n_tokens, uint64_t* pieces_out, int max_pieces) {
+  return atenia_moe_plan_exec_pieces_measured(cfg, n_tokens, 0.0, 0.0, 0.0, pieces_out, max_pieces);
+}
+
+int atenia_moe_plan_exec_pieces_measured(const AteniaMoeConfig* cfg, uint64_t n_tokens, double forward_base_ms,
+                                         double forward_token_ms, double copy_token_ms, uint64_t* pieces_out,
+                                         int max_pieces) {
   if (!cfg || !pieces_out) return ATENIA_ERR_NULL;
   if (max_pieces <= 0 || cfg->max_tokens <= 0 || cfg->d_model <= 0 || cfg->num_experts <= 0) return ATENIA_ERR_SHAPE;
-  const std::vector<uint64_t> pieces = plan_exec_pieces(*cfg, n_tokens, (uint64_t)cfg->max_tokens, nullptr);
+  if (forward_base_ms < 0.0 || forward_token_ms < 0.0 || copy_token_ms < 0.0) return ATENIA_ERR_SHAPE;
+  ExecFit fit;
+  fit.a_ms = forward_base_ms;
+  fit.b_ms = forward_token_ms;
+  fit.copy_token_ms = copy_token_ms;
+  fit.valid = forward_token_ms > 0.0 && copy_token_ms > 0.0;  // all zero: the analytical model
+  const std::vector<uint64_t> pieces = plan_exec_pieces(*cfg, n_tokens, (uint64_t)cfg->max_tokens, &fit);
   if ((int)pieces.size() > max_pieces) return ATENIA_ERR_CAPACITY;
   for (size_t i = 0; i < pieces.size(); ++i) pieces_out[i] = pieces[i];
   return (int)pieces.size();

@@ -478,14 +478,17 @@ def workspace_bytes(config, shared_d_ff=0, int8=False, max_tokens=4096, ep_world
     return int(_lib.lib().atenia_moe_workspace_bytes(C.byref(cfg)))
 
 
-def plan_exec_pieces(config, n_tokens, shared_d_ff=0, int8=False, max_tokens=4096):
+def plan_exec_pieces(config, n_tokens, shared_d_ff=0, int8=False, max_tokens=4096, measured=None):
     """Sub-batch sizes execute_real_moe_layer uses for a batch of `n_tokens` (their sum is n_tokens;
-    one piece: the batch runs whole, without copy / compute overlap)."""
+    one piece: the batch runs whole, without copy / compute overlap).  `measured` =
+    (forward_base_ms, forward_token_ms, copy_token_ms) plans from timings instead of the model."""
     cfg = _plan_config(config, shared_d_ff, int8, max_tokens)
     buf = (C.c_uint64 * 64)()
-    n = _lib.lib().atenia_moe_plan_exec_pieces(C.byref(cfg), int(n_tokens), buf, 64)
+    a, b, c = measured if measured is not None else (0.0, 0.0, 0.0)
+    n = _lib.lib().atenia_moe_plan_exec_pieces_measured(C.byref(cfg), int(n_tokens), float(a), float(b), float(c),
+                                                        buf, 64)
     if n < 0:
-        raise _lib.AteniaError(n, "atenia_moe_plan_exec_pieces")
+        raise _lib.AteniaError(n, "atenia_moe_plan_exec_pieces_measured")
     return [int(buf[i]) for i in range(n)]
 
 

@@ -389,6 +389,14 @@ ATENIA_API uint64_t atenia_moe_workspace_bytes(const AteniaMoeConfig* cfg);
  * returns their number; ATENIA_ERR_CAPACITY if max_pieces is too small.  Host arithmetic only. */
 ATENIA_API int atenia_moe_plan_exec_pieces(const AteniaMoeConfig* cfg, uint64_t n_tokens, uint64_t* pieces_out,
                                            int max_pieces);
+/* The same plan from measured figures instead of the analytical model (no counterpart in the reference):
+ * a forward of T tokens takes forward_base_ms + forward_token_ms * T and a token's copy over the link
+ * copy_token_ms, each way.  This is what the operator does after its first pipelined call, with the
+ * figures it timed itself; exported so that a host can plan with its own measurements and so that the
+ * choice can be tested without a GPU.  All three zero: the analytical model. */
+ATENIA_API int atenia_moe_plan_exec_pieces_measured(const AteniaMoeConfig* cfg, uint64_t n_tokens,
+                                                    double forward_base_ms, double forward_token_ms,
+                                                    double copy_token_ms, uint64_t* pieces_out, int max_pieces);
 
 /* ---- layer stack ------------------------------------------------------------------------------
  * RealMoeStack::forward (src/moe/stack.rs:197-210): x <- layer_l(x) for l = 0..n-1, every layer with

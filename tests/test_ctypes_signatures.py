@@ -22,14 +22,15 @@ def _kind(decl):
     if "*" in decl:
         return "ptr"
     base = decl.replace("const ", "").split()[0]
-    return {"int": "i32", "int32_t": "i32", "int64_t": "i64", "size_t": "u64", "float": "f32", "uint64_t": "u64"}[base]  # LP64: size_t is 64 bits
+    return {"int": "i32", "int32_t": "i32", "int64_t": "i64", "size_t": "u64", "float": "f32", "uint64_t": "u64",
+            "double": "f64"}[base]  # LP64: size_t is 64 bits
 
 
 def _ckind(t):
     if t in (C.c_void_p, C.c_char_p) or (isinstance(t, type) and issubclass(t, C._Pointer)):
         return "ptr"
     return {C.c_int: "i32", C.c_int32: "i32", C.c_int64: "i64", C.c_size_t: "u64", C.c_float: "f32",
-            C.c_uint64: "u64"}[t]
+            C.c_uint64: "u64", C.c_double: "f64"}[t]
 
 
 def test_argtypes_follow_the_header():

@@ -49,3 +49,26 @@ def test_argument_checks():
     assert lib.atenia_moe_plan_exec_pieces(C.byref(c), 4096, buf, 0) == -2    # ATENIA_ERR_SHAPE
     assert lib.atenia_moe_plan_exec_pieces(C.byref(c), 4096, buf, 2) == -3    # three pieces do not fit two slots
     assert lib.atenia_moe_plan_exec_pieces(C.byref(c), 0, buf, 2) == 0
+
+
+def test_plan_follows_measured_figures():
+    """The cut from timings: the forward of an end piece should last about as long as the copy of the
+    middle one when the layer is slower than the link; a link slower than the layer wants similar pieces;
+    a forward that is nearly all fixed cost is not cut at all."""
+    from ateniaengine_b200 import plan_exec_pieces
+    s, cfg = _cfg("mixtral")
+    # Mixtral shape as measured on B200: forward(T) = 0.49 + 0.00041 T ms, 0.00031 ms per token and copy
+    p = plan_exec_pieces(cfg, 4096, max_tokens=4096, measured=(0.49, 0.00041, 0.00031))
+    assert len(p) == 3 and p[0] == p[2] and 512 <= p[0] <= 1024
+    end_forward = 0.49 + 0.00041 * p[0]
+    middle_copy = 0.00031 * p[1]
+    assert abs(end_forward - middle_copy) < 0.15
+    # the same layer behind a link ten times slower: copies dominate, pieces of similar size
+    q = plan_exec_pieces(cfg, 4096, max_tokens=4096, measured=(0.49, 0.00041, 0.0031))
+    assert len(q) >= 3 and max(q) <= 3 * min(q)
+    # a forward that costs 5 ms whatever the batch: every extra piece costs more than its overlap gains
+    assert plan_exec_pieces(cfg, 4096, max_tokens=4096, measured=(5.0, 0.00001, 0.00031)) == [4096]
+    # negative figures are refused
+    from ateniaengine_b200 import _lib
+    with pytest.raises(_lib.AteniaError):
+        plan_exec_pieces(cfg, 4096, max_tokens=4096, measured=(-1.0, 0.1, 0.1))
